@@ -1,0 +1,366 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 backend hot path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload lut|attention|matmul|decoder]
+  python bench.py --impl reference ...      # the reference CPU path (oracle restatement) on host cores
+
+One JSON line on stdout (rank 0). Timed with CUDA events on the stream the kernels are
+launched on; inputs are larger than L2 or rotated over buffers larger than L2.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower().startswith("active")})
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# Workloads. Each returns a dict: run_device(step), run_host(step) (end-to-end through the
+# host-workspace C-ABI call), units per step, algorithmic bytes (or flops) per launch of the
+# dominant kernel, and a cpu_baseline callable.
+# ------------------------------------------------------------------------------------------
+
+def bf16_rne(x):
+    from oracle import oracle as orc
+    return orc.f32_to_bf16_rne(x)
+
+
+def synth_c1(n, seed):
+    """Config 1 input law: 99% N(0, 3^2) rounded to bf16, 1% special bit patterns."""
+    rng = np.random.default_rng(seed)
+    bits = bf16_rne((rng.standard_normal(n, dtype=np.float32) * np.float32(3.0)))
+    special = np.array([0x0000, 0x8000, 0x7F80, 0xFF80, 0x7FC0, 0xFFC0] + list(range(1, 0x80)) +
+                       list(range(0x8001, 0x8080)), dtype=np.uint16)
+    k = n // 100
+    bits[rng.choice(n, size=k, replace=False)] = rng.choice(special, size=k)
+    return bits
+
+
+def workload_lut(be, torch, rank, args):
+    import hologram_b200 as hb
+    from hologram_b200 import kernel_call as kc
+    n = 16_777_216
+    pairs = 8  # 8 x (32 MiB in + 32 MiB out) = 512 MiB rotated: every step misses the 126 MB L2
+    host_in = torch.from_numpy(synth_c1(n, 0xC1 + rank).view(np.int16)).pin_memory()
+    host_out = torch.empty(n, dtype=torch.int16).pin_memory()
+    dev_in = [host_in.cuda() for _ in range(pairs)]
+    dev_out = [torch.empty(n, dtype=torch.int16, device="cuda") for _ in range(pairs)]
+    ws = hb.DeviceWorkspace(be, 2 * pairs)
+    for i in range(pairs):
+        ws.bind(2 * i, dev_in[i].data_ptr(), n * 2)
+        ws.bind(2 * i + 1, dev_out[i].data_ptr(), n * 2)
+    calls = [kc.KernelCall.Gelu(kc.UnaryCall(kc.rb(2 * i), kc.rb(2 * i + 1), n, 16, kc.DTYPE_BF16)) for i in range(pairs)]
+    hws = hb.HostWorkspace([host_in.numpy(), host_out.numpy()])
+    hcall = kc.KernelCall.Gelu(kc.UnaryCall(kc.rb(0), kc.rb(1), n, 16, kc.DTYPE_BF16))
+
+    def cpu_baseline():
+        from oracle import oracle as orc
+        x = host_in.numpy().view(np.uint16)
+        fast = orc.fast_lib()
+        orc.unary_lut(kc.LUT_GELU, kc.DTYPE_BF16, x[:1024], which=fast)
+        best = 1e9
+        t_end = time.time() + 10
+        while time.time() < t_end:
+            t0 = time.perf_counter()
+            orc.unary_lut(kc.LUT_GELU, kc.DTYPE_BF16, x, which=fast)
+            best = min(best, time.perf_counter() - t0)
+        return {"value": n * 4 / best / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                "sample": "full 16,777,216-element tensor, best of ~10 s of serial passes (the reference loop is serial)"}
+
+    def ref_step():
+        from oracle import oracle as orc
+        orc.unary_lut(kc.LUT_GELU, kc.DTYPE_BF16, host_in.numpy().view(np.uint16), which=orc.fast_lib(), mt=True)
+
+    return {
+        "name": "lut_gelu_bf16_16777216",
+        "metric": "lut_activation_GBps", "unit": "GB/s", "dtype": "u16",
+        "run_device": lambda step: be.dispatch(calls[step % pairs], ws),
+        "run_host": lambda step: be.dispatch(hcall, hws),
+        "ref_step": ref_step, "ref_fraction": 1.0,
+        "units_per_step": n * 4 / 1e9,  # GB of algorithmic traffic per step
+        "launches_per_step": 1,
+        "roofline": {"bound": "hbm", "bytes_per_launch": n * 4},
+        "h2d": n * 2, "d2h": n * 2,
+        "cpu_baseline": cpu_baseline,
+        "config": {"workload": "config[0]: bf16 GELU via the 65536-entry u16 LUT, 16,777,216 elements, 99% N(0,9) + 1% specials",
+                   "l2": "8 rotated buffer pairs (512 MiB) > 126 MB L2"},
+        "keep": (dev_in, dev_out, host_in, host_out),
+    }
+
+
+def workload_attention(be, torch, rank, args, world=1):
+    import hologram_b200 as hb
+    from hologram_b200 import kernel_call as kc
+    b, h, kv, past, d = 32, 32 // world, 8 // world, 8192, 128   # sharded by KV head
+    rng = np.random.default_rng(0xC4 + rank)
+    rows = b * kv * past
+
+    def quant_on_device(nrows, seed):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        src = torch.randn(nrows * d, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        codes = torch.empty(nrows * d, dtype=torch.int8, device="cuda")
+        scales = torch.empty(nrows, dtype=torch.float32, device="cuda")
+        w = hb.DeviceWorkspace(be, 3)
+        w.bind(0, src.data_ptr(), nrows * d * 2)
+        w.bind(1, codes.data_ptr(), nrows * d)
+        w.bind(2, scales.data_ptr(), nrows * 4)
+        be.dispatch(kc.KernelCall.QuantizeRowsI8(kc.QuantizeRowsI8Call(kc.rb(0), kc.rb(1), kc.rb(2), nrows, d, kc.DTYPE_BF16)), w)
+        be.synchronize()
+        return codes, scales
+
+    kp, kps = quant_on_device(rows, 1 + rank)
+    vp, vps = quant_on_device(rows, 2 + rank)
+    kn, kns = quant_on_device(b * kv, 3 + rank)
+    vn, vns = quant_on_device(b * kv, 4 + rank)
+    q = torch.from_numpy(bf16_rne(rng.standard_normal(b * h * d).astype(np.float32)).view(np.int16)).cuda()
+    vl = torch.tensor([past], dtype=torch.int32, device="cuda")
+    out = torch.empty(b * h * d, dtype=torch.int16, device="cuda")
+    tensors = [q, kp, kps, vp, vps, kn, kns, vn, vns, vl, out]
+    ws = hb.DeviceWorkspace(be, 11)
+    for i, t in enumerate(tensors):
+        ws.bind(i, t.data_ptr(), t.numel() * t.element_size())
+    call = kc.KernelCall.DecodeAttentionValidQ8(kc.DecodeAttentionValidQ8Call(*[kc.rb(i) for i in range(11)], b, h, kv, 1, past, 1, d, 0, kc.DTYPE_BF16))
+    host = [t.cpu().pin_memory() for t in tensors]
+    hws = hb.HostWorkspace([t.numpy() for t in host])
+    algo = 2 * rows * d + 2 * rows * 4 + 2 * b * h * d * 2 + 2 * b * kv * (d + 4)
+
+    def cpu_args(nb):
+        f = lambda t, n: t.numpy()[:n]
+        hq = host[0].numpy().view(np.uint16)[:nb * h * d]
+        return (hq, kc.DTYPE_BF16, f(host[1], nb * kv * past * d), f(host[2], nb * kv * past), f(host[3], nb * kv * past * d),
+                f(host[4], nb * kv * past), f(host[5], nb * kv * d), f(host[6], nb * kv), f(host[7], nb * kv * d), f(host[8], nb * kv),
+                past, nb, h, kv, 1, past, 1, d, 0)
+
+    def cpu_baseline():
+        from oracle import oracle as orc
+        nb = 2
+        a = cpu_args(nb)
+        t0 = time.perf_counter()
+        orc.decode_attention_valid_q8(*a, which=orc.fast_lib())
+        dt = time.perf_counter() - t0
+        return {"value": algo * nb / b / dt / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+                "sample": f"{nb} of {b} sequences (dequantize + f32 attention, rows split over all host threads)"}
+
+    def ref_step():
+        from oracle import oracle as orc
+        orc.decode_attention_valid_q8(*cpu_args(2), which=orc.fast_lib())
+
+    return {
+        "name": f"decode_attention_q8_b{b}_h{h}_kv{kv}_d{d}_L{past}",
+        "metric": "q8kv_decode_attention_GBps", "unit": "GB/s", "dtype": "i8/f32",
+        "run_device": lambda step: be.dispatch(call, ws),
+        "run_host": lambda step: be.dispatch(call, hws),
+        "ref_step": ref_step, "ref_fraction": 2 / b,
+        "units_per_step": algo / 1e9,
+        "launches_per_step": 2,
+        "roofline": {"bound": "hbm", "bytes_per_launch": algo},
+        "h2d": sum(t.numel() * t.element_size() for t in tensors[:-1]), "d2h": out.numel() * 2,
+        "cpu_baseline": cpu_baseline,
+        "config": {"workload": f"config[3]: single-token decode attention, batch {b}, {h} q / {kv} kv heads, head_dim {d}, {past} cached positions, int8 KV",
+                   "l2": "KV codes (512 MiB per GPU at N=1) exceed the 126 MB L2"},
+        "keep": (tensors, host),
+    }
+
+
+WORKLOADS = {"lut": workload_lut, "attention": workload_attention}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=os.environ.get("HOLO_BENCH_WORKLOAD", "lut"))
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        return main_reference(args, rank, world)
+
+    import torch
+    import torch.distributed as dist
+    import hologram_b200 as hb
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    be = hb.B200Backend(local_rank)
+    stream = torch.cuda.current_stream()
+    be.set_stream(stream.cuda_stream)
+
+    fn = WORKLOADS[args.workload]
+    wl = fn(be, torch, rank, args, world) if args.workload == "attention" else fn(be, torch, rank, args)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(run, steps, warmup):
+        for s in range(warmup):
+            run(s)
+        barrier()
+        l0 = be.launch_count
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for s in range(steps):
+            run(warmup + s)
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches = be.launch_count - l0
+        if world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, launches
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, launches = timed(wl["run_device"], args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(3, min(args.steps, 10))
+        ems, _ = timed(wl["run_host"], e2e_steps, 2)
+        e2e = {"value": wl["units_per_step"] * world * e2e_steps / (ems / 1e3), "unit": wl["unit"],
+               "h2d_bytes_per_step": wl["h2d"], "d2h_bytes_per_step": wl["d2h"], "steps": e2e_steps}
+
+    if rank == 0:
+        peaks = measured_peaks()
+        per_step_ms = ms / args.steps
+        value = wl["units_per_step"] * world * args.steps / (ms / 1e3)
+        achieved = wl["roofline"]["bytes_per_launch"] / (per_step_ms / 1e3) / 1e9
+        line = {
+            "metric": wl["metric"], "value": value, "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": per_step_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic (seeded)",
+            "config": dict(wl["config"], name=wl["name"]),
+            "clocks": clocks, "gpu_launches": launches,
+            "roofline": {"bound": wl["roofline"]["bound"], "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                         "peak_source": peaks["source"], "frac_of_8TBps_nominal": achieved / 8000.0},
+            "e2e": e2e,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = wl["cpu_baseline"]()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main_reference(args, rank, world):
+    """The reference's CPU implementation of the path (the C restatement, all host threads),
+    timed on a bounded sample per step. Rank 0 only."""
+    if rank != 0:
+        return
+    import types
+    torch = None
+    try:
+        import torch as _t
+        torch = _t
+    except Exception:
+        pass
+    # host-only construction of the same inputs
+    from hologram_b200 import kernel_call as kc
+    from oracle import oracle as orc
+    wlname = args.workload
+    if wlname == "lut":
+        n = 16_777_216
+        x = synth_c1(n, 0xC1)
+        units = n * 4 / 1e9
+        step = lambda: orc.unary_lut(kc.LUT_GELU, kc.DTYPE_BF16, x, which=orc.fast_lib(), mt=True)
+        frac, metric, unit, dtype = 1.0, "lut_activation_GBps", "GB/s", "u16"
+        cfg = {"workload": "config[0]: bf16 GELU via the 65536-entry u16 LUT, 16,777,216 elements, 99% N(0,9) + 1% specials"}
+        sample = "full tensor per step, table lookups partitioned over all host threads"
+    else:
+        b, h, kv, past, d, nb = 32, 32, 8, 8192, 128, 2
+        rng = np.random.default_rng(0xC4)
+        q = bf16_rne(rng.standard_normal(nb * h * d).astype(np.float32))
+        mk = lambda rows: orc.quantize_rows_i8(bf16_rne(rng.standard_normal(rows * d).astype(np.float32)), kc.DTYPE_BF16, rows, d)
+        kp, vp, kn, vn = mk(nb * kv * past), mk(nb * kv * past), mk(nb * kv), mk(nb * kv)
+        algo = 2 * b * kv * past * (d + 4) + 2 * b * h * d * 2 + 2 * b * kv * (d + 4)
+        units = algo / 1e9
+        step = lambda: orc.decode_attention_valid_q8(q, kc.DTYPE_BF16, kp[0], kp[1], vp[0], vp[1], kn[0], kn[1], vn[0], vn[1],
+                                                     past, nb, h, kv, 1, past, 1, d, 0, which=orc.fast_lib())
+        frac, metric, unit, dtype = nb / b, "q8kv_decode_attention_GBps", "GB/s", "i8/f32"
+        cfg = {"workload": f"config[3]: single-token decode attention, batch {b}, {h} q / {kv} kv heads, head_dim {d}, {past} cached positions, int8 KV"}
+        sample = f"{nb} of {b} sequences per step"
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = units * frac * args.steps / dt
+    cores = os.cpu_count()
+    print(json.dumps({
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3 / frac, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": dtype, "data": "synthetic (seeded)", "config": cfg,
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,777 @@
+// C ABI entry points: context, device workspace, and the `Backend::dispatch` replacement.
+// Validation mirrors the reference CPU kernels: geometry and slot extents are checked before
+// anything is enqueued, failures are loud (negative status + thread-local message), nothing
+// is silently truncated or zero-filled (crates/hologram-compute/src/error.rs, cpu/lut.rs:84-92).
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.h"
+
+// ---- thread-local error state (hologram-ffi src/lib.rs:48-92 convention) --------------------
+static thread_local char g_err[512] = "";
+static thread_local uint32_t g_err_slot = HOLO_NO_SLOT;
+
+int32_t holo_fail(int32_t code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return code;
+}
+int32_t holo_fail_slot(uint32_t slot, const char* what) {
+    g_err_slot = slot;
+    snprintf(g_err, sizeof g_err, "buffer slot out of range: %u (%s)", slot, what);
+    return HOLO_ERR_SLOT_OUT_OF_RANGE;
+}
+int32_t holo_cuda_fail(cudaError_t e, const char* where) {
+    snprintf(g_err, sizeof g_err, "dispatch failed: CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), where);
+    return HOLO_ERR_DISPATCH;
+}
+
+extern "C" const char* holo_b200_last_error(void) { return g_err; }
+extern "C" uint32_t holo_b200_last_error_slot(void) { return g_err_slot; }
+extern "C" const char* holo_b200_version(void) { return "hologram-b200 0.1 (sm_100a)"; }
+
+// ---- context --------------------------------------------------------------------------------
+extern "C" int32_t holo_b200_ctx_create(int32_t device, holo_b200_ctx** out) {
+    if (!out) return holo_fail(HOLO_ERR_INIT, "backend init failed: null out pointer");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return holo_fail(HOLO_ERR_INIT, "backend init failed: no CUDA device (%s)", cudaGetErrorString(e));
+    if (device < 0 || device >= count) return holo_fail(HOLO_ERR_INIT, "backend init failed: device %d of %d", device, count);
+    if (cudaSetDevice(device) != cudaSuccess) return holo_fail(HOLO_ERR_INIT, "backend init failed: cudaSetDevice");
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess)
+        return holo_fail(HOLO_ERR_INIT, "backend init failed: cudaGetDeviceProperties");
+    if (prop.major != 10)
+        return holo_fail(HOLO_ERR_INIT, "backend init failed: device is sm_%d%d, this library is built for sm_100a only",
+                         prop.major, prop.minor);
+    holo_b200_ctx* ctx = new holo_b200_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->smem_optin = (int)prop.sharedMemPerBlockOptin;
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete ctx;
+        return holo_fail(HOLO_ERR_INIT, "backend init failed: cudaStreamCreate");
+    }
+    ctx->own_stream = true;
+    if (cudaMalloc(&ctx->dev_status, 256) != cudaSuccess || cudaMemset(ctx->dev_status, 0, 256) != cudaSuccess) {
+        cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return holo_fail(HOLO_ERR_INIT, "backend init failed: status word allocation");
+    }
+    *out = ctx;
+    return HOLO_OK;
+}
+
+extern "C" void holo_b200_ctx_destroy(holo_b200_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    holo_tp_destroy(ctx);
+    for (auto& row : ctx->lut)
+        for (auto& t : row)
+            if (t) cudaFree(t);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->stage) cudaFree(ctx->stage);
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+extern "C" void* holo_b200_ctx_stream(holo_b200_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+extern "C" int32_t holo_b200_ctx_set_stream(holo_b200_ctx* ctx, void* stream) {
+    if (!ctx) return holo_fail(HOLO_ERR_INIT, "null context");
+    HOLO_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+    ctx->stream = (cudaStream_t)stream;
+    ctx->own_stream = false;
+    return HOLO_OK;
+}
+
+// Asynchronous device-side failures (an out-of-range gather index, a bounded wait that gave
+// up) are recorded in a status word and surface at the next synchronising call.
+static int32_t check_dev_status(holo_b200_ctx* ctx) {
+    uint32_t st = 0;
+    HOLO_CUDA(cudaMemcpyAsync(&st, ctx->dev_status, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    HOLO_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (st == 0) return HOLO_OK;
+    cudaMemsetAsync(ctx->dev_status, 0, 4, ctx->stream);
+    if (st & 1u) return holo_fail_slot(HOLO_NO_SLOT, "gather index outside [−axis_dim, axis_dim)");
+    return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: a device-side bounded wait gave up (status 0x%x)", st);
+}
+
+extern "C" int32_t holo_b200_ctx_synchronize(holo_b200_ctx* ctx) {
+    if (!ctx) return holo_fail(HOLO_ERR_INIT, "null context");
+    return check_dev_status(ctx);
+}
+
+extern "C" uint64_t holo_b200_ctx_launch_count(holo_b200_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" int32_t holo_b200_ctx_set_lut_table(holo_b200_ctx* ctx, uint8_t act, uint8_t dtype, const uint16_t* table) {
+    if (!ctx || !table) return holo_fail(HOLO_ERR_INIT, "null argument");
+    const uint16_t* dev = nullptr;
+    HOLO_TRY(holo_lut_table(ctx, act, dtype, &dev));
+    HOLO_CUDA(cudaMemcpyAsync((void*)dev, table, 65536 * 2, cudaMemcpyHostToDevice, ctx->stream));
+    HOLO_CUDA(cudaStreamSynchronize(ctx->stream));
+    return HOLO_OK;
+}
+
+extern "C" int32_t holo_b200_ctx_get_lut_table(holo_b200_ctx* ctx, uint8_t act, uint8_t dtype, uint16_t* table) {
+    if (!ctx || !table) return holo_fail(HOLO_ERR_INIT, "null argument");
+    const uint16_t* dev = nullptr;
+    HOLO_TRY(holo_lut_table(ctx, act, dtype, &dev));
+    HOLO_CUDA(cudaMemcpyAsync(table, dev, 65536 * 2, cudaMemcpyDeviceToHost, ctx->stream));
+    HOLO_CUDA(cudaStreamSynchronize(ctx->stream));
+    return HOLO_OK;
+}
+
+int32_t holo_ensure_scratch(holo_b200_ctx* ctx, uint64_t bytes) {
+    if (bytes <= ctx->scratch_bytes) return HOLO_OK;
+    HOLO_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+    uint64_t want = (bytes + (1u << 20) - 1) & ~((uint64_t)(1u << 20) - 1);
+    HOLO_CUDA(cudaMalloc(&ctx->scratch, want));
+    ctx->scratch_bytes = want;
+    return HOLO_OK;
+}
+
+// ---- workspace ------------------------------------------------------------------------------
+extern "C" int32_t holo_b200_workspace_create(holo_b200_ctx* ctx, uint32_t n_slots, holo_b200_workspace** out) {
+    if (!ctx || !out) return holo_fail(HOLO_ERR_INIT, "null argument");
+    auto* ws = new holo_b200_workspace();
+    ws->ctx = ctx;
+    ws->slots.resize(n_slots);
+    *out = ws;
+    return HOLO_OK;
+}
+
+extern "C" void holo_b200_workspace_destroy(holo_b200_workspace* ws) {
+    if (!ws) return;
+    cudaSetDevice(ws->ctx->device);
+    cudaStreamSynchronize(ws->ctx->stream);
+    for (auto& s : ws->slots)
+        if (s.owned && s.ptr) cudaFree(s.ptr);
+    delete ws;
+}
+
+extern "C" int32_t holo_b200_workspace_alloc(holo_b200_workspace* ws, uint32_t slot, uint64_t bytes) {
+    if (!ws) return holo_fail(HOLO_ERR_INIT, "null workspace");
+    if (slot >= ws->slots.size()) return holo_fail_slot(slot, "alloc");
+    HoloSlot& s = ws->slots[slot];
+    // 64-byte size granularity like the arena (crates/hologram-exec/src/buffer.rs:63).
+    uint64_t cap = bytes ? ((bytes + 63) & ~63ull) : 64;
+    if (!(s.owned && s.ptr && s.bytes == bytes)) {
+        if (s.owned && s.ptr) {
+            HOLO_CUDA(cudaStreamSynchronize(ws->ctx->stream));
+            cudaFree(s.ptr);
+        }
+        s = HoloSlot();
+        HOLO_CUDA(cudaMalloc(&s.ptr, cap));
+        s.bytes = bytes;
+        s.owned = true;
+    }
+    HOLO_CUDA(cudaMemsetAsync(s.ptr, 0, cap, ws->ctx->stream));
+    return HOLO_OK;
+}
+
+extern "C" int32_t holo_b200_workspace_bind(holo_b200_workspace* ws, uint32_t slot, void* device_ptr, uint64_t bytes) {
+    if (!ws) return holo_fail(HOLO_ERR_INIT, "null workspace");
+    if (slot >= ws->slots.size()) return holo_fail_slot(slot, "bind");
+    HoloSlot& s = ws->slots[slot];
+    if (s.owned && s.ptr) {
+        HOLO_CUDA(cudaStreamSynchronize(ws->ctx->stream));
+        cudaFree(s.ptr);
+    }
+    s.ptr = device_ptr;
+    s.bytes = bytes;
+    s.owned = false;
+    return HOLO_OK;
+}
+
+extern "C" int32_t holo_b200_workspace_slot(holo_b200_workspace* ws, uint32_t slot, void** device_ptr, uint64_t* bytes) {
+    if (!ws) return holo_fail(HOLO_ERR_INIT, "null workspace");
+    if (slot >= ws->slots.size() || !ws->slots[slot].ptr) return holo_fail_slot(slot, "unbound");
+    if (device_ptr) *device_ptr = ws->slots[slot].ptr;
+    if (bytes) *bytes = ws->slots[slot].bytes;
+    return HOLO_OK;
+}
+
+int32_t holo_resolve(holo_b200_workspace* ws, HoloBufferRef ref, uint64_t need, uint8_t** ptr, uint64_t* extent) {
+    if (ref.slot >= ws->slots.size()) return holo_fail_slot(ref.slot, "no such slot");
+    const HoloSlot& s = ws->slots[ref.slot];
+    if (!s.ptr) return holo_fail_slot(ref.slot, "slot is not bound");
+    if (ref.offset > s.bytes) return holo_fail_slot(ref.slot, "offset beyond slot");
+    uint64_t ext = ref.length ? ref.length : s.bytes - ref.offset;
+    if (ext > s.bytes - ref.offset) return holo_fail_slot(ref.slot, "range beyond slot");
+    if (need > ext) return holo_fail_slot(ref.slot, "buffer shorter than the call's geometry requires");
+    *ptr = (uint8_t*)s.ptr + ref.offset;
+    if (extent) *extent = ext;
+    return HOLO_OK;
+}
+
+extern "C" int32_t holo_b200_workspace_upload(holo_b200_workspace* ws, HoloBufferRef dst, const void* host, uint64_t bytes) {
+    if (!ws) return holo_fail(HOLO_ERR_INIT, "null workspace");
+    uint8_t* p;
+    HOLO_TRY(holo_resolve(ws, dst, bytes, &p, nullptr));
+    if (bytes) HOLO_CUDA(cudaMemcpyAsync(p, host, bytes, cudaMemcpyHostToDevice, ws->ctx->stream));
+    return HOLO_OK;
+}
+
+extern "C" int32_t holo_b200_workspace_download(holo_b200_workspace* ws, HoloBufferRef src, void* host, uint64_t bytes) {
+    if (!ws) return holo_fail(HOLO_ERR_INIT, "null workspace");
+    uint8_t* p;
+    HOLO_TRY(holo_resolve(ws, src, bytes, &p, nullptr));
+    if (bytes) HOLO_CUDA(cudaMemcpyAsync(host, p, bytes, cudaMemcpyDeviceToHost, ws->ctx->stream));
+    return check_dev_status(ws->ctx);
+}
+
+// ---- dispatch -------------------------------------------------------------------------------
+namespace {
+
+struct Range {
+    const uint8_t* p;
+    uint64_t n;
+};
+// split_borrow rule (workspace.rs:43-55, buffer.rs:955-999): the written range must not
+// overlap any read range; the reference reports the failure against the output slot.
+int32_t check_disjoint(const Range& w, uint32_t out_slot, std::initializer_list<Range> reads) {
+    for (const Range& r : reads) {
+        if (r.n == 0 || w.n == 0) continue;
+        if (r.p < w.p + w.n && w.p < r.p + r.n) return holo_fail_slot(out_slot, "output overlaps an input range");
+    }
+    return HOLO_OK;
+}
+
+int lut_act_of_kind(uint16_t kind) {
+    switch (kind) {
+        case HOLO_K_SIGMOID: return HOLO_LUT_SIGMOID;
+        case HOLO_K_TANH: return HOLO_LUT_TANH;
+        case HOLO_K_GELU: return HOLO_LUT_GELU;
+        case HOLO_K_SILU: return HOLO_LUT_SILU;
+        case HOLO_K_EXP: return HOLO_LUT_EXP;
+        case HOLO_K_ERF: return HOLO_LUT_ERF;
+        default: return -1;
+    }
+}
+
+// unary_act -> lut::unary_lut (cpu/kernels.rs:1586-1598, cpu/lut.rs:76-98)
+int32_t do_unary_lut(holo_b200_ctx* ctx, const HoloUnaryCall& c, int act, holo_b200_workspace* ws) {
+    if (c.dtype == HOLO_DTYPE_F64)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: f64 is not a supported compute dtype (hologram computes in f16/bf16/f32)");
+    if (c.dtype != HOLO_DTYPE_F16 && c.dtype != HOLO_DTYPE_BF16)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: this backend serves unary activations through the 16-bit LUT only (dtype %u)", c.dtype);
+    uint64_t n = c.element_count;
+    if (n == 0) return HOLO_OK;
+    uint8_t *in, *out;
+    // the reference resolves the borrow first (output slot reported), then the lengths
+    HOLO_TRY(holo_resolve(ws, c.output, 0, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.input, n * 2, &in, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, n * 2, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, n * 2}, c.output.slot, {{in, n * 2}}));
+    const uint16_t* table;
+    HOLO_TRY(holo_lut_table(ctx, (uint8_t)act, c.dtype, &table));
+    return holo_launch_lut(ctx, table, (const uint16_t*)in, (uint16_t*)out, n);
+}
+
+// binary_float_acc (cpu/float_kernels.rs:252-296)
+int32_t do_binary(holo_b200_ctx* ctx, const HoloBinaryCall& c, int op, holo_b200_workspace* ws) {
+    if (c.dtype == HOLO_DTYPE_F64)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: f64 is not a supported compute dtype (hologram computes in f16/bf16/f32)");
+    if (!holo_is_compute_float(c.dtype))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: integer-ring Add/Mul are not served by this backend (dtype %u)", c.dtype);
+    uint64_t bytes = c.element_count * holo_dtype_size(c.dtype);
+    uint8_t *a, *b, *out;
+    HOLO_TRY(holo_resolve(ws, c.a, bytes, &a, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.b, bytes, &b, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, bytes, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, bytes}, c.a.slot, {{a, bytes}, {b, bytes}}));
+    return holo_launch_binary(ctx, op, a, b, out, c.element_count, c.dtype);
+}
+
+// matmul_float and its fused epilogues (cpu/float_kernels.rs:298-399, 822-891)
+int32_t do_matmul(holo_b200_ctx* ctx, const HoloMatMulCall& c, uint8_t act, const HoloBufferRef* residual,
+                  holo_b200_workspace* ws) {
+    if (c.m == 0 || c.k == 0 || c.n == 0) return HOLO_OK;
+    if (c.dtype == HOLO_DTYPE_F64)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: f64 is not a supported compute dtype (hologram computes in f16/bf16/f32)");
+    if (c.dtype != HOLO_DTYPE_BF16)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul is served for bf16 only (dtype %u)", c.dtype);
+    if (c.b_packed) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: panel-packed B is an f32-only layout");
+    if (act != 0 && act != HOLO_FUSED_GELU && act != HOLO_FUSED_SILU && act != HOLO_FUSED_SIGMOID && act != HOLO_FUSED_TANH &&
+        act != HOLO_FUSED_EXP)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: fused activation %u is not table-backed", act);
+    uint64_t ab = (uint64_t)c.m * c.k * 2, bb = (uint64_t)c.k * c.n * 2, ob = (uint64_t)c.m * c.n * 2;
+    uint8_t *a, *b, *out, *res = nullptr;
+    HOLO_TRY(holo_resolve(ws, c.a, ab, &a, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.b, bb, &b, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, ob, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, ob}, c.a.slot, {{a, ab}, {b, bb}}));
+    if (residual) {
+        HOLO_TRY(holo_resolve(ws, *residual, ob, &res, nullptr));
+        HOLO_TRY(check_disjoint({out, ob}, c.output.slot, {{res, ob}}));
+    }
+    return holo_launch_matmul(ctx, a, b, out, c.m, c.k, c.n, c.dtype, act, res);
+}
+
+// rms_norm_float (cpu/float_kernels.rs:1683-1756), epsilon rule :1324-1336
+int32_t do_rms_norm(holo_b200_ctx* ctx, const HoloNormCall& c, holo_b200_workspace* ws) {
+    if (c.batch == 0 || c.feature == 0) return HOLO_OK;
+    if (!holo_is_compute_float(c.dtype))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: rms_norm dtype %u", c.dtype);
+    if (c.num_groups != 0) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: grouped norms are not served by this backend");
+    float eps = 1e-9f;
+    if (c.epsilon_bits != 0) {
+        uint32_t b = (uint32_t)c.epsilon_bits;
+        memcpy(&eps, &b, 4);
+        if (!(isfinite(eps) && eps > 0.0f))
+            return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: norm epsilon must be a positive finite f32 (0 selects the default)");
+    }
+    size_t es = holo_dtype_size(c.dtype);
+    uint64_t total = (uint64_t)c.batch * c.feature * es;
+    uint8_t *x, *g = nullptr, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, 0, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.x, total, &x, nullptr));
+    if (c.gamma.slot != HOLO_NO_SLOT) HOLO_TRY(holo_resolve(ws, c.gamma, (uint64_t)c.feature * es, &g, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, total, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, total}, c.output.slot, {{x, total}, {g, g ? (uint64_t)c.feature * es : 0}}));
+    return holo_launch_rms_norm(ctx, x, g, out, c.batch, c.feature, eps, c.dtype);
+}
+
+// rope_float (cpu/float_kernels.rs:3123-3190)
+int32_t do_rope(holo_b200_ctx* ctx, const HoloRoPECall& c, holo_b200_workspace* ws) {
+    uint64_t n = c.element_count;
+    uint32_t d = c.head_dim;
+    if (d == 0 || d % 2 != 0 || n % d != 0)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: rope: head_dim must be even and divide the element count");
+    if (!holo_is_compute_float(c.dtype)) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: rope dtype %u", c.dtype);
+    uint64_t bytes = n * holo_dtype_size(c.dtype);
+    uint8_t *x, *cs, *sn, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, bytes, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.x, bytes, &x, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.cos, bytes, &cs, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.sin, bytes, &sn, nullptr));
+    HOLO_TRY(check_disjoint({out, bytes}, c.output.slot, {{x, bytes}, {cs, bytes}, {sn, bytes}}));
+    return holo_launch_rope(ctx, x, cs, sn, out, d, n, c.dtype);
+}
+
+// gather (cpu/kernels.rs:389-446)
+int32_t do_gather(holo_b200_ctx* ctx, const HoloGatherCall& c, holo_b200_workspace* ws) {
+    size_t es = holo_dtype_size(c.dtype);
+    if (es == 0) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: gather: sub-byte or unknown element dtype not supported");
+    size_t iw = c.idx_dtype == HOLO_DTYPE_I32 ? 4 : c.idx_dtype == HOLO_DTYPE_I64 ? 8 : 0;
+    if (iw == 0) return holo_fail_slot(c.indices.slot, "gather index dtype must be i32 or i64");
+    uint64_t row = c.inner * es;
+    uint8_t *data, *idx, *out;
+    uint64_t db = c.outer * c.axis_dim * row, ib = c.num_indices * iw, ob = c.outer * c.num_indices * row;
+    if (holo_resolve(ws, c.data, db, &data, nullptr) != HOLO_OK || holo_resolve(ws, c.indices, ib, &idx, nullptr) != HOLO_OK ||
+        holo_resolve(ws, c.output, ob, &out, nullptr) != HOLO_OK)
+        return holo_fail_slot(c.output.slot, "gather operand shorter than its geometry");
+    HOLO_TRY(check_disjoint({out, ob}, c.output.slot, {{data, db}, {idx, ib}}));
+    return holo_launch_gather(ctx, data, idx, c.idx_dtype, out, c.outer, c.axis_dim, row, c.num_indices);
+}
+
+// cast (cpu/kernels.rs:560-594)
+int32_t do_cast(holo_b200_ctx* ctx, const HoloCastCall& c, holo_b200_workspace* ws) {
+    size_t sw = holo_dtype_size(c.src_dtype), dw = holo_dtype_size(c.dst_dtype);
+    if (sw == 0 || dw == 0)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: cast: unsupported source/destination dtype (sub-byte not castable)");
+    if (c.dst_dtype == HOLO_DTYPE_F64 || c.dst_dtype == HOLO_DTYPE_U64)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: cast to dtype %u is not served by this backend", c.dst_dtype);
+    uint8_t *in, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, 0, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.input, c.element_count * sw, &in, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, c.element_count * dw, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, c.element_count * dw}, c.output.slot, {{in, c.element_count * sw}}));
+    return holo_launch_cast(ctx, in, c.src_dtype, out, c.dst_dtype, c.element_count);
+}
+
+// Reshape dispatched as a call is a byte copy (the executor normally label-propagates it,
+// crates/hologram-exec/src/session.rs:1112-1114).
+int32_t do_reshape(holo_b200_ctx* ctx, const HoloLayoutCall& c, holo_b200_workspace* ws) {
+    size_t es = holo_dtype_size(c.dtype);
+    if (es == 0) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: reshape of a sub-byte dtype");
+    uint64_t bytes = c.element_count * es;
+    uint8_t *in, *out;
+    HOLO_TRY(holo_resolve(ws, c.input, bytes, &in, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, bytes, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, bytes}, c.output.slot, {{in, bytes}}));
+    if (bytes) HOLO_CUDA(cudaMemcpyAsync(out, in, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return HOLO_OK;
+}
+
+// dequantize (cpu/kernels.rs:185-296)
+int32_t do_dequantize(holo_b200_ctx* ctx, const HoloDequantizeCall& c, holo_b200_workspace* ws) {
+    if (c.quant_dtype != HOLO_DTYPE_I8 && c.quant_dtype != HOLO_DTYPE_U8) return holo_fail_slot(c.input.slot, "dequantize source must be i8 or u8");
+    if (!holo_is_compute_float(c.dtype)) return holo_fail_slot(c.output.slot, "dequantize destination must be f32, bf16 or f16");
+    uint64_t n = c.element_count;
+    bool per_ch = c.channels > 0 && c.scales.slot != HOLO_NO_SLOT;
+    uint8_t *in, *out, *sc = nullptr, *zp = nullptr;
+    uint64_t ob = n * holo_dtype_size(c.dtype);
+    HOLO_TRY(holo_resolve(ws, c.output, ob, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.input, n, &in, nullptr));
+    if (per_ch) {
+        HOLO_TRY(holo_resolve(ws, c.scales, (uint64_t)c.channels * 4, &sc, nullptr));
+        if (c.zero_points.slot != HOLO_NO_SLOT) HOLO_TRY(holo_resolve(ws, c.zero_points, (uint64_t)c.channels * 4, &zp, nullptr));
+        else return holo_fail_slot(c.zero_points.slot, "per-channel dequantize needs a zero-point vector");
+    }
+    HOLO_TRY(check_disjoint({out, ob}, c.output.slot, {{in, n}}));
+    return holo_launch_dequantize(ctx, c, in, (const float*)sc, (const int32_t*)zp, out);
+}
+
+// kv_cache_write (cpu/kernels.rs:455-501)
+int32_t do_kv_write(holo_b200_ctx* ctx, const HoloKvCacheWriteCall& c, holo_b200_workspace* ws) {
+    if (c.bucket_rows == 0 || c.row_bytes == 0)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: kv_cache_write: bucket_rows and row_bytes must be >= 1");
+    if (c.new_rows > c.bucket_rows)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: kv_cache_write: new_rows exceeds bucket_rows");
+    uint64_t plane = (uint64_t)c.bucket_rows * c.row_bytes, total = plane * c.planes;
+    uint64_t nb = (uint64_t)c.planes * c.new_rows * c.row_bytes;
+    uint8_t *cache, *nw, *pos, *out;
+    if (holo_resolve(ws, c.cache, total, &cache, nullptr) != HOLO_OK || holo_resolve(ws, c.new_rows_buf, nb, &nw, nullptr) != HOLO_OK ||
+        holo_resolve(ws, c.pos, 4, &pos, nullptr) != HOLO_OK || holo_resolve(ws, c.output, total, &out, nullptr) != HOLO_OK)
+        return holo_fail_slot(c.output.slot, "kv_cache_write operand shorter than its geometry");
+    if (out == cache) {
+        // in-place move form: only the new rows are written
+        HOLO_TRY(check_disjoint({out, total}, c.output.slot, {{nw, nb}, {pos, 4}}));
+    } else {
+        HOLO_TRY(check_disjoint({out, total}, c.output.slot, {{cache, total}, {nw, nb}, {pos, 4}}));
+    }
+    if (((uintptr_t)pos & 3u) != 0) return holo_fail_slot(c.pos.slot, "pos operand must be 4-byte aligned on the device");
+    return holo_launch_kv_write(ctx, cache, nw, (const uint32_t*)pos, out, c.planes, c.bucket_rows, c.new_rows, c.row_bytes);
+}
+
+int32_t do_quantize_rows(holo_b200_ctx* ctx, const HoloQuantizeRowsI8Call& c, holo_b200_workspace* ws) {
+    if (!holo_is_compute_float(c.dtype)) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: quantize_rows_i8 input dtype %u", c.dtype);
+    uint64_t n = c.rows * c.row_len;
+    uint64_t ib = n * holo_dtype_size(c.dtype);
+    uint8_t *in, *codes, *scales;
+    HOLO_TRY(holo_resolve(ws, c.input, ib, &in, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.codes, n, &codes, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.scales, c.rows * 4, &scales, nullptr));
+    HOLO_TRY(check_disjoint({codes, n}, c.codes.slot, {{in, ib}, {scales, c.rows * 4}}));
+    HOLO_TRY(check_disjoint({scales, c.rows * 4}, c.scales.slot, {{in, ib}}));
+    if (((uintptr_t)scales & 3u) != 0) return holo_fail_slot(c.scales.slot, "scales must be 4-byte aligned");
+    return holo_launch_quantize_rows(ctx, in, c.dtype, c.rows, c.row_len, (int8_t*)codes, (float*)scales);
+}
+
+// Geometry rules shared by both attention forms (cpu/float_kernels.rs:4192-4266).
+int32_t attn_geometry(uint32_t b, uint32_t h, uint32_t kv, uint32_t m, uint32_t nnew, uint32_t d, uint32_t scale_bits,
+                      uint32_t* hkv, float* scale_div, bool* empty) {
+    *empty = (b == 0 || h == 0 || d == 0);
+    if (*empty) return HOLO_OK;
+    if (m == 0 || m != nnew)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP,
+                         "unsupported op: decode_attention_valid: q_rows must equal new_len and be at least 1 "
+                         "(the causal law pairs query row i with chunk key row i)");
+    *hkv = kv == 0 ? h : kv;
+    if (*hkv == 0 || h % *hkv != 0)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: decode_attention_valid: heads must be a multiple of kv_heads (grouped-query)");
+    float dflt = sqrtf((float)d);
+    if (dflt < 1.0f) dflt = 1.0f;
+    *scale_div = dflt;
+    if (scale_bits != 0) {
+        float sm;
+        memcpy(&sm, &scale_bits, 4);
+        if (sm > 0.0f) *scale_div = 1.0f / sm;
+    }
+    return HOLO_OK;
+}
+
+// decode_attention_valid_float (cpu/float_kernels.rs:4192-4307)
+int32_t do_attention(holo_b200_ctx* ctx, const HoloDecodeAttentionValidCall& c, holo_b200_workspace* ws) {
+    HoloAttnArgs a = {};
+    bool empty;
+    HOLO_TRY(attn_geometry(c.batch, c.heads, c.kv_heads, c.q_rows, c.new_len, c.head_dim, c.scale_bits, &a.hkv, &a.scale_div, &empty));
+    if (empty) return HOLO_OK;
+    if (c.dtype == HOLO_DTYPE_F64)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: f64 is not a supported compute dtype (hologram computes in f16/bf16/f32)");
+    if (!holo_is_compute_float(c.dtype))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: decode_attention_valid: only f32/f16/bf16 are supported compute dtypes");
+    size_t es = holo_dtype_size(c.dtype);
+    uint64_t qt = (uint64_t)c.batch * c.heads * c.q_rows * c.head_dim * es;
+    uint64_t pt = (uint64_t)c.batch * a.hkv * c.past_len * c.head_dim * es;
+    uint64_t nt = (uint64_t)c.batch * a.hkv * c.new_len * c.head_dim * es;
+    uint8_t *q, *kp, *vp, *kn, *vn, *vl, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, 0, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.q, qt, &q, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.k_past, pt, &kp, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.v_past, pt, &vp, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.k_new, nt, &kn, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.v_new, nt, &vn, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.valid_len, 4, &vl, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, qt, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, qt}, c.output.slot, {{q, qt}, {kp, pt}, {vp, pt}, {kn, nt}, {vn, nt}, {vl, 4}}));
+    if (((uintptr_t)vl & 3u) != 0) return holo_fail_slot(c.valid_len.slot, "valid_len operand must be 4-byte aligned on the device");
+    a.q = q; a.k_past = kp; a.v_past = vp; a.k_new = kn; a.v_new = vn;
+    a.valid_len = (const uint32_t*)vl; a.out = out;
+    a.b = c.batch; a.h = c.heads; a.m = c.q_rows; a.past = c.past_len; a.nnew = c.new_len; a.d = c.head_dim;
+    a.dtype = c.dtype; a.quantized = false;
+    return holo_launch_decode_attention(ctx, a);
+}
+
+int32_t do_attention_q8(holo_b200_ctx* ctx, const HoloDecodeAttentionValidQ8Call& c, holo_b200_workspace* ws) {
+    HoloAttnArgs a = {};
+    bool empty;
+    HOLO_TRY(attn_geometry(c.batch, c.heads, c.kv_heads, c.q_rows, c.new_len, c.head_dim, c.scale_bits, &a.hkv, &a.scale_div, &empty));
+    if (empty) return HOLO_OK;
+    if (!holo_is_compute_float(c.dtype))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: decode_attention_valid_q8: q/output dtype must be f32, f16 or bf16");
+    size_t es = holo_dtype_size(c.dtype);
+    uint64_t qt = (uint64_t)c.batch * c.heads * c.q_rows * c.head_dim * es;
+    uint64_t prow = (uint64_t)c.batch * a.hkv * c.past_len, nrow = (uint64_t)c.batch * a.hkv * c.new_len;
+    uint64_t pt = prow * c.head_dim, nt = nrow * c.head_dim;
+    uint8_t *q, *kp, *kps, *vp, *vps, *kn, *kns, *vn, *vns, *vl, *out;
+    HOLO_TRY(holo_resolve(ws, c.q, qt, &q, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.k_past, pt, &kp, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.k_past_scales, prow * 4, &kps, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.v_past, pt, &vp, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.v_past_scales, prow * 4, &vps, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.k_new, nt, &kn, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.k_new_scales, nrow * 4, &kns, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.v_new, nt, &vn, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.v_new_scales, nrow * 4, &vns, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.valid_len, 4, &vl, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, qt, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, qt}, c.output.slot,
+                            {{q, qt}, {kp, pt}, {vp, pt}, {kn, nt}, {vn, nt}, {kps, prow * 4}, {vps, prow * 4}, {kns, nrow * 4}, {vns, nrow * 4}, {vl, 4}}));
+    if ((((uintptr_t)vl | (uintptr_t)kps | (uintptr_t)vps | (uintptr_t)kns | (uintptr_t)vns) & 3u) != 0)
+        return holo_fail_slot(c.valid_len.slot, "valid_len and scale operands must be 4-byte aligned on the device");
+    a.q = q; a.k_past = kp; a.v_past = vp; a.k_new = kn; a.v_new = vn;
+    a.k_past_s = (const float*)kps; a.v_past_s = (const float*)vps; a.k_new_s = (const float*)kns; a.v_new_s = (const float*)vns;
+    a.valid_len = (const uint32_t*)vl; a.out = out;
+    a.b = c.batch; a.h = c.heads; a.m = c.q_rows; a.past = c.past_len; a.nnew = c.new_len; a.d = c.head_dim;
+    a.dtype = c.dtype; a.quantized = true;
+    return holo_launch_decode_attention(ctx, a);
+}
+
+int32_t do_all_reduce(holo_b200_ctx* ctx, const HoloAllReduceCall& c, holo_b200_workspace* ws) {
+    size_t es = holo_dtype_size(c.dtype);
+    if (c.dtype != HOLO_DTYPE_F32 && c.dtype != HOLO_DTYPE_BF16 && c.dtype != HOLO_DTYPE_F16)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: all_reduce dtype %u", c.dtype);
+    uint8_t* buf;
+    HOLO_TRY(holo_resolve(ws, c.buffer, c.element_count * es, &buf, nullptr));
+    return holo_all_reduce(ctx, buf, c.element_count, c.dtype);
+}
+
+}  // namespace
+
+static int32_t dispatch_impl(holo_b200_ctx* ctx, const HoloKernelCall* call, holo_b200_workspace* ws) {
+    int act = lut_act_of_kind(call->kind);
+    if (act >= 0) return do_unary_lut(ctx, call->u.unary, act, ws);
+    switch (call->kind) {
+        case HOLO_K_ADD: return do_binary(ctx, call->u.binary, 0, ws);
+        case HOLO_K_MUL: return do_binary(ctx, call->u.binary, 1, ws);
+        case HOLO_K_MATMUL: return do_matmul(ctx, call->u.matmul, 0, nullptr, ws);
+        case HOLO_K_MATMUL_ACTIVATION: return do_matmul(ctx, call->u.matmul_activation.mm, call->u.matmul_activation.act, nullptr, ws);
+        case HOLO_K_MATMUL_ADD: return do_matmul(ctx, call->u.matmul_add.mm, 0, &call->u.matmul_add.residual, ws);
+        case HOLO_K_RMS_NORM: return do_rms_norm(ctx, call->u.norm, ws);
+        case HOLO_K_ROTARY: return do_rope(ctx, call->u.rope, ws);
+        case HOLO_K_GATHER: return do_gather(ctx, call->u.gather, ws);
+        case HOLO_K_CAST: return do_cast(ctx, call->u.cast, ws);
+        case HOLO_K_RESHAPE: return do_reshape(ctx, call->u.layout, ws);
+        case HOLO_K_DEQUANTIZE: return do_dequantize(ctx, call->u.dequantize, ws);
+        case HOLO_K_KV_CACHE_WRITE: return do_kv_write(ctx, call->u.kv_cache_write, ws);
+        case HOLO_K_DECODE_ATTENTION_VALID: return do_attention(ctx, call->u.decode_attention_valid, ws);
+        case HOLO_K_QUANTIZE_ROWS_I8: return do_quantize_rows(ctx, call->u.quantize_rows_i8, ws);
+        case HOLO_K_DECODE_ATTENTION_VALID_Q8: return do_attention_q8(ctx, call->u.decode_attention_valid_q8, ws);
+        case HOLO_K_ALL_REDUCE: return do_all_reduce(ctx, call->u.all_reduce, ws);
+        default:
+            return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: KernelCall variant %u is not served by the B200 backend (no CPU fallback)", call->kind);
+    }
+}
+
+extern "C" int32_t holo_b200_dispatch(holo_b200_ctx* ctx, const HoloKernelCall* call, holo_b200_workspace* ws) {
+    if (!ctx || !call || !ws) return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: null argument");
+    if (ws->ctx != ctx) return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: workspace belongs to another context");
+    HOLO_CUDA(cudaSetDevice(ctx->device));
+    return dispatch_impl(ctx, call, ws);
+}
+
+// ---- host-workspace form ---------------------------------------------------------------------
+namespace {
+
+// Every BufferRef of a call; `out_bytes` > 0 marks a written operand and gives the number of
+// bytes the kernel produces there (inputs carry 0).
+struct RefList {
+    HoloBufferRef* refs[12];
+    uint64_t out_bytes[12];
+    bool written[12];
+    int n = 0;
+    void in(HoloBufferRef* r) {
+        refs[n] = r;
+        out_bytes[n] = 0;
+        written[n] = false;
+        ++n;
+    }
+    void out(HoloBufferRef* r, uint64_t bytes) {
+        refs[n] = r;
+        out_bytes[n] = bytes;
+        written[n] = true;
+        ++n;
+    }
+};
+
+bool collect_refs(HoloKernelCall* c, RefList* l) {
+    switch (c->kind) {
+        case HOLO_K_SIGMOID: case HOLO_K_TANH: case HOLO_K_GELU: case HOLO_K_SILU: case HOLO_K_EXP: case HOLO_K_ERF:
+            l->in(&c->u.unary.input);
+            l->out(&c->u.unary.output, c->u.unary.element_count * holo_dtype_size(c->u.unary.dtype));
+            return true;
+        case HOLO_K_ADD: case HOLO_K_MUL:
+            l->in(&c->u.binary.a); l->in(&c->u.binary.b);
+            l->out(&c->u.binary.output, c->u.binary.element_count * holo_dtype_size(c->u.binary.dtype));
+            return true;
+        case HOLO_K_MATMUL: case HOLO_K_MATMUL_ACTIVATION: case HOLO_K_MATMUL_ADD: {
+            // the three variants start with the same MatMulCall
+            HoloMatMulCall& mm = c->u.matmul;
+            l->in(&mm.a); l->in(&mm.b);
+            if (c->kind == HOLO_K_MATMUL_ADD) l->in(&c->u.matmul_add.residual);
+            l->out(&mm.output, (uint64_t)mm.m * mm.n * holo_dtype_size(mm.dtype));
+            return true;
+        }
+        case HOLO_K_RMS_NORM:
+            l->in(&c->u.norm.x); l->in(&c->u.norm.gamma);
+            l->out(&c->u.norm.output, (uint64_t)c->u.norm.batch * c->u.norm.feature * holo_dtype_size(c->u.norm.dtype));
+            return true;
+        case HOLO_K_ROTARY:
+            l->in(&c->u.rope.x); l->in(&c->u.rope.cos); l->in(&c->u.rope.sin);
+            l->out(&c->u.rope.output, c->u.rope.element_count * holo_dtype_size(c->u.rope.dtype));
+            return true;
+        case HOLO_K_GATHER:
+            l->in(&c->u.gather.data); l->in(&c->u.gather.indices);
+            l->out(&c->u.gather.output, c->u.gather.outer * c->u.gather.num_indices * c->u.gather.inner * holo_dtype_size(c->u.gather.dtype));
+            return true;
+        case HOLO_K_CAST:
+            l->in(&c->u.cast.input);
+            l->out(&c->u.cast.output, c->u.cast.element_count * holo_dtype_size(c->u.cast.dst_dtype));
+            return true;
+        case HOLO_K_RESHAPE:
+            l->in(&c->u.layout.input);
+            l->out(&c->u.layout.output, c->u.layout.element_count * holo_dtype_size(c->u.layout.dtype));
+            return true;
+        case HOLO_K_DEQUANTIZE:
+            l->in(&c->u.dequantize.input); l->in(&c->u.dequantize.scales); l->in(&c->u.dequantize.zero_points);
+            l->out(&c->u.dequantize.output, c->u.dequantize.element_count * holo_dtype_size(c->u.dequantize.dtype));
+            return true;
+        case HOLO_K_KV_CACHE_WRITE: {
+            auto& k = c->u.kv_cache_write;
+            l->in(&k.cache); l->in(&k.new_rows_buf); l->in(&k.pos);
+            l->out(&k.output, (uint64_t)k.planes * k.bucket_rows * k.row_bytes);
+            return true;
+        }
+        case HOLO_K_DECODE_ATTENTION_VALID: {
+            auto& a = c->u.decode_attention_valid;
+            l->in(&a.q); l->in(&a.k_past); l->in(&a.v_past); l->in(&a.k_new); l->in(&a.v_new); l->in(&a.valid_len);
+            l->out(&a.output, (uint64_t)a.batch * a.heads * a.q_rows * a.head_dim * holo_dtype_size(a.dtype));
+            return true;
+        }
+        case HOLO_K_QUANTIZE_ROWS_I8: {
+            auto& q = c->u.quantize_rows_i8;
+            l->in(&q.input);
+            l->out(&q.codes, q.rows * q.row_len);
+            l->out(&q.scales, q.rows * 4);
+            return true;
+        }
+        case HOLO_K_DECODE_ATTENTION_VALID_Q8: {
+            auto& a = c->u.decode_attention_valid_q8;
+            l->in(&a.q); l->in(&a.k_past); l->in(&a.k_past_scales); l->in(&a.v_past); l->in(&a.v_past_scales);
+            l->in(&a.k_new); l->in(&a.k_new_scales); l->in(&a.v_new); l->in(&a.v_new_scales); l->in(&a.valid_len);
+            l->out(&a.output, (uint64_t)a.batch * a.heads * a.q_rows * a.head_dim * holo_dtype_size(a.dtype));
+            return true;
+        }
+        default: return false;
+    }
+}
+
+}  // namespace
+
+extern "C" int32_t holo_b200_dispatch_host(holo_b200_ctx* ctx, const HoloKernelCall* call, HoloHostSlot* host_slots, uint32_t n_slots) {
+    if (!ctx || !call || !host_slots) return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: null argument");
+    HOLO_CUDA(cudaSetDevice(ctx->device));
+    HoloKernelCall local = *call;
+    RefList refs;
+    if (!collect_refs(&local, &refs))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: KernelCall variant %u has no host-workspace form", call->kind);
+    // Each referenced host range gets a 256-byte aligned range of one device arena; the call
+    // is rewritten to index a temporary device workspace with one slot per operand. Inputs
+    // are uploaded whole; written operands are not uploaded and only the bytes the kernel
+    // produces are copied back.
+    uint64_t total = 0;
+    uint64_t off[12], len[12];
+    uint32_t orig_slot[12];
+    uint8_t* host_ptr[12];
+    for (int i = 0; i < refs.n; ++i) {
+        HoloBufferRef r = *refs.refs[i];
+        off[i] = len[i] = 0;
+        orig_slot[i] = r.slot;
+        host_ptr[i] = nullptr;
+        if (r.slot == HOLO_NO_SLOT) continue;
+        if (r.slot >= n_slots || !host_slots[r.slot].ptr) return holo_fail_slot(r.slot, "no such host slot");
+        uint64_t sb = host_slots[r.slot].bytes;
+        if (r.offset > sb) return holo_fail_slot(r.slot, "offset beyond slot");
+        uint64_t ext = r.length ? r.length : sb - r.offset;
+        if (ext > sb - r.offset) return holo_fail_slot(r.slot, "range beyond slot");
+        if (refs.written[i] && refs.out_bytes[i] > ext) return holo_fail_slot(r.slot, "buffer shorter than the call's geometry requires");
+        host_ptr[i] = (uint8_t*)host_slots[r.slot].ptr + r.offset;
+        off[i] = total;
+        len[i] = ext;
+        total += (ext + 255) & ~255ull;
+    }
+    // split_borrow rule on the host ranges: a written range may not overlap any other operand
+    for (int i = 0; i < refs.n; ++i) {
+        if (!refs.written[i] || !host_ptr[i]) continue;
+        for (int j = 0; j < refs.n; ++j) {
+            if (j == i || !host_ptr[j] || len[j] == 0 || refs.out_bytes[i] == 0) continue;
+            uint64_t lj = refs.written[j] ? refs.out_bytes[j] : len[j];
+            if (host_ptr[j] < host_ptr[i] + refs.out_bytes[i] && host_ptr[i] < host_ptr[j] + lj)
+                return holo_fail_slot(orig_slot[i], "output overlaps another operand");
+        }
+    }
+    if (total > ctx->stage_bytes) {
+        HOLO_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (ctx->stage) cudaFree(ctx->stage);
+        ctx->stage = nullptr;
+        ctx->stage_bytes = 0;
+        HOLO_CUDA(cudaMalloc(&ctx->stage, total));
+        ctx->stage_bytes = total;
+    }
+    holo_b200_workspace tmp;
+    tmp.ctx = ctx;
+    tmp.slots.resize(refs.n);
+    for (int i = 0; i < refs.n; ++i) {
+        HoloBufferRef& r = *refs.refs[i];
+        if (r.slot == HOLO_NO_SLOT) continue;
+        tmp.slots[i].ptr = (uint8_t*)ctx->stage + off[i];
+        tmp.slots[i].bytes = len[i];
+        if (!refs.written[i] && len[i])
+            HOLO_CUDA(cudaMemcpyAsync(tmp.slots[i].ptr, host_ptr[i], len[i], cudaMemcpyHostToDevice, ctx->stream));
+        r.slot = (uint32_t)i;
+        r.offset = 0;
+        r.length = len[i];
+    }
+    int32_t rc = dispatch_impl(ctx, &local, &tmp);
+    if (rc == HOLO_OK) {
+        for (int i = 0; i < refs.n; ++i)
+            if (refs.written[i] && host_ptr[i] && refs.out_bytes[i])
+                HOLO_CUDA(cudaMemcpyAsync(host_ptr[i], tmp.slots[i].ptr, refs.out_bytes[i], cudaMemcpyDeviceToHost, ctx->stream));
+        rc = check_dev_status(ctx);
+    } else {
+        cudaStreamSynchronize(ctx->stream);
+        // report slot errors in the caller's slot numbering
+        if (rc == HOLO_ERR_SLOT_OUT_OF_RANGE && g_err_slot < (uint32_t)refs.n) {
+            uint32_t o = orig_slot[g_err_slot];
+            char msg[400];
+            snprintf(msg, sizeof msg, "%s", g_err);
+            const char* paren = strchr(msg, '(');
+            holo_fail_slot(o, paren ? "operand shorter than the call's geometry requires, or overlapping" : "slot error");
+        }
+    }
+    return rc;
+}

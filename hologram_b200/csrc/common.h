@@ -1,0 +1,113 @@
+// Internal declarations shared by the backend's translation units. Not part of the C ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/hologram_b200.h"
+
+struct HoloSlot {
+    void* ptr = nullptr;
+    uint64_t bytes = 0;
+    bool owned = false;
+};
+
+struct holo_b200_ctx {
+    int device = 0;
+    int sm_count = 0;
+    int smem_optin = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    uint64_t launches = 0;
+    uint16_t* lut[HOLO_LUT_COUNT][2] = {};  // device tables, [act][0 = f16, 1 = bf16]
+    // split-KV partials of the decode attention / split-K partials of the skinny GEMM
+    void* scratch = nullptr;
+    uint64_t scratch_bytes = 0;
+    // device staging arena used by the host-workspace dispatch form
+    void* stage = nullptr;
+    uint64_t stage_bytes = 0;
+    // device-side error word (bounded waits record where they gave up)
+    uint32_t* dev_status = nullptr;
+    // tensor-parallel group
+    void* nccl_comm = nullptr;
+    int tp_rank = 0, tp_world = 1;
+};
+
+struct holo_b200_workspace {
+    holo_b200_ctx* ctx = nullptr;
+    std::vector<HoloSlot> slots;
+};
+
+// ---- errors -------------------------------------------------------------------------------
+int32_t holo_fail(int32_t code, const char* fmt, ...);
+int32_t holo_fail_slot(uint32_t slot, const char* what);
+int32_t holo_cuda_fail(cudaError_t e, const char* where);
+#define HOLO_CUDA(expr)                                             \
+    do {                                                            \
+        cudaError_t _e = (expr);                                    \
+        if (_e != cudaSuccess) return holo_cuda_fail(_e, #expr);    \
+    } while (0)
+#define HOLO_TRY(expr)                 \
+    do {                               \
+        int32_t _rc = (expr);          \
+        if (_rc != HOLO_OK) return _rc; \
+    } while (0)
+
+// Resolve a BufferRef to a device range holding at least `need` bytes
+// (length == 0 => the slot's extent from offset; workspace.rs:21-23, buffer.rs:318-327).
+int32_t holo_resolve(holo_b200_workspace* ws, HoloBufferRef ref, uint64_t need, uint8_t** ptr, uint64_t* extent);
+// Grow the context scratch buffer to at least `bytes` (never shrinks).
+int32_t holo_ensure_scratch(holo_b200_ctx* ctx, uint64_t bytes);
+static inline size_t holo_dtype_size(uint8_t dtype) {
+    switch (dtype) {
+        case HOLO_DTYPE_BOOL: case HOLO_DTYPE_U8: case HOLO_DTYPE_I8: return 1;
+        case HOLO_DTYPE_F16: case HOLO_DTYPE_BF16: return 2;
+        case HOLO_DTYPE_I32: case HOLO_DTYPE_F32: return 4;
+        case HOLO_DTYPE_U64: case HOLO_DTYPE_I64: case HOLO_DTYPE_F64: return 8;
+        default: return 0;
+    }
+}
+static inline bool holo_is_compute_float(uint8_t d) {
+    return d == HOLO_DTYPE_F16 || d == HOLO_DTYPE_BF16 || d == HOLO_DTYPE_F32;
+}
+
+// ---- kernel launchers (each validates nothing: geometry is checked by the dispatcher) ------
+// lut.cu
+int32_t holo_lut_table(holo_b200_ctx* ctx, uint8_t act, uint8_t dtype, const uint16_t** table);
+int32_t holo_launch_lut(holo_b200_ctx* ctx, const uint16_t* table, const uint16_t* in, uint16_t* out, uint64_t n);
+// glue.cu
+int32_t holo_launch_binary(holo_b200_ctx* ctx, int op, const void* a, const void* b, void* out, uint64_t n, uint8_t dtype);
+int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* gamma, void* out, uint32_t batch,
+                             uint32_t feature, float eps, uint8_t dtype);
+int32_t holo_launch_rope(holo_b200_ctx* ctx, const void* x, const void* c, const void* s, void* out, uint32_t head_dim,
+                         uint64_t n, uint8_t dtype);
+int32_t holo_launch_gather(holo_b200_ctx* ctx, const uint8_t* data, const void* idx, uint8_t idx_dtype, uint8_t* out,
+                           uint64_t outer, uint64_t axis_dim, uint64_t inner_bytes, uint64_t num_idx);
+int32_t holo_launch_cast(holo_b200_ctx* ctx, const void* in, uint8_t src, void* out, uint8_t dst, uint64_t n);
+int32_t holo_launch_dequantize(holo_b200_ctx* ctx, const HoloDequantizeCall& c, const void* in, const float* scales,
+                               const int32_t* zps, void* out);
+int32_t holo_launch_kv_write(holo_b200_ctx* ctx, const uint8_t* cache, const uint8_t* newr, const uint32_t* pos,
+                             uint8_t* out, uint32_t planes, uint32_t bucket, uint32_t new_rows, uint32_t row_bytes);
+int32_t holo_launch_quantize_rows(holo_b200_ctx* ctx, const void* x, uint8_t dtype, uint64_t rows, uint32_t d,
+                                  int8_t* codes, float* scales);
+// attention.cu
+struct HoloAttnArgs {
+    const void* q;
+    const void *k_past, *v_past, *k_new, *v_new;              // bf16/f16/f32 rows, or i8 codes when quantized
+    const float *k_past_s, *v_past_s, *k_new_s, *v_new_s;     // per-row scales (quantized form only)
+    const uint32_t* valid_len;
+    void* out;
+    uint32_t b, h, hkv, m, past, nnew, d;
+    float scale_div;  // scores are divided by this
+    uint8_t dtype;    // q / out dtype (and KV dtype in the unquantized form)
+    bool quantized;
+};
+int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a);
+// gemm.cu
+int32_t holo_launch_matmul(holo_b200_ctx* ctx, const void* a, const void* b, void* out, uint32_t m, uint32_t k,
+                           uint32_t n, uint8_t dtype, uint8_t fused_act, const void* residual);
+// tp.cu
+int32_t holo_all_reduce(holo_b200_ctx* ctx, void* buf, uint64_t n, uint8_t dtype);
+void holo_tp_destroy(holo_b200_ctx* ctx);

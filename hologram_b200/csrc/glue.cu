@@ -1,0 +1,363 @@
+// Decoder glue ops: the small HBM-bound kernels around the three hot families.
+// Each replaces one CPU kernel of crates/hologram-compute/src/cpu (cited per kernel).
+// Elementwise arithmetic uses explicit round-to-nearest intrinsics in the reference's
+// evaluation order, so Add / Mul / RoPE / Cast / Dequantize / the row quantizer are
+// bit-identical to the CPU path; RMSNorm reduces its sum of squares in parallel and is
+// therefore a tolerance-class op.
+#include "common.h"
+#include "numerics.cuh"
+
+namespace {
+
+constexpr int EW_THREADS = 256;
+inline unsigned ew_blocks(uint64_t n, int per_thread = 1) {
+    uint64_t b = (n + (uint64_t)EW_THREADS * per_thread - 1) / ((uint64_t)EW_THREADS * per_thread);
+    if (b < 1) b = 1;
+    if (b > 1u << 20) b = 1u << 20;
+    return (unsigned)b;
+}
+
+// binary_float_acc, cpu/float_kernels.rs:252-296: widen, op, narrow.
+__global__ void binary_kernel(int op, const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ out,
+                              uint64_t n, int dtype) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float va = holo::load_float(a, i, dtype), vb = holo::load_float(b, i, dtype);
+        holo::store_float(out, i, op == 0 ? __fadd_rn(va, vb) : __fmul_rn(va, vb), dtype);
+    }
+}
+
+// 16-bit fast path: eight elements per thread through 128-bit loads and stores.
+__global__ void binary16_vec_kernel(int op, const uint4* __restrict__ a, const uint4* __restrict__ b,
+                                    uint4* __restrict__ out, uint64_t nvec, int dtype) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        uint4 va = a[i], vb = b[i], r;
+        const uint32_t* pa = &va.x;
+        const uint32_t* pb = &vb.x;
+        uint32_t* pr = &r.x;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            float a0 = holo::widen16((uint16_t)(pa[w] & 0xffffu), dtype), a1 = holo::widen16((uint16_t)(pa[w] >> 16), dtype);
+            float b0 = holo::widen16((uint16_t)(pb[w] & 0xffffu), dtype), b1 = holo::widen16((uint16_t)(pb[w] >> 16), dtype);
+            float r0 = op == 0 ? __fadd_rn(a0, b0) : __fmul_rn(a0, b0);
+            float r1 = op == 0 ? __fadd_rn(a1, b1) : __fmul_rn(a1, b1);
+            pr[w] = (uint32_t)holo::narrow16(r0, dtype) | ((uint32_t)holo::narrow16(r1, dtype) << 16);
+        }
+        out[i] = r;
+    }
+}
+
+// rms_norm_float, cpu/float_kernels.rs:1683-1756: inv = 1/sqrt(sumsq/f + eps),
+// out = x * inv * gamma (left to right). One CTA per row.
+__global__ void rms_norm_kernel(const void* __restrict__ x, const void* __restrict__ gamma, void* __restrict__ out,
+                                uint32_t feature, float eps, int dtype) {
+    __shared__ float s_part[32];
+    __shared__ float s_inv;
+    const uint64_t off = (uint64_t)blockIdx.x * feature;
+    float acc = 0.0f;
+    for (uint32_t j = threadIdx.x; j < feature; j += blockDim.x) {
+        float v = holo::load_float(x, off + j, dtype);
+        acc = fmaf(v, v, acc);
+    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? s_part[threadIdx.x] : 0.0f;
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (threadIdx.x == 0) s_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)feature), eps)));
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    for (uint32_t j = threadIdx.x; j < feature; j += blockDim.x) {
+        float g = gamma ? holo::load_float(gamma, j, dtype) : 1.0f;
+        float v = __fmul_rn(__fmul_rn(holo::load_float(x, off + j, dtype), inv), g);
+        holo::store_float(out, off + j, v, dtype);
+    }
+}
+
+// rope_float, cpu/float_kernels.rs:3123-3190 (rotate-half; cos/sin share x's layout).
+__global__ void rope_kernel(const void* __restrict__ x, const void* __restrict__ c, const void* __restrict__ s,
+                            void* __restrict__ out, uint32_t d, uint64_t n, int dtype) {
+    const uint32_t half = d >> 1;
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
+        uint32_t pos = (uint32_t)(e % d);
+        uint64_t base = e - pos;
+        float xe = holo::load_float(x, e, dtype), ce = holo::load_float(c, e, dtype), se = holo::load_float(s, e, dtype);
+        float v;
+        if (pos < half) v = __fsub_rn(__fmul_rn(xe, ce), __fmul_rn(holo::load_float(x, base + pos + half, dtype), se));
+        else v = __fadd_rn(__fmul_rn(xe, ce), __fmul_rn(holo::load_float(x, base + pos - half, dtype), se));
+        holo::store_float(out, e, v, dtype);
+    }
+}
+
+// gather, cpu/kernels.rs:389-446: out[o,k,:] = data[o, idx[k], :]; negative indices wrap;
+// an out-of-range index raises bit 0 of the status word and copies nothing.
+__global__ void gather_kernel(const uint8_t* __restrict__ data, const void* __restrict__ idx, int idx_dtype,
+                              uint8_t* __restrict__ out, uint64_t axis_dim, uint64_t row_bytes, uint64_t num_idx,
+                              uint32_t* status) {
+    const uint64_t o = blockIdx.y, k = blockIdx.x;
+    long long ix = idx_dtype == HOLO_DTYPE_I32 ? (long long)((const int32_t*)idx)[k] : ((const long long*)idx)[k];
+    if (ix < 0) ix += (long long)axis_dim;
+    if (ix < 0 || (uint64_t)ix >= axis_dim) {
+        if (threadIdx.x == 0) atomicOr(status, 1u);
+        return;
+    }
+    const uint8_t* src = data + (o * axis_dim + (uint64_t)ix) * row_bytes;
+    uint8_t* dst = out + (o * num_idx + k) * row_bytes;
+    if ((((uintptr_t)src | (uintptr_t)dst | row_bytes) & 15u) == 0) {
+        for (uint64_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
+            ((uint4*)dst)[i] = ((const uint4*)src)[i];
+    } else {
+        for (uint64_t i = threadIdx.x; i < row_bytes; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// cast, cpu/kernels.rs:560-594. Float sources travel through f64 in the reference; every
+// f16/bf16/f32 value is exact in f32 as well, so f32 is used as the carrier here.
+__device__ __forceinline__ double load_num(const void* p, uint64_t i, int dt) {
+    switch (dt) {
+        case HOLO_DTYPE_F32: case HOLO_DTYPE_F16: case HOLO_DTYPE_BF16: return (double)holo::load_float(p, i, dt);
+        case HOLO_DTYPE_F64: return ((const double*)p)[i];
+        case HOLO_DTYPE_BOOL: case HOLO_DTYPE_U8: return (double)((const uint8_t*)p)[i];
+        case HOLO_DTYPE_I8: return (double)((const int8_t*)p)[i];
+        case HOLO_DTYPE_I32: return (double)((const int32_t*)p)[i];
+        default: return (double)((const long long*)p)[i];
+    }
+}
+__global__ void cast_kernel(const void* __restrict__ in, int src, void* __restrict__ out, int dst, uint64_t n) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    const bool src_f = src >= HOLO_DTYPE_F16 && src <= HOLO_DTYPE_F64;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        if (dst == HOLO_DTYPE_F32 || dst == HOLO_DTYPE_F16 || dst == HOLO_DTYPE_BF16) {
+            holo::store_float(out, i, (float)load_num(in, i, src), dst);
+        } else {
+            long long v;
+            if (src_f) {
+                double t = trunc(load_num(in, i, src));
+                // Rust `f64 as i64`: saturating, NaN -> 0
+                v = t != t ? 0 : (t >= 9223372036854775808.0 ? LLONG_MAX : (t <= -9223372036854775808.0 ? LLONG_MIN : (long long)t));
+            } else if (src == HOLO_DTYPE_I64 || src == HOLO_DTYPE_U64) {
+                v = ((const long long*)in)[i];
+            } else {
+                v = (long long)load_num(in, i, src);
+            }
+            switch (dst) {
+                case HOLO_DTYPE_BOOL: ((uint8_t*)out)[i] = v != 0; break;
+                case HOLO_DTYPE_U8: ((uint8_t*)out)[i] = (uint8_t)v; break;
+                case HOLO_DTYPE_I8: ((int8_t*)out)[i] = (int8_t)v; break;
+                case HOLO_DTYPE_I32: ((int32_t*)out)[i] = (int32_t)v; break;
+                default: ((long long*)out)[i] = v; break;
+            }
+        }
+    }
+}
+
+// dequantize, cpu/kernels.rs:185-296: out = ((q - zp) as f32) * scale, channel = (i/inner) % channels.
+__global__ void dequantize_kernel(const void* __restrict__ in, int qdt, const float* __restrict__ scales,
+                                  const int32_t* __restrict__ zps, uint32_t channels, uint32_t inner, float scale,
+                                  int32_t zp, void* __restrict__ out, int dtype, uint64_t n) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        int q = qdt == HOLO_DTYPE_I8 ? (int)((const int8_t*)in)[i] : (int)((const uint8_t*)in)[i];
+        float s = scale;
+        int z = zp;
+        if (scales) {
+            uint64_t ch = (i / inner) % channels;
+            s = scales[ch];
+            z = zps ? zps[ch] : 0;
+        }
+        holo::store_float(out, i, __fmul_rn(__int2float_rn(q - z), s), dtype);
+    }
+}
+
+// kv_cache_write rows, cpu/kernels.rs:455-501: out[p][(pos + j) % bucket] = new[p][j].
+// `pos` is read on the device from its 4-byte operand (no host round-trip).
+__global__ void kv_write_rows_kernel(const uint8_t* __restrict__ newr, const uint32_t* __restrict__ pos,
+                                     uint8_t* __restrict__ out, uint32_t bucket, uint32_t new_rows, uint32_t row_bytes) {
+    const uint32_t p = blockIdx.y, j = blockIdx.x;
+    const uint32_t p0 = *pos % bucket;
+    const uint8_t* src = newr + ((uint64_t)p * new_rows + j) * row_bytes;
+    uint8_t* dst = out + ((uint64_t)p * bucket + (p0 + j) % bucket) * row_bytes;
+    if ((((uintptr_t)src | (uintptr_t)dst | row_bytes) & 15u) == 0) {
+        for (uint32_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) ((uint4*)dst)[i] = ((const uint4*)src)[i];
+    } else {
+        for (uint32_t i = threadIdx.x; i < row_bytes; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// quantize_row_i8 per row, cpu/simd.rs:4761-4785. One warp per row: max|a| by shuffles
+// (max is exact in any order), inv = 127/amax, t = a*inv, r = trunc(t ± 0.5) (saturating
+// cvt.rzi, NaN -> 0), clamp to ±127, scale = amax/127. A zero row gives zero codes, scale 0.
+__global__ void quantize_rows_kernel(const void* __restrict__ x, int dtype, uint64_t rows, uint32_t d,
+                                     int8_t* __restrict__ codes, float* __restrict__ scales) {
+    const uint64_t row = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint64_t off = row * d;
+    float amax = 0.0f;
+    for (uint32_t j = lane; j < d; j += 32) {
+        float v = holo::load_float(x, off + j, dtype);
+        float av = v < 0.0f ? -v : v;
+        if (av > amax) amax = av;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        float other = __shfl_xor_sync(0xffffffffu, amax, o);
+        if (other > amax) amax = other;
+    }
+    if (amax == 0.0f) {
+        for (uint32_t j = lane; j < d; j += 32) codes[off + j] = 0;
+        if (lane == 0) scales[row] = 0.0f;
+        return;
+    }
+    const float inv = __fdiv_rn(127.0f, amax);
+    for (uint32_t j = lane; j < d; j += 32) {
+        float t = __fmul_rn(holo::load_float(x, off + j, dtype), inv);
+        int r = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
+        r = max(-127, min(127, r));
+        codes[off + j] = (int8_t)r;
+    }
+    if (lane == 0) scales[row] = __fdiv_rn(amax, 127.0f);
+}
+
+// d % 128 == 0, 16-bit input, 8-byte aligned rows: each lane owns 4 consecutive elements
+// of every 128-element segment (one 64-bit load, one 32-bit store).
+__global__ void quantize_rows16_vec_kernel(const uint16_t* __restrict__ x, int dtype, uint64_t rows, uint32_t d,
+                                           int8_t* __restrict__ codes, float* __restrict__ scales) {
+    const uint64_t row = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint64_t off = row * d;
+    const uint32_t segs = d >> 7;
+    float amax = 0.0f;
+    for (uint32_t s = 0; s < segs; ++s) {
+        uint2 w = *reinterpret_cast<const uint2*>(x + off + s * 128 + lane * 4);
+        float v[4] = {holo::widen16((uint16_t)(w.x & 0xffffu), dtype), holo::widen16((uint16_t)(w.x >> 16), dtype),
+                      holo::widen16((uint16_t)(w.y & 0xffffu), dtype), holo::widen16((uint16_t)(w.y >> 16), dtype)};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float av = v[e] < 0.0f ? -v[e] : v[e];
+            if (av > amax) amax = av;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        float other = __shfl_xor_sync(0xffffffffu, amax, o);
+        if (other > amax) amax = other;
+    }
+    const bool zero = amax == 0.0f;
+    const float inv = zero ? 0.0f : __fdiv_rn(127.0f, amax);
+    for (uint32_t s = 0; s < segs; ++s) {
+        uint32_t packed = 0;
+        if (!zero) {
+            uint2 w = *reinterpret_cast<const uint2*>(x + off + s * 128 + lane * 4);
+            float v[4] = {holo::widen16((uint16_t)(w.x & 0xffffu), dtype), holo::widen16((uint16_t)(w.x >> 16), dtype),
+                          holo::widen16((uint16_t)(w.y & 0xffffu), dtype), holo::widen16((uint16_t)(w.y >> 16), dtype)};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float t = __fmul_rn(v[e], inv);
+                int r = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
+                r = max(-127, min(127, r));
+                packed |= ((uint32_t)r & 0xffu) << (8 * e);
+            }
+        }
+        *reinterpret_cast<uint32_t*>(codes + off + s * 128 + lane * 4) = packed;
+    }
+    if (lane == 0) scales[row] = zero ? 0.0f : __fdiv_rn(amax, 127.0f);
+}
+
+}  // namespace
+
+#define LAUNCH_CHECK(ctx)                 \
+    do {                                  \
+        HOLO_CUDA(cudaGetLastError());    \
+        (ctx)->launches++;                \
+    } while (0)
+
+int32_t holo_launch_binary(holo_b200_ctx* ctx, int op, const void* a, const void* b, void* out, uint64_t n, uint8_t dtype) {
+    if (n == 0) return HOLO_OK;
+    const bool aligned = (((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15u) == 0;
+    if (dtype != HOLO_DTYPE_F32 && aligned && (n % 8) == 0) {
+        binary16_vec_kernel<<<ew_blocks(n / 8), EW_THREADS, 0, ctx->stream>>>(op, (const uint4*)a, (const uint4*)b,
+                                                                             (uint4*)out, n / 8, dtype);
+    } else {
+        binary_kernel<<<ew_blocks(n), EW_THREADS, 0, ctx->stream>>>(op, a, b, out, n, dtype);
+    }
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* gamma, void* out, uint32_t batch,
+                             uint32_t feature, float eps, uint8_t dtype) {
+    if (batch == 0 || feature == 0) return HOLO_OK;
+    rms_norm_kernel<<<batch, 256, 0, ctx->stream>>>(x, gamma, out, feature, eps, dtype);
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_rope(holo_b200_ctx* ctx, const void* x, const void* c, const void* s, void* out, uint32_t head_dim,
+                         uint64_t n, uint8_t dtype) {
+    if (n == 0) return HOLO_OK;
+    rope_kernel<<<ew_blocks(n), EW_THREADS, 0, ctx->stream>>>(x, c, s, out, head_dim, n, dtype);
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_gather(holo_b200_ctx* ctx, const uint8_t* data, const void* idx, uint8_t idx_dtype, uint8_t* out,
+                           uint64_t outer, uint64_t axis_dim, uint64_t inner_bytes, uint64_t num_idx) {
+    if (outer == 0 || num_idx == 0 || inner_bytes == 0) return HOLO_OK;
+    if (outer > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "gather: outer %llu exceeds 65535", (unsigned long long)outer);
+    dim3 grid((unsigned)num_idx, (unsigned)outer);
+    gather_kernel<<<grid, 128, 0, ctx->stream>>>(data, idx, idx_dtype, out, axis_dim, inner_bytes, num_idx, ctx->dev_status);
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_cast(holo_b200_ctx* ctx, const void* in, uint8_t src, void* out, uint8_t dst, uint64_t n) {
+    if (n == 0) return HOLO_OK;
+    cast_kernel<<<ew_blocks(n), EW_THREADS, 0, ctx->stream>>>(in, src, out, dst, n);
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_dequantize(holo_b200_ctx* ctx, const HoloDequantizeCall& c, const void* in, const float* scales,
+                               const int32_t* zps, void* out) {
+    if (c.element_count == 0) return HOLO_OK;
+    float scale;
+    uint32_t sb = c.scale_bits;
+    memcpy(&scale, &sb, 4);
+    dequantize_kernel<<<ew_blocks(c.element_count), EW_THREADS, 0, ctx->stream>>>(
+        in, c.quant_dtype, scales, zps, c.channels, c.inner ? c.inner : 1, scale, c.zero_point, out, c.dtype,
+        c.element_count);
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_kv_write(holo_b200_ctx* ctx, const uint8_t* cache, const uint8_t* newr, const uint32_t* pos,
+                             uint8_t* out, uint32_t planes, uint32_t bucket, uint32_t new_rows, uint32_t row_bytes) {
+    if (planes == 0) return HOLO_OK;
+    if (out != cache)
+        HOLO_CUDA(cudaMemcpyAsync(out, cache, (size_t)planes * bucket * row_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    if (new_rows == 0) return HOLO_OK;
+    if (planes > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "kv_cache_write: planes %u exceeds 65535", planes);
+    dim3 grid(new_rows, planes);
+    kv_write_rows_kernel<<<grid, 32, 0, ctx->stream>>>(newr, pos, out, bucket, new_rows, row_bytes);
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_quantize_rows(holo_b200_ctx* ctx, const void* x, uint8_t dtype, uint64_t rows, uint32_t d,
+                                  int8_t* codes, float* scales) {
+    if (rows == 0 || d == 0) return HOLO_OK;
+    const int warps = 8;
+    uint64_t blocks = (rows + warps - 1) / warps;
+    if (blocks > 0x7fffffffull) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "quantize_rows_i8: too many rows");
+    const bool vec = dtype != HOLO_DTYPE_F32 && (d % 128) == 0 && (((uintptr_t)x & 7u) == 0) && (((uintptr_t)codes & 3u) == 0);
+    if (vec)
+        quantize_rows16_vec_kernel<<<(unsigned)blocks, warps * 32, 0, ctx->stream>>>((const uint16_t*)x, dtype, rows, d, codes, scales);
+    else
+        quantize_rows_kernel<<<(unsigned)blocks, warps * 32, 0, ctx->stream>>>(x, dtype, rows, d, codes, scales);
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}

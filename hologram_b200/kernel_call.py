@@ -1,0 +1,216 @@
+"""ctypes mirror of include/hologram_b200.h: the `KernelCall` tagged union and its payloads.
+
+Names follow the reference (crates/hologram-compute/src/kernel_call.rs): BufferRef,
+UnaryCall, MatMulCall, DecodeAttentionValidCall ... so tests read like the reference's own.
+"""
+import ctypes as C
+
+# dtype tags (crates/hologram-types/src/dtype_id.rs:51-74)
+DTYPE_BOOL, DTYPE_U8, DTYPE_I8, DTYPE_U64, DTYPE_I32, DTYPE_I64 = 0, 1, 2, 3, 4, 5
+DTYPE_F16, DTYPE_BF16, DTYPE_F32, DTYPE_F64 = 6, 7, 8, 9
+
+# lut_act ids (kernel_call.rs:877-885)
+LUT_SIGMOID, LUT_TANH, LUT_GELU, LUT_SILU, LUT_EXP, LUT_ERF = 0, 1, 2, 3, 4, 5
+LUT_NAMES = {LUT_SIGMOID: "sigmoid", LUT_TANH: "tanh", LUT_GELU: "gelu", LUT_SILU: "silu", LUT_EXP: "exp", LUT_ERF: "erf"}
+
+# fused_activation ids (kernel_call.rs:861-870)
+FUSED_RELU, FUSED_GELU, FUSED_SILU, FUSED_SIGMOID, FUSED_TANH, FUSED_EXP = 1, 2, 3, 4, 5, 8
+
+# variant tags = archive wire discriminants (crates/hologram-archive/src/kernel_codec.rs:19-128)
+K_ADD, K_MUL = 5, 7
+K_SIGMOID, K_TANH, K_GELU, K_SILU, K_EXP, K_ERF = 12, 13, 14, 15, 18, 32
+K_MATMUL, K_RMS_NORM, K_RESHAPE, K_ROTARY = 46, 51, 60, 75
+K_DEQUANTIZE, K_MATMUL_ACTIVATION, K_MATMUL_ADD = 105, 106, 107
+K_GATHER, K_CAST, K_KV_CACHE_WRITE, K_DECODE_ATTENTION_VALID = 114, 115, 120, 121
+K_QUANTIZE_ROWS_I8, K_DECODE_ATTENTION_VALID_Q8, K_ALL_REDUCE = 0x8001, 0x8002, 0x8003
+LUT_KIND = {LUT_SIGMOID: K_SIGMOID, LUT_TANH: K_TANH, LUT_GELU: K_GELU, LUT_SILU: K_SILU, LUT_EXP: K_EXP, LUT_ERF: K_ERF}
+
+NO_SLOT = 0xFFFFFFFF
+
+# status codes (crates/hologram-compute/src/error.rs:6-20)
+OK, ERR_SLOT_OUT_OF_RANGE, ERR_SHAPE_MISMATCH, ERR_UNSUPPORTED_OP, ERR_INIT, ERR_DISPATCH = 0, -1, -2, -3, -4, -5
+
+
+class BufferRef(C.Structure):
+    _fields_ = [("slot", C.c_uint32), ("offset", C.c_uint64), ("length", C.c_uint64)]
+
+
+def rb(slot, offset=0, length=0):
+    """BufferRef over a whole slot (the reference tests' `rb` helper, tests/lut.rs:51-57)."""
+    return BufferRef(slot, offset, length)
+
+
+NONE = BufferRef(NO_SLOT, 0, 0)
+
+
+class UnaryCall(C.Structure):
+    _fields_ = [("input", BufferRef), ("output", BufferRef), ("element_count", C.c_uint64),
+                ("witt_bits", C.c_uint16), ("dtype", C.c_uint8)]
+
+
+class BinaryCall(C.Structure):
+    _fields_ = [("a", BufferRef), ("b", BufferRef), ("output", BufferRef), ("element_count", C.c_uint64),
+                ("witt_bits", C.c_uint16), ("dtype", C.c_uint8)]
+
+
+class MatMulCall(C.Structure):
+    _fields_ = [("a", BufferRef), ("b", BufferRef), ("output", BufferRef), ("m", C.c_uint32), ("k", C.c_uint32),
+                ("n", C.c_uint32), ("dtype", C.c_uint8), ("b_packed", C.c_uint8)]
+
+
+class MatMulActivationCall(C.Structure):
+    _fields_ = [("mm", MatMulCall), ("act", C.c_uint8)]
+
+
+class MatMulAddCall(C.Structure):
+    _fields_ = [("mm", MatMulCall), ("residual", BufferRef)]
+
+
+class NormCall(C.Structure):
+    _fields_ = [("x", BufferRef), ("gamma", BufferRef), ("beta", BufferRef), ("residual", BufferRef),
+                ("output", BufferRef), ("batch", C.c_uint32), ("feature", C.c_uint32), ("channels", C.c_uint32),
+                ("num_groups", C.c_uint32), ("epsilon_bits", C.c_uint64), ("dtype", C.c_uint8)]
+
+
+class RoPECall(C.Structure):
+    _fields_ = [("x", BufferRef), ("cos", BufferRef), ("sin", BufferRef), ("output", BufferRef),
+                ("head_dim", C.c_uint32), ("element_count", C.c_uint64), ("dtype", C.c_uint8)]
+
+
+class GatherCall(C.Structure):
+    _fields_ = [("data", BufferRef), ("indices", BufferRef), ("output", BufferRef), ("outer", C.c_uint64),
+                ("axis_dim", C.c_uint64), ("inner", C.c_uint64), ("num_indices", C.c_uint64),
+                ("idx_dtype", C.c_uint8), ("dtype", C.c_uint8)]
+
+
+class CastCall(C.Structure):
+    _fields_ = [("input", BufferRef), ("output", BufferRef), ("element_count", C.c_uint64),
+                ("src_dtype", C.c_uint8), ("dst_dtype", C.c_uint8)]
+
+
+class LayoutCall(C.Structure):
+    _fields_ = [("input", BufferRef), ("output", BufferRef), ("element_count", C.c_uint64), ("dtype", C.c_uint8)]
+
+
+class DequantizeCall(C.Structure):
+    _fields_ = [("input", BufferRef), ("scales", BufferRef), ("zero_points", BufferRef), ("output", BufferRef),
+                ("element_count", C.c_uint64), ("channels", C.c_uint32), ("inner", C.c_uint32),
+                ("quant_dtype", C.c_uint8), ("dtype", C.c_uint8), ("scale_bits", C.c_uint32),
+                ("zero_point", C.c_int32)]
+
+
+class KvCacheWriteCall(C.Structure):
+    _fields_ = [("cache", BufferRef), ("new", BufferRef), ("pos", BufferRef), ("output", BufferRef),
+                ("planes", C.c_uint32), ("bucket_rows", C.c_uint32), ("new_rows", C.c_uint32),
+                ("row_bytes", C.c_uint32)]
+
+
+class DecodeAttentionValidCall(C.Structure):
+    _fields_ = [("q", BufferRef), ("k_past", BufferRef), ("v_past", BufferRef), ("k_new", BufferRef),
+                ("v_new", BufferRef), ("valid_len", BufferRef), ("output", BufferRef), ("batch", C.c_uint32),
+                ("heads", C.c_uint32), ("kv_heads", C.c_uint32), ("q_rows", C.c_uint32), ("past_len", C.c_uint32),
+                ("new_len", C.c_uint32), ("head_dim", C.c_uint32), ("scale_bits", C.c_uint32), ("dtype", C.c_uint8)]
+
+
+class QuantizeRowsI8Call(C.Structure):
+    _fields_ = [("input", BufferRef), ("codes", BufferRef), ("scales", BufferRef), ("rows", C.c_uint64),
+                ("row_len", C.c_uint32), ("dtype", C.c_uint8)]
+
+
+class DecodeAttentionValidQ8Call(C.Structure):
+    _fields_ = [("q", BufferRef), ("k_past", BufferRef), ("k_past_scales", BufferRef), ("v_past", BufferRef),
+                ("v_past_scales", BufferRef), ("k_new", BufferRef), ("k_new_scales", BufferRef), ("v_new", BufferRef),
+                ("v_new_scales", BufferRef), ("valid_len", BufferRef), ("output", BufferRef), ("batch", C.c_uint32),
+                ("heads", C.c_uint32), ("kv_heads", C.c_uint32), ("q_rows", C.c_uint32), ("past_len", C.c_uint32),
+                ("new_len", C.c_uint32), ("head_dim", C.c_uint32), ("scale_bits", C.c_uint32), ("dtype", C.c_uint8)]
+
+
+class AllReduceCall(C.Structure):
+    _fields_ = [("buffer", BufferRef), ("element_count", C.c_uint64), ("dtype", C.c_uint8)]
+
+
+class _Payload(C.Union):
+    _fields_ = [("unary", UnaryCall), ("binary", BinaryCall), ("matmul", MatMulCall),
+                ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("norm", NormCall),
+                ("rope", RoPECall), ("gather", GatherCall), ("cast", CastCall), ("layout", LayoutCall),
+                ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
+                ("decode_attention_valid", DecodeAttentionValidCall), ("quantize_rows_i8", QuantizeRowsI8Call),
+                ("decode_attention_valid_q8", DecodeAttentionValidQ8Call), ("all_reduce", AllReduceCall)]
+
+
+class KernelCall(C.Structure):
+    """`enum KernelCall` (kernel_call.rs:1146-1276) as tag + union."""
+    _fields_ = [("kind", C.c_uint16), ("u", _Payload)]
+
+    _FIELD = {}
+
+    @classmethod
+    def of(cls, kind, payload):
+        kc = cls()
+        kc.kind = kind
+        setattr(kc.u, cls._FIELD[type(payload)], payload)
+        return kc
+
+    # constructors named after the reference variants
+    @classmethod
+    def Sigmoid(cls, c): return cls.of(K_SIGMOID, c)
+    @classmethod
+    def Tanh(cls, c): return cls.of(K_TANH, c)
+    @classmethod
+    def Gelu(cls, c): return cls.of(K_GELU, c)
+    @classmethod
+    def Silu(cls, c): return cls.of(K_SILU, c)
+    @classmethod
+    def Exp(cls, c): return cls.of(K_EXP, c)
+    @classmethod
+    def Erf(cls, c): return cls.of(K_ERF, c)
+    @classmethod
+    def Add(cls, c): return cls.of(K_ADD, c)
+    @classmethod
+    def Mul(cls, c): return cls.of(K_MUL, c)
+    @classmethod
+    def MatMul(cls, c): return cls.of(K_MATMUL, c)
+    @classmethod
+    def MatMulActivation(cls, c): return cls.of(K_MATMUL_ACTIVATION, c)
+    @classmethod
+    def MatMulAdd(cls, c): return cls.of(K_MATMUL_ADD, c)
+    @classmethod
+    def RmsNorm(cls, c): return cls.of(K_RMS_NORM, c)
+    @classmethod
+    def RotaryEmbedding(cls, c): return cls.of(K_ROTARY, c)
+    @classmethod
+    def Gather(cls, c): return cls.of(K_GATHER, c)
+    @classmethod
+    def Cast(cls, c): return cls.of(K_CAST, c)
+    @classmethod
+    def Reshape(cls, c): return cls.of(K_RESHAPE, c)
+    @classmethod
+    def Dequantize(cls, c): return cls.of(K_DEQUANTIZE, c)
+    @classmethod
+    def KvCacheWrite(cls, c): return cls.of(K_KV_CACHE_WRITE, c)
+    @classmethod
+    def DecodeAttentionValid(cls, c): return cls.of(K_DECODE_ATTENTION_VALID, c)
+    @classmethod
+    def QuantizeRowsI8(cls, c): return cls.of(K_QUANTIZE_ROWS_I8, c)
+    @classmethod
+    def DecodeAttentionValidQ8(cls, c): return cls.of(K_DECODE_ATTENTION_VALID_Q8, c)
+    @classmethod
+    def AllReduce(cls, c): return cls.of(K_ALL_REDUCE, c)
+
+
+KernelCall._FIELD = {
+    UnaryCall: "unary", BinaryCall: "binary", MatMulCall: "matmul", MatMulActivationCall: "matmul_activation",
+    MatMulAddCall: "matmul_add", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
+    LayoutCall: "layout", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
+    DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
+    DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce",
+}
+
+
+class HostSlot(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("bytes", C.c_uint64)]
+
+
+def lut_call(act, c):
+    """KernelCall for LUT activation id `act` over UnaryCall `c`."""
+    return KernelCall.of(LUT_KIND[act], c)

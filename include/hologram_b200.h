@@ -1,0 +1,334 @@
+/*
+ * hologram_b200.h — C ABI of the B200 (sm_100a) backend for hologram's tensor engine.
+ *
+ * The library is a drop-in for ONE boundary of the reference: `Backend::dispatch(&KernelCall,
+ * &mut Workspace)` (crates/hologram-compute/src/backend.rs:8-15). A Rust `impl Backend` (see
+ * INTEGRATION.md) forwards each call through `holo_b200_dispatch`; everything above that
+ * boundary (compiler, archive, session walk) stays the reference's.
+ *
+ * Conventions follow crates/hologram-ffi (src/lib.rs:48-92): every function returns an
+ * int32_t status (0 = ok, negative = one `BackendError` variant), the text of the last
+ * failure is thread-local, the caller owns every struct it passes, nothing returned is
+ * heap-owned by the callee except opaque handles with an explicit destroy call.
+ *
+ * No torch types appear here: plain pointers, sizes, PODs. There is no CPU fallback:
+ * an op/dtype the backend does not implement returns HOLO_ERR_UNSUPPORTED_OP.
+ */
+#ifndef HOLOGRAM_B200_H
+#define HOLOGRAM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes: one per BackendError variant (crates/hologram-compute/src/error.rs:6-20) */
+#define HOLO_OK 0
+#define HOLO_ERR_SLOT_OUT_OF_RANGE (-1) /* BackendError::SlotOutOfRange(slot) */
+#define HOLO_ERR_SHAPE_MISMATCH (-2)    /* BackendError::ShapeMismatch{..}   */
+#define HOLO_ERR_UNSUPPORTED_OP (-3)    /* BackendError::UnsupportedOp(msg)   */
+#define HOLO_ERR_INIT (-4)              /* BackendError::Init(msg)            */
+#define HOLO_ERR_DISPATCH (-5)          /* BackendError::Dispatch(msg)        */
+
+/* ---- dtype tags: DTypeId (crates/hologram-types/src/dtype_id.rs:51-74), wire-stable u8 */
+#define HOLO_DTYPE_BOOL 0
+#define HOLO_DTYPE_U8 1
+#define HOLO_DTYPE_I8 2
+#define HOLO_DTYPE_U64 3
+#define HOLO_DTYPE_I32 4
+#define HOLO_DTYPE_I64 5
+#define HOLO_DTYPE_F16 6
+#define HOLO_DTYPE_BF16 7
+#define HOLO_DTYPE_F32 8
+#define HOLO_DTYPE_F64 9
+
+/* ---- lut_act ids (crates/hologram-compute/src/kernel_call.rs:877-885) */
+#define HOLO_LUT_SIGMOID 0
+#define HOLO_LUT_TANH 1
+#define HOLO_LUT_GELU 2
+#define HOLO_LUT_SILU 3
+#define HOLO_LUT_EXP 4
+#define HOLO_LUT_ERF 5
+#define HOLO_LUT_COUNT 6
+
+/* ---- fused_activation ids (kernel_call.rs:861-870) */
+#define HOLO_FUSED_RELU 1
+#define HOLO_FUSED_GELU 2
+#define HOLO_FUSED_SILU 3
+#define HOLO_FUSED_SIGMOID 4
+#define HOLO_FUSED_TANH 5
+#define HOLO_FUSED_EXP 8
+
+/* ---- KernelCall variant tags. Values are the archive wire discriminants
+ * (crates/hologram-archive/src/kernel_codec.rs:19-128) so a decoded .holo call list maps
+ * 1:1. Tags >= 0x8000 are extensions with no reference counterpart (documented below). */
+#define HOLO_K_ADD 5
+#define HOLO_K_MUL 7
+#define HOLO_K_SIGMOID 12
+#define HOLO_K_TANH 13
+#define HOLO_K_GELU 14
+#define HOLO_K_SILU 15
+#define HOLO_K_EXP 18
+#define HOLO_K_ERF 32
+#define HOLO_K_MATMUL 46
+#define HOLO_K_RMS_NORM 51
+#define HOLO_K_RESHAPE 60
+#define HOLO_K_ROTARY 75
+#define HOLO_K_DEQUANTIZE 105
+#define HOLO_K_MATMUL_ACTIVATION 106
+#define HOLO_K_MATMUL_ADD 107
+#define HOLO_K_GATHER 114
+#define HOLO_K_CAST 115
+#define HOLO_K_KV_CACHE_WRITE 120
+#define HOLO_K_DECODE_ATTENTION_VALID 121
+/* Extensions (the reference has no KV quantizer op and no quantized-KV attention):
+ * QUANTIZE_ROWS_I8 applies the reference's only f32->i8 quantizer, `quantize_row_i8`
+ * (crates/hologram-compute/src/cpu/simd.rs:4761-4785), to every row;
+ * DECODE_ATTENTION_VALID_Q8 is DecodeAttentionValid over Dequantize'd int8 K/V;
+ * ALL_REDUCE is the tensor-parallel sum after o-proj / down-proj. */
+#define HOLO_K_QUANTIZE_ROWS_I8 0x8001
+#define HOLO_K_DECODE_ATTENTION_VALID_Q8 0x8002
+#define HOLO_K_ALL_REDUCE 0x8003
+
+/* BufferRef (crates/hologram-compute/src/workspace.rs:16-24). length == 0 means "the slot's
+ * full extent from offset". slot == UINT32_MAX marks an absent optional operand
+ * (kernel_call.rs:217-228, 450-458). */
+typedef struct HoloBufferRef {
+    uint32_t slot;
+    uint64_t offset;
+    uint64_t length;
+} HoloBufferRef;
+#define HOLO_NO_SLOT 0xFFFFFFFFu
+
+/* UnaryCall (kernel_call.rs:30-36) */
+typedef struct HoloUnaryCall {
+    HoloBufferRef input, output;
+    uint64_t element_count;
+    uint16_t witt_bits;
+    uint8_t dtype;
+} HoloUnaryCall;
+
+/* BinaryCall (kernel_call.rs:38-46) */
+typedef struct HoloBinaryCall {
+    HoloBufferRef a, b, output;
+    uint64_t element_count;
+    uint16_t witt_bits;
+    uint8_t dtype;
+} HoloBinaryCall;
+
+/* MatMulCall (kernel_call.rs:49-65): A [m,k] row-major, B [k,n] row-major, f32 accumulation */
+typedef struct HoloMatMulCall {
+    HoloBufferRef a, b, output;
+    uint32_t m, k, n;
+    uint8_t dtype;
+    uint8_t b_packed; /* must be 0: panel packing is f32-only in the reference (compiler.rs:609) */
+} HoloMatMulCall;
+
+/* MatMulActivationCall (kernel_call.rs:887-897) */
+typedef struct HoloMatMulActivationCall {
+    HoloMatMulCall mm;
+    uint8_t act; /* HOLO_FUSED_* */
+} HoloMatMulActivationCall;
+
+/* MatMulAddCall (kernel_call.rs:899-911) */
+typedef struct HoloMatMulAddCall {
+    HoloMatMulCall mm;
+    HoloBufferRef residual;
+} HoloMatMulAddCall;
+
+/* NormCall (kernel_call.rs:423-446); RmsNorm uses x, gamma, output, batch, feature, epsilon_bits */
+typedef struct HoloNormCall {
+    HoloBufferRef x, gamma, beta, residual, output;
+    uint32_t batch, feature, channels, num_groups;
+    uint64_t epsilon_bits;
+    uint8_t dtype;
+} HoloNormCall;
+
+/* RoPECall (kernel_call.rs:506-514): cos/sin are full tensors with x's element layout */
+typedef struct HoloRoPECall {
+    HoloBufferRef x, cos, sin, output;
+    uint32_t head_dim;
+    uint64_t element_count;
+    uint8_t dtype;
+} HoloRoPECall;
+
+/* GatherCall (kernel_call.rs:387-403) */
+typedef struct HoloGatherCall {
+    HoloBufferRef data, indices, output;
+    uint64_t outer, axis_dim, inner, num_indices;
+    uint8_t idx_dtype, dtype;
+} HoloGatherCall;
+
+/* CastCall (kernel_call.rs:411-419) */
+typedef struct HoloCastCall {
+    HoloBufferRef input, output;
+    uint64_t element_count;
+    uint8_t src_dtype, dst_dtype;
+} HoloCastCall;
+
+/* LayoutCall (kernel_call.rs:479-485): Reshape is a byte copy when dispatched */
+typedef struct HoloLayoutCall {
+    HoloBufferRef input, output;
+    uint64_t element_count;
+    uint8_t dtype;
+} HoloLayoutCall;
+
+/* DequantizeCall (kernel_call.rs:782-818); i8/u8 sources, per-tensor or per-channel */
+typedef struct HoloDequantizeCall {
+    HoloBufferRef input, scales, zero_points, output;
+    uint64_t element_count;
+    uint32_t channels, inner;
+    uint8_t quant_dtype, dtype;
+    uint32_t scale_bits;
+    int32_t zero_point;
+} HoloDequantizeCall;
+
+/* KvCacheWriteCall (kernel_call.rs:742-759). When cache and output resolve to the same
+ * device range the write is the O(new_rows) in-place move the executor performs
+ * (crates/hologram-exec/src/session.rs:1313-1370); otherwise the honest O(bucket) copy. */
+typedef struct HoloKvCacheWriteCall {
+    HoloBufferRef cache, new_rows_buf, pos, output;
+    uint32_t planes, bucket_rows, new_rows, row_bytes;
+} HoloKvCacheWriteCall;
+
+/* DecodeAttentionValidCall (kernel_call.rs:691-716) */
+typedef struct HoloDecodeAttentionValidCall {
+    HoloBufferRef q, k_past, v_past, k_new, v_new, valid_len, output;
+    uint32_t batch, heads, kv_heads, q_rows, past_len, new_len, head_dim, scale_bits;
+    uint8_t dtype;
+} HoloDecodeAttentionValidCall;
+
+/* Extension. Rows of `row_len` values of `dtype` (f32/bf16/f16) -> i8 codes [rows,row_len]
+ * and f32 scales [rows], bit-for-bit `quantize_row_i8` (simd.rs:4761-4785); an all-zero row
+ * gives zero codes and scale 0.0. */
+typedef struct HoloQuantizeRowsI8Call {
+    HoloBufferRef input, codes, scales;
+    uint64_t rows;
+    uint32_t row_len;
+    uint8_t dtype;
+} HoloQuantizeRowsI8Call;
+
+/* Extension. DecodeAttentionValid whose K/V operands are int8 codes [b,kv,rows,d] with f32
+ * per-row scales [b,kv,rows]; q and output have `dtype`. Defined as the reference
+ * composition Cast(q) / Dequantize(K,V per row, zero-point 0) / DecodeAttentionValid(f32) /
+ * Cast(output). */
+typedef struct HoloDecodeAttentionValidQ8Call {
+    HoloBufferRef q, k_past, k_past_scales, v_past, v_past_scales;
+    HoloBufferRef k_new, k_new_scales, v_new, v_new_scales, valid_len, output;
+    uint32_t batch, heads, kv_heads, q_rows, past_len, new_len, head_dim, scale_bits;
+    uint8_t dtype;
+} HoloDecodeAttentionValidQ8Call;
+
+/* Extension. In-place sum over the context's tensor-parallel group (NCCL); a no-op when the
+ * context has no group. */
+typedef struct HoloAllReduceCall {
+    HoloBufferRef buffer;
+    uint64_t element_count;
+    uint8_t dtype;
+} HoloAllReduceCall;
+
+/* The tagged union standing in for `enum KernelCall` (kernel_call.rs:1146-1276). */
+typedef struct HoloKernelCall {
+    uint16_t kind; /* HOLO_K_* */
+    union {
+        HoloUnaryCall unary;            /* SIGMOID TANH GELU SILU EXP ERF */
+        HoloBinaryCall binary;          /* ADD MUL */
+        HoloMatMulCall matmul;          /* MATMUL */
+        HoloMatMulActivationCall matmul_activation;
+        HoloMatMulAddCall matmul_add;
+        HoloNormCall norm;              /* RMS_NORM */
+        HoloRoPECall rope;              /* ROTARY */
+        HoloGatherCall gather;
+        HoloCastCall cast;
+        HoloLayoutCall layout;          /* RESHAPE */
+        HoloDequantizeCall dequantize;
+        HoloKvCacheWriteCall kv_cache_write;
+        HoloDecodeAttentionValidCall decode_attention_valid;
+        HoloQuantizeRowsI8Call quantize_rows_i8;
+        HoloDecodeAttentionValidQ8Call decode_attention_valid_q8;
+        HoloAllReduceCall all_reduce;
+    } u;
+} HoloKernelCall;
+
+typedef struct holo_b200_ctx holo_b200_ctx;             /* per-GPU backend state (the `Backend` impl) */
+typedef struct holo_b200_workspace holo_b200_workspace; /* device-resident `Workspace` */
+
+/* ---- errors (hologram-ffi src/lib.rs:48-92 convention) */
+/* Text of the calling thread's last failure ("" if none). Valid until the next failing call
+ * on this thread. */
+const char* holo_b200_last_error(void);
+/* The slot number attached to the last HOLO_ERR_SLOT_OUT_OF_RANGE on this thread. */
+uint32_t holo_b200_last_error_slot(void);
+
+/* ---- context: replaces `CpuBackend::new()` (crates/hologram-compute/src/cpu.rs:60-86).
+ * Creates a stream on `device`, uploads nothing yet; LUT tables are built on device on first
+ * use of each (activation, dtype) pair, as cpu/lut.rs:38-72 does lazily on the host. */
+int32_t holo_b200_ctx_create(int32_t device, holo_b200_ctx** out);
+void holo_b200_ctx_destroy(holo_b200_ctx* ctx);
+/* The CUDA stream (cudaStream_t) every dispatch is ordered on. */
+void* holo_b200_ctx_stream(holo_b200_ctx* ctx);
+/* Order every later dispatch on a caller-owned stream instead (e.g. the host framework's
+ * current stream, so its events bracket these kernels). */
+int32_t holo_b200_ctx_set_stream(holo_b200_ctx* ctx, void* cuda_stream);
+/* Wait for the stream; also reports device-side failures recorded since the last check
+ * (an out-of-range Gather index, a bounded wait that gave up). */
+int32_t holo_b200_ctx_synchronize(holo_b200_ctx* ctx);
+/* Number of this library's kernels launched through the context since creation. */
+uint64_t holo_b200_ctx_launch_count(holo_b200_ctx* ctx);
+/* Install a 65536-entry table for (lut_act, dtype) instead of the built-in one (tables are
+ * data: a table generated by the reference itself can be dropped in unchanged). */
+int32_t holo_b200_ctx_set_lut_table(holo_b200_ctx* ctx, uint8_t lut_act, uint8_t dtype, const uint16_t* table65536);
+/* Copy the table in use for (lut_act, dtype) to the host. */
+int32_t holo_b200_ctx_get_lut_table(holo_b200_ctx* ctx, uint8_t lut_act, uint8_t dtype, uint16_t* table65536);
+
+/* ---- device workspace: replaces the `Workspace` trait object the executor passes
+ * (workspace.rs:26-55; implemented by BufferArena, crates/hologram-exec/src/buffer.rs:955-999).
+ * A table of `n_slots` slots, each bound to a device range. */
+int32_t holo_b200_workspace_create(holo_b200_ctx* ctx, uint32_t n_slots, holo_b200_workspace** out);
+void holo_b200_workspace_destroy(holo_b200_workspace* ws);
+/* Allocate (or re-allocate) an owned, zero-filled device buffer of `bytes` for `slot`
+ * (bind_fresh, buffer.rs:427; zero-on-reuse, buffer.rs:86-108). 256-byte aligned. */
+int32_t holo_b200_workspace_alloc(holo_b200_workspace* ws, uint32_t slot, uint64_t bytes);
+/* Bind `slot` to caller-owned device memory (bind_resident / bind_view, buffer.rs:437;
+ * a memo hit is this pointer rebind, no host round-trip). */
+int32_t holo_b200_workspace_bind(holo_b200_workspace* ws, uint32_t slot, void* device_ptr, uint64_t bytes);
+/* Device pointer and extent of a slot. */
+int32_t holo_b200_workspace_slot(holo_b200_workspace* ws, uint32_t slot, void** device_ptr, uint64_t* bytes);
+/* Host <-> device copies of a slot range (Workspace::write / ::read at graph boundaries;
+ * resolve, buffer.rs:887). Ordered on the context stream; download synchronises. */
+int32_t holo_b200_workspace_upload(holo_b200_workspace* ws, HoloBufferRef dst, const void* host, uint64_t bytes);
+int32_t holo_b200_workspace_download(holo_b200_workspace* ws, HoloBufferRef src, void* host, uint64_t bytes);
+
+/* ---- dispatch: replaces `Backend::dispatch` (backend.rs:12-14; CPU body cpu/kernels.rs:16-181).
+ * Validates geometry and slot extents first (fail loud, nothing written on error), then
+ * enqueues the kernel(s) on the context stream and returns without synchronising. */
+int32_t holo_b200_dispatch(holo_b200_ctx* ctx, const HoloKernelCall* call, holo_b200_workspace* ws);
+
+/* Host-memory workspace form: the call's BufferRefs index `host_slots` (pointer + byte size
+ * per slot, the reference tests' `TestWorkspace { slots: Vec<Vec<u8>> }`, tests/lut.rs:13-49).
+ * Operands are staged to the device, the call dispatched, the output range copied back, and
+ * the call returns after synchronising — the per-call upload/dispatch/readback shape of the
+ * reference's own GPU backends (wgpu_backend/mod.rs:157-268). Host buffers should be pinned
+ * for full transfer speed but need not be. */
+typedef struct HoloHostSlot {
+    void* ptr;
+    uint64_t bytes;
+} HoloHostSlot;
+int32_t holo_b200_dispatch_host(holo_b200_ctx* ctx, const HoloKernelCall* call, HoloHostSlot* host_slots,
+                                uint32_t n_slots);
+
+/* ---- tensor-parallel group (no reference counterpart: the reference is single-device).
+ * `nccl_unique_id` is the 128-byte ncclUniqueId produced by holo_b200_nccl_unique_id on rank 0
+ * and broadcast by the host launcher. */
+int32_t holo_b200_nccl_unique_id(uint8_t out128[128]);
+int32_t holo_b200_ctx_init_tp(holo_b200_ctx* ctx, const uint8_t nccl_unique_id[128], int32_t rank, int32_t world);
+
+/* Library version / build info string (static storage). */
+const char* holo_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HOLOGRAM_B200_H */

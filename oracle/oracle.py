@@ -1,0 +1,219 @@
+"""numpy front end to the CPU oracle (oracle/hologram_oracle.c).
+
+TEST INFRASTRUCTURE ONLY: loaded by tests/, by __graft_entry__.smoke() and by bench.py's
+CPU-baseline legs. The product package never imports this module.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import build as _build
+
+DTYPE_I8, DTYPE_I32, DTYPE_I64, DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 2, 4, 5, 6, 7, 8
+_c = C.c_void_p
+
+
+def _load(path):
+    lib = C.CDLL(path)
+    u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
+    sig = {
+        "holo_or_bf16_to_f32": (C.c_float, [C.c_uint16]),
+        "holo_or_f32_to_bf16": (C.c_uint16, [C.c_float]),
+        "holo_or_f16_to_f32": (C.c_float, [C.c_uint16]),
+        "holo_or_f32_to_f16": (C.c_uint16, [C.c_float]),
+        "holo_or_exp_det": (C.c_float, [C.c_float]),
+        "holo_or_act": (C.c_float, [C.c_int, C.c_float]),
+        "holo_or_build_table": (None, [C.c_int, C.c_int, u16p]),
+        "holo_or_unary_lut": (C.c_int, [C.c_int, C.c_int, _c, _c, C.c_uint64]),
+        "holo_or_unary_lut_mt": (C.c_int, [C.c_int, C.c_int, _c, _c, C.c_uint64]),
+        "holo_or_quantize_row_i8": (C.c_float, [_c, _c, C.c_size_t]),
+        "holo_or_quantize_rows_i8": (C.c_int, [_c, C.c_int, C.c_uint64, C.c_uint32, _c, _c]),
+        "holo_or_matmul_i8_pc_omajor": (None, [_c, _c, _c, _c, C.c_size_t, C.c_size_t, C.c_size_t]),
+        "holo_or_dequantize": (C.c_int, [_c, C.c_int, _c, _c, C.c_uint32, C.c_uint32, C.c_float, C.c_int32, _c,
+                                          C.c_int, C.c_uint64]),
+        "holo_or_cast_float": (C.c_int, [_c, C.c_int, _c, C.c_int, C.c_uint64]),
+        "holo_or_matmul": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int]),
+        "holo_or_matmul_activation": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, C.c_int]),
+        "holo_or_matmul_add": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int]),
+        "holo_or_binary": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
+        "holo_or_rms_norm": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
+        "holo_or_rope": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint64, C.c_int]),
+        "holo_or_gather": (C.c_int, [_c, _c, C.c_int, _c, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int]),
+        "holo_or_kv_cache_write": (C.c_int, [_c, _c, C.c_uint32, _c, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
+        "holo_or_decode_attention_valid_f32": (C.c_int, [_c] * 5 + [C.c_uint32, _c] + [C.c_uint32] * 8),
+        "holo_or_decode_attention_valid": (C.c_int, [_c] * 5 + [C.c_uint32, _c] + [C.c_uint32] * 8 + [C.c_int]),
+        "holo_or_decode_attention_valid_q8": (C.c_int, [_c, C.c_int] + [_c] * 8 + [C.c_uint32, _c] + [C.c_uint32] * 8),
+        "holo_or_fnv1a64_f32": (C.c_uint64, [_c, C.c_size_t]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+_PARITY, _FAST = _build.build()
+lib = _load(_PARITY)
+_fast = None
+
+
+def fast_lib():
+    """The -O3 build, for timed CPU-baseline legs only."""
+    global _fast
+    if _fast is None:
+        _fast = _load(_FAST)
+    return _fast
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _np_store(dtype):
+    return np.float32 if dtype == DTYPE_F32 else np.uint16
+
+
+def build_table(act, dtype):
+    t = np.empty(65536, dtype=np.uint16)
+    lib.holo_or_build_table(act, dtype, t)
+    return t
+
+
+def unary_lut(act, dtype, x_bits, which=None, mt=False):
+    x = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    out = np.empty_like(x)
+    L = which or lib
+    fn = L.holo_or_unary_lut_mt if mt else L.holo_or_unary_lut
+    rc = fn(act, dtype, _p(x), _p(out), x.size)
+    assert rc == 0, rc
+    return out
+
+
+def f32_to_bf16_trunc(x):
+    return (np.ascontiguousarray(x, dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(bits):
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_rne(x):
+    """Round-to-nearest-even narrowing, for input synthesis only (outputs truncate)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    nan = np.isnan(x)
+    r[nan] = 0x7FC0
+    return r
+
+
+def quantize_rows_i8(x, dtype, rows, d):
+    x = np.ascontiguousarray(x)
+    codes = np.zeros(rows * d, dtype=np.int8)
+    scales = np.zeros(rows, dtype=np.float32)
+    rc = lib.holo_or_quantize_rows_i8(_p(x), dtype, rows, d, _p(codes), _p(scales))
+    assert rc == 0, rc
+    return codes, scales
+
+
+def matmul(a, b, m, k, n, dtype, act=0, residual=None, which=None):
+    L = which or lib
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b)
+    out = np.zeros(m * n, dtype=_np_store(dtype))
+    if residual is not None:
+        r = np.ascontiguousarray(residual)
+        rc = L.holo_or_matmul_add(_p(a), _p(b), _p(r), _p(out), m, k, n, dtype)
+    elif act:
+        rc = L.holo_or_matmul_activation(_p(a), _p(b), _p(out), m, k, n, dtype, act)
+    else:
+        rc = L.holo_or_matmul(_p(a), _p(b), _p(out), m, k, n, dtype)
+    assert rc == 0, rc
+    return out
+
+
+def binary(op, a, b, dtype):
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b)
+    out = np.empty_like(a)
+    assert lib.holo_or_binary(op, _p(a), _p(b), _p(out), a.size, dtype) == 0
+    return out
+
+
+def rms_norm(x, gamma, batch, feature, eps_bits, dtype):
+    x = np.ascontiguousarray(x)
+    out = np.empty_like(x)
+    g = None if gamma is None else np.ascontiguousarray(gamma)
+    rc = lib.holo_or_rms_norm(_p(x), _p(g), _p(out), batch, feature, eps_bits, dtype)
+    assert rc == 0, rc
+    return out
+
+
+def rope(x, cos, sin, head_dim, dtype):
+    x, cos, sin = (np.ascontiguousarray(v) for v in (x, cos, sin))
+    out = np.empty_like(x)
+    rc = lib.holo_or_rope(_p(x), _p(cos), _p(sin), _p(out), head_dim, x.size, dtype)
+    assert rc == 0, rc
+    return out
+
+
+def gather(data, idx, outer, axis_dim, inner, dtype):
+    data = np.ascontiguousarray(data)
+    idx = np.ascontiguousarray(idx)
+    idt = DTYPE_I32 if idx.dtype == np.int32 else DTYPE_I64
+    es = data.dtype.itemsize
+    out = np.zeros(outer * idx.size * inner, dtype=data.dtype)
+    rc = lib.holo_or_gather(_p(data), _p(idx), idt, _p(out), outer, axis_dim, inner, idx.size,
+                            {1: 1, 2: DTYPE_BF16, 4: DTYPE_F32, 8: DTYPE_I64}[es])
+    return rc, out
+
+
+def kv_cache_write(cache, new, pos, planes, bucket, new_rows, row_bytes):
+    cache = np.ascontiguousarray(cache).view(np.uint8)
+    new = np.ascontiguousarray(new).view(np.uint8)
+    out = np.empty_like(cache)
+    rc = lib.holo_or_kv_cache_write(_p(cache), _p(new), pos, _p(out), planes, bucket, new_rows, row_bytes)
+    return rc, out
+
+
+def dequantize(codes, scales, zps, channels, inner, scale, zp, dtype, quant_dtype=DTYPE_I8):
+    codes = np.ascontiguousarray(codes)
+    out = np.zeros(codes.size, dtype=_np_store(dtype))
+    s = None if scales is None else np.ascontiguousarray(scales, dtype=np.float32)
+    z = None if zps is None else np.ascontiguousarray(zps, dtype=np.int32)
+    rc = lib.holo_or_dequantize(_p(codes), quant_dtype, _p(s), _p(z), channels, inner, scale, zp, _p(out), dtype,
+                                codes.size)
+    assert rc == 0, rc
+    return out
+
+
+def cast_float(x, src, dst):
+    x = np.ascontiguousarray(x)
+    out = np.zeros(x.size, dtype=_np_store(dst))
+    assert lib.holo_or_cast_float(_p(x), src, _p(out), dst, x.size) == 0
+    return out
+
+
+def decode_attention_valid(q, kp, vp, kn, vn, valid_len, b, h, kv, m, past, new, d, scale_bits, dtype, which=None):
+    L = which or lib
+    arrs = [np.ascontiguousarray(v) for v in (q, kp, vp, kn, vn)]
+    out = np.zeros(b * h * m * d, dtype=_np_store(dtype))
+    rc = L.holo_or_decode_attention_valid(*[_p(v) for v in arrs], valid_len, _p(out), b, h, kv, m, past, new, d,
+                                          scale_bits, dtype)
+    return rc, out
+
+
+def decode_attention_valid_q8(q, dtype, kp, kps, vp, vps, kn, kns, vn, vns, valid_len, b, h, kv, m, past, new, d,
+                              scale_bits, which=None):
+    L = which or lib
+    arrs = [np.ascontiguousarray(v) for v in (kp, kps, vp, vps, kn, kns, vn, vns)]
+    q = np.ascontiguousarray(q)
+    out = np.zeros(b * h * m * d, dtype=_np_store(dtype))
+    rc = L.holo_or_decode_attention_valid_q8(_p(q), dtype, *[_p(v) for v in arrs], valid_len, _p(out), b, h, kv, m,
+                                             past, new, d, scale_bits)
+    return rc, out
+
+
+def fnv1a64_f32(v):
+    v = np.ascontiguousarray(v, dtype=np.float32)
+    return int(lib.holo_or_fnv1a64_f32(_p(v), v.size))

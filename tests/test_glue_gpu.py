@@ -1,0 +1,171 @@
+"""Decoder glue ops on the GPU against the oracle (through the C ABI)."""
+import struct
+
+import numpy as np
+import pytest
+
+import hologram_b200 as hb
+from hologram_b200 import kernel_call as kc
+from oracle import oracle as orc
+from helpers import norm_max_err, synth_bf16
+
+pytestmark = pytest.mark.gpu
+BF = kc.DTYPE_BF16
+
+
+def f32bits(x):
+    return struct.unpack("<I", struct.pack("<f", x))[0]
+
+
+def test_add_mul_bit_exact(backend):
+    n = 64 * 4096 + 3
+    a, b = synth_bf16(n, 1.0, 1), synth_bf16(n, 2.0, 2)
+    for op, ctor in ((0, kc.KernelCall.Add), (1, kc.KernelCall.Mul)):
+        ws = hb.DeviceWorkspace(backend, 3)
+        ws.put(0, a)
+        ws.put(1, b)
+        ws.alloc(2, n * 2)
+        backend.dispatch(ctor(kc.BinaryCall(kc.rb(0), kc.rb(1), kc.rb(2), n, 16, BF)), ws)
+        assert np.array_equal(ws.read(2, n * 2, np.uint16), orc.binary(op, a, b, BF))
+    # f32 form
+    af, bf_ = np.random.default_rng(0).standard_normal((2, 1000)).astype(np.float32)
+    ws = hb.DeviceWorkspace(backend, 3)
+    ws.put(0, af)
+    ws.put(1, bf_)
+    ws.alloc(2, af.nbytes)
+    backend.dispatch(kc.KernelCall.Add(kc.BinaryCall(kc.rb(0), kc.rb(1), kc.rb(2), af.size, 32, kc.DTYPE_F32)), ws)
+    assert np.array_equal(ws.read(2, af.nbytes, np.float32), af + bf_)
+
+
+def test_rms_norm_within_tolerance(backend):
+    batch, feature = 64, 4096
+    x, g = synth_bf16(batch * feature, 1.5, 3), synth_bf16(feature, 1.0, 4)
+    ws = hb.DeviceWorkspace(backend, 3)
+    ws.put(0, x)
+    ws.put(1, g)
+    ws.alloc(2, x.nbytes)
+    call = kc.NormCall(kc.rb(0), kc.rb(1), kc.NONE, kc.NONE, kc.rb(2), batch, feature, 0, 0, f32bits(1e-5), BF)
+    backend.dispatch(kc.KernelCall.RmsNorm(call), ws)
+    got = orc.bf16_to_f32(ws.read(2, x.nbytes, np.uint16))
+    want = orc.bf16_to_f32(orc.rms_norm(x, g, batch, feature, f32bits(1e-5), BF))
+    # the sum of squares is reduced in parallel: a 1-ulp bf16 difference is allowed
+    assert norm_max_err(got, want) <= 1e-2
+    assert np.mean(got.view(np.uint32) == want.view(np.uint32)) > 0.99
+    bad = kc.NormCall(kc.rb(0), kc.rb(1), kc.NONE, kc.NONE, kc.rb(2), batch, feature, 0, 0, f32bits(-1.0), BF)
+    with pytest.raises(hb.BackendError) as e:
+        backend.dispatch(kc.KernelCall.RmsNorm(bad), ws)
+    assert e.value.variant == "UnsupportedOp"
+
+
+def test_rope_bit_exact(backend):
+    n, d = 64 * 32 * 128, 128
+    x, c, s = synth_bf16(n, 1.0, 5), synth_bf16(n, 0.7, 6), synth_bf16(n, 0.7, 7)
+    ws = hb.DeviceWorkspace(backend, 4)
+    for i, v in enumerate((x, c, s)):
+        ws.put(i, v)
+    ws.alloc(3, x.nbytes)
+    backend.dispatch(kc.KernelCall.RotaryEmbedding(kc.RoPECall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), d, n, BF)), ws)
+    assert np.array_equal(ws.read(3, x.nbytes, np.uint16), orc.rope(x, c, s, d, BF))
+    with pytest.raises(hb.BackendError):
+        backend.dispatch(kc.KernelCall.RotaryEmbedding(kc.RoPECall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), 7, n, BF)), ws)
+
+
+def test_gather_embedding_rows(backend):
+    vocab, dm, k = 1000, 256, 64
+    data = synth_bf16(vocab * dm, 1.0, 8)
+    idx = np.random.default_rng(9).integers(-vocab, vocab, size=k).astype(np.int32)
+    ws = hb.DeviceWorkspace(backend, 3)
+    ws.put(0, data)
+    ws.put(1, idx)
+    ws.alloc(2, k * dm * 2)
+    call = kc.GatherCall(kc.rb(0), kc.rb(1), kc.rb(2), 1, vocab, dm, k, kc.DTYPE_I32, BF)
+    backend.dispatch(kc.KernelCall.Gather(call), ws)
+    rc, want = orc.gather(data, idx, 1, vocab, dm, BF)
+    assert rc == 0 and np.array_equal(ws.read(2, k * dm * 2, np.uint16), want)
+    # out-of-range index fails loud at the next synchronising call
+    idx[3] = vocab
+    ws.write(1, idx)
+    backend.dispatch(kc.KernelCall.Gather(call), ws)
+    with pytest.raises(hb.BackendError) as e:
+        backend.synchronize()
+    assert e.value.variant == "SlotOutOfRange"
+    backend.synchronize()
+
+
+def test_cast_and_dequantize(backend):
+    n = 10007
+    x = synth_bf16(n, 3.0, 10)
+    ws = hb.DeviceWorkspace(backend, 4)
+    ws.put(0, x)
+    ws.alloc(1, n * 4)
+    backend.dispatch(kc.KernelCall.Cast(kc.CastCall(kc.rb(0), kc.rb(1), n, BF, kc.DTYPE_F32)), ws)
+    f = ws.read(1, n * 4, np.float32)
+    assert np.array_equal(f.view(np.uint32), orc.bf16_to_f32(x).view(np.uint32))
+    ws.alloc(2, n * 2)
+    backend.dispatch(kc.KernelCall.Cast(kc.CastCall(kc.rb(1), kc.rb(2), n, kc.DTYPE_F32, kc.DTYPE_F16)), ws)
+    assert np.array_equal(ws.read(2, n * 2, np.uint16), orc.cast_float(f, kc.DTYPE_F32, kc.DTYPE_F16))
+    # per-row dequantize: channels = rows, inner = d, zero-point 0
+    rows, d = 37, 128
+    rng = np.random.default_rng(11)
+    codes = rng.integers(-127, 128, size=rows * d).astype(np.int8)
+    scales = rng.random(rows).astype(np.float32)
+    zps = np.zeros(rows, dtype=np.int32)
+    ws2 = hb.DeviceWorkspace(backend, 4)
+    ws2.put(0, codes)
+    ws2.put(1, scales)
+    ws2.put(2, zps)
+    ws2.alloc(3, rows * d * 4)
+    call = kc.DequantizeCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), rows * d, rows, d, kc.DTYPE_I8, kc.DTYPE_F32, 0, 0)
+    backend.dispatch(kc.KernelCall.Dequantize(call), ws2)
+    want = orc.dequantize(codes, scales, zps, rows, d, 0.0, 0, kc.DTYPE_F32)
+    assert np.array_equal(ws2.read(3, rows * d * 4, np.float32).view(np.uint32), want.view(np.uint32))
+
+
+def test_kv_cache_write_copy_and_in_place(backend):
+    planes, bucket, new_rows, row = 16, 40, 3, 128
+    rng = np.random.default_rng(12)
+    cache = rng.integers(0, 256, size=planes * bucket * row).astype(np.uint8)
+    new = rng.integers(0, 256, size=planes * new_rows * row).astype(np.uint8)
+    for pos in (0, 17, 38, 39, 4000000001):
+        rc, want = orc.kv_cache_write(cache, new, pos % (1 << 32), planes, bucket, new_rows, row)
+        ws = hb.DeviceWorkspace(backend, 4)
+        ws.put(0, cache)
+        ws.put(1, new)
+        ws.put(2, np.array([pos % (1 << 32)], dtype=np.uint32))
+        ws.alloc(3, cache.nbytes)
+        call = kc.KvCacheWriteCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), planes, bucket, new_rows, row)
+        backend.dispatch(kc.KernelCall.KvCacheWrite(call), ws)
+        assert np.array_equal(ws.read(3, cache.nbytes), want)
+        # in-place move form (cache == output): same bytes, O(new_rows) work
+        call2 = kc.KvCacheWriteCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(0), planes, bucket, new_rows, row)
+        backend.dispatch(kc.KernelCall.KvCacheWrite(call2), ws)
+        assert np.array_equal(ws.read(0, cache.nbytes), want)
+    with pytest.raises(hb.BackendError) as e:
+        bad = kc.KvCacheWriteCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), planes, 2, 3, row)
+        backend.dispatch(kc.KernelCall.KvCacheWrite(bad), ws)
+    assert e.value.variant == "UnsupportedOp"
+
+
+@pytest.mark.parametrize("dtype,d", [(kc.DTYPE_BF16, 128), (kc.DTYPE_BF16, 96), (kc.DTYPE_F32, 64), (kc.DTYPE_F16, 256)])
+def test_quantize_rows_bit_exact(backend, dtype, d):
+    rows = 4099
+    rng = np.random.default_rng(d)
+    x = rng.standard_normal(rows * d).astype(np.float32)
+    x.reshape(rows, d)[5] = 0.0                      # all-zero row
+    x.reshape(rows, d)[6, 3] = np.inf                # inf row
+    x.reshape(rows, d)[7, 1] = np.nan                # NaN element is skipped by the max scan
+    x.reshape(rows, d)[8] *= 1e-30
+    if dtype == kc.DTYPE_BF16:
+        xs = orc.f32_to_bf16_rne(x)
+    elif dtype == kc.DTYPE_F16:
+        xs = x.astype(np.float16).view(np.uint16)
+    else:
+        xs = x
+    ws = hb.DeviceWorkspace(backend, 3)
+    ws.put(0, xs)
+    ws.alloc(1, rows * d)
+    ws.alloc(2, rows * 4)
+    backend.dispatch(kc.KernelCall.QuantizeRowsI8(kc.QuantizeRowsI8Call(kc.rb(0), kc.rb(1), kc.rb(2), rows, d, dtype)), ws)
+    codes, scales = orc.quantize_rows_i8(xs, dtype, rows, d)
+    assert np.array_equal(ws.read(1, rows * d, np.int8), codes)
+    assert np.array_equal(ws.read(2, rows * 4, np.uint32), scales.view(np.uint32))

@@ -1,0 +1,247 @@
+"""The oracle against every known-answer value the reference's own tests hold for this path
+(no GPU). File:line citations are into the reference tree."""
+import math
+import struct
+
+import numpy as np
+import pytest
+
+from hologram_b200 import kernel_call as kc
+from oracle import oracle as orc
+
+L = orc.lib
+
+
+def bits(f):
+    return struct.unpack("<I", struct.pack("<f", f))[0]
+
+
+def test_exp_det_edges_bit_exact():
+    # crates/hologram-compute/src/cpu/simd.rs:7621-7624
+    assert bits(L.holo_or_exp_det(0.0)) == bits(1.0)
+    for x in (float("-inf"), float("nan"), -1000.0):
+        assert bits(L.holo_or_exp_det(x)) == bits(0.0)
+    assert bits(L.holo_or_exp_det(-0.0)) == bits(1.0)
+
+
+def test_exp_det_accuracy():
+    # simd.rs:7610-7620: relative error < 2e-6 against the true exponential on [-87, 88]
+    v, worst = -87.0, 0.0
+    while v <= 88.0:
+        x = np.float32(v)
+        e = float(L.holo_or_exp_det(float(x)))
+        r = math.exp(float(x))
+        worst = max(worst, abs(e - r) / r)
+        v += 0.0173
+    assert worst < 2e-6
+
+
+def test_quantizer_pinned_by_the_w8a8_golden():
+    # simd.rs:8236-8262: FNV-1a-64 over the W8A8 output-major GEMV output bits
+    m, k, n = 3, 64, 24
+    a = (np.array([float(i * 37 % 91) for i in range(m * k)], dtype=np.float32) - np.float32(45.0)) * np.float32(0.031)
+    scales = np.float32(0.011) + np.arange(n, dtype=np.float32) * np.float32(0.0007)
+    bq = np.array([(i * 31 % 255) - 127 for i in range(k * n)], dtype=np.int8)
+    out = np.zeros(m * n, dtype=np.float32)
+    L.holo_or_matmul_i8_pc_omajor(a.ctypes.data, bq.ctypes.data, scales.ctypes.data, out.ctypes.data, m, k, n)
+    assert orc.fnv1a64_f32(out) == 0x787CCDC172029F9B
+
+
+def test_bf16_narrow_truncates():
+    # crates/hologram-compute/tests/dtype_codec.rs:19-32: bf16 write is bits >> 16, never rounds up
+    x = struct.unpack("<f", struct.pack("<I", 0x3F80FFFF))[0]
+    assert L.holo_or_f32_to_bf16(x) == 0x3F80
+    for v in (1.0, -2.5, 3.140625, 1e-20, -7e30):
+        h = L.holo_or_f32_to_bf16(v)
+        assert h == bits(np.float32(v)) >> 16
+        assert bits(L.holo_or_bf16_to_f32(h)) == (h << 16)
+
+
+def test_f16_widen_matches_ieee_for_all_patterns():
+    # cpu/dtype.rs:94-118 is an exact widening; numpy's float16 is the independent authority
+    allbits = np.arange(65536, dtype=np.uint16)
+    want = allbits.view(np.float16).astype(np.float32).view(np.uint32)
+    got = np.array([bits(L.holo_or_f16_to_f32(int(b))) for b in allbits], dtype=np.uint32)
+    nan = np.isnan(allbits.view(np.float16))
+    assert np.array_equal(got[~nan], want[~nan])
+    # NaN: payload shifted up by 13 bits (dtype.rs:112-114)
+    assert np.array_equal(got[nan] & 0x7F800000, np.full(nan.sum(), 0x7F800000, dtype=np.uint32))
+
+
+def test_f16_narrow_rule():
+    # cpu/dtype.rs:121-153: add-half-then-shift (ties go up in magnitude), one NaN pattern,
+    # overflow to inf, flush below 2^-25
+    f = L.holo_or_f32_to_f16
+    assert f(1.0) == 0x3C00 and f(-2.0) == 0xC000
+    assert f(65520.0) == 0x7C00 and f(1e9) == 0x7C00 and f(-1e9) == 0xFC00
+    assert f(float("nan")) & 0x7FFF == 0x7E00
+    assert f(2.0 ** -26) == 0x0000 and f(-(2.0 ** -26)) == 0x8000
+    # 1 + 2^-11 is a tie between 0x3C00 and 0x3C01: this codec rounds it up, RNE would not
+    assert f(1.0 + 2.0 ** -11) == 0x3C01
+    assert np.float32(1.0 + 2.0 ** -11).astype(np.float16).view(np.uint16) == 0x3C00
+    # round trip of every finite f16 is the identity
+    for b in list(range(0, 0x7C00, 37)) + list(range(0x8000, 0xFC00, 41)):
+        assert f(L.holo_or_f16_to_f32(b)) == b
+
+
+def test_lut_gelu_bf16_against_f64_reference():
+    # crates/hologram-compute/tests/lut.rs:68-100
+    n = 64
+    x = np.array([i * 0.25 - 8.0 for i in range(n)], dtype=np.float32)
+    xb = orc.f32_to_bf16_trunc(x)
+    got = orc.bf16_to_f32(orc.unary_lut(kc.LUT_GELU, kc.DTYPE_BF16, xb))
+    c = math.sqrt(2.0 / math.pi)
+    for i in range(n):
+        xv = float(orc.bf16_to_f32(xb[i:i + 1])[0])
+        want = 0.5 * xv * (1.0 + math.tanh(c * (xv + 0.044715 * xv ** 3)))
+        assert abs(float(got[i]) - want) <= 0.02 + 0.02 * abs(want)
+
+
+def test_lut_sigmoid_bf16_against_f64_reference():
+    # tests/lut.rs:103-132
+    n = 48
+    xb = orc.f32_to_bf16_trunc(np.array([i * 0.4 - 9.0 for i in range(n)], dtype=np.float32))
+    got = orc.bf16_to_f32(orc.unary_lut(kc.LUT_SIGMOID, kc.DTYPE_BF16, xb))
+    x = orc.bf16_to_f32(xb)
+    for i in range(n):
+        assert abs(float(got[i]) - 1.0 / (1.0 + math.exp(-float(x[i])))) <= 0.01
+
+
+def test_table_special_values():
+    # consequences of lut_act_ref + exp_f32_det (float_kernels.rs:3548-3566, simd.rs:4217-4239)
+    bf = kc.DTYPE_BF16
+    sig, tanh, gelu, silu = (orc.build_table(a, bf) for a in (kc.LUT_SIGMOID, kc.LUT_TANH, kc.LUT_GELU, kc.LUT_SILU))
+    qnan = 0x7FC0
+    assert sig[qnan] == 0x3F80            # 1 / (1 + exp_det(NaN) = 0) = 1.0
+    assert tanh[qnan] == 0xBF80           # (0 - 1) / (0 + 1) = -1.0
+    assert np.isnan(orc.bf16_to_f32(gelu[qnan:qnan + 1])[0])
+    assert np.isnan(orc.bf16_to_f32(silu[qnan:qnan + 1])[0])
+    assert tanh[0x7F80] == 0x3F80 and tanh[0x4120] == 0x3F80   # tanh(+inf) = tanh(10) = exactly 1.0
+    assert sig[0x0000] == 0x3F00 and sig[0x8000] == 0x3F00     # sigmoid(±0) = 0.5
+    exp_t = orc.build_table(kc.LUT_EXP, bf)
+    assert exp_t[0x0000] == 0x3F80 and exp_t[0x8000] == 0x3F80 and exp_t[0xFF80] == 0x0000
+    assert exp_t[0x7F80] == 0x7F80
+
+
+def test_lut_is_the_table():
+    for act in range(6):
+        for dt in (kc.DTYPE_F16, kc.DTYPE_BF16):
+            t = orc.build_table(act, dt)
+            allbits = np.arange(65536, dtype=np.uint16)
+            assert np.array_equal(orc.unary_lut(act, dt, allbits), t)
+
+
+def test_quantize_row_edges():
+    # all-zero row -> zero codes, scale 0.0 (simd.rs:4769-4771); clamp at ±127; half away from zero
+    codes, scales = orc.quantize_rows_i8(np.zeros(8, dtype=np.float32), kc.DTYPE_F32, 1, 8)
+    assert not codes.any() and scales[0] == 0.0
+    x = np.array([127.0, -127.0, 0.5, -0.5, 1.5, -1.5, 0.49, 63.5], dtype=np.float32)
+    codes, scales = orc.quantize_rows_i8(x, kc.DTYPE_F32, 1, 8)
+    assert scales[0] == np.float32(127.0) / np.float32(127.0)
+    assert codes.tolist() == [127, -127, 1, -1, 2, -2, 0, 64]
+
+
+def _fixture(n, seed):
+    # tests/decode_attention.rs:95-99 integer-formula corpus
+    return np.array([(((i * 13 + seed * 7) % 41) - 20.0) * 0.043 for i in range(n)], dtype=np.float32)
+
+
+def test_attention_witness_relations_on_oracle():
+    # tests/decode_attention_valid.rs: garbage beyond valid_len is never read; valid_len >= past
+    # means the whole bucket; zero visible past keys still sees the causal chunk.
+    b, h, hkv, m, past, d = 1, 4, 2, 4, 12, 16
+    q = _fixture(b * h * m * d, 1)
+    kp, vp = _fixture(b * hkv * past * d, 2), _fixture(b * hkv * past * d, 3)
+    kn, vn = _fixture(b * hkv * m * d, 4), _fixture(b * hkv * m * d, 5)
+    f32 = kc.DTYPE_F32
+    rc, full = orc.decode_attention_valid(q, kp, vp, kn, vn, past, b, h, hkv, m, past, m, d, 0, f32)
+    assert rc == 0
+    rc, over = orc.decode_attention_valid(q, kp, vp, kn, vn, 10 ** 6, b, h, hkv, m, past, m, d, 0, f32)
+    assert np.array_equal(full.view(np.uint32), over.view(np.uint32))
+    valid = 5
+    kg, vg = kp.copy().reshape(b * hkv, past, d), vp.copy().reshape(b * hkv, past, d)
+    kg[:, valid:, :] = np.nan
+    vg[:, valid:, :] = np.nan
+    rc, a = orc.decode_attention_valid(q, kg, vg, kn, vn, valid, b, h, hkv, m, past, m, d, 0, f32)
+    tight_k = np.ascontiguousarray(kp.reshape(b * hkv, past, d)[:, :valid, :])
+    tight_v = np.ascontiguousarray(vp.reshape(b * hkv, past, d)[:, :valid, :])
+    rc, t = orc.decode_attention_valid(q, tight_k, tight_v, kn, vn, valid, b, h, hkv, m, valid, m, d, 0, f32)
+    assert np.array_equal(a.view(np.uint32), t.view(np.uint32))   # padded == tight, bitwise
+    assert not np.isnan(a).any()
+    # q_rows != new_len is refused (float_kernels.rs:4205-4210)
+    rc, _ = orc.decode_attention_valid(q, kp, vp, kn, vn, past, b, h, hkv, m, past, m - 1, d, 0, f32)
+    assert rc == -3
+    # heads not a multiple of kv_heads is refused (:4216-4220)
+    rc, _ = orc.decode_attention_valid(q, kp, vp, kn, vn, past, b, h, 3, m, past, m, d, 0, f32)
+    assert rc == -3
+
+
+def test_attention_against_independent_f64_softmax():
+    b, h, hkv, m, past, d = 2, 4, 2, 1, 9, 8
+    rng = np.random.default_rng(5)
+    q = rng.standard_normal(b * h * m * d).astype(np.float32)
+    kp, vp = (rng.standard_normal(b * hkv * past * d).astype(np.float32) for _ in range(2))
+    kn, vn = (rng.standard_normal(b * hkv * m * d).astype(np.float32) for _ in range(2))
+    rc, got = orc.decode_attention_valid(q, kp, vp, kn, vn, 7, b, h, hkv, m, past, m, d, 0, kc.DTYPE_F32)
+    assert rc == 0
+    Q = q.reshape(b, h, d).astype(np.float64)
+    K = np.concatenate([kp.reshape(b, hkv, past, d)[:, :, :7], kn.reshape(b, hkv, 1, d)], axis=2).astype(np.float64)
+    V = np.concatenate([vp.reshape(b, hkv, past, d)[:, :, :7], vn.reshape(b, hkv, 1, d)], axis=2).astype(np.float64)
+    want = np.zeros((b, h, d))
+    for bi in range(b):
+        for hi in range(h):
+            s = K[bi, hi // 2] @ Q[bi, hi] / math.sqrt(d)
+            p = np.exp(s - s.max())
+            want[bi, hi] = (p / p.sum()) @ V[bi, hi // 2]
+    assert np.max(np.abs(got.reshape(b, h, d) - want)) < 1e-5
+
+
+def test_matmul_is_an_ascending_fma_chain_then_truncation():
+    m, k, n = 3, 37, 16
+    rng = np.random.default_rng(7)
+    a = orc.f32_to_bf16_rne(rng.standard_normal(m * k).astype(np.float32))
+    b = orc.f32_to_bf16_rne(rng.standard_normal(k * n).astype(np.float32))
+    got = orc.matmul(a, b, m, k, n, kc.DTYPE_BF16)
+    A, B = orc.bf16_to_f32(a).reshape(m, k), orc.bf16_to_f32(b).reshape(k, n)
+    want = np.zeros((m, n), dtype=np.float32)
+    for i in range(m):
+        for j in range(n):
+            acc = np.float32(0)
+            for kk in range(k):
+                acc = np.float32(math.fma(float(A[i, kk]), float(B[kk, j]), float(acc))) if hasattr(math, "fma") else acc
+            want[i, j] = acc
+    if hasattr(math, "fma"):
+        assert np.array_equal(got.reshape(m, n), orc.f32_to_bf16_trunc(want).reshape(m, n))
+    # f64 reference bound of the reference's conformance test (tests/conformance.rs:256): 8e-3
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    err = np.max(np.abs(orc.bf16_to_f32(got).reshape(m, n) - ref)) / np.max(np.abs(ref))
+    assert err <= 8e-3
+
+
+def test_fused_epilogues_equal_the_unfused_pair():
+    # float_kernels.rs:822-891: narrow, re-widen, epilogue, narrow
+    m, k, n = 4, 32, 24
+    rng = np.random.default_rng(11)
+    a = orc.f32_to_bf16_rne(rng.standard_normal(m * k).astype(np.float32))
+    b = orc.f32_to_bf16_rne(rng.standard_normal(k * n).astype(np.float32))
+    r = orc.f32_to_bf16_rne(rng.standard_normal(m * n).astype(np.float32))
+    plain = orc.matmul(a, b, m, k, n, kc.DTYPE_BF16)
+    assert np.array_equal(orc.matmul(a, b, m, k, n, kc.DTYPE_BF16, act=kc.FUSED_SILU),
+                          orc.unary_lut(kc.LUT_SILU, kc.DTYPE_BF16, plain))
+    assert np.array_equal(orc.matmul(a, b, m, k, n, kc.DTYPE_BF16, residual=r),
+                          orc.binary(0, plain, r, kc.DTYPE_BF16))
+
+
+def test_kv_cache_write_ring():
+    # cpu/kernels.rs:455-501; tests/kv_cache_write.rs:126-156 (wrap-around)
+    planes, bucket, new_rows, row = 2, 5, 2, 3
+    cache = np.arange(planes * bucket * row, dtype=np.uint8)
+    new = 200 + np.arange(planes * new_rows * row, dtype=np.uint8)
+    rc, out = orc.kv_cache_write(cache, new, 4 + 5 * 3, planes, bucket, new_rows, row)   # pos wraps to 4
+    assert rc == 0
+    o = out.reshape(planes, bucket, row)
+    n = new.reshape(planes, new_rows, row)
+    assert np.array_equal(o[:, 4], n[:, 0]) and np.array_equal(o[:, 0], n[:, 1])
+    assert np.array_equal(o[:, 1:4], cache.reshape(planes, bucket, row)[:, 1:4])
+    assert orc.kv_cache_write(cache, new, 0, planes, 0, new_rows, row)[0] == -3
+    assert orc.kv_cache_write(cache, new, 0, planes, 1, 2, row)[0] == -3
