@@ -11,6 +11,7 @@ The CUDA library is mandatory: importing this module without the built
 """
 import ctypes as C
 import os
+import weakref
 
 import numpy as np
 
@@ -100,9 +101,13 @@ class B200Backend:
         _check(lib.holo_b200_ctx_create(device, C.byref(h)))
         self._h = h
         self.device = device
+        self._workspaces = weakref.WeakSet()
 
     def close(self):
+        """Destroy the context; device workspaces created on it are destroyed first."""
         if getattr(self, "_h", None):
+            for ws in list(self._workspaces):
+                ws.close()
             lib.holo_b200_ctx_destroy(self._h)
             self._h = None
 
@@ -163,6 +168,7 @@ class DeviceWorkspace:
         self._h = h
         self.backend = backend
         self.n_slots = n_slots
+        backend._workspaces.add(self)
 
     def close(self):
         if getattr(self, "_h", None):

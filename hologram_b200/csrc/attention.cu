@@ -338,9 +338,13 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                     float full = part + __shfl_xor_sync(0xffffffffu, part, 16);
                     float kscale = e ? k2.y : k2.x;
                     float sval = full * (kscale * cq);
-                    if (key + e >= limit) sval = -INFINITY;
+                    float vscale = e ? v2.y : v2.x;
+                    if (key + e >= limit) {  // unrealized row: whatever bytes it holds never count
+                        sval = -INFINITY;
+                        vscale = 0.0f;
+                    }
                     sc[nt * 2 + e] = sval;
-                    svv[nt * 2 + e] = e ? v2.y : v2.x;
+                    svv[nt * 2 + e] = vscale;
                     mt = fmaxf(mt, sval);
                 }
             }

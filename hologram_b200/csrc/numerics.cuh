@@ -117,16 +117,23 @@ __device__ __forceinline__ float silu_ref(float x) { return __fmul_rn(x, sigmoid
 __device__ __forceinline__ float exp_standin(float x) { return (float)exp((double)x); }
 __device__ __forceinline__ float erf_standin(float x) { return (float)erf((double)x); }
 
-// lut_act_ref, cpu/float_kernels.rs:3628-3638
+// lut_act_ref, cpu/float_kernels.rs:3628-3638.
+// NaN results follow the x86-64 SSE convention the reference's CPU tables are built under
+// (CUDA arithmetic would return the canonical 0x7fffffff instead): an operation with a NaN
+// operand returns that NaN quieted (payload and sign kept), an invalid operation such as
+// 0 * inf returns the default NaN 0xFFC00000.
 __device__ __forceinline__ float lut_act_ref(int act, float x) {
+    float y;
     switch (act) {
-        case HOLO_LUT_SIGMOID: return sigmoid_ref(x);
-        case HOLO_LUT_TANH: return tanh_ref(x);
-        case HOLO_LUT_GELU: return gelu_ref(x);
-        case HOLO_LUT_SILU: return silu_ref(x);
-        case HOLO_LUT_EXP: return exp_standin(x);
-        default: return erf_standin(x);
+        case HOLO_LUT_SIGMOID: y = sigmoid_ref(x); break;
+        case HOLO_LUT_TANH: y = tanh_ref(x); break;
+        case HOLO_LUT_GELU: y = gelu_ref(x); break;
+        case HOLO_LUT_SILU: y = silu_ref(x); break;
+        case HOLO_LUT_EXP: y = exp_standin(x); break;
+        default: y = erf_standin(x); break;
     }
+    if (y != y) y = (x != x) ? __uint_as_float(__float_as_uint(x) | 0x00400000u) : __uint_as_float(0xFFC00000u);
+    return y;
 }
 
 }  // namespace holo
