@@ -528,22 +528,25 @@ int32_t make_scales_map(CUtensorMap* map, const void* ptr, uint32_t past, uint32
 }
 
 uint32_t pick_splits(uint32_t tiles, uint32_t planes, int sm_count) {
-    // CTAs of roughly 3..8 tiles; among those, the split count that fills whole waves of
-    // 2 CTAs per SM best.
+    // Each CTA pays a fixed prologue (query digits) and epilogue (fold + merge), so it should
+    // walk many tiles; but the grid should also fill whole waves of 2 CTAs per SM. Take the
+    // smallest split count (<= 16 tiles per CTA) whose last wave is at least 96% full, else
+    // the best-filling one.
     const uint32_t slots = 2u * (uint32_t)sm_count;
-    uint32_t lo = (tiles + 7) / 8, hi = (tiles + 2) / 3;
-    if (lo < 1) lo = 1;
-    if (hi < lo) hi = lo;
-    if (hi > tiles) hi = tiles;
     const char* env = getenv("HOLO_ATTN_SPLITS");
     if (env && atoi(env) > 0) return (uint32_t)min((int)tiles, atoi(env));
+    uint32_t lo = (tiles + 15) / 16, hi = (tiles + 2) / 3;
+    if (lo < 1) lo = 1;
+    while ((uint64_t)planes * lo < slots && lo < tiles) ++lo;  // at least one full wave when possible
+    if (hi < lo) hi = lo;
+    if (hi > tiles) hi = tiles;
     uint32_t best = lo;
     double best_eff = -1.0;
     for (uint32_t s = lo; s <= hi; ++s) {
         uint64_t ctas = (uint64_t)planes * s;
         uint64_t waves = (ctas + slots - 1) / slots;
         double eff = (double)ctas / (double)(waves * slots);
-        if (ctas < slots) eff = (double)ctas / slots;
+        if (eff >= 0.96) return s;
         if (eff > best_eff + 1e-9) {
             best_eff = eff;
             best = s;

@@ -1,4 +1,408 @@
+// bf16 matmul with f32 accumulation and bf16 (truncated) output, plus the fused epilogues.
+// Replaces matmul_float / matmul_activation_float / matmul_add_float
+// (crates/hologram-compute/src/cpu/float_kernels.rs:298-399, 822-891): C = trunc_bf16(A[m,k] . B[k,n]),
+// both operands row-major; the epilogue re-widens the truncated product, applies the
+// activation (as a lookup in the 16-bit LUT, bit-identical to the CPU's scalar function) or
+// adds the residual in f32, and truncates again.
+//
+// Tensor-core kernel (sm_100a): one 128 x BN output tile per CTA, K in 64-wide blocks.
+//   warp 0   TMA producer: A tile (K-major, 128B swizzle) and B tile (N-major, 128B swizzle)
+//            into a shared-memory ring, mbarrier full/empty pairs
+//   warp 1   tcgen05.mma issuer (one elected lane), accumulator in TMEM (128 lanes x BN columns);
+//            tcgen05.commit releases ring slots and signals the epilogue
+//   warps 2-5 epilogue: tcgen05.ld the accumulator rows, narrow, epilogue op, store
+// Skinny problems (few output tiles) split K across CTAs: f32 partial tiles go to scratch and a
+// second kernel sums them in split order and applies the epilogue (one truncation, as the
+// reference).  Every mbarrier wait is bounded; a wait that gives up raises a status bit, and
+// the CTA still frees its TMEM before it exits.
+#include <cuda.h>
+#include <stdlib.h>
+
 #include "common.h"
-int32_t holo_launch_matmul(holo_b200_ctx*, const void*, const void*, void*, uint32_t, uint32_t, uint32_t, uint8_t, uint8_t, const void*) {
-    return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul kernel not built");
+#include "numerics.cuh"
+
+namespace {
+
+constexpr int BM = 128, BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+
+struct GemmParams {
+    uint16_t* out;            // bf16 output (direct epilogue)
+    float* partial;           // [splits][m][n] f32 (split-K)
+    const uint16_t* residual; // bf16 or null
+    const uint16_t* table;    // 65536-entry LUT of the fused activation or null
+    uint32_t* status;
+    uint32_t m, n, k, kblocks, splits, box_m;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (it > 64) __nanosleep(64);
+    }
+    *abort_flag = 1;
+    atomicOr(status, 4u);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+// Shared-memory matrix descriptor for tcgen05.mma: start address, leading / stride byte
+// offsets (all in 16-byte units), descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// One bf16 result: truncate the accumulator, then the fused epilogue on the truncated value
+// (float_kernels.rs:844-847, 886-889).
+__device__ __forceinline__ uint16_t epilogue_elem(float acc, const uint16_t* table, const uint16_t* residual, uint64_t idx) {
+    uint16_t h = holo::f32_to_bf16_trunc(acc);
+    if (table) h = __ldg(table + h);
+    if (residual) h = holo::f32_to_bf16_trunc(__fadd_rn(holo::bf16_to_f32(h), holo::bf16_to_f32(__ldg(residual + idx))));
+    return h;
+}
+
+template <int BN, int STAGES>
+struct GemmSmem {
+    static constexpr uint32_t A_BYTES = BM * BK * 2;           // 16 KiB
+    static constexpr uint32_t B_BYTES = BK * BN * 2;           // 8 or 16 KiB
+    static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
+    static constexpr uint32_t BARS = STAGES * STAGE;            // full[STAGES], empty[STAGES], accum, tmem slot, abort
+    static constexpr uint32_t TOTAL = BARS + 256 + 1024;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS)
+matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    using S = GemmSmem<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* sm = smem_raw + (base - raw);
+    const uint32_t bar_full = base + S::BARS, bar_empty = bar_full + 8 * STAGES, bar_accum = bar_empty + 8 * STAGES;
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sm + S::BARS + 16 * STAGES + 8);
+    volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(sm + S::BARS + 16 * STAGES + 12);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, split = blockIdx.z;
+    const uint32_t kb_begin = (uint32_t)(((uint64_t)p.kblocks * split) / p.splits);
+    const uint32_t kb_end = (uint32_t)(((uint64_t)p.kblocks * (split + 1)) / p.splits);
+    const uint32_t nkb = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_accum, 1);
+        *s_abort = (*reinterpret_cast<volatile uint32_t*>(p.status) & 4u) ? 1u : 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        // TMEM accumulator: BN columns (power of two >= 32) x 128 lanes of f32
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *s_tmem;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0 && !*s_abort) {
+            const uint32_t tx = p.box_m * BK * 2 + S::B_BYTES;
+            for (uint32_t i = 0; i < nkb; ++i) {
+                const uint32_t s = i % STAGES, use = i / STAGES;
+                if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1, s_abort, p.status)) break;
+                const uint32_t st = base + s * S::STAGE;
+                const int k0 = (int)((kb_begin + i) * BK);
+                mbar_arrive_expect_tx(bar_full + 8 * s, tx);
+                tma_load_2d(st, &map_a, k0, (int)m0, bar_full + 8 * s);
+#pragma unroll
+                for (int h = 0; h < BN / 64; ++h)
+                    tma_load_2d(st + S::A_BYTES + h * (BK * 128), &map_b, (int)(n0 + 64 * h), k0, bar_full + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0 && !*s_abort) {
+            // instruction descriptor: D = f32, A = B = bf16, A K-major, B N-major, N = BN, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (uint32_t i = 0; i < nkb && ok; ++i) {
+                const uint32_t s = i % STAGES, use = i / STAGES;
+                ok = mbar_wait(bar_full + 8 * s, use & 1, s_abort, p.status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = base + s * S::STAGE, b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+                for (int j = 0; j < BK / 16; ++j) {
+                    // A: 16 k-elements = 32 bytes inside the swizzled 128-byte row; 8-row groups 1024 B apart
+                    const uint64_t da = smem_desc(a_addr + j * 32, 16, 1024);
+                    // B: 16 k-rows = two 8-row groups (1024 B apart); 64-column chunks BK*128 B apart
+                    const uint64_t db = smem_desc(b_addr + j * 2048, BK * 128, 1024);
+                    umma_bf16(tmem_base, da, db, idesc, (i | (uint32_t)j) != 0 ? 1u : 0u);
+                }
+                umma_commit(bar_empty + 8 * s);  // frees the ring slot once these MMAs have read it
+            }
+            if (ok) umma_commit(bar_accum);      // accumulator complete
+        }
+    } else {
+        // ---------------- epilogue warps (TMEM lane quarter = warp % 4) ----------------
+        const uint32_t quarter = warp & 3u;
+        const uint32_t row = m0 + quarter * 32 + lane;
+        bool ok = nkb == 0 ? true : mbar_wait(bar_accum, 0, s_abort, p.status);
+        ok = __all_sync(0xffffffffu, ok) && !*s_abort;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                if (nkb != 0) {
+                    tmem_ld32(tmem_base + ((quarter * 32u) << 16) + (uint32_t)(c * 32), v);
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) v[x] = 0u;
+                }
+                const uint32_t col0 = n0 + c * 32;
+                if (row < p.m && col0 < p.n) {
+                    if (p.splits > 1) {
+                        float* dst = p.partial + ((uint64_t)split * p.m + row) * p.n + col0;
+                        if (col0 + 32 <= p.n && ((uintptr_t)dst & 15u) == 0) {
+#pragma unroll
+                            for (int x = 0; x < 8; ++x)
+                                reinterpret_cast<uint4*>(dst)[x] = make_uint4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
+                        } else {
+                            for (int x = 0; x < 32 && col0 + x < p.n; ++x) dst[x] = __uint_as_float(v[x]);
+                        }
+                    } else {
+                        const uint64_t idx0 = (uint64_t)row * p.n + col0;
+                        uint16_t* dst = p.out + idx0;
+                        if (col0 + 32 <= p.n && ((uintptr_t)dst & 15u) == 0) {
+                            uint32_t w[16];
+#pragma unroll
+                            for (int x = 0; x < 16; ++x) {
+                                uint16_t lo = epilogue_elem(__uint_as_float(v[2 * x]), p.table, p.residual, idx0 + 2 * x);
+                                uint16_t hi = epilogue_elem(__uint_as_float(v[2 * x + 1]), p.table, p.residual, idx0 + 2 * x + 1);
+                                w[x] = (uint32_t)lo | ((uint32_t)hi << 16);
+                            }
+#pragma unroll
+                            for (int x = 0; x < 4; ++x)
+                                reinterpret_cast<uint4*>(dst)[x] = make_uint4(w[4 * x], w[4 * x + 1], w[4 * x + 2], w[4 * x + 3]);
+                        } else {
+                            for (int x = 0; x < 32 && col0 + x < p.n; ++x)
+                                dst[x] = epilogue_elem(__uint_as_float(v[x]), p.table, p.residual, idx0 + x);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // everyone meets here, whatever happened above, so that TMEM is always released
+    __syncwarp();  // the single-lane producer / issuer loops rejoin their warps first
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+// Sum the split-K partial tiles in split order, then the epilogue (one truncation).
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint16_t* __restrict__ out, const uint16_t* __restrict__ table,
+                                     const uint16_t* __restrict__ residual, uint64_t mn, uint32_t splits) {
+    uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= mn) return;
+    if (i + 4 <= mn && ((uintptr_t)(out + i) & 7u) == 0 && (mn & 3u) == 0) {
+        float4 acc = *reinterpret_cast<const float4*>(partial + i);
+        for (uint32_t s = 1; s < splits; ++s) {
+            float4 v = *reinterpret_cast<const float4*>(partial + (uint64_t)s * mn + i);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        uint16_t h0 = epilogue_elem(acc.x, table, residual, i), h1 = epilogue_elem(acc.y, table, residual, i + 1);
+        uint16_t h2 = epilogue_elem(acc.z, table, residual, i + 2), h3 = epilogue_elem(acc.w, table, residual, i + 3);
+        *reinterpret_cast<uint2*>(out + i) = make_uint2((uint32_t)h0 | ((uint32_t)h1 << 16), (uint32_t)h2 | ((uint32_t)h3 << 16));
+    } else {
+        for (uint64_t e = i; e < mn && e < i + 4; ++e) {
+            float acc = partial[e];
+            for (uint32_t s = 1; s < splits; ++s) acc += partial[(uint64_t)s * mn + e];
+            out[e] = epilogue_elem(acc, table, residual, e);
+        }
+    }
+}
+
+// Shapes the tensor-core path cannot take (row pitches that are not 16-byte multiples,
+// unaligned bases) and tiny problems: one thread per output cell running the reference's
+// own per-cell recurrence, an ascending-k fused multiply-add chain (mul-then-add in the
+// n % 8 column tail, cpu/simd.rs:746-799) -- bit-identical to the CPU kernel.
+__global__ void matmul_bf16_cell_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, uint16_t* __restrict__ out,
+                                        const uint16_t* __restrict__ table, const uint16_t* __restrict__ residual, uint32_t m,
+                                        uint32_t k, uint32_t n) {
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x, i = blockIdx.y;
+    if (j >= n || i >= m) return;
+    const bool fused = j < n - (n % 8);
+    float acc = 0.0f;
+    for (uint32_t kk = 0; kk < k; ++kk) {
+        float av = holo::bf16_to_f32(a[(uint64_t)i * k + kk]), bv = holo::bf16_to_f32(b[(uint64_t)kk * n + j]);
+        acc = fused ? __fmaf_rn(av, bv, acc) : __fadd_rn(acc, __fmul_rn(av, bv));
+    }
+    out[(uint64_t)i * n + j] = epilogue_elem(acc, table, residual, (uint64_t)i * n + j);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    }
+    return fn;
+}
+
+int32_t make_map_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer) {
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * 2};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t es[2] = {1, 1};
+    CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: cuTensorMapEncodeTiled (matmul) returned %d", (int)r);
+    return HOLO_OK;
+}
+
+template <int BN, int STAGES>
+int32_t launch_umma(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid) {
+    using S = GemmSmem<BN, STAGES>;
+    static thread_local int configured_device = -1;
+    if (configured_device != ctx->device) {
+        HOLO_CUDA(cudaFuncSetAttribute(matmul_bf16_umma_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+        configured_device = ctx->device;
+    }
+    matmul_bf16_umma_kernel<BN, STAGES><<<grid, GEMM_THREADS, S::TOTAL, ctx->stream>>>(ma, mb, p);
+    HOLO_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return HOLO_OK;
+}
+
+}  // namespace
+
+int32_t holo_launch_matmul(holo_b200_ctx* ctx, const void* a, const void* b, void* out, uint32_t m, uint32_t k, uint32_t n,
+                           uint8_t dtype, uint8_t fused_act, const void* residual) {
+    (void)dtype;
+    const uint16_t* table = nullptr;
+    if (fused_act) {
+        int act = fused_act == HOLO_FUSED_GELU ? HOLO_LUT_GELU : fused_act == HOLO_FUSED_SILU ? HOLO_LUT_SILU
+                : fused_act == HOLO_FUSED_SIGMOID ? HOLO_LUT_SIGMOID : fused_act == HOLO_FUSED_TANH ? HOLO_LUT_TANH : HOLO_LUT_EXP;
+        HOLO_TRY(holo_lut_table(ctx, (uint8_t)act, HOLO_DTYPE_BF16, &table));
+    }
+    const bool tma_ok = (k % 8) == 0 && (n % 8) == 0 && (((uintptr_t)a | (uintptr_t)b) & 15u) == 0 && encode_tiled_fn() != nullptr;
+    const bool tiny = (uint64_t)m * n * k < (1ull << 18);
+    if (!tma_ok || tiny || getenv("HOLO_GEMM_FORCE_CELL")) {
+        dim3 grid((n + 127) / 128, m);
+        if (m > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul m %u on the per-cell path", m);
+        matmul_bf16_cell_kernel<<<grid, 128, 0, ctx->stream>>>((const uint16_t*)a, (const uint16_t*)b, (uint16_t*)out, table,
+                                                            (const uint16_t*)residual, m, k, n);
+        HOLO_CUDA(cudaGetLastError());
+        ctx->launches++;
+        return HOLO_OK;
+    }
+    const uint32_t kblocks = (k + BK - 1) / BK, mtiles = (m + BM - 1) / BM;
+    const uint32_t slots = 2u * (uint32_t)ctx->sm_count;
+    // Tile width and K split. Compute-bound shapes (many tiles) take 128-wide tiles and no
+    // split. HBM-bound skinny shapes want 128..slots co-resident CTAs sharing the memory
+    // system: narrow tiles first, then a K split whose f32 partials stay small.
+    int bn = 128;
+    uint32_t splits = 1;
+    const uint32_t tiles128 = mtiles * ((n + 127) / 128), tiles64 = mtiles * ((n + 63) / 64);
+    if (tiles128 < slots / 2 + slots / 4) {
+        bn = tiles64 <= slots ? 64 : 128;
+        const uint32_t tiles = bn == 64 ? tiles64 : tiles128;
+        if (tiles < slots / 2) {
+            splits = slots / 2 / tiles + ((slots / 2) % tiles ? 1 : 0);
+            if (splits > kblocks / 4) splits = kblocks / 4 ? kblocks / 4 : 1;
+        }
+    }
+    if (const char* e = getenv("HOLO_GEMM_BN")) bn = atoi(e) == 64 ? 64 : 128;
+    if (const char* e = getenv("HOLO_GEMM_SPLITS")) splits = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : 1;
+    if (splits > kblocks) splits = kblocks;
+    if (mtiles > 65535 || splits > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul grid too large");
+
+    GemmParams p;
+    p.out = (uint16_t*)out;
+    p.partial = nullptr;
+    p.residual = splits > 1 ? nullptr : (const uint16_t*)residual;
+    p.table = splits > 1 ? nullptr : table;
+    p.status = ctx->dev_status;
+    p.m = m; p.n = n; p.k = k; p.kblocks = kblocks; p.splits = splits;
+    p.box_m = m < (uint32_t)BM ? m : (uint32_t)BM;
+    if (splits > 1) {
+        HOLO_TRY(holo_ensure_scratch(ctx, (uint64_t)splits * m * n * 4));
+        p.partial = (float*)ctx->scratch;
+    }
+    CUtensorMap ma, mb;
+    HOLO_TRY(make_map_2d(&ma, a, k, m, BK, p.box_m));
+    HOLO_TRY(make_map_2d(&mb, b, n, k, 64, BK));
+    dim3 grid((n + bn - 1) / bn, mtiles, splits);
+    if (bn == 128) HOLO_TRY((launch_umma<128, 3>(ctx, ma, mb, p, grid)));
+    else HOLO_TRY((launch_umma<64, 4>(ctx, ma, mb, p, grid)));
+    if (splits > 1) {
+        const uint64_t mn = (uint64_t)m * n;
+        const uint64_t blocks = (mn / 4 + 255) / 256 + 1;
+        splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p.partial, (uint16_t*)out, table, (const uint16_t*)residual, mn, splits);
+        HOLO_CUDA(cudaGetLastError());
+        ctx->launches++;
+    }
+    return HOLO_OK;
 }
