@@ -6,5 +6,7 @@ Host-side mirror of the reference `hologram-compute` backend boundary
 from . import kernel_call
 from .backend import B200Backend, BackendError, DeviceWorkspace, HostWorkspace, EXPORTED_SYMBOLS, LIB_PATH
 
-__all__ = ["kernel_call", "B200Backend", "BackendError", "DeviceWorkspace", "HostWorkspace", "EXPORTED_SYMBOLS",
+from .session import InferenceSession, archive_check
+
+__all__ = ["InferenceSession", "archive_check", "kernel_call", "B200Backend", "BackendError", "DeviceWorkspace", "HostWorkspace", "EXPORTED_SYMBOLS",
            "LIB_PATH"]

@@ -36,7 +36,7 @@ class BackendError(RuntimeError):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m hologram_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python hologram_b200/build.py` "
             "(the B200 backend has no CPU fallback)")
     lib = C.CDLL(LIB_PATH)
     vp, u32, u64, i32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32

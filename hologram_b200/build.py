@@ -1,6 +1,6 @@
 """Build libhologram_b200.so (sm_100a only) in-tree with nvcc.
 
-Run: python -m hologram_b200.build [--force] [--verbose]
+Run: python hologram_b200/build.py [--force] [--verbose]   (by path: importing the package needs the built library)
 """
 import os
 import subprocess
@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libhologram_b200.so")
-SOURCES = ["api.cu", "lut.cu", "glue.cu", "attention.cu", "gemm.cu", "tp.cu"]
+SOURCES = ["api.cu", "lut.cu", "glue.cu", "attention.cu", "gemm.cu", "tp.cu", "session.cu", "archive.cpp", "blake3.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fno-fast-math", "--expt-relaxed-constexpr",
@@ -37,7 +37,7 @@ def build(force=False, verbose=False):
     procs = []
     for name in SOURCES:
         src = os.path.join(CSRC, name)
-        obj = os.path.join(CSRC, name[:-3] + ".o")
+        obj = os.path.join(CSRC, os.path.splitext(name)[0] + ".o")
         objs.append(obj)
         newest = max(os.path.getmtime(d) for d in _deps(src))
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < newest:

@@ -562,7 +562,7 @@ int32_t do_all_reduce(holo_b200_ctx* ctx, const HoloAllReduceCall& c, holo_b200_
 
 }  // namespace
 
-static int32_t dispatch_impl(holo_b200_ctx* ctx, const HoloKernelCall* call, holo_b200_workspace* ws) {
+int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, holo_b200_workspace* ws) {
     int act = lut_act_of_kind(call->kind);
     if (act >= 0) return do_unary_lut(ctx, call->u.unary, act, ws);
     switch (call->kind) {
@@ -591,34 +591,15 @@ extern "C" int32_t holo_b200_dispatch(holo_b200_ctx* ctx, const HoloKernelCall* 
     if (!ctx || !call || !ws) return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: null argument");
     if (ws->ctx != ctx) return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: workspace belongs to another context");
     HOLO_CUDA(cudaSetDevice(ctx->device));
-    return dispatch_impl(ctx, call, ws);
+    return holo_dispatch_internal(ctx, call, ws);
 }
 
 // ---- host-workspace form ---------------------------------------------------------------------
 namespace {
 
-// Every BufferRef of a call; `out_bytes` > 0 marks a written operand and gives the number of
-// bytes the kernel produces there (inputs carry 0).
-struct RefList {
-    HoloBufferRef* refs[12];
-    uint64_t out_bytes[12];
-    bool written[12];
-    int n = 0;
-    void in(HoloBufferRef* r) {
-        refs[n] = r;
-        out_bytes[n] = 0;
-        written[n] = false;
-        ++n;
-    }
-    void out(HoloBufferRef* r, uint64_t bytes) {
-        refs[n] = r;
-        out_bytes[n] = bytes;
-        written[n] = true;
-        ++n;
-    }
-};
+}  // namespace
 
-bool collect_refs(HoloKernelCall* c, RefList* l) {
+bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
     switch (c->kind) {
         case HOLO_K_SIGMOID: case HOLO_K_TANH: case HOLO_K_GELU: case HOLO_K_SILU: case HOLO_K_EXP: case HOLO_K_ERF:
             l->in(&c->u.unary.input);
@@ -686,18 +667,21 @@ bool collect_refs(HoloKernelCall* c, RefList* l) {
             l->out(&a.output, (uint64_t)a.batch * a.heads * a.q_rows * a.head_dim * holo_dtype_size(a.dtype));
             return true;
         }
+        case HOLO_K_ALL_REDUCE:
+            l->out(&c->u.all_reduce.buffer, c->u.all_reduce.element_count * holo_dtype_size(c->u.all_reduce.dtype));
+            return true;
         default: return false;
     }
 }
 
-}  // namespace
+
 
 extern "C" int32_t holo_b200_dispatch_host(holo_b200_ctx* ctx, const HoloKernelCall* call, HoloHostSlot* host_slots, uint32_t n_slots) {
     if (!ctx || !call || !host_slots) return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: null argument");
     HOLO_CUDA(cudaSetDevice(ctx->device));
     HoloKernelCall local = *call;
-    RefList refs;
-    if (!collect_refs(&local, &refs))
+    HoloRefList refs;
+    if (!holo_collect_refs(&local, &refs))
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: KernelCall variant %u has no host-workspace form", call->kind);
     // Each referenced host range gets a 256-byte aligned range of one device arena; the call
     // is rewritten to index a temporary device workspace with one slot per operand. Inputs
@@ -756,7 +740,7 @@ extern "C" int32_t holo_b200_dispatch_host(holo_b200_ctx* ctx, const HoloKernelC
         r.offset = 0;
         r.length = len[i];
     }
-    int32_t rc = dispatch_impl(ctx, &local, &tmp);
+    int32_t rc = holo_dispatch_internal(ctx, &local, &tmp);
     if (rc == HOLO_OK) {
         for (int i = 0; i < refs.n; ++i)
             if (refs.written[i] && host_ptr[i] && refs.out_bytes[i])

@@ -73,6 +73,30 @@ static inline bool holo_is_compute_float(uint8_t d) {
     return d == HOLO_DTYPE_F16 || d == HOLO_DTYPE_BF16 || d == HOLO_DTYPE_F32;
 }
 
+// Every BufferRef of a call; `out_bytes` > 0 marks a written operand and gives the number of
+// bytes the kernel produces there (inputs carry 0).
+struct HoloRefList {
+    HoloBufferRef* refs[12];
+    uint64_t out_bytes[12];
+    bool written[12];
+    int n = 0;
+    void in(HoloBufferRef* r) {
+        refs[n] = r;
+        out_bytes[n] = 0;
+        written[n] = false;
+        ++n;
+    }
+    void out(HoloBufferRef* r, uint64_t bytes) {
+        refs[n] = r;
+        out_bytes[n] = bytes;
+        written[n] = true;
+        ++n;
+    }
+};
+bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l);
+// Backend::dispatch body shared by the C entry points and the session walk.
+int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, holo_b200_workspace* ws);
+
 // ---- kernel launchers (each validates nothing: geometry is checked by the dispatcher) ------
 // lut.cu
 int32_t holo_lut_table(holo_b200_ctx* ctx, uint8_t act, uint8_t dtype, const uint16_t** table);

@@ -1,0 +1,107 @@
+"""`InferenceSession` over the C ABI: load a `.holo` image onto the device and walk it
+(crates/hologram-exec/src/session.rs `InferenceSession::{load, execute}`)."""
+import ctypes as C
+
+import numpy as np
+
+from . import kernel_call as kc
+from .backend import DeviceWorkspace, _check, _host_ptr, lib
+
+vp, u32, u64, i32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32
+for _name, _res, _args in [
+    ("holo_b200_session_load", i32, [vp, vp, u64, i32, C.POINTER(vp)]),
+    ("holo_b200_session_destroy", None, [vp]),
+    ("holo_b200_session_workspace", vp, [vp]),
+    ("holo_b200_session_info", i32, [vp] + [C.POINTER(u32)] * 5 + [C.POINTER(u64)]),
+    ("holo_b200_session_port", i32, [vp, i32, u32, C.c_char_p, u32, C.POINTER(u32), C.POINTER(u64), C.POINTER(C.c_uint8)]),
+    ("holo_b200_session_call", i32, [vp, u32, C.POINTER(kc.KernelCall)]),
+    ("holo_b200_session_execute", i32, [vp]),
+    ("holo_b200_session_capture", i32, [vp]),
+    ("holo_b200_archive_check", i32, [vp, u64, i32] + [C.POINTER(u32)] * 4),
+]:
+    _fn = getattr(lib, _name)
+    _fn.restype, _fn.argtypes = _res, _args
+
+SESSION_SYMBOLS = ["holo_b200_session_load", "holo_b200_session_destroy", "holo_b200_session_workspace",
+                   "holo_b200_session_info", "holo_b200_session_port", "holo_b200_session_call",
+                   "holo_b200_session_execute", "holo_b200_session_capture", "holo_b200_archive_check"]
+
+
+def archive_check(archive_bytes, verify=True):
+    """Host-only parse of a `.holo` image; returns (calls, inputs, outputs, constants) counts."""
+    buf = np.frombuffer(archive_bytes, dtype=np.uint8)
+    vals = [u32() for _ in range(4)]
+    _check(lib.holo_b200_archive_check(_host_ptr(buf), buf.size, 1 if verify else 0, *[C.byref(v) for v in vals]))
+    return tuple(v.value for v in vals)
+
+
+class Port:
+    def __init__(self, name, slot, element_count, dtype):
+        self.name, self.slot, self.element_count, self.dtype = name, slot, element_count, dtype
+
+    @property
+    def nbytes(self):
+        return self.element_count * {0: 1, 1: 1, 2: 1, 3: 8, 4: 4, 5: 8, 6: 2, 7: 2, 8: 4, 9: 8}[self.dtype]
+
+
+class InferenceSession:
+    def __init__(self, backend, archive_bytes, verify=True):
+        h = vp()
+        buf = np.frombuffer(archive_bytes, dtype=np.uint8)
+        _check(lib.holo_b200_session_load(backend._h, _host_ptr(buf), buf.size, 1 if verify else 0, C.byref(h)))
+        self._h = h
+        self.backend = backend
+        backend._workspaces.add(self)
+        ws = DeviceWorkspace.__new__(DeviceWorkspace)
+        ws._h, ws.backend, ws.n_slots = vp(lib.holo_b200_session_workspace(h)), backend, None
+        ws.close = lambda: None          # owned by the session
+        self.workspace = ws
+        vals = [u32() for _ in range(5)]
+        dev = u64()
+        _check(lib.holo_b200_session_info(h, *[C.byref(v) for v in vals], C.byref(dev)))
+        self.n_calls, self.fused_count, self.moved_in_place, n_in, n_out = (v.value for v in vals)
+        self.device_bytes = dev.value
+        self.inputs = [self._port(0, i) for i in range(n_in)]
+        self.outputs = [self._port(1, i) for i in range(n_out)]
+        self._by_name = {p.name: p for p in self.inputs + self.outputs}
+
+    def _port(self, is_output, i):
+        name = C.create_string_buffer(256)
+        slot, cnt, dt = u32(), u64(), C.c_uint8()
+        _check(lib.holo_b200_session_port(self._h, is_output, i, name, 256, C.byref(slot), C.byref(cnt), C.byref(dt)))
+        return Port(name.value.decode(), slot.value, cnt.value, dt.value)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib.holo_b200_session_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def port(self, name):
+        return self._by_name[name]
+
+    def call(self, index):
+        out = kc.KernelCall()
+        _check(lib.holo_b200_session_call(self._h, index, C.byref(out)))
+        return out
+
+    def write(self, name, array):
+        self.workspace.write(kc.rb(self.port(name).slot), array)
+
+    def read(self, name, dtype=np.uint8):
+        p = self.port(name)
+        return self.workspace.read(kc.rb(p.slot), p.nbytes, dtype)
+
+    def device_ptr(self, name):
+        return self.workspace.slot(self.port(name).slot)
+
+    def execute(self):
+        _check(lib.holo_b200_session_execute(self._h))
+
+    def capture(self):
+        _check(lib.holo_b200_session_capture(self._h))

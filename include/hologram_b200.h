@@ -319,6 +319,42 @@ typedef struct HoloHostSlot {
 int32_t holo_b200_dispatch_host(holo_b200_ctx* ctx, const HoloKernelCall* call, HoloHostSlot* host_slots,
                                 uint32_t n_slots);
 
+/* ---- archive session: the device-side counterpart of `InferenceSession::load` / `execute`
+ * (crates/hologram-exec/src/session.rs:399-792, 846-932) for archives made of the served call
+ * variants. Load parses the `.holo` image (BLAKE3 footer and weight fingerprints checked when
+ * `verify` != 0), applies the load-time MatMul epilogue fusion (session.rs:2150-2377), places
+ * every slot in HBM, uploads constants once, and realises input-port -> output-port
+ * KvCacheWrite calls as in-place moves (session.rs:1313-1370). The image may be freed after
+ * load returns. */
+typedef struct holo_b200_session holo_b200_session;
+int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* archive, uint64_t len, int32_t verify,
+                               holo_b200_session** out);
+void holo_b200_session_destroy(holo_b200_session* s);
+/* The session's device workspace (owned by the session): upload inputs / download outputs
+ * through it, or bind caller-owned device memory to a port's slot. */
+holo_b200_workspace* holo_b200_session_workspace(holo_b200_session* s);
+/* Counters (session.rs:1294-1303, 1385-1440 style): calls after fusion, fused pairs, in-place
+ * KV moves, port counts, bytes of HBM held by slots. Any pointer may be NULL. */
+int32_t holo_b200_session_info(holo_b200_session* s, uint32_t* n_calls, uint32_t* n_fused, uint32_t* n_moved,
+                               uint32_t* n_inputs, uint32_t* n_outputs, uint64_t* device_bytes);
+/* Port `index` of the Inputs (is_output == 0) or Outputs section (writer.rs:246-263). */
+int32_t holo_b200_session_port(holo_b200_session* s, int32_t is_output, uint32_t index, char* name, uint32_t name_cap,
+                               uint32_t* slot, uint64_t* element_count, uint8_t* dtype);
+/* Copy of call `index` in post-fusion execution order. */
+int32_t holo_b200_session_call(holo_b200_session* s, uint32_t index, HoloKernelCall* out);
+/* One walk over the call list (compute_and_label, session.rs:1052-1289, without the κ
+ * bookkeeping): every call is enqueued on the context stream; returns without synchronising. */
+int32_t holo_b200_session_execute(holo_b200_session* s);
+/* Capture one walk into a CUDA graph that later `execute` calls replay. Call after at least
+ * one plain execute. */
+int32_t holo_b200_session_capture(holo_b200_session* s);
+
+/* Parse an archive image on the host only (header, section table, call codec, ports,
+ * constants; BLAKE3 footer and weight fingerprints when `verify` != 0): the HoloLoader checks
+ * (crates/hologram-archive/src/loader.rs:141-267). Needs no device. */
+int32_t holo_b200_archive_check(const uint8_t* archive, uint64_t len, int32_t verify, uint32_t* n_calls,
+                                uint32_t* n_inputs, uint32_t* n_outputs, uint32_t* n_constants);
+
 /* ---- tensor-parallel group (no reference counterpart: the reference is single-device).
  * `nccl_unique_id` is the 128-byte ncclUniqueId produced by holo_b200_nccl_unique_id on rank 0
  * and broadcast by the host launcher. */

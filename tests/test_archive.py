@@ -1,0 +1,79 @@
+"""`.holo` wire format: writer vs the reference's frozen bytes, and the host-only loader checks (no GPU)."""
+import struct
+
+import blake3
+import numpy as np
+import pytest
+
+import hologram_b200 as hb
+from hologram_b200 import decoder_holo as dh
+from hologram_b200 import holo
+from hologram_b200 import kernel_call as kc
+
+
+def test_plain_matmul_wire_bytes_are_the_reference_golden():
+    # crates/hologram-archive/tests/wire_stability.rs:103-108
+    c = kc.KernelCall.MatMul(kc.MatMulCall(kc.rb(0, 0, 64), kc.rb(1, 0, 64), kc.rb(2, 0, 64), 2, 8, 4, 8, 0))
+    want = ("010000002e0000000000000000000000000040000000000000000100000000000000000000004000000000000000"
+            "020000000000000000000000400000000000000002000000080000000400000008" "00")
+    assert holo.encode_calls([c]).hex() == want
+
+
+def small_cfg():
+    return dh.DecoderConfig(d_model=256, n_heads=2, n_kv_heads=1, head_dim=128, ffn=512, vocab=512, n_layers=1, batch=2, bucket=32)
+
+
+def test_framing_and_footer():
+    img, info = dh.build_decoder_step(small_cfg())
+    assert img[:4] == b"HOLO" and struct.unpack("<H", img[4:6])[0] == 3
+    assert blake3.blake3(img[:-32]).digest() == img[-32:]        # writer.rs:217-225
+    calls, n_in, n_out, n_const = hb.archive_check(img)
+    assert calls == info["n_calls"] and n_in == len(info["inputs"]) and n_out == len(info["outputs"])
+    assert n_const == len(info["constants"])
+
+
+def test_corruption_is_refused():
+    img, _ = dh.build_decoder_step(small_cfg())
+    bad = bytearray(img)
+    bad[len(bad) // 2] ^= 1
+    with pytest.raises(hb.BackendError) as e:
+        hb.archive_check(bytes(bad))
+    assert "checksum" in str(e.value) or "fingerprint" in str(e.value)
+    with pytest.raises(hb.BackendError):
+        hb.archive_check(b"HOLX" + img[4:])
+    with pytest.raises(hb.BackendError):
+        hb.archive_check(img[:40])
+    v9 = bytearray(img)
+    v9[4:6] = struct.pack("<H", 9)
+    with pytest.raises(hb.BackendError) as e:
+        hb.archive_check(bytes(v9), verify=False)
+    assert "version" in str(e.value)
+
+
+def test_unserved_discriminant_is_refused():
+    w = holo.HoloWriter()
+    body = struct.pack("<IH", 1, 48) + b"\0" * 64          # Conv2d
+    img = holo.assemble([(holo.SEC_KERNEL_CALLS, [body]), (holo.SEC_WEIGHTS, [struct.pack("<I", 0)])])
+    with pytest.raises(hb.BackendError) as e:
+        hb.archive_check(img)
+    assert e.value.variant == "UnsupportedOp"
+
+
+def test_tensor_parallel_shards_partition_the_weights():
+    cfg = small_cfg()
+    cfg.n_heads, cfg.n_kv_heads = 4, 2
+    cfg.d_model = 512
+    full = dh.default_weights(cfg)
+    _, i0 = dh.build_decoder_step(cfg, 0, 2)
+    _, i1 = dh.build_decoder_step(cfg, 1, 2)
+    assert i0["heads"] == 2 and i0["kv_heads"] == 1 and i0["ffn"] == cfg.ffn // 2
+    # the column shards of wq, concatenated, are the full matrix
+    def find(info, nbytes, nth=0):
+        hits = [np.frombuffer(bytes(b), dtype=np.uint16) for _, (dt, b) in sorted(info["constants"].items()) if len(b) == nbytes]
+        return hits[nth]
+    hq = 2 * 128
+    a, b = find(i0, 512 * hq * 2).reshape(512, hq), find(i1, 512 * hq * 2).reshape(512, hq)
+    assert np.array_equal(np.concatenate([a, b], axis=1), full("l0.wq"))
+    # AllReduce precedes each residual add on every rank
+    kinds = [c.kind for c in i0["calls"]]
+    assert kinds.count(kc.K_ALL_REDUCE) == 2 * cfg.n_layers
