@@ -122,7 +122,7 @@ def workload_lut(be, torch, rank, args):
 
     return {
         "name": "lut_gelu_bf16_16777216",
-        "metric": "lut_activation_GBps", "unit": "GB/s", "dtype": "u16",
+        "metric": "lut_activation_GBps", "unit": "GB/s", "dtype": "u16", "scaling": "weak",
         "run_device": lambda step: be.dispatch(calls[step % pairs], ws),
         "run_host": lambda step: be.dispatch(hcall, hws),
         "ref_step": ref_step, "ref_fraction": 1.0,
@@ -196,7 +196,7 @@ def workload_attention(be, torch, rank, args, world=1):
 
     return {
         "name": f"decode_attention_q8_b{b}_h{h}_kv{kv}_d{d}_L{past}",
-        "metric": "q8kv_decode_attention_GBps", "unit": "GB/s", "dtype": "i8/f32",
+        "metric": "q8kv_decode_attention_GBps", "unit": "GB/s", "dtype": "i8/f32", "scaling": "strong",
         "run_device": lambda step: be.dispatch(call, ws),
         "run_host": lambda step: be.dispatch(call, hws),
         "ref_step": ref_step, "ref_fraction": 2 / b,
@@ -211,7 +211,158 @@ def workload_attention(be, torch, rank, args, world=1):
     }
 
 
-WORKLOADS = {"lut": workload_lut, "attention": workload_attention}
+def workload_decoder(be, torch, rank, args, world=1):
+    """Config 5: 8-layer Llama-style decoder `.holo`, batch 64, 4096 cached positions, int8 KV."""
+    import hologram_b200 as hb
+    from hologram_b200 import decoder_holo as dh
+    from hologram_b200 import kernel_call as kc
+    cfg = dh.DecoderConfig()
+    if os.environ.get("HOLO_BENCH_LAYERS"):
+        cfg.n_layers = int(os.environ["HOLO_BENCH_LAYERS"])
+    shapes = {"wq": (cfg.d_model, cfg.n_heads * cfg.head_dim), "wk": (cfg.d_model, cfg.n_kv_heads * cfg.head_dim),
+              "wv": (cfg.d_model, cfg.n_kv_heads * cfg.head_dim), "wo": (cfg.n_heads * cfg.head_dim, cfg.d_model),
+              "wg": (cfg.d_model, cfg.ffn), "wu": (cfg.d_model, cfg.ffn), "wd": (cfg.ffn, cfg.d_model),
+              "embed": (cfg.vocab, cfg.d_model), "lm_head": (cfg.d_model, cfg.vocab)}
+
+    def weights(name):
+        # random-init N(0, 0.02^2) bf16, generated on the GPU (same seed on every rank), read back
+        base = name.split(".")[-1]
+        g = torch.Generator(device="cuda").manual_seed(0xC5 * 1000003 + sum(ord(c) * (i + 1) for i, c in enumerate(name)))
+        if base in ("g1", "g2", "gf"):
+            t = 1.0 + 0.02 * torch.randn(cfg.d_model, generator=g, device="cuda")
+        else:
+            t = 0.02 * torch.randn(shapes[base], generator=g, device="cuda")
+        return t.to(torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
+
+    t0 = time.time()
+    img, info = dh.build_decoder_step(cfg, rank, world, weights=weights)
+    t1 = time.time()
+    sess = hb.InferenceSession(be, img, verify=True)
+    t2 = time.time()
+    nbytes_img = len(img)
+    del img
+    H, KV, hd, B, L = info["heads"], info["kv_heads"], cfg.head_dim, cfg.batch, cfg.bucket
+    # KV cache content: the row quantizer applied on the device to seeded N(0,1) bf16 rows
+    rows = B * KV * L
+    scratch = hb.DeviceWorkspace(be, 3)
+    g = torch.Generator(device="cuda").manual_seed(0xC5 + rank)
+    for l in range(cfg.n_layers):
+        for which in ("k", "v"):
+            src = torch.randn(rows * hd, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+            scratch.bind(0, src.data_ptr(), rows * hd * 2)
+            scratch.bind(1, *sess.device_ptr(f"l{l}.{which}_codes"))
+            scratch.bind(2, *sess.device_ptr(f"l{l}.{which}_scales"))
+            be.dispatch(kc.KernelCall.QuantizeRowsI8(kc.QuantizeRowsI8Call(kc.rb(0), kc.rb(1), kc.rb(2), rows, hd, kc.DTYPE_BF16)), scratch)
+            be.synchronize()
+            del src
+    rng = np.random.default_rng(0xC5)
+    position = 4096 + 17
+    host = {"token_ids": rng.integers(0, cfg.vocab, size=B).astype(np.int32),
+            "pos": np.array([position], dtype=np.int32), "valid_len": np.array([L], dtype=np.int32)}
+    host["cos_q"], host["sin_q"] = dh.rope_tables(cfg, position, H)
+    host["cos_k"], host["sin_k"] = dh.rope_tables(cfg, position, KV)
+    pinned = {k: torch.from_numpy(np.ascontiguousarray(v).view(np.uint8).copy()).pin_memory() for k, v in host.items()}
+    for k, v in pinned.items():
+        sess.write(k, v.numpy())
+    sess.execute()          # eager walk: allocates scratch, builds LUT tables
+    be.synchronize()
+    use_graph = os.environ.get("HOLO_BENCH_GRAPH", "1") != "0"
+    if use_graph:
+        sess.capture()
+    logits_host = torch.empty(B * info["vocab"], dtype=torch.int16).pin_memory()
+    lp, lbytes = sess.device_ptr("logits")
+    import ctypes
+    from hologram_b200.backend import lib, _check
+
+    def run_host(step):
+        for k, v in pinned.items():
+            sess.write(k, v.numpy())
+        sess.execute()
+        _check(lib.holo_b200_workspace_download(sess.workspace._h, kc.rb(sess.port("logits").slot), ctypes.c_void_p(logits_host.data_ptr()), B * info["vocab"] * 2))
+
+    weight_bytes = sum(len(b) for s_, (dt, b) in info["constants"].items()) - cfg.vocab * cfg.d_model * 2 + B * cfg.d_model * 2
+    kv_bytes = cfg.n_layers * 2 * rows * (hd + 4)
+    algo = weight_bytes + kv_bytes
+
+    def cpu_baseline():
+        return decoder_cpu_sample(cfg)
+
+    return {
+        "name": f"llama8L_d{cfg.d_model}_b{B}_L{L}_tp{world}",
+        "metric": "decode_tokens_per_s", "unit": "tokens/s", "dtype": "bf16 (int8 KV cache, f32 accumulation)", "scaling": "strong",
+        "run_device": lambda step: sess.execute(),
+        "run_host": run_host,
+        "units_per_step": B / world,   # the batch is replicated over the TP group: count it once
+        "launches_per_step": sess.n_calls,
+        "roofline": {"bound": "hbm", "bytes_per_launch": algo},
+        "h2d": sum(v.numel() for v in pinned.values()), "d2h": B * info["vocab"] * 2,
+        "cpu_baseline": cpu_baseline,
+        "config": {"workload": f"config[4]: {cfg.n_layers}-layer Llama-style decoder .holo, d_model {cfg.d_model}, {cfg.n_heads} q / {cfg.n_kv_heads} kv heads, "
+                               f"head_dim {hd}, SwiGLU {cfg.ffn}, vocab {cfg.vocab}, batch {B} x 1 token per step, {L} cached positions, int8 KV, TP {world}",
+                   "l2": "per-step working set (weights + KV, >= 1 GB per GPU) exceeds the 126 MB L2",
+                   "cuda_graph": use_graph, "calls_per_step": sess.n_calls, "fused_pairs": sess.fused_count,
+                   "archive_bytes": nbytes_img, "build_s": round(t1 - t0, 1), "load_s": round(t2 - t1, 1),
+                   "roofline_note": "roofline is for the whole step: algorithmic bytes = per-GPU matmul weights + KV codes and scales read once"},
+        "keep": (sess, pinned, logits_host, scratch),
+    }
+
+
+def decoder_cpu_sample(cfg, steps=1):
+    """Reference CPU path for the decoder on a bounded sample: one full-shape layer plus the
+    LM head through the CPU interpreter (all host threads); tokens/s extrapolated to the
+    configured layer count."""
+    from hologram_b200 import decoder_holo as dh
+    from oracle import interp, oracle as orc
+    one = dh.DecoderConfig(d_model=cfg.d_model, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim, ffn=cfg.ffn,
+                           vocab=cfg.vocab, n_layers=1, batch=cfg.batch, bucket=cfg.bucket)
+    rng = np.random.default_rng(5)
+
+    def weights(name):
+        base = name.split(".")[-1]
+        shp = {"wq": (one.d_model, one.n_heads * one.head_dim), "wk": (one.d_model, one.n_kv_heads * one.head_dim),
+               "wv": (one.d_model, one.n_kv_heads * one.head_dim), "wo": (one.n_heads * one.head_dim, one.d_model),
+               "wg": (one.d_model, one.ffn), "wu": (one.d_model, one.ffn), "wd": (one.ffn, one.d_model),
+               "embed": (one.vocab, one.d_model), "lm_head": (one.d_model, one.vocab)}.get(base, (one.d_model,))
+        n = int(np.prod(shp))
+        # uniform bf16 bit patterns in the N(0, 0.02^2) magnitude range: content does not change CPU time
+        return (rng.integers(0x3A00, 0x3D00, size=n, dtype=np.uint16) | (rng.integers(0, 2, size=n, dtype=np.uint16) << 15)).reshape(shp)
+
+    _, info = dh.build_decoder_step(one, 0, 1, weights=weights)
+    slots = {s: np.frombuffer(bytes(body), dtype=np.uint8).copy() for s, (dt, body) in info["constants"].items()}
+    rows = one.batch * one.n_kv_heads * one.bucket
+    for p in info["inputs"]:
+        nb = info["slot_bytes"][p.slot]
+        if "codes" in p.name:
+            slots[p.slot] = rng.integers(-127, 128, size=nb, dtype=np.int8).view(np.uint8)
+        elif "scales" in p.name:
+            slots[p.slot] = (rng.random(nb // 4, dtype=np.float32) * 0.03).view(np.uint8)
+        elif p.name == "valid_len":
+            slots[p.slot] = np.array([one.bucket], dtype=np.int32).view(np.uint8)
+        elif p.name == "token_ids":
+            slots[p.slot] = rng.integers(0, one.vocab, size=one.batch).astype(np.int32).view(np.uint8)
+        elif p.name.startswith("cos"):
+            slots[p.slot] = np.full(nb // 2, 0x3F80, dtype=np.uint16).view(np.uint8)
+        else:
+            slots[p.slot] = np.zeros(nb, dtype=np.uint8)
+    calls = info["calls"]
+    head = calls[-6:-4] if False else None
+    t0 = time.perf_counter()
+    interp.run(calls, slots)
+    t_all = time.perf_counter() - t0
+    # split: time the LM head (final norm + matmul) separately so the layer time can be scaled
+    lm = [c for c in calls if c.kind == 46][-1]
+    t0 = time.perf_counter()
+    interp.run([lm], slots)
+    t_head = time.perf_counter() - t0
+    t_layer = max(t_all - t_head, 1e-9)
+    t_step = cfg.n_layers * t_layer + t_head
+    return {"value": cfg.batch / t_step, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"1 of {cfg.n_layers} layers + LM head at full shapes through the CPU interpreter "
+                      f"(layer {t_layer:.2f} s, head {t_head:.2f} s), extrapolated to {cfg.n_layers} layers",
+            "t_step_s": t_step}
+
+
+WORKLOADS = {"lut": workload_lut, "attention": workload_attention, "decoder": workload_decoder}
 
 
 def main():
@@ -219,7 +370,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default=os.environ.get("HOLO_BENCH_WORKLOAD", "lut"))
+    ap.add_argument("--workload", default=os.environ.get("HOLO_BENCH_WORKLOAD", "decoder"))
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -241,11 +392,16 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     be = hb.B200Backend(local_rank)
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream()          # a real stream: the legacy default stream cannot be captured into a graph
+    torch.cuda.set_stream(stream)
     be.set_stream(stream.cuda_stream)
 
+    if world > 1 and args.workload == "decoder":
+        uid = [hb.B200Backend.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        be.init_tp(uid[0], rank, world)
     fn = WORKLOADS[args.workload]
-    wl = fn(be, torch, rank, args, world) if args.workload == "attention" else fn(be, torch, rank, args)
+    wl = fn(be, torch, rank, args, world) if args.workload in ("attention", "decoder") else fn(be, torch, rank, args)
 
     def barrier():
         torch.cuda.synchronize()
@@ -292,7 +448,7 @@ def main():
         achieved = wl["roofline"]["bytes_per_launch"] / (per_step_ms / 1e3) / 1e9
         line = {
             "metric": wl["metric"], "value": value, "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": per_step_ms, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": per_step_ms, "higher_is_better": True, "scaling": wl["scaling"],
             "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic (seeded)",
             "config": dict(wl["config"], name=wl["name"]),
             "clocks": clocks, "gpu_launches": launches,
@@ -324,6 +480,27 @@ def main_reference(args, rank, world):
     from hologram_b200 import kernel_call as kc
     from oracle import oracle as orc
     wlname = args.workload
+    if wlname == "decoder":
+        from hologram_b200 import decoder_holo as dh
+        cfg = dh.DecoderConfig()
+        budget, used, t_steps = 150.0, 0, []
+        t_start = time.perf_counter()
+        while used < max(1, args.steps) and (time.perf_counter() - t_start) < budget:
+            t_steps.append(decoder_cpu_sample(cfg)["t_step_s"])
+            used += 1
+        t_step = float(np.mean(t_steps))
+        value = cfg.batch / t_step
+        print(json.dumps({
+            "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": used, "warmup": 0, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 (int8 KV cache, f32 accumulation)", "data": "synthetic (seeded)",
+            "config": {"workload": f"config[4]: {cfg.n_layers}-layer Llama-style decoder, batch {cfg.batch}, {cfg.bucket} cached positions, int8 KV"},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+                             "sample": "per step: 1 of 8 layers + LM head at full shapes on all host threads, extrapolated to 8 layers; "
+                                       f"{used} sample steps fit the time budget"},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }), flush=True)
+        return
     if wlname == "lut":
         n = 16_777_216
         x = synth_c1(n, 0xC1)

@@ -2,6 +2,9 @@
 
 #include <string.h>
 
+#include <thread>
+#include <vector>
+
 namespace {
 
 const uint32_t IV[8] = {0x6A09E667u, 0xBB67AE85u, 0x3C6EF372u, 0xA54FF53Au, 0x510E527Fu, 0x9B05688Cu, 0x1F83D9ABu, 0x5BE0CD19u};
@@ -79,32 +82,78 @@ void parent_cv(const uint32_t left[8], const uint32_t right[8], uint32_t extra_f
     compress(IV, block, 0, 64, PARENT | extra_flags, out);
 }
 
+
+
+// Chaining value of a block of 2^k whole chunks starting at chunk `first` (a complete subtree).
+void subtree_cv(const uint8_t* data, size_t nchunks, uint64_t first, uint32_t out[8]) {
+    uint32_t stack[32][8];
+    int depth = 0;
+    for (size_t i = 0; i < nchunks; ++i) {
+        uint32_t cv[8];
+        chunk_cv(data + i * 1024, 1024, first + i, 0, cv);
+        size_t total = i + 1;
+        while ((total & 1) == 0) {
+            uint32_t merged[8];
+            parent_cv(stack[depth - 1], cv, 0, merged);
+            memcpy(cv, merged, sizeof cv);
+            --depth;
+            total >>= 1;
+        }
+        memcpy(stack[depth++], cv, sizeof cv);
+    }
+    memcpy(out, stack[0], 8 * sizeof(uint32_t));
+}
+
 }  // namespace
 
 void holo_blake3(const uint8_t* data, size_t len, uint8_t out[32]) {
     uint32_t result[8];
-    const size_t CHUNK = 1024;
+    const size_t CHUNK = 1024, BLOCK_CHUNKS = 1024;  // 1 MiB complete subtrees, hashed in parallel
     size_t nchunks = len == 0 ? 1 : (len + CHUNK - 1) / CHUNK;
     if (nchunks == 1) {
         chunk_cv(data, len, 0, ROOT, result);
     } else {
-        // Left-to-right merge with a stack of subtree chaining values: after chunk i is pushed,
-        // subtrees are merged while the count of completed chunks has trailing zero bits. The
-        // last chunk is held back so the final merges can carry the ROOT flag.
+        // Left-to-right merge with a stack of subtree chaining values: whenever the count of
+        // completed chunks has trailing zero bits, the top subtrees of equal size are merged.
+        // The last chunk is held back so that the final merges can carry the ROOT flag. Whole
+        // 1 MiB blocks in front of it are complete subtrees and are hashed by worker threads.
+        const size_t nblocks = (nchunks - 1) / BLOCK_CHUNKS;
+        std::vector<uint32_t> block_cvs(nblocks * 8);
+        if (nblocks > 0) {
+            unsigned hw = std::thread::hardware_concurrency();
+            size_t nthreads = hw == 0 ? 4 : hw;
+            if (nthreads > 32) nthreads = 32;
+            if (nthreads > nblocks) nthreads = nblocks;
+            std::vector<std::thread> pool;
+            for (size_t t = 0; t < nthreads; ++t)
+                pool.emplace_back([&, t]() {
+                    for (size_t b = t; b < nblocks; b += nthreads)
+                        subtree_cv(data + b * BLOCK_CHUNKS * CHUNK, BLOCK_CHUNKS, b * BLOCK_CHUNKS, &block_cvs[b * 8]);
+                });
+            for (auto& th : pool) th.join();
+        }
         uint32_t stack[64][8];
         int depth = 0;
-        for (size_t i = 0; i + 1 < nchunks; ++i) {
-            uint32_t cv[8];
-            chunk_cv(data + i * CHUNK, CHUNK, i, 0, cv);
-            size_t total = i + 1;
+        auto push = [&](uint32_t* cv, size_t total_chunks, size_t unit) {
+            size_t total = total_chunks / unit;
             while ((total & 1) == 0) {
                 uint32_t merged[8];
                 parent_cv(stack[depth - 1], cv, 0, merged);
-                memcpy(cv, merged, sizeof cv);
+                memcpy(cv, merged, 8 * sizeof(uint32_t));
                 --depth;
                 total >>= 1;
             }
-            memcpy(stack[depth++], cv, sizeof cv);
+            memcpy(stack[depth++], cv, 8 * sizeof(uint32_t));
+        };
+        for (size_t b = 0; b < nblocks; ++b) {
+            uint32_t cv[8];
+            memcpy(cv, &block_cvs[b * 8], sizeof cv);
+            push(cv, (b + 1) * BLOCK_CHUNKS, BLOCK_CHUNKS);
+        }
+        for (size_t i = nblocks * BLOCK_CHUNKS; i + 1 < nchunks; ++i) {
+            uint32_t cv[8];
+            chunk_cv(data + i * CHUNK, CHUNK, i, 0, cv);
+            push(cv, i + 1, 1);
         }
         uint32_t cv[8];
         size_t last = nchunks - 1;
