@@ -620,3 +620,111 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a) 
     }
     return HOLO_OK;
 }
+
+// ---- allocation-free entry point ----------------------------------------------------------------
+// Some callers must not allocate device memory when they run attention: a serving loop that
+// has handed all of HBM to its own arena and treats any cudaMalloc as a fault, or code running
+// where the CUDA allocator may synchronise the device and stall every other stream. For them
+// the split-KV partials live in a fixed array that is part of the library image instead of the
+// context's growable scratch buffer. Every GPU that loads the library holds these 16 MiB until
+// the process exits.
+constexpr uint64_t STATIC_SCRATCH_BYTES = 16ull << 20;
+static __device__ __align__(256) unsigned char g_attn_static_scratch[STATIC_SCRATCH_BYTES];
+static __device__ __align__(256) uint32_t g_attn_static_status[64];
+
+namespace {
+struct StaticDevice {
+    void* scratch = nullptr;
+    uint32_t* status = nullptr;
+    int sm_count = 0;
+    bool ready = false;
+};
+StaticDevice g_static_dev[64];
+}  // namespace
+
+extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const void* q, const int8_t* k_past,
+                                                        const float* k_past_scales, const int8_t* v_past,
+                                                        const float* v_past_scales, const int8_t* k_new,
+                                                        const float* k_new_scales, const int8_t* v_new,
+                                                        const float* v_new_scales, const uint32_t* valid_len, void* out,
+                                                        uint32_t batch, uint32_t heads, uint32_t kv_heads, uint32_t past_len,
+                                                        uint32_t head_dim, uint32_t scale_bits, uint8_t dtype) {
+    if (batch == 0 || heads == 0 || head_dim == 0) return HOLO_OK;
+    const uint32_t hkv = kv_heads == 0 ? heads : kv_heads;
+    if (hkv == 0 || heads % hkv != 0)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: decode_attention_valid: heads must be a multiple of kv_heads (grouped-query)");
+    if (!holo_is_compute_float(dtype))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: decode_attention_q8_static: q/output dtype must be f32, f16 or bf16");
+    const uint32_t G = heads / hkv, planes = batch * hkv;
+    const bool aligned = (((uintptr_t)k_past | (uintptr_t)v_past | (uintptr_t)k_past_scales | (uintptr_t)v_past_scales |
+                           (uintptr_t)k_new | (uintptr_t)v_new) & 15u) == 0 &&
+                         (((uintptr_t)valid_len | (uintptr_t)k_new_scales | (uintptr_t)v_new_scales) & 3u) == 0;
+    if (head_dim != HD || G > MAXG || past_len < 4 || (past_len % 4) != 0 || !aligned || planes > 65535 || encode_tiled_fn() == nullptr)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP,
+                         "unsupported op: decode_attention_q8_static serves head_dim 128, at most 4 query heads per kv head, a cache "
+                         "bucket that is a multiple of 4 rows, 16-byte aligned code/scale pointers and batch*kv_heads <= 65535");
+    int dev = 0;
+    HOLO_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: device ordinal %d", dev);
+    StaticDevice& sd = g_static_dev[dev];
+    if (!sd.ready) {
+        // One-time set-up for this device (its first call; make it before any stream capture).
+        // In host code the array's name is only a handle for the runtime: the address a
+        // kernel can use comes from cudaGetSymbolAddress, with this device current.
+        HOLO_CUDA(cudaGetSymbolAddress(&sd.scratch, g_attn_static_scratch));
+        HOLO_CUDA(cudaGetSymbolAddress((void**)&sd.status, g_attn_static_status));
+        HOLO_CUDA(cudaDeviceGetAttribute(&sd.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        HOLO_CUDA(cudaFuncSetAttribute(decode_attention_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        sd.ready = true;
+    }
+    const uint32_t tiles = (past_len + TK - 1) / TK + 1;
+    const uint32_t splits = pick_splits(tiles, planes, sd.sm_count);
+    const uint64_t po_bytes = (uint64_t)planes * splits * MAXG * HD * 4, pml_bytes = (uint64_t)planes * splits * MAXG * 2 * 4;
+    if (splits > 1 && po_bytes + pml_bytes > STATIC_SCRATCH_BYTES)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP,
+                         "unsupported op: decode_attention_q8_static needs %llu bytes of split-KV partials for this shape; the built-in "
+                         "scratch holds %llu (use holo_b200_dispatch, whose scratch grows)",
+                         (unsigned long long)(po_bytes + pml_bytes), (unsigned long long)STATIC_SCRATCH_BYTES);
+    float scale_div = sqrtf((float)head_dim);
+    if (scale_div < 1.0f) scale_div = 1.0f;
+    if (scale_bits != 0) {
+        float sm;
+        memcpy(&sm, &scale_bits, 4);
+        if (sm > 0.0f) scale_div = 1.0f / sm;
+    }
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    const uint32_t box_rows = past_len < (uint32_t)TK ? past_len : (uint32_t)TK;
+    CUtensorMap mk, mv, mks, mvs;
+    HOLO_TRY(make_codes_map(&mk, k_past, past_len, planes, box_rows));
+    HOLO_TRY(make_codes_map(&mv, v_past, past_len, planes, box_rows));
+    HOLO_TRY(make_scales_map(&mks, k_past_scales, past_len, planes, box_rows));
+    HOLO_TRY(make_scales_map(&mvs, v_past_scales, past_len, planes, box_rows));
+    // The status word must start at zero (a CTA that sees bit 1 set does not start); the
+    // partials need no clearing: every (plane, split) slot the merge reads is rewritten first.
+    HOLO_CUDA(cudaMemsetAsync(sd.status, 0, sizeof(uint32_t), stream));
+    FaParams p;
+    p.q = q;
+    p.k_new = k_new;
+    p.v_new = v_new;
+    p.k_new_s = k_new_scales;
+    p.v_new_s = v_new_scales;
+    p.valid_len = valid_len;
+    p.out = out;
+    p.part_o = (float*)sd.scratch;
+    p.part_ml = (float*)((uint8_t*)sd.scratch + po_bytes);
+    p.status = sd.status;
+    p.past = past_len;
+    p.G = G;
+    p.splits = splits;
+    p.box_rows = box_rows;
+    p.scale_div = scale_div;
+    p.dtype = dtype;
+    dim3 grid(splits, planes);
+    decode_attention_q8_kernel<<<grid, FA_THREADS, SMEM_TOTAL, stream>>>(mk, mv, mks, mvs, p);
+    HOLO_CUDA(cudaGetLastError());
+    if (splits > 1) {
+        decode_attention_combine_kernel<<<planes * G, HD, 0, stream>>>(p.part_o, p.part_ml, out, splits, G, dtype);
+        HOLO_CUDA(cudaGetLastError());
+    }
+    return HOLO_OK;
+}

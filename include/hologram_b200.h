@@ -355,6 +355,26 @@ int32_t holo_b200_session_capture(holo_b200_session* s);
 int32_t holo_b200_archive_check(const uint8_t* archive, uint64_t len, int32_t verify, uint32_t* n_calls,
                                 uint32_t* n_inputs, uint32_t* n_outputs, uint32_t* n_constants);
 
+/* Decode attention over an int8 KV cache for callers that must not allocate device memory.
+ * It has no counterpart in the reference; it is DecodeAttentionValidQ8 (q_rows = new_len = 1)
+ * taken with plain device pointers and a CUDA stream instead of a context and a workspace.
+ * The split-KV partial results go to a 16 MiB array built into the library (each GPU that loads
+ * the library keeps that array until the process exits) rather than to the context's growable
+ * scratch buffer, so the call performs no cudaMalloc / cudaFree and needs no context.
+ * Limits: head_dim 128; heads / kv_heads <= 4; past_len a multiple of 4 and >= 4; code and scale
+ * pointers 16-byte aligned; shapes whose partials exceed the array (batch * kv_heads * splits * 4 *
+ * 130 floats, about 260 kv-head planes at 8 splits) are refused with HOLO_ERR_UNSUPPORTED_OP.
+ * The first call on each device looks the array up (the device of the calling thread must be the
+ * stream's device); make that first call before any stream capture begins. All calls share the
+ * array: two calls that overlap on the GPU (different streams) race on it. Enqueues on
+ * `cuda_stream` and returns without synchronising. */
+int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const void* q, const int8_t* k_past,
+                                             const float* k_past_scales, const int8_t* v_past, const float* v_past_scales,
+                                             const int8_t* k_new, const float* k_new_scales, const int8_t* v_new,
+                                             const float* v_new_scales, const uint32_t* valid_len, void* out,
+                                             uint32_t batch, uint32_t heads, uint32_t kv_heads, uint32_t past_len,
+                                             uint32_t head_dim, uint32_t scale_bits, uint8_t dtype);
+
 /* ---- tensor-parallel group (no reference counterpart: the reference is single-device).
  * `nccl_unique_id` is the 128-byte ncclUniqueId produced by holo_b200_nccl_unique_id on rank 0
  * and broadcast by the host launcher. */
