@@ -362,7 +362,61 @@ def decoder_cpu_sample(cfg, steps=1):
             "t_step_s": t_step}
 
 
-WORKLOADS = {"lut": workload_lut, "attention": workload_attention, "decoder": workload_decoder}
+def workload_matmul(be, torch, rank, args, skinny=False):
+    """Config 2: bf16 matmul, f32 accumulation, bf16 output. 4096^3 (tensor-core bound) or
+    16 x 4096 x 14336 (HBM bound); operands rotated over buffers larger than L2."""
+    import hologram_b200 as hb
+    from hologram_b200 import kernel_call as kc
+    m, k, n = (16, 4096, 14336) if skinny else (4096, 4096, 4096)
+    if os.environ.get("HOLO_BENCH_MKN"):
+        m, k, n = (int(v) for v in os.environ["HOLO_BENCH_MKN"].split(","))
+    sets = max(2, int(300e6 // (2 * (m * k + k * n + m * n))) + 1)
+    g = torch.Generator(device="cuda").manual_seed(0xC3 + rank)
+    A = [(torch.randn(m * k, generator=g, device="cuda") / k ** 0.5).to(torch.bfloat16) for _ in range(sets)]
+    Bm = [(torch.randn(k * n, generator=g, device="cuda") / k ** 0.5).to(torch.bfloat16) for _ in range(sets)]
+    C = [torch.empty(m * n, dtype=torch.bfloat16, device="cuda") for _ in range(sets)]
+    ws = hb.DeviceWorkspace(be, 3 * sets)
+    calls = []
+    for i in range(sets):
+        for j, t in enumerate((A[i], Bm[i], C[i])):
+            ws.bind(3 * i + j, t.data_ptr(), t.numel() * 2)
+        calls.append(kc.KernelCall.MatMul(kc.MatMulCall(kc.rb(3 * i), kc.rb(3 * i + 1), kc.rb(3 * i + 2), m, k, n, kc.DTYPE_BF16, 0)))
+    host = [t.cpu().pin_memory() for t in (A[0], Bm[0], C[0])]
+    hws = hb.HostWorkspace([t.view(torch.int16).numpy() for t in host])
+    hcall = kc.KernelCall.MatMul(kc.MatMulCall(kc.rb(0), kc.rb(1), kc.rb(2), m, k, n, kc.DTYPE_BF16, 0))
+    flops, nbytes = 2.0 * m * k * n, 2.0 * (m * k + k * n + m * n)
+
+    def cpu_baseline():
+        from oracle import oracle as orc
+        mm = min(m, 64)
+        a = host[0].view(torch.int16).numpy().view(np.uint16)[:mm * k]
+        b = host[1].view(torch.int16).numpy().view(np.uint16)
+        t0 = time.perf_counter()
+        orc.matmul(a, b, mm, k, n, kc.DTYPE_BF16, which=orc.fast_lib())
+        dt = time.perf_counter() - t0
+        v = (2.0 * mm * k * n / dt / 1e12) if not skinny else (nbytes * mm / m / dt / 1e9)
+        return {"value": v, "unit": "TFLOP/s" if not skinny else "GB/s", "cores": os.cpu_count(), "kind": "port",
+                "sample": f"{mm} of {m} rows of A against the full B, all host threads"}
+
+    return {
+        "name": f"matmul_bf16_{m}x{k}x{n}",
+        "metric": "matmul_bf16_GBps" if skinny else "matmul_bf16_TFLOPs", "unit": "GB/s" if skinny else "TFLOP/s",
+        "dtype": "bf16 (f32 accumulation)", "scaling": "weak",
+        "run_device": lambda step: be.dispatch(calls[step % sets], ws),
+        "run_host": lambda step: be.dispatch(hcall, hws),
+        "units_per_step": nbytes / 1e9 if skinny else flops / 1e12,
+        "launches_per_step": 1,
+        "roofline": {"bound": "hbm", "bytes_per_launch": nbytes} if skinny else {"bound": "tensor", "flops_per_launch": flops},
+        "h2d": 2 * (m * k + k * n), "d2h": 2 * m * n,
+        "cpu_baseline": cpu_baseline,
+        "config": {"workload": f"config[2]: bf16 matmul M={m} K={k} N={n}, f32 accumulation, bf16 output, A,B ~ N(0, 1/K)",
+                   "l2": f"{sets} rotated operand sets (> 126 MB L2)"},
+        "keep": (A, Bm, C, host),
+    }
+
+
+WORKLOADS = {"lut": workload_lut, "attention": workload_attention, "decoder": workload_decoder,
+             "matmul": workload_matmul, "gemv": lambda *a: workload_matmul(*a, skinny=True)}
 
 
 def main():
@@ -445,16 +499,20 @@ def main():
         peaks = measured_peaks()
         per_step_ms = ms / args.steps
         value = wl["units_per_step"] * world * args.steps / (ms / 1e3)
-        achieved = wl["roofline"]["bytes_per_launch"] / (per_step_ms / 1e3) / 1e9
+        if wl["roofline"]["bound"] == "tensor":
+            achieved = wl["roofline"]["flops_per_launch"] / (per_step_ms / 1e3) / 1e12
+            peak, punit = peaks["bf16_tflops"], "TFLOP/s"
+        else:
+            achieved = wl["roofline"]["bytes_per_launch"] / (per_step_ms / 1e3) / 1e9
+            peak, punit = peaks["hbm_gbs"], "GB/s"
         line = {
             "metric": wl["metric"], "value": value, "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": per_step_ms, "higher_is_better": True, "scaling": wl["scaling"],
             "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic (seeded)",
             "config": dict(wl["config"], name=wl["name"]),
             "clocks": clocks, "gpu_launches": launches,
-            "roofline": {"bound": wl["roofline"]["bound"], "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None,
-                         "peak_source": peaks["source"], "frac_of_8TBps_nominal": achieved / 8000.0},
+            "roofline": {"bound": wl["roofline"]["bound"], "achieved": achieved, "peak": peak, "unit": punit,
+                         "frac": achieved / peak, "traffic": None, "peak_source": peaks["source"]},
             "e2e": e2e,
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -29,7 +29,13 @@ namespace {
 
 constexpr int TK = 128;           // keys per tile
 constexpr int HD = 128;           // head_dim served by the tiled kernel
-constexpr int STAGES = 3;
+#ifndef HOLO_ATTN_STAGES
+#define HOLO_ATTN_STAGES 2
+#endif
+#ifndef HOLO_ATTN_MINB
+#define HOLO_ATTN_MINB 3
+#endif
+constexpr int STAGES = HOLO_ATTN_STAGES;
 constexpr int CONSUMER_WARPS = 4;
 constexpr int FA_THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr int MAXG = 4;           // query heads per kv head served by the tiled kernel
@@ -53,6 +59,7 @@ struct FaParams {
     uint32_t past, G, splits, box_rows;
     float scale_div;
     int dtype;
+    int debug_skip;  // measurement aid: 1 = consumers only release the tiles (pure streaming)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -129,7 +136,7 @@ __device__ __forceinline__ float exp2_guard(float s, float m) {
     return exp2f((s - m) * LOG2E);
 }
 
-__global__ void __launch_bounds__(FA_THREADS, 2)
+__global__ void __launch_bounds__(FA_THREADS, HOLO_ATTN_MINB)
 decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                            const __grid_constant__ CUtensorMap map_ks, const __grid_constant__ CUtensorMap map_vs,
                            const FaParams p) {
@@ -307,7 +314,7 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         // keys of this warp: tile rows 32*warp .. +31; number of visible rows in the tile
         const uint32_t limit = t < tiles_past ? min((uint32_t)TK, vis_past - t * TK) : 1u;
         const uint32_t row0 = warp * 32;
-        if (row0 < limit) {
+        if (row0 < limit && !p.debug_skip) {
             // ---- scores: S[(head,digit)][key] = sum_c Qdigit * Kcode (exact i32) ----
             int sacc[4][4];
 #pragma unroll
@@ -532,7 +539,7 @@ uint32_t pick_splits(uint32_t tiles, uint32_t planes, int sm_count) {
     // walk many tiles; but the grid should also fill whole waves of 2 CTAs per SM. Take the
     // smallest split count (<= 16 tiles per CTA) whose last wave is at least 96% full, else
     // the best-filling one.
-    const uint32_t slots = 2u * (uint32_t)sm_count;
+    const uint32_t slots = (uint32_t)HOLO_ATTN_MINB * (uint32_t)sm_count;
     const char* env = getenv("HOLO_ATTN_SPLITS");
     if (env && atoi(env) > 0) return (uint32_t)min((int)tiles, atoi(env));
     uint32_t lo = (tiles + 15) / 16, hi = (tiles + 2) / 3;
@@ -609,6 +616,7 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a) 
     p.box_rows = box_rows;
     p.scale_div = a.scale_div;
     p.dtype = a.dtype;
+    p.debug_skip = getenv("HOLO_ATTN_DEBUG_SKIP") ? 1 : 0;
     dim3 grid(splits, planes);
     decode_attention_q8_kernel<<<grid, FA_THREADS, SMEM_TOTAL, ctx->stream>>>(mk, mv, mks, mvs, p);
     HOLO_CUDA(cudaGetLastError());
@@ -719,6 +727,7 @@ extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const
     p.box_rows = box_rows;
     p.scale_div = scale_div;
     p.dtype = dtype;
+    p.debug_skip = 0;
     dim3 grid(splits, planes);
     decode_attention_q8_kernel<<<grid, FA_THREADS, SMEM_TOTAL, stream>>>(mk, mv, mks, mvs, p);
     HOLO_CUDA(cudaGetLastError());

@@ -132,6 +132,16 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a);
 // gemm.cu
 int32_t holo_launch_matmul(holo_b200_ctx* ctx, const void* a, const void* b, void* out, uint32_t m, uint32_t k,
                            uint32_t n, uint8_t dtype, uint8_t fused_act, const void* residual);
+// One column segment of a merged matmul: `width` columns of the product go to `out`
+// ([m, width] row-major) through their own epilogue.
+struct HoloMatmulSeg {
+    void* out;
+    const void* residual;
+    uint32_t width;
+    uint8_t fused_act;
+};
+int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* b, uint32_t m, uint32_t k, uint32_t n,
+                                 const HoloMatmulSeg* segs, uint32_t nseg);
 // tp.cu
 int32_t holo_all_reduce(holo_b200_ctx* ctx, void* buf, uint64_t n, uint8_t dtype);
 void holo_tp_destroy(holo_b200_ctx* ctx);

@@ -11,9 +11,9 @@
 //   warp 1   tcgen05.mma issuer (one elected lane), accumulator in TMEM (128 lanes x BN columns);
 //            tcgen05.commit releases ring slots and signals the epilogue
 //   warps 2-5 epilogue: tcgen05.ld the accumulator rows, narrow, epilogue op, store
-// Skinny problems (few output tiles) split K across CTAs: f32 partial tiles go to scratch and a
-// second kernel sums them in split order and applies the epilogue (one truncation, as the
-// reference).  Every mbarrier wait is bounded; a wait that gives up raises a status bit, and
+// Skinny problems (few output tiles) split K across CTAs: f32 partial tiles go to scratch (they
+// stay in L2) and a second kernel sums them in split order and applies the epilogue (one
+// truncation, as the reference).  Every mbarrier wait is bounded; a wait that gives up raises a status bit, and
 // the CTA still frees its TMEM before it exits.
 #include <cuda.h>
 #include <stdlib.h>
@@ -27,11 +27,22 @@ constexpr int BM = 128, BK = 64;
 constexpr int GEMM_THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 
-struct GemmParams {
-    uint16_t* out;            // bf16 output (direct epilogue)
-    float* partial;           // [splits][m][n] f32 (split-K)
-    const uint16_t* residual; // bf16 or null
+// One output segment: columns [col_begin, col_end) of the product go to their own row-major
+// [m, col_end - col_begin] buffer with their own epilogue. A plain matmul has one segment; the
+// session's sibling-matmul merge (several products of the same A against concatenated weights)
+// has up to three. Segment boundaries are multiples of 32 columns.
+struct GemmSeg {
+    uint16_t* out;            // bf16 output
     const uint16_t* table;    // 65536-entry LUT of the fused activation or null
+    const uint16_t* residual; // bf16 [m, width] or null
+    uint32_t col_begin, col_end;
+};
+constexpr int MAX_SEGS = 3;
+
+struct GemmParams {
+    GemmSeg seg[MAX_SEGS];
+    uint32_t nseg;
+    float* partial;           // [splits][m][n] f32 (split-K)
     uint32_t* status;
     uint32_t m, n, k, kblocks, splits, box_m;
 };
@@ -105,19 +116,24 @@ __device__ __forceinline__ uint16_t epilogue_elem(float acc, const uint16_t* tab
     return h;
 }
 
-template <int BN, int STAGES>
+// A_ROWS = rows of the A tile that are backed by the ring (the TMA box never has more rows than
+// min(m, 128)). With fewer than 128 the MMA still reads 128 rows: the rest is whatever follows in
+// shared memory, and those accumulator rows are never stored. A smaller A slot buys more stages,
+// i.e. more weight bytes in flight per CTA, which is what an HBM-bound skinny product needs.
+template <int BN, int STAGES, int A_ROWS>
 struct GemmSmem {
-    static constexpr uint32_t A_BYTES = BM * BK * 2;           // 16 KiB
+    static constexpr uint32_t A_BYTES = A_ROWS * BK * 2;       // 2, 8 or 16 KiB
     static constexpr uint32_t B_BYTES = BK * BN * 2;           // 8 or 16 KiB
     static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
-    static constexpr uint32_t BARS = STAGES * STAGE;            // full[STAGES], empty[STAGES], accum, tmem slot, abort
+    static constexpr uint32_t RING = STAGES * STAGE + (BM - A_ROWS) * BK * 2;  // tail pad: the last A read stays in bounds
+    static constexpr uint32_t BARS = (RING + 1023u) & ~1023u;   // full[STAGES], empty[STAGES], accum, tmem slot, abort, flag
     static constexpr uint32_t TOTAL = BARS + 256 + 1024;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int A_ROWS>
 __global__ void __launch_bounds__(GEMM_THREADS)
 matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
-    using S = GemmSmem<BN, STAGES>;
+    using S = GemmSmem<BN, STAGES, A_ROWS>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -195,48 +211,59 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         // ---------------- epilogue warps (TMEM lane quarter = warp % 4) ----------------
         const uint32_t quarter = warp & 3u;
         const uint32_t row = m0 + quarter * 32 + lane;
-        bool ok = nkb == 0 ? true : mbar_wait(bar_accum, 0, s_abort, p.status);
-        ok = __all_sync(0xffffffffu, ok) && !*s_abort;
+        const uint32_t epi_tid = threadIdx.x - 64;
+        if (nkb != 0) mbar_wait(bar_accum, 0, s_abort, p.status);
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // all four epilogue warps see the same abort state
+        const bool ok = !*s_abort;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
+        if (ok && p.splits == 1) {
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
-                if (nkb != 0) {
-                    tmem_ld32(tmem_base + ((quarter * 32u) << 16) + (uint32_t)(c * 32), v);
-                } else {
-#pragma unroll
-                    for (int x = 0; x < 32; ++x) v[x] = 0u;
-                }
+                tmem_ld32(tmem_base + ((quarter * 32u) << 16) + (uint32_t)(c * 32), v);
                 const uint32_t col0 = n0 + c * 32;
                 if (row < p.m && col0 < p.n) {
-                    if (p.splits > 1) {
-                        float* dst = p.partial + ((uint64_t)split * p.m + row) * p.n + col0;
-                        if (col0 + 32 <= p.n && ((uintptr_t)dst & 15u) == 0) {
+                    uint32_t si = 0;
+                    while (si + 1 < p.nseg && col0 >= p.seg[si].col_end) ++si;
+                    const GemmSeg sg = p.seg[si];
+                    const uint64_t idx0 = (uint64_t)row * (sg.col_end - sg.col_begin) + (col0 - sg.col_begin);
+                    uint16_t* dst = sg.out + idx0;
+                    if (col0 + 32 <= sg.col_end && ((uintptr_t)dst & 15u) == 0) {
+                        uint32_t w[16];
 #pragma unroll
-                            for (int x = 0; x < 8; ++x)
-                                reinterpret_cast<uint4*>(dst)[x] = make_uint4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
-                        } else {
-                            for (int x = 0; x < 32 && col0 + x < p.n; ++x) dst[x] = __uint_as_float(v[x]);
+                        for (int x = 0; x < 16; ++x) {
+                            uint16_t lo = epilogue_elem(__uint_as_float(v[2 * x]), sg.table, sg.residual, idx0 + 2 * x);
+                            uint16_t hi = epilogue_elem(__uint_as_float(v[2 * x + 1]), sg.table, sg.residual, idx0 + 2 * x + 1);
+                            w[x] = (uint32_t)lo | ((uint32_t)hi << 16);
                         }
+#pragma unroll
+                        for (int x = 0; x < 4; ++x)
+                            reinterpret_cast<uint4*>(dst)[x] = make_uint4(w[4 * x], w[4 * x + 1], w[4 * x + 2], w[4 * x + 3]);
                     } else {
-                        const uint64_t idx0 = (uint64_t)row * p.n + col0;
-                        uint16_t* dst = p.out + idx0;
-                        if (col0 + 32 <= p.n && ((uintptr_t)dst & 15u) == 0) {
-                            uint32_t w[16];
 #pragma unroll
-                            for (int x = 0; x < 16; ++x) {
-                                uint16_t lo = epilogue_elem(__uint_as_float(v[2 * x]), p.table, p.residual, idx0 + 2 * x);
-                                uint16_t hi = epilogue_elem(__uint_as_float(v[2 * x + 1]), p.table, p.residual, idx0 + 2 * x + 1);
-                                w[x] = (uint32_t)lo | ((uint32_t)hi << 16);
-                            }
+                        for (int x = 0; x < 32; ++x)
+                            if (col0 + x < sg.col_end) dst[x] = epilogue_elem(__uint_as_float(v[x]), sg.table, sg.residual, idx0 + x);
+                    }
+                }
+            }
+        } else if (ok) {
+            // split-K: store this CTA's f32 partial tile; a second kernel sums the partials in split
+            // order and applies the epilogue (one truncation).
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((quarter * 32u) << 16) + (uint32_t)(c * 32), v);
+                const uint32_t col0 = n0 + c * 32;
+                if (row < p.m && col0 < p.n) {
+                    float* dst = p.partial + ((uint64_t)split * p.m + row) * p.n + col0;
+                    if (col0 + 32 <= p.n) {
 #pragma unroll
-                            for (int x = 0; x < 4; ++x)
-                                reinterpret_cast<uint4*>(dst)[x] = make_uint4(w[4 * x], w[4 * x + 1], w[4 * x + 2], w[4 * x + 3]);
-                        } else {
-                            for (int x = 0; x < 32 && col0 + x < p.n; ++x)
-                                dst[x] = epilogue_elem(__uint_as_float(v[x]), p.table, p.residual, idx0 + x);
-                        }
+                        for (int x = 0; x < 8; ++x)
+                            reinterpret_cast<uint4*>(dst)[x] = make_uint4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 32; ++x)
+                            if (col0 + x < p.n) dst[x] = __uint_as_float(v[x]);
                     }
                 }
             }
@@ -252,26 +279,34 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
 }
 
-// Sum the split-K partial tiles in split order, then the epilogue (one truncation).
-__global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint16_t* __restrict__ out, const uint16_t* __restrict__ table,
-                                     const uint16_t* __restrict__ residual, uint64_t mn, uint32_t splits) {
-    uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (i >= mn) return;
-    if (i + 4 <= mn && ((uintptr_t)(out + i) & 7u) == 0 && (mn & 3u) == 0) {
-        float4 acc = *reinterpret_cast<const float4*>(partial + i);
-        for (uint32_t s = 1; s < splits; ++s) {
-            float4 v = *reinterpret_cast<const float4*>(partial + (uint64_t)s * mn + i);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
-        uint16_t h0 = epilogue_elem(acc.x, table, residual, i), h1 = epilogue_elem(acc.y, table, residual, i + 1);
-        uint16_t h2 = epilogue_elem(acc.z, table, residual, i + 2), h3 = epilogue_elem(acc.w, table, residual, i + 3);
-        *reinterpret_cast<uint2*>(out + i) = make_uint2((uint32_t)h0 | ((uint32_t)h1 << 16), (uint32_t)h2 | ((uint32_t)h3 << 16));
+
+// Sum the split-K partial tiles in split order, then the epilogue (one truncation). Four
+// consecutive columns per thread (segment boundaries are multiples of 32, n of 8).
+struct ReduceParams {
+    GemmSeg seg[MAX_SEGS];
+    uint32_t nseg, splits, n;
+    uint64_t mn;
+};
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, const ReduceParams p) {
+    const uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= p.mn) return;
+    float4 acc = *reinterpret_cast<const float4*>(partial + i);
+    for (uint32_t s = 1; s < p.splits; ++s) {
+        float4 v = *reinterpret_cast<const float4*>(partial + (uint64_t)s * p.mn + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const uint32_t row = (uint32_t)(i / p.n), col = (uint32_t)(i % p.n);
+    uint32_t si = 0;
+    while (si + 1 < p.nseg && col >= p.seg[si].col_end) ++si;
+    const GemmSeg sg = p.seg[si];
+    const uint64_t idx = (uint64_t)row * (sg.col_end - sg.col_begin) + (col - sg.col_begin);
+    uint16_t h0 = epilogue_elem(acc.x, sg.table, sg.residual, idx), h1 = epilogue_elem(acc.y, sg.table, sg.residual, idx + 1);
+    uint16_t h2 = epilogue_elem(acc.z, sg.table, sg.residual, idx + 2), h3 = epilogue_elem(acc.w, sg.table, sg.residual, idx + 3);
+    uint16_t* dst = sg.out + idx;
+    if (((uintptr_t)dst & 7u) == 0) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)h0 | ((uint32_t)h1 << 16), (uint32_t)h2 | ((uint32_t)h3 << 16));
     } else {
-        for (uint64_t e = i; e < mn && e < i + 4; ++e) {
-            float acc = partial[e];
-            for (uint32_t s = 1; s < splits; ++s) acc += partial[(uint64_t)s * mn + e];
-            out[e] = epilogue_elem(acc, table, residual, e);
-        }
+        dst[0] = h0; dst[1] = h1; dst[2] = h2; dst[3] = h3;
     }
 }
 
@@ -322,15 +357,15 @@ int32_t make_map_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t 
     return HOLO_OK;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int A_ROWS>
 int32_t launch_umma(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid) {
-    using S = GemmSmem<BN, STAGES>;
+    using S = GemmSmem<BN, STAGES, A_ROWS>;
     static thread_local int configured_device = -1;
     if (configured_device != ctx->device) {
-        HOLO_CUDA(cudaFuncSetAttribute(matmul_bf16_umma_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+        HOLO_CUDA(cudaFuncSetAttribute(matmul_bf16_umma_kernel<BN, STAGES, A_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
         configured_device = ctx->device;
     }
-    matmul_bf16_umma_kernel<BN, STAGES><<<grid, GEMM_THREADS, S::TOTAL, ctx->stream>>>(ma, mb, p);
+    matmul_bf16_umma_kernel<BN, STAGES, A_ROWS><<<grid, GEMM_THREADS, S::TOTAL, ctx->stream>>>(ma, mb, p);
     HOLO_CUDA(cudaGetLastError());
     ctx->launches++;
     return HOLO_OK;
@@ -338,17 +373,46 @@ int32_t launch_umma(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap
 
 }  // namespace
 
-int32_t holo_launch_matmul(holo_b200_ctx* ctx, const void* a, const void* b, void* out, uint32_t m, uint32_t k, uint32_t n,
-                           uint8_t dtype, uint8_t fused_act, const void* residual) {
-    (void)dtype;
-    const uint16_t* table = nullptr;
+static int32_t act_table(holo_b200_ctx* ctx, uint8_t fused_act, const uint16_t** table) {
+    *table = nullptr;
     if (fused_act) {
         int act = fused_act == HOLO_FUSED_GELU ? HOLO_LUT_GELU : fused_act == HOLO_FUSED_SILU ? HOLO_LUT_SILU
                 : fused_act == HOLO_FUSED_SIGMOID ? HOLO_LUT_SIGMOID : fused_act == HOLO_FUSED_TANH ? HOLO_LUT_TANH : HOLO_LUT_EXP;
-        HOLO_TRY(holo_lut_table(ctx, (uint8_t)act, HOLO_DTYPE_BF16, &table));
+        HOLO_TRY(holo_lut_table(ctx, (uint8_t)act, HOLO_DTYPE_BF16, table));
     }
+    return HOLO_OK;
+}
+
+int32_t holo_launch_matmul(holo_b200_ctx* ctx, const void* a, const void* b, void* out, uint32_t m, uint32_t k, uint32_t n,
+                           uint8_t dtype, uint8_t fused_act, const void* residual) {
+    (void)dtype;
+    HoloMatmulSeg sg = {out, residual, n, fused_act};
+    return holo_launch_matmul_multi(ctx, a, b, m, k, n, &sg, 1);
+}
+
+// C[:, segment i] = epilogue_i(A . B[:, segment i]) for 1..3 column segments of one [k, n] B.
+int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* b, uint32_t m, uint32_t k, uint32_t n,
+                                 const HoloMatmulSeg* segs, uint32_t nseg) {
+    if (nseg < 1 || nseg > MAX_SEGS) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul segment count %u", nseg);
+    GemmSeg gs[MAX_SEGS] = {};
+    uint32_t col = 0;
+    for (uint32_t i = 0; i < nseg; ++i) {
+        HOLO_TRY(act_table(ctx, segs[i].fused_act, &gs[i].table));
+        gs[i].out = (uint16_t*)segs[i].out;
+        gs[i].residual = (const uint16_t*)segs[i].residual;
+        gs[i].col_begin = col;
+        col += segs[i].width;
+        gs[i].col_end = col;
+        if (i + 1 < nseg && (col % 32) != 0) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul segment boundary %u is not a multiple of 32", col);
+    }
+    if (col != n) return holo_fail(HOLO_ERR_SHAPE_MISMATCH, "shape mismatch: matmul segments cover %u of %u columns", col, n);
+    const uint16_t* table = gs[0].table;
+    const void* residual = gs[0].residual;
+    void* out = gs[0].out;
     const bool tma_ok = (k % 8) == 0 && (n % 8) == 0 && (((uintptr_t)a | (uintptr_t)b) & 15u) == 0 && encode_tiled_fn() != nullptr;
     const bool tiny = (uint64_t)m * n * k < (1ull << 18);
+    if (nseg > 1 && (!tma_ok || tiny))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: merged matmul needs the tensor-core path");
     if (!tma_ok || tiny || getenv("HOLO_GEMM_FORCE_CELL")) {
         dim3 grid((n + 127) / 128, m);
         if (m > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul m %u on the per-cell path", m);
@@ -363,27 +427,37 @@ int32_t holo_launch_matmul(holo_b200_ctx* ctx, const void* a, const void* b, voi
     // Tile width and K split. Compute-bound shapes (many tiles) take 128-wide tiles and no
     // split. HBM-bound skinny shapes want 128..slots co-resident CTAs sharing the memory
     // system: narrow tiles first, then a K split whose f32 partials stay small.
+    // Tile width and K split. Compute-bound shapes (many row tiles) take 128-wide tiles, no split.
+    // One-row-tile shapes (decode) are HBM-bound: loaded HBM latency is 2-3 us, so 15-20 MB of
+    // weight bytes must be in flight across the chip. Measured on B200: with >= ~200 128-wide
+    // tiles, or >= one 64-wide tile per SM, no split is best (every CTA walks K in step with its
+    // neighbours, which keeps DRAM pages open); narrower outputs split K about 8 ways, partials stay
+    // in L2 and a second kernel reduces them.
     int bn = 128;
     uint32_t splits = 1;
     const uint32_t tiles128 = mtiles * ((n + 127) / 128), tiles64 = mtiles * ((n + 63) / 64);
-    if (tiles128 < slots / 2 + slots / 4) {
-        bn = tiles64 <= slots ? 64 : 128;
-        const uint32_t tiles = bn == 64 ? tiles64 : tiles128;
-        if (tiles < slots / 2) {
-            splits = slots / 2 / tiles + ((slots / 2) % tiles ? 1 : 0);
-            if (splits > kblocks / 4) splits = kblocks / 4 ? kblocks / 4 : 1;
+    if (mtiles == 1 && tiles128 < 200) {
+        if (tiles64 >= (uint32_t)ctx->sm_count) {
+            bn = 64;
+        } else {
+            bn = tiles128 >= 16 ? 128 : 64;
+            const uint32_t tiles = bn == 128 ? tiles128 : tiles64;
+            splits = (256 + tiles - 1) / tiles;
+            if (splits > 8) splits = 8;
+            if (splits > kblocks / 8) splits = kblocks / 8 ? kblocks / 8 : 1;
         }
+    } else if (tiles128 < slots / 2) {
+        bn = tiles64 <= slots ? 64 : 128;
     }
-    if (const char* e = getenv("HOLO_GEMM_BN")) bn = atoi(e) == 64 ? 64 : 128;
+    if (const char* e = getenv("HOLO_GEMM_BN")) bn = atoi(e) == 64 ? 64 : atoi(e) == 256 ? 256 : 128;
     if (const char* e = getenv("HOLO_GEMM_SPLITS")) splits = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : 1;
     if (splits > kblocks) splits = kblocks;
     if (mtiles > 65535 || splits > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul grid too large");
 
     GemmParams p;
-    p.out = (uint16_t*)out;
+    for (uint32_t i = 0; i < MAX_SEGS; ++i) p.seg[i] = gs[i];
+    p.nseg = nseg;
     p.partial = nullptr;
-    p.residual = splits > 1 ? nullptr : (const uint16_t*)residual;
-    p.table = splits > 1 ? nullptr : table;
     p.status = ctx->dev_status;
     p.m = m; p.n = n; p.k = k; p.kblocks = kblocks; p.splits = splits;
     p.box_m = m < (uint32_t)BM ? m : (uint32_t)BM;
@@ -395,12 +469,29 @@ int32_t holo_launch_matmul(holo_b200_ctx* ctx, const void* a, const void* b, voi
     HOLO_TRY(make_map_2d(&ma, a, k, m, BK, p.box_m));
     HOLO_TRY(make_map_2d(&mb, b, n, k, 64, BK));
     dim3 grid((n + bn - 1) / bn, mtiles, splits);
-    if (bn == 128) HOLO_TRY((launch_umma<128, 3>(ctx, ma, mb, p, grid)));
-    else HOLO_TRY((launch_umma<64, 4>(ctx, ma, mb, p, grid)));
+    if (bn == 256) {
+        if (m <= 16) HOLO_TRY((launch_umma<256, 6, 16>(ctx, ma, mb, p, grid)));
+        else if (m <= 64) HOLO_TRY((launch_umma<256, 5, 64>(ctx, ma, mb, p, grid)));
+        else HOLO_TRY((launch_umma<256, 4, 128>(ctx, ma, mb, p, grid)));
+    } else if (bn == 128) {
+        if (m <= 16) HOLO_TRY((launch_umma<128, 5, 16>(ctx, ma, mb, p, grid)));
+        else if (m <= 64) HOLO_TRY((launch_umma<128, 4, 64>(ctx, ma, mb, p, grid)));
+        else HOLO_TRY((launch_umma<128, 3, 128>(ctx, ma, mb, p, grid)));
+    } else {
+        if (m <= 16) HOLO_TRY((launch_umma<64, 9, 16>(ctx, ma, mb, p, grid)));
+        else if (m <= 64) HOLO_TRY((launch_umma<64, 6, 64>(ctx, ma, mb, p, grid)));
+        else HOLO_TRY((launch_umma<64, 4, 128>(ctx, ma, mb, p, grid)));
+    }
     if (splits > 1) {
         const uint64_t mn = (uint64_t)m * n;
         const uint64_t blocks = (mn / 4 + 255) / 256 + 1;
-        splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p.partial, (uint16_t*)out, table, (const uint16_t*)residual, mn, splits);
+        ReduceParams rp;
+        for (uint32_t i = 0; i < MAX_SEGS; ++i) rp.seg[i] = gs[i];
+        rp.nseg = nseg;
+        rp.splits = splits;
+        rp.n = n;
+        rp.mn = mn;
+        splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p.partial, rp);
         HOLO_CUDA(cudaGetLastError());
         ctx->launches++;
     }

@@ -77,6 +77,54 @@ __global__ void rms_norm_kernel(const void* __restrict__ x, const void* __restri
     }
 }
 
+// 16-bit rows with feature % 8 == 0 and feature <= 8192: one pass, eight elements per thread
+// held in registers between the reduction and the scaling.
+__global__ void __launch_bounds__(1024)
+rms_norm16_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gamma, uint4* __restrict__ out,
+                      uint32_t feature, float eps, int dtype) {
+    __shared__ float s_part[32];
+    __shared__ float s_inv;
+    const uint32_t nvec = feature >> 3;
+    const uint64_t off = (uint64_t)blockIdx.x * nvec;
+    const bool active = threadIdx.x < nvec;
+    float v[8];
+    float acc = 0.0f;
+    if (active) {
+        uint4 w = x[off + threadIdx.x];
+        const uint32_t* pw = &w.x;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = holo::widen16((uint16_t)(pw[i] & 0xffffu), dtype);
+            v[2 * i + 1] = holo::widen16((uint16_t)(pw[i] >> 16), dtype);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = fmaf(v[i], v[i], acc);
+    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? s_part[threadIdx.x] : 0.0f;
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (threadIdx.x == 0) s_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)feature), eps)));
+    }
+    __syncthreads();
+    if (!active) return;
+    const float inv = s_inv;
+    uint4 g = gamma ? gamma[threadIdx.x] : make_uint4(0, 0, 0, 0);
+    const uint32_t* pg = &g.x;
+    uint4 r;
+    uint32_t* pr = &r.x;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float g0 = gamma ? holo::widen16((uint16_t)(pg[i] & 0xffffu), dtype) : 1.0f;
+        float g1 = gamma ? holo::widen16((uint16_t)(pg[i] >> 16), dtype) : 1.0f;
+        float r0 = __fmul_rn(__fmul_rn(v[2 * i], inv), g0), r1 = __fmul_rn(__fmul_rn(v[2 * i + 1], inv), g1);
+        pr[i] = (uint32_t)holo::narrow16(r0, dtype) | ((uint32_t)holo::narrow16(r1, dtype) << 16);
+    }
+    out[off + threadIdx.x] = r;
+}
+
 // rope_float, cpu/float_kernels.rs:3123-3190 (rotate-half; cos/sin share x's layout).
 __global__ void rope_kernel(const void* __restrict__ x, const void* __restrict__ c, const void* __restrict__ s,
                             void* __restrict__ out, uint32_t d, uint64_t n, int dtype) {
@@ -291,7 +339,14 @@ int32_t holo_launch_binary(holo_b200_ctx* ctx, int op, const void* a, const void
 int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* gamma, void* out, uint32_t batch,
                              uint32_t feature, float eps, uint8_t dtype) {
     if (batch == 0 || feature == 0) return HOLO_OK;
-    rms_norm_kernel<<<batch, 256, 0, ctx->stream>>>(x, gamma, out, feature, eps, dtype);
+    const bool vec = dtype != HOLO_DTYPE_F32 && (feature % 8) == 0 && feature <= 8192 &&
+                     (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)out) & 15u) == 0;
+    if (vec) {
+        uint32_t threads = ((feature / 8 + 31) / 32) * 32;
+        rms_norm16_vec_kernel<<<batch, threads, 0, ctx->stream>>>((const uint4*)x, (const uint4*)gamma, (uint4*)out, feature, eps, dtype);
+    } else {
+        rms_norm_kernel<<<batch, 256, 0, ctx->stream>>>(x, gamma, out, feature, eps, dtype);
+    }
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }

@@ -20,12 +20,31 @@
 #include "archive.h"
 #include "common.h"
 
+// A merged group of sibling matmuls: products of one A against several constant weights,
+// executed as one matmul against the column-concatenated weights with one output segment each.
+struct MergedMatmul {
+    HoloBufferRef a;
+    uint32_t m = 0, k = 0, n = 0, nseg = 0;
+    void* b_concat = nullptr;          // [k, n] bf16, owned by the session
+    HoloBufferRef out[3];
+    uint32_t width[3] = {0, 0, 0};
+    uint8_t act[3] = {0, 0, 0};
+    HoloBufferRef b_src[3];
+};
+
+struct SessionNode {
+    int merged = -1;                   // index into holo_b200_session::merged, or -1 for a plain call
+    HoloKernelCall call;
+};
+
 struct holo_b200_session {
     holo_b200_ctx* ctx = nullptr;
     holo_b200_workspace* ws = nullptr;
     HoloArchive ar;
-    std::vector<HoloKernelCall> calls;  // execution order, after fusion
-    uint32_t fused = 0, moved_in_place = 0;
+    std::vector<HoloKernelCall> calls;  // execution order, after fusion (merged groups keep their members here)
+    std::vector<SessionNode> nodes;     // what a walk actually launches
+    std::vector<MergedMatmul> merged;
+    uint32_t fused = 0, moved_in_place = 0, merged_calls = 0;
     uint64_t device_bytes = 0;
     cudaGraphExec_t graph = nullptr;
 };
@@ -106,8 +125,117 @@ uint32_t fuse_matmul_epilogue(std::vector<HoloKernelCall>& calls, const std::set
     return fused;
 }
 
+bool is_plain_or_act_matmul(const HoloKernelCall& c) { return c.kind == HOLO_K_MATMUL || c.kind == HOLO_K_MATMUL_ACTIVATION; }
+
+// Sibling-matmul merge (a device-side analogue of the reference's load-time weight-layout
+// choices, e.g. panel packing, crates/hologram-compute/src/layout.rs): consecutive MatMul /
+// MatMulActivation calls that multiply the same A by constant weights become one product
+// against the column-concatenated weights, each member keeping its own output buffer and
+// epilogue. Per-element arithmetic is unchanged (same k-order accumulation per column).
+void plan_sibling_merges(holo_b200_session* s, const std::set<uint32_t>& const_slots, const std::set<uint32_t>& written_slots) {
+    const std::vector<HoloKernelCall>& calls = s->calls;
+    size_t i = 0;
+    while (i < calls.size()) {
+        SessionNode node;
+        node.call = calls[i];
+        if (!is_plain_or_act_matmul(calls[i])) {
+            s->nodes.push_back(node);
+            ++i;
+            continue;
+        }
+        const HoloMatMulCall& first = calls[i].u.matmul;
+        auto mergeable = [&](const HoloKernelCall& c) {
+            if (!is_plain_or_act_matmul(c)) return false;
+            const HoloMatMulCall& mm = c.u.matmul;
+            return mm.dtype == HOLO_DTYPE_BF16 && !mm.b_packed && mm.a.slot == first.a.slot && mm.a.offset == first.a.offset &&
+                   mm.m == first.m && mm.k == first.k && (mm.n % 32) == 0 && (mm.k % 8) == 0 && const_slots.count(mm.b.slot) &&
+                   !written_slots.count(mm.b.slot) && mm.b.offset % 16 == 0 && (uint64_t)mm.m * mm.n * mm.k >= (1ull << 18);
+        };
+        size_t j = i;
+        MergedMatmul g;
+        while (j < calls.size() && g.nseg < 3 && mergeable(calls[j])) {
+            const HoloMatMulCall& mm = calls[j].u.matmul;
+            bool distinct = true;
+            for (uint32_t t = 0; t < g.nseg; ++t) distinct &= g.out[t].slot != mm.output.slot;
+            if (!distinct || mm.output.slot == first.a.slot) break;
+            g.out[g.nseg] = mm.output;
+            g.b_src[g.nseg] = mm.b;
+            g.width[g.nseg] = mm.n;
+            g.act[g.nseg] = calls[j].kind == HOLO_K_MATMUL_ACTIVATION ? calls[j].u.matmul_activation.act : 0;
+            g.n += mm.n;
+            ++g.nseg;
+            ++j;
+        }
+        if (g.nseg >= 2 && first.m <= 128 && !getenv("HOLO_SESSION_NO_MERGE")) {
+            g.a = first.a;
+            g.m = first.m;
+            g.k = first.k;
+            node.merged = (int)s->merged.size();
+            s->merged.push_back(g);
+            s->nodes.push_back(node);
+            s->merged_calls += g.nseg;
+            i = j;
+        } else {
+            s->nodes.push_back(node);
+            ++i;
+        }
+    }
+}
+
+int32_t build_merged_weights(holo_b200_session* s) {
+    for (MergedMatmul& g : s->merged) {
+        HOLO_CUDA(cudaMalloc(&g.b_concat, (size_t)g.k * g.n * 2));
+        s->device_bytes += (uint64_t)g.k * g.n * 2;
+        uint32_t col = 0;
+        for (uint32_t t = 0; t < g.nseg; ++t) {
+            uint8_t* src;
+            HOLO_TRY(holo_resolve(s->ws, g.b_src[t], (uint64_t)g.k * g.width[t] * 2, &src, nullptr));
+            HOLO_CUDA(cudaMemcpy2DAsync((uint8_t*)g.b_concat + (size_t)col * 2, (size_t)g.n * 2, src, (size_t)g.width[t] * 2,
+                                        (size_t)g.width[t] * 2, g.k, cudaMemcpyDeviceToDevice, s->ctx->stream));
+            col += g.width[t];
+        }
+    }
+    HOLO_CUDA(cudaStreamSynchronize(s->ctx->stream));
+    // the separate weights are no longer read by any node: give their memory back
+    std::set<uint32_t> still_used;
+    for (const SessionNode& n : s->nodes) {
+        if (n.merged >= 0) continue;
+        HoloKernelCall tmp = n.call;
+        HoloRefList refs;
+        if (holo_collect_refs(&tmp, &refs))
+            for (int r = 0; r < refs.n; ++r) still_used.insert(refs.refs[r]->slot);
+    }
+    for (const MergedMatmul& g : s->merged)
+        for (uint32_t t = 0; t < g.nseg; ++t)
+            if (!still_used.count(g.b_src[t].slot)) {
+                uint64_t nb = 0;
+                void* ptr = nullptr;
+                if (holo_b200_workspace_slot(s->ws, g.b_src[t].slot, &ptr, &nb) == HOLO_OK) s->device_bytes -= std::min<uint64_t>(s->device_bytes, nb);
+                holo_b200_workspace_bind(s->ws, g.b_src[t].slot, nullptr, 0);
+            }
+    return HOLO_OK;
+}
+
+int32_t run_merged(holo_b200_session* s, const MergedMatmul& g) {
+    uint8_t* a;
+    HOLO_TRY(holo_resolve(s->ws, g.a, (uint64_t)g.m * g.k * 2, &a, nullptr));
+    HoloMatmulSeg segs[3];
+    for (uint32_t t = 0; t < g.nseg; ++t) {
+        uint8_t* o;
+        HOLO_TRY(holo_resolve(s->ws, g.out[t], (uint64_t)g.m * g.width[t] * 2, &o, nullptr));
+        segs[t].out = o;
+        segs[t].residual = nullptr;
+        segs[t].width = g.width[t];
+        segs[t].fused_act = g.act[t];
+    }
+    return holo_launch_matmul_multi(s->ctx, a, g.b_concat, g.m, g.k, g.n, segs, g.nseg);
+}
+
 int32_t run_calls(holo_b200_session* s) {
-    for (const HoloKernelCall& c : s->calls) HOLO_TRY(holo_dispatch_internal(s->ctx, &c, s->ws));
+    for (const SessionNode& n : s->nodes) {
+        if (n.merged >= 0) HOLO_TRY(run_merged(s, s->merged[n.merged]));
+        else HOLO_TRY(holo_dispatch_internal(s->ctx, &n.call, s->ws));
+    }
     return HOLO_OK;
 }
 
@@ -135,6 +263,18 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
     for (const HoloPort& p : s->ar.inputs) in_slots.insert(p.slot);
     for (const HoloPort& p : s->ar.outputs) out_slots.insert(p.slot);
     s->fused = fuse_matmul_epilogue(s->calls, out_slots);
+    {
+        std::set<uint32_t> const_slots, written_slots;
+        for (const HoloConstant& k : s->ar.constants) const_slots.insert(k.slot);
+        for (HoloKernelCall& c : s->calls) {
+            HoloRefList refs;
+            if (holo_collect_refs(&c, &refs))
+                for (int r = 0; r < refs.n; ++r)
+                    if (refs.written[r]) written_slots.insert(refs.refs[r]->slot);
+        }
+        for (const HoloPort& p : s->ar.inputs) written_slots.insert(p.slot);   // inputs are rewritten by the caller
+        plan_sibling_merges(s, const_slots, written_slots);
+    }
 
     // slot sizing (session.rs:544-629)
     uint32_t n_slots = 0;
@@ -197,6 +337,7 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
         rc = holo_b200_workspace_upload(s->ws, ref, k.bytes, k.len);
     }
     if (rc == HOLO_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = holo_fail(HOLO_ERR_INIT, "backend init failed: constant upload");
+    if (rc == HOLO_OK) rc = build_merged_weights(s);
     if (rc != HOLO_OK) {
         if (s->ws) holo_b200_workspace_destroy(s->ws);
         delete s;
@@ -211,6 +352,8 @@ extern "C" void holo_b200_session_destroy(holo_b200_session* s) {
     cudaSetDevice(s->ctx->device);
     cudaStreamSynchronize(s->ctx->stream);
     if (s->graph) cudaGraphExecDestroy(s->graph);
+    for (MergedMatmul& g : s->merged)
+        if (g.b_concat) cudaFree(g.b_concat);
     if (s->ws) holo_b200_workspace_destroy(s->ws);
     delete s;
 }
@@ -226,6 +369,13 @@ extern "C" int32_t holo_b200_session_info(holo_b200_session* s, uint32_t* n_call
     if (n_inputs) *n_inputs = (uint32_t)s->ar.inputs.size();
     if (n_outputs) *n_outputs = (uint32_t)s->ar.outputs.size();
     if (device_bytes) *device_bytes = s->device_bytes;
+    return HOLO_OK;
+}
+
+extern "C" int32_t holo_b200_session_nodes(holo_b200_session* s, uint32_t* n_nodes, uint32_t* n_merged_calls) {
+    if (!s) return holo_fail(HOLO_ERR_INIT, "null session");
+    if (n_nodes) *n_nodes = (uint32_t)s->nodes.size();
+    if (n_merged_calls) *n_merged_calls = s->merged_calls;
     return HOLO_OK;
 }
 
@@ -259,7 +409,7 @@ extern "C" int32_t holo_b200_session_execute(holo_b200_session* s) {
     HOLO_CUDA(cudaSetDevice(s->ctx->device));
     if (s->graph) {
         HOLO_CUDA(cudaGraphLaunch(s->graph, s->ctx->stream));
-        s->ctx->launches += s->calls.size();
+        s->ctx->launches += s->nodes.size();
         return HOLO_OK;
     }
     return run_calls(s);

@@ -13,6 +13,7 @@ for _name, _res, _args in [
     ("holo_b200_session_destroy", None, [vp]),
     ("holo_b200_session_workspace", vp, [vp]),
     ("holo_b200_session_info", i32, [vp] + [C.POINTER(u32)] * 5 + [C.POINTER(u64)]),
+    ("holo_b200_session_nodes", i32, [vp, C.POINTER(u32), C.POINTER(u32)]),
     ("holo_b200_session_port", i32, [vp, i32, u32, C.c_char_p, u32, C.POINTER(u32), C.POINTER(u64), C.POINTER(C.c_uint8)]),
     ("holo_b200_session_call", i32, [vp, u32, C.POINTER(kc.KernelCall)]),
     ("holo_b200_session_execute", i32, [vp]),
@@ -23,7 +24,7 @@ for _name, _res, _args in [
     _fn.restype, _fn.argtypes = _res, _args
 
 SESSION_SYMBOLS = ["holo_b200_session_load", "holo_b200_session_destroy", "holo_b200_session_workspace",
-                   "holo_b200_session_info", "holo_b200_session_port", "holo_b200_session_call",
+                   "holo_b200_session_info", "holo_b200_session_nodes", "holo_b200_session_port", "holo_b200_session_call",
                    "holo_b200_session_execute", "holo_b200_session_capture", "holo_b200_archive_check"]
 
 
@@ -61,6 +62,9 @@ class InferenceSession:
         _check(lib.holo_b200_session_info(h, *[C.byref(v) for v in vals], C.byref(dev)))
         self.n_calls, self.fused_count, self.moved_in_place, n_in, n_out = (v.value for v in vals)
         self.device_bytes = dev.value
+        nn, nm = u32(), u32()
+        _check(lib.holo_b200_session_nodes(h, C.byref(nn), C.byref(nm)))
+        self.n_nodes, self.merged_calls = nn.value, nm.value
         self.inputs = [self._port(0, i) for i in range(n_in)]
         self.outputs = [self._port(1, i) for i in range(n_out)]
         self._by_name = {p.name: p for p in self.inputs + self.outputs}

@@ -337,6 +337,11 @@ holo_b200_workspace* holo_b200_session_workspace(holo_b200_session* s);
  * KV moves, port counts, bytes of HBM held by slots. Any pointer may be NULL. */
 int32_t holo_b200_session_info(holo_b200_session* s, uint32_t* n_calls, uint32_t* n_fused, uint32_t* n_moved,
                                uint32_t* n_inputs, uint32_t* n_outputs, uint64_t* device_bytes);
+/* What one walk launches: the number of launch nodes, and how many calls were absorbed into
+ * merged sibling matmuls (consecutive MatMul / MatMulActivation calls over the same A and
+ * constant weights run as one product against column-concatenated weights, each call keeping
+ * its own output buffer and epilogue). */
+int32_t holo_b200_session_nodes(holo_b200_session* s, uint32_t* n_nodes, uint32_t* n_merged_calls);
 /* Port `index` of the Inputs (is_output == 0) or Outputs section (writer.rs:246-263). */
 int32_t holo_b200_session_port(holo_b200_session* s, int32_t is_output, uint32_t index, char* name, uint32_t name_cap,
                                uint32_t* slot, uint64_t* element_count, uint8_t* dtype);
