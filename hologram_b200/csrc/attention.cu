@@ -30,10 +30,10 @@ namespace {
 constexpr int TK = 128;           // keys per tile
 constexpr int HD = 128;           // head_dim served by the tiled kernel
 #ifndef HOLO_ATTN_STAGES
-#define HOLO_ATTN_STAGES 2
+#define HOLO_ATTN_STAGES 3
 #endif
 #ifndef HOLO_ATTN_MINB
-#define HOLO_ATTN_MINB 3
+#define HOLO_ATTN_MINB 2
 #endif
 constexpr int STAGES = HOLO_ATTN_STAGES;
 constexpr int CONSUMER_WARPS = 4;

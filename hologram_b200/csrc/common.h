@@ -14,6 +14,16 @@ struct HoloSlot {
     bool owned = false;
 };
 
+// One small op of a batched launch (see micro_batch_kernel).
+enum { HOLO_MICRO_KV_WRITE = 0, HOLO_MICRO_ROPE, HOLO_MICRO_QUANT_VEC, HOLO_MICRO_QUANT, HOLO_MICRO_BINARY_VEC, HOLO_MICRO_BINARY };
+struct HoloMicroOp {
+    uint32_t kind, cta_begin, cta_count, dtype;
+    const void *p0, *p1, *p2;
+    void *o0, *o1;
+    uint64_t n;
+    uint32_t a, b, c, d;
+};
+
 struct holo_b200_ctx {
     int device = 0;
     int sm_count = 0;
@@ -30,6 +40,9 @@ struct holo_b200_ctx {
     uint64_t stage_bytes = 0;
     // device-side error word (bounded waits record where they gave up)
     uint32_t* dev_status = nullptr;
+    // set by a session while it records a batch: launchers append here instead of launching
+    std::vector<HoloMicroOp>* record = nullptr;
+    bool record_failed = false;
     // tensor-parallel group
     void* nccl_comm = nullptr;
     int tp_rank = 0, tp_world = 1;
@@ -116,6 +129,7 @@ int32_t holo_launch_kv_write(holo_b200_ctx* ctx, const uint8_t* cache, const uin
                              uint8_t* out, uint32_t planes, uint32_t bucket, uint32_t new_rows, uint32_t row_bytes);
 int32_t holo_launch_quantize_rows(holo_b200_ctx* ctx, const void* x, uint8_t dtype, uint64_t rows, uint32_t d,
                                   int8_t* codes, float* scales);
+int32_t holo_launch_micro_batch(holo_b200_ctx* ctx, const HoloMicroOp* dev_ops, uint32_t nops, uint32_t total_ctas);
 // attention.cu
 struct HoloAttnArgs {
     const void* q;

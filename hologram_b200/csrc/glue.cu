@@ -18,20 +18,25 @@ inline unsigned ew_blocks(uint64_t n, int per_thread = 1) {
 }
 
 // binary_float_acc, cpu/float_kernels.rs:252-296: widen, op, narrow.
-__global__ void binary_kernel(int op, const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ out,
-                              uint64_t n, int dtype) {
-    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+__device__ __forceinline__ void binary_body(int op, const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ out,
+                                            uint64_t n, int dtype, uint32_t block, uint32_t nblocks) {
+    uint64_t stride = (uint64_t)nblocks * blockDim.x;
+    for (uint64_t i = (uint64_t)block * blockDim.x + threadIdx.x; i < n; i += stride) {
         float va = holo::load_float(a, i, dtype), vb = holo::load_float(b, i, dtype);
         holo::store_float(out, i, op == 0 ? __fadd_rn(va, vb) : __fmul_rn(va, vb), dtype);
     }
 }
 
+__global__ void binary_kernel(int op, const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ out,
+                              uint64_t n, int dtype) {
+    binary_body(op, a, b, out, n, dtype, blockIdx.x, gridDim.x);
+}
+
 // 16-bit fast path: eight elements per thread through 128-bit loads and stores.
-__global__ void binary16_vec_kernel(int op, const uint4* __restrict__ a, const uint4* __restrict__ b,
-                                    uint4* __restrict__ out, uint64_t nvec, int dtype) {
-    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+__device__ __forceinline__ void binary16_vec_body(int op, const uint4* __restrict__ a, const uint4* __restrict__ b,
+                                                  uint4* __restrict__ out, uint64_t nvec, int dtype, uint32_t block, uint32_t nblocks) {
+    uint64_t stride = (uint64_t)nblocks * blockDim.x;
+    for (uint64_t i = (uint64_t)block * blockDim.x + threadIdx.x; i < nvec; i += stride) {
         uint4 va = a[i], vb = b[i], r;
         const uint32_t* pa = &va.x;
         const uint32_t* pb = &vb.x;
@@ -46,6 +51,10 @@ __global__ void binary16_vec_kernel(int op, const uint4* __restrict__ a, const u
         }
         out[i] = r;
     }
+}
+__global__ void binary16_vec_kernel(int op, const uint4* __restrict__ a, const uint4* __restrict__ b,
+                                    uint4* __restrict__ out, uint64_t nvec, int dtype) {
+    binary16_vec_body(op, a, b, out, nvec, dtype, blockIdx.x, gridDim.x);
 }
 
 // rms_norm_float, cpu/float_kernels.rs:1683-1756: inv = 1/sqrt(sumsq/f + eps),
@@ -126,11 +135,11 @@ rms_norm16_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gam
 }
 
 // rope_float, cpu/float_kernels.rs:3123-3190 (rotate-half; cos/sin share x's layout).
-__global__ void rope_kernel(const void* __restrict__ x, const void* __restrict__ c, const void* __restrict__ s,
-                            void* __restrict__ out, uint32_t d, uint64_t n, int dtype) {
+__device__ __forceinline__ void rope_body(const void* __restrict__ x, const void* __restrict__ c, const void* __restrict__ s,
+                                          void* __restrict__ out, uint32_t d, uint64_t n, int dtype, uint32_t block, uint32_t nblocks) {
     const uint32_t half = d >> 1;
-    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
+    uint64_t stride = (uint64_t)nblocks * blockDim.x;
+    for (uint64_t e = (uint64_t)block * blockDim.x + threadIdx.x; e < n; e += stride) {
         uint32_t pos = (uint32_t)(e % d);
         uint64_t base = e - pos;
         float xe = holo::load_float(x, e, dtype), ce = holo::load_float(c, e, dtype), se = holo::load_float(s, e, dtype);
@@ -139,6 +148,10 @@ __global__ void rope_kernel(const void* __restrict__ x, const void* __restrict__
         else v = __fadd_rn(__fmul_rn(xe, ce), __fmul_rn(holo::load_float(x, base + pos - half, dtype), se));
         holo::store_float(out, e, v, dtype);
     }
+}
+__global__ void rope_kernel(const void* __restrict__ x, const void* __restrict__ c, const void* __restrict__ s,
+                            void* __restrict__ out, uint32_t d, uint64_t n, int dtype) {
+    rope_body(x, c, s, out, d, n, dtype, blockIdx.x, gridDim.x);
 }
 
 // gather, cpu/kernels.rs:389-446: out[o,k,:] = data[o, idx[k], :]; negative indices wrap;
@@ -236,12 +249,29 @@ __global__ void kv_write_rows_kernel(const uint8_t* __restrict__ newr, const uin
     }
 }
 
+// Same row copy with one warp per (plane, new row) pair, for the batched launch.
+__device__ __forceinline__ void kv_write_rows_body(const uint8_t* __restrict__ newr, const uint32_t* __restrict__ pos,
+                                                   uint8_t* __restrict__ out, uint32_t planes, uint32_t bucket, uint32_t new_rows,
+                                                   uint32_t row_bytes, uint32_t block) {
+    const uint64_t item = (uint64_t)block * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (uint64_t)planes * new_rows) return;
+    const uint32_t p = (uint32_t)(item / new_rows), j = (uint32_t)(item % new_rows), lane = threadIdx.x & 31;
+    const uint32_t p0 = *pos % bucket;
+    const uint8_t* src = newr + ((uint64_t)p * new_rows + j) * row_bytes;
+    uint8_t* dst = out + ((uint64_t)p * bucket + (p0 + j) % bucket) * row_bytes;
+    if ((((uintptr_t)src | (uintptr_t)dst | row_bytes) & 15u) == 0) {
+        for (uint32_t i = lane; i < row_bytes / 16; i += 32) ((uint4*)dst)[i] = ((const uint4*)src)[i];
+    } else {
+        for (uint32_t i = lane; i < row_bytes; i += 32) dst[i] = src[i];
+    }
+}
+
 // quantize_row_i8 per row, cpu/simd.rs:4761-4785. One warp per row: max|a| by shuffles
 // (max is exact in any order), inv = 127/amax, t = a*inv, r = trunc(t ± 0.5) (saturating
 // cvt.rzi, NaN -> 0), clamp to ±127, scale = amax/127. A zero row gives zero codes, scale 0.
-__global__ void quantize_rows_kernel(const void* __restrict__ x, int dtype, uint64_t rows, uint32_t d,
-                                     int8_t* __restrict__ codes, float* __restrict__ scales) {
-    const uint64_t row = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+__device__ __forceinline__ void quantize_rows_body(const void* __restrict__ x, int dtype, uint64_t rows, uint32_t d,
+                                                   int8_t* __restrict__ codes, float* __restrict__ scales, uint32_t block) {
+    const uint64_t row = (uint64_t)block * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const uint32_t lane = threadIdx.x & 31;
     const uint64_t off = row * d;
@@ -269,12 +299,16 @@ __global__ void quantize_rows_kernel(const void* __restrict__ x, int dtype, uint
     }
     if (lane == 0) scales[row] = __fdiv_rn(amax, 127.0f);
 }
+__global__ void quantize_rows_kernel(const void* __restrict__ x, int dtype, uint64_t rows, uint32_t d,
+                                     int8_t* __restrict__ codes, float* __restrict__ scales) {
+    quantize_rows_body(x, dtype, rows, d, codes, scales, blockIdx.x);
+}
 
 // d % 128 == 0, 16-bit input, 8-byte aligned rows: each lane owns 4 consecutive elements
 // of every 128-element segment (one 64-bit load, one 32-bit store).
-__global__ void quantize_rows16_vec_kernel(const uint16_t* __restrict__ x, int dtype, uint64_t rows, uint32_t d,
-                                           int8_t* __restrict__ codes, float* __restrict__ scales) {
-    const uint64_t row = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+__device__ __forceinline__ void quantize_rows16_vec_body(const uint16_t* __restrict__ x, int dtype, uint64_t rows, uint32_t d,
+                                                         int8_t* __restrict__ codes, float* __restrict__ scales, uint32_t block) {
+    const uint64_t row = (uint64_t)block * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const uint32_t lane = threadIdx.x & 31;
     const uint64_t off = row * d;
@@ -314,8 +348,64 @@ __global__ void quantize_rows16_vec_kernel(const uint16_t* __restrict__ x, int d
     }
     if (lane == 0) scales[row] = zero ? 0.0f : __fdiv_rn(amax, 127.0f);
 }
+__global__ void quantize_rows16_vec_kernel(const uint16_t* __restrict__ x, int dtype, uint64_t rows, uint32_t d,
+                                           int8_t* __restrict__ codes, float* __restrict__ scales) {
+    quantize_rows16_vec_body(x, dtype, rows, d, codes, scales, blockIdx.x);
+}
+
+// Several independent small ops in one launch: each CTA looks up the op that owns its block
+// index and runs that op's body with a block index local to the op. Used by the session for
+// runs of mutually independent glue calls (the trailing KV appends of all layers, the RoPE
+// pair, the K/V quantizer pair), whose individual launches cost more than their work.
+__global__ void __launch_bounds__(256) micro_batch_kernel(const HoloMicroOp* __restrict__ ops, uint32_t nops) {
+    uint32_t oi = 0;
+    while (oi + 1 < nops && blockIdx.x >= ops[oi].cta_begin + ops[oi].cta_count) ++oi;
+    const HoloMicroOp op = ops[oi];
+    const uint32_t block = blockIdx.x - op.cta_begin;
+    switch (op.kind) {
+        case HOLO_MICRO_KV_WRITE:
+            kv_write_rows_body((const uint8_t*)op.p0, (const uint32_t*)op.p1, (uint8_t*)op.o0, op.a, op.b, op.c, op.d, block);
+            break;
+        case HOLO_MICRO_ROPE:
+            rope_body(op.p0, op.p1, op.p2, op.o0, op.a, op.n, (int)op.dtype, block, op.cta_count);
+            break;
+        case HOLO_MICRO_QUANT_VEC:
+            quantize_rows16_vec_body((const uint16_t*)op.p0, (int)op.dtype, op.n, op.a, (int8_t*)op.o0, (float*)op.o1, block);
+            break;
+        case HOLO_MICRO_QUANT:
+            quantize_rows_body(op.p0, (int)op.dtype, op.n, op.a, (int8_t*)op.o0, (float*)op.o1, block);
+            break;
+        case HOLO_MICRO_BINARY_VEC:
+            binary16_vec_body((int)op.a, (const uint4*)op.p0, (const uint4*)op.p1, (uint4*)op.o0, op.n, (int)op.dtype, block, op.cta_count);
+            break;
+        default:
+            binary_body((int)op.a, op.p0, op.p1, op.o0, op.n, (int)op.dtype, block, op.cta_count);
+            break;
+    }
+}
 
 }  // namespace
+
+int32_t holo_launch_micro_batch(holo_b200_ctx* ctx, const HoloMicroOp* dev_ops, uint32_t nops, uint32_t total_ctas) {
+    if (nops == 0 || total_ctas == 0) return HOLO_OK;
+    micro_batch_kernel<<<total_ctas, 256, 0, ctx->stream>>>(dev_ops, nops);
+    HOLO_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return HOLO_OK;
+}
+
+// While a session records a batch, launchers append a descriptor instead of launching.
+static bool record_op(holo_b200_ctx* ctx, HoloMicroOp op, uint64_t ctas) {
+    if (!ctx->record) return false;
+    if (ctas == 0 || ctas > 0x7fffffffull) {
+        ctx->record_failed = true;
+        return true;
+    }
+    op.cta_begin = 0;
+    op.cta_count = (uint32_t)ctas;
+    ctx->record->push_back(op);
+    return true;
+}
 
 #define LAUNCH_CHECK(ctx)                 \
     do {                                  \
@@ -326,6 +416,14 @@ __global__ void quantize_rows16_vec_kernel(const uint16_t* __restrict__ x, int d
 int32_t holo_launch_binary(holo_b200_ctx* ctx, int op, const void* a, const void* b, void* out, uint64_t n, uint8_t dtype) {
     if (n == 0) return HOLO_OK;
     const bool aligned = (((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15u) == 0;
+    if (ctx->record) {
+        HoloMicroOp m = {};
+        const bool vec = dtype != HOLO_DTYPE_F32 && aligned && (n % 8) == 0;
+        m.kind = vec ? HOLO_MICRO_BINARY_VEC : HOLO_MICRO_BINARY;
+        m.p0 = a; m.p1 = b; m.o0 = out; m.a = (uint32_t)op; m.dtype = dtype; m.n = vec ? n / 8 : n;
+        record_op(ctx, m, ew_blocks(m.n));
+        return HOLO_OK;
+    }
     if (dtype != HOLO_DTYPE_F32 && aligned && (n % 8) == 0) {
         binary16_vec_kernel<<<ew_blocks(n / 8), EW_THREADS, 0, ctx->stream>>>(op, (const uint4*)a, (const uint4*)b,
                                                                              (uint4*)out, n / 8, dtype);
@@ -354,6 +452,13 @@ int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* gamm
 int32_t holo_launch_rope(holo_b200_ctx* ctx, const void* x, const void* c, const void* s, void* out, uint32_t head_dim,
                          uint64_t n, uint8_t dtype) {
     if (n == 0) return HOLO_OK;
+    if (ctx->record) {
+        HoloMicroOp m = {};
+        m.kind = HOLO_MICRO_ROPE;
+        m.p0 = x; m.p1 = c; m.p2 = s; m.o0 = out; m.a = head_dim; m.n = n; m.dtype = dtype;
+        record_op(ctx, m, ew_blocks(n));
+        return HOLO_OK;
+    }
     rope_kernel<<<ew_blocks(n), EW_THREADS, 0, ctx->stream>>>(x, c, s, out, head_dim, n, dtype);
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
@@ -392,6 +497,17 @@ int32_t holo_launch_dequantize(holo_b200_ctx* ctx, const HoloDequantizeCall& c, 
 int32_t holo_launch_kv_write(holo_b200_ctx* ctx, const uint8_t* cache, const uint8_t* newr, const uint32_t* pos,
                              uint8_t* out, uint32_t planes, uint32_t bucket, uint32_t new_rows, uint32_t row_bytes) {
     if (planes == 0) return HOLO_OK;
+    if (ctx->record) {
+        if (out != cache || new_rows == 0) {   // only the in-place form is a pure row scatter
+            ctx->record_failed = true;
+            return HOLO_OK;
+        }
+        HoloMicroOp m = {};
+        m.kind = HOLO_MICRO_KV_WRITE;
+        m.p0 = newr; m.p1 = pos; m.o0 = out; m.a = planes; m.b = bucket; m.c = new_rows; m.d = row_bytes;
+        record_op(ctx, m, ((uint64_t)planes * new_rows + 7) / 8);
+        return HOLO_OK;
+    }
     if (out != cache)
         HOLO_CUDA(cudaMemcpyAsync(out, cache, (size_t)planes * bucket * row_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     if (new_rows == 0) return HOLO_OK;
@@ -409,6 +525,13 @@ int32_t holo_launch_quantize_rows(holo_b200_ctx* ctx, const void* x, uint8_t dty
     uint64_t blocks = (rows + warps - 1) / warps;
     if (blocks > 0x7fffffffull) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "quantize_rows_i8: too many rows");
     const bool vec = dtype != HOLO_DTYPE_F32 && (d % 128) == 0 && (((uintptr_t)x & 7u) == 0) && (((uintptr_t)codes & 3u) == 0);
+    if (ctx->record) {
+        HoloMicroOp m = {};
+        m.kind = vec ? HOLO_MICRO_QUANT_VEC : HOLO_MICRO_QUANT;
+        m.p0 = x; m.o0 = codes; m.o1 = scales; m.a = d; m.n = rows; m.dtype = dtype;
+        record_op(ctx, m, blocks);
+        return HOLO_OK;
+    }
     if (vec)
         quantize_rows16_vec_kernel<<<(unsigned)blocks, warps * 32, 0, ctx->stream>>>((const uint16_t*)x, dtype, rows, d, codes, scales);
     else

@@ -32,9 +32,16 @@ struct MergedMatmul {
     HoloBufferRef b_src[3];
 };
 
+// A run of mutually independent small glue calls executed as one launch.
+struct MicroBatch {
+    HoloMicroOp* dev_ops = nullptr;    // owned by the session
+    uint32_t nops = 0, total_ctas = 0, ncalls = 0;
+};
+
 struct SessionNode {
-    int merged = -1;                   // index into holo_b200_session::merged, or -1 for a plain call
-    HoloKernelCall call;
+    int merged = -1;                   // index into holo_b200_session::merged, or -1
+    int batch = -1;                    // index into holo_b200_session::batches, or -1
+    HoloKernelCall call;               // the plain call when both are -1
 };
 
 struct holo_b200_session {
@@ -44,7 +51,8 @@ struct holo_b200_session {
     std::vector<HoloKernelCall> calls;  // execution order, after fusion (merged groups keep their members here)
     std::vector<SessionNode> nodes;     // what a walk actually launches
     std::vector<MergedMatmul> merged;
-    uint32_t fused = 0, moved_in_place = 0, merged_calls = 0;
+    std::vector<MicroBatch> batches;
+    uint32_t fused = 0, moved_in_place = 0, merged_calls = 0, batched_calls = 0;
     uint64_t device_bytes = 0;
     cudaGraphExec_t graph = nullptr;
 };
@@ -231,9 +239,103 @@ int32_t run_merged(holo_b200_session* s, const MergedMatmul& g) {
     return holo_launch_matmul_multi(s->ctx, a, g.b_concat, g.m, g.k, g.n, segs, g.nseg);
 }
 
+bool batchable_kind(uint16_t k) {
+    return k == HOLO_K_KV_CACHE_WRITE || k == HOLO_K_ROTARY || k == HOLO_K_QUANTIZE_ROWS_I8 || k == HOLO_K_ADD || k == HOLO_K_MUL;
+}
+
+// Group consecutive, mutually independent small glue calls (no member reads or writes a slot
+// another member writes) into single launches. Each member is first dispatched in recording
+// mode, which runs its full validation and slot resolution but appends a descriptor instead
+// of launching; slots never move after load, so the descriptors stay valid for every walk.
+int32_t plan_micro_batches(holo_b200_session* s) {
+    if (getenv("HOLO_SESSION_NO_BATCH")) return HOLO_OK;
+    std::vector<SessionNode> out;
+    size_t i = 0;
+    while (i < s->nodes.size()) {
+        const SessionNode& n0 = s->nodes[i];
+        if (n0.merged >= 0 || !batchable_kind(n0.call.kind)) {
+            out.push_back(n0);
+            ++i;
+            continue;
+        }
+        std::set<uint32_t> reads, writes;
+        size_t j = i;
+        while (j < s->nodes.size() && j - i < 64) {
+            const SessionNode& nj = s->nodes[j];
+            if (nj.merged >= 0 || !batchable_kind(nj.call.kind)) break;
+            HoloKernelCall tmp = nj.call;
+            HoloRefList refs;
+            if (!holo_collect_refs(&tmp, &refs)) break;
+            bool ok = true;
+            for (int r = 0; r < refs.n && ok; ++r) {
+                const uint32_t slot = refs.refs[r]->slot;
+                if (slot == HOLO_NO_SLOT) continue;
+                // aliased slots (the in-place KV move) share memory: compare device pointers
+                void* ptr = nullptr;
+                uint64_t nb = 0;
+                if (holo_b200_workspace_slot(s->ws, slot, &ptr, &nb) != HOLO_OK) { ok = false; break; }
+                const uint32_t key = (uint32_t)((uintptr_t)ptr >> 6);
+                if (refs.written[r]) ok = !reads.count(key) && !writes.count(key);
+                else ok = !writes.count(key);
+            }
+            if (!ok) break;
+            for (int r = 0; r < refs.n; ++r) {
+                const uint32_t slot = refs.refs[r]->slot;
+                if (slot == HOLO_NO_SLOT) continue;
+                void* ptr = nullptr;
+                uint64_t nb = 0;
+                holo_b200_workspace_slot(s->ws, slot, &ptr, &nb);
+                const uint32_t key = (uint32_t)((uintptr_t)ptr >> 6);
+                // a KvCacheWrite reads its cache only to carry it over: in place that is no access
+                if (nj.call.kind == HOLO_K_KV_CACHE_WRITE && refs.refs[r] == &tmp.u.kv_cache_write.cache) continue;
+                (refs.written[r] ? writes : reads).insert(key);
+            }
+            ++j;
+        }
+        if (j - i < 2) {
+            out.push_back(n0);
+            ++i;
+            continue;
+        }
+        std::vector<HoloMicroOp> ops;
+        s->ctx->record = &ops;
+        s->ctx->record_failed = false;
+        int32_t rc = HOLO_OK;
+        for (size_t t = i; t < j && rc == HOLO_OK; ++t) rc = holo_dispatch_internal(s->ctx, &s->nodes[t].call, s->ws);
+        s->ctx->record = nullptr;
+        if (rc != HOLO_OK) return rc;
+        if (s->ctx->record_failed || ops.size() != j - i) {   // something in the run cannot be batched: keep the calls
+            for (size_t t = i; t < j; ++t) out.push_back(s->nodes[t]);
+            i = j;
+            continue;
+        }
+        MicroBatch b;
+        uint32_t cta = 0;
+        for (HoloMicroOp& op : ops) {
+            op.cta_begin = cta;
+            cta += op.cta_count;
+        }
+        b.nops = (uint32_t)ops.size();
+        b.total_ctas = cta;
+        b.ncalls = (uint32_t)(j - i);
+        HOLO_CUDA(cudaMalloc(&b.dev_ops, ops.size() * sizeof(HoloMicroOp)));
+        HOLO_CUDA(cudaMemcpy(b.dev_ops, ops.data(), ops.size() * sizeof(HoloMicroOp), cudaMemcpyHostToDevice));
+        SessionNode node;
+        node.batch = (int)s->batches.size();
+        node.call = n0.call;
+        s->batches.push_back(b);
+        s->batched_calls += b.ncalls;
+        out.push_back(node);
+        i = j;
+    }
+    s->nodes.swap(out);
+    return HOLO_OK;
+}
+
 int32_t run_calls(holo_b200_session* s) {
     for (const SessionNode& n : s->nodes) {
         if (n.merged >= 0) HOLO_TRY(run_merged(s, s->merged[n.merged]));
+        else if (n.batch >= 0) HOLO_TRY(holo_launch_micro_batch(s->ctx, s->batches[n.batch].dev_ops, s->batches[n.batch].nops, s->batches[n.batch].total_ctas));
         else HOLO_TRY(holo_dispatch_internal(s->ctx, &n.call, s->ws));
     }
     return HOLO_OK;
@@ -338,6 +440,7 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
     }
     if (rc == HOLO_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = holo_fail(HOLO_ERR_INIT, "backend init failed: constant upload");
     if (rc == HOLO_OK) rc = build_merged_weights(s);
+    if (rc == HOLO_OK) rc = plan_micro_batches(s);
     if (rc != HOLO_OK) {
         if (s->ws) holo_b200_workspace_destroy(s->ws);
         delete s;
@@ -354,6 +457,8 @@ extern "C" void holo_b200_session_destroy(holo_b200_session* s) {
     if (s->graph) cudaGraphExecDestroy(s->graph);
     for (MergedMatmul& g : s->merged)
         if (g.b_concat) cudaFree(g.b_concat);
+    for (MicroBatch& b : s->batches)
+        if (b.dev_ops) cudaFree(b.dev_ops);
     if (s->ws) holo_b200_workspace_destroy(s->ws);
     delete s;
 }
@@ -375,7 +480,7 @@ extern "C" int32_t holo_b200_session_info(holo_b200_session* s, uint32_t* n_call
 extern "C" int32_t holo_b200_session_nodes(holo_b200_session* s, uint32_t* n_nodes, uint32_t* n_merged_calls) {
     if (!s) return holo_fail(HOLO_ERR_INIT, "null session");
     if (n_nodes) *n_nodes = (uint32_t)s->nodes.size();
-    if (n_merged_calls) *n_merged_calls = s->merged_calls;
+    if (n_merged_calls) *n_merged_calls = s->merged_calls + s->batched_calls;
     return HOLO_OK;
 }
 
