@@ -128,7 +128,8 @@ def workload_lut(be, torch, rank, args):
         "ref_step": ref_step, "ref_fraction": 1.0,
         "units_per_step": n * 4 / 1e9,  # GB of algorithmic traffic per step
         "launches_per_step": 1,
-        "roofline": {"bound": "hbm", "bytes_per_launch": n * 4},
+        "roofline": {"bound": "hbm", "bytes_per_launch": n * 4, "kernel": "lut_stream_kernel",
+                     "traffic": 34_255_360, "traffic_note": "ncu, profiles/lut_stream_kernel_gelu_bf16_16Mi.md: 33.69 MB read + 0.56 MB written inside the kernel window (the output is still dirty in L2)"},
         "h2d": n * 2, "d2h": n * 2,
         "cpu_baseline": cpu_baseline,
         "config": {"workload": "config[0]: bf16 GELU via the 65536-entry u16 LUT, 16,777,216 elements, 99% N(0,9) + 1% specials",
@@ -202,7 +203,8 @@ def workload_attention(be, torch, rank, args, world=1):
         "ref_step": ref_step, "ref_fraction": 2 / b,
         "units_per_step": algo / 1e9,
         "launches_per_step": 2,
-        "roofline": {"bound": "hbm", "bytes_per_launch": algo},
+        "roofline": {"bound": "hbm", "bytes_per_launch": algo, "kernel": "decode_attention_q8_kernel",
+                     "traffic": 560_797_696 // world, "traffic_note": "ncu at N=1, profiles/decode_attention_q8_kernel_b32_h32_kv8_L8192.md: 554.05 MB read + 6.75 MB written"},
         "h2d": sum(t.numel() * t.element_size() for t in tensors[:-1]), "d2h": out.numel() * 2,
         "cpu_baseline": cpu_baseline,
         "config": {"workload": f"config[3]: single-token decode attention, batch {b}, {h} q / {kv} kv heads, head_dim {d}, {past} cached positions, int8 KV",
@@ -280,6 +282,13 @@ def workload_decoder(be, torch, rank, args, world=1):
         sess.execute()
         _check(lib.holo_b200_workspace_download(sess.workspace._h, kc.rb(sess.port("logits").slot), ctypes.c_void_p(logits_host.data_ptr()), B * info["vocab"] * 2))
 
+    # the dominant kernel of the step (44 % of the ncu launch list): one layer's int8-KV attention
+    attn_calls = [sess.call(i) for i in range(sess.n_calls) if sess.call(i).kind == kc.K_DECODE_ATTENTION_VALID_Q8]
+    attn_bytes = 2 * rows * (hd + 4) + 2 * B * H * hd * 2 + 2 * B * KV * (hd + 4)
+
+    def run_dominant(step):
+        be.dispatch(attn_calls[step % len(attn_calls)], sess.workspace)
+
     weight_bytes = sum(len(b) for s_, (dt, b) in info["constants"].items()) - cfg.vocab * cfg.d_model * 2 + B * cfg.d_model * 2
     kv_bytes = cfg.n_layers * 2 * rows * (hd + 4)
     algo = weight_bytes + kv_bytes
@@ -294,7 +303,11 @@ def workload_decoder(be, torch, rank, args, world=1):
         "run_host": run_host,
         "units_per_step": B / world,   # the batch is replicated over the TP group: count it once
         "launches_per_step": sess.n_calls,
-        "roofline": {"bound": "hbm", "bytes_per_launch": algo},
+        "roofline": {"bound": "hbm", "bytes_per_launch": attn_bytes, "kernel": "decode_attention_q8_kernel (+ combine), one layer",
+                     "run": run_dominant, "traffic": (560_797_696 // world) if (B, L) == (64, 4096) else None,
+                     "traffic_note": "ncu capture of the same kernel on the same number of key rows (config[3]: 32 x 8 x 8192 = 64 x 8 x 4096 rows), "
+                                     "profiles/decode_attention_q8_kernel_b32_h32_kv8_L8192.md",
+                     "step_bytes": algo},
         "h2d": sum(v.numel() for v in pinned.values()), "d2h": B * info["vocab"] * 2,
         "cpu_baseline": cpu_baseline,
         "config": {"workload": f"config[4]: {cfg.n_layers}-layer Llama-style decoder .holo, d_model {cfg.d_model}, {cfg.n_heads} q / {cfg.n_kv_heads} kv heads, "
@@ -302,7 +315,7 @@ def workload_decoder(be, torch, rank, args, world=1):
                    "l2": "per-step working set (weights + KV, >= 1 GB per GPU) exceeds the 126 MB L2",
                    "cuda_graph": use_graph, "calls_per_step": sess.n_calls, "fused_pairs": sess.fused_count,
                    "archive_bytes": nbytes_img, "build_s": round(t1 - t0, 1), "load_s": round(t2 - t1, 1),
-                   "roofline_note": "roofline is for the whole step: algorithmic bytes = per-GPU matmul weights + KV codes and scales read once"},
+                   "roofline_note": "roofline = the dominant kernel (one layer's attention) timed alone with CUDA events after the step loop; step_roofline = the whole step"},
         "keep": (sess, pinned, logits_host, scratch),
     }
 
@@ -406,7 +419,10 @@ def workload_matmul(be, torch, rank, args, skinny=False):
         "run_host": lambda step: be.dispatch(hcall, hws),
         "units_per_step": nbytes / 1e9 if skinny else flops / 1e12,
         "launches_per_step": 1,
-        "roofline": {"bound": "hbm", "bytes_per_launch": nbytes} if skinny else {"bound": "tensor", "flops_per_launch": flops},
+        "roofline": ({"bound": "hbm", "bytes_per_launch": nbytes, "kernel": "matmul_bf16_umma_kernel", "traffic": None} if skinny else
+                     {"bound": "tensor", "flops_per_launch": flops, "kernel": "matmul_bf16_umma_kernel",
+                      "traffic": 82_481_152 if (m, k, n) == (4096, 4096, 4096) else None,
+                      "traffic_note": "ncu, profiles/matmul_bf16_umma_kernel.md: 67.35 MB read + 15.13 MB written inside the kernel window"}),
         "h2d": 2 * (m * k + k * n), "d2h": 2 * m * n,
         "cpu_baseline": cpu_baseline,
         "config": {"workload": f"config[2]: bf16 matmul M={m} K={k} N={n}, f32 accumulation, bf16 output, A,B ~ N(0, 1/K)",
@@ -487,6 +503,11 @@ def main():
         sampler.start()
     ms, launches = timed(wl["run_device"], args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
+    dom_ms = None
+    if "run" in wl["roofline"]:
+        dom_steps = 24
+        dom_total, _ = timed(wl["roofline"]["run"], dom_steps, 3)
+        dom_ms = dom_total / dom_steps
 
     e2e = None
     if not args.no_e2e:
@@ -499,11 +520,12 @@ def main():
         peaks = measured_peaks()
         per_step_ms = ms / args.steps
         value = wl["units_per_step"] * world * args.steps / (ms / 1e3)
+        kernel_ms = dom_ms if dom_ms is not None else per_step_ms
         if wl["roofline"]["bound"] == "tensor":
-            achieved = wl["roofline"]["flops_per_launch"] / (per_step_ms / 1e3) / 1e12
+            achieved = wl["roofline"]["flops_per_launch"] / (kernel_ms / 1e3) / 1e12
             peak, punit = peaks["bf16_tflops"], "TFLOP/s"
         else:
-            achieved = wl["roofline"]["bytes_per_launch"] / (per_step_ms / 1e3) / 1e9
+            achieved = wl["roofline"]["bytes_per_launch"] / (kernel_ms / 1e3) / 1e9
             peak, punit = peaks["hbm_gbs"], "GB/s"
         line = {
             "metric": wl["metric"], "value": value, "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
@@ -511,10 +533,16 @@ def main():
             "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic (seeded)",
             "config": dict(wl["config"], name=wl["name"]),
             "clocks": clocks, "gpu_launches": launches,
-            "roofline": {"bound": wl["roofline"]["bound"], "achieved": achieved, "peak": peak, "unit": punit,
-                         "frac": achieved / peak, "traffic": None, "peak_source": peaks["source"]},
+            "roofline": {"bound": wl["roofline"]["bound"], "kernel": wl["roofline"].get("kernel"), "achieved": achieved, "peak": peak,
+                         "unit": punit, "frac": achieved / peak, "kernel_us": kernel_ms * 1e3,
+                         "traffic": wl["roofline"].get("traffic"), "traffic_note": wl["roofline"].get("traffic_note"),
+                         "peak_source": peaks["source"] + " (MEASURED_PEAKS.json copy / cuBLAS burst)"},
             "e2e": e2e,
         }
+        if "step_bytes" in wl["roofline"]:
+            sb = wl["roofline"]["step_bytes"] / (per_step_ms / 1e3) / 1e9
+            line["step_roofline"] = {"bound": "hbm", "achieved": sb, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": sb / peaks["hbm_gbs"],
+                                     "note": "whole step: per-GPU matmul weights + KV codes and scales read once / step time"}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = wl["cpu_baseline"]()
         print(json.dumps(line), flush=True)
