@@ -5,9 +5,10 @@
 //   Cast(q) -> Dequantize(K, V per cache row) -> DecodeAttentionValid(f32) -> Cast(out).
 //
 // The tiled kernel is HBM-bound: every K/V code byte is read once per GQA group. Design:
-//   * grid = (split, plane) with plane = (batch, kv head); each CTA walks a contiguous range of
-//     128-key tiles of its plane (flash-decoding split-KV); partial (max, sum, context) triples
-//     go to a scratch buffer and a small second kernel merges the splits.
+//   * persistent grid (2 CTAs per SM): the (plane, 128-key tile) pairs, plane = (batch, kv head),
+//     form one list in plane-major order and every CTA walks an equal contiguous share of it
+//     (flash-decoding split-KV with no idle tail and a ring that never drains); partial (max, sum,
+//     context) triples per (plane, CTA) go to a scratch buffer and a small second kernel merges them.
 //   * a producer warp feeds a 3-stage ring with TMA (cp.async.bulk.tensor, 128B swizzle):
 //     K codes, V codes, K scales, V scales per stage; mbarrier full/empty pairs, bounded waits.
 //   * dequantisation is never materialised. q is split into three signed base-256 digits per
@@ -43,7 +44,8 @@ constexpr uint32_t STAGE_K = 0, STAGE_V = TK * HD, STAGE_SK = 2 * TK * HD, STAGE
 constexpr uint32_t STAGE_BYTES = 2 * TK * HD + 2 * TK * 4;  // 33792
 constexpr uint32_t SMEM_Q = STAGES * STAGE_BYTES;            // 16 x 128 B digit tile
 constexpr uint32_t SMEM_MISC = SMEM_Q + 16 * HD;             // cq[4], bad[4], abort, barriers
-constexpr uint32_t SMEM_TOTAL = SMEM_MISC + 256 + 1024;      // + alignment slack
+constexpr uint32_t SMEM_MERGE = SMEM_MISC + 256;             // 4 warps x 4 heads x (128 + 2) f32
+constexpr uint32_t SMEM_TOTAL = SMEM_MERGE + CONSUMER_WARPS * MAXG * (HD + 2) * 4 + 1024;  // + alignment slack
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -53,10 +55,10 @@ struct FaParams {
     const float *k_new_s, *v_new_s;
     const uint32_t* valid_len;
     void* out;
-    float* part_o;   // [plane][split][MAXG][HD]
-    float* part_ml;  // [plane][split][MAXG][2]
+    float* part_o;   // [plane][slot][MAXG][HD]
+    float* part_ml;  // [plane][slot][MAXG][2]
     uint32_t* status;
-    uint32_t past, G, splits, box_rows;
+    uint32_t past, G, planes, max_slots, box_rows;
     float scale_div;
     int dtype;
     int debug_skip;  // measurement aid: 1 = consumers only release the tiles (pure streaming)
@@ -136,6 +138,24 @@ __device__ __forceinline__ float exp2_guard(float s, float m) {
     return exp2f((s - m) * LOG2E);
 }
 
+// Ownership of the global tile list: CTA c of n takes tiles [total*c/n, total*(c+1)/n).
+__device__ __forceinline__ uint32_t fa_start(uint32_t c, uint32_t total, uint32_t nctas) {
+    return (uint32_t)(((uint64_t)total * c) / nctas);
+}
+__device__ __forceinline__ uint32_t fa_owner(uint32_t g, uint32_t total, uint32_t nctas) {
+    uint32_t c = (uint32_t)(((uint64_t)g * nctas) / total);
+    while (c + 1 < nctas && fa_start(c + 1, total, nctas) <= g) ++c;
+    while (c > 0 && fa_start(c, total, nctas) > g) --c;
+    return c;
+}
+
+// Persistent kernel. The work is the list of (plane, tile) pairs in plane-major order, every
+// plane contributing ceil(visible/128) cache tiles plus one tile for this step's new row. Each
+// CTA owns an equal contiguous share of that list, so its TMA ring never drains between planes
+// and no wave of CTAs ends with idle SMs. A share covers parts of a few planes ("segments"); for
+// each segment the consumers rebuild the query digits, run the tiles, merge their four running
+// (max, sum, context) triples and store one partial; decode_attention_combine_kernel merges the
+// partials of the CTAs that shared a plane.
 __global__ void __launch_bounds__(FA_THREADS, HOLO_ATTN_MINB)
 decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                            const __grid_constant__ CUtensorMap map_ks, const __grid_constant__ CUtensorMap map_vs,
@@ -149,17 +169,18 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(sm + SMEM_MISC + 32);
     float* s_red = reinterpret_cast<float*>(sm + SMEM_MISC + 64);       // [4 warps][4 heads]
     const uint32_t bar_full = base + SMEM_MISC + 128, bar_empty = bar_full + 8 * STAGES;
+    float* mo = reinterpret_cast<float*>(sm + SMEM_MERGE);  // [warp][head][HD]
+    float* mml = mo + CONSUMER_WARPS * MAXG * HD;            // [warp][head][2]
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t split = blockIdx.x, plane = blockIdx.y;
-    const uint32_t G = p.G;
+    const uint32_t G = p.G, nctas = gridDim.x, cta = blockIdx.x;
     const uint32_t vis_past = min(*p.valid_len, p.past);
     const uint32_t tiles_past = (vis_past + TK - 1) / TK;
     const uint32_t T = tiles_past + 1;  // + the tile holding this step's new row
-    const uint32_t t_begin = (uint32_t)(((uint64_t)T * split) / p.splits);
-    const uint32_t t_end = (uint32_t)(((uint64_t)T * (split + 1)) / p.splits);
+    const uint32_t total = p.planes * T;
+    const uint32_t g0 = fa_start(cta, total, nctas), g1 = fa_start(cta + 1, total, nctas);
 
-    // an earlier CTA of this launch (or an earlier launch) gave up on a wait: do not start
+    // an earlier launch gave up on a wait: do not start
     if (*reinterpret_cast<volatile uint32_t*>(p.status) & 2u) return;
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -169,57 +190,15 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // ---- query digits: q = (L0*65536 + L1*256 + L2) * 2^(ex-21), one row of the m16 tile per
-    // (head, digit): rows g, 4+g, 8+g hold L0, L1, L2 of head g; rows 12.. stay zero.
-    if (tid < 128) {
-        int8_t* sq = reinterpret_cast<int8_t*>(sm + SMEM_Q);
-        float qv[MAXG];
-#pragma unroll
-        for (int g = 0; g < MAXG; ++g) {
-            qv[g] = (uint32_t)g < G ? holo::load_float(p.q, ((uint64_t)plane * G + g) * HD + tid, p.dtype) : 0.0f;
-            float a = fabsf(qv[g]);
-            for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-            // NaN elements are dropped by fmaxf; detect them separately
-            uint32_t nanbit = __any_sync(0xffffffffu, qv[g] != qv[g]);
-            if (lane == 0) s_red[warp * 4 + g] = nanbit ? INFINITY : a;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-#pragma unroll
-        for (int g = 0; g < MAXG; ++g) {
-            float amax = fmaxf(fmaxf(s_red[g], s_red[4 + g]), fmaxf(s_red[8 + g], s_red[12 + g]));
-            uint32_t be = (__float_as_uint(amax) >> 23) & 0xffu;
-            int L0 = 0, L1 = 0, L2 = 0;
-            float cq = 0.0f;
-            uint32_t bad = 0;
-            if (be == 255u) {
-                bad = 1;  // inf / NaN in q: the reference yields NaN for the whole head
-            } else if (be != 0u) {
-                int ex = (int)be - 127;  // amax < 2^(ex+1)
-                int qi = __float2int_rn(scalbnf(qv[g], 21 - ex));  // |qi| < 2^22 keeps L0 within int8
-                L2 = ((qi + 128) & 255) - 128;
-                int q1 = (qi - L2) >> 8;
-                L1 = ((q1 + 128) & 255) - 128;
-                L0 = (q1 - L1) >> 8;
-                cq = scalbnf(1.0f, ex - 21) / p.scale_div;
-            }
-            sq[(g)*HD + tid] = (int8_t)L0;
-            sq[(4 + g) * HD + tid] = (int8_t)L1;
-            sq[(8 + g) * HD + tid] = (int8_t)L2;
-            sq[(12 + g) * HD + tid] = 0;
-            if (tid == 0) {
-                s_cq[g] = cq;
-                s_bad[g] = bad;
-            }
-        }
-    }
     __syncthreads();
 
     if (warp == CONSUMER_WARPS) {
         // ---------------- producer warp ----------------
         const uint32_t tx_bytes = p.box_rows * HD * 2 + p.box_rows * 4 * 2;
         uint32_t it = 0;
-        for (uint32_t t = t_begin; t < t_end; ++t, ++it) {
+        for (uint32_t g = g0; g < g1; ++g, ++it) {
             const uint32_t s = it % STAGES, use = it / STAGES;
+            const uint32_t plane = g / T, t = g % T;
             if (use > 0) {
                 bool ok = true;
                 if (lane == 0) ok = mbar_wait(bar_empty + 8 * s, (use - 1) & 1, s_abort, p.status);
@@ -253,32 +232,14 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     const uint32_t r = lane >> 2, i = lane & 3;
     const bool hi_group = r >= 4;       // lanes holding digit L1 (and the zero row)
     const uint32_t g = r & 3;           // head served by this lane
-    const float cq = s_cq[g];
-    uint32_t qa[4][4];
-    {
-        const uint32_t* sq32 = reinterpret_cast<const uint32_t*>(sm + SMEM_Q);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            qa[ks][0] = sq32[(r * HD + 32 * ks + 4 * i) >> 2];
-            qa[ks][1] = sq32[((r + 8) * HD + 32 * ks + 4 * i) >> 2];
-            qa[ks][2] = sq32[(r * HD + 32 * ks + 16 + 4 * i) >> 2];
-            qa[ks][3] = sq32[((r + 8) * HD + 32 * ks + 16 + 4 * i) >> 2];
-        }
-    }
-    int acc[8][2][4];
-    float of[32];
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-#pragma unroll
-        for (int e = 0; e < 2; ++e)
-#pragma unroll
-            for (int x = 0; x < 4; ++x) acc[c][e][x] = 0;
-#pragma unroll
-    for (int x = 0; x < 32; ++x) of[x] = 0.0f;
-    float m_ref = -INFINITY, l_sum = 0.0f, sref = 0.0f, inv_sref = 0.0f;
-    uint32_t since_fold = 0;
     const uint32_t selA = hi_group ? 0x0051u : 0x0062u;  // digit byte of (x, y): L1 = byte 1, L0 = byte 2
     const uint32_t selB = hi_group ? 0x0073u : 0x0040u;  // zero byte 3, or L2 = byte 0
+    int acc[8][2][4];
+    float of[32];
+    float m_ref, l_sum, sref, inv_sref;
+    uint32_t since_fold;
+    uint32_t qa[4][4];
+    float cq;
 
     auto fold = [&]() {
         if (sref != 0.0f) {
@@ -301,168 +262,232 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         since_fold = 0;
     };
 
+
     uint32_t it = 0;
     bool aborted = false;
-    for (uint32_t t = t_begin; t < t_end; ++t, ++it) {
-        const uint32_t s = it % STAGES, use = it / STAGES;
-        if (!mbar_wait(bar_full + 8 * s, use & 1, s_abort, p.status)) {
-            aborted = true;
-            break;
+    uint32_t gt = g0;
+    while (gt < g1) {
+        const uint32_t plane = gt / T;
+        const uint32_t seg_end = min(g1, (plane + 1) * T);
+        // ---- query digits of this plane: q = (L0*65536 + L1*256 + L2) * 2^(ex-21), one row of
+        // the m16 tile per (head, digit): rows g, 4+g, 8+g hold L0, L1, L2 of head g; rows 12.. zero.
+        {
+            int8_t* sq = reinterpret_cast<int8_t*>(sm + SMEM_Q);
+            float qv[MAXG];
+#pragma unroll
+            for (int gg = 0; gg < MAXG; ++gg) {
+                qv[gg] = (uint32_t)gg < G ? holo::load_float(p.q, ((uint64_t)plane * G + gg) * HD + tid, p.dtype) : 0.0f;
+                float a = fabsf(qv[gg]);
+                for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+                // NaN elements are dropped by fmaxf; detect them separately
+                uint32_t nanbit = __any_sync(0xffffffffu, qv[gg] != qv[gg]);
+                if (lane == 0) s_red[warp * 4 + gg] = nanbit ? INFINITY : a;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+            for (int gg = 0; gg < MAXG; ++gg) {
+                float amax = fmaxf(fmaxf(s_red[gg], s_red[4 + gg]), fmaxf(s_red[8 + gg], s_red[12 + gg]));
+                uint32_t be = (__float_as_uint(amax) >> 23) & 0xffu;
+                int L0 = 0, L1 = 0, L2 = 0;
+                float cqv = 0.0f;
+                uint32_t bad = 0;
+                if (be == 255u) {
+                    bad = 1;  // inf / NaN in q: the reference yields NaN for the whole head
+                } else if (be != 0u) {
+                    int ex = (int)be - 127;  // amax < 2^(ex+1)
+                    int qi = __float2int_rn(scalbnf(qv[gg], 21 - ex));  // |qi| < 2^22 keeps L0 within int8
+                    L2 = ((qi + 128) & 255) - 128;
+                    int q1 = (qi - L2) >> 8;
+                    L1 = ((q1 + 128) & 255) - 128;
+                    L0 = (q1 - L1) >> 8;
+                    cqv = scalbnf(1.0f, ex - 21) / p.scale_div;
+                }
+                sq[(gg)*HD + tid] = (int8_t)L0;
+                sq[(4 + gg) * HD + tid] = (int8_t)L1;
+                sq[(8 + gg) * HD + tid] = (int8_t)L2;
+                sq[(12 + gg) * HD + tid] = 0;
+                if (tid == 0) {
+                    s_cq[gg] = cqv;
+                    s_bad[gg] = bad;
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            cq = s_cq[g];
+            const uint32_t* sq32 = reinterpret_cast<const uint32_t*>(sm + SMEM_Q);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                qa[ks][0] = sq32[(r * HD + 32 * ks + 4 * i) >> 2];
+                qa[ks][1] = sq32[((r + 8) * HD + 32 * ks + 4 * i) >> 2];
+                qa[ks][2] = sq32[(r * HD + 32 * ks + 16 + 4 * i) >> 2];
+                qa[ks][3] = sq32[((r + 8) * HD + 32 * ks + 16 + 4 * i) >> 2];
+            }
         }
-        const uint32_t st = base + s * STAGE_BYTES;
-        const uint8_t* sp = sm + s * STAGE_BYTES;
-        // keys of this warp: tile rows 32*warp .. +31; number of visible rows in the tile
-        const uint32_t limit = t < tiles_past ? min((uint32_t)TK, vis_past - t * TK) : 1u;
-        const uint32_t row0 = warp * 32;
-        if (row0 < limit && !p.debug_skip) {
-            // ---- scores: S[(head,digit)][key] = sum_c Qdigit * Kcode (exact i32) ----
-            int sacc[4][4];
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-#pragma unroll
-                for (int x = 0; x < 4; ++x) sacc[nt][x] = 0;
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t kb[4];
-                    ldsm_x4(kb, swz(st + STAGE_K, row0 + 8 * nt + (lane & 7), 4 * half + (lane >> 3)));
-                    mma_s8s8(sacc[nt], qa[2 * half], kb[0], kb[1]);
-                    mma_s8s8(sacc[nt], qa[2 * half + 1], kb[2], kb[3]);
-                }
-            }
-            const float* sk = reinterpret_cast<const float*>(sp + STAGE_SK);
-            const float* sv = reinterpret_cast<const float*>(sp + STAGE_SV);
-            float sc[8], svv[8];
-            float mt = -INFINITY;
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const uint32_t key = row0 + 8 * nt + 2 * i;
-                const float2 k2 = *reinterpret_cast<const float2*>(sk + key);
-                const float2 v2 = *reinterpret_cast<const float2*>(sv + key);
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    float part = hi_group ? __int2float_rn(sacc[nt][e]) * 256.0f
-                                          : fmaf(__int2float_rn(sacc[nt][e]), 65536.0f, __int2float_rn(sacc[nt][2 + e]));
-                    float full = part + __shfl_xor_sync(0xffffffffu, part, 16);
-                    float kscale = e ? k2.y : k2.x;
-                    float sval = full * (kscale * cq);
-                    float vscale = e ? v2.y : v2.x;
-                    if (key + e >= limit) {  // unrealized row: whatever bytes it holds never count
-                        sval = -INFINITY;
-                        vscale = 0.0f;
-                    }
-                    sc[nt * 2 + e] = sval;
-                    svv[nt * 2 + e] = vscale;
-                    mt = fmaxf(mt, sval);
-                }
-            }
-            mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
-            mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
-            // ---- weights relative to the running reference, scaled for digit extraction ----
-            float pe[8], ps[8];
-            float pmax = 0.0f;
-#pragma unroll
-            for (int x = 0; x < 8; ++x) {
-                pe[x] = exp2_guard(sc[x], m_ref);
-                ps[x] = pe[x] * svv[x] * sref;
-                pmax = fmaxf(pmax, ps[x] != ps[x] ? INFINITY : ps[x]);
-            }
-            pmax = fmaxf(pmax, __shfl_xor_sync(0xffffffffu, pmax, 1));
-            pmax = fmaxf(pmax, __shfl_xor_sync(0xffffffffu, pmax, 2));
-            const bool need = !(pmax < 16777215.0f) || mt > m_ref + 60.0f || sref == 0.0f || since_fold >= 1024;
-            if (__any_sync(0xffffffffu, need)) {
-                fold();
-                const float m_new = fmaxf(m_ref, mt);
-                const float alpha = m_ref == -INFINITY ? 0.0f : exp2f((m_ref - m_new) * LOG2E);
-#pragma unroll
-                for (int x = 0; x < 32; ++x) of[x] *= alpha;
-                l_sum *= alpha;
-                m_ref = m_new;
-                float pm = 0.0f;
-#pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                    pe[x] = exp2_guard(sc[x], m_ref);
-                    float w = pe[x] * svv[x];
-                    pm = fmaxf(pm, w);
-                }
-                pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, 1));
-                pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, 2));
-                int sexp = 0;
-                const uint32_t pbe = (__float_as_uint(pm) >> 23) & 0xffu;
-                if (pbe != 0u && pbe != 255u) sexp = 15 - ((int)pbe - 127);
-                sexp = max(-100, min(100, sexp));
-                sref = __uint_as_float((uint32_t)(127 + sexp) << 23);
-                inv_sref = __uint_as_float((uint32_t)(127 - sexp) << 23);
-#pragma unroll
-                for (int x = 0; x < 8; ++x) ps[x] = fminf(pe[x] * svv[x] * sref, 16777215.0f);
-            }
-            uint32_t pi[8];
-#pragma unroll
-            for (int x = 0; x < 8; ++x) {
-                l_sum += pe[x];
-                pi[x] = __float2uint_rn(fmaxf(ps[x], 0.0f));
-            }
-            uint32_t pa[4];
-            pa[0] = __byte_perm(__byte_perm(pi[0], pi[1], selA), __byte_perm(pi[2], pi[3], selA), 0x5410);
-            pa[1] = __byte_perm(__byte_perm(pi[0], pi[1], selB), __byte_perm(pi[2], pi[3], selB), 0x5410);
-            pa[2] = __byte_perm(__byte_perm(pi[4], pi[5], selA), __byte_perm(pi[6], pi[7], selA), 0x5410);
-            pa[3] = __byte_perm(__byte_perm(pi[4], pi[5], selB), __byte_perm(pi[6], pi[7], selB), 0x5410);
-            // ---- context: O[(head,digit)][c] += sum_key Pdigit * Vcode ----
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                uint32_t vr[4];
-                ldsm_x4_trans(vr, swz(st + STAGE_V, row0 + 8 * (lane >> 3) + (lane & 7), ch));
-                mma_u8s8(acc[ch][0], pa, __byte_perm(vr[0], vr[1], 0x6420), __byte_perm(vr[2], vr[3], 0x6420));
-                mma_u8s8(acc[ch][1], pa, __byte_perm(vr[0], vr[1], 0x7531), __byte_perm(vr[2], vr[3], 0x7531));
-            }
-            ++since_fold;
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_empty + 8 * s);
-    }
-    fold();
-    // ---- per-warp partials -> shared memory (aliases the stage ring; every consumer has
-    // finished reading it once all four warps reach the barrier) ----
-    l_sum += __shfl_xor_sync(0xffffffffu, l_sum, 1);
-    l_sum += __shfl_xor_sync(0xffffffffu, l_sum, 2);
-#pragma unroll
-    for (int x = 0; x < 32; ++x) of[x] += __shfl_xor_sync(0xffffffffu, of[x], 16);
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    float* mo = reinterpret_cast<float*>(sm);           // [warp][head][HD]
-    float* mml = mo + CONSUMER_WARPS * MAXG * HD;        // [warp][head][2]
-    if (!hi_group) {
 #pragma unroll
         for (int c = 0; c < 8; ++c)
-            *reinterpret_cast<float4*>(mo + ((warp * MAXG + g) * HD + 16 * c + 4 * i)) =
-                make_float4(of[c * 4 + 0], of[c * 4 + 1], of[c * 4 + 2], of[c * 4 + 3]);
-        if (i == 0) {
-            mml[(warp * MAXG + g) * 2 + 0] = m_ref;
-            mml[(warp * MAXG + g) * 2 + 1] = l_sum;
-        }
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (aborted || *s_abort) return;
-    {
-        const uint32_t c = tid;  // 0..127
-        for (uint32_t gg = 0; gg < G; ++gg) {
-            float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; ++w) M = fmaxf(M, mml[(w * MAXG + gg) * 2]);
-            float L = 0.0f, O = 0.0f;
+            for (int e = 0; e < 2; ++e)
 #pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; ++w) {
-                float wm = mml[(w * MAXG + gg) * 2];
-                if (wm != -INFINITY) {
-                    float f = exp2f((wm - M) * LOG2E);
-                    L = fmaf(mml[(w * MAXG + gg) * 2 + 1], f, L);
-                    O = fmaf(mo[(w * MAXG + gg) * HD + c], f, O);
+                for (int x = 0; x < 4; ++x) acc[c][e][x] = 0;
+#pragma unroll
+        for (int x = 0; x < 32; ++x) of[x] = 0.0f;
+        m_ref = -INFINITY;
+        l_sum = 0.0f;
+        sref = 0.0f;
+        inv_sref = 0.0f;
+        since_fold = 0;
+
+        for (; gt < seg_end; ++gt, ++it) {
+            const uint32_t s = it % STAGES, use = it / STAGES;
+            const uint32_t t = gt % T;
+            // after a failed wait the warp keeps walking (so that every barrier below is still
+            // reached by all four warps) but touches no tile
+            if (!aborted && !mbar_wait(bar_full + 8 * s, use & 1, s_abort, p.status)) aborted = true;
+            const uint32_t st = base + s * STAGE_BYTES;
+            const uint8_t* sp = sm + s * STAGE_BYTES;
+            // keys of this warp: tile rows 32*warp .. +31; number of visible rows in the tile
+            const uint32_t limit = t < tiles_past ? min((uint32_t)TK, vis_past - t * TK) : 1u;
+            const uint32_t row0 = warp * 32;
+            if (!aborted && row0 < limit && !p.debug_skip) {
+                // ---- scores: S[(head,digit)][key] = sum_c Qdigit * Kcode (exact i32) ----
+                int sacc[4][4];
+    #pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+    #pragma unroll
+                    for (int x = 0; x < 4; ++x) sacc[nt][x] = 0;
+    #pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t kb[4];
+                        ldsm_x4(kb, swz(st + STAGE_K, row0 + 8 * nt + (lane & 7), 4 * half + (lane >> 3)));
+                        mma_s8s8(sacc[nt], qa[2 * half], kb[0], kb[1]);
+                        mma_s8s8(sacc[nt], qa[2 * half + 1], kb[2], kb[3]);
+                    }
                 }
+                const float* sk = reinterpret_cast<const float*>(sp + STAGE_SK);
+                const float* sv = reinterpret_cast<const float*>(sp + STAGE_SV);
+                float sc[8], svv[8];
+                float mt = -INFINITY;
+    #pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const uint32_t key = row0 + 8 * nt + 2 * i;
+                    const float2 k2 = *reinterpret_cast<const float2*>(sk + key);
+                    const float2 v2 = *reinterpret_cast<const float2*>(sv + key);
+    #pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        float part = hi_group ? __int2float_rn(sacc[nt][e]) * 256.0f
+                                              : fmaf(__int2float_rn(sacc[nt][e]), 65536.0f, __int2float_rn(sacc[nt][2 + e]));
+                        float full = part + __shfl_xor_sync(0xffffffffu, part, 16);
+                        float kscale = e ? k2.y : k2.x;
+                        float sval = full * (kscale * cq);
+                        float vscale = e ? v2.y : v2.x;
+                        if (key + e >= limit) {  // unrealized row: whatever bytes it holds never count
+                            sval = -INFINITY;
+                            vscale = 0.0f;
+                        }
+                        sc[nt * 2 + e] = sval;
+                        svv[nt * 2 + e] = vscale;
+                        mt = fmaxf(mt, sval);
+                    }
+                }
+                mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
+                mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
+                // ---- weights relative to the running reference, scaled for digit extraction ----
+                float pe[8], ps[8];
+                float pmax = 0.0f;
+    #pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    pe[x] = exp2_guard(sc[x], m_ref);
+                    ps[x] = pe[x] * svv[x] * sref;
+                    pmax = fmaxf(pmax, ps[x] != ps[x] ? INFINITY : ps[x]);
+                }
+                pmax = fmaxf(pmax, __shfl_xor_sync(0xffffffffu, pmax, 1));
+                pmax = fmaxf(pmax, __shfl_xor_sync(0xffffffffu, pmax, 2));
+                const bool need = !(pmax < 16777215.0f) || mt > m_ref + 60.0f || sref == 0.0f || since_fold >= 1024;
+                if (__any_sync(0xffffffffu, need)) {
+                    fold();
+                    const float m_new = fmaxf(m_ref, mt);
+                    const float alpha = m_ref == -INFINITY ? 0.0f : exp2f((m_ref - m_new) * LOG2E);
+    #pragma unroll
+                    for (int x = 0; x < 32; ++x) of[x] *= alpha;
+                    l_sum *= alpha;
+                    m_ref = m_new;
+                    float pm = 0.0f;
+    #pragma unroll
+                    for (int x = 0; x < 8; ++x) {
+                        pe[x] = exp2_guard(sc[x], m_ref);
+                        float w = pe[x] * svv[x];
+                        pm = fmaxf(pm, w);
+                    }
+                    pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, 1));
+                    pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, 2));
+                    int sexp = 0;
+                    const uint32_t pbe = (__float_as_uint(pm) >> 23) & 0xffu;
+                    if (pbe != 0u && pbe != 255u) sexp = 15 - ((int)pbe - 127);
+                    sexp = max(-100, min(100, sexp));
+                    sref = __uint_as_float((uint32_t)(127 + sexp) << 23);
+                    inv_sref = __uint_as_float((uint32_t)(127 - sexp) << 23);
+    #pragma unroll
+                    for (int x = 0; x < 8; ++x) ps[x] = fminf(pe[x] * svv[x] * sref, 16777215.0f);
+                }
+                uint32_t pi[8];
+    #pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    l_sum += pe[x];
+                    pi[x] = __float2uint_rn(fmaxf(ps[x], 0.0f));
+                }
+                uint32_t pa[4];
+                pa[0] = __byte_perm(__byte_perm(pi[0], pi[1], selA), __byte_perm(pi[2], pi[3], selA), 0x5410);
+                pa[1] = __byte_perm(__byte_perm(pi[0], pi[1], selB), __byte_perm(pi[2], pi[3], selB), 0x5410);
+                pa[2] = __byte_perm(__byte_perm(pi[4], pi[5], selA), __byte_perm(pi[6], pi[7], selA), 0x5410);
+                pa[3] = __byte_perm(__byte_perm(pi[4], pi[5], selB), __byte_perm(pi[6], pi[7], selB), 0x5410);
+                // ---- context: O[(head,digit)][c] += sum_key Pdigit * Vcode ----
+    #pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    uint32_t vr[4];
+                    ldsm_x4_trans(vr, swz(st + STAGE_V, row0 + 8 * (lane >> 3) + (lane & 7), ch));
+                    mma_u8s8(acc[ch][0], pa, __byte_perm(vr[0], vr[1], 0x6420), __byte_perm(vr[2], vr[3], 0x6420));
+                    mma_u8s8(acc[ch][1], pa, __byte_perm(vr[0], vr[1], 0x7531), __byte_perm(vr[2], vr[3], 0x7531));
+                }
+                ++since_fold;
             }
-            if (s_bad[gg]) { O = NAN; L = 1.0f; M = 0.0f; }
-            if (p.splits == 1) {
-                float res = O / fmaxf(L, 1e-30f);
-                holo::store_float(p.out, ((uint64_t)plane * G + gg) * HD + c, res, p.dtype);
-            } else {
-                const uint64_t pidx = ((uint64_t)plane * p.splits + split) * MAXG + gg;
+            __syncwarp();
+            if (lane == 0 && !aborted) mbar_arrive(bar_empty + 8 * s);
+        }
+        fold();
+        // ---- merge the four warps' triples and store this segment's partial ----
+        l_sum += __shfl_xor_sync(0xffffffffu, l_sum, 1);
+        l_sum += __shfl_xor_sync(0xffffffffu, l_sum, 2);
+#pragma unroll
+        for (int x = 0; x < 32; ++x) of[x] += __shfl_xor_sync(0xffffffffu, of[x], 16);
+        if (!hi_group) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<float4*>(mo + ((warp * MAXG + g) * HD + 16 * c + 4 * i)) =
+                    make_float4(of[c * 4 + 0], of[c * 4 + 1], of[c * 4 + 2], of[c * 4 + 3]);
+            if (i == 0) {
+                mml[(warp * MAXG + g) * 2 + 0] = m_ref;
+                mml[(warp * MAXG + g) * 2 + 1] = l_sum;
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (!aborted && !*s_abort) {
+            const uint32_t slot = cta - fa_owner(plane * T, total, nctas);
+            const uint32_t c = tid;  // 0..127
+            for (uint32_t gg = 0; gg < G; ++gg) {
+                float M = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < CONSUMER_WARPS; ++w) M = fmaxf(M, mml[(w * MAXG + gg) * 2]);
+                float L = 0.0f, O = 0.0f;
+#pragma unroll
+                for (int w = 0; w < CONSUMER_WARPS; ++w) {
+                    float wm = mml[(w * MAXG + gg) * 2];
+                    if (wm != -INFINITY) {
+                        float f = exp2f((wm - M) * LOG2E);
+                        L = fmaf(mml[(w * MAXG + gg) * 2 + 1], f, L);
+                        O = fmaf(mo[(w * MAXG + gg) * HD + c], f, O);
+                    }
+                }
+                if (s_bad[gg]) { O = NAN; L = 1.0f; M = 0.0f; }
+                const uint64_t pidx = ((uint64_t)plane * p.max_slots + slot) * MAXG + gg;
                 p.part_o[pidx * HD + c] = O;
                 if (c == 0) {
                     p.part_ml[pidx * 2] = M;
@@ -470,19 +495,32 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 }
             }
         }
+        // the merge area, the digit tile and s_red are rewritten by the next segment
+        asm volatile("bar.sync 1, 128;" ::: "memory");
     }
 }
 
-// Merge the split partials of one (plane, head): out = sum_s O_s e^(m_s - M) / sum_s l_s e^(m_s - M).
+// Merge the partials of the CTAs that shared one plane, per (plane, head):
+// out = sum_s O_s e^(m_s - M) / sum_s l_s e^(m_s - M).
 __global__ void __launch_bounds__(HD)
 decode_attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, void* out,
-                                uint32_t splits, uint32_t G, int dtype) {
+                                const uint32_t* __restrict__ valid_len, uint32_t past, uint32_t planes, uint32_t nctas,
+                                uint32_t max_slots, uint32_t G, int dtype) {
     const uint32_t plane = blockIdx.x / G, gg = blockIdx.x % G, c = threadIdx.x;
+    const uint32_t vis_past = min(*valid_len, past);
+    const uint32_t T = (vis_past + TK - 1) / TK + 1, total = planes * T;
+    const uint32_t first = fa_owner(plane * T, total, nctas), last = fa_owner(plane * T + T - 1, total, nctas);
+    const uint32_t slots = last - first + 1;
+    // a CTA whose share of the list is empty (more CTAs than tiles) wrote nothing: skip its slot
     float M = -INFINITY;
-    for (uint32_t s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(((uint64_t)plane * splits + s) * MAXG + gg) * 2]);
+    for (uint32_t s = 0; s < slots; ++s) {
+        if (fa_start(first + s, total, nctas) == fa_start(first + s + 1, total, nctas)) continue;
+        M = fmaxf(M, part_ml[(((uint64_t)plane * max_slots + s) * MAXG + gg) * 2]);
+    }
     float L = 0.0f, O = 0.0f;
-    for (uint32_t s = 0; s < splits; ++s) {
-        const uint64_t pidx = ((uint64_t)plane * splits + s) * MAXG + gg;
+    for (uint32_t s = 0; s < slots; ++s) {
+        if (fa_start(first + s, total, nctas) == fa_start(first + s + 1, total, nctas)) continue;
+        const uint64_t pidx = ((uint64_t)plane * max_slots + s) * MAXG + gg;
         const float wm = part_ml[pidx * 2];
         if (wm != -INFINITY) {
             const float f = exp2f((wm - M) * LOG2E);
@@ -534,32 +572,14 @@ int32_t make_scales_map(CUtensorMap* map, const void* ptr, uint32_t past, uint32
     return HOLO_OK;
 }
 
-uint32_t pick_splits(uint32_t tiles, uint32_t planes, int sm_count) {
-    // Each CTA pays a fixed prologue (query digits) and epilogue (fold + merge), so it should
-    // walk many tiles; but the grid should also fill whole waves of 2 CTAs per SM. Take the
-    // smallest split count (<= 16 tiles per CTA) whose last wave is at least 96% full, else
-    // the best-filling one.
-    const uint32_t slots = (uint32_t)HOLO_ATTN_MINB * (uint32_t)sm_count;
-    const char* env = getenv("HOLO_ATTN_SPLITS");
-    if (env && atoi(env) > 0) return (uint32_t)min((int)tiles, atoi(env));
-    uint32_t lo = (tiles + 15) / 16, hi = (tiles + 2) / 3;
-    if (lo < 1) lo = 1;
-    while ((uint64_t)planes * lo < slots && lo < tiles) ++lo;  // at least one full wave when possible
-    if (hi < lo) hi = lo;
-    if (hi > tiles) hi = tiles;
-    uint32_t best = lo;
-    double best_eff = -1.0;
-    for (uint32_t s = lo; s <= hi; ++s) {
-        uint64_t ctas = (uint64_t)planes * s;
-        uint64_t waves = (ctas + slots - 1) / slots;
-        double eff = (double)ctas / (double)(waves * slots);
-        if (eff >= 0.96) return s;
-        if (eff > best_eff + 1e-9) {
-            best_eff = eff;
-            best = s;
-        }
-    }
-    return best;
+// Grid of the persistent kernel: HOLO_ATTN_MINB CTAs per SM (all co-resident), never more than
+// there are tiles. A plane is then shared by at most nctas / planes + 2 CTAs.
+uint32_t persistent_ctas(uint32_t tiles_per_plane, uint32_t planes, int sm_count) {
+    uint64_t want = (uint64_t)HOLO_ATTN_MINB * (uint32_t)sm_count;
+    if (const char* env = getenv("HOLO_ATTN_CTAS"))
+        if (atoi(env) > 0) want = (uint64_t)atoi(env);
+    const uint64_t total = (uint64_t)tiles_per_plane * planes;
+    return (uint32_t)(want < total ? want : total);
 }
 
 }  // namespace
@@ -590,10 +610,11 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a) 
         configured_device = ctx->device;
     }
     const uint32_t tiles = (a.past + TK - 1) / TK + 1;
-    const uint32_t splits = pick_splits(tiles, planes, ctx->sm_count);
+    const uint32_t nctas = persistent_ctas(tiles, planes, ctx->sm_count);
+    const uint32_t max_slots = nctas / planes + 2;
     const uint32_t box_rows = a.past < (uint32_t)TK ? a.past : (uint32_t)TK;
-    const uint64_t po_bytes = (uint64_t)planes * splits * MAXG * HD * 4, pml_bytes = (uint64_t)planes * splits * MAXG * 2 * 4;
-    if (splits > 1) HOLO_TRY(holo_ensure_scratch(ctx, po_bytes + pml_bytes));
+    const uint64_t po_bytes = (uint64_t)planes * max_slots * MAXG * HD * 4, pml_bytes = (uint64_t)planes * max_slots * MAXG * 2 * 4;
+    HOLO_TRY(holo_ensure_scratch(ctx, po_bytes + pml_bytes));
     CUtensorMap mk, mv, mks, mvs;
     HOLO_TRY(make_codes_map(&mk, a.k_past, a.past, planes, box_rows));
     HOLO_TRY(make_codes_map(&mv, a.v_past, a.past, planes, box_rows));
@@ -612,20 +633,19 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a) 
     p.status = ctx->dev_status;
     p.past = a.past;
     p.G = G;
-    p.splits = splits;
+    p.planes = planes;
+    p.max_slots = max_slots;
     p.box_rows = box_rows;
     p.scale_div = a.scale_div;
     p.dtype = a.dtype;
     p.debug_skip = getenv("HOLO_ATTN_DEBUG_SKIP") ? 1 : 0;
-    dim3 grid(splits, planes);
-    decode_attention_q8_kernel<<<grid, FA_THREADS, SMEM_TOTAL, ctx->stream>>>(mk, mv, mks, mvs, p);
+    decode_attention_q8_kernel<<<nctas, FA_THREADS, SMEM_TOTAL, ctx->stream>>>(mk, mv, mks, mvs, p);
     HOLO_CUDA(cudaGetLastError());
     ctx->launches++;
-    if (splits > 1) {
-        decode_attention_combine_kernel<<<planes * G, HD, 0, ctx->stream>>>(p.part_o, p.part_ml, a.out, splits, G, a.dtype);
-        HOLO_CUDA(cudaGetLastError());
-        ctx->launches++;
-    }
+    decode_attention_combine_kernel<<<planes * G, HD, 0, ctx->stream>>>(p.part_o, p.part_ml, a.out, a.valid_len, a.past, planes, nctas,
+                                                                        max_slots, G, a.dtype);
+    HOLO_CUDA(cudaGetLastError());
+    ctx->launches++;
     return HOLO_OK;
 }
 
@@ -686,9 +706,10 @@ extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const
         sd.ready = true;
     }
     const uint32_t tiles = (past_len + TK - 1) / TK + 1;
-    const uint32_t splits = pick_splits(tiles, planes, sd.sm_count);
-    const uint64_t po_bytes = (uint64_t)planes * splits * MAXG * HD * 4, pml_bytes = (uint64_t)planes * splits * MAXG * 2 * 4;
-    if (splits > 1 && po_bytes + pml_bytes > STATIC_SCRATCH_BYTES)
+    const uint32_t nctas = persistent_ctas(tiles, planes, sd.sm_count);
+    const uint32_t max_slots = nctas / planes + 2;
+    const uint64_t po_bytes = (uint64_t)planes * max_slots * MAXG * HD * 4, pml_bytes = (uint64_t)planes * max_slots * MAXG * 2 * 4;
+    if (po_bytes + pml_bytes > STATIC_SCRATCH_BYTES)
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP,
                          "unsupported op: decode_attention_q8_static needs %llu bytes of split-KV partials for this shape; the built-in "
                          "scratch holds %llu (use holo_b200_dispatch, whose scratch grows)",
@@ -723,17 +744,15 @@ extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const
     p.status = sd.status;
     p.past = past_len;
     p.G = G;
-    p.splits = splits;
+    p.planes = planes;
+    p.max_slots = max_slots;
     p.box_rows = box_rows;
     p.scale_div = scale_div;
     p.dtype = dtype;
     p.debug_skip = 0;
-    dim3 grid(splits, planes);
-    decode_attention_q8_kernel<<<grid, FA_THREADS, SMEM_TOTAL, stream>>>(mk, mv, mks, mvs, p);
+    decode_attention_q8_kernel<<<nctas, FA_THREADS, SMEM_TOTAL, stream>>>(mk, mv, mks, mvs, p);
     HOLO_CUDA(cudaGetLastError());
-    if (splits > 1) {
-        decode_attention_combine_kernel<<<planes * G, HD, 0, stream>>>(p.part_o, p.part_ml, out, splits, G, dtype);
-        HOLO_CUDA(cudaGetLastError());
-    }
+    decode_attention_combine_kernel<<<planes * G, HD, 0, stream>>>(p.part_o, p.part_ml, out, valid_len, past_len, planes, nctas, max_slots, G, dtype);
+    HOLO_CUDA(cudaGetLastError());
     return HOLO_OK;
 }

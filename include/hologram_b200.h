@@ -367,8 +367,9 @@ int32_t holo_b200_archive_check(const uint8_t* archive, uint64_t len, int32_t ve
  * the library keeps that array until the process exits) rather than to the context's growable
  * scratch buffer, so the call performs no cudaMalloc / cudaFree and needs no context.
  * Limits: head_dim 128; heads / kv_heads <= 4; past_len a multiple of 4 and >= 4; code and scale
- * pointers 16-byte aligned; shapes whose partials exceed the array (batch * kv_heads * splits * 4 *
- * 130 floats, about 260 kv-head planes at 8 splits) are refused with HOLO_ERR_UNSUPPORTED_OP.
+ * pointers 16-byte aligned; shapes whose partials exceed the array ((2 * SM count + 2 * batch *
+ * kv_heads) * 4 * 130 floats: about 3800 (batch, kv head) planes) are refused with
+ * HOLO_ERR_UNSUPPORTED_OP.
  * The first call on each device looks the array up (the device of the calling thread must be the
  * stream's device); make that first call before any stream capture begins. All calls share the
  * array: two calls that overlap on the GPU (different streams) race on it. Enqueues on
