@@ -2,8 +2,8 @@
 // Replaces crates/hologram-compute/src/cpu/lut.rs (build_table :43-67, unary_lut :76-98).
 //
 // The stream kernel is HBM-bound: 2 B read + 2 B written per element. One persistent CTA per
-// SM stages the 128 KiB table into shared memory once, then walks the input with 128-bit
-// coalesced loads, does eight shared-memory lookups per vector and writes 128-bit stores.
+// SM holds the 128 KiB table in shared memory, receives the input through a ring of bulk async
+// copies, does eight shared-memory lookups per 128-bit vector and writes 128-bit stores.
 #include "common.h"
 #include "numerics.cuh"
 
@@ -18,8 +18,6 @@ __global__ void build_table_kernel(uint16_t* table, int act, int dtype) {
     table[bits] = holo::narrow16(y, dtype);
 }
 
-constexpr int LUT_THREADS = 1024;
-constexpr int LUT_UNROLL = 4;
 constexpr int TABLE_BYTES = 65536 * 2;
 
 __device__ __forceinline__ uint32_t lookup2(const uint16_t* tab, uint32_t w) {
@@ -28,71 +26,127 @@ __device__ __forceinline__ uint32_t lookup2(const uint16_t* tab, uint32_t w) {
     return lo | (hi << 16);
 }
 
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
 __device__ __forceinline__ void st_stream(uint4* p, uint4 v) {
     asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                  : "memory");
 }
 
-// Persistent stream kernel. `in`/`out` are 16-byte aligned; nvec = n / 8 full vectors; the
-// n % 8 tail elements are handled by the first CTA.
-__global__ void __launch_bounds__(LUT_THREADS, 1)
-lut_stream_kernel(const uint16_t* __restrict__ table, const uint16_t* __restrict__ in, uint16_t* __restrict__ out,
-                  uint64_t n) {
-    extern __shared__ __align__(16) uint16_t s_tab[];
-    const uint4* in4 = reinterpret_cast<const uint4*>(in);
-    uint4* out4 = reinterpret_cast<uint4*>(out);
-    const uint64_t nvec = n >> 3;
-    const uint64_t chunk = (uint64_t)LUT_THREADS * LUT_UNROLL;
-    uint64_t base = (uint64_t)blockIdx.x * chunk;
-    const uint64_t stride = (uint64_t)gridDim.x * chunk;
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-    // Issue the first batch of input loads before staging the table so their latency
-    // overlaps the table copy.
-    uint4 v[LUT_UNROLL];
-#pragma unroll
-    for (int u = 0; u < LUT_UNROLL; ++u) {
-        uint64_t i = base + (uint64_t)u * LUT_THREADS + threadIdx.x;
-        if (i < nvec) v[u] = ld_stream(in4 + i);
+// Bounded mbarrier wait: false after LUT_WAIT_LIMIT polls.
+constexpr uint32_t LUT_WAIT_LIMIT = 1u << 22;
+__device__ __forceinline__ bool lut_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok = 0;
+    for (uint32_t it = 0; it < LUT_WAIT_LIMIT && !ok; ++it) {
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     }
-    {
-        const uint4* t4 = reinterpret_cast<const uint4*>(table);
-        uint4* s4 = reinterpret_cast<uint4*>(s_tab);
-#pragma unroll
-        for (int i = 0; i < TABLE_BYTES / 16 / LUT_THREADS; ++i)
-            s4[i * LUT_THREADS + threadIdx.x] = __ldg(t4 + i * LUT_THREADS + threadIdx.x);
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bar_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// Persistent stream kernel: one CTA per SM = 31 lookup warps + 1 copy warp.
+//   * The input is cut into tiles of 992 vectors of 16 bytes (one vector per lookup thread); CTA c
+//     takes tiles c, c + grid, c + 2 grid, ... so that at any moment the whole chip reads one
+//     compact window of the input (measured: 7 % faster than one contiguous range per CTA).
+//   * The copy warp keeps a ring of LUT_STAGES tiles in flight with bulk async copies
+//     (global -> shared, completion on an mbarrier), and brings the 128 KiB table in as 16 copies
+//     of 8 KiB right after the first two tiles, each CTA starting at a different piece so that the
+//     CTAs do not all ask the same L2 lines at the same moment.
+//   * A lookup thread reads its vector from the ring, frees the slot at once (the values are in
+//     registers), does its eight shared-memory lookups and writes one 128-bit streaming store.
+// `in`/`out` are 16-byte aligned; the n % 8 tail elements are done by the first CTA. Every wait is
+// bounded: on timeout the thread raises status bit 2 and leaves.
+constexpr int LUT_WARPS = 31;
+constexpr int LUT_STAGES = 6;
+constexpr uint32_t LUT_TILE_VEC = LUT_WARPS * 32;
+constexpr uint32_t LUT_TILE_BYTES = LUT_TILE_VEC * 16;
+constexpr int TABLE_PIECES = 16;
+constexpr int LUT_SMEM = TABLE_BYTES + LUT_STAGES * LUT_TILE_BYTES + 8 * (1 + 2 * LUT_STAGES);
+
+__global__ void __launch_bounds__((LUT_WARPS + 1) * 32, 1)
+lut_stream_kernel(const uint16_t* __restrict__ table, const uint16_t* __restrict__ in, uint16_t* __restrict__ out,
+                  uint64_t n, uint32_t* status) {
+    extern __shared__ __align__(128) unsigned char lut_smem[];
+    uint16_t* s_tab = reinterpret_cast<uint16_t*>(lut_smem);
+    unsigned char* ring = lut_smem + TABLE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + LUT_STAGES * LUT_TILE_BYTES);
+    const uint32_t bar_tab = smem_u32(bars), bar_full = smem_u32(bars + 1), bar_empty = smem_u32(bars + 1 + LUT_STAGES);
+    const uint64_t nvec = n >> 3;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint64_t first = (uint64_t)blockIdx.x * LUT_TILE_VEC;
+    const uint64_t step = (uint64_t)gridDim.x * LUT_TILE_VEC;
+
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_tab));
+        for (int s = 0; s < LUT_STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_full + 8 * s));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_empty + 8 * s), "r"(LUT_WARPS));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    while (base < nvec) {
-        const uint64_t next = base + stride;
-        uint4 nv[LUT_UNROLL];
-#pragma unroll
-        for (int u = 0; u < LUT_UNROLL; ++u) {
-            uint64_t i = next + (uint64_t)u * LUT_THREADS + threadIdx.x;
-            if (i < nvec) nv[u] = ld_stream(in4 + i);
-        }
-#pragma unroll
-        for (int u = 0; u < LUT_UNROLL; ++u) {
-            uint64_t i = base + (uint64_t)u * LUT_THREADS + threadIdx.x;
-            if (i < nvec) {
-                uint4 r;
-                r.x = lookup2(s_tab, v[u].x);
-                r.y = lookup2(s_tab, v[u].y);
-                r.z = lookup2(s_tab, v[u].z);
-                r.w = lookup2(s_tab, v[u].w);
-                st_stream(out4 + i, r);
+    if (warp == LUT_WARPS) {
+        if (lane != 0) return;
+        uint32_t k = 0;
+        bool table_sent = false;
+        for (uint64_t pos = first;; pos += step, ++k) {
+            if (!table_sent && (k == 2 || pos >= nvec)) {
+                table_sent = true;
+                bar_expect(bar_tab, TABLE_BYTES);
+                constexpr uint32_t piece = TABLE_BYTES / TABLE_PIECES;
+                for (int c = 0; c < TABLE_PIECES; ++c) {
+                    const uint32_t off = ((c + blockIdx.x) % TABLE_PIECES) * piece;
+                    bulk_load(smem_u32(s_tab) + off, reinterpret_cast<const unsigned char*>(table) + off, piece, bar_tab);
+                }
             }
+            if (pos >= nvec) break;
+            const uint32_t s = k % LUT_STAGES, use = k / LUT_STAGES;
+            if (use > 0 && !lut_wait(bar_empty + 8 * s, (use - 1) & 1)) {
+                atomicOr(status, 2u);
+                break;
+            }
+            const uint64_t left = nvec - pos;
+            const uint32_t vec = left < LUT_TILE_VEC ? (uint32_t)left : LUT_TILE_VEC;
+            bar_expect(bar_full + 8 * s, vec * 16);
+            bulk_load(smem_u32(ring + s * LUT_TILE_BYTES), reinterpret_cast<const uint4*>(in) + pos, vec * 16, bar_full + 8 * s);
         }
-#pragma unroll
-        for (int u = 0; u < LUT_UNROLL; ++u) v[u] = nv[u];
-        base = next;
+        return;
+    }
+
+    if (!lut_wait(bar_tab, 0)) {
+        atomicOr(status, 2u);
+        return;
+    }
+    uint32_t k = 0;
+    for (uint64_t pos = first; pos < nvec; pos += step, ++k) {
+        const uint32_t s = k % LUT_STAGES, use = k / LUT_STAGES;
+        if (!lut_wait(bar_full + 8 * s, use & 1)) {
+            atomicOr(status, 2u);
+            return;
+        }
+        const uint64_t left = nvec - pos;
+        const bool live = threadIdx.x < left;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (live) v = reinterpret_cast<const uint4*>(ring + s * LUT_TILE_BYTES)[threadIdx.x];
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_empty + 8 * s) : "memory");
+        if (live) {
+            uint4 r;
+            r.x = lookup2(s_tab, v.x);
+            r.y = lookup2(s_tab, v.y);
+            r.z = lookup2(s_tab, v.z);
+            r.w = lookup2(s_tab, v.w);
+            st_stream(reinterpret_cast<uint4*>(out) + pos + threadIdx.x, r);
+        }
     }
     if (blockIdx.x == 0) {
         uint64_t i = (nvec << 3) + threadIdx.x;
@@ -159,13 +213,12 @@ int32_t holo_launch_lut(holo_b200_ctx* ctx, const uint16_t* table, const uint16_
     if (aligned && n >= (1ull << 21)) {
         static thread_local int configured_device = -1;
         if (configured_device != ctx->device) {
-            HOLO_CUDA(cudaFuncSetAttribute(lut_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TABLE_BYTES));
+            HOLO_CUDA(cudaFuncSetAttribute(lut_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LUT_SMEM));
             configured_device = ctx->device;
         }
-        const uint64_t chunk = (uint64_t)LUT_THREADS * LUT_UNROLL;
-        uint64_t want = (nvec + chunk - 1) / chunk;
+        uint64_t want = (nvec + LUT_TILE_VEC - 1) / LUT_TILE_VEC;
         int grid = (int)(want < (uint64_t)ctx->sm_count ? want : (uint64_t)ctx->sm_count);
-        lut_stream_kernel<<<grid, LUT_THREADS, TABLE_BYTES, ctx->stream>>>(table, in, out, n);
+        lut_stream_kernel<<<grid, (LUT_WARPS + 1) * 32, LUT_SMEM, ctx->stream>>>(table, in, out, n, ctx->dev_status);
     } else if (aligned && nvec > 0) {
         uint64_t blocks = (nvec + 255) / 256;
         lut_gather_vec_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(table, in, out, n);
