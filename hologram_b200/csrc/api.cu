@@ -63,6 +63,12 @@ extern "C" int32_t holo_b200_ctx_create(int32_t device, holo_b200_ctx** out) {
         delete ctx;
         return holo_fail(HOLO_ERR_INIT, "backend init failed: status word allocation");
     }
+    if (cudaMalloc(&ctx->attn_arrivals, 65536 * 4) != cudaSuccess || cudaMemset(ctx->attn_arrivals, 0, 65536 * 4) != cudaSuccess) {
+        cudaFree(ctx->dev_status);
+        cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return holo_fail(HOLO_ERR_INIT, "backend init failed: arrival counter allocation");
+    }
     *out = ctx;
     return HOLO_OK;
 }
@@ -78,6 +84,7 @@ extern "C" void holo_b200_ctx_destroy(holo_b200_ctx* ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->stage) cudaFree(ctx->stage);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->attn_arrivals) cudaFree(ctx->attn_arrivals);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -101,6 +108,7 @@ static int32_t check_dev_status(holo_b200_ctx* ctx) {
     HOLO_CUDA(cudaStreamSynchronize(ctx->stream));
     if (st == 0) return HOLO_OK;
     cudaMemsetAsync(ctx->dev_status, 0, 4, ctx->stream);
+    if (st & 2u) cudaMemsetAsync(ctx->attn_arrivals, 0, 65536 * 4, ctx->stream);  // a launch that gave up may have left counts behind
     if (st & 1u) return holo_fail_slot(HOLO_NO_SLOT, "gather index outside [−axis_dim, axis_dim)");
     return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: a device-side bounded wait gave up (status 0x%x)", st);
 }

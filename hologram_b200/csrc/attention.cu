@@ -58,6 +58,7 @@ struct FaParams {
     float* part_o;   // [plane][slot][MAXG][HD]
     float* part_ml;  // [plane][slot][MAXG][2]
     uint32_t* status;
+    uint32_t* arrivals;  // [planes] zero between launches: CTAs that have stored their partial of a shared plane
     uint32_t past, G, planes, max_slots, box_rows;
     float scale_div;
     int dtype;
@@ -142,11 +143,53 @@ __device__ __forceinline__ float exp2_guard(float s, float m) {
 __device__ __forceinline__ uint32_t fa_start(uint32_t c, uint32_t total, uint32_t nctas) {
     return (uint32_t)(((uint64_t)total * c) / nctas);
 }
+// The CTA whose share holds tile g: the largest c with fa_start(c) <= g, i.e. c < (g + 1) n / total.
 __device__ __forceinline__ uint32_t fa_owner(uint32_t g, uint32_t total, uint32_t nctas) {
-    uint32_t c = (uint32_t)(((uint64_t)g * nctas) / total);
-    while (c + 1 < nctas && fa_start(c + 1, total, nctas) <= g) ++c;
-    while (c > 0 && fa_start(c, total, nctas) > g) --c;
-    return c;
+    return (uint32_t)((((uint64_t)g + 1) * nctas - 1) / total);
+}
+
+// Fold the stored partials of slots [from, nsl) of one plane onto the running (max, sum, context)
+// triples of element c of each head, in slot order, and write the plane's result. Four slots per
+// round, with all of a round's loads issued before the first use (each is an L2 round trip).
+__device__ __forceinline__ void merge_slots(const FaParams& p, uint32_t plane, uint32_t first, uint32_t from, uint32_t nsl,
+                                            uint32_t total, uint32_t nctas, uint32_t G, uint32_t c, float (&M)[MAXG],
+                                            float (&L)[MAXG], float (&O)[MAXG]) {
+    for (uint32_t s0 = from; s0 < nsl; s0 += 4) {
+        float2 ml[4][MAXG];
+        float ov[4][MAXG];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t sl = s0 + j;
+            // a CTA whose share of the list is empty (more CTAs than tiles) stored nothing
+            const bool live = sl < nsl && !(nctas > total && fa_start(first + sl, total, nctas) == fa_start(first + sl + 1, total, nctas));
+#pragma unroll
+            for (int gg = 0; gg < MAXG; ++gg) {
+                ml[j][gg] = make_float2(-INFINITY, 0.0f);
+                ov[j][gg] = 0.0f;
+                if (live && (uint32_t)gg < G) {
+                    const uint64_t pidx = ((uint64_t)plane * p.max_slots + sl) * MAXG + gg;
+                    ml[j][gg] = __ldcg(reinterpret_cast<const float2*>(p.part_ml + pidx * 2));
+                    ov[j][gg] = __ldcg(p.part_o + pidx * HD + c);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int gg = 0; gg < MAXG; ++gg) {
+                const float wm = ml[j][gg].x;
+                if (wm != -INFINITY) {
+                    const float nm = fmaxf(M[gg], wm);
+                    const float fo = exp2_guard(M[gg], nm), fn = exp2f((wm - nm) * LOG2E);
+                    L[gg] = fmaf(ml[j][gg].y, fn, L[gg] * fo);
+                    O[gg] = fmaf(ov[j][gg], fn, O[gg] * fo);
+                    M[gg] = nm;
+                }
+            }
+    }
+#pragma unroll
+    for (int gg = 0; gg < MAXG; ++gg)
+        if ((uint32_t)gg < G) holo::store_float(p.out, ((uint64_t)plane * G + gg) * HD + c, O[gg] / fmaxf(L[gg], 1e-30f), p.dtype);
 }
 
 // Persistent kernel. The work is the list of (plane, tile) pairs in plane-major order, every
@@ -154,8 +197,9 @@ __device__ __forceinline__ uint32_t fa_owner(uint32_t g, uint32_t total, uint32_
 // CTA owns an equal contiguous share of that list, so its TMA ring never drains between planes
 // and no wave of CTAs ends with idle SMs. A share covers parts of a few planes ("segments"); for
 // each segment the consumers rebuild the query digits, run the tiles, merge their four running
-// (max, sum, context) triples and store one partial; decode_attention_combine_kernel merges the
-// partials of the CTAs that shared a plane.
+// (max, sum, context) triples, and either write the plane's result (the CTA had the whole plane)
+// or store a partial and count in on the plane's arrival counter; the CTA that counts in last
+// merges the plane's partials. Nobody waits for anybody: a CTA that is not last simply goes on.
 __global__ void __launch_bounds__(FA_THREADS, HOLO_ATTN_MINB)
 decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                            const __grid_constant__ CUtensorMap map_ks, const __grid_constant__ CUtensorMap map_vs,
@@ -167,6 +211,8 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     float* s_cq = reinterpret_cast<float*>(sm + SMEM_MISC);            // [4]
     uint32_t* s_bad = reinterpret_cast<uint32_t*>(sm + SMEM_MISC + 16);  // [4]
     volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(sm + SMEM_MISC + 32);
+    uint32_t* s_fast = reinterpret_cast<uint32_t*>(sm + SMEM_MISC + 36);
+    uint32_t* s_last = reinterpret_cast<uint32_t*>(sm + SMEM_MISC + 192);  // [9]
     float* s_red = reinterpret_cast<float*>(sm + SMEM_MISC + 64);       // [4 warps][4 heads]
     const uint32_t bar_full = base + SMEM_MISC + 128, bar_empty = bar_full + 8 * STAGES;
     float* mo = reinterpret_cast<float*>(sm + SMEM_MERGE);  // [warp][head][HD]
@@ -266,9 +312,15 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     uint32_t it = 0;
     bool aborted = false;
     uint32_t gt = g0;
+    uint32_t npend = 0, pend_plane[2], pend_first[2], pend_last[2], pend_sharers[2], pend_before[2];  // thread 0 only
     while (gt < g1) {
         const uint32_t plane = gt / T;
         const uint32_t seg_end = min(g1, (plane + 1) * T);
+        // the plane's first sharer looks at the arrival counter now and uses the value when the
+        // segment ends, so the round trip is hidden behind the segment's tiles
+        uint32_t probe = 0;
+        if (tid == 0 && fa_owner(plane * T, total, nctas) == cta && fa_owner(plane * T + T - 1, total, nctas) != cta)
+            asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(probe) : "l"(p.arrivals + plane) : "memory");
         // ---- query digits of this plane: q = (L0*65536 + L1*256 + L2) * 2^(ex-21), one row of
         // the m16 tile per (head, digit): rows g, 4+g, 8+g hold L0, L1, L2 of head g; rows 12.. zero.
         {
@@ -453,7 +505,7 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             if (lane == 0 && !aborted) mbar_arrive(bar_empty + 8 * s);
         }
         fold();
-        // ---- merge the four warps' triples and store this segment's partial ----
+        // ---- merge the four warps' triples; finish the plane or publish this segment's partial ----
         l_sum += __shfl_xor_sync(0xffffffffu, l_sum, 1);
         l_sum += __shfl_xor_sync(0xffffffffu, l_sum, 2);
 #pragma unroll
@@ -468,67 +520,106 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 mml[(warp * MAXG + g) * 2 + 1] = l_sum;
             }
         }
+        // CTAs first..last hold parts of this plane; those with a non-empty share are its sharers
+        const uint32_t first = fa_owner(plane * T, total, nctas), last = fa_owner(plane * T + T - 1, total, nctas);
+        uint32_t sharers = last - first + 1;
+        if (nctas > total) {
+            sharers = 0;
+            for (uint32_t cc = first; cc <= last; ++cc) sharers += fa_start(cc, total, nctas) != fa_start(cc + 1, total, nctas);
+        }
+        if (tid == 0) *s_fast = sharers > 1 && cta == first && probe + 1 == sharers;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (!aborted && !*s_abort) {
-            const uint32_t slot = cta - fa_owner(plane * T, total, nctas);
+            // CTAs first..last share this plane; each but one stores a partial and counts in on the
+            // plane's arrival counter, and one CTA merges. The first sharer reaches its part last
+            // (it is the tail of its share), so it normally finds everybody else counted in (the
+            // probe taken when the segment began) and merges their partials on top of its own
+            // triple without a round trip of its own. Otherwise it publishes like the others, and
+            // whoever counts in last merges. Either way the merge runs over the slots in order on
+            // the same f32 values, so the result does not depend on who merged.
             const uint32_t c = tid;  // 0..127
-            for (uint32_t gg = 0; gg < G; ++gg) {
-                float M = -INFINITY;
+            float M[MAXG], L[MAXG], O[MAXG];
 #pragma unroll
-                for (int w = 0; w < CONSUMER_WARPS; ++w) M = fmaxf(M, mml[(w * MAXG + gg) * 2]);
-                float L = 0.0f, O = 0.0f;
+            for (int gg = 0; gg < MAXG; ++gg) {
+                M[gg] = -INFINITY;
+                L[gg] = 0.0f;
+                O[gg] = 0.0f;
+                if ((uint32_t)gg < G) {
 #pragma unroll
-                for (int w = 0; w < CONSUMER_WARPS; ++w) {
-                    float wm = mml[(w * MAXG + gg) * 2];
-                    if (wm != -INFINITY) {
-                        float f = exp2f((wm - M) * LOG2E);
-                        L = fmaf(mml[(w * MAXG + gg) * 2 + 1], f, L);
-                        O = fmaf(mo[(w * MAXG + gg) * HD + c], f, O);
+                    for (int w = 0; w < CONSUMER_WARPS; ++w) M[gg] = fmaxf(M[gg], mml[(w * MAXG + gg) * 2]);
+#pragma unroll
+                    for (int w = 0; w < CONSUMER_WARPS; ++w) {
+                        float wm = mml[(w * MAXG + gg) * 2];
+                        if (wm != -INFINITY) {
+                            float f = exp2f((wm - M[gg]) * LOG2E);
+                            L[gg] = fmaf(mml[(w * MAXG + gg) * 2 + 1], f, L[gg]);
+                            O[gg] = fmaf(mo[(w * MAXG + gg) * HD + c], f, O[gg]);
+                        }
                     }
+                    if (s_bad[gg]) { O[gg] = NAN; L[gg] = 1.0f; M[gg] = 0.0f; }
                 }
-                if (s_bad[gg]) { O = NAN; L = 1.0f; M = 0.0f; }
-                const uint64_t pidx = ((uint64_t)plane * p.max_slots + slot) * MAXG + gg;
-                p.part_o[pidx * HD + c] = O;
-                if (c == 0) {
-                    p.part_ml[pidx * 2] = M;
-                    p.part_ml[pidx * 2 + 1] = L;
+            }
+            if (sharers == 1) {
+#pragma unroll
+                for (int gg = 0; gg < MAXG; ++gg)
+                    if ((uint32_t)gg < G)
+                        holo::store_float(p.out, ((uint64_t)plane * G + gg) * HD + c, O[gg] / fmaxf(L[gg], 1e-30f), p.dtype);
+            } else if (*s_fast) {
+                // the probe was an acquire load by thread 0 and a barrier lies between it and here,
+                // so the others' partials are visible to every thread of the CTA (read from L2)
+                merge_slots(p, plane, first, 1, last - first + 1, total, nctas, G, c, M, L, O);
+                if (tid == 0) p.arrivals[plane] = 0;  // everybody else has counted in: ready for the next launch
+            } else {
+                const uint32_t slot = cta - first;
+#pragma unroll
+                for (int gg = 0; gg < MAXG; ++gg)
+                    if ((uint32_t)gg < G) {
+                        const uint64_t pidx = ((uint64_t)plane * p.max_slots + slot) * MAXG + gg;
+                        p.part_o[pidx * HD + c] = O[gg];
+                        if (c == 0) *reinterpret_cast<float2*>(p.part_ml + pidx * 2) = make_float2(M[gg], L[gg]);
+                    }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (tid == 0 && npend < 2) {
+                    // the count comes back while the next segment streams; it is read at the end
+                    pend_before[npend] = atomicAdd(p.arrivals + plane, 1u);
+                    pend_plane[npend] = plane;
+                    pend_first[npend] = first;
+                    pend_last[npend] = last;
+                    pend_sharers[npend] = sharers;
+                    ++npend;
                 }
             }
         }
         // the merge area, the digit tile and s_red are rewritten by the next segment
         asm volatile("bar.sync 1, 128;" ::: "memory");
     }
-}
 
-// Merge the partials of the CTAs that shared one plane, per (plane, head):
-// out = sum_s O_s e^(m_s - M) / sum_s l_s e^(m_s - M).
-__global__ void __launch_bounds__(HD)
-decode_attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, void* out,
-                                const uint32_t* __restrict__ valid_len, uint32_t past, uint32_t planes, uint32_t nctas,
-                                uint32_t max_slots, uint32_t G, int dtype) {
-    const uint32_t plane = blockIdx.x / G, gg = blockIdx.x % G, c = threadIdx.x;
-    const uint32_t vis_past = min(*valid_len, past);
-    const uint32_t T = (vis_past + TK - 1) / TK + 1, total = planes * T;
-    const uint32_t first = fa_owner(plane * T, total, nctas), last = fa_owner(plane * T + T - 1, total, nctas);
-    const uint32_t slots = last - first + 1;
-    // a CTA whose share of the list is empty (more CTAs than tiles) wrote nothing: skip its slot
-    float M = -INFINITY;
-    for (uint32_t s = 0; s < slots; ++s) {
-        if (fa_start(first + s, total, nctas) == fa_start(first + s + 1, total, nctas)) continue;
-        M = fmaxf(M, part_ml[(((uint64_t)plane * max_slots + s) * MAXG + gg) * 2]);
-    }
-    float L = 0.0f, O = 0.0f;
-    for (uint32_t s = 0; s < slots; ++s) {
-        if (fa_start(first + s, total, nctas) == fa_start(first + s + 1, total, nctas)) continue;
-        const uint64_t pidx = ((uint64_t)plane * max_slots + s) * MAXG + gg;
-        const float wm = part_ml[pidx * 2];
-        if (wm != -INFINITY) {
-            const float f = exp2f((wm - M) * LOG2E);
-            L = fmaf(part_ml[pidx * 2 + 1], f, L);
-            O = fmaf(part_o[pidx * HD + c], f, O);
+    // ---- a CTA that counted in last on a plane merges that plane's partials ----
+    if (tid == 0) {
+        s_last[0] = s_last[1] = 0;
+        s_last[2] = npend;
+        for (uint32_t k = 0; k < npend; ++k) {
+            const uint32_t is_last = pend_before[k] + 1 == pend_sharers[k];
+            if (is_last) p.arrivals[pend_plane[k]] = 0;
+            s_last[k] = is_last;
+            s_last[3 + 3 * k] = pend_plane[k];
+            s_last[4 + 3 * k] = pend_first[k];
+            s_last[5 + 3 * k] = pend_last[k];
         }
+        __threadfence();  // acquire side of the counts read above, for the whole CTA through the barrier
     }
-    holo::store_float(out, ((uint64_t)plane * G + gg) * HD + c, O / fmaxf(L, 1e-30f), dtype);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (aborted || *s_abort) return;
+    const uint32_t n_published = s_last[2];
+    for (uint32_t k = 0; k < n_published; ++k) {
+        if (!s_last[k]) continue;
+        const uint32_t plane = s_last[3 + 3 * k], first = s_last[4 + 3 * k], last = s_last[5 + 3 * k];
+        float M[MAXG], L[MAXG], O[MAXG];
+#pragma unroll
+        for (int gg = 0; gg < MAXG; ++gg) { M[gg] = -INFINITY; L[gg] = 0.0f; O[gg] = 0.0f; }
+        merge_slots(p, plane, first, 0, last - first + 1, total, nctas, G, tid, M, L, O);
+    }
 }
 
 // ---- host side --------------------------------------------------------------------------------
@@ -631,6 +722,7 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a) 
     p.part_o = (float*)ctx->scratch;
     p.part_ml = (float*)((uint8_t*)ctx->scratch + po_bytes);
     p.status = ctx->dev_status;
+    p.arrivals = ctx->attn_arrivals;
     p.past = a.past;
     p.G = G;
     p.planes = planes;
@@ -640,10 +732,6 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a) 
     p.dtype = a.dtype;
     p.debug_skip = getenv("HOLO_ATTN_DEBUG_SKIP") ? 1 : 0;
     decode_attention_q8_kernel<<<nctas, FA_THREADS, SMEM_TOTAL, ctx->stream>>>(mk, mv, mks, mvs, p);
-    HOLO_CUDA(cudaGetLastError());
-    ctx->launches++;
-    decode_attention_combine_kernel<<<planes * G, HD, 0, ctx->stream>>>(p.part_o, p.part_ml, a.out, a.valid_len, a.past, planes, nctas,
-                                                                        max_slots, G, a.dtype);
     HOLO_CUDA(cudaGetLastError());
     ctx->launches++;
     return HOLO_OK;
@@ -658,7 +746,8 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a) 
 // the process exits.
 constexpr uint64_t STATIC_SCRATCH_BYTES = 16ull << 20;
 static __device__ __align__(256) unsigned char g_attn_static_scratch[STATIC_SCRATCH_BYTES];
-static __device__ __align__(256) uint32_t g_attn_static_status[64];
+// word 0: status; words 64..: one arrival counter per plane (at most 65535 planes)
+static __device__ __align__(256) uint32_t g_attn_static_status[64 + 65536];
 
 namespace {
 struct StaticDevice {
@@ -728,9 +817,10 @@ extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const
     HOLO_TRY(make_codes_map(&mv, v_past, past_len, planes, box_rows));
     HOLO_TRY(make_scales_map(&mks, k_past_scales, past_len, planes, box_rows));
     HOLO_TRY(make_scales_map(&mvs, v_past_scales, past_len, planes, box_rows));
-    // The status word must start at zero (a CTA that sees bit 1 set does not start); the
-    // partials need no clearing: every (plane, split) slot the merge reads is rewritten first.
-    HOLO_CUDA(cudaMemsetAsync(sd.status, 0, sizeof(uint32_t), stream));
+    // The status word and the planes' arrival counters must start at zero (a CTA that sees
+    // status bit 1 set does not start; a launch that gave up may have left counters behind). The
+    // partials need no clearing: every (plane, slot) the merge reads is rewritten first.
+    HOLO_CUDA(cudaMemsetAsync(sd.status, 0, (64 + (size_t)planes) * sizeof(uint32_t), stream));
     FaParams p;
     p.q = q;
     p.k_new = k_new;
@@ -742,6 +832,7 @@ extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const
     p.part_o = (float*)sd.scratch;
     p.part_ml = (float*)((uint8_t*)sd.scratch + po_bytes);
     p.status = sd.status;
+    p.arrivals = sd.status + 64;
     p.past = past_len;
     p.G = G;
     p.planes = planes;
@@ -751,8 +842,6 @@ extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const
     p.dtype = dtype;
     p.debug_skip = 0;
     decode_attention_q8_kernel<<<nctas, FA_THREADS, SMEM_TOTAL, stream>>>(mk, mv, mks, mvs, p);
-    HOLO_CUDA(cudaGetLastError());
-    decode_attention_combine_kernel<<<planes * G, HD, 0, stream>>>(p.part_o, p.part_ml, out, valid_len, past_len, planes, nctas, max_slots, G, dtype);
     HOLO_CUDA(cudaGetLastError());
     return HOLO_OK;
 }

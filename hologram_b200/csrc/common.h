@@ -40,6 +40,7 @@ struct holo_b200_ctx {
     uint64_t stage_bytes = 0;
     // device-side error word (bounded waits record where they gave up)
     uint32_t* dev_status = nullptr;
+    uint32_t* attn_arrivals = nullptr;  // 65536 counters, zero between launches (decode attention)
     // set by a session while it records a batch: launchers append here instead of launching
     std::vector<HoloMicroOp>* record = nullptr;
     bool record_failed = false;
