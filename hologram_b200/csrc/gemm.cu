@@ -11,9 +11,11 @@
 //   warp 1   tcgen05.mma issuer (one elected lane), accumulator in TMEM (128 lanes x BN columns);
 //            tcgen05.commit releases ring slots and signals the epilogue
 //   warps 2-5 epilogue: tcgen05.ld the accumulator rows, narrow, epilogue op, store
-// Skinny problems (few output tiles) split K across CTAs: f32 partial tiles go to scratch (they
-// stay in L2) and a second kernel sums them in split order and applies the epilogue (one
-// truncation, as the reference).  Every mbarrier wait is bounded; a wait that gives up raises a status bit, and
+// Skinny problems (few output tiles) split K across the CTAs of a thread-block cluster (up to 8
+// along grid z): every CTA parks its f32 accumulator tile in its own shared memory, and after a
+// cluster barrier CTA r sums rows r, r + S, ... of the tile over all S CTAs through distributed
+// shared memory, in split order, and applies the epilogue (one truncation, as the reference).
+// No partial ever goes to global memory and there is no second launch. Every mbarrier wait is bounded; a wait that gives up raises a status bit, and
 // the CTA still frees its TMEM before it exits.
 #include <cuda.h>
 #include <stdlib.h>
@@ -42,7 +44,6 @@ constexpr int MAX_SEGS = 3;
 struct GemmParams {
     GemmSeg seg[MAX_SEGS];
     uint32_t nseg;
-    float* partial;           // [splits][m][n] f32 (split-K)
     uint32_t* status;
     uint32_t m, n, k, kblocks, splits, box_m;
 };
@@ -211,7 +212,6 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         // ---------------- epilogue warps (TMEM lane quarter = warp % 4) ----------------
         const uint32_t quarter = warp & 3u;
         const uint32_t row = m0 + quarter * 32 + lane;
-        const uint32_t epi_tid = threadIdx.x - 64;
         if (nkb != 0) mbar_wait(bar_accum, 0, s_abort, p.status);
         asm volatile("bar.sync 1, 128;" ::: "memory");   // all four epilogue warps see the same abort state
         const bool ok = !*s_abort;
@@ -247,27 +247,81 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 }
             }
         } else if (ok) {
-            // split-K: store this CTA's f32 partial tile; a second kernel sums the partials in split
-            // order and applies the epilogue (one truncation).
+            // split-K: park this CTA's f32 accumulator rows in the (now idle) ring; 16-byte units of a
+            // row are XOR-swizzled with the row number so that the 32 rows of a warp do not hit one bank
+            const uint32_t row_local = quarter * 32 + lane;
+            if (m0 + quarter * 32 < p.m) {  // warp-uniform: the TMEM load is a whole-warp instruction
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((quarter * 32u) << 16) + (uint32_t)(c * 32), v);
-                const uint32_t col0 = n0 + c * 32;
-                if (row < p.m && col0 < p.n) {
-                    float* dst = p.partial + ((uint64_t)split * p.m + row) * p.n + col0;
-                    if (col0 + 32 <= p.n) {
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((quarter * 32u) << 16) + (uint32_t)(c * 32), v);
+                    if (row < p.m) {
 #pragma unroll
-                        for (int x = 0; x < 8; ++x)
-                            reinterpret_cast<uint4*>(dst)[x] = make_uint4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
-                    } else {
-#pragma unroll
-                        for (int x = 0; x < 32; ++x)
-                            if (col0 + x < p.n) dst[x] = __uint_as_float(v[x]);
+                        for (int x = 0; x < 8; ++x) {
+                            const uint32_t unit = (uint32_t)(c * 8 + x) ^ (row_local & 7u);
+                            *reinterpret_cast<uint4*>(sm + (size_t)row_local * (BN * 4) + unit * 16) =
+                                make_uint4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
+                        }
                     }
                 }
             }
         }
+    }
+    if (p.splits > 1) {
+        // ---- cluster reduction (all threads of all CTAs of the cluster pass both barriers) ----
+        __syncwarp();  // the single-lane producer / issuer loops rejoin their warps first
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (warp >= 2 && !*s_abort) {
+            const uint32_t rank = split, S_ = p.splits, ew = warp - 2;
+            const uint32_t rows_valid = min(p.m - m0, (uint32_t)BM);
+            uint32_t remote[8];
+#pragma unroll
+            for (uint32_t sidx = 0; sidx < 8; ++sidx) {
+                remote[sidx] = 0;
+                if (sidx < S_) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[sidx]) : "r"(base), "r"(sidx));
+            }
+            for (uint32_t rl = rank + S_ * ew; rl < rows_valid; rl += S_ * 4) {
+                for (uint32_t u = lane; u < BN / 4; u += 32) {
+                    const uint32_t off = rl * (BN * 4) + ((u ^ (rl & 7u)) * 16);
+                    float4 part[8];
+#pragma unroll
+                    for (uint32_t sidx = 0; sidx < 8; ++sidx) {
+                        part[sidx] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (sidx < S_)
+                            asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(part[sidx].x), "=f"(part[sidx].y), "=f"(part[sidx].z), "=f"(part[sidx].w)
+                                         : "r"(remote[sidx] + off));
+                    }
+                    float4 acc = part[0];
+#pragma unroll
+                    for (uint32_t sidx = 1; sidx < 8; ++sidx)
+                        if (sidx < S_) { acc.x += part[sidx].x; acc.y += part[sidx].y; acc.z += part[sidx].z; acc.w += part[sidx].w; }
+                    const uint32_t col = n0 + u * 4, grow = m0 + rl;
+                    if (col < p.n) {
+                        uint32_t si = 0;
+                        while (si + 1 < p.nseg && col >= p.seg[si].col_end) ++si;
+                        const GemmSeg sg = p.seg[si];
+                        const uint64_t idx = (uint64_t)grow * (sg.col_end - sg.col_begin) + (col - sg.col_begin);
+                        uint16_t* dst = sg.out + idx;
+                        const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+                        if (col + 4 <= sg.col_end && ((uintptr_t)dst & 7u) == 0) {
+                            uint16_t h[4];
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) h[x] = epilogue_elem(a4[x], sg.table, sg.residual, idx + x);
+                            *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+                        } else {
+#pragma unroll
+                            for (int x = 0; x < 4; ++x)
+                                if (col + x < sg.col_end) dst[x] = epilogue_elem(a4[x], sg.table, sg.residual, idx + x);
+                        }
+                    }
+                }
+            }
+        }
+        // nobody leaves (and frees its shared memory) while a neighbour may still read it
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     // everyone meets here, whatever happened above, so that TMEM is always released
     __syncwarp();  // the single-lane producer / issuer loops rejoin their warps first
@@ -279,36 +333,6 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
 }
 
-
-// Sum the split-K partial tiles in split order, then the epilogue (one truncation). Four
-// consecutive columns per thread (segment boundaries are multiples of 32, n of 8).
-struct ReduceParams {
-    GemmSeg seg[MAX_SEGS];
-    uint32_t nseg, splits, n;
-    uint64_t mn;
-};
-__global__ void splitk_reduce_kernel(const float* __restrict__ partial, const ReduceParams p) {
-    const uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (i >= p.mn) return;
-    float4 acc = *reinterpret_cast<const float4*>(partial + i);
-    for (uint32_t s = 1; s < p.splits; ++s) {
-        float4 v = *reinterpret_cast<const float4*>(partial + (uint64_t)s * p.mn + i);
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
-    const uint32_t row = (uint32_t)(i / p.n), col = (uint32_t)(i % p.n);
-    uint32_t si = 0;
-    while (si + 1 < p.nseg && col >= p.seg[si].col_end) ++si;
-    const GemmSeg sg = p.seg[si];
-    const uint64_t idx = (uint64_t)row * (sg.col_end - sg.col_begin) + (col - sg.col_begin);
-    uint16_t h0 = epilogue_elem(acc.x, sg.table, sg.residual, idx), h1 = epilogue_elem(acc.y, sg.table, sg.residual, idx + 1);
-    uint16_t h2 = epilogue_elem(acc.z, sg.table, sg.residual, idx + 2), h3 = epilogue_elem(acc.w, sg.table, sg.residual, idx + 3);
-    uint16_t* dst = sg.out + idx;
-    if (((uintptr_t)dst & 7u) == 0) {
-        *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)h0 | ((uint32_t)h1 << 16), (uint32_t)h2 | ((uint32_t)h3 << 16));
-    } else {
-        dst[0] = h0; dst[1] = h1; dst[2] = h2; dst[3] = h3;
-    }
-}
 
 // Shapes the tensor-core path cannot take (row pitches that are not 16-byte multiples,
 // unaligned bases) and tiny problems: one thread per output cell running the reference's
@@ -365,8 +389,19 @@ int32_t launch_umma(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap
         HOLO_CUDA(cudaFuncSetAttribute(matmul_bf16_umma_kernel<BN, STAGES, A_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
         configured_device = ctx->device;
     }
-    matmul_bf16_umma_kernel<BN, STAGES, A_ROWS><<<grid, GEMM_THREADS, S::TOTAL, ctx->stream>>>(ma, mb, p);
-    HOLO_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = p.splits;  // the K slices of one output tile form a cluster
+    cfg.attrs = attr;
+    cfg.numAttrs = p.splits > 1 ? 1 : 0;
+    HOLO_CUDA(cudaLaunchKernelEx(&cfg, matmul_bf16_umma_kernel<BN, STAGES, A_ROWS>, ma, mb, p));
     ctx->launches++;
     return HOLO_OK;
 }
@@ -431,8 +466,8 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     // One-row-tile shapes (decode) are HBM-bound: loaded HBM latency is 2-3 us, so 15-20 MB of
     // weight bytes must be in flight across the chip. Measured on B200: with >= ~200 128-wide
     // tiles, or >= one 64-wide tile per SM, no split is best (every CTA walks K in step with its
-    // neighbours, which keeps DRAM pages open); narrower outputs split K about 8 ways, partials stay
-    // in L2 and a second kernel reduces them.
+    // neighbours, which keeps DRAM pages open); narrower outputs split K up to 8 ways inside a
+    // thread-block cluster, which reduces the slices through distributed shared memory.
     int bn = 128;
     uint32_t splits = 1;
     const uint32_t tiles128 = mtiles * ((n + 127) / 128), tiles64 = mtiles * ((n + 63) / 64);
@@ -452,19 +487,15 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     if (const char* e = getenv("HOLO_GEMM_BN")) bn = atoi(e) == 64 ? 64 : atoi(e) == 256 ? 256 : 128;
     if (const char* e = getenv("HOLO_GEMM_SPLITS")) splits = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : 1;
     if (splits > kblocks) splits = kblocks;
+    if (splits > 8) splits = 8;  // one cluster (portable size) per output tile
     if (mtiles > 65535 || splits > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul grid too large");
 
     GemmParams p;
     for (uint32_t i = 0; i < MAX_SEGS; ++i) p.seg[i] = gs[i];
     p.nseg = nseg;
-    p.partial = nullptr;
     p.status = ctx->dev_status;
     p.m = m; p.n = n; p.k = k; p.kblocks = kblocks; p.splits = splits;
     p.box_m = m < (uint32_t)BM ? m : (uint32_t)BM;
-    if (splits > 1) {
-        HOLO_TRY(holo_ensure_scratch(ctx, (uint64_t)splits * m * n * 4));
-        p.partial = (float*)ctx->scratch;
-    }
     CUtensorMap ma, mb;
     HOLO_TRY(make_map_2d(&ma, a, k, m, BK, p.box_m));
     HOLO_TRY(make_map_2d(&mb, b, n, k, 64, BK));
@@ -481,19 +512,6 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
         if (m <= 16) HOLO_TRY((launch_umma<64, 9, 16>(ctx, ma, mb, p, grid)));
         else if (m <= 64) HOLO_TRY((launch_umma<64, 6, 64>(ctx, ma, mb, p, grid)));
         else HOLO_TRY((launch_umma<64, 4, 128>(ctx, ma, mb, p, grid)));
-    }
-    if (splits > 1) {
-        const uint64_t mn = (uint64_t)m * n;
-        const uint64_t blocks = (mn / 4 + 255) / 256 + 1;
-        ReduceParams rp;
-        for (uint32_t i = 0; i < MAX_SEGS; ++i) rp.seg[i] = gs[i];
-        rp.nseg = nseg;
-        rp.splits = splits;
-        rp.n = n;
-        rp.mn = mn;
-        splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p.partial, rp);
-        HOLO_CUDA(cudaGetLastError());
-        ctx->launches++;
     }
     return HOLO_OK;
 }

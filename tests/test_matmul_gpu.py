@@ -53,7 +53,7 @@ def test_small_and_odd_shapes_are_bit_exact(backend, m, k, n):
 
 @pytest.mark.parametrize("m,k,n", [
     (128, 64, 128), (128, 256, 256), (200, 192, 512), (64, 512, 1024), (16, 4096, 1024), (64, 4096, 4096),
-    (256, 1000 * 8, 136), (129, 72, 8 * 33), (1024, 1024, 1024),
+    (256, 1000 * 8, 136), (129, 72, 8 * 33), (1024, 1024, 1024), (40, 2048, 512), (100, 4096, 256), (64, 14336, 4096),
 ])
 def test_tensor_core_path_within_tolerance(backend, m, k, n):
     a, b = synth(m, k, n, m * 7 + n)
