@@ -7,6 +7,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <stdlib.h>
+
 #include "common.h"
 
 // ---- thread-local error state (hologram-ffi src/lib.rs:48-92 convention) --------------------
@@ -58,6 +60,7 @@ extern "C" int32_t holo_b200_ctx_create(int32_t device, holo_b200_ctx** out) {
         return holo_fail(HOLO_ERR_INIT, "backend init failed: cudaStreamCreate");
     }
     ctx->own_stream = true;
+    if (const char* e = getenv("HOLO_PDL")) ctx->pdl = atoi(e) != 0;
     if (cudaMalloc(&ctx->dev_status, 256) != cudaSuccess || cudaMemset(ctx->dev_status, 0, 256) != cudaSuccess) {
         cudaStreamDestroy(ctx->stream);
         delete ctx;

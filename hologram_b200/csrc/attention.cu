@@ -204,6 +204,8 @@ __global__ void __launch_bounds__(FA_THREADS, HOLO_ATTN_MINB)
 decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                            const __grid_constant__ CUtensorMap map_ks, const __grid_constant__ CUtensorMap map_vs,
                            const FaParams p) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -688,9 +690,9 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a) 
         if (rows > 0x7fffffffull) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: decode attention row count too large");
         const size_t smem = (size_t)holo_attn::GEN_WARPS * (a.d + 2) * sizeof(float);
         if (a.quantized)
-            holo_attn::decode_attention_generic_kernel<true><<<(unsigned)rows, holo_attn::GEN_WARPS * 32, smem, ctx->stream>>>(a);
+            HOLO_CUDA(holo_launch_kernel(ctx, holo_attn::decode_attention_generic_kernel<true>, dim3((unsigned)rows), dim3(holo_attn::GEN_WARPS * 32), smem, 1, a));
         else
-            holo_attn::decode_attention_generic_kernel<false><<<(unsigned)rows, holo_attn::GEN_WARPS * 32, smem, ctx->stream>>>(a);
+            HOLO_CUDA(holo_launch_kernel(ctx, holo_attn::decode_attention_generic_kernel<false>, dim3((unsigned)rows), dim3(holo_attn::GEN_WARPS * 32), smem, 1, a));
         HOLO_CUDA(cudaGetLastError());
         ctx->launches++;
         return HOLO_OK;
@@ -731,7 +733,7 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a) 
     p.scale_div = a.scale_div;
     p.dtype = a.dtype;
     p.debug_skip = getenv("HOLO_ATTN_DEBUG_SKIP") ? 1 : 0;
-    decode_attention_q8_kernel<<<nctas, FA_THREADS, SMEM_TOTAL, ctx->stream>>>(mk, mv, mks, mvs, p);
+    HOLO_CUDA(holo_launch_kernel(ctx, decode_attention_q8_kernel, dim3(nctas), dim3(FA_THREADS), SMEM_TOTAL, 1, mk, mv, mks, mvs, p));
     HOLO_CUDA(cudaGetLastError());
     ctx->launches++;
     return HOLO_OK;

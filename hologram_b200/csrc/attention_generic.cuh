@@ -27,6 +27,8 @@ __device__ __forceinline__ float kv_elem(const void* base, const float* scales, 
 template <bool Q8>
 __global__ void __launch_bounds__(GEN_WARPS * 32)
 decode_attention_generic_kernel(HoloAttnArgs a) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     extern __shared__ float s_mem[];  // [GEN_WARPS][d + 2]
     const uint32_t r = blockIdx.x;    // output row: (batch, head, query row)
     const uint32_t d = a.d, h = a.h, m = a.m, hkv = a.hkv;

@@ -41,6 +41,8 @@ struct holo_b200_ctx {
     // device-side error word (bounded waits record where they gave up)
     uint32_t* dev_status = nullptr;
     uint32_t* attn_arrivals = nullptr;  // 65536 counters, zero between launches (decode attention)
+    // launch every kernel with programmatic stream serialization (HOLO_PDL=0 turns it off)
+    bool pdl = true;
     // set by a session while it records a batch: launchers append here instead of launching
     std::vector<HoloMicroOp>* record = nullptr;
     bool record_failed = false;
@@ -110,6 +112,47 @@ struct HoloRefList {
 bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l);
 // Backend::dispatch body shared by the C entry points and the session walk.
 int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, holo_b200_workspace* ws);
+
+#ifdef __CUDACC__
+// Programmatic dependent launch. Every kernel of the library starts with holo_pdl_trigger()
+// ("my successor may be scheduled") and calls holo_pdl_wait() before its first access to global
+// memory ("my predecessor has finished and its writes are visible"). Launched through
+// holo_launch_kernel with the context's pdl flag set, a kernel's CTAs are then placed on SMs,
+// and run their prologue (barrier set-up, TMEM allocation), while the previous kernel drains,
+// instead of after it has fully retired; without the attribute both instructions do nothing.
+// Because every kernel waits before it reads or writes global memory, and completion of a
+// kernel implies completion of everything it waited for, ordering along the stream is kept.
+__device__ __forceinline__ void holo_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void holo_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// cluster_z > 1 makes grid z a thread-block cluster dimension.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t holo_launch_kernel(holo_b200_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                             unsigned cluster_z, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    unsigned na = 0;
+    if (ctx->pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (cluster_z > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = cluster_z;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 
 // ---- kernel launchers (each validates nothing: geometry is checked by the dispatcher) ------
 // lut.cu

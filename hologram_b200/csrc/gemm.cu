@@ -149,12 +149,14 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     const uint32_t kb_end = (uint32_t)(((uint64_t)p.kblocks * (split + 1)) / p.splits);
     const uint32_t nkb = kb_end - kb_begin;
 
+    holo_pdl_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_accum, 1);
+        holo_pdl_wait();  // the status word is the first thing read from global memory
         *s_abort = (*reinterpret_cast<volatile uint32_t*>(p.status) & 4u) ? 1u : 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -167,6 +169,7 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *s_tmem;
+    holo_pdl_wait();  // barriers and TMEM were set up while the previous kernel drained
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -341,6 +344,8 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 __global__ void matmul_bf16_cell_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, uint16_t* __restrict__ out,
                                         const uint16_t* __restrict__ table, const uint16_t* __restrict__ residual, uint32_t m,
                                         uint32_t k, uint32_t n) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x, i = blockIdx.y;
     if (j >= n || i >= m) return;
     const bool fused = j < n - (n % 8);
@@ -389,19 +394,8 @@ int32_t launch_umma(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap
         HOLO_CUDA(cudaFuncSetAttribute(matmul_bf16_umma_kernel<BN, STAGES, A_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
         configured_device = ctx->device;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(GEMM_THREADS);
-    cfg.dynamicSmemBytes = S::TOTAL;
-    cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = p.splits;  // the K slices of one output tile form a cluster
-    cfg.attrs = attr;
-    cfg.numAttrs = p.splits > 1 ? 1 : 0;
-    HOLO_CUDA(cudaLaunchKernelEx(&cfg, matmul_bf16_umma_kernel<BN, STAGES, A_ROWS>, ma, mb, p));
+    // the K slices of one output tile form a cluster along grid z
+    HOLO_CUDA(holo_launch_kernel(ctx, matmul_bf16_umma_kernel<BN, STAGES, A_ROWS>, grid, dim3(GEMM_THREADS), S::TOTAL, p.splits, ma, mb, p));
     ctx->launches++;
     return HOLO_OK;
 }
@@ -451,8 +445,8 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     if (!tma_ok || tiny || getenv("HOLO_GEMM_FORCE_CELL")) {
         dim3 grid((n + 127) / 128, m);
         if (m > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul m %u on the per-cell path", m);
-        matmul_bf16_cell_kernel<<<grid, 128, 0, ctx->stream>>>((const uint16_t*)a, (const uint16_t*)b, (uint16_t*)out, table,
-                                                            (const uint16_t*)residual, m, k, n);
+        HOLO_CUDA(holo_launch_kernel(ctx, matmul_bf16_cell_kernel, dim3(grid), dim3(128), 0, 1, (const uint16_t*)a, (const uint16_t*)b, (uint16_t*)out, table,
+                                                            (const uint16_t*)residual, m, k, n));
         HOLO_CUDA(cudaGetLastError());
         ctx->launches++;
         return HOLO_OK;

@@ -29,6 +29,8 @@ __device__ __forceinline__ void binary_body(int op, const void* __restrict__ a, 
 
 __global__ void binary_kernel(int op, const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ out,
                               uint64_t n, int dtype) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     binary_body(op, a, b, out, n, dtype, blockIdx.x, gridDim.x);
 }
 
@@ -54,6 +56,8 @@ __device__ __forceinline__ void binary16_vec_body(int op, const uint4* __restric
 }
 __global__ void binary16_vec_kernel(int op, const uint4* __restrict__ a, const uint4* __restrict__ b,
                                     uint4* __restrict__ out, uint64_t nvec, int dtype) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     binary16_vec_body(op, a, b, out, nvec, dtype, blockIdx.x, gridDim.x);
 }
 
@@ -61,6 +65,8 @@ __global__ void binary16_vec_kernel(int op, const uint4* __restrict__ a, const u
 // out = x * inv * gamma (left to right). One CTA per row.
 __global__ void rms_norm_kernel(const void* __restrict__ x, const void* __restrict__ gamma, void* __restrict__ out,
                                 uint32_t feature, float eps, int dtype) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     __shared__ float s_part[32];
     __shared__ float s_inv;
     const uint64_t off = (uint64_t)blockIdx.x * feature;
@@ -91,6 +97,8 @@ __global__ void rms_norm_kernel(const void* __restrict__ x, const void* __restri
 __global__ void __launch_bounds__(1024)
 rms_norm16_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gamma, uint4* __restrict__ out,
                       uint32_t feature, float eps, int dtype) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     __shared__ float s_part[32];
     __shared__ float s_inv;
     const uint32_t nvec = feature >> 3;
@@ -151,6 +159,8 @@ __device__ __forceinline__ void rope_body(const void* __restrict__ x, const void
 }
 __global__ void rope_kernel(const void* __restrict__ x, const void* __restrict__ c, const void* __restrict__ s,
                             void* __restrict__ out, uint32_t d, uint64_t n, int dtype) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     rope_body(x, c, s, out, d, n, dtype, blockIdx.x, gridDim.x);
 }
 
@@ -159,6 +169,8 @@ __global__ void rope_kernel(const void* __restrict__ x, const void* __restrict__
 __global__ void gather_kernel(const uint8_t* __restrict__ data, const void* __restrict__ idx, int idx_dtype,
                               uint8_t* __restrict__ out, uint64_t axis_dim, uint64_t row_bytes, uint64_t num_idx,
                               uint32_t* status) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     const uint64_t o = blockIdx.y, k = blockIdx.x;
     long long ix = idx_dtype == HOLO_DTYPE_I32 ? (long long)((const int32_t*)idx)[k] : ((const long long*)idx)[k];
     if (ix < 0) ix += (long long)axis_dim;
@@ -189,6 +201,8 @@ __device__ __forceinline__ double load_num(const void* p, uint64_t i, int dt) {
     }
 }
 __global__ void cast_kernel(const void* __restrict__ in, int src, void* __restrict__ out, int dst, uint64_t n) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     const bool src_f = src >= HOLO_DTYPE_F16 && src <= HOLO_DTYPE_F64;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -220,6 +234,8 @@ __global__ void cast_kernel(const void* __restrict__ in, int src, void* __restri
 __global__ void dequantize_kernel(const void* __restrict__ in, int qdt, const float* __restrict__ scales,
                                   const int32_t* __restrict__ zps, uint32_t channels, uint32_t inner, float scale,
                                   int32_t zp, void* __restrict__ out, int dtype, uint64_t n) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         int q = qdt == HOLO_DTYPE_I8 ? (int)((const int8_t*)in)[i] : (int)((const uint8_t*)in)[i];
@@ -238,6 +254,8 @@ __global__ void dequantize_kernel(const void* __restrict__ in, int qdt, const fl
 // `pos` is read on the device from its 4-byte operand (no host round-trip).
 __global__ void kv_write_rows_kernel(const uint8_t* __restrict__ newr, const uint32_t* __restrict__ pos,
                                      uint8_t* __restrict__ out, uint32_t bucket, uint32_t new_rows, uint32_t row_bytes) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     const uint32_t p = blockIdx.y, j = blockIdx.x;
     const uint32_t p0 = *pos % bucket;
     const uint8_t* src = newr + ((uint64_t)p * new_rows + j) * row_bytes;
@@ -301,6 +319,8 @@ __device__ __forceinline__ void quantize_rows_body(const void* __restrict__ x, i
 }
 __global__ void quantize_rows_kernel(const void* __restrict__ x, int dtype, uint64_t rows, uint32_t d,
                                      int8_t* __restrict__ codes, float* __restrict__ scales) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     quantize_rows_body(x, dtype, rows, d, codes, scales, blockIdx.x);
 }
 
@@ -350,6 +370,8 @@ __device__ __forceinline__ void quantize_rows16_vec_body(const uint16_t* __restr
 }
 __global__ void quantize_rows16_vec_kernel(const uint16_t* __restrict__ x, int dtype, uint64_t rows, uint32_t d,
                                            int8_t* __restrict__ codes, float* __restrict__ scales) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     quantize_rows16_vec_body(x, dtype, rows, d, codes, scales, blockIdx.x);
 }
 
@@ -358,6 +380,8 @@ __global__ void quantize_rows16_vec_kernel(const uint16_t* __restrict__ x, int d
 // runs of mutually independent glue calls (the trailing KV appends of all layers, the RoPE
 // pair, the K/V quantizer pair), whose individual launches cost more than their work.
 __global__ void __launch_bounds__(256) micro_batch_kernel(const HoloMicroOp* __restrict__ ops, uint32_t nops) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     uint32_t oi = 0;
     while (oi + 1 < nops && blockIdx.x >= ops[oi].cta_begin + ops[oi].cta_count) ++oi;
     const HoloMicroOp op = ops[oi];
@@ -388,7 +412,7 @@ __global__ void __launch_bounds__(256) micro_batch_kernel(const HoloMicroOp* __r
 
 int32_t holo_launch_micro_batch(holo_b200_ctx* ctx, const HoloMicroOp* dev_ops, uint32_t nops, uint32_t total_ctas) {
     if (nops == 0 || total_ctas == 0) return HOLO_OK;
-    micro_batch_kernel<<<total_ctas, 256, 0, ctx->stream>>>(dev_ops, nops);
+    HOLO_CUDA(holo_launch_kernel(ctx, micro_batch_kernel, dim3(total_ctas), dim3(256), 0, 1, dev_ops, nops));
     HOLO_CUDA(cudaGetLastError());
     ctx->launches++;
     return HOLO_OK;
@@ -425,10 +449,10 @@ int32_t holo_launch_binary(holo_b200_ctx* ctx, int op, const void* a, const void
         return HOLO_OK;
     }
     if (dtype != HOLO_DTYPE_F32 && aligned && (n % 8) == 0) {
-        binary16_vec_kernel<<<ew_blocks(n / 8), EW_THREADS, 0, ctx->stream>>>(op, (const uint4*)a, (const uint4*)b,
-                                                                             (uint4*)out, n / 8, dtype);
+        HOLO_CUDA(holo_launch_kernel(ctx, binary16_vec_kernel, dim3(ew_blocks(n / 8)), dim3(EW_THREADS), 0, 1, op, (const uint4*)a, (const uint4*)b,
+                                                                             (uint4*)out, n / 8, dtype));
     } else {
-        binary_kernel<<<ew_blocks(n), EW_THREADS, 0, ctx->stream>>>(op, a, b, out, n, dtype);
+        HOLO_CUDA(holo_launch_kernel(ctx, binary_kernel, dim3(ew_blocks(n)), dim3(EW_THREADS), 0, 1, op, a, b, out, n, dtype));
     }
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
@@ -441,9 +465,9 @@ int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* gamm
                      (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)out) & 15u) == 0;
     if (vec) {
         uint32_t threads = ((feature / 8 + 31) / 32) * 32;
-        rms_norm16_vec_kernel<<<batch, threads, 0, ctx->stream>>>((const uint4*)x, (const uint4*)gamma, (uint4*)out, feature, eps, dtype);
+        HOLO_CUDA(holo_launch_kernel(ctx, rms_norm16_vec_kernel, dim3(batch), dim3(threads), 0, 1, (const uint4*)x, (const uint4*)gamma, (uint4*)out, feature, eps, dtype));
     } else {
-        rms_norm_kernel<<<batch, 256, 0, ctx->stream>>>(x, gamma, out, feature, eps, dtype);
+        HOLO_CUDA(holo_launch_kernel(ctx, rms_norm_kernel, dim3(batch), dim3(256), 0, 1, x, gamma, out, feature, eps, dtype));
     }
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
@@ -459,7 +483,7 @@ int32_t holo_launch_rope(holo_b200_ctx* ctx, const void* x, const void* c, const
         record_op(ctx, m, ew_blocks(n));
         return HOLO_OK;
     }
-    rope_kernel<<<ew_blocks(n), EW_THREADS, 0, ctx->stream>>>(x, c, s, out, head_dim, n, dtype);
+    HOLO_CUDA(holo_launch_kernel(ctx, rope_kernel, dim3(ew_blocks(n)), dim3(EW_THREADS), 0, 1, x, c, s, out, head_dim, n, dtype));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }
@@ -469,14 +493,14 @@ int32_t holo_launch_gather(holo_b200_ctx* ctx, const uint8_t* data, const void* 
     if (outer == 0 || num_idx == 0 || inner_bytes == 0) return HOLO_OK;
     if (outer > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "gather: outer %llu exceeds 65535", (unsigned long long)outer);
     dim3 grid((unsigned)num_idx, (unsigned)outer);
-    gather_kernel<<<grid, 128, 0, ctx->stream>>>(data, idx, idx_dtype, out, axis_dim, inner_bytes, num_idx, ctx->dev_status);
+    HOLO_CUDA(holo_launch_kernel(ctx, gather_kernel, dim3(grid), dim3(128), 0, 1, data, idx, idx_dtype, out, axis_dim, inner_bytes, num_idx, ctx->dev_status));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }
 
 int32_t holo_launch_cast(holo_b200_ctx* ctx, const void* in, uint8_t src, void* out, uint8_t dst, uint64_t n) {
     if (n == 0) return HOLO_OK;
-    cast_kernel<<<ew_blocks(n), EW_THREADS, 0, ctx->stream>>>(in, src, out, dst, n);
+    HOLO_CUDA(holo_launch_kernel(ctx, cast_kernel, dim3(ew_blocks(n)), dim3(EW_THREADS), 0, 1, in, src, out, dst, n));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }
@@ -487,9 +511,9 @@ int32_t holo_launch_dequantize(holo_b200_ctx* ctx, const HoloDequantizeCall& c, 
     float scale;
     uint32_t sb = c.scale_bits;
     memcpy(&scale, &sb, 4);
-    dequantize_kernel<<<ew_blocks(c.element_count), EW_THREADS, 0, ctx->stream>>>(
+    HOLO_CUDA(holo_launch_kernel(ctx, dequantize_kernel, dim3(ew_blocks(c.element_count)), dim3(EW_THREADS), 0, 1, 
         in, c.quant_dtype, scales, zps, c.channels, c.inner ? c.inner : 1, scale, c.zero_point, out, c.dtype,
-        c.element_count);
+        c.element_count));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }
@@ -513,7 +537,7 @@ int32_t holo_launch_kv_write(holo_b200_ctx* ctx, const uint8_t* cache, const uin
     if (new_rows == 0) return HOLO_OK;
     if (planes > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "kv_cache_write: planes %u exceeds 65535", planes);
     dim3 grid(new_rows, planes);
-    kv_write_rows_kernel<<<grid, 32, 0, ctx->stream>>>(newr, pos, out, bucket, new_rows, row_bytes);
+    HOLO_CUDA(holo_launch_kernel(ctx, kv_write_rows_kernel, dim3(grid), dim3(32), 0, 1, newr, pos, out, bucket, new_rows, row_bytes));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }
@@ -533,9 +557,9 @@ int32_t holo_launch_quantize_rows(holo_b200_ctx* ctx, const void* x, uint8_t dty
         return HOLO_OK;
     }
     if (vec)
-        quantize_rows16_vec_kernel<<<(unsigned)blocks, warps * 32, 0, ctx->stream>>>((const uint16_t*)x, dtype, rows, d, codes, scales);
+        HOLO_CUDA(holo_launch_kernel(ctx, quantize_rows16_vec_kernel, dim3((unsigned)blocks), dim3(warps * 32), 0, 1, (const uint16_t*)x, dtype, rows, d, codes, scales));
     else
-        quantize_rows_kernel<<<(unsigned)blocks, warps * 32, 0, ctx->stream>>>(x, dtype, rows, d, codes, scales);
+        HOLO_CUDA(holo_launch_kernel(ctx, quantize_rows_kernel, dim3((unsigned)blocks), dim3(warps * 32), 0, 1, x, dtype, rows, d, codes, scales));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }

@@ -11,6 +11,8 @@ namespace {
 
 // table[bits] = narrow(f(widen(bits))), one thread per bit pattern (cpu/lut.rs:43-67).
 __global__ void build_table_kernel(uint16_t* table, int act, int dtype) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     uint32_t bits = blockIdx.x * blockDim.x + threadIdx.x;
     if (bits >= 65536u) return;
     float x = holo::widen16((uint16_t)bits, dtype);
@@ -84,6 +86,7 @@ lut_stream_kernel(const uint16_t* __restrict__ table, const uint16_t* __restrict
     const uint64_t first = (uint64_t)blockIdx.x * LUT_TILE_VEC;
     const uint64_t step = (uint64_t)gridDim.x * LUT_TILE_VEC;
 
+    holo_pdl_trigger();
     if (threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_tab));
         for (int s = 0; s < LUT_STAGES; ++s) {
@@ -93,6 +96,7 @@ lut_stream_kernel(const uint16_t* __restrict__ table, const uint16_t* __restrict
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    holo_pdl_wait();  // nothing above touches global memory
 
     if (warp == LUT_WARPS) {
         if (lane != 0) return;
@@ -157,6 +161,8 @@ lut_stream_kernel(const uint16_t* __restrict__ table, const uint16_t* __restrict
 // Small or unaligned inputs: gather straight from the global table (L1/L2 resident).
 __global__ void lut_gather_kernel(const uint16_t* __restrict__ table, const uint16_t* __restrict__ in,
                                   uint16_t* __restrict__ out, uint64_t n) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (; i < n; i += stride) out[i] = __ldg(table + in[i]);
@@ -165,6 +171,8 @@ __global__ void lut_gather_kernel(const uint16_t* __restrict__ table, const uint
 // Aligned, medium-size inputs: one 128-bit vector per thread, table read through L1.
 __global__ void lut_gather_vec_kernel(const uint16_t* __restrict__ table, const uint16_t* __restrict__ in,
                                       uint16_t* __restrict__ out, uint64_t n) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
     const uint64_t nvec = n >> 3;
     uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < nvec) {
@@ -193,8 +201,7 @@ int32_t holo_lut_table(holo_b200_ctx* ctx, uint8_t act, uint8_t dtype, const uin
     if (!ctx->lut[act][di]) {
         uint16_t* t = nullptr;
         HOLO_CUDA(cudaMalloc(&t, TABLE_BYTES));
-        build_table_kernel<<<65536 / 256, 256, 0, ctx->stream>>>(t, act, dtype);
-        cudaError_t e = cudaGetLastError();
+        cudaError_t e = holo_launch_kernel(ctx, build_table_kernel, dim3(65536 / 256), dim3(256), 0, 1, t, (int)act, (int)dtype);
         if (e != cudaSuccess) {
             cudaFree(t);
             return holo_cuda_fail(e, "build_table_kernel");
@@ -218,14 +225,14 @@ int32_t holo_launch_lut(holo_b200_ctx* ctx, const uint16_t* table, const uint16_
         }
         uint64_t want = (nvec + LUT_TILE_VEC - 1) / LUT_TILE_VEC;
         int grid = (int)(want < (uint64_t)ctx->sm_count ? want : (uint64_t)ctx->sm_count);
-        lut_stream_kernel<<<grid, (LUT_WARPS + 1) * 32, LUT_SMEM, ctx->stream>>>(table, in, out, n, ctx->dev_status);
+        HOLO_CUDA(holo_launch_kernel(ctx, lut_stream_kernel, dim3(grid), dim3((LUT_WARPS + 1) * 32), LUT_SMEM, 1, table, in, out, n, ctx->dev_status));
     } else if (aligned && nvec > 0) {
         uint64_t blocks = (nvec + 255) / 256;
-        lut_gather_vec_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(table, in, out, n);
+        HOLO_CUDA(holo_launch_kernel(ctx, lut_gather_vec_kernel, dim3((unsigned)blocks), dim3(256), 0, 1, table, in, out, n));
     } else {
         uint64_t blocks = (n + 255) / 256;
         if (blocks > 65535ull * 16) blocks = 65535ull * 16;
-        lut_gather_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(table, in, out, n);
+        HOLO_CUDA(holo_launch_kernel(ctx, lut_gather_kernel, dim3((unsigned)blocks), dim3(256), 0, 1, table, in, out, n));
     }
     HOLO_CUDA(cudaGetLastError());
     ctx->launches++;
