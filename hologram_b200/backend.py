@@ -63,6 +63,7 @@ def _load():
         "holo_b200_dispatch_host": (i32, [vp, C.POINTER(kc.KernelCall), C.POINTER(kc.HostSlot), u32]),
         "holo_b200_nccl_unique_id": (i32, [vp]),
         "holo_b200_ctx_init_tp": (i32, [vp, vp, i32, i32]),
+        "holo_b200_ctx_tp_transport": (i32, [vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -79,7 +80,7 @@ EXPORTED_SYMBOLS = [
     "holo_b200_workspace_create", "holo_b200_workspace_destroy", "holo_b200_workspace_alloc",
     "holo_b200_workspace_bind", "holo_b200_workspace_slot", "holo_b200_workspace_upload",
     "holo_b200_workspace_download", "holo_b200_dispatch", "holo_b200_dispatch_host", "holo_b200_nccl_unique_id",
-    "holo_b200_ctx_init_tp",
+    "holo_b200_ctx_init_tp", "holo_b200_ctx_tp_transport",
 ]
 
 
@@ -144,6 +145,11 @@ class B200Backend:
     def init_tp(self, unique_id, rank, world):
         buf = (C.c_uint8 * 128).from_buffer_copy(bytes(unique_id))
         _check(lib.holo_b200_ctx_init_tp(self._h, buf, rank, world))
+
+    @property
+    def tp_transport(self):
+        """0 = no tensor-parallel group, 1 = NCCL, 2 = the one-shot peer-memory kernel."""
+        return int(lib.holo_b200_ctx_tp_transport(self._h))
 
     @staticmethod
     def nccl_unique_id():

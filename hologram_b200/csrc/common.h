@@ -49,6 +49,10 @@ struct holo_b200_ctx {
     // tensor-parallel group
     void* nccl_comm = nullptr;
     int tp_rank = 0, tp_world = 1;
+    // peer-memory transport: every rank's mailbox as mapped here, per-chunk epoch counters
+    bool tp_p2p = false;
+    uint8_t* tp_mailbox[8] = {};
+    uint32_t* tp_epochs = nullptr;
 };
 
 struct holo_b200_workspace {
@@ -202,4 +206,5 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
                                  const HoloMatmulSeg* segs, uint32_t nseg);
 // tp.cu
 int32_t holo_all_reduce(holo_b200_ctx* ctx, void* buf, uint64_t n, uint8_t dtype);
+int32_t holo_all_reduce_add(holo_b200_ctx* ctx, const void* partial, const void* residual, void* out, uint64_t n, uint8_t dtype);
 void holo_tp_destroy(holo_b200_ctx* ctx);

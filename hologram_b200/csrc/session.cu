@@ -42,6 +42,10 @@ struct SessionNode {
     int merged = -1;                   // index into holo_b200_session::merged, or -1
     int batch = -1;                    // index into holo_b200_session::batches, or -1
     HoloKernelCall call;               // the plain call when both are -1
+    // AllReduce followed by the residual Add, run as one launch: `call` is the AllReduce,
+    // `residual` / `sum_out` come from the Add
+    bool reduce_add = false;
+    HoloBufferRef residual = {HOLO_NO_SLOT, 0, 0}, sum_out = {HOLO_NO_SLOT, 0, 0};
 };
 
 struct holo_b200_session {
@@ -52,7 +56,7 @@ struct holo_b200_session {
     std::vector<SessionNode> nodes;     // what a walk actually launches
     std::vector<MergedMatmul> merged;
     std::vector<MicroBatch> batches;
-    uint32_t fused = 0, moved_in_place = 0, merged_calls = 0, batched_calls = 0;
+    uint32_t fused = 0, moved_in_place = 0, merged_calls = 0, batched_calls = 0, reduce_adds = 0;
     uint64_t device_bytes = 0;
     cudaGraphExec_t graph = nullptr;
 };
@@ -239,6 +243,58 @@ int32_t run_merged(holo_b200_session* s, const MergedMatmul& g) {
     return holo_launch_matmul_multi(s->ctx, a, g.b_concat, g.m, g.k, g.n, segs, g.nseg);
 }
 
+// Tensor parallel: an AllReduce over a buffer, directly followed by the Add of that buffer and
+// a residual, with nothing else reading the reduced buffer afterwards, becomes one node (one
+// launch of the peer-memory kernel: sum over ranks, truncate, add the residual, truncate).
+void fuse_all_reduce_add(holo_b200_session* s, const std::set<uint32_t>& output_slots) {
+    std::vector<SessionNode> out;
+    for (size_t i = 0; i < s->nodes.size(); ++i) {
+        SessionNode n = s->nodes[i];
+        const bool plain = n.merged < 0 && n.batch < 0;
+        if (plain && n.call.kind == HOLO_K_ALL_REDUCE && i + 1 < s->nodes.size()) {
+            const SessionNode& nx = s->nodes[i + 1];
+            const HoloAllReduceCall& ar = n.call.u.all_reduce;
+            if (nx.merged < 0 && nx.batch < 0 && nx.call.kind == HOLO_K_ADD && nx.call.u.binary.element_count == ar.element_count &&
+                nx.call.u.binary.dtype == ar.dtype && !output_slots.count(ar.buffer.slot) &&
+                (same_range(nx.call.u.binary.a, ar.buffer) != same_range(nx.call.u.binary.b, ar.buffer))) {
+                bool read_later = false;
+                for (size_t j = i + 2; j < s->nodes.size() && !read_later; ++j) {
+                    if (s->nodes[j].merged >= 0) {
+                        read_later = s->merged[s->nodes[j].merged].a.slot == ar.buffer.slot;
+                        continue;
+                    }
+                    HoloKernelCall tmp = s->nodes[j].call;
+                    HoloRefList refs;
+                    if (!holo_collect_refs(&tmp, &refs)) continue;
+                    for (int r = 0; r < refs.n; ++r)
+                        if (refs.refs[r]->slot == ar.buffer.slot && !refs.written[r]) read_later = true;
+                }
+                if (!read_later) {
+                    n.reduce_add = true;
+                    n.residual = same_range(nx.call.u.binary.a, ar.buffer) ? nx.call.u.binary.b : nx.call.u.binary.a;
+                    n.sum_out = nx.call.u.binary.output;
+                    out.push_back(n);
+                    ++s->reduce_adds;
+                    ++i;  // the Add is absorbed
+                    continue;
+                }
+            }
+        }
+        out.push_back(n);
+    }
+    s->nodes.swap(out);
+}
+
+int32_t run_reduce_add(holo_b200_session* s, const SessionNode& n) {
+    const HoloAllReduceCall& ar = n.call.u.all_reduce;
+    const uint64_t bytes = ar.element_count * holo_dtype_size(ar.dtype);
+    uint8_t *buf, *res, *dst;
+    HOLO_TRY(holo_resolve(s->ws, ar.buffer, bytes, &buf, nullptr));
+    HOLO_TRY(holo_resolve(s->ws, n.residual, bytes, &res, nullptr));
+    HOLO_TRY(holo_resolve(s->ws, n.sum_out, bytes, &dst, nullptr));
+    return holo_all_reduce_add(s->ctx, buf, res, dst, ar.element_count, ar.dtype);
+}
+
 bool batchable_kind(uint16_t k) {
     return k == HOLO_K_KV_CACHE_WRITE || k == HOLO_K_ROTARY || k == HOLO_K_QUANTIZE_ROWS_I8 || k == HOLO_K_ADD || k == HOLO_K_MUL;
 }
@@ -334,7 +390,8 @@ int32_t plan_micro_batches(holo_b200_session* s) {
 
 int32_t run_calls(holo_b200_session* s) {
     for (const SessionNode& n : s->nodes) {
-        if (n.merged >= 0) HOLO_TRY(run_merged(s, s->merged[n.merged]));
+        if (n.reduce_add) HOLO_TRY(run_reduce_add(s, n));
+        else if (n.merged >= 0) HOLO_TRY(run_merged(s, s->merged[n.merged]));
         else if (n.batch >= 0) HOLO_TRY(holo_launch_micro_batch(s->ctx, s->batches[n.batch].dev_ops, s->batches[n.batch].nops, s->batches[n.batch].total_ctas));
         else HOLO_TRY(holo_dispatch_internal(s->ctx, &n.call, s->ws));
     }
@@ -376,6 +433,7 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
         }
         for (const HoloPort& p : s->ar.inputs) written_slots.insert(p.slot);   // inputs are rewritten by the caller
         plan_sibling_merges(s, const_slots, written_slots);
+        fuse_all_reduce_add(s, out_slots);
     }
 
     // slot sizing (session.rs:544-629)
@@ -480,7 +538,7 @@ extern "C" int32_t holo_b200_session_info(holo_b200_session* s, uint32_t* n_call
 extern "C" int32_t holo_b200_session_nodes(holo_b200_session* s, uint32_t* n_nodes, uint32_t* n_merged_calls) {
     if (!s) return holo_fail(HOLO_ERR_INIT, "null session");
     if (n_nodes) *n_nodes = (uint32_t)s->nodes.size();
-    if (n_merged_calls) *n_merged_calls = s->merged_calls + s->batched_calls;
+    if (n_merged_calls) *n_merged_calls = s->merged_calls + s->batched_calls + 2 * s->reduce_adds;
     return HOLO_OK;
 }
 

@@ -1,11 +1,20 @@
-// Tensor-parallel all-reduce over NCCL (NVLink 5 / NVSwitch). The reference is single-device
-// and has no collective; this is the sum after the row-parallel o-proj / down-proj matmuls.
-// NCCL is bound at run time with dlopen so the library loads (and every single-GPU path
-// runs) on a host without NCCL.
+// Tensor-parallel all-reduce (NVLink 5 / NVSwitch). The reference is single-device and has no
+// collective; this is the sum after the row-parallel o-proj / down-proj matmuls, optionally with
+// the residual add that follows it folded in.
+//
+// Two transports. NCCL (bound at run time with dlopen, so the library loads and every
+// single-GPU path runs on a host without it) sets up the group and carries messages over 1 MiB.
+// Decode-sized messages (64 x 4096 bf16 = 512 KiB) are latency-bound, so they go through the
+// library's own kernel over peer memory instead (see "peer-memory transport" below): every rank
+// owns a mailbox (cudaMalloc + CUDA IPC, opened by all peers at group set-up) that its peers
+// write into with plain stores over NVLink; data and ready-flag travel in the same 16-byte store.
 #include <dlfcn.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.h"
+#include "numerics.cuh"
 
 namespace {
 
@@ -13,6 +22,7 @@ typedef struct { char internal[128]; } NcclUniqueId;
 typedef int (*GetUniqueIdFn)(NcclUniqueId*);
 typedef int (*CommInitRankFn)(void**, int, NcclUniqueId, int);
 typedef int (*AllReduceFn)(const void*, void*, size_t, int, int, void*, cudaStream_t);
+typedef int (*AllGatherFn)(const void*, void*, size_t, int, void*, cudaStream_t);
 typedef int (*CommDestroyFn)(void*);
 typedef const char* (*GetErrorStringFn)(int);
 
@@ -21,6 +31,7 @@ struct Nccl {
     GetUniqueIdFn get_unique_id = nullptr;
     CommInitRankFn comm_init_rank = nullptr;
     AllReduceFn all_reduce = nullptr;
+    AllGatherFn all_gather = nullptr;
     CommDestroyFn comm_destroy = nullptr;
     GetErrorStringFn get_error_string = nullptr;
 };
@@ -36,12 +47,125 @@ Nccl* nccl() {
             n.get_unique_id = (GetUniqueIdFn)dlsym(n.lib, "ncclGetUniqueId");
             n.comm_init_rank = (CommInitRankFn)dlsym(n.lib, "ncclCommInitRank");
             n.all_reduce = (AllReduceFn)dlsym(n.lib, "ncclAllReduce");
+            n.all_gather = (AllGatherFn)dlsym(n.lib, "ncclAllGather");
             n.comm_destroy = (CommDestroyFn)dlsym(n.lib, "ncclCommDestroy");
             n.get_error_string = (GetErrorStringFn)dlsym(n.lib, "ncclGetErrorString");
         }
     }
     if (!n.lib || !n.get_unique_id || !n.comm_init_rank || !n.all_reduce || !n.comm_destroy) return nullptr;
     return &n;
+}
+
+// ---- peer-memory transport --------------------------------------------------------------------
+// Message of n 16-bit elements = n/4 units of four elements; rank j owns the j-th of W equal
+// slices. A unit travels as one 16-byte store {lo32, epoch, hi32, epoch}: each 8-byte half
+// carries its own flag, so a reader that sees the epoch in both halves has the data, with no
+// fence and no separate flag write (the data IS the signal). Three phases per thread:
+//   1. scatter: push my partial of every other rank's slice into that rank's mailbox
+//   2. reduce:  for my slice, poll the W-1 incoming partials, sum in rank order in f32, truncate,
+//               add the residual, truncate; store locally and push the result to every peer
+//   3. gather:  poll the W-1 incoming result slices and store them
+// Phase 1 never waits, phase 2 waits only for phase 1 of peers, phase 3 only for their phase 2:
+// no cycle. Every poll is bounded. A mailbox region is rewritten one epoch later, which a rank
+// reaches only after it has received (hence the peer has finished reading) everything of this one.
+constexpr uint32_t P2P_MAX_ELEMS = 512 * 1024;              // 1 MiB of 16-bit elements
+constexpr uint32_t P2P_THREADS = 256;
+constexpr uint32_t P2P_MAX_CTAS = 64;
+constexpr uint64_t P2P_REGION_BYTES = (uint64_t)P2P_MAX_ELEMS * 4;   // n/4 units x 16 bytes
+constexpr uint64_t P2P_MAILBOX_BYTES = 2 * P2P_REGION_BYTES;         // incoming partials, incoming results
+constexpr uint32_t P2P_WAIT_LIMIT = 1u << 22;               // polls before a thread gives up
+
+struct P2PParams {
+    const uint16_t* partial;   // local, [n] 16-bit floats
+    const uint16_t* residual;  // local or null
+    uint16_t* out;             // local (may alias partial)
+    uint8_t* mailbox[8];       // mailbox[r] = rank r's mailbox as mapped in this process
+    uint32_t* state;           // local: [0] = epochs completed, [1] = CTAs finished in this launch
+    uint32_t* status;
+    uint32_t units_per_slice;  // n / 4 / world
+    int rank, world, dtype;
+};
+
+__device__ __forceinline__ void ll_store(uint8_t* base, uint64_t unit, uint2 d, uint32_t epoch) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(base + unit * 16), "r"(d.x), "r"(epoch), "r"(d.y), "r"(epoch)
+                 : "memory");
+}
+// Poll one unit until both halves carry `epoch`; false after P2P_WAIT_LIMIT polls.
+__device__ __forceinline__ bool ll_load(const uint8_t* base, uint64_t unit, uint32_t epoch, uint2* d) {
+    for (uint32_t it = 0; it < P2P_WAIT_LIMIT; ++it) {
+        uint32_t a, fa, b, fb;
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(fa), "=r"(b), "=r"(fb) : "l"(base + unit * 16) : "memory");
+        if (fa == epoch && fb == epoch) {
+            *d = make_uint2(a, b);
+            return true;
+        }
+        if (it > 1024) __nanosleep(100);
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(P2P_THREADS) all_reduce_p2p_kernel(const P2PParams p) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    const uint32_t T = gridDim.x * P2P_THREADS, t = blockIdx.x * P2P_THREADS + threadIdx.x;
+    const uint32_t U = p.units_per_slice, W = (uint32_t)p.world, me = (uint32_t)p.rank;
+    const uint32_t epoch = p.state[0] + 1;
+    const uint2* part2 = reinterpret_cast<const uint2*>(p.partial);
+    const uint2* res2 = reinterpret_cast<const uint2*>(p.residual);
+    uint2* out2 = reinterpret_cast<uint2*>(p.out);
+    bool ok = true;
+
+    // my slice's partials first: phase 2 may write `out` over them when out aliases partial only
+    // at the same unit, which is read before it is written
+    // 1. scatter
+    for (uint32_t idx = t; idx < (W - 1) * U; idx += T) {
+        const uint32_t j = (me + 1 + idx / U) % W, u = idx % U;
+        ll_store(p.mailbox[j], (uint64_t)me * U + u, part2[(uint64_t)j * U + u], epoch);
+    }
+    // 2. reduce my slice
+    uint8_t* box = p.mailbox[me];
+    for (uint32_t u = t; u < U && ok; u += T) {
+        const uint2 own = part2[(uint64_t)me * U + u];
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t r = 0; r < W && ok; ++r) {
+            uint2 v = own;
+            if (r != me) ok = ll_load(box, (uint64_t)r * U + u, epoch, &v);
+            acc[0] = __fadd_rn(acc[0], holo::widen16((uint16_t)(v.x & 0xffffu), p.dtype));
+            acc[1] = __fadd_rn(acc[1], holo::widen16((uint16_t)(v.x >> 16), p.dtype));
+            acc[2] = __fadd_rn(acc[2], holo::widen16((uint16_t)(v.y & 0xffffu), p.dtype));
+            acc[3] = __fadd_rn(acc[3], holo::widen16((uint16_t)(v.y >> 16), p.dtype));
+        }
+        if (!ok) break;
+        uint16_t h[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) h[x] = holo::narrow16(acc[x], p.dtype);
+        if (res2) {
+            const uint2 rv = res2[(uint64_t)me * U + u];
+            const uint16_t rr[4] = {(uint16_t)(rv.x & 0xffffu), (uint16_t)(rv.x >> 16), (uint16_t)(rv.y & 0xffffu), (uint16_t)(rv.y >> 16)};
+#pragma unroll
+            for (int x = 0; x < 4; ++x) h[x] = holo::narrow16(__fadd_rn(holo::widen16(h[x], p.dtype), holo::widen16(rr[x], p.dtype)), p.dtype);
+        }
+        const uint2 res = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+        out2[(uint64_t)me * U + u] = res;
+        for (uint32_t k = 1; k < W; ++k) ll_store(p.mailbox[(me + k) % W] + P2P_REGION_BYTES, (uint64_t)me * U + u, res, epoch);
+    }
+    // 3. gather the other slices' results
+    for (uint32_t idx = t; idx < (W - 1) * U && ok; idx += T) {
+        const uint32_t r = (me + 1 + idx / U) % W, u = idx % U;
+        uint2 v;
+        ok = ll_load(box + P2P_REGION_BYTES, (uint64_t)r * U + u, epoch, &v);
+        if (ok) out2[(uint64_t)r * U + u] = v;
+    }
+    if (!ok) atomicOr(p.status, 8u);
+    // the launch's last CTA advances the epoch (every CTA has read it by then)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t done = atomicAdd(p.state + 1, 1u);
+        if (done == gridDim.x - 1) {
+            p.state[1] = 0;
+            p.state[0] = epoch;
+        }
+    }
 }
 
 int32_t nccl_fail(Nccl* n, int rc, const char* where) {
@@ -80,10 +204,83 @@ extern "C" int32_t holo_b200_ctx_init_tp(holo_b200_ctx* ctx, const uint8_t id128
     ctx->nccl_comm = comm;
     ctx->tp_rank = rank;
     ctx->tp_world = world;
+    // Peer-memory mailboxes. Any failure here (IPC not permitted, no peer access, more than 8
+    // ranks) leaves the group on NCCL alone; the ranks agree on the outcome through a min-reduce.
+    const char* env = getenv("HOLO_TP_P2P");
+    bool want = world <= 8 && n->all_gather && !(env && atoi(env) == 0);
+    uint8_t* mine = nullptr;
+    uint8_t* dev_handles = nullptr;
+    cudaIpcMemHandle_t handles[8];
+    bool ok = want;
+    if (ok) ok = cudaMalloc(&mine, P2P_MAILBOX_BYTES) == cudaSuccess && cudaMemset(mine, 0, P2P_MAILBOX_BYTES) == cudaSuccess;
+    if (ok) ok = cudaMalloc(&dev_handles, 8 * sizeof(cudaIpcMemHandle_t)) == cudaSuccess;
+    cudaIpcMemHandle_t h;
+    memset(&h, 0, sizeof h);
+    if (ok) ok = cudaIpcGetMemHandle(&h, mine) == cudaSuccess;
+    if (dev_handles) {
+        // every rank takes part in the gather, whether or not its own set-up worked
+        cudaMemcpy(dev_handles + (size_t)rank * sizeof h, &h, sizeof h, cudaMemcpyHostToDevice);
+        rc = n->all_gather(dev_handles + (size_t)rank * sizeof h, dev_handles, sizeof h, /*ncclInt8*/ 0, comm, ctx->stream);
+        if (rc != 0 || cudaStreamSynchronize(ctx->stream) != cudaSuccess) ok = false;
+        if (cudaMemcpy(handles, dev_handles, world * sizeof h, cudaMemcpyDeviceToHost) != cudaSuccess) ok = false;
+    } else {
+        ok = false;
+    }
+    if (ok) {
+        for (int r = 0; r < world && ok; ++r) {
+            if (r == rank) {
+                ctx->tp_mailbox[r] = mine;
+            } else {
+                void* q = nullptr;
+                ok = cudaIpcOpenMemHandle(&q, handles[r], cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+                ctx->tp_mailbox[r] = (uint8_t*)q;
+            }
+        }
+    }
+    if (ok) ok = cudaMalloc(&ctx->tp_epochs, 256) == cudaSuccess && cudaMemset(ctx->tp_epochs, 0, 256) == cudaSuccess;
+    cudaGetLastError();  // a failed attempt above must not poison later launches
+    // agreement: min over ranks of "my set-up worked" (want == false on one rank switches all off;
+    // a rank without a gather buffer cannot take part in a collective, so it has to fail init)
+    if (!dev_handles && want) return holo_fail(HOLO_ERR_INIT, "backend init failed: tensor-parallel set-up could not allocate device memory");
+    if (dev_handles) {
+        float flag = ok ? 1.0f : 0.0f;
+        cudaMemcpy(dev_handles, &flag, 4, cudaMemcpyHostToDevice);
+        rc = n->all_reduce(dev_handles, dev_handles, 1, /*ncclFloat32*/ 7, /*ncclMin*/ 3, comm, ctx->stream);
+        if (rc != 0 || cudaStreamSynchronize(ctx->stream) != cudaSuccess) return nccl_fail(n, rc, "ncclAllReduce (transport agreement)");
+        cudaMemcpy(&flag, dev_handles, 4, cudaMemcpyDeviceToHost);
+        ok = flag > 0.5f;
+        cudaFree(dev_handles);
+    }
+    ctx->tp_p2p = ok;
+    if (!ok) {
+        for (int r = 0; r < world; ++r)
+            if (r != rank && ctx->tp_mailbox[r]) cudaIpcCloseMemHandle(ctx->tp_mailbox[r]);
+        memset(ctx->tp_mailbox, 0, sizeof ctx->tp_mailbox);
+        if (mine) cudaFree(mine);
+        if (ctx->tp_epochs) cudaFree(ctx->tp_epochs);
+        ctx->tp_epochs = nullptr;
+        cudaGetLastError();
+    }
     return HOLO_OK;
 }
 
+extern "C" int32_t holo_b200_ctx_tp_transport(holo_b200_ctx* ctx) {
+    if (!ctx || ctx->tp_world <= 1) return 0;
+    return ctx->tp_p2p ? 2 : 1;
+}
+
 void holo_tp_destroy(holo_b200_ctx* ctx) {
+    if (ctx->tp_p2p) {
+        for (int r = 0; r < ctx->tp_world; ++r) {
+            if (!ctx->tp_mailbox[r]) continue;
+            if (r == ctx->tp_rank) cudaFree(ctx->tp_mailbox[r]);
+            else cudaIpcCloseMemHandle(ctx->tp_mailbox[r]);
+            ctx->tp_mailbox[r] = nullptr;
+        }
+        if (ctx->tp_epochs) cudaFree(ctx->tp_epochs);
+        ctx->tp_epochs = nullptr;
+        ctx->tp_p2p = false;
+    }
     if (ctx->nccl_comm) {
         Nccl* n = nccl();
         if (n) n->comm_destroy(ctx->nccl_comm);
@@ -91,13 +288,47 @@ void holo_tp_destroy(holo_b200_ctx* ctx) {
     }
 }
 
+// out = all_reduce(partial) (+ residual). `out` may alias `partial`; `residual` may be null.
+int32_t holo_all_reduce_add(holo_b200_ctx* ctx, const void* partial, const void* residual, void* out, uint64_t count, uint8_t dtype) {
+    if (count == 0) return HOLO_OK;
+    const bool sixteen = dtype == HOLO_DTYPE_BF16 || dtype == HOLO_DTYPE_F16;
+    const bool aligned = (((uintptr_t)partial | (uintptr_t)residual | (uintptr_t)out) & 7u) == 0;
+    if (ctx->tp_world > 1 && ctx->tp_p2p && sixteen && aligned && count <= P2P_MAX_ELEMS && (count % (4ull * ctx->tp_world)) == 0) {
+        P2PParams p;
+        p.partial = (const uint16_t*)partial;
+        p.residual = (const uint16_t*)residual;
+        p.out = (uint16_t*)out;
+        for (int r = 0; r < 8; ++r) p.mailbox[r] = ctx->tp_mailbox[r];
+        p.state = ctx->tp_epochs;
+        p.status = ctx->dev_status;
+        p.units_per_slice = (uint32_t)(count / 4 / ctx->tp_world);
+        p.rank = ctx->tp_rank;
+        p.world = ctx->tp_world;
+        p.dtype = dtype;
+        // enough threads for one unit of the widest phase each, at most P2P_MAX_CTAS CTAs (all co-resident)
+        const uint64_t widest = (uint64_t)p.units_per_slice * (ctx->tp_world - 1);
+        uint32_t ctas = (uint32_t)((widest + P2P_THREADS - 1) / P2P_THREADS);
+        if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
+        if (ctas < 1) ctas = 1;
+        HOLO_CUDA(holo_launch_kernel(ctx, all_reduce_p2p_kernel, dim3(ctas), dim3(P2P_THREADS), 0, 1, p));
+        ctx->launches++;
+        return HOLO_OK;
+    }
+    if (out != partial)
+        HOLO_CUDA(cudaMemcpyAsync(out, partial, count * holo_dtype_size(dtype), cudaMemcpyDeviceToDevice, ctx->stream));
+    if (ctx->tp_world > 1) {
+        Nccl* n = nccl();
+        if (!n || !ctx->nccl_comm) return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: all_reduce without a tensor-parallel group");
+        // ncclDataType_t: ncclFloat16 = 6, ncclFloat32 = 7, ncclBfloat16 = 9; ncclSum = 0
+        int dt = dtype == HOLO_DTYPE_F32 ? 7 : dtype == HOLO_DTYPE_F16 ? 6 : 9;
+        int rc = n->all_reduce(out, out, (size_t)count, dt, 0, ctx->nccl_comm, ctx->stream);
+        if (rc != 0) return nccl_fail(n, rc, "ncclAllReduce");
+    }
+    if (residual) return holo_launch_binary(ctx, 0, out, residual, out, count, dtype);
+    return HOLO_OK;
+}
+
 int32_t holo_all_reduce(holo_b200_ctx* ctx, void* buf, uint64_t count, uint8_t dtype) {
     if (ctx->tp_world <= 1 || count == 0) return HOLO_OK;
-    Nccl* n = nccl();
-    if (!n || !ctx->nccl_comm) return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: all_reduce without a tensor-parallel group");
-    // ncclDataType_t: ncclFloat16 = 6, ncclFloat32 = 7, ncclBfloat16 = 9; ncclSum = 0
-    int dt = dtype == HOLO_DTYPE_F32 ? 7 : dtype == HOLO_DTYPE_F16 ? 6 : 9;
-    int rc = n->all_reduce(buf, buf, (size_t)count, dt, 0, ctx->nccl_comm, ctx->stream);
-    if (rc != 0) return nccl_fail(n, rc, "ncclAllReduce");
-    return HOLO_OK;
+    return holo_all_reduce_add(ctx, buf, nullptr, buf, count, dtype);
 }

@@ -386,6 +386,10 @@ int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const void* q, c
  * and broadcast by the host launcher. */
 int32_t holo_b200_nccl_unique_id(uint8_t out128[128]);
 int32_t holo_b200_ctx_init_tp(holo_b200_ctx* ctx, const uint8_t nccl_unique_id[128], int32_t rank, int32_t world);
+/* How the group's all-reduces of decode-sized 16-bit messages travel: 0 = no group, 1 = NCCL,
+ * 2 = the library's own one-shot kernel over peer memory (CUDA IPC mailboxes; every rank sums
+ * in rank order, so all ranks hold identical bits). Set HOLO_TP_P2P=0 to stay on NCCL. */
+int32_t holo_b200_ctx_tp_transport(holo_b200_ctx* ctx);
 
 /* Library version / build info string (static storage). */
 const char* holo_b200_version(void);

@@ -34,11 +34,25 @@ else:
     uid = [hb.B200Backend.nccl_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(uid, src=0)
     be.init_tp(uid[0], rank, world)
+    # a bare AllReduce through the C ABI: 64 x 4096 bf16 partials, seeded per rank, twice in a
+    # row (the second call reuses the other message slot and the next epoch)
+    from hologram_b200 import kernel_call as kc
+    n = 64 * 4096
+    ws = hb.DeviceWorkspace(be, 1)
+    for rep in range(3):
+        part = orc.f32_to_bf16_rne(np.random.default_rng(100 * rep + rank).standard_normal(n).astype(np.float32))
+        ws.put(0, part)
+        be.dispatch(kc.KernelCall.AllReduce(kc.AllReduceCall(kc.rb(0), n, kc.DTYPE_BF16)), ws)
+        np.save(os.path.join(%(out)r, f"allreduce_{rep}_{rank}.npy"), ws.read(0, dtype=np.uint16).copy())
+    ws.close()
+    with open(os.path.join(%(out)r, f"transport_{rank}.txt"), "w") as f:
+        f.write(str(be.tp_transport))
     sess = hb.InferenceSession(be, img)
     for name, arr in vals.items():
         sess.write(name, arr)
     sess.execute()
     logits = orc.bf16_to_f32(sess.read("logits", np.uint16))
+    sess.close()
     be.close()
 np.save(os.path.join(%(out)r, f"logits_{mode}_{rank}.npy"), logits)
 dist.destroy_process_group()
@@ -90,6 +104,22 @@ def test_tp2_on_two_gpus_matches_single_rank(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     r0, r1 = _launch("gpu", tmp_path)
+    # the bare all-reduces: both ranks hold the same bits; over peer memory they are exactly the
+    # f32 sum in rank order, truncated to bf16 (NCCL rounds and orders differently: tolerance)
+    sys.path.insert(0, ROOT)
+    from oracle import oracle as orc
+    transport = [int(open(tmp_path / f"transport_{r}.txt").read()) for r in range(2)]
+    assert transport[0] == transport[1] and transport[0] in (1, 2)
+    for rep in range(3):
+        got = [np.load(tmp_path / f"allreduce_{rep}_{r}.npy") for r in range(2)]
+        assert np.array_equal(got[0], got[1])
+        parts = [orc.bf16_to_f32(orc.f32_to_bf16_rne(np.random.default_rng(100 * rep + r).standard_normal(64 * 4096).astype(np.float32)))
+                 for r in range(2)]
+        total = (np.float32(0.0) + parts[0]) + parts[1]
+        if transport[0] == 2:
+            assert np.array_equal(got[0], (total.view(np.uint32) >> 16).astype(np.uint16))
+        else:
+            assert np.max(np.abs(orc.bf16_to_f32(got[0]) - total)) <= 2.0 ** -6 * np.max(np.abs(total))
     want = _single_rank_reference()
     got = np.concatenate([r0.reshape(want.shape[0], -1), r1.reshape(want.shape[0], -1)], axis=1)
     err = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
