@@ -312,13 +312,14 @@ int32_t do_matmul(holo_b200_ctx* ctx, const HoloMatMulCall& c, uint8_t act, cons
     if (c.m == 0 || c.k == 0 || c.n == 0) return HOLO_OK;
     if (c.dtype == HOLO_DTYPE_F64)
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: f64 is not a supported compute dtype (hologram computes in f16/bf16/f32)");
-    if (c.dtype != HOLO_DTYPE_BF16)
-        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul is served for bf16 only (dtype %u)", c.dtype);
+    if (!holo_is_compute_float(c.dtype))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul: only f32/f16/bf16 are supported compute dtypes (dtype %u)", c.dtype);
     if (c.b_packed) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: panel-packed B is an f32-only layout");
     if (act != 0 && act != HOLO_FUSED_GELU && act != HOLO_FUSED_SILU && act != HOLO_FUSED_SIGMOID && act != HOLO_FUSED_TANH &&
         act != HOLO_FUSED_EXP)
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: fused activation %u is not table-backed", act);
-    uint64_t ab = (uint64_t)c.m * c.k * 2, bb = (uint64_t)c.k * c.n * 2, ob = (uint64_t)c.m * c.n * 2;
+    const uint64_t es = holo_dtype_size(c.dtype);
+    uint64_t ab = (uint64_t)c.m * c.k * es, bb = (uint64_t)c.k * c.n * es, ob = (uint64_t)c.m * c.n * es;
     uint8_t *a, *b, *out, *res = nullptr;
     HOLO_TRY(holo_resolve(ws, c.a, ab, &a, nullptr));
     HOLO_TRY(holo_resolve(ws, c.b, bb, &b, nullptr));
@@ -332,7 +333,8 @@ int32_t do_matmul(holo_b200_ctx* ctx, const HoloMatMulCall& c, uint8_t act, cons
 }
 
 // rms_norm_float (cpu/float_kernels.rs:1683-1756), epsilon rule :1324-1336
-int32_t do_rms_norm(holo_b200_ctx* ctx, const HoloNormCall& c, holo_b200_workspace* ws) {
+// `with_residual`: add_rms_norm_float (:1567-1681); an absent residual operand makes it a plain RmsNorm
+int32_t do_rms_norm(holo_b200_ctx* ctx, const HoloNormCall& c, bool with_residual, holo_b200_workspace* ws) {
     if (c.batch == 0 || c.feature == 0) return HOLO_OK;
     if (!holo_is_compute_float(c.dtype))
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: rms_norm dtype %u", c.dtype);
@@ -346,13 +348,14 @@ int32_t do_rms_norm(holo_b200_ctx* ctx, const HoloNormCall& c, holo_b200_workspa
     }
     size_t es = holo_dtype_size(c.dtype);
     uint64_t total = (uint64_t)c.batch * c.feature * es;
-    uint8_t *x, *g = nullptr, *out;
+    uint8_t *x, *g = nullptr, *res = nullptr, *out;
     HOLO_TRY(holo_resolve(ws, c.output, 0, &out, nullptr));
     HOLO_TRY(holo_resolve(ws, c.x, total, &x, nullptr));
+    if (with_residual && c.residual.slot != HOLO_NO_SLOT) HOLO_TRY(holo_resolve(ws, c.residual, total, &res, nullptr));
     if (c.gamma.slot != HOLO_NO_SLOT) HOLO_TRY(holo_resolve(ws, c.gamma, (uint64_t)c.feature * es, &g, nullptr));
     HOLO_TRY(holo_resolve(ws, c.output, total, &out, nullptr));
-    HOLO_TRY(check_disjoint({out, total}, c.output.slot, {{x, total}, {g, g ? (uint64_t)c.feature * es : 0}}));
-    return holo_launch_rms_norm(ctx, x, g, out, c.batch, c.feature, eps, c.dtype);
+    HOLO_TRY(check_disjoint({out, total}, c.output.slot, {{x, total}, {res, res ? total : 0}, {g, g ? (uint64_t)c.feature * es : 0}}));
+    return holo_launch_rms_norm(ctx, x, res, g, out, c.batch, c.feature, eps, c.dtype);
 }
 
 // rope_float (cpu/float_kernels.rs:3123-3190)
@@ -415,6 +418,41 @@ int32_t do_reshape(holo_b200_ctx* ctx, const HoloLayoutCall& c, holo_b200_worksp
     HOLO_TRY(check_disjoint({out, bytes}, c.output.slot, {{in, bytes}}));
     if (bytes) HOLO_CUDA(cudaMemcpyAsync(out, in, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     return HOLO_OK;
+}
+
+// concat_float (cpu/float_kernels.rs:2963-2974): out = a || b, both taken at their resolved
+// extents; dtype-agnostic byte placement.
+int32_t do_concat(holo_b200_ctx* ctx, const HoloBinaryCall& c, holo_b200_workspace* ws) {
+    uint8_t *a, *b, *out;
+    uint64_t alen = 0, blen = 0, olen = 0;
+    HOLO_TRY(holo_resolve(ws, c.output, 0, &out, &olen));
+    HOLO_TRY(holo_resolve(ws, c.a, 0, &a, &alen));
+    HOLO_TRY(holo_resolve(ws, c.b, 0, &b, &blen));
+    if (olen < alen + blen) return holo_fail_slot(c.output.slot, "concat output shorter than a || b");
+    HOLO_TRY(check_disjoint({out, alen + blen}, c.output.slot, {{a, alen}, {b, blen}}));
+    if (alen) HOLO_CUDA(cudaMemcpyAsync(out, a, alen, cudaMemcpyDeviceToDevice, ctx->stream));
+    if (blen) HOLO_CUDA(cudaMemcpyAsync(out + alen, b, blen, cudaMemcpyDeviceToDevice, ctx->stream));
+    return HOLO_OK;
+}
+
+// transpose_float (cpu/float_kernels.rs:2980-3027)
+int32_t do_transpose(holo_b200_ctx* ctx, const HoloTransposeCall& c, holo_b200_workspace* ws) {
+    if (c.rank == 0 || c.rank > 8) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: transpose: rank must be 1..=8");
+    size_t es = holo_dtype_size(c.dtype);
+    if (es == 0) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: transpose of a sub-byte dtype");
+    uint64_t total = 1;
+    uint32_t seen = 0;
+    for (uint32_t i = 0; i < c.rank; ++i) {
+        total *= c.dims[i];
+        if (c.perm[i] >= c.rank || (seen & (1u << c.perm[i]))) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: transpose: perm is not a permutation of the axes");
+        seen |= 1u << c.perm[i];
+    }
+    uint8_t *in, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, total * es, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.input, total * es, &in, nullptr));
+    HOLO_TRY(check_disjoint({out, total * es}, c.output.slot, {{in, total * es}}));
+    if (((uintptr_t)in | (uintptr_t)out) % es != 0) return holo_fail_slot(c.input.slot, "transpose operands must be aligned to the element size on the device");
+    return holo_launch_transpose(ctx, in, out, c.rank, c.dims, c.perm, (uint32_t)es);
 }
 
 // dequantize (cpu/kernels.rs:185-296)
@@ -527,6 +565,49 @@ int32_t do_attention(holo_b200_ctx* ctx, const HoloDecodeAttentionValidCall& c, 
     return holo_launch_decode_attention(ctx, a);
 }
 
+// decode_attention_float, the additive-mask form (cpu/float_kernels.rs:2482-2600)
+int32_t do_attention_mask(holo_b200_ctx* ctx, const HoloDecodeAttentionCall& c, holo_b200_workspace* ws) {
+    if (c.batch == 0 || c.heads == 0 || c.q_rows == 0 || c.head_dim == 0) return HOLO_OK;
+    const uint64_t l = (uint64_t)c.past_len + c.new_len;
+    if (l == 0) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: decode_attention: past_len + new_len must be at least 1");
+    HoloAttnArgs a = {};
+    a.hkv = c.kv_heads == 0 ? c.heads : c.kv_heads;
+    if (a.hkv == 0 || c.heads % a.hkv != 0)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: decode_attention: heads must be a multiple of kv_heads (grouped-query)");
+    if (c.dtype == HOLO_DTYPE_F64)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: f64 is not a supported compute dtype (hologram computes in f16/bf16/f32)");
+    if (!holo_is_compute_float(c.dtype))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: decode_attention: only f32/f16/bf16 are supported compute dtypes");
+    a.scale_div = sqrtf((float)c.head_dim);
+    if (a.scale_div < 1.0f) a.scale_div = 1.0f;
+    if (c.scale_bits != 0) {
+        float sm;
+        memcpy(&sm, &c.scale_bits, 4);
+        if (sm > 0.0f) a.scale_div = 1.0f / sm;
+    }
+    size_t es = holo_dtype_size(c.dtype);
+    uint64_t qt = (uint64_t)c.batch * c.heads * c.q_rows * c.head_dim * es;
+    uint64_t pt = (uint64_t)c.batch * a.hkv * c.past_len * c.head_dim * es;
+    uint64_t nt = (uint64_t)c.batch * a.hkv * c.new_len * c.head_dim * es;
+    uint64_t mt = (uint64_t)c.q_rows * l * 4;   // the mask is always f32
+    uint8_t *q, *kp, *vp, *kn, *vn, *mk, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, 0, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.q, qt, &q, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.k_past, pt, &kp, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.v_past, pt, &vp, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.k_new, nt, &kn, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.v_new, nt, &vn, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.mask, mt, &mk, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, qt, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, qt}, c.output.slot, {{q, qt}, {kp, pt}, {vp, pt}, {kn, nt}, {vn, nt}, {mk, mt}}));
+    if (((uintptr_t)mk & 3u) != 0) return holo_fail_slot(c.mask.slot, "mask operand must be 4-byte aligned on the device");
+    a.q = q; a.k_past = kp; a.v_past = vp; a.k_new = kn; a.v_new = vn;
+    a.mask = (const float*)mk; a.out = out;
+    a.b = c.batch; a.h = c.heads; a.m = c.q_rows; a.past = c.past_len; a.nnew = c.new_len; a.d = c.head_dim;
+    a.dtype = c.dtype; a.quantized = false;
+    return holo_launch_decode_attention(ctx, a);
+}
+
 int32_t do_attention_q8(holo_b200_ctx* ctx, const HoloDecodeAttentionValidQ8Call& c, holo_b200_workspace* ws) {
     HoloAttnArgs a = {};
     bool empty;
@@ -582,13 +663,17 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         case HOLO_K_MATMUL: return do_matmul(ctx, call->u.matmul, 0, nullptr, ws);
         case HOLO_K_MATMUL_ACTIVATION: return do_matmul(ctx, call->u.matmul_activation.mm, call->u.matmul_activation.act, nullptr, ws);
         case HOLO_K_MATMUL_ADD: return do_matmul(ctx, call->u.matmul_add.mm, 0, &call->u.matmul_add.residual, ws);
-        case HOLO_K_RMS_NORM: return do_rms_norm(ctx, call->u.norm, ws);
+        case HOLO_K_RMS_NORM: return do_rms_norm(ctx, call->u.norm, false, ws);
+        case HOLO_K_ADD_RMS_NORM: return do_rms_norm(ctx, call->u.norm, true, ws);
         case HOLO_K_ROTARY: return do_rope(ctx, call->u.rope, ws);
         case HOLO_K_GATHER: return do_gather(ctx, call->u.gather, ws);
         case HOLO_K_CAST: return do_cast(ctx, call->u.cast, ws);
-        case HOLO_K_RESHAPE: return do_reshape(ctx, call->u.layout, ws);
+        case HOLO_K_RESHAPE: case HOLO_K_SLICE: return do_reshape(ctx, call->u.layout, ws);
+        case HOLO_K_CONCAT: return do_concat(ctx, call->u.binary, ws);
+        case HOLO_K_TRANSPOSE: return do_transpose(ctx, call->u.transpose, ws);
         case HOLO_K_DEQUANTIZE: return do_dequantize(ctx, call->u.dequantize, ws);
         case HOLO_K_KV_CACHE_WRITE: return do_kv_write(ctx, call->u.kv_cache_write, ws);
+        case HOLO_K_DECODE_ATTENTION: return do_attention_mask(ctx, call->u.decode_attention, ws);
         case HOLO_K_DECODE_ATTENTION_VALID: return do_attention(ctx, call->u.decode_attention_valid, ws);
         case HOLO_K_QUANTIZE_ROWS_I8: return do_quantize_rows(ctx, call->u.quantize_rows_i8, ws);
         case HOLO_K_DECODE_ATTENTION_VALID_Q8: return do_attention_q8(ctx, call->u.decode_attention_valid_q8, ws);
@@ -628,6 +713,9 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             l->out(&mm.output, (uint64_t)mm.m * mm.n * holo_dtype_size(mm.dtype));
             return true;
         }
+        case HOLO_K_ADD_RMS_NORM:
+            l->in(&c->u.norm.residual);
+            /* fall through */
         case HOLO_K_RMS_NORM:
             l->in(&c->u.norm.x); l->in(&c->u.norm.gamma);
             l->out(&c->u.norm.output, (uint64_t)c->u.norm.batch * c->u.norm.feature * holo_dtype_size(c->u.norm.dtype));
@@ -644,6 +732,22 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             l->in(&c->u.cast.input);
             l->out(&c->u.cast.output, c->u.cast.element_count * holo_dtype_size(c->u.cast.dst_dtype));
             return true;
+        case HOLO_K_CONCAT: {
+            auto& b = c->u.binary;
+            l->in(&b.a); l->in(&b.b);
+            // produced bytes = |a| + |b| when both extents are explicit (host staging needs them)
+            l->out(&b.output, b.a.length && b.b.length ? b.a.length + b.b.length : b.output.length);
+            return true;
+        }
+        case HOLO_K_TRANSPOSE: {
+            auto& t = c->u.transpose;
+            uint64_t total = holo_dtype_size(t.dtype);
+            for (uint32_t i = 0; i < t.rank && i < 8; ++i) total *= t.dims[i];
+            l->in(&t.input);
+            l->out(&t.output, total);
+            return true;
+        }
+        case HOLO_K_SLICE:
         case HOLO_K_RESHAPE:
             l->in(&c->u.layout.input);
             l->out(&c->u.layout.output, c->u.layout.element_count * holo_dtype_size(c->u.layout.dtype));
@@ -656,6 +760,12 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             auto& k = c->u.kv_cache_write;
             l->in(&k.cache); l->in(&k.new_rows_buf); l->in(&k.pos);
             l->out(&k.output, (uint64_t)k.planes * k.bucket_rows * k.row_bytes);
+            return true;
+        }
+        case HOLO_K_DECODE_ATTENTION: {
+            auto& a = c->u.decode_attention;
+            l->in(&a.q); l->in(&a.k_past); l->in(&a.v_past); l->in(&a.k_new); l->in(&a.v_new); l->in(&a.mask);
+            l->out(&a.output, (uint64_t)a.batch * a.heads * a.q_rows * a.head_dim * holo_dtype_size(a.dtype));
             return true;
         }
         case HOLO_K_DECODE_ATTENTION_VALID: {

@@ -66,11 +66,19 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
     switch (d) {
         case HOLO_K_SIGMOID: case HOLO_K_TANH: case HOLO_K_GELU: case HOLO_K_SILU: case HOLO_K_EXP: case HOLO_K_ERF:
             get_unary(r, out->u.unary); break;
-        case HOLO_K_ADD: case HOLO_K_MUL: get_binary(r, out->u.binary); break;
+        case HOLO_K_ADD: case HOLO_K_MUL: case HOLO_K_CONCAT: get_binary(r, out->u.binary); break;
+        case HOLO_K_TRANSPOSE: {
+            HoloTransposeCall& c = out->u.transpose;
+            c.input = r.buf(); c.output = r.buf(); c.rank = r.u8();
+            for (int i = 0; i < 8; ++i) c.dims[i] = r.u32();
+            for (int i = 0; i < 8; ++i) c.perm[i] = r.u8();
+            c.dtype = r.u8();
+            break;
+        }
         case HOLO_K_MATMUL: get_matmul(r, out->u.matmul); break;
         case HOLO_K_MATMUL_ACTIVATION: get_matmul(r, out->u.matmul_activation.mm); out->u.matmul_activation.act = r.u8(); break;
         case HOLO_K_MATMUL_ADD: get_matmul(r, out->u.matmul_add.mm); out->u.matmul_add.residual = r.buf(); break;
-        case HOLO_K_RMS_NORM: {
+        case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM: {
             HoloNormCall& c = out->u.norm;
             c.x = r.buf(); c.gamma = r.buf(); c.beta = r.buf(); c.residual = r.buf(); c.output = r.buf();
             c.batch = r.u32(); c.feature = r.u32(); c.channels = r.u32(); c.num_groups = r.u32(); c.epsilon_bits = r.u64(); c.dtype = r.u8();
@@ -92,7 +100,7 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             c.input = r.buf(); c.output = r.buf(); c.element_count = r.u64(); c.src_dtype = r.u8(); c.dst_dtype = r.u8();
             break;
         }
-        case HOLO_K_RESHAPE: {
+        case HOLO_K_RESHAPE: case HOLO_K_SLICE: {
             HoloLayoutCall& c = out->u.layout;
             c.input = r.buf(); c.output = r.buf(); c.element_count = r.u64(); c.dtype = r.u8();
             break;
@@ -107,6 +115,13 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             HoloKvCacheWriteCall& c = out->u.kv_cache_write;
             c.cache = r.buf(); c.new_rows_buf = r.buf(); c.pos = r.buf(); c.output = r.buf();
             c.planes = r.u32(); c.bucket_rows = r.u32(); c.new_rows = r.u32(); c.row_bytes = r.u32();
+            break;
+        }
+        case HOLO_K_DECODE_ATTENTION: {
+            HoloDecodeAttentionCall& c = out->u.decode_attention;
+            c.q = r.buf(); c.k_past = r.buf(); c.v_past = r.buf(); c.k_new = r.buf(); c.v_new = r.buf(); c.mask = r.buf(); c.output = r.buf();
+            c.batch = r.u32(); c.heads = r.u32(); c.kv_heads = r.u32(); c.q_rows = r.u32(); c.past_len = r.u32(); c.new_len = r.u32();
+            c.head_dim = r.u32(); c.scale_bits = r.u32(); c.dtype = r.u8();
             break;
         }
         case HOLO_K_DECODE_ATTENTION_VALID: {

@@ -681,7 +681,7 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a) 
     const uint32_t G = a.h / a.hkv, planes = a.b * a.hkv;
     const bool aligned = (((uintptr_t)a.k_past | (uintptr_t)a.v_past | (uintptr_t)a.k_past_s | (uintptr_t)a.v_past_s |
                            (uintptr_t)a.k_new | (uintptr_t)a.v_new) & 15u) == 0;
-    const bool tiled = a.quantized && a.d == HD && a.m == 1 && a.nnew == 1 && G <= MAXG && a.past >= 4 && (a.past % 4) == 0 &&
+    const bool tiled = !a.mask && a.quantized && a.d == HD && a.m == 1 && a.nnew == 1 && G <= MAXG && a.past >= 4 && (a.past % 4) == 0 &&
                        aligned && planes <= 65535 && encode_tiled_fn() != nullptr && !getenv("HOLO_ATTN_FORCE_GENERIC");
     if (!tiled) {
         if (a.d > 32 * holo_attn::GEN_MAX_PER_LANE)

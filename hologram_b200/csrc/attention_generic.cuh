@@ -34,8 +34,12 @@ decode_attention_generic_kernel(HoloAttnArgs a) {
     const uint32_t d = a.d, h = a.h, m = a.m, hkv = a.hkv;
     const uint32_t bi = r / (h * m), hi = (r / m) % h, qi = r % m;
     const uint32_t kvh = bi * hkv + hi / (h / hkv);
-    const uint32_t vis_past = min(*a.valid_len, a.past);
-    const uint32_t new_vis = min(qi + 1, a.nnew);
+    // scalar-mask form: the first min(valid_len, past) cache rows, then chunk rows 0..qi;
+    // additive-mask form (decode_attention_row, cpu/float_kernels.rs:2420-2477): every key, the
+    // mask row added to the scaled score
+    const uint32_t vis_past = a.mask ? a.past : min(*a.valid_len, a.past);
+    const uint32_t new_vis = a.mask ? a.nnew : min(qi + 1, a.nnew);
+    const float* mask_row = a.mask ? a.mask + (uint64_t)qi * (a.past + a.nnew) : nullptr;
     const uint32_t vis = vis_past + new_vis;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -61,7 +65,11 @@ decode_attention_generic_kernel(HoloAttnArgs a) {
             if (c < d) part = fmaf(q[i], kv_elem<Q8>(kb, ks, row, d, c, a.dtype), part);
         }
         for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-        const float s = __fdiv_rn(part, a.scale_div);
+        float s = __fdiv_rn(part, a.scale_div);
+        if (mask_row) {
+            s = __fadd_rn(s, mask_row[kj]);
+            if (s == -INFINITY) continue;   // erased exactly: contributes 0 to the sum and the context
+        }
         const float nm = fmaxf(mx, s);
         const float corr = mx == -INFINITY ? 0.0f : expf(mx - nm);
         const float p = expf(s - nm);
@@ -98,8 +106,9 @@ decode_attention_generic_kernel(HoloAttnArgs a) {
             float wm = s_mem[(size_t)w * (d + 2) + d];
             if (wm != -INFINITY) acc += s_mem[(size_t)w * (d + 2) + c] * expf(wm - gm);
         }
-        // zero visible keys => exact zero vector (cpu/float_kernels.rs:3851-3854)
-        holo::store_float(a.out, (uint64_t)r * d + c, vis == 0 ? 0.0f : acc / denom, a.dtype);
+        // zero visible keys (or every key erased by the mask) => exact zero vector
+        // (cpu/float_kernels.rs:3851-3854, 2451-2454)
+        holo::store_float(a.out, (uint64_t)r * d + c, (vis == 0 || gm == -INFINITY) ? 0.0f : acc / denom, a.dtype);
     }
 }
 

@@ -164,8 +164,10 @@ int32_t holo_lut_table(holo_b200_ctx* ctx, uint8_t act, uint8_t dtype, const uin
 int32_t holo_launch_lut(holo_b200_ctx* ctx, const uint16_t* table, const uint16_t* in, uint16_t* out, uint64_t n);
 // glue.cu
 int32_t holo_launch_binary(holo_b200_ctx* ctx, int op, const void* a, const void* b, void* out, uint64_t n, uint8_t dtype);
-int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* gamma, void* out, uint32_t batch,
-                             uint32_t feature, float eps, uint8_t dtype);
+int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* residual, const void* gamma, void* out,
+                             uint32_t batch, uint32_t feature, float eps, uint8_t dtype);
+int32_t holo_launch_transpose(holo_b200_ctx* ctx, const uint8_t* in, uint8_t* out, uint32_t rank, const uint32_t* dims,
+                              const uint8_t* perm, uint32_t es);
 int32_t holo_launch_rope(holo_b200_ctx* ctx, const void* x, const void* c, const void* s, void* out, uint32_t head_dim,
                          uint64_t n, uint8_t dtype);
 int32_t holo_launch_gather(holo_b200_ctx* ctx, const uint8_t* data, const void* idx, uint8_t idx_dtype, uint8_t* out,
@@ -183,7 +185,8 @@ struct HoloAttnArgs {
     const void* q;
     const void *k_past, *v_past, *k_new, *v_new;              // bf16/f16/f32 rows, or i8 codes when quantized
     const float *k_past_s, *v_past_s, *k_new_s, *v_new_s;     // per-row scales (quantized form only)
-    const uint32_t* valid_len;
+    const uint32_t* valid_len;   // scalar-mask form
+    const float* mask;           // additive-mask form ([m, past + nnew] f32) when non-null: every key takes part
     void* out;
     uint32_t b, h, hkv, m, past, nnew, d;
     float scale_div;  // scores are divided by this
@@ -203,7 +206,7 @@ struct HoloMatmulSeg {
     uint8_t fused_act;
 };
 int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* b, uint32_t m, uint32_t k, uint32_t n,
-                                 const HoloMatmulSeg* segs, uint32_t nseg);
+                                 uint8_t dtype, const HoloMatmulSeg* segs, uint32_t nseg);
 // tp.cu
 int32_t holo_all_reduce(holo_b200_ctx* ctx, void* buf, uint64_t n, uint8_t dtype);
 int32_t holo_all_reduce_add(holo_b200_ctx* ctx, const void* partial, const void* residual, void* out, uint64_t n, uint8_t dtype);

@@ -46,6 +46,7 @@ struct GemmParams {
     uint32_t nseg;
     uint32_t* status;
     uint32_t m, n, k, kblocks, splits, box_m;
+    int dtype;                // HOLO_DTYPE_BF16 or HOLO_DTYPE_F16 (operands and output)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -108,12 +109,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// One bf16 result: truncate the accumulator, then the fused epilogue on the truncated value
+// One 16-bit result: narrow the accumulator (bf16: truncation; f16: the reference's
+// add-half rounding), then the fused epilogue on the narrowed value
 // (float_kernels.rs:844-847, 886-889).
-__device__ __forceinline__ uint16_t epilogue_elem(float acc, const uint16_t* table, const uint16_t* residual, uint64_t idx) {
-    uint16_t h = holo::f32_to_bf16_trunc(acc);
+__device__ __forceinline__ uint16_t epilogue_elem(float acc, const uint16_t* table, const uint16_t* residual, uint64_t idx, int dtype) {
+    uint16_t h = holo::narrow16(acc, dtype);
     if (table) h = __ldg(table + h);
-    if (residual) h = holo::f32_to_bf16_trunc(__fadd_rn(holo::bf16_to_f32(h), holo::bf16_to_f32(__ldg(residual + idx))));
+    if (residual) h = holo::narrow16(__fadd_rn(holo::widen16(h, dtype), holo::widen16(__ldg(residual + idx), dtype)), dtype);
     return h;
 }
 
@@ -190,8 +192,10 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0 && !*s_abort) {
-            // instruction descriptor: D = f32, A = B = bf16, A K-major, B N-major, N = BN, M = 128
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // instruction descriptor: D = f32, A = B = bf16 (format 1) or f16 (format 0), A K-major,
+            // B N-major, N = BN, M = 128
+            const uint32_t fmt = p.dtype == HOLO_DTYPE_BF16 ? 1u : 0u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             bool ok = true;
             for (uint32_t i = 0; i < nkb && ok; ++i) {
                 const uint32_t s = i % STAGES, use = i / STAGES;
@@ -235,8 +239,8 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         uint32_t w[16];
 #pragma unroll
                         for (int x = 0; x < 16; ++x) {
-                            uint16_t lo = epilogue_elem(__uint_as_float(v[2 * x]), sg.table, sg.residual, idx0 + 2 * x);
-                            uint16_t hi = epilogue_elem(__uint_as_float(v[2 * x + 1]), sg.table, sg.residual, idx0 + 2 * x + 1);
+                            uint16_t lo = epilogue_elem(__uint_as_float(v[2 * x]), sg.table, sg.residual, idx0 + 2 * x, p.dtype);
+                            uint16_t hi = epilogue_elem(__uint_as_float(v[2 * x + 1]), sg.table, sg.residual, idx0 + 2 * x + 1, p.dtype);
                             w[x] = (uint32_t)lo | ((uint32_t)hi << 16);
                         }
 #pragma unroll
@@ -245,7 +249,7 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     } else {
 #pragma unroll
                         for (int x = 0; x < 32; ++x)
-                            if (col0 + x < sg.col_end) dst[x] = epilogue_elem(__uint_as_float(v[x]), sg.table, sg.residual, idx0 + x);
+                            if (col0 + x < sg.col_end) dst[x] = epilogue_elem(__uint_as_float(v[x]), sg.table, sg.residual, idx0 + x, p.dtype);
                     }
                 }
             }
@@ -311,12 +315,12 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         if (col + 4 <= sg.col_end && ((uintptr_t)dst & 7u) == 0) {
                             uint16_t h[4];
 #pragma unroll
-                            for (int x = 0; x < 4; ++x) h[x] = epilogue_elem(a4[x], sg.table, sg.residual, idx + x);
+                            for (int x = 0; x < 4; ++x) h[x] = epilogue_elem(a4[x], sg.table, sg.residual, idx + x, p.dtype);
                             *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
                         } else {
 #pragma unroll
                             for (int x = 0; x < 4; ++x)
-                                if (col + x < sg.col_end) dst[x] = epilogue_elem(a4[x], sg.table, sg.residual, idx + x);
+                                if (col + x < sg.col_end) dst[x] = epilogue_elem(a4[x], sg.table, sg.residual, idx + x, p.dtype);
                         }
                     }
                 }
@@ -338,12 +342,13 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 
 
 // Shapes the tensor-core path cannot take (row pitches that are not 16-byte multiples,
-// unaligned bases) and tiny problems: one thread per output cell running the reference's
-// own per-cell recurrence, an ascending-k fused multiply-add chain (mul-then-add in the
-// n % 8 column tail, cpu/simd.rs:746-799) -- bit-identical to the CPU kernel.
-__global__ void matmul_bf16_cell_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, uint16_t* __restrict__ out,
-                                        const uint16_t* __restrict__ table, const uint16_t* __restrict__ residual, uint32_t m,
-                                        uint32_t k, uint32_t n) {
+// unaligned bases), tiny problems and every f32 product: one thread per output cell running the
+// reference's own per-cell recurrence, an ascending-k fused multiply-add chain (mul-then-add in
+// the n % 8 column tail, cpu/simd.rs:746-799) -- bit-identical to the CPU kernel. For f32 the
+// fused activation is the scalar function itself (no table exists for 32-bit patterns).
+__global__ void matmul_cell_kernel(const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ out,
+                                   const uint16_t* __restrict__ table, int act, const void* __restrict__ residual, uint32_t m,
+                                   uint32_t k, uint32_t n, int dtype) {
     holo_pdl_trigger();
     holo_pdl_wait();
     const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x, i = blockIdx.y;
@@ -351,10 +356,17 @@ __global__ void matmul_bf16_cell_kernel(const uint16_t* __restrict__ a, const ui
     const bool fused = j < n - (n % 8);
     float acc = 0.0f;
     for (uint32_t kk = 0; kk < k; ++kk) {
-        float av = holo::bf16_to_f32(a[(uint64_t)i * k + kk]), bv = holo::bf16_to_f32(b[(uint64_t)kk * n + j]);
+        float av = holo::load_float(a, (uint64_t)i * k + kk, dtype), bv = holo::load_float(b, (uint64_t)kk * n + j, dtype);
         acc = fused ? __fmaf_rn(av, bv, acc) : __fadd_rn(acc, __fmul_rn(av, bv));
     }
-    out[(uint64_t)i * n + j] = epilogue_elem(acc, table, residual, (uint64_t)i * n + j);
+    const uint64_t idx = (uint64_t)i * n + j;
+    if (dtype == HOLO_DTYPE_F32) {
+        if (act >= 0) acc = holo::lut_act_ref(act, acc);
+        if (residual) acc = __fadd_rn(acc, reinterpret_cast<const float*>(residual)[idx]);
+        reinterpret_cast<float*>(out)[idx] = acc;
+    } else {
+        reinterpret_cast<uint16_t*>(out)[idx] = epilogue_elem(acc, table, reinterpret_cast<const uint16_t*>(residual), idx, dtype);
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -402,31 +414,35 @@ int32_t launch_umma(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap
 
 }  // namespace
 
-static int32_t act_table(holo_b200_ctx* ctx, uint8_t fused_act, const uint16_t** table) {
+static int lut_id_of_fused(uint8_t fused_act) {
+    return fused_act == HOLO_FUSED_GELU ? HOLO_LUT_GELU : fused_act == HOLO_FUSED_SILU ? HOLO_LUT_SILU
+         : fused_act == HOLO_FUSED_SIGMOID ? HOLO_LUT_SIGMOID : fused_act == HOLO_FUSED_TANH ? HOLO_LUT_TANH : HOLO_LUT_EXP;
+}
+
+static int32_t act_table(holo_b200_ctx* ctx, uint8_t fused_act, uint8_t dtype, const uint16_t** table) {
     *table = nullptr;
     if (fused_act) {
         int act = fused_act == HOLO_FUSED_GELU ? HOLO_LUT_GELU : fused_act == HOLO_FUSED_SILU ? HOLO_LUT_SILU
                 : fused_act == HOLO_FUSED_SIGMOID ? HOLO_LUT_SIGMOID : fused_act == HOLO_FUSED_TANH ? HOLO_LUT_TANH : HOLO_LUT_EXP;
-        HOLO_TRY(holo_lut_table(ctx, (uint8_t)act, HOLO_DTYPE_BF16, table));
+        HOLO_TRY(holo_lut_table(ctx, (uint8_t)act, dtype, table));
     }
     return HOLO_OK;
 }
 
 int32_t holo_launch_matmul(holo_b200_ctx* ctx, const void* a, const void* b, void* out, uint32_t m, uint32_t k, uint32_t n,
                            uint8_t dtype, uint8_t fused_act, const void* residual) {
-    (void)dtype;
     HoloMatmulSeg sg = {out, residual, n, fused_act};
-    return holo_launch_matmul_multi(ctx, a, b, m, k, n, &sg, 1);
+    return holo_launch_matmul_multi(ctx, a, b, m, k, n, dtype, &sg, 1);
 }
 
 // C[:, segment i] = epilogue_i(A . B[:, segment i]) for 1..3 column segments of one [k, n] B.
 int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* b, uint32_t m, uint32_t k, uint32_t n,
-                                 const HoloMatmulSeg* segs, uint32_t nseg) {
+                                 uint8_t dtype, const HoloMatmulSeg* segs, uint32_t nseg) {
     if (nseg < 1 || nseg > MAX_SEGS) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul segment count %u", nseg);
     GemmSeg gs[MAX_SEGS] = {};
     uint32_t col = 0;
     for (uint32_t i = 0; i < nseg; ++i) {
-        HOLO_TRY(act_table(ctx, segs[i].fused_act, &gs[i].table));
+        if (dtype != HOLO_DTYPE_F32) HOLO_TRY(act_table(ctx, segs[i].fused_act, dtype, &gs[i].table));
         gs[i].out = (uint16_t*)segs[i].out;
         gs[i].residual = (const uint16_t*)segs[i].residual;
         gs[i].col_begin = col;
@@ -438,15 +454,15 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     const uint16_t* table = gs[0].table;
     const void* residual = gs[0].residual;
     void* out = gs[0].out;
-    const bool tma_ok = (k % 8) == 0 && (n % 8) == 0 && (((uintptr_t)a | (uintptr_t)b) & 15u) == 0 && encode_tiled_fn() != nullptr;
+    const bool tma_ok = dtype != HOLO_DTYPE_F32 && (k % 8) == 0 && (n % 8) == 0 && (((uintptr_t)a | (uintptr_t)b) & 15u) == 0 && encode_tiled_fn() != nullptr;
     const bool tiny = (uint64_t)m * n * k < (1ull << 18);
     if (nseg > 1 && (!tma_ok || tiny))
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: merged matmul needs the tensor-core path");
     if (!tma_ok || tiny || getenv("HOLO_GEMM_FORCE_CELL")) {
         dim3 grid((n + 127) / 128, m);
         if (m > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul m %u on the per-cell path", m);
-        HOLO_CUDA(holo_launch_kernel(ctx, matmul_bf16_cell_kernel, dim3(grid), dim3(128), 0, 1, (const uint16_t*)a, (const uint16_t*)b, (uint16_t*)out, table,
-                                                            (const uint16_t*)residual, m, k, n));
+        HOLO_CUDA(holo_launch_kernel(ctx, matmul_cell_kernel, dim3(grid), dim3(128), 0, 1, a, b, out, table,
+                                     segs[0].fused_act ? lut_id_of_fused(segs[0].fused_act) : -1, residual, m, k, n, (int)dtype));
         HOLO_CUDA(cudaGetLastError());
         ctx->launches++;
         return HOLO_OK;
@@ -471,7 +487,7 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
         } else {
             bn = tiles128 >= 16 ? 128 : 64;
             const uint32_t tiles = bn == 128 ? tiles128 : tiles64;
-            splits = (256 + tiles - 1) / tiles;
+            splits = (192 + tiles - 1) / tiles;   // measured: about one CTA per SM beats two at these sizes
             if (splits > 8) splits = 8;
             if (splits > kblocks / 8) splits = kblocks / 8 ? kblocks / 8 : 1;
         }
@@ -490,6 +506,7 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     p.status = ctx->dev_status;
     p.m = m; p.n = n; p.k = k; p.kblocks = kblocks; p.splits = splits;
     p.box_m = m < (uint32_t)BM ? m : (uint32_t)BM;
+    p.dtype = dtype;
     CUtensorMap ma, mb;
     HOLO_TRY(make_map_2d(&ma, a, k, m, BK, p.box_m));
     HOLO_TRY(make_map_2d(&mb, b, n, k, 64, BK));

@@ -63,8 +63,10 @@ __global__ void binary16_vec_kernel(int op, const uint4* __restrict__ a, const u
 
 // rms_norm_float, cpu/float_kernels.rs:1683-1756: inv = 1/sqrt(sumsq/f + eps),
 // out = x * inv * gamma (left to right). One CTA per row.
-__global__ void rms_norm_kernel(const void* __restrict__ x, const void* __restrict__ gamma, void* __restrict__ out,
-                                uint32_t feature, float eps, int dtype) {
+// With `residual` (add_rms_norm_float, :1567-1681) the row is x + residual, summed in f32 and not
+// narrowed before the norm.
+__global__ void rms_norm_kernel(const void* __restrict__ x, const void* __restrict__ residual, const void* __restrict__ gamma,
+                                void* __restrict__ out, uint32_t feature, float eps, int dtype) {
     holo_pdl_trigger();
     holo_pdl_wait();
     __shared__ float s_part[32];
@@ -73,6 +75,7 @@ __global__ void rms_norm_kernel(const void* __restrict__ x, const void* __restri
     float acc = 0.0f;
     for (uint32_t j = threadIdx.x; j < feature; j += blockDim.x) {
         float v = holo::load_float(x, off + j, dtype);
+        if (residual) v = __fadd_rn(v, holo::load_float(residual, off + j, dtype));
         acc = fmaf(v, v, acc);
     }
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -87,7 +90,9 @@ __global__ void rms_norm_kernel(const void* __restrict__ x, const void* __restri
     const float inv = s_inv;
     for (uint32_t j = threadIdx.x; j < feature; j += blockDim.x) {
         float g = gamma ? holo::load_float(gamma, j, dtype) : 1.0f;
-        float v = __fmul_rn(__fmul_rn(holo::load_float(x, off + j, dtype), inv), g);
+        float xv = holo::load_float(x, off + j, dtype);
+        if (residual) xv = __fadd_rn(xv, holo::load_float(residual, off + j, dtype));
+        float v = __fmul_rn(__fmul_rn(xv, inv), g);
         holo::store_float(out, off + j, v, dtype);
     }
 }
@@ -95,8 +100,8 @@ __global__ void rms_norm_kernel(const void* __restrict__ x, const void* __restri
 // 16-bit rows with feature % 8 == 0 and feature <= 8192: one pass, eight elements per thread
 // held in registers between the reduction and the scaling.
 __global__ void __launch_bounds__(1024)
-rms_norm16_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gamma, uint4* __restrict__ out,
-                      uint32_t feature, float eps, int dtype) {
+rms_norm16_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ residual, const uint4* __restrict__ gamma,
+                      uint4* __restrict__ out, uint32_t feature, float eps, int dtype) {
     holo_pdl_trigger();
     holo_pdl_wait();
     __shared__ float s_part[32];
@@ -113,6 +118,15 @@ rms_norm16_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gam
         for (int i = 0; i < 4; ++i) {
             v[2 * i] = holo::widen16((uint16_t)(pw[i] & 0xffffu), dtype);
             v[2 * i + 1] = holo::widen16((uint16_t)(pw[i] >> 16), dtype);
+        }
+        if (residual) {
+            uint4 rw = residual[off + threadIdx.x];
+            const uint32_t* pr = &rw.x;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __fadd_rn(v[2 * i], holo::widen16((uint16_t)(pr[i] & 0xffffu), dtype));
+                v[2 * i + 1] = __fadd_rn(v[2 * i + 1], holo::widen16((uint16_t)(pr[i] >> 16), dtype));
+            }
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc = fmaf(v[i], v[i], acc);
@@ -140,6 +154,34 @@ rms_norm16_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gam
         pr[i] = (uint32_t)holo::narrow16(r0, dtype) | ((uint32_t)holo::narrow16(r1, dtype) << 16);
     }
     out[off + threadIdx.x] = r;
+}
+
+// transpose_float, cpu/float_kernels.rs:2980-3027: output axis i is input axis perm[i]; every
+// output element is gathered from its permuted input position (element size 1, 2, 4 or 8 bytes).
+struct TransposeParams {
+    uint32_t out_dims[8];
+    uint64_t in_strides_perm[8];   // stride (in elements) of the input axis feeding output axis i
+    uint32_t rank, es;
+    uint64_t total;
+};
+__global__ void transpose_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, const TransposeParams p) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; o < p.total; o += stride) {
+        uint64_t rem = o, src = 0;
+        for (int i = (int)p.rank - 1; i >= 0; --i) {
+            const uint32_t c = (uint32_t)(rem % p.out_dims[i]);
+            rem /= p.out_dims[i];
+            src += (uint64_t)c * p.in_strides_perm[i];
+        }
+        switch (p.es) {
+            case 1: out[o] = in[src]; break;
+            case 2: reinterpret_cast<uint16_t*>(out)[o] = reinterpret_cast<const uint16_t*>(in)[src]; break;
+            case 4: reinterpret_cast<uint32_t*>(out)[o] = reinterpret_cast<const uint32_t*>(in)[src]; break;
+            default: reinterpret_cast<uint64_t*>(out)[o] = reinterpret_cast<const uint64_t*>(in)[src]; break;
+        }
+    }
 }
 
 // rope_float, cpu/float_kernels.rs:3123-3190 (rotate-half; cos/sin share x's layout).
@@ -458,17 +500,39 @@ int32_t holo_launch_binary(holo_b200_ctx* ctx, int op, const void* a, const void
     return HOLO_OK;
 }
 
-int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* gamma, void* out, uint32_t batch,
+int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* residual, const void* gamma, void* out, uint32_t batch,
                              uint32_t feature, float eps, uint8_t dtype) {
     if (batch == 0 || feature == 0) return HOLO_OK;
     const bool vec = dtype != HOLO_DTYPE_F32 && (feature % 8) == 0 && feature <= 8192 &&
-                     (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)out) & 15u) == 0;
+                     (((uintptr_t)x | (uintptr_t)residual | (uintptr_t)gamma | (uintptr_t)out) & 15u) == 0;
     if (vec) {
         uint32_t threads = ((feature / 8 + 31) / 32) * 32;
-        HOLO_CUDA(holo_launch_kernel(ctx, rms_norm16_vec_kernel, dim3(batch), dim3(threads), 0, 1, (const uint4*)x, (const uint4*)gamma, (uint4*)out, feature, eps, dtype));
+        HOLO_CUDA(holo_launch_kernel(ctx, rms_norm16_vec_kernel, dim3(batch), dim3(threads), 0, 1, (const uint4*)x, (const uint4*)residual,
+                                     (const uint4*)gamma, (uint4*)out, feature, eps, (int)dtype));
     } else {
-        HOLO_CUDA(holo_launch_kernel(ctx, rms_norm_kernel, dim3(batch), dim3(256), 0, 1, x, gamma, out, feature, eps, dtype));
+        HOLO_CUDA(holo_launch_kernel(ctx, rms_norm_kernel, dim3(batch), dim3(256), 0, 1, x, residual, gamma, out, feature, eps, (int)dtype));
     }
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_transpose(holo_b200_ctx* ctx, const uint8_t* in, uint8_t* out, uint32_t rank, const uint32_t* dims,
+                              const uint8_t* perm, uint32_t es) {
+    TransposeParams p = {};
+    uint64_t in_strides[8], stride = 1;
+    for (int i = (int)rank - 1; i >= 0; --i) {
+        in_strides[i] = stride;
+        stride *= dims[i];
+    }
+    p.total = stride;
+    p.rank = rank;
+    p.es = es;
+    for (uint32_t i = 0; i < rank; ++i) {
+        p.out_dims[i] = dims[perm[i]];
+        p.in_strides_perm[i] = in_strides[perm[i]];
+    }
+    if (p.total == 0) return HOLO_OK;
+    HOLO_CUDA(holo_launch_kernel(ctx, transpose_kernel, dim3(ew_blocks(p.total)), dim3(EW_THREADS), 0, 1, in, out, p));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }

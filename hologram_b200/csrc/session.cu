@@ -240,7 +240,7 @@ int32_t run_merged(holo_b200_session* s, const MergedMatmul& g) {
         segs[t].width = g.width[t];
         segs[t].fused_act = g.act[t];
     }
-    return holo_launch_matmul_multi(s->ctx, a, g.b_concat, g.m, g.k, g.n, segs, g.nseg);
+    return holo_launch_matmul_multi(s->ctx, a, g.b_concat, g.m, g.k, g.n, HOLO_DTYPE_BF16, segs, g.nseg);
 }
 
 // Tensor parallel: an AllReduce over a buffer, directly followed by the Add of that buffer and

@@ -35,7 +35,7 @@ def encode_call(call):
     out = struct.pack("<H", k)
     if k in (kc.K_SIGMOID, kc.K_TANH, kc.K_GELU, kc.K_SILU, kc.K_EXP, kc.K_ERF):
         return out + _unary(u.unary)
-    if k in (kc.K_ADD, kc.K_MUL):
+    if k in (kc.K_ADD, kc.K_MUL, kc.K_CONCAT):
         return out + _binary(u.binary)
     if k == kc.K_MATMUL:
         return out + _matmul(u.matmul)
@@ -43,7 +43,7 @@ def encode_call(call):
         return out + _matmul(u.matmul_activation.mm) + struct.pack("<B", u.matmul_activation.act)
     if k == kc.K_MATMUL_ADD:
         return out + _matmul(u.matmul_add.mm) + _buf(u.matmul_add.residual)
-    if k == kc.K_RMS_NORM:
+    if k in (kc.K_RMS_NORM, kc.K_ADD_RMS_NORM):
         c = u.norm
         return out + _buf(c.x) + _buf(c.gamma) + _buf(c.beta) + _buf(c.residual) + _buf(c.output) + struct.pack(
             "<IIIIQB", c.batch, c.feature, c.channels, c.num_groups, c.epsilon_bits, c.dtype)
@@ -57,7 +57,10 @@ def encode_call(call):
     if k == kc.K_CAST:
         c = u.cast
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<QBB", c.element_count, c.src_dtype, c.dst_dtype)
-    if k == kc.K_RESHAPE:
+    if k == kc.K_TRANSPOSE:
+        c = u.transpose
+        return out + _buf(c.input) + _buf(c.output) + struct.pack("<B8I8BB", c.rank, *c.dims, *c.perm, c.dtype)
+    if k in (kc.K_RESHAPE, kc.K_SLICE):
         c = u.layout
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<QB", c.element_count, c.dtype)
     if k == kc.K_DEQUANTIZE:
@@ -68,9 +71,10 @@ def encode_call(call):
         c = u.kv_cache_write
         return out + _buf(c.cache) + _buf(c.new) + _buf(c.pos) + _buf(c.output) + struct.pack(
             "<IIII", c.planes, c.bucket_rows, c.new_rows, c.row_bytes)
-    if k == kc.K_DECODE_ATTENTION_VALID:
-        c = u.decode_attention_valid
-        bufs = b"".join(_buf(b) for b in (c.q, c.k_past, c.v_past, c.k_new, c.v_new, c.valid_len, c.output))
+    if k in (kc.K_DECODE_ATTENTION, kc.K_DECODE_ATTENTION_VALID):
+        c = u.decode_attention if k == kc.K_DECODE_ATTENTION else u.decode_attention_valid
+        sixth = c.mask if k == kc.K_DECODE_ATTENTION else c.valid_len
+        bufs = b"".join(_buf(b) for b in (c.q, c.k_past, c.v_past, c.k_new, c.v_new, sixth, c.output))
         return out + bufs + struct.pack("<IIIIIIIIB", c.batch, c.heads, c.kv_heads, c.q_rows, c.past_len, c.new_len,
                                         c.head_dim, c.scale_bits, c.dtype)
     # extension discriminants (no counterpart in the reference codec)

@@ -20,6 +20,8 @@ FUSED_RELU, FUSED_GELU, FUSED_SILU, FUSED_SIGMOID, FUSED_TANH, FUSED_EXP = 1, 2,
 K_ADD, K_MUL = 5, 7
 K_SIGMOID, K_TANH, K_GELU, K_SILU, K_EXP, K_ERF = 12, 13, 14, 15, 18, 32
 K_MATMUL, K_RMS_NORM, K_RESHAPE, K_ROTARY = 46, 51, 60, 75
+K_ADD_RMS_NORM, K_TRANSPOSE, K_CONCAT, K_SLICE = 54, 61, 62, 63
+K_DECODE_ATTENTION = 119
 K_DEQUANTIZE, K_MATMUL_ACTIVATION, K_MATMUL_ADD = 105, 106, 107
 K_GATHER, K_CAST, K_KV_CACHE_WRITE, K_DECODE_ATTENTION_VALID = 114, 115, 120, 121
 K_QUANTIZE_ROWS_I8, K_DECODE_ATTENTION_VALID_Q8, K_ALL_REDUCE = 0x8001, 0x8002, 0x8003
@@ -92,6 +94,20 @@ class LayoutCall(C.Structure):
     _fields_ = [("input", BufferRef), ("output", BufferRef), ("element_count", C.c_uint64), ("dtype", C.c_uint8)]
 
 
+class TransposeCall(C.Structure):
+    """kernel_call.rs:491-499: output axis i is input axis perm[i]."""
+    _fields_ = [("input", BufferRef), ("output", BufferRef), ("rank", C.c_uint8), ("dims", C.c_uint32 * 8),
+                ("perm", C.c_uint8 * 8), ("dtype", C.c_uint8)]
+
+    @classmethod
+    def make(cls, inp, out, dims, perm, dtype):
+        c = cls()
+        c.input, c.output, c.rank, c.dtype = inp, out, len(dims), dtype
+        for i, (d, p) in enumerate(zip(dims, perm)):
+            c.dims[i], c.perm[i] = d, p
+        return c
+
+
 class DequantizeCall(C.Structure):
     _fields_ = [("input", BufferRef), ("scales", BufferRef), ("zero_points", BufferRef), ("output", BufferRef),
                 ("element_count", C.c_uint64), ("channels", C.c_uint32), ("inner", C.c_uint32),
@@ -108,6 +124,14 @@ class KvCacheWriteCall(C.Structure):
 class DecodeAttentionValidCall(C.Structure):
     _fields_ = [("q", BufferRef), ("k_past", BufferRef), ("v_past", BufferRef), ("k_new", BufferRef),
                 ("v_new", BufferRef), ("valid_len", BufferRef), ("output", BufferRef), ("batch", C.c_uint32),
+                ("heads", C.c_uint32), ("kv_heads", C.c_uint32), ("q_rows", C.c_uint32), ("past_len", C.c_uint32),
+                ("new_len", C.c_uint32), ("head_dim", C.c_uint32), ("scale_bits", C.c_uint32), ("dtype", C.c_uint8)]
+
+
+class DecodeAttentionCall(C.Structure):
+    """The additive-mask form (kernel_call.rs:632-655): mask is f32 [q_rows, past_len + new_len]."""
+    _fields_ = [("q", BufferRef), ("k_past", BufferRef), ("v_past", BufferRef), ("k_new", BufferRef),
+                ("v_new", BufferRef), ("mask", BufferRef), ("output", BufferRef), ("batch", C.c_uint32),
                 ("heads", C.c_uint32), ("kv_heads", C.c_uint32), ("q_rows", C.c_uint32), ("past_len", C.c_uint32),
                 ("new_len", C.c_uint32), ("head_dim", C.c_uint32), ("scale_bits", C.c_uint32), ("dtype", C.c_uint8)]
 
@@ -133,7 +157,8 @@ class _Payload(C.Union):
     _fields_ = [("unary", UnaryCall), ("binary", BinaryCall), ("matmul", MatMulCall),
                 ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("norm", NormCall),
                 ("rope", RoPECall), ("gather", GatherCall), ("cast", CastCall), ("layout", LayoutCall),
-                ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
+                ("transpose", TransposeCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
+                ("decode_attention", DecodeAttentionCall),
                 ("decode_attention_valid", DecodeAttentionValidCall), ("quantize_rows_i8", QuantizeRowsI8Call),
                 ("decode_attention_valid_q8", DecodeAttentionValidQ8Call), ("all_reduce", AllReduceCall)]
 
@@ -177,6 +202,14 @@ class KernelCall(C.Structure):
     @classmethod
     def RmsNorm(cls, c): return cls.of(K_RMS_NORM, c)
     @classmethod
+    def AddRmsNorm(cls, c): return cls.of(K_ADD_RMS_NORM, c)
+    @classmethod
+    def Transpose(cls, c): return cls.of(K_TRANSPOSE, c)
+    @classmethod
+    def Concat(cls, c): return cls.of(K_CONCAT, c)
+    @classmethod
+    def Slice(cls, c): return cls.of(K_SLICE, c)
+    @classmethod
     def RotaryEmbedding(cls, c): return cls.of(K_ROTARY, c)
     @classmethod
     def Gather(cls, c): return cls.of(K_GATHER, c)
@@ -188,6 +221,8 @@ class KernelCall(C.Structure):
     def Dequantize(cls, c): return cls.of(K_DEQUANTIZE, c)
     @classmethod
     def KvCacheWrite(cls, c): return cls.of(K_KV_CACHE_WRITE, c)
+    @classmethod
+    def DecodeAttention(cls, c): return cls.of(K_DECODE_ATTENTION, c)
     @classmethod
     def DecodeAttentionValid(cls, c): return cls.of(K_DECODE_ATTENTION_VALID, c)
     @classmethod
@@ -201,8 +236,8 @@ class KernelCall(C.Structure):
 KernelCall._FIELD = {
     UnaryCall: "unary", BinaryCall: "binary", MatMulCall: "matmul", MatMulActivationCall: "matmul_activation",
     MatMulAddCall: "matmul_add", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
-    LayoutCall: "layout", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
-    DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
+    LayoutCall: "layout", TransposeCall: "transpose", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
+    DecodeAttentionCall: "decode_attention", DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
     DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce",
 }
 

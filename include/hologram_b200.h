@@ -74,13 +74,18 @@ extern "C" {
 #define HOLO_K_ERF 32
 #define HOLO_K_MATMUL 46
 #define HOLO_K_RMS_NORM 51
+#define HOLO_K_ADD_RMS_NORM 54
 #define HOLO_K_RESHAPE 60
+#define HOLO_K_TRANSPOSE 61
+#define HOLO_K_CONCAT 62
+#define HOLO_K_SLICE 63
 #define HOLO_K_ROTARY 75
 #define HOLO_K_DEQUANTIZE 105
 #define HOLO_K_MATMUL_ACTIVATION 106
 #define HOLO_K_MATMUL_ADD 107
 #define HOLO_K_GATHER 114
 #define HOLO_K_CAST 115
+#define HOLO_K_DECODE_ATTENTION 119
 #define HOLO_K_KV_CACHE_WRITE 120
 #define HOLO_K_DECODE_ATTENTION_VALID 121
 /* Extensions (the reference has no KV quantizer op and no quantized-KV attention):
@@ -146,6 +151,15 @@ typedef struct HoloNormCall {
     uint8_t dtype;
 } HoloNormCall;
 
+/* TransposeCall (kernel_call.rs:491-499): output axis i is input axis perm[i]; rank <= 8 */
+typedef struct HoloTransposeCall {
+    HoloBufferRef input, output;
+    uint8_t rank;
+    uint32_t dims[8];
+    uint8_t perm[8];
+    uint8_t dtype;
+} HoloTransposeCall;
+
 /* RoPECall (kernel_call.rs:506-514): cos/sin are full tensors with x's element layout */
 typedef struct HoloRoPECall {
     HoloBufferRef x, cos, sin, output;
@@ -193,6 +207,16 @@ typedef struct HoloKvCacheWriteCall {
     uint32_t planes, bucket_rows, new_rows, row_bytes;
 } HoloKvCacheWriteCall;
 
+/* DecodeAttentionCall (kernel_call.rs:632-655), the additive-mask form: every past and new key
+ * takes part, `mask` is f32 [q_rows, past_len + new_len] shared by batch and heads and is added to
+ * the scaled score (-inf erases a key exactly); a row whose keys are all erased is the zero
+ * vector. q_rows is independent of new_len; past_len + new_len must be at least 1. */
+typedef struct HoloDecodeAttentionCall {
+    HoloBufferRef q, k_past, v_past, k_new, v_new, mask, output;
+    uint32_t batch, heads, kv_heads, q_rows, past_len, new_len, head_dim, scale_bits;
+    uint8_t dtype;
+} HoloDecodeAttentionCall;
+
 /* DecodeAttentionValidCall (kernel_call.rs:691-716) */
 typedef struct HoloDecodeAttentionValidCall {
     HoloBufferRef q, k_past, v_past, k_new, v_new, valid_len, output;
@@ -234,17 +258,19 @@ typedef struct HoloKernelCall {
     uint16_t kind; /* HOLO_K_* */
     union {
         HoloUnaryCall unary;            /* SIGMOID TANH GELU SILU EXP ERF */
-        HoloBinaryCall binary;          /* ADD MUL */
+        HoloBinaryCall binary;          /* ADD MUL CONCAT (out = a || b, extents taken from the BufferRefs) */
         HoloMatMulCall matmul;          /* MATMUL */
         HoloMatMulActivationCall matmul_activation;
         HoloMatMulAddCall matmul_add;
-        HoloNormCall norm;              /* RMS_NORM */
+        HoloNormCall norm;              /* RMS_NORM, ADD_RMS_NORM (norm of x + residual) */
         HoloRoPECall rope;              /* ROTARY */
         HoloGatherCall gather;
         HoloCastCall cast;
-        HoloLayoutCall layout;          /* RESHAPE */
+        HoloLayoutCall layout;          /* RESHAPE SLICE (contiguous copies; a slice's start is the input ref's offset) */
+        HoloTransposeCall transpose;
         HoloDequantizeCall dequantize;
         HoloKvCacheWriteCall kv_cache_write;
+        HoloDecodeAttentionCall decode_attention;
         HoloDecodeAttentionValidCall decode_attention_valid;
         HoloQuantizeRowsI8Call quantize_rows_i8;
         HoloDecodeAttentionValidQ8Call decode_attention_valid_q8;

@@ -438,6 +438,57 @@ int holo_or_rms_norm(const void* x, const void* gamma, void* out, uint32_t batch
     return 0;
 }
 
+/* ---- AddRmsNorm: rms_norm over x + residual, the sum kept in f32 (not narrowed) before the
+ * norm; a null residual makes it RmsNorm. cpu/float_kernels.rs:1567-1681 (generic-dtype loop
+ * :1656-1679). */
+int holo_or_add_rms_norm(const void* x, const void* residual, const void* gamma, void* out, uint32_t batch,
+                         uint32_t feature, uint64_t epsilon_bits, int dtype) {
+    float eps;
+    if (epsilon_bits == 0) eps = 1e-9f;
+    else {
+        eps = f32_from_bits((uint32_t)epsilon_bits);
+        if (!(isfinite(eps) && eps > 0.0f)) return -3;
+    }
+    for (uint32_t bi = 0; bi < batch; ++bi) {
+        size_t off = (size_t)bi * feature;
+        float sumsq = 0.0f;
+        for (uint32_t j = 0; j < feature; ++j) {
+            float v = read_float(x, off + j, dtype) + (residual ? read_float(residual, off + j, dtype) : 0.0f);
+            sumsq += v * v;
+        }
+        float inv_rms = 1.0f / sqrtf(sumsq / (float)feature + eps);
+        for (uint32_t j = 0; j < feature; ++j) {
+            float v = read_float(x, off + j, dtype) + (residual ? read_float(residual, off + j, dtype) : 0.0f);
+            float g = gamma ? read_float(gamma, j, dtype) : 1.0f;
+            write_float(out, off + j, v * inv_rms * g, dtype);
+        }
+    }
+    return 0;
+}
+
+/* ---- Transpose: output axis i is input axis perm[i]; gather per output element.
+ * cpu/float_kernels.rs:2980-3027. */
+int holo_or_transpose(const uint8_t* in, uint8_t* out, uint32_t rank, const uint32_t* dims, const uint8_t* perm, uint32_t es) {
+    if (rank == 0 || rank > 8) return -3;
+    size_t in_strides[8], out_dims[8], coord[8], total = 1, stride = 1;
+    for (int i = (int)rank - 1; i >= 0; --i) {
+        in_strides[i] = stride;
+        stride *= dims[i];
+    }
+    total = stride;
+    for (uint32_t i = 0; i < rank; ++i) out_dims[i] = dims[perm[i]];
+    for (size_t o = 0; o < total; ++o) {
+        size_t rem = o, in_idx = 0;
+        for (int i = (int)rank - 1; i >= 0; --i) {
+            coord[i] = rem % out_dims[i];
+            rem /= out_dims[i];
+        }
+        for (uint32_t i = 0; i < rank; ++i) in_idx += coord[i] * in_strides[perm[i]];
+        memcpy(out + o * es, in + in_idx * es, es);
+    }
+    return 0;
+}
+
 /* ---- RoPE (rotate-half, cos/sin given with x's layout): cpu/float_kernels.rs:3123-3190 - */
 int holo_or_rope(const void* x, const void* cosv, const void* sinv, void* out, uint32_t head_dim,
                  uint64_t n, int dtype) {
@@ -595,6 +646,64 @@ int holo_or_decode_attention_valid(const void* q, const void* kp, const void* vp
         for (size_t i = 0; i < qt; ++i) write_float(out, i, o32[i], dtype);
     free(q32); free(kp32); free(vp32); free(kn32); free(vn32); free(o32);
     return rc;
+}
+
+/* Additive-mask form: decode_attention_row, cpu/float_kernels.rs:2420-2477 (all past and new keys,
+ * score = dot / scale + mask[qi][kj]; every key erased => zero vector), engine and dtype front end
+ * :2482-2600 (mask f32 [q_rows, past + new]; widen, run in f32, narrow). */
+int holo_or_decode_attention_mask(const void* q, const void* kp, const void* vp, const void* kn, const void* vn,
+                                  const float* mask, void* out, uint32_t b, uint32_t h, uint32_t kv_heads,
+                                  uint32_t q_rows, uint32_t past, uint32_t new_len, uint32_t d, uint32_t scale_bits,
+                                  int dtype) {
+    if (dtype != HOLO_DTYPE_F32 && dtype != HOLO_DTYPE_BF16 && dtype != HOLO_DTYPE_F16) return -3;
+    if (b == 0 || h == 0 || q_rows == 0 || d == 0) return 0;
+    size_t l = (size_t)past + new_len;
+    if (l == 0) return -3;
+    uint32_t hkv = kv_heads == 0 ? h : kv_heads;
+    if (hkv == 0 || h % hkv != 0) return -3;
+    float scale, dflt = sqrtf((float)d);
+    if (dflt < 1.0f) dflt = 1.0f;
+    if (scale_bits == 0) scale = dflt;
+    else {
+        float sm = f32_from_bits(scale_bits);
+        scale = sm > 0.0f ? 1.0f / sm : dflt;
+    }
+    size_t rows = (size_t)b * h * q_rows, group = h / hkv;
+    float* sc = (float*)malloc(sizeof(float) * (l + 1));
+    float* qrow = (float*)malloc(sizeof(float) * d);
+    float* krow = (float*)malloc(sizeof(float) * d);
+    float* orow = (float*)malloc(sizeof(float) * d);
+    for (size_t r = 0; r < rows; ++r) {
+        size_t bi = r / ((size_t)h * q_rows), hi = (r / q_rows) % h, qi = r % q_rows;
+        size_t kvh = bi * hkv + hi / group;
+        for (size_t j = 0; j < d; ++j) qrow[j] = read_float(q, r * d + j, dtype);
+        for (size_t kj = 0; kj < l; ++kj) {
+            for (size_t j = 0; j < d; ++j)
+                krow[j] = kj < past ? read_float(kp, (kvh * past + kj) * d + j, dtype)
+                                    : read_float(kn, (kvh * new_len + (kj - past)) * d + j, dtype);
+            sc[kj] = dot_avx2_order(qrow, krow, d) / scale + mask[qi * l + kj];
+        }
+        float mx = -INFINITY;
+        for (size_t kj = 0; kj < l; ++kj) mx = sc[kj] > mx ? sc[kj] : (mx != mx ? sc[kj] : mx);   /* f32::max fold */
+        for (size_t j = 0; j < d; ++j) orow[j] = 0.0f;
+        if (mx != -INFINITY) {
+            for (size_t kj = 0; kj < l; ++kj) sc[kj] = holo_or_exp_det(sc[kj] - mx);
+            float sum = 0.0f;
+            for (size_t kj = 0; kj < l; ++kj) sum += sc[kj];
+            float denom = sum > 1e-30f ? sum : 1e-30f;
+            for (size_t kj = 0; kj < l; ++kj) {
+                float p = sc[kj] / denom;
+                for (size_t j = 0; j < d; ++j) {
+                    float v = kj < past ? read_float(vp, (kvh * past + kj) * d + j, dtype)
+                                        : read_float(vn, (kvh * new_len + (kj - past)) * d + j, dtype);
+                    orow[j] = orow[j] + p * v;
+                }
+            }
+        }
+        for (size_t j = 0; j < d; ++j) write_float(out, r * d + j, orow[j], dtype);
+    }
+    free(sc); free(qrow); free(krow); free(orow);
+    return 0;
 }
 
 /* Decode attention over an int8 KV cache, as the composition of reference ops the path is

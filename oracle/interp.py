@@ -55,6 +55,23 @@ def run(calls, slots, all_reduce=None):
             x = _get(slots, c.x, c.batch * c.feature * es(c.dtype), c.dtype)
             g = _get(slots, c.gamma, c.feature * es(c.dtype), c.dtype) if c.gamma.slot != kc.NO_SLOT else None
             _put(slots, c.output, orc.rms_norm(x, g, c.batch, c.feature, c.epsilon_bits, c.dtype))
+        elif k == kc.K_CONCAT:
+            c = u.binary
+            a = slots[c.a.slot][c.a.offset:c.a.offset + c.a.length] if c.a.length else slots[c.a.slot][c.a.offset:]
+            b = slots[c.b.slot][c.b.offset:c.b.offset + c.b.length] if c.b.length else slots[c.b.slot][c.b.offset:]
+            _put(slots, c.output, np.concatenate([a, b]))
+        elif k == kc.K_ADD_RMS_NORM:
+            c = u.norm
+            n = c.batch * c.feature * es(c.dtype)
+            x = _get(slots, c.x, n, c.dtype)
+            r = _get(slots, c.residual, n, c.dtype) if c.residual.slot != kc.NO_SLOT else None
+            g = _get(slots, c.gamma, c.feature * es(c.dtype), c.dtype) if c.gamma.slot != kc.NO_SLOT else None
+            _put(slots, c.output, orc.add_rms_norm(x, r, g, c.batch, c.feature, c.epsilon_bits, c.dtype))
+        elif k == kc.K_TRANSPOSE:
+            c = u.transpose
+            dims = [c.dims[i] for i in range(c.rank)]
+            total = int(np.prod(dims)) * es(c.dtype)
+            _put(slots, c.output, orc.transpose(_get(slots, c.input, total, kc.DTYPE_U8), dims, [c.perm[i] for i in range(c.rank)], es(c.dtype)))
         elif k == kc.K_ROTARY:
             c = u.rope
             n = c.element_count * es(c.dtype)

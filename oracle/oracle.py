@@ -38,11 +38,14 @@ def _load(path):
         "holo_or_matmul_add": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int]),
         "holo_or_binary": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_rms_norm": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
+        "holo_or_add_rms_norm": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
+        "holo_or_transpose": (C.c_int, [_c, _c, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint8), C.c_uint32]),
         "holo_or_rope": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint64, C.c_int]),
         "holo_or_gather": (C.c_int, [_c, _c, C.c_int, _c, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int]),
         "holo_or_kv_cache_write": (C.c_int, [_c, _c, C.c_uint32, _c, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
         "holo_or_decode_attention_valid_f32": (C.c_int, [_c] * 5 + [C.c_uint32, _c] + [C.c_uint32] * 8),
         "holo_or_decode_attention_valid": (C.c_int, [_c] * 5 + [C.c_uint32, _c] + [C.c_uint32] * 8 + [C.c_int]),
+        "holo_or_decode_attention_mask": (C.c_int, [_c] * 7 + [C.c_uint32] * 8 + [C.c_int]),
         "holo_or_decode_attention_valid_q8": (C.c_int, [_c, C.c_int] + [_c] * 8 + [C.c_uint32, _c] + [C.c_uint32] * 8),
         "holo_or_fnv1a64_f32": (C.c_uint64, [_c, C.c_size_t]),
     }
@@ -145,6 +148,39 @@ def rms_norm(x, gamma, batch, feature, eps_bits, dtype):
     out = np.empty_like(x)
     g = None if gamma is None else np.ascontiguousarray(gamma)
     rc = lib.holo_or_rms_norm(_p(x), _p(g), _p(out), batch, feature, eps_bits, dtype)
+    assert rc == 0, rc
+    return out
+
+
+def decode_attention_mask(q, kp, vp, kn, vn, mask, b, h, kv, m, past, new, d, scale_bits, dtype):
+    """The additive-mask form (kernel_call.rs:632-655); operands flat, mask f32 [m, past + new]."""
+    q, kp, vp, kn, vn = (np.ascontiguousarray(v) for v in (q, kp, vp, kn, vn))
+    mask = np.ascontiguousarray(mask, dtype=np.float32)
+    out = np.empty_like(q)
+    rc = lib.holo_or_decode_attention_mask(_p(q), _p(kp), _p(vp), _p(kn), _p(vn), _p(mask), _p(out), b, h, kv, m, past, new, d,
+                                           scale_bits, dtype)
+    assert rc == 0, rc
+    return out
+
+
+def add_rms_norm(x, residual, gamma, batch, feature, eps_bits, dtype):
+    x = np.ascontiguousarray(x)
+    out = np.empty_like(x)
+    r = None if residual is None else np.ascontiguousarray(residual)
+    g = None if gamma is None else np.ascontiguousarray(gamma)
+    rc = lib.holo_or_add_rms_norm(_p(x), _p(r), _p(g), _p(out), batch, feature, eps_bits, dtype)
+    assert rc == 0, rc
+    return out
+
+
+def transpose(x, dims, perm, itemsize):
+    """x: flat array of prod(dims) elements of `itemsize` bytes; returns the permuted flat bytes."""
+    import ctypes as C
+    b = np.ascontiguousarray(x).view(np.uint8).reshape(-1)
+    out = np.empty_like(b)
+    d = (C.c_uint32 * 8)(*dims)
+    pm = (C.c_uint8 * 8)(*perm)
+    rc = lib.holo_or_transpose(_p(b), _p(out), len(dims), d, pm, itemsize)
     assert rc == 0, rc
     return out
 

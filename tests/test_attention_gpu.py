@@ -172,6 +172,59 @@ def test_unquantized_decode_attention_valid(backend):
         assert e.value.variant == "UnsupportedOp"
 
 
+def test_mask_form_decode_attention(backend):
+    # KernelCall::DecodeAttention (wire 119): additive f32 mask [q_rows, past + new], every key takes
+    # part, -inf erases exactly, an all-erased row is the zero vector, q_rows independent of new_len
+    b, h, kv, m, past, new, d = 2, 4, 2, 3, 37, 2, 32
+    l = past + new
+    for dtype, tol in ((F32, 1e-5), (BF, 3e-2)):
+        rng = np.random.default_rng(8)
+        arrs = [rng.standard_normal(n).astype(np.float32) for n in
+                (b * h * m * d, b * kv * past * d, b * kv * past * d, b * kv * new * d, b * kv * new * d)]
+        if dtype == BF:
+            arrs = [orc.f32_to_bf16_rne(a) for a in arrs]
+        mask = np.where(rng.random((m, l)) < 0.3, -np.inf, 0.0).astype(np.float32)
+        mask[0, 5] = 0.75            # a finite bias
+        mask[1, :] = -np.inf         # every key erased: zero vector
+        for scale_bits in (0, int(np.float32(0.2).view(np.uint32))):
+            ws = hb.DeviceWorkspace(backend, 7)
+            for i, a in enumerate(arrs):
+                ws.put(i, a)
+            ws.put(5, mask)
+            ws.alloc(6, arrs[0].nbytes)
+            call = kc.DecodeAttentionCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), kc.rb(5), kc.rb(6),
+                                          b, h, kv, m, past, new, d, scale_bits, dtype)
+            backend.dispatch(kc.KernelCall.DecodeAttention(call), ws)
+            got = as_f32(ws.read(6, arrs[0].nbytes, np.float32 if dtype == F32 else np.uint16), dtype)
+            want = as_f32(orc.decode_attention_mask(*arrs, mask, b, h, kv, m, past, new, d, scale_bits, dtype), dtype)
+            assert norm_max_err(got, want) <= tol
+            assert not np.any(got.reshape(b * h, m, d)[:, 1, :])
+    # the realized-length mask reproduces the scalar form (decode step: m = new = 1)
+    b, h, kv, past, d, valid = 1, 4, 2, 24, 16, 9
+    rng = np.random.default_rng(4)
+    arrs = [rng.standard_normal(n).astype(np.float32) for n in (b * h * d, b * kv * past * d, b * kv * past * d, b * kv * d, b * kv * d)]
+    mask = np.zeros((1, past + 1), np.float32)
+    mask[0, valid:past] = -np.inf
+    ws = hb.DeviceWorkspace(backend, 9)
+    for i, a in enumerate(arrs):
+        ws.put(i, a)
+    ws.put(5, mask)
+    ws.put(6, np.array([valid], dtype=np.uint32))
+    ws.alloc(7, arrs[0].nbytes)
+    ws.alloc(8, arrs[0].nbytes)
+    backend.dispatch(kc.KernelCall.DecodeAttention(kc.DecodeAttentionCall(
+        kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), kc.rb(5), kc.rb(7), b, h, kv, 1, past, 1, d, 0, F32)), ws)
+    backend.dispatch(kc.KernelCall.DecodeAttentionValid(kc.DecodeAttentionValidCall(
+        kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), kc.rb(6), kc.rb(8), b, h, kv, 1, past, 1, d, 0, F32)), ws)
+    assert norm_max_err(ws.read(7, arrs[0].nbytes, np.float32), ws.read(8, arrs[0].nbytes, np.float32)) <= 1e-6
+    # refusals: no key at all; heads not a multiple of kv_heads
+    for bad in (kc.DecodeAttentionCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), kc.rb(5), kc.rb(7), 1, 4, 2, 1, 0, 0, 16, 0, F32),
+                kc.DecodeAttentionCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), kc.rb(5), kc.rb(7), 1, 4, 3, 1, 4, 1, 16, 0, F32)):
+        with pytest.raises(hb.BackendError) as e:
+            backend.dispatch(kc.KernelCall.DecodeAttention(bad), ws)
+        assert e.value.variant == "UnsupportedOp"
+
+
 def test_config4_full_size_codes_and_attention(backend):
     # batch 32, 32 query / 8 kv heads, head_dim 128, 8192 cached positions: quantizer codes
     # bit-exact on the full cache, attention within tolerance of the oracle on every row.

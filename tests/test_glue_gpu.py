@@ -169,3 +169,93 @@ def test_quantize_rows_bit_exact(backend, dtype, d):
     codes, scales = orc.quantize_rows_i8(xs, dtype, rows, d)
     assert np.array_equal(ws.read(1, rows * d, np.int8), codes)
     assert np.array_equal(ws.read(2, rows * 4, np.uint32), scales.view(np.uint32))
+
+
+def test_add_rms_norm_within_tolerance(backend):
+    # AddRmsNorm (cpu/float_kernels.rs:1567-1681): the norm of x + residual, the sum kept in f32
+    for batch, feature, dt in ((64, 4096, BF), (5, 100, BF), (3, 257, kc.DTYPE_F32)):
+        if dt == BF:
+            x, r, g = synth_bf16(batch * feature, 1.5, 30), synth_bf16(batch * feature, 0.7, 31), synth_bf16(feature, 1.0, 32)
+        else:
+            rng = np.random.default_rng(5)
+            x, r = rng.standard_normal((2, batch * feature)).astype(np.float32)
+            g = rng.standard_normal(feature).astype(np.float32)
+        ws = hb.DeviceWorkspace(backend, 4)
+        ws.put(0, x)
+        ws.put(1, g)
+        ws.put(2, r)
+        ws.alloc(3, x.nbytes)
+        call = kc.NormCall(kc.rb(0), kc.rb(1), kc.NONE, kc.rb(2), kc.rb(3), batch, feature, 0, 0, f32bits(1e-5), dt)
+        backend.dispatch(kc.KernelCall.AddRmsNorm(call), ws)
+        want = orc.add_rms_norm(x, r, g, batch, feature, f32bits(1e-5), dt)
+        if dt == BF:
+            got, want = orc.bf16_to_f32(ws.read(3, x.nbytes, np.uint16)), orc.bf16_to_f32(want)
+            assert norm_max_err(got, want) <= 1e-2
+            assert np.mean(got.view(np.uint32) == want.view(np.uint32)) > 0.99
+        else:
+            assert norm_max_err(ws.read(3, x.nbytes, np.float32), want) <= 1e-5
+        # without the residual operand it is RmsNorm
+        call = kc.NormCall(kc.rb(0), kc.rb(1), kc.NONE, kc.NONE, kc.rb(3), batch, feature, 0, 0, f32bits(1e-5), dt)
+        backend.dispatch(kc.KernelCall.AddRmsNorm(call), ws)
+        plain = orc.rms_norm(x, g, batch, feature, f32bits(1e-5), dt)
+        view = np.uint16 if dt == BF else np.float32
+        got = ws.read(3, x.nbytes, view)
+        if dt == BF:
+            assert norm_max_err(orc.bf16_to_f32(got), orc.bf16_to_f32(plain)) <= 1e-2
+        else:
+            assert norm_max_err(got, plain) <= 1e-5
+
+
+@pytest.mark.parametrize("dims,perm,dt", [
+    ((64, 32, 128), (1, 0, 2), kc.DTYPE_BF16),       # [tokens, heads, d] -> [heads, tokens, d]
+    ((7, 5), (1, 0), kc.DTYPE_F32),
+    ((2, 3, 4, 5), (3, 1, 0, 2), kc.DTYPE_I8),
+    ((3, 1, 4, 1, 5, 2, 2, 3), (7, 0, 6, 1, 5, 2, 4, 3), kc.DTYPE_I64),
+    ((11,), (0,), kc.DTYPE_BF16),
+])
+def test_transpose_bit_exact(backend, dims, perm, dt):
+    es = {kc.DTYPE_BF16: 2, kc.DTYPE_F32: 4, kc.DTYPE_I8: 1, kc.DTYPE_I64: 8}[dt]
+    total = int(np.prod(dims))
+    x = np.random.default_rng(total).integers(0, 256, total * es, dtype=np.uint8)
+    ws = hb.DeviceWorkspace(backend, 2)
+    ws.put(0, x)
+    ws.alloc(1, x.nbytes)
+    backend.dispatch(kc.KernelCall.Transpose(kc.TransposeCall.make(kc.rb(0), kc.rb(1), dims, perm, dt)), ws)
+    got = ws.read(1, x.nbytes)
+    assert np.array_equal(got, orc.transpose(x, dims, perm, es))
+    # independent check against numpy's own transpose
+    ref = np.transpose(x.reshape(*dims, es), list(perm) + [len(dims)]).reshape(-1)
+    assert np.array_equal(got, ref)
+
+
+def test_transpose_refusals(backend):
+    ws = hb.DeviceWorkspace(backend, 2)
+    ws.alloc(0, 64)
+    ws.alloc(1, 64)
+    with pytest.raises(hb.BackendError) as e:   # not a permutation
+        backend.dispatch(kc.KernelCall.Transpose(kc.TransposeCall.make(kc.rb(0), kc.rb(1), (2, 3), (0, 0), BF)), ws)
+    assert e.value.variant == "UnsupportedOp"
+    with pytest.raises(hb.BackendError) as e:   # output too short
+        backend.dispatch(kc.KernelCall.Transpose(kc.TransposeCall.make(kc.rb(0), kc.rb(1), (8, 8), (1, 0), BF)), ws)
+    assert e.value.variant == "SlotOutOfRange"
+
+
+def test_slice_and_concat_are_byte_placement(backend):
+    # Slice: a contiguous copy whose start is the input ref's offset (cpu/kernels.rs:688-700);
+    # Concat: out = a || b at the refs' extents (cpu/float_kernels.rs:2963-2974)
+    a = synth_bf16(1000, 1.0, 40)
+    b = synth_bf16(300, 1.0, 41)
+    ws = hb.DeviceWorkspace(backend, 4)
+    ws.put(0, a)
+    ws.put(1, b)
+    ws.alloc(2, 4096)
+    ws.alloc(3, 4096)
+    backend.dispatch(kc.KernelCall.Slice(kc.LayoutCall(kc.rb(0, 200, 0), kc.rb(2), 400, BF)), ws)
+    assert np.array_equal(ws.read(kc.rb(2, 0, 800), dtype=np.uint16), a[100:500])
+    backend.dispatch(kc.KernelCall.Concat(kc.BinaryCall(kc.rb(0, 0, 2000), kc.rb(1, 0, 600), kc.rb(3), 1300, 16, BF)), ws)
+    assert np.array_equal(ws.read(kc.rb(3, 0, 2600), dtype=np.uint16), np.concatenate([a, b]))
+    # an output shorter than a || b is refused against the output slot
+    ws.alloc(3, 1024)
+    with pytest.raises(hb.BackendError) as e:
+        backend.dispatch(kc.KernelCall.Concat(kc.BinaryCall(kc.rb(0, 0, 2000), kc.rb(1, 0, 600), kc.rb(3), 1300, 16, BF)), ws)
+    assert e.value.variant == "SlotOutOfRange" and e.value.slot == 3

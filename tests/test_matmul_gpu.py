@@ -115,3 +115,65 @@ def test_config3_decode_16x4096x14336(backend):
     err = norm_max_err(got, want)
     print(f"16x4096x14336 matmul: max|err|/max|ref| = {err:.3e}")
     assert err <= 1e-2
+
+
+def run_dt(backend, a, b, m, k, n, dt, act=0, residual=None):
+    es = 4 if dt == kc.DTYPE_F32 else 2
+    ws = hb.DeviceWorkspace(backend, 4)
+    ws.put(0, a)
+    ws.put(1, b)
+    ws.alloc(2, m * n * es)
+    mm = kc.MatMulCall(kc.rb(0), kc.rb(1), kc.rb(2), m, k, n, dt, 0)
+    if residual is not None:
+        ws.put(3, residual)
+        call = kc.KernelCall.MatMulAdd(kc.MatMulAddCall(mm, kc.rb(3)))
+    elif act:
+        call = kc.KernelCall.MatMulActivation(kc.MatMulActivationCall(mm, act))
+    else:
+        call = kc.KernelCall.MatMul(mm)
+    backend.dispatch(call, ws)
+    out = ws.read(2, m * n * es, np.float32 if dt == kc.DTYPE_F32 else np.uint16)
+    ws.close()
+    return out
+
+
+def f16_to_f32(h):
+    return h.view(np.float16).astype(np.float32)
+
+
+@pytest.mark.parametrize("m,k,n", [(64, 1024, 2048), (16, 4096, 512), (200, 192, 512), (5, 64, 20)])
+def test_f16_matmul(backend, m, k, n):
+    # f16 takes the same tensor-core kernel (operand format f16, the reference's add-half narrow);
+    # the last shape takes the per-cell kernel and is bit-exact
+    rng = np.random.default_rng(m + n)
+    s = np.float32(1.0 / np.sqrt(k))
+    a = (rng.standard_normal(m * k, dtype=np.float32) * s).astype(np.float16).view(np.uint16)
+    b = (rng.standard_normal(k * n, dtype=np.float32) * s).astype(np.float16).view(np.uint16)
+    r = rng.standard_normal(m * n, dtype=np.float32).astype(np.float16).view(np.uint16)
+    F16 = kc.DTYPE_F16
+    plain = run_dt(backend, a, b, m, k, n, F16)
+    want = orc.matmul(a, b, m, k, n, F16)
+    if (m, k, n) == (5, 64, 20):
+        assert np.array_equal(plain, want)
+    else:
+        assert norm_max_err(f16_to_f32(plain), f16_to_f32(want)) <= 2e-3
+    # fused epilogues act on the narrowed product exactly as the unfused pair
+    assert np.array_equal(run_dt(backend, a, b, m, k, n, F16, act=kc.FUSED_SILU), orc.unary_lut(kc.LUT_SILU, F16, plain))
+    assert np.array_equal(run_dt(backend, a, b, m, k, n, F16, residual=r), orc.binary(0, plain, r, F16))
+
+
+@pytest.mark.parametrize("m,k,n", [(8, 256, 64), (33, 100, 20), (64, 512, 128)])
+def test_f32_matmul_is_the_reference_recurrence(backend, m, k, n):
+    # every f32 product runs the per-cell ascending-k fused-multiply-add chain: bit-exact;
+    # the fused activation is the scalar function on the f32 product (no table for 32-bit patterns)
+    rng = np.random.default_rng(m * n)
+    a = rng.standard_normal(m * k, dtype=np.float32)
+    b = rng.standard_normal(k * n, dtype=np.float32) * np.float32(1.0 / np.sqrt(k))
+    r = rng.standard_normal(m * n, dtype=np.float32)
+    F32 = kc.DTYPE_F32
+    assert np.array_equal(run_dt(backend, a, b, m, k, n, F32).view(np.uint32), orc.matmul(a, b, m, k, n, F32).view(np.uint32))
+    assert np.array_equal(run_dt(backend, a, b, m, k, n, F32, residual=r).view(np.uint32),
+                          orc.matmul(a, b, m, k, n, F32, residual=r).view(np.uint32))
+    got = run_dt(backend, a, b, m, k, n, F32, act=kc.FUSED_GELU)
+    want = orc.matmul(a, b, m, k, n, F32, act=kc.FUSED_GELU)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))

@@ -245,3 +245,39 @@ def test_kv_cache_write_ring():
     assert np.array_equal(o[:, 1:4], cache.reshape(planes, bucket, row)[:, 1:4])
     assert orc.kv_cache_write(cache, new, 0, planes, 0, new_rows, row)[0] == -3
     assert orc.kv_cache_write(cache, new, 0, planes, 1, 2, row)[0] == -3
+
+
+def test_add_rms_norm_and_transpose_restatements():
+    # AddRmsNorm = RmsNorm over the f32 sum x + residual (cpu/float_kernels.rs:1656-1679); with the
+    # residual folded into x beforehand in f32 the two restatements must agree bit for bit
+    rng = np.random.default_rng(9)
+    x, r = rng.standard_normal((2, 6 * 50)).astype(np.float32)
+    g = rng.standard_normal(50).astype(np.float32)
+    eps = struct.unpack("<I", struct.pack("<f", 1e-5))[0]
+    a = orc.add_rms_norm(x, r, g, 6, 50, eps, kc.DTYPE_F32)
+    b = orc.rms_norm(x + r, g, 6, 50, eps, kc.DTYPE_F32)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    assert np.array_equal(orc.add_rms_norm(x, None, g, 6, 50, eps, kc.DTYPE_F32).view(np.uint32),
+                          orc.rms_norm(x, g, 6, 50, eps, kc.DTYPE_F32).view(np.uint32))
+    # Transpose: output axis i is input axis perm[i] (cpu/float_kernels.rs:2980-3027)
+    t = np.arange(2 * 3 * 4 * 5, dtype=np.uint16)
+    for perm in ((0, 1, 2, 3), (3, 2, 1, 0), (1, 3, 0, 2)):
+        got = orc.transpose(t, (2, 3, 4, 5), perm, 2).view(np.uint16)
+        assert np.array_equal(got, np.transpose(t.reshape(2, 3, 4, 5), perm).reshape(-1))
+
+
+def test_mask_form_restatement_equals_scalar_form_bitwise():
+    # the reference pins that a realized-length mask reproduces DecodeAttentionValid bit for bit
+    # (crates/hologram-compute/tests/decode_attention_valid.rs:226-282); all-erased row = zeros
+    b, h, kv, past, d = 2, 4, 2, 19, 24
+    rng = np.random.default_rng(12)
+    arrs = [rng.standard_normal(n).astype(np.float32) for n in (b * h * d, b * kv * past * d, b * kv * past * d, b * kv * d, b * kv * d)]
+    for valid in (0, 7, 19):
+        mask = np.zeros((1, past + 1), np.float32)
+        mask[0, valid:past] = -np.inf
+        a = orc.decode_attention_mask(*arrs, mask, b, h, kv, 1, past, 1, d, 0, kc.DTYPE_F32)
+        rc, v = orc.decode_attention_valid(*arrs, valid, b, h, kv, 1, past, 1, d, 0, kc.DTYPE_F32)
+        assert rc == 0 and np.array_equal(a.view(np.uint32), v.view(np.uint32))
+    mask = np.full((1, past + 1), -np.inf, np.float32)
+    z = orc.decode_attention_mask(*arrs, mask, b, h, kv, 1, past, 1, d, 0, kc.DTYPE_F32)
+    assert not np.any(z)
