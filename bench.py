@@ -129,7 +129,7 @@ def workload_lut(be, torch, rank, args):
         "units_per_step": n * 4 / 1e9,  # GB of algorithmic traffic per step
         "launches_per_step": 1,
         "roofline": {"bound": "hbm", "bytes_per_launch": n * 4, "kernel": "lut_stream_kernel",
-                     "traffic": 34_255_360, "traffic_note": "ncu, profiles/lut_stream_kernel_gelu_bf16_16Mi.md: 33.69 MB read + 0.56 MB written inside the kernel window (the output is still dirty in L2)"},
+                     "traffic": 34_192_896, "traffic_note": "ncu, profiles/lut_stream_kernel_gelu_bf16_16Mi.md: 33.70 MB read + 0.49 MB written inside the kernel window (the output is still dirty in L2)"},
         "h2d": n * 2, "d2h": n * 2,
         "cpu_baseline": cpu_baseline,
         "config": {"workload": "config[0]: bf16 GELU via the 65536-entry u16 LUT, 16,777,216 elements, 99% N(0,9) + 1% specials",
@@ -202,9 +202,9 @@ def workload_attention(be, torch, rank, args, world=1):
         "run_host": lambda step: be.dispatch(call, hws),
         "ref_step": ref_step, "ref_fraction": 2 / b,
         "units_per_step": algo / 1e9,
-        "launches_per_step": 2,
+        "launches_per_step": 1,
         "roofline": {"bound": "hbm", "bytes_per_launch": algo, "kernel": "decode_attention_q8_kernel",
-                     "traffic": 560_797_696 // world, "traffic_note": "ncu at N=1, profiles/decode_attention_q8_kernel_b32_h32_kv8_L8192.md: 554.05 MB read + 6.75 MB written"},
+                     "traffic": 560_289_536 // world, "traffic_note": "ncu at N=1, profiles/decode_attention_q8_kernel_b32_h32_kv8_L8192.md: 554.85 MB read + 5.44 MB written"},
         "h2d": sum(t.numel() * t.element_size() for t in tensors[:-1]), "d2h": out.numel() * 2,
         "cpu_baseline": cpu_baseline,
         "config": {"workload": f"config[3]: single-token decode attention, batch {b}, {h} q / {kv} kv heads, head_dim {d}, {past} cached positions, int8 KV",
@@ -303,8 +303,8 @@ def workload_decoder(be, torch, rank, args, world=1):
         "run_host": run_host,
         "units_per_step": B / world,   # the batch is replicated over the TP group: count it once
         "launches_per_step": sess.n_calls,
-        "roofline": {"bound": "hbm", "bytes_per_launch": attn_bytes, "kernel": "decode_attention_q8_kernel (+ combine), one layer",
-                     "run": run_dominant, "traffic": (560_797_696 // world) if (B, L) == (64, 4096) else None,
+        "roofline": {"bound": "hbm", "bytes_per_launch": attn_bytes, "kernel": "decode_attention_q8_kernel, one layer",
+                     "run": run_dominant, "traffic": (560_289_536 // world) if (B, L) == (64, 4096) else None,
                      "traffic_note": "ncu capture of the same kernel on the same number of key rows (config[3]: 32 x 8 x 8192 = 64 x 8 x 4096 rows), "
                                      "profiles/decode_attention_q8_kernel_b32_h32_kv8_L8192.md",
                      "step_bytes": algo},

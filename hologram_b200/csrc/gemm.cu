@@ -112,7 +112,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 // One 16-bit result: narrow the accumulator (bf16: truncation; f16: the reference's
 // add-half rounding), then the fused epilogue on the narrowed value
 // (float_kernels.rs:844-847, 886-889).
-__device__ __forceinline__ uint16_t epilogue_elem(float acc, const uint16_t* table, const uint16_t* residual, uint64_t idx, int dtype) {
+template <bool F16>
+__device__ __forceinline__ uint16_t epilogue_elem(float acc, const uint16_t* table, const uint16_t* residual, uint64_t idx) {
+    // the dtype is a compile-time choice: a run-time test per element made the bf16 epilogue of the
+    // 4096^3 product a third slower
+    constexpr int dtype = F16 ? HOLO_DTYPE_F16 : HOLO_DTYPE_BF16;
     uint16_t h = holo::narrow16(acc, dtype);
     if (table) h = __ldg(table + h);
     if (residual) h = holo::narrow16(__fadd_rn(holo::widen16(h, dtype), holo::widen16(__ldg(residual + idx), dtype)), dtype);
@@ -133,7 +137,7 @@ struct GemmSmem {
     static constexpr uint32_t TOTAL = BARS + 256 + 1024;
 };
 
-template <int BN, int STAGES, int A_ROWS>
+template <int BN, int STAGES, int A_ROWS, bool F16>
 __global__ void __launch_bounds__(GEMM_THREADS)
 matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
     using S = GemmSmem<BN, STAGES, A_ROWS>;
@@ -194,7 +198,7 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         if (lane == 0 && !*s_abort) {
             // instruction descriptor: D = f32, A = B = bf16 (format 1) or f16 (format 0), A K-major,
             // B N-major, N = BN, M = 128
-            const uint32_t fmt = p.dtype == HOLO_DTYPE_BF16 ? 1u : 0u;
+            constexpr uint32_t fmt = F16 ? 0u : 1u;
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             bool ok = true;
             for (uint32_t i = 0; i < nkb && ok; ++i) {
@@ -239,8 +243,8 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         uint32_t w[16];
 #pragma unroll
                         for (int x = 0; x < 16; ++x) {
-                            uint16_t lo = epilogue_elem(__uint_as_float(v[2 * x]), sg.table, sg.residual, idx0 + 2 * x, p.dtype);
-                            uint16_t hi = epilogue_elem(__uint_as_float(v[2 * x + 1]), sg.table, sg.residual, idx0 + 2 * x + 1, p.dtype);
+                            uint16_t lo = epilogue_elem<F16>(__uint_as_float(v[2 * x]), sg.table, sg.residual, idx0 + 2 * x);
+                            uint16_t hi = epilogue_elem<F16>(__uint_as_float(v[2 * x + 1]), sg.table, sg.residual, idx0 + 2 * x + 1);
                             w[x] = (uint32_t)lo | ((uint32_t)hi << 16);
                         }
 #pragma unroll
@@ -249,7 +253,7 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     } else {
 #pragma unroll
                         for (int x = 0; x < 32; ++x)
-                            if (col0 + x < sg.col_end) dst[x] = epilogue_elem(__uint_as_float(v[x]), sg.table, sg.residual, idx0 + x, p.dtype);
+                            if (col0 + x < sg.col_end) dst[x] = epilogue_elem<F16>(__uint_as_float(v[x]), sg.table, sg.residual, idx0 + x);
                     }
                 }
             }
@@ -315,12 +319,12 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         if (col + 4 <= sg.col_end && ((uintptr_t)dst & 7u) == 0) {
                             uint16_t h[4];
 #pragma unroll
-                            for (int x = 0; x < 4; ++x) h[x] = epilogue_elem(a4[x], sg.table, sg.residual, idx + x, p.dtype);
+                            for (int x = 0; x < 4; ++x) h[x] = epilogue_elem<F16>(a4[x], sg.table, sg.residual, idx + x);
                             *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
                         } else {
 #pragma unroll
                             for (int x = 0; x < 4; ++x)
-                                if (col + x < sg.col_end) dst[x] = epilogue_elem(a4[x], sg.table, sg.residual, idx + x, p.dtype);
+                                if (col + x < sg.col_end) dst[x] = epilogue_elem<F16>(a4[x], sg.table, sg.residual, idx + x);
                         }
                     }
                 }
@@ -365,7 +369,8 @@ __global__ void matmul_cell_kernel(const void* __restrict__ a, const void* __res
         if (residual) acc = __fadd_rn(acc, reinterpret_cast<const float*>(residual)[idx]);
         reinterpret_cast<float*>(out)[idx] = acc;
     } else {
-        reinterpret_cast<uint16_t*>(out)[idx] = epilogue_elem(acc, table, reinterpret_cast<const uint16_t*>(residual), idx, dtype);
+        const uint16_t* res16 = reinterpret_cast<const uint16_t*>(residual);
+        reinterpret_cast<uint16_t*>(out)[idx] = dtype == HOLO_DTYPE_F16 ? epilogue_elem<true>(acc, table, res16, idx) : epilogue_elem<false>(acc, table, res16, idx);
     }
 }
 
@@ -398,18 +403,24 @@ int32_t make_map_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t 
     return HOLO_OK;
 }
 
-template <int BN, int STAGES, int A_ROWS>
-int32_t launch_umma(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid) {
+template <int BN, int STAGES, int A_ROWS, bool F16>
+int32_t launch_umma_dt(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid) {
     using S = GemmSmem<BN, STAGES, A_ROWS>;
     static thread_local int configured_device = -1;
     if (configured_device != ctx->device) {
-        HOLO_CUDA(cudaFuncSetAttribute(matmul_bf16_umma_kernel<BN, STAGES, A_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+        HOLO_CUDA(cudaFuncSetAttribute(matmul_bf16_umma_kernel<BN, STAGES, A_ROWS, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
         configured_device = ctx->device;
     }
     // the K slices of one output tile form a cluster along grid z
-    HOLO_CUDA(holo_launch_kernel(ctx, matmul_bf16_umma_kernel<BN, STAGES, A_ROWS>, grid, dim3(GEMM_THREADS), S::TOTAL, p.splits, ma, mb, p));
+    HOLO_CUDA(holo_launch_kernel(ctx, matmul_bf16_umma_kernel<BN, STAGES, A_ROWS, F16>, grid, dim3(GEMM_THREADS), S::TOTAL, p.splits, ma, mb, p));
     ctx->launches++;
     return HOLO_OK;
+}
+
+template <int BN, int STAGES, int A_ROWS>
+int32_t launch_umma(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid) {
+    if (p.dtype == HOLO_DTYPE_F16) return launch_umma_dt<BN, STAGES, A_ROWS, true>(ctx, ma, mb, p, grid);
+    return launch_umma_dt<BN, STAGES, A_ROWS, false>(ctx, ma, mb, p, grid);
 }
 
 }  // namespace

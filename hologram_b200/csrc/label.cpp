@@ -1,0 +1,203 @@
+#include "label.h"
+
+#include <string.h>
+
+#include "blake3.h"
+
+void holo_label_from_digest(const uint8_t digest[32], uint8_t out[HOLO_LABEL_BYTES]) {
+    static const char HEX[] = "0123456789abcdef";
+    memcpy(out, "blake3:", 7);
+    for (int i = 0; i < 32; ++i) {
+        out[7 + 2 * i] = (uint8_t)HEX[digest[i] >> 4];
+        out[7 + 2 * i + 1] = (uint8_t)HEX[digest[i] & 15];
+    }
+}
+
+void holo_label_of_bytes(const uint8_t* data, size_t len, uint8_t out[HOLO_LABEL_BYTES]) {
+    uint8_t d[32];
+    holo_blake3(data, len, d);
+    holo_label_from_digest(d, out);
+}
+
+void holo_label_derive(uint16_t opcode, const uint8_t* params, size_t params_len, const uint8_t* labels, size_t n_labels,
+                       uint8_t out[HOLO_LABEL_BYTES]) {
+    // the reference folds the pieces through a streaming hasher; hashing their concatenation is
+    // the same digest
+    std::vector<uint8_t> buf;
+    buf.reserve(2 + params_len + n_labels * HOLO_LABEL_BYTES);
+    buf.push_back((uint8_t)(opcode & 0xff));
+    buf.push_back((uint8_t)(opcode >> 8));
+    buf.insert(buf.end(), params, params + params_len);
+    buf.insert(buf.end(), labels, labels + n_labels * HOLO_LABEL_BYTES);
+    uint8_t d[32];
+    holo_blake3(buf.data(), buf.size(), d);
+    holo_label_from_digest(d, out);
+}
+
+namespace {
+// Little-endian parameter builder (kernel_call.rs:950-993).
+struct Pb {
+    HoloOpSignature* s;
+    Pb& raw(const void* p, size_t n) {
+        if (s->len + n <= sizeof s->params) {
+            memcpy(s->params + s->len, p, n);
+            s->len += (uint32_t)n;
+        }
+        return *this;
+    }
+    Pb& u8(uint8_t v) { return raw(&v, 1); }
+    Pb& u16(uint16_t v) { return raw(&v, 2); }
+    Pb& u32(uint32_t v) { return raw(&v, 4); }
+    Pb& i32(int32_t v) { return raw(&v, 4); }
+    Pb& u64(uint64_t v) { return raw(&v, 8); }
+};
+void p_matmul(Pb& b, const HoloMatMulCall& c) { b.u32(c.m).u32(c.k).u32(c.n).u8(c.dtype); }
+void p_attn(Pb& b, uint32_t batch, uint32_t heads, uint32_t kv, uint32_t m, uint32_t past, uint32_t nnew, uint32_t d, uint32_t scale_bits,
+            uint8_t dtype) {
+    b.u32(batch).u32(heads).u32(kv).u32(m).u32(past).u32(nnew).u32(d).u32(scale_bits).u8(dtype);
+}
+bool present(const HoloBufferRef& r) { return r.slot != HOLO_NO_SLOT; }
+}  // namespace
+
+bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
+    *sig = HoloOpSignature();
+    Pb b{sig};
+    const auto& u = call.u;
+    switch (call.kind) {
+        // unary / binary: element_count u64, witt_bits u16, dtype u8 (p_unary / p_binary)
+        case HOLO_K_SIGMOID: sig->opcode = 11; break;
+        case HOLO_K_TANH: sig->opcode = 12; break;
+        case HOLO_K_GELU: sig->opcode = 13; break;
+        case HOLO_K_SILU: sig->opcode = 14; break;
+        case HOLO_K_EXP: sig->opcode = 17; break;
+        case HOLO_K_ERF: sig->opcode = 31; break;
+        case HOLO_K_ADD: sig->opcode = 4; sig->commutative = true; break;
+        case HOLO_K_MUL: sig->opcode = 6; sig->commutative = true; break;
+        case HOLO_K_CONCAT: sig->opcode = 61; break;
+        case HOLO_K_MATMUL: sig->opcode = 45; p_matmul(b, u.matmul); return true;
+        case HOLO_K_MATMUL_ACTIVATION: sig->opcode = 105; p_matmul(b, u.matmul_activation.mm); b.u8(u.matmul_activation.act); return true;
+        case HOLO_K_MATMUL_ADD: sig->opcode = 106; p_matmul(b, u.matmul_add.mm); return true;
+        case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM: {
+            const HoloNormCall& c = u.norm;
+            sig->opcode = call.kind == HOLO_K_RMS_NORM ? 50 : 53;
+            b.u32(c.batch).u32(c.feature).u32(c.channels).u32(c.num_groups).u64(c.epsilon_bits).u8(c.dtype).u8(present(c.residual) ? 1 : 0);
+            return true;
+        }
+        case HOLO_K_RESHAPE: case HOLO_K_SLICE:
+            sig->opcode = call.kind == HOLO_K_RESHAPE ? 59 : 62;
+            b.u64(u.layout.element_count).u8(u.layout.dtype);
+            return true;
+        case HOLO_K_TRANSPOSE: {
+            const HoloTransposeCall& c = u.transpose;
+            sig->opcode = 60;
+            b.u8(c.rank).u8(c.dtype);
+            for (uint32_t i = 0; i < c.rank && i < 8; ++i) b.u32(c.dims[i]).u8(c.perm[i]);
+            return true;
+        }
+        case HOLO_K_ROTARY: sig->opcode = 74; b.u64(u.rope.element_count).u32(u.rope.head_dim).u8(u.rope.dtype); return true;
+        case HOLO_K_GATHER: {
+            const HoloGatherCall& c = u.gather;
+            sig->opcode = 114;
+            b.u64(c.outer).u64(c.axis_dim).u64(c.inner).u64(c.num_indices).u8(c.idx_dtype).u8(c.dtype);
+            return true;
+        }
+        case HOLO_K_CAST: sig->opcode = 115; b.u64(u.cast.element_count).u8(u.cast.src_dtype).u8(u.cast.dst_dtype); return true;
+        case HOLO_K_DEQUANTIZE: {
+            const HoloDequantizeCall& c = u.dequantize;
+            sig->opcode = 104;
+            b.u64(c.element_count).u32(c.channels).u32(c.inner).u8(c.quant_dtype).u8(c.dtype).u32(c.scale_bits).i32(c.zero_point)
+                .u8(present(c.scales) ? 1 : 0);
+            return true;
+        }
+        case HOLO_K_DECODE_ATTENTION: {
+            const HoloDecodeAttentionCall& c = u.decode_attention;
+            sig->opcode = 119;
+            p_attn(b, c.batch, c.heads, c.kv_heads, c.q_rows, c.past_len, c.new_len, c.head_dim, c.scale_bits, c.dtype);
+            return true;
+        }
+        case HOLO_K_KV_CACHE_WRITE: {
+            const HoloKvCacheWriteCall& c = u.kv_cache_write;
+            sig->opcode = 120;
+            b.u32(c.planes).u32(c.bucket_rows).u32(c.new_rows).u32(c.row_bytes);
+            return true;
+        }
+        case HOLO_K_DECODE_ATTENTION_VALID: {
+            const HoloDecodeAttentionValidCall& c = u.decode_attention_valid;
+            sig->opcode = 121;
+            p_attn(b, c.batch, c.heads, c.kv_heads, c.q_rows, c.past_len, c.new_len, c.head_dim, c.scale_bits, c.dtype);
+            return true;
+        }
+        // extensions: the tag doubles as the opcode
+        case HOLO_K_QUANTIZE_ROWS_I8: {
+            const HoloQuantizeRowsI8Call& c = u.quantize_rows_i8;
+            sig->opcode = HOLO_K_QUANTIZE_ROWS_I8;
+            b.u64(c.rows).u32(c.row_len).u8(c.dtype);
+            return true;
+        }
+        case HOLO_K_DECODE_ATTENTION_VALID_Q8: {
+            const HoloDecodeAttentionValidQ8Call& c = u.decode_attention_valid_q8;
+            sig->opcode = HOLO_K_DECODE_ATTENTION_VALID_Q8;
+            p_attn(b, c.batch, c.heads, c.kv_heads, c.q_rows, c.past_len, c.new_len, c.head_dim, c.scale_bits, c.dtype);
+            return true;
+        }
+        default: return false;   // AllReduce: its value depends on the other ranks, not on local labels
+    }
+    // the unary / binary group
+    if (call.kind == HOLO_K_ADD || call.kind == HOLO_K_MUL || call.kind == HOLO_K_CONCAT)
+        b.u64(u.binary.element_count).u16(u.binary.witt_bits).u8(u.binary.dtype);
+    else
+        b.u64(u.unary.element_count).u16(u.unary.witt_bits).u8(u.unary.dtype);
+    return true;
+}
+
+bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* inputs, uint32_t* output) {
+    inputs->clear();
+    auto in = [&](const HoloBufferRef& r) {
+        if (present(r)) inputs->push_back(r.slot);
+    };
+    const auto& u = call.u;
+    switch (call.kind) {
+        case HOLO_K_SIGMOID: case HOLO_K_TANH: case HOLO_K_GELU: case HOLO_K_SILU: case HOLO_K_EXP: case HOLO_K_ERF:
+            in(u.unary.input); *output = u.unary.output.slot; return true;
+        case HOLO_K_ADD: case HOLO_K_MUL: case HOLO_K_CONCAT:
+            in(u.binary.a); in(u.binary.b); *output = u.binary.output.slot; return true;
+        case HOLO_K_MATMUL: in(u.matmul.a); in(u.matmul.b); *output = u.matmul.output.slot; return true;
+        case HOLO_K_MATMUL_ACTIVATION:
+            in(u.matmul_activation.mm.a); in(u.matmul_activation.mm.b); *output = u.matmul_activation.mm.output.slot; return true;
+        case HOLO_K_MATMUL_ADD:
+            in(u.matmul_add.mm.a); in(u.matmul_add.mm.b); in(u.matmul_add.residual); *output = u.matmul_add.mm.output.slot; return true;
+        case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM:
+            // the reference lists x, gamma, beta (kernel_call.rs:1612-1616); the residual operand of
+            // AddRmsNorm is added here so that two sums over different residuals never share a label
+            in(u.norm.x); in(u.norm.gamma); in(u.norm.beta);
+            if (call.kind == HOLO_K_ADD_RMS_NORM) in(u.norm.residual);
+            *output = u.norm.output.slot; return true;
+        case HOLO_K_RESHAPE: case HOLO_K_SLICE: in(u.layout.input); *output = u.layout.output.slot; return true;
+        case HOLO_K_TRANSPOSE: in(u.transpose.input); *output = u.transpose.output.slot; return true;
+        case HOLO_K_ROTARY: in(u.rope.x); in(u.rope.cos); in(u.rope.sin); *output = u.rope.output.slot; return true;
+        case HOLO_K_GATHER: in(u.gather.data); in(u.gather.indices); *output = u.gather.output.slot; return true;
+        case HOLO_K_CAST: in(u.cast.input); *output = u.cast.output.slot; return true;
+        case HOLO_K_DEQUANTIZE:
+            in(u.dequantize.input);
+            if (present(u.dequantize.scales)) { in(u.dequantize.scales); in(u.dequantize.zero_points); }
+            *output = u.dequantize.output.slot; return true;
+        case HOLO_K_DECODE_ATTENTION: {
+            const auto& c = u.decode_attention;
+            in(c.q); in(c.k_past); in(c.v_past); in(c.k_new); in(c.v_new); in(c.mask); *output = c.output.slot; return true;
+        }
+        case HOLO_K_KV_CACHE_WRITE: {
+            const auto& c = u.kv_cache_write;
+            in(c.cache); in(c.new_rows_buf); in(c.pos); *output = c.output.slot; return true;
+        }
+        case HOLO_K_DECODE_ATTENTION_VALID: {
+            const auto& c = u.decode_attention_valid;
+            in(c.q); in(c.k_past); in(c.v_past); in(c.k_new); in(c.v_new); in(c.valid_len); *output = c.output.slot; return true;
+        }
+        case HOLO_K_DECODE_ATTENTION_VALID_Q8: {
+            const auto& c = u.decode_attention_valid_q8;
+            in(c.q); in(c.k_past); in(c.k_past_scales); in(c.v_past); in(c.v_past_scales); in(c.k_new); in(c.k_new_scales);
+            in(c.v_new); in(c.v_new_scales); in(c.valid_len); *output = c.output.slot; return true;
+        }
+        default: return false;   // QuantizeRowsI8 has two outputs, AllReduce is not a function of local labels
+    }
+}
