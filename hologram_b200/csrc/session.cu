@@ -17,8 +17,13 @@
 #include <algorithm>
 #include <set>
 
+#include <array>
+#include <string>
+#include <unordered_map>
+
 #include "archive.h"
 #include "common.h"
+#include "label.h"
 
 // A merged group of sibling matmuls: products of one A against several constant weights,
 // executed as one matmul against the column-concatenated weights with one output segment each.
@@ -59,6 +64,34 @@ struct holo_b200_session {
     uint32_t fused = 0, moved_in_place = 0, merged_calls = 0, batched_calls = 0, reduce_adds = 0;
     uint64_t device_bytes = 0;
     cudaGraphExec_t graph = nullptr;
+
+    // ---- content-addressed execution (loaded with HOLO_SESSION_ADDRESSED) ----
+    // The walk of crates/hologram-exec/src/session.rs:1052-1289 over device memory: every value
+    // has a label derived from its operation and its operands' labels; the pool keeps device
+    // buffers by label, so a value that is already resident is bound to its consumer's slot by
+    // pointer (no dispatch, no copy, no host round trip), and a whole-graph repeat is answered
+    // from the memo of input labels -> output labels.
+    bool addressed = false;
+    struct NodeMeta {
+        HoloOpSignature sig;
+        std::vector<uint32_t> inputs, outputs;
+        bool addressable = false;
+    };
+    struct PoolEntry {
+        void* ptr = nullptr;
+        uint64_t bytes = 0;
+        uint64_t last_walk = 0;
+    };
+    std::vector<NodeMeta> meta;                           // one per call
+    std::vector<uint64_t> slot_need;                      // bytes a slot must hold
+    std::vector<HoloSlot> static_binding;                 // the load-time buffer of every slot
+    std::vector<std::string> slot_label_init;             // constants' labels ("" = none)
+    std::vector<uint8_t> is_output_slot;
+    std::unordered_map<std::string, PoolEntry> pool;      // label -> resident device buffer (owned)
+    std::vector<PoolEntry> free_list;                     // released buffers, reused best-fit <= 2x
+    std::vector<PoolEntry> transients;                    // unlabelled results of the current walk
+    std::unordered_map<std::string, std::pair<std::string, uint64_t>> memo;   // input labels -> (output labels, tick)
+    uint64_t walk_no = 0, memo_tick = 0, pool_bytes = 0;
 };
 
 namespace {
@@ -388,6 +421,249 @@ int32_t plan_micro_batches(holo_b200_session* s) {
     return HOLO_OK;
 }
 
+// ---- content-addressed execution ---------------------------------------------------------------
+std::string label_str(const uint8_t* l) { return std::string(reinterpret_cast<const char*>(l), HOLO_LABEL_BYTES); }
+
+int32_t prepare_addressed(holo_b200_session* s) {
+    const size_t n_slots = s->ws->slots.size();
+    s->static_binding = s->ws->slots;
+    s->slot_label_init.assign(n_slots, std::string());
+    s->is_output_slot.assign(n_slots, 0);
+    for (const HoloPort& p : s->ar.outputs) s->is_output_slot[p.slot] = 1;
+    // constants are leaves: their label is the label of their bytes (for a weight that is the
+    // archive's fingerprint, crates/hologram-archive/src/address.rs:63-74)
+    for (const HoloConstant& k : s->ar.constants) {
+        uint8_t l[HOLO_LABEL_BYTES];
+        holo_label_of_bytes(k.bytes, k.len, l);
+        s->slot_label_init[k.slot] = label_str(l);
+    }
+    s->meta.resize(s->calls.size());
+    for (size_t i = 0; i < s->calls.size(); ++i) {
+        holo_b200_session::NodeMeta& m = s->meta[i];
+        const HoloKernelCall& c = s->calls[i];
+        uint32_t out = HOLO_NO_SLOT;
+        m.addressable = holo_op_signature(c, &m.sig) && holo_call_operands(c, &m.inputs, &out);
+        if (m.addressable) {
+            m.outputs.push_back(out);
+        } else if (c.kind == HOLO_K_QUANTIZE_ROWS_I8) {
+            // two outputs: codes take the plain derivation, scales the derivation with an index byte
+            m.addressable = holo_op_signature(c, &m.sig);
+            m.inputs = {c.u.quantize_rows_i8.input.slot};
+            m.outputs = {c.u.quantize_rows_i8.codes.slot, c.u.quantize_rows_i8.scales.slot};
+        } else {
+            HoloKernelCall tmp = c;
+            HoloRefList refs;
+            if (holo_collect_refs(&tmp, &refs))
+                for (int r = 0; r < refs.n; ++r)
+                    if (refs.written[r]) m.outputs.push_back(refs.refs[r]->slot);
+        }
+    }
+    return HOLO_OK;
+}
+
+// A zero-filled device buffer of at least `bytes`: the best fit from the released buffers that
+// is no more than twice the size (crates/hologram-exec/src/buffer.rs:528-551), else a new one.
+int32_t pool_acquire(holo_b200_session* s, uint64_t bytes, holo_b200_session::PoolEntry* out) {
+    bytes = (std::max<uint64_t>(bytes, 64) + 63) & ~63ull;
+    int best = -1;
+    for (size_t i = 0; i < s->free_list.size(); ++i) {
+        const uint64_t have = s->free_list[i].bytes;
+        if (have >= bytes && have <= 2 * bytes && (best < 0 || have < s->free_list[best].bytes)) best = (int)i;
+    }
+    if (best >= 0) {
+        *out = s->free_list[best];
+        s->free_list.erase(s->free_list.begin() + best);
+    } else {
+        out->ptr = nullptr;
+        HOLO_CUDA(cudaMalloc(&out->ptr, bytes));
+        out->bytes = bytes;
+        s->pool_bytes += bytes;
+    }
+    HOLO_CUDA(cudaMemsetAsync(out->ptr, 0, out->bytes, s->ctx->stream));   // reuse never leaks old bytes (buffer.rs:86-108)
+    return HOLO_OK;
+}
+
+void bind_slot_static(holo_b200_session* s, uint32_t slot) {
+    s->ws->slots[slot].ptr = s->static_binding[slot].ptr;
+    s->ws->slots[slot].bytes = s->static_binding[slot].bytes;
+    s->ws->slots[slot].owned = false;
+}
+
+void bind_slot(holo_b200_session* s, uint32_t slot, void* ptr, uint64_t bytes) {
+    HoloSlot& sl = s->ws->slots[slot];
+    sl.ptr = ptr;
+    sl.bytes = bytes;
+    sl.owned = false;   // the pool (or static_binding) owns it
+}
+
+}  // namespace
+
+extern "C" int32_t holo_b200_session_execute_addressed(holo_b200_session* s, const uint8_t* input_labels, uint32_t n_inputs,
+                                                       uint8_t* output_labels, uint32_t n_outputs, HoloAddressedStats* stats) {
+    if (!s) return holo_fail(HOLO_ERR_INIT, "null session");
+    if (!s->addressed) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: the session was not loaded with HOLO_SESSION_ADDRESSED");
+    if (n_inputs != s->ar.inputs.size() || n_outputs != s->ar.outputs.size() || !input_labels || !output_labels)
+        return holo_fail(HOLO_ERR_SHAPE_MISMATCH, "shape mismatch: execute_addressed takes %zu input labels and %zu output labels",
+                         s->ar.inputs.size(), s->ar.outputs.size());
+    HOLO_CUDA(cudaSetDevice(s->ctx->device));
+    HoloAddressedStats st = {};
+    ++s->walk_no;
+
+    // whole-graph memo (session.rs:63-111): the same input labels give the same output labels;
+    // the outputs are bound from the pool if they are all still resident
+    const std::string key(reinterpret_cast<const char*>(input_labels), (size_t)n_inputs * HOLO_LABEL_BYTES);
+    auto hit = s->memo.find(key);
+    if (hit != s->memo.end()) {
+        bool resident = true;
+        for (uint32_t o = 0; o < n_outputs && resident; ++o)
+            resident = s->pool.count(hit->second.first.substr((size_t)o * HOLO_LABEL_BYTES, HOLO_LABEL_BYTES)) != 0;
+        if (resident) {
+            hit->second.second = ++s->memo_tick;
+            for (uint32_t o = 0; o < n_outputs; ++o) {
+                holo_b200_session::PoolEntry& e = s->pool[hit->second.first.substr((size_t)o * HOLO_LABEL_BYTES, HOLO_LABEL_BYTES)];
+                e.last_walk = s->walk_no;
+                bind_slot(s, s->ar.outputs[o].slot, e.ptr, e.bytes);
+            }
+            memcpy(output_labels, hit->second.first.data(), (size_t)n_outputs * HOLO_LABEL_BYTES);
+            st.memo_hit = 1;
+            st.pool_bytes = s->pool_bytes;
+            if (stats) *stats = st;
+            return HOLO_OK;
+        }
+    }
+
+    // results of the previous walk that had no label are free again
+    for (auto& e : s->transients) s->free_list.push_back(e);
+    s->transients.clear();
+
+    std::vector<std::string> label = s->slot_label_init;
+    for (uint32_t i = 0; i < n_inputs; ++i) {
+        const uint32_t slot = s->ar.inputs[i].slot;
+        label[slot] = label_str(input_labels + (size_t)i * HOLO_LABEL_BYTES);
+        bind_slot(s, slot, s->static_binding[slot].ptr, s->static_binding[slot].bytes);   // the caller wrote the input there
+    }
+    for (size_t ci = 0; ci < s->calls.size(); ++ci) {
+        const holo_b200_session::NodeMeta& m = s->meta[ci];
+        // operand labels, in kernel order; a commutative op sorts them (session.rs:1095-1102)
+        std::vector<std::string> in;
+        bool addressable = m.addressable;
+        for (uint32_t sl : m.inputs) {
+            if (label[sl].empty()) { addressable = false; break; }
+            in.push_back(label[sl]);
+        }
+        std::vector<std::string> out_label(m.outputs.size());
+        if (addressable) {
+            if (m.sig.commutative) std::sort(in.begin(), in.end());
+            std::string cat;
+            for (const std::string& l : in) cat += l;
+            for (size_t o = 0; o < m.outputs.size(); ++o) {
+                uint8_t l[HOLO_LABEL_BYTES];
+                if (s->calls[ci].kind == HOLO_K_RESHAPE && !in.empty()) {
+                    out_label[o] = in[0];   // a reshape relabels nothing: its value is its input's (session.rs:1107-1114)
+                    continue;
+                }
+                uint8_t params[80];
+                memcpy(params, m.sig.params, m.sig.len);
+                size_t plen = m.sig.len;
+                if (o > 0) params[plen++] = (uint8_t)o;
+                holo_label_derive(m.sig.opcode, params, plen, reinterpret_cast<const uint8_t*>(cat.data()), in.size(), l);
+                out_label[o] = label_str(l);
+            }
+        }
+        // interior reuse: every result resident and none a graph output -> bind, do not dispatch
+        bool reuse = addressable;
+        for (size_t o = 0; o < m.outputs.size() && reuse; ++o)
+            reuse = !s->is_output_slot[m.outputs[o]] && s->pool.count(out_label[o]) != 0;
+        if (reuse) {
+            for (size_t o = 0; o < m.outputs.size(); ++o) {
+                holo_b200_session::PoolEntry& e = s->pool[out_label[o]];
+                e.last_walk = s->walk_no;
+                bind_slot(s, m.outputs[o], e.ptr, e.bytes);
+                label[m.outputs[o]] = out_label[o];
+            }
+            ++st.skipped;
+            continue;
+        }
+        for (size_t o = 0; o < m.outputs.size(); ++o) {
+            const uint32_t slot = m.outputs[o];
+            holo_b200_session::PoolEntry e;
+            HOLO_TRY(pool_acquire(s, slot < s->slot_need.size() ? s->slot_need[slot] : 64, &e));
+            e.last_walk = s->walk_no;
+            bind_slot(s, slot, e.ptr, e.bytes);
+            if (addressable) {
+                auto old = s->pool.find(out_label[o]);
+                if (old != s->pool.end()) s->free_list.push_back(old->second);   // recomputed (a graph output): the old copy goes
+                s->pool[out_label[o]] = e;
+                label[slot] = out_label[o];
+            } else {
+                s->transients.push_back(e);
+                label[slot].clear();
+            }
+        }
+        HOLO_TRY(holo_dispatch_internal(s->ctx, &s->calls[ci], s->ws));
+        ++st.dispatched;
+    }
+    // output labels; an output without a label (not derivable) reports 71 zero bytes
+    std::string outs;
+    bool all = true;
+    for (uint32_t o = 0; o < n_outputs; ++o) {
+        const std::string& l = label[s->ar.outputs[o].slot];
+        if (l.empty()) {
+            memset(output_labels + (size_t)o * HOLO_LABEL_BYTES, 0, HOLO_LABEL_BYTES);
+            all = false;
+        } else {
+            memcpy(output_labels + (size_t)o * HOLO_LABEL_BYTES, l.data(), HOLO_LABEL_BYTES);
+        }
+        outs += l.empty() ? std::string(HOLO_LABEL_BYTES, '\0') : l;
+    }
+    if (all) {
+        if (s->memo.size() >= 1024 && !s->memo.count(key)) {   // least recently used entry goes (session.rs:93-105)
+            auto lru = s->memo.begin();
+            for (auto it = s->memo.begin(); it != s->memo.end(); ++it)
+                if (it->second.second < lru->second.second) lru = it;
+            s->memo.erase(lru);
+        }
+        s->memo[key] = {outs, ++s->memo_tick};
+    }
+    // two-generation rotation: what neither this walk nor the one before touched is released
+    for (auto it = s->pool.begin(); it != s->pool.end();) {
+        if (it->second.last_walk + 1 < s->walk_no) {
+            s->free_list.push_back(it->second);
+            it = s->pool.erase(it);
+        } else {
+            ++it;
+        }
+    }
+    st.pool_bytes = s->pool_bytes;
+    if (stats) *stats = st;
+    return HOLO_OK;
+}
+
+extern "C" int32_t holo_b200_label_bytes(const uint8_t* data, uint64_t len, uint8_t out71[71]) {
+    if ((!data && len) || !out71) return holo_fail(HOLO_ERR_INIT, "null argument");
+    holo_label_of_bytes(data, (size_t)len, out71);
+    return HOLO_OK;
+}
+
+extern "C" int32_t holo_b200_label_derive(uint16_t opcode, const uint8_t* params, uint32_t params_len, const uint8_t* labels,
+                                          uint32_t n_labels, uint8_t out71[71]) {
+    if ((!params && params_len) || (!labels && n_labels) || !out71) return holo_fail(HOLO_ERR_INIT, "null argument");
+    holo_label_derive(opcode, params, params_len, labels, n_labels, out71);
+    return HOLO_OK;
+}
+
+extern "C" int32_t holo_b200_op_signature(const HoloKernelCall* call, uint16_t* opcode, uint8_t params64[64], uint32_t* params_len) {
+    HoloOpSignature sig;
+    if (!call || !holo_op_signature(*call, &sig))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: no operation signature for KernelCall variant %u", call ? call->kind : 0);
+    if (opcode) *opcode = sig.opcode;
+    if (params64) memcpy(params64, sig.params, sig.len);
+    if (params_len) *params_len = sig.len;
+    return HOLO_OK;
+}
+
+namespace {
+
 int32_t run_calls(holo_b200_session* s) {
     for (const SessionNode& n : s->nodes) {
         if (n.reduce_add) HOLO_TRY(run_reduce_add(s, n));
@@ -406,7 +682,8 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
     HOLO_CUDA(cudaSetDevice(ctx->device));
     holo_b200_session* s = new holo_b200_session();
     s->ctx = ctx;
-    int32_t rc = holo_archive_parse(archive, len, verify != 0, &s->ar);
+    s->addressed = (verify & HOLO_SESSION_ADDRESSED) != 0;
+    int32_t rc = holo_archive_parse(archive, len, (verify & HOLO_SESSION_VERIFY) != 0, &s->ar);
     if (rc != HOLO_OK) {
         delete s;
         return rc;
@@ -432,8 +709,18 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
                     if (refs.written[r]) written_slots.insert(refs.refs[r]->slot);
         }
         for (const HoloPort& p : s->ar.inputs) written_slots.insert(p.slot);   // inputs are rewritten by the caller
-        plan_sibling_merges(s, const_slots, written_slots);
-        fuse_all_reduce_add(s, out_slots);
+        if (s->addressed) {
+            // one node per call: merged weights, batched launches and aliased slots all bake
+            // device pointers in at load, which the label-keyed pool rebinds per walk
+            for (const HoloKernelCall& c : s->calls) {
+                SessionNode node;
+                node.call = c;
+                s->nodes.push_back(node);
+            }
+        } else {
+            plan_sibling_merges(s, const_slots, written_slots);
+            fuse_all_reduce_add(s, out_slots);
+        }
     }
 
     // slot sizing (session.rs:544-629)
@@ -469,8 +756,8 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
     for (const HoloKernelCall& c : s->calls) {
         if (c.kind != HOLO_K_KV_CACHE_WRITE) continue;
         const HoloKvCacheWriteCall& k = c.u.kv_cache_write;
-        if (in_slots.count(k.cache.slot) && out_slots.count(k.output.slot) && k.cache.offset == 0 && k.output.offset == 0 &&
-            k.cache.slot != k.output.slot) {
+        if (!s->addressed && in_slots.count(k.cache.slot) && out_slots.count(k.output.slot) && k.cache.offset == 0 &&
+            k.output.offset == 0 && k.cache.slot != k.output.slot) {
             alias[k.output.slot] = k.cache.slot;
             need[k.cache.slot] = std::max(need[k.cache.slot], need[k.output.slot]);
             ++s->moved_in_place;
@@ -498,7 +785,11 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
     }
     if (rc == HOLO_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = holo_fail(HOLO_ERR_INIT, "backend init failed: constant upload");
     if (rc == HOLO_OK) rc = build_merged_weights(s);
-    if (rc == HOLO_OK) rc = plan_micro_batches(s);
+    if (rc == HOLO_OK && !s->addressed) rc = plan_micro_batches(s);
+    if (rc == HOLO_OK && s->addressed) {
+        s->slot_need.assign(need.begin(), need.end());
+        rc = prepare_addressed(s);
+    }
     if (rc != HOLO_OK) {
         if (s->ws) holo_b200_workspace_destroy(s->ws);
         delete s;
@@ -517,6 +808,13 @@ extern "C" void holo_b200_session_destroy(holo_b200_session* s) {
         if (g.b_concat) cudaFree(g.b_concat);
     for (MicroBatch& b : s->batches)
         if (b.dev_ops) cudaFree(b.dev_ops);
+    if (s->addressed) {
+        // hand the load-time buffers back to the workspace before it frees them, then the pool's own
+        for (size_t i = 0; i < s->static_binding.size() && i < s->ws->slots.size(); ++i) s->ws->slots[i] = s->static_binding[i];
+        for (auto& kv : s->pool) cudaFree(kv.second.ptr);
+        for (auto& e : s->free_list) cudaFree(e.ptr);
+        for (auto& e : s->transients) cudaFree(e.ptr);
+    }
     if (s->ws) holo_b200_workspace_destroy(s->ws);
     delete s;
 }
@@ -569,6 +867,9 @@ extern "C" int32_t holo_b200_session_call(holo_b200_session* s, uint32_t index, 
 
 extern "C" int32_t holo_b200_session_execute(holo_b200_session* s) {
     if (!s) return holo_fail(HOLO_ERR_INIT, "null session");
+    if (s->addressed) {   // the plain walk of an addressed session runs on the load-time buffers
+        for (size_t i = 0; i < s->static_binding.size(); ++i) bind_slot_static(s, (uint32_t)i);
+    }
     HOLO_CUDA(cudaSetDevice(s->ctx->device));
     if (s->graph) {
         HOLO_CUDA(cudaGraphLaunch(s->graph, s->ctx->stream));

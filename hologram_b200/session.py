@@ -19,13 +19,51 @@ for _name, _res, _args in [
     ("holo_b200_session_execute", i32, [vp]),
     ("holo_b200_session_capture", i32, [vp]),
     ("holo_b200_archive_check", i32, [vp, u64, i32] + [C.POINTER(u32)] * 4),
+    ("holo_b200_session_execute_addressed", i32, [vp, vp, u32, vp, u32, vp]),
+    ("holo_b200_label_bytes", i32, [vp, u64, vp]),
+    ("holo_b200_label_derive", i32, [C.c_uint16, vp, u32, vp, u32, vp]),
+    ("holo_b200_op_signature", i32, [C.POINTER(kc.KernelCall), C.POINTER(C.c_uint16), vp, C.POINTER(u32)]),
 ]:
     _fn = getattr(lib, _name)
     _fn.restype, _fn.argtypes = _res, _args
 
 SESSION_SYMBOLS = ["holo_b200_session_load", "holo_b200_session_destroy", "holo_b200_session_workspace",
                    "holo_b200_session_info", "holo_b200_session_nodes", "holo_b200_session_port", "holo_b200_session_call",
-                   "holo_b200_session_execute", "holo_b200_session_capture", "holo_b200_archive_check"]
+                   "holo_b200_session_execute", "holo_b200_session_capture", "holo_b200_archive_check",
+                   "holo_b200_session_execute_addressed", "holo_b200_label_bytes", "holo_b200_label_derive",
+                   "holo_b200_op_signature"]
+
+LABEL_BYTES = 71
+
+
+class AddressedStats(C.Structure):
+    _fields_ = [("dispatched", u32), ("skipped", u32), ("memo_hit", u32), ("pool_bytes", u64)]
+
+
+def label_bytes(data):
+    """`address_bytes` (crates/hologram-archive/src/address.rs:83-86): the 71-byte label of a leaf value."""
+    a = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+    out = np.empty(LABEL_BYTES, dtype=np.uint8)
+    _check(lib.holo_b200_label_bytes(_host_ptr(a) if a.size else None, a.size, _host_ptr(out)))
+    return out.tobytes()
+
+
+def label_derive(opcode, params, labels):
+    """`derive_label` (address.rs:108-116) over an opcode, parameter bytes and ordered operand labels."""
+    pr = np.frombuffer(bytes(params), dtype=np.uint8)
+    lb = np.frombuffer(b"".join(labels), dtype=np.uint8)
+    out = np.empty(LABEL_BYTES, dtype=np.uint8)
+    _check(lib.holo_b200_label_derive(opcode, _host_ptr(pr) if pr.size else None, pr.size, _host_ptr(lb) if lb.size else None,
+                                      len(labels), _host_ptr(out)))
+    return out.tobytes()
+
+
+def op_signature(call):
+    """`KernelCall::op_signature` (kernel_call.rs:1321-1516): (opcode, parameter bytes)."""
+    op, n = C.c_uint16(), u32()
+    buf = np.zeros(64, dtype=np.uint8)
+    _check(lib.holo_b200_op_signature(C.byref(call), C.byref(op), _host_ptr(buf), C.byref(n)))
+    return op.value, buf[:n.value].tobytes()
 
 
 def archive_check(archive_bytes, verify=True):
@@ -46,10 +84,12 @@ class Port:
 
 
 class InferenceSession:
-    def __init__(self, backend, archive_bytes, verify=True):
+    def __init__(self, backend, archive_bytes, verify=True, addressed=False):
         h = vp()
         buf = np.frombuffer(archive_bytes, dtype=np.uint8)
-        _check(lib.holo_b200_session_load(backend._h, _host_ptr(buf), buf.size, 1 if verify else 0, C.byref(h)))
+        flags = (1 if verify else 0) | (2 if addressed else 0)
+        _check(lib.holo_b200_session_load(backend._h, _host_ptr(buf), buf.size, flags, C.byref(h)))
+        self.addressed = addressed
         self._h = h
         self.backend = backend
         backend._workspaces.add(self)
@@ -74,6 +114,18 @@ class InferenceSession:
         slot, cnt, dt = u32(), u64(), C.c_uint8()
         _check(lib.holo_b200_session_port(self._h, is_output, i, name, 256, C.byref(slot), C.byref(cnt), C.byref(dt)))
         return Port(name.value.decode(), slot.value, cnt.value, dt.value)
+
+    def execute_addressed(self, input_labels):
+        """`execute_addressed` (session.rs:942-984): the inputs have been written; `input_labels` are their
+        71-byte labels in port order. Returns (output labels, AddressedStats)."""
+        assert len(input_labels) == len(self.inputs)
+        ins = np.frombuffer(b"".join(input_labels), dtype=np.uint8)
+        outs = np.zeros(LABEL_BYTES * len(self.outputs), dtype=np.uint8)
+        st = AddressedStats()
+        _check(lib.holo_b200_session_execute_addressed(self._h, _host_ptr(ins), len(self.inputs), _host_ptr(outs),
+                                                       len(self.outputs), C.byref(st)))
+        raw = outs.tobytes()
+        return [raw[i * LABEL_BYTES:(i + 1) * LABEL_BYTES] for i in range(len(self.outputs))], st
 
     def close(self):
         if getattr(self, "_h", None):

@@ -407,6 +407,32 @@ int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const void* q, c
                                              uint32_t batch, uint32_t heads, uint32_t kv_heads, uint32_t past_len,
                                              uint32_t head_dim, uint32_t scale_bits, uint8_t dtype);
 
+/* ---- content-addressed execution (crates/hologram-exec/src/session.rs:942-984 execute_addressed,
+ * :1052-1289 the walk; labels crates/hologram-archive/src/address.rs:83-116).
+ * A label is 71 ASCII bytes, "blake3:" + 64 hex digits. Load the session with
+ * HOLO_SESSION_ADDRESSED or-ed into `verify`; write the inputs, pass their labels (port order) and
+ * receive the outputs' labels. A node whose derived label is already resident in the session's
+ * device pool is bound by pointer and not dispatched; a repeat of the same input labels is answered
+ * from the memo without touching the device. Labels returned for outputs are the internal
+ * derivation (derive_label); the witnessed boundary form of the reference is not produced. */
+#define HOLO_SESSION_VERIFY 1
+#define HOLO_SESSION_ADDRESSED 2
+typedef struct HoloAddressedStats {
+    uint32_t dispatched; /* calls launched by this walk */
+    uint32_t skipped;    /* calls answered by a resident value */
+    uint32_t memo_hit;   /* 1: the whole graph was answered from the memo */
+    uint64_t pool_bytes; /* device bytes owned by the label pool (resident + released) */
+} HoloAddressedStats;
+int32_t holo_b200_session_execute_addressed(holo_b200_session* s, const uint8_t* input_labels, uint32_t n_inputs,
+                                            uint8_t* output_labels, uint32_t n_outputs, HoloAddressedStats* stats);
+/* address_bytes: the label of a leaf value (address.rs:83-86). */
+int32_t holo_b200_label_bytes(const uint8_t* data, uint64_t len, uint8_t out71[71]);
+/* derive_label: BLAKE3(opcode LE16 || params || labels...) as a label (address.rs:108-116). */
+int32_t holo_b200_label_derive(uint16_t opcode, const uint8_t* params, uint32_t params_len, const uint8_t* labels,
+                               uint32_t n_labels, uint8_t out71[71]);
+/* KernelCall::op_signature (kernel_call.rs:1321-1516): opcode and scalar parameter bytes. */
+int32_t holo_b200_op_signature(const HoloKernelCall* call, uint16_t* opcode, uint8_t params64[64], uint32_t* params_len);
+
 /* ---- tensor-parallel group (no reference counterpart: the reference is single-device).
  * `nccl_unique_id` is the 128-byte ncclUniqueId produced by holo_b200_nccl_unique_id on rank 0
  * and broadcast by the host launcher. */

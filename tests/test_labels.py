@@ -1,0 +1,76 @@
+"""Content labels and operation signatures (host only, no GPU): the identity machinery of the
+reference's content-addressed executor, restated behind the C ABI.
+
+Pins: the frozen op-signature bytes of `plain_matmul`
+(crates/hologram-archive/tests/wire_stability.rs:103-108, 116-125); label shape and sensitivity as
+in crates/hologram-archive/src/address.rs:293-330; the digest itself against the independent
+Python `blake3` package."""
+import struct
+
+import blake3
+import numpy as np
+import pytest
+
+from hologram_b200 import kernel_call as kc
+from hologram_b200 import session as hs
+
+
+def test_label_of_bytes_is_blake3_hex():
+    for data in (b"", b"abc", bytes(range(256)) * 5000):
+        lab = hs.label_bytes(np.frombuffer(data, dtype=np.uint8))
+        assert len(lab) == 71 and lab == b"blake3:" + blake3.blake3(data).hexdigest().encode()
+    assert hs.label_bytes(np.frombuffer(b"abc", np.uint8)) != hs.label_bytes(np.frombuffer(b"abd", np.uint8))
+
+
+def test_derive_label_folds_opcode_params_and_ordered_operands():
+    a = hs.label_bytes(np.arange(10, dtype=np.uint8))
+    b = hs.label_bytes(np.arange(11, dtype=np.uint8))
+    params = bytes([1, 2, 3])
+    got = hs.label_derive(45, params, [a, b])
+    assert got == b"blake3:" + blake3.blake3(struct.pack("<H", 45) + params + a + b).hexdigest().encode()
+    # order-, opcode- and parameter-sensitive (address.rs:321-330)
+    assert hs.label_derive(45, params, [b, a]) != got
+    assert hs.label_derive(46, params, [a, b]) != got
+    assert hs.label_derive(45, bytes([1, 2, 4]), [a, b]) != got
+    assert hs.label_derive(45, params, [a, b]) == got
+
+
+def test_op_signature_frozen_bytes():
+    rb = kc.rb
+    mm = kc.MatMulCall(rb(0, 0, 64), rb(1, 0, 64), rb(2, 0, 64), 2, 8, 4, 8, 0)
+    assert hs.op_signature(kc.KernelCall.MatMul(mm)) == (45, bytes.fromhex("02000000080000000400000008"))
+    # the other variants follow kernel_call.rs:996-1142 / 1321-1516 field for field
+    assert hs.op_signature(kc.KernelCall.MatMulActivation(kc.MatMulActivationCall(mm, kc.FUSED_SILU))) == (
+        105, bytes.fromhex("02000000080000000400000008") + bytes([kc.FUSED_SILU]))
+    assert hs.op_signature(kc.KernelCall.MatMulAdd(kc.MatMulAddCall(mm, rb(3))))[0] == 106
+    un = kc.UnaryCall(rb(0), rb(1), 1000, 16, kc.DTYPE_BF16)
+    assert hs.op_signature(kc.KernelCall.Gelu(un)) == (13, struct.pack("<QHB", 1000, 16, kc.DTYPE_BF16))
+    assert hs.op_signature(kc.KernelCall.Silu(un))[0] == 14 and hs.op_signature(kc.KernelCall.Erf(un))[0] == 31
+    bi = kc.BinaryCall(rb(0), rb(1), rb(2), 77, 16, kc.DTYPE_BF16)
+    assert hs.op_signature(kc.KernelCall.Add(bi)) == (4, struct.pack("<QHB", 77, 16, kc.DTYPE_BF16))
+    assert hs.op_signature(kc.KernelCall.Mul(bi))[0] == 6 and hs.op_signature(kc.KernelCall.Concat(bi))[0] == 61
+    nc = kc.NormCall(rb(0), rb(1), kc.NONE, kc.NONE, rb(2), 64, 4096, 0, 0, 0x3727C5AC, kc.DTYPE_BF16)
+    assert hs.op_signature(kc.KernelCall.RmsNorm(nc)) == (50, struct.pack("<IIIIQBB", 64, 4096, 0, 0, 0x3727C5AC, kc.DTYPE_BF16, 0))
+    nr = kc.NormCall(rb(0), rb(1), kc.NONE, rb(3), rb(2), 64, 4096, 0, 0, 0x3727C5AC, kc.DTYPE_BF16)
+    assert hs.op_signature(kc.KernelCall.AddRmsNorm(nr)) == (53, struct.pack("<IIIIQBB", 64, 4096, 0, 0, 0x3727C5AC, kc.DTYPE_BF16, 1))
+    ro = kc.RoPECall(rb(0), rb(1), rb(2), rb(3), 128, 8192, kc.DTYPE_BF16)
+    assert hs.op_signature(kc.KernelCall.RotaryEmbedding(ro)) == (74, struct.pack("<QIB", 8192, 128, kc.DTYPE_BF16))
+    tr = kc.TransposeCall.make(rb(0), rb(1), (2, 3, 4), (2, 0, 1), kc.DTYPE_F32)
+    assert hs.op_signature(kc.KernelCall.Transpose(tr)) == (60, struct.pack("<BBIBIBIB", 3, kc.DTYPE_F32, 2, 2, 3, 0, 4, 1))
+    kv = kc.KvCacheWriteCall(rb(0), rb(1), rb(2), rb(3), 16, 4096, 1, 128)
+    assert hs.op_signature(kc.KernelCall.KvCacheWrite(kv)) == (120, struct.pack("<IIII", 16, 4096, 1, 128))
+    da = kc.DecodeAttentionValidCall(rb(0), rb(1), rb(2), rb(3), rb(4), rb(5), rb(6), 2, 8, 2, 1, 64, 1, 128, 0, kc.DTYPE_BF16)
+    assert hs.op_signature(kc.KernelCall.DecodeAttentionValid(da)) == (121, struct.pack("<IIIIIIIIB", 2, 8, 2, 1, 64, 1, 128, 0, kc.DTYPE_BF16))
+    dm = kc.DecodeAttentionCall(rb(0), rb(1), rb(2), rb(3), rb(4), rb(5), rb(6), 2, 8, 2, 1, 64, 1, 128, 0, kc.DTYPE_BF16)
+    assert hs.op_signature(kc.KernelCall.DecodeAttention(dm))[0] == 119
+    ly = kc.LayoutCall(rb(0), rb(1), 99, kc.DTYPE_BF16)
+    assert hs.op_signature(kc.KernelCall.Reshape(ly)) == (59, struct.pack("<QB", 99, kc.DTYPE_BF16))
+    assert hs.op_signature(kc.KernelCall.Slice(ly))[0] == 62
+    ga = kc.GatherCall(rb(0), rb(1), rb(2), 1, 32000, 4096, 64, kc.DTYPE_I32, kc.DTYPE_BF16)
+    assert hs.op_signature(kc.KernelCall.Gather(ga)) == (114, struct.pack("<QQQQBB", 1, 32000, 4096, 64, kc.DTYPE_I32, kc.DTYPE_BF16))
+    ca = kc.CastCall(rb(0), rb(1), 50, kc.DTYPE_BF16, kc.DTYPE_F32)
+    assert hs.op_signature(kc.KernelCall.Cast(ca)) == (115, struct.pack("<QBB", 50, kc.DTYPE_BF16, kc.DTYPE_F32))
+    # an all-reduce is not a function of local labels: no signature
+    import hologram_b200 as hb
+    with pytest.raises(hb.BackendError):
+        hs.op_signature(kc.KernelCall.AllReduce(kc.AllReduceCall(rb(0), 8, kc.DTYPE_BF16)))
