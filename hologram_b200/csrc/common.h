@@ -204,6 +204,10 @@ struct HoloMatmulSeg {
     const void* residual;
     uint32_t width;
     uint8_t fused_act;
+    // 1: the product has 2 * width columns laid out as alternating 64-column blocks of a "gate" and an
+    // "up" projection; out[:, j] = narrow(widen(act(narrow(gate_j))) * widen(narrow(up_j))) (the
+    // MatMulActivation -> Mul pair of a gated FFN in one epilogue). Single segment only.
+    uint8_t gated = 0;
 };
 int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* b, uint32_t m, uint32_t k, uint32_t n,
                                  uint8_t dtype, const HoloMatmulSeg* segs, uint32_t nseg);

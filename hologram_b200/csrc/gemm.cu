@@ -47,6 +47,7 @@ struct GemmParams {
     uint32_t* status;
     uint32_t m, n, k, kblocks, splits, box_m;
     int dtype;                // HOLO_DTYPE_BF16 or HOLO_DTYPE_F16 (operands and output)
+    uint32_t gated;           // see HoloMatmulSeg::gated (BN = 128: columns 0..63 of a tile are gate, 64..127 up)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -121,6 +122,17 @@ __device__ __forceinline__ uint16_t epilogue_elem(float acc, const uint16_t* tab
     if (table) h = __ldg(table + h);
     if (residual) h = holo::narrow16(__fadd_rn(holo::widen16(h, dtype), holo::widen16(__ldg(residual + idx), dtype)), dtype);
     return h;
+}
+
+// Gated pair: act(narrow(gate)) * narrow(up), both factors narrowed first, as the unfused
+// MatMulActivation and MatMul would have stored them, the product narrowed once (binary Mul).
+template <bool F16>
+__device__ __forceinline__ uint16_t gated_elem(float gate, float up, const uint16_t* table) {
+    constexpr int dtype = F16 ? HOLO_DTYPE_F16 : HOLO_DTYPE_BF16;
+    uint16_t g = holo::narrow16(gate, dtype);
+    if (table) g = __ldg(table + g);
+    const uint16_t u = holo::narrow16(up, dtype);
+    return holo::narrow16(__fmul_rn(holo::widen16(g, dtype), holo::widen16(u, dtype)), dtype);
 }
 
 // A_ROWS = rows of the A tile that are backed by the ring (the TMA box never has more rows than
@@ -227,7 +239,31 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         asm volatile("bar.sync 1, 128;" ::: "memory");   // all four epilogue warps see the same abort state
         const bool ok = !*s_abort;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok && p.splits == 1) {
+        if (ok && p.splits == 1 && p.gated) {
+            if constexpr (BN == 128) {
+                const uint32_t half_n = p.n >> 1;
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t v[32], w[32];
+                    tmem_ld32(tmem_base + ((quarter * 32u) << 16) + (uint32_t)(c * 32), v);
+                    tmem_ld32(tmem_base + ((quarter * 32u) << 16) + (uint32_t)(64 + c * 32), w);
+                    const uint32_t col0 = (n0 >> 1) + c * 32;
+                    if (row < p.m && col0 < half_n) {
+                        uint16_t* dst = p.seg[0].out + (uint64_t)row * half_n + col0;
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int x = 0; x < 16; ++x) {
+                            const uint16_t lo = gated_elem<F16>(__uint_as_float(v[2 * x]), __uint_as_float(w[2 * x]), p.seg[0].table);
+                            const uint16_t hi = gated_elem<F16>(__uint_as_float(v[2 * x + 1]), __uint_as_float(w[2 * x + 1]), p.seg[0].table);
+                            packed[x] = (uint32_t)lo | ((uint32_t)hi << 16);
+                        }
+#pragma unroll
+                        for (int x = 0; x < 4; ++x)
+                            reinterpret_cast<uint4*>(dst)[x] = make_uint4(packed[4 * x], packed[4 * x + 1], packed[4 * x + 2], packed[4 * x + 3]);
+                    }
+                }
+            }
+        } else if (ok && p.splits == 1) {
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
@@ -292,6 +328,39 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 remote[sidx] = 0;
                 if (sidx < S_) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[sidx]) : "r"(base), "r"(sidx));
             }
+            if (p.gated) {
+                // BN = 128: units 0..15 of a row are gate columns, 16..31 the matching up columns
+                const uint32_t half_n = p.n >> 1;
+                for (uint32_t rl = rank + S_ * ew; rl < rows_valid; rl += S_ * 4) {
+                    if (lane >= 16 || BN != 128) continue;
+                    float4 acc[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t u = lane + 16 * h;
+                        const uint32_t off = rl * (BN * 4) + ((u ^ (rl & 7u)) * 16);
+                        float4 part[8];
+#pragma unroll
+                        for (uint32_t sidx = 0; sidx < 8; ++sidx) {
+                            part[sidx] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (sidx < S_)
+                                asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                             : "=f"(part[sidx].x), "=f"(part[sidx].y), "=f"(part[sidx].z), "=f"(part[sidx].w)
+                                             : "r"(remote[sidx] + off));
+                        }
+                        acc[h] = part[0];
+#pragma unroll
+                        for (uint32_t sidx = 1; sidx < 8; ++sidx)
+                            if (sidx < S_) { acc[h].x += part[sidx].x; acc[h].y += part[sidx].y; acc[h].z += part[sidx].z; acc[h].w += part[sidx].w; }
+                    }
+                    const uint32_t col = (n0 >> 1) + lane * 4, grow = m0 + rl;
+                    if (col < half_n) {
+                        const uint16_t h0 = gated_elem<F16>(acc[0].x, acc[1].x, p.seg[0].table), h1 = gated_elem<F16>(acc[0].y, acc[1].y, p.seg[0].table);
+                        const uint16_t h2 = gated_elem<F16>(acc[0].z, acc[1].z, p.seg[0].table), h3 = gated_elem<F16>(acc[0].w, acc[1].w, p.seg[0].table);
+                        *reinterpret_cast<uint2*>(p.seg[0].out + (uint64_t)grow * half_n + col) =
+                            make_uint2((uint32_t)h0 | ((uint32_t)h1 << 16), (uint32_t)h2 | ((uint32_t)h3 << 16));
+                    }
+                }
+            } else
             for (uint32_t rl = rank + S_ * ew; rl < rows_valid; rl += S_ * 4) {
                 for (uint32_t u = lane; u < BN / 4; u += 32) {
                     const uint32_t off = rl * (BN * 4) + ((u ^ (rl & 7u)) * 16);
@@ -461,13 +530,20 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
         gs[i].col_end = col;
         if (i + 1 < nseg && (col % 32) != 0) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul segment boundary %u is not a multiple of 32", col);
     }
+    const bool gated = segs[0].gated != 0;
+    if (gated) {
+        if (nseg != 1 || (segs[0].width % 64) != 0 || dtype == HOLO_DTYPE_F32)
+            return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: gated matmul takes one 16-bit segment whose width is a multiple of 64");
+        col *= 2;
+        gs[0].col_end = col;
+    }
     if (col != n) return holo_fail(HOLO_ERR_SHAPE_MISMATCH, "shape mismatch: matmul segments cover %u of %u columns", col, n);
     const uint16_t* table = gs[0].table;
     const void* residual = gs[0].residual;
     void* out = gs[0].out;
     const bool tma_ok = dtype != HOLO_DTYPE_F32 && (k % 8) == 0 && (n % 8) == 0 && (((uintptr_t)a | (uintptr_t)b) & 15u) == 0 && encode_tiled_fn() != nullptr;
     const bool tiny = (uint64_t)m * n * k < (1ull << 18);
-    if (nseg > 1 && (!tma_ok || tiny))
+    if ((nseg > 1 || gated) && (!tma_ok || tiny))
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: merged matmul needs the tensor-core path");
     if (!tma_ok || tiny || getenv("HOLO_GEMM_FORCE_CELL")) {
         dim3 grid((n + 127) / 128, m);
@@ -506,6 +582,12 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
         bn = tiles64 <= slots ? 64 : 128;
     }
     if (const char* e = getenv("HOLO_GEMM_BN")) bn = atoi(e) == 64 ? 64 : atoi(e) == 256 ? 256 : 128;
+    if (gated && bn != 128) {   // the gate / up pairing is per 128-wide tile
+        bn = 128;
+        splits = tiles128 >= 148 ? 1 : (192 + tiles128 - 1) / tiles128;
+        if (splits > 8) splits = 8;
+        if (splits > kblocks / 8) splits = kblocks / 8 ? kblocks / 8 : 1;
+    }
     if (const char* e = getenv("HOLO_GEMM_SPLITS")) splits = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : 1;
     if (splits > kblocks) splits = kblocks;
     if (splits > 8) splits = 8;  // one cluster (portable size) per output tile
@@ -518,6 +600,7 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     p.m = m; p.n = n; p.k = k; p.kblocks = kblocks; p.splits = splits;
     p.box_m = m < (uint32_t)BM ? m : (uint32_t)BM;
     p.dtype = dtype;
+    p.gated = gated ? 1u : 0u;
     CUtensorMap ma, mb;
     HOLO_TRY(make_map_2d(&ma, a, k, m, BK, p.box_m));
     HOLO_TRY(make_map_2d(&mb, b, n, k, 64, BK));

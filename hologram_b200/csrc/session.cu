@@ -35,6 +35,10 @@ struct MergedMatmul {
     uint32_t width[3] = {0, 0, 0};
     uint8_t act[3] = {0, 0, 0};
     HoloBufferRef b_src[3];
+    // gated pair: out[0] = act(A W0), out[1] = A W1 and the Mul of the two run as one product whose
+    // weights alternate 64-column blocks of W0 and W1; `gated_out` receives act(A W0) * (A W1)
+    bool gated = false;
+    HoloBufferRef gated_out = {HOLO_NO_SLOT, 0, 0};
 };
 
 // A run of mutually independent small glue calls executed as one launch.
@@ -235,6 +239,13 @@ int32_t build_merged_weights(holo_b200_session* s) {
         for (uint32_t t = 0; t < g.nseg; ++t) {
             uint8_t* src;
             HOLO_TRY(holo_resolve(s->ws, g.b_src[t], (uint64_t)g.k * g.width[t] * 2, &src, nullptr));
+            if (g.gated) {
+                // block j of weight t (64 columns) lands at columns 128 j + 64 t of the concatenation
+                for (uint32_t j = 0; j < g.width[t] / 64; ++j)
+                    HOLO_CUDA(cudaMemcpy2DAsync((uint8_t*)g.b_concat + ((size_t)128 * j + 64 * t) * 2, (size_t)g.n * 2, src + (size_t)64 * j * 2,
+                                                (size_t)g.width[t] * 2, 64 * 2, g.k, cudaMemcpyDeviceToDevice, s->ctx->stream));
+                continue;
+            }
             HOLO_CUDA(cudaMemcpy2DAsync((uint8_t*)g.b_concat + (size_t)col * 2, (size_t)g.n * 2, src, (size_t)g.width[t] * 2,
                                         (size_t)g.width[t] * 2, g.k, cudaMemcpyDeviceToDevice, s->ctx->stream));
             col += g.width[t];
@@ -265,6 +276,16 @@ int32_t run_merged(holo_b200_session* s, const MergedMatmul& g) {
     uint8_t* a;
     HOLO_TRY(holo_resolve(s->ws, g.a, (uint64_t)g.m * g.k * 2, &a, nullptr));
     HoloMatmulSeg segs[3];
+    if (g.gated) {
+        uint8_t* o;
+        HOLO_TRY(holo_resolve(s->ws, g.gated_out, (uint64_t)g.m * g.width[0] * 2, &o, nullptr));
+        segs[0].out = o;
+        segs[0].residual = nullptr;
+        segs[0].width = g.width[0];
+        segs[0].fused_act = g.act[0];
+        segs[0].gated = 1;
+        return holo_launch_matmul_multi(s->ctx, a, g.b_concat, g.m, g.k, g.n, HOLO_DTYPE_BF16, segs, 1);
+    }
     for (uint32_t t = 0; t < g.nseg; ++t) {
         uint8_t* o;
         HOLO_TRY(holo_resolve(s->ws, g.out[t], (uint64_t)g.m * g.width[t] * 2, &o, nullptr));
@@ -274,6 +295,52 @@ int32_t run_merged(holo_b200_session* s, const MergedMatmul& g) {
         segs[t].fused_act = g.act[t];
     }
     return holo_launch_matmul_multi(s->ctx, a, g.b_concat, g.m, g.k, g.n, HOLO_DTYPE_BF16, segs, g.nseg);
+}
+
+// Gated FFN: a merged pair {act(A W0), A W1} whose two results are read only by the Mul that follows
+// becomes one product with a gated epilogue; the Mul node is absorbed and the two intermediates are
+// never written. Per-element arithmetic is that of the three calls (both factors narrowed before
+// the multiply, one narrowing after).
+void fuse_gated_pairs(holo_b200_session* s, const std::set<uint32_t>& output_slots) {
+    if (getenv("HOLO_SESSION_NO_GATED")) return;
+    std::vector<SessionNode> out;
+    for (size_t i = 0; i < s->nodes.size(); ++i) {
+        SessionNode n = s->nodes[i];
+        if (n.merged >= 0 && i + 1 < s->nodes.size()) {
+            MergedMatmul& g = s->merged[n.merged];
+            const SessionNode& nx = s->nodes[i + 1];
+            const uint64_t count = (uint64_t)g.m * g.width[0];
+            bool ok = g.nseg == 2 && g.act[0] != 0 && g.act[1] == 0 && g.width[0] == g.width[1] && (g.width[0] % 64) == 0 &&
+                      nx.merged < 0 && nx.batch < 0 && nx.call.kind == HOLO_K_MUL && nx.call.u.binary.dtype == HOLO_DTYPE_BF16 &&
+                      nx.call.u.binary.element_count == count && !output_slots.count(g.out[0].slot) && !output_slots.count(g.out[1].slot);
+            if (ok) {
+                const HoloBinaryCall& b = nx.call.u.binary;
+                ok = (same_range(b.a, g.out[0]) && same_range(b.b, g.out[1])) || (same_range(b.a, g.out[1]) && same_range(b.b, g.out[0]));
+            }
+            for (size_t j = i + 2; ok && j < s->nodes.size(); ++j) {   // nobody else reads the two intermediates
+                if (s->nodes[j].merged >= 0) {
+                    const uint32_t a = s->merged[s->nodes[j].merged].a.slot;
+                    ok = a != g.out[0].slot && a != g.out[1].slot;
+                    continue;
+                }
+                HoloKernelCall tmp = s->nodes[j].call;
+                HoloRefList refs;
+                if (!holo_collect_refs(&tmp, &refs)) continue;
+                for (int r = 0; r < refs.n; ++r)
+                    if (!refs.written[r] && (refs.refs[r]->slot == g.out[0].slot || refs.refs[r]->slot == g.out[1].slot)) ok = false;
+            }
+            if (ok) {
+                g.gated = true;
+                g.gated_out = nx.call.u.binary.output;
+                s->merged_calls += 1;
+                out.push_back(n);
+                ++i;   // the Mul is absorbed
+                continue;
+            }
+        }
+        out.push_back(n);
+    }
+    s->nodes.swap(out);
 }
 
 // Tensor parallel: an AllReduce over a buffer, directly followed by the Add of that buffer and
@@ -719,6 +786,7 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
             }
         } else {
             plan_sibling_merges(s, const_slots, written_slots);
+            fuse_gated_pairs(s, out_slots);
             fuse_all_reduce_add(s, out_slots);
         }
     }

@@ -33,11 +33,12 @@ def test_load_fuses_and_moves_in_place(backend):
     kinds = [sess.call(i).kind for i in range(sess.n_calls)]
     assert kinds.count(kc.K_MATMUL_ACTIVATION) == cfg.n_layers and kinds.count(kc.K_MATMUL_ADD) == 2 * cfg.n_layers
     assert kc.K_SILU not in kinds and kc.K_ADD not in kinds
-    # launches per walk: q/k/v and gate/up (shared A) run as 2 merged matmuls per layer; the RoPE
-    # pair, the quantizer pair and all trailing KV appends run as batched launches
+    # launches per walk: q/k/v and gate/up (shared A) run as 2 merged matmuls per layer, the gate/up
+    # product also absorbing the SwiGLU Mul; the RoPE pair, the quantizer pair and all trailing KV
+    # appends run as batched launches
     L = cfg.n_layers
-    assert sess.merged_calls == 5 * L + 4 * L + 4 * L
-    assert sess.n_nodes == 10 * L + 4
+    assert sess.merged_calls == 6 * L + 4 * L + 4 * L
+    assert sess.n_nodes == 9 * L + 4
     assert [p.name for p in sess.outputs][0] == "logits"
     # the moved cache shares its buffer with the input port
     assert sess.device_ptr("l0.k_codes")[0] == sess.device_ptr("l0.k_codes_next")[0]
