@@ -64,6 +64,7 @@ def _load():
         "holo_b200_nccl_unique_id": (i32, [vp]),
         "holo_b200_ctx_init_tp": (i32, [vp, vp, i32, i32]),
         "holo_b200_ctx_tp_transport": (i32, [vp]),
+        "holo_b200_tp_emulate_all_reduce": (i32, [vp, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), u64, C.c_uint8, i32]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -80,7 +81,7 @@ EXPORTED_SYMBOLS = [
     "holo_b200_workspace_create", "holo_b200_workspace_destroy", "holo_b200_workspace_alloc",
     "holo_b200_workspace_bind", "holo_b200_workspace_slot", "holo_b200_workspace_upload",
     "holo_b200_workspace_download", "holo_b200_dispatch", "holo_b200_dispatch_host", "holo_b200_nccl_unique_id",
-    "holo_b200_ctx_init_tp", "holo_b200_ctx_tp_transport",
+    "holo_b200_ctx_init_tp", "holo_b200_ctx_tp_transport", "holo_b200_tp_emulate_all_reduce",
 ]
 
 
@@ -150,6 +151,13 @@ class B200Backend:
     def tp_transport(self):
         """0 = no tensor-parallel group, 1 = NCCL, 2 = the one-shot peer-memory kernel."""
         return int(lib.holo_b200_ctx_tp_transport(self._h))
+
+    def emulate_all_reduce(self, workspace, partial_slots, out_slots, count, dtype, residual_slots=None, repeats=1):
+        """The peer-memory all-reduce with every rank emulated on this GPU (one cooperative launch)."""
+        w = len(partial_slots)
+        arr = lambda slots: (C.c_void_p * w)(*[workspace.slot(s)[0] for s in slots])
+        res = arr(residual_slots) if residual_slots is not None else None
+        _check(lib.holo_b200_tp_emulate_all_reduce(self._h, w, arr(partial_slots), res, arr(out_slots), count, dtype, repeats))
 
     @staticmethod
     def nccl_unique_id():

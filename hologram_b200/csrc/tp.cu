@@ -104,10 +104,9 @@ __device__ __forceinline__ bool ll_load(const uint8_t* base, uint64_t unit, uint
     return false;
 }
 
-__global__ void __launch_bounds__(P2P_THREADS) all_reduce_p2p_kernel(const P2PParams p) {
-    holo_pdl_trigger();
-    holo_pdl_wait();
-    const uint32_t T = gridDim.x * P2P_THREADS, t = blockIdx.x * P2P_THREADS + threadIdx.x;
+// One rank's part of the all-reduce, run by `nctas` CTAs of which this is number `cta`.
+__device__ __forceinline__ void all_reduce_p2p_body(const P2PParams& p, uint32_t cta, uint32_t nctas) {
+    const uint32_t T = nctas * P2P_THREADS, t = cta * P2P_THREADS + threadIdx.x;
     const uint32_t U = p.units_per_slice, W = (uint32_t)p.world, me = (uint32_t)p.rank;
     const uint32_t epoch = p.state[0] + 1;
     const uint2* part2 = reinterpret_cast<const uint2*>(p.partial);
@@ -161,11 +160,27 @@ __global__ void __launch_bounds__(P2P_THREADS) all_reduce_p2p_kernel(const P2PPa
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t done = atomicAdd(p.state + 1, 1u);
-        if (done == gridDim.x - 1) {
+        if (done == nctas - 1) {
             p.state[1] = 0;
             p.state[0] = epoch;
         }
     }
+}
+
+__global__ void __launch_bounds__(P2P_THREADS) all_reduce_p2p_kernel(const P2PParams p) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    all_reduce_p2p_body(p, blockIdx.x, gridDim.x);
+}
+
+// All ranks of a group as one cooperative launch on one GPU (grid.y = rank): the same device code
+// with every mailbox in local memory. Lets the protocol be run for any world size on a single GPU;
+// the ranks' CTAs wait on one another, hence the cooperative launch (all CTAs co-resident).
+struct P2PEmulation {
+    P2PParams rank[8];
+};
+__global__ void __launch_bounds__(P2P_THREADS) all_reduce_p2p_emulation_kernel(const P2PEmulation e) {
+    all_reduce_p2p_body(e.rank[blockIdx.y], blockIdx.x, gridDim.x);
 }
 
 int32_t nccl_fail(Nccl* n, int rc, const char* where) {
@@ -331,4 +346,51 @@ int32_t holo_all_reduce_add(holo_b200_ctx* ctx, const void* partial, const void*
 int32_t holo_all_reduce(holo_b200_ctx* ctx, void* buf, uint64_t count, uint8_t dtype) {
     if (ctx->tp_world <= 1 || count == 0) return HOLO_OK;
     return holo_all_reduce_add(ctx, buf, nullptr, buf, count, dtype);
+}
+
+// Runs the peer-memory all-reduce for `world` emulated ranks on this context's GPU: partials[r] and
+// outs[r] are device pointers to rank r's `count` 16-bit elements (residuals[r] may be null, outs
+// may alias partials). Mailboxes are allocated for the call and freed again. For tests.
+extern "C" int32_t holo_b200_tp_emulate_all_reduce(holo_b200_ctx* ctx, int32_t world, const void* const* partials, const void* const* residuals,
+                                                   void* const* outs, uint64_t count, uint8_t dtype, int32_t repeats) {
+    if (!ctx || world < 2 || world > 8 || !partials || !outs) return holo_fail(HOLO_ERR_INIT, "backend init failed: bad argument");
+    if ((dtype != HOLO_DTYPE_BF16 && dtype != HOLO_DTYPE_F16) || count == 0 || count > P2P_MAX_ELEMS || (count % (4ull * world)) != 0)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: the peer-memory all-reduce takes 16-bit messages of at most %u elements, a multiple of 4 x world",
+                         P2P_MAX_ELEMS);
+    HOLO_CUDA(cudaSetDevice(ctx->device));
+    uint8_t* boxes = nullptr;
+    uint32_t* states = nullptr;
+    HOLO_CUDA(cudaMalloc(&boxes, (size_t)world * P2P_MAILBOX_BYTES));
+    HOLO_CUDA(cudaMemset(boxes, 0, (size_t)world * P2P_MAILBOX_BYTES));
+    HOLO_CUDA(cudaMalloc(&states, (size_t)world * 256));
+    HOLO_CUDA(cudaMemset(states, 0, (size_t)world * 256));
+    P2PEmulation e;
+    for (int r = 0; r < world; ++r) {
+        P2PParams& p = e.rank[r];
+        p.partial = (const uint16_t*)partials[r];
+        p.residual = residuals ? (const uint16_t*)residuals[r] : nullptr;
+        p.out = (uint16_t*)outs[r];
+        for (int q = 0; q < 8; ++q) p.mailbox[q] = q < world ? boxes + (size_t)q * P2P_MAILBOX_BYTES : nullptr;
+        p.state = states + r * 64;
+        p.status = ctx->dev_status;
+        p.units_per_slice = (uint32_t)(count / 4 / world);
+        p.rank = r;
+        p.world = world;
+        p.dtype = dtype;
+    }
+    const uint64_t widest = (uint64_t)e.rank[0].units_per_slice * (world - 1);
+    uint32_t ctas = (uint32_t)((widest + P2P_THREADS - 1) / P2P_THREADS);
+    if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
+    if (ctas < 1) ctas = 1;
+    void* args[] = {&e};
+    cudaError_t err = cudaSuccess;
+    for (int i = 0; i < repeats && err == cudaSuccess; ++i) {
+        err = cudaLaunchCooperativeKernel((const void*)all_reduce_p2p_emulation_kernel, dim3(ctas, world), dim3(P2P_THREADS), args, 0, ctx->stream);
+        ctx->launches++;
+    }
+    if (err == cudaSuccess) err = cudaStreamSynchronize(ctx->stream);
+    cudaFree(boxes);
+    cudaFree(states);
+    if (err != cudaSuccess) return holo_cuda_fail(err, "all_reduce_p2p_emulation_kernel");
+    return HOLO_OK;
 }

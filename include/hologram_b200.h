@@ -442,6 +442,12 @@ int32_t holo_b200_ctx_init_tp(holo_b200_ctx* ctx, const uint8_t nccl_unique_id[1
  * 2 = the library's own one-shot kernel over peer memory (CUDA IPC mailboxes; every rank sums
  * in rank order, so all ranks hold identical bits). Set HOLO_TP_P2P=0 to stay on NCCL. */
 int32_t holo_b200_ctx_tp_transport(holo_b200_ctx* ctx);
+/* Self-check of the peer-memory all-reduce on ONE GPU: `world` (2..8) ranks run as one cooperative
+ * launch of the same device code, every mailbox in local memory. partials / residuals / outs are
+ * host arrays of `world` device pointers to `count` 16-bit elements each (residuals or its entries
+ * may be null; outs may alias partials). Synchronises. */
+int32_t holo_b200_tp_emulate_all_reduce(holo_b200_ctx* ctx, int32_t world, const void* const* partials, const void* const* residuals,
+                                        void* const* outs, uint64_t count, uint8_t dtype, int32_t repeats);
 
 /* Library version / build info string (static storage). */
 const char* holo_b200_version(void);
