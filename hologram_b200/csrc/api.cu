@@ -72,6 +72,7 @@ extern "C" int32_t holo_b200_ctx_create(int32_t device, holo_b200_ctx** out) {
         delete ctx;
         return holo_fail(HOLO_ERR_INIT, "backend init failed: arrival counter allocation");
     }
+    cudaDeviceSynchronize();   // the clears above ran on the default stream, which the context's stream does not wait for
     *out = ctx;
     return HOLO_OK;
 }
@@ -510,6 +511,26 @@ int32_t do_quantize_rows(holo_b200_ctx* ctx, const HoloQuantizeRowsI8Call& c, ho
     return holo_launch_quantize_rows(ctx, in, c.dtype, c.rows, c.row_len, (int8_t*)codes, (float*)scales);
 }
 
+// Extension: RotaryEmbedding + QuantizeRowsI8 over the rotated rows (one row = one head).
+int32_t do_rope_quantize(holo_b200_ctx* ctx, const HoloRopeQuantizeCall& c, holo_b200_workspace* ws) {
+    if (!holo_is_compute_float(c.dtype)) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: rope_quantize_rows_i8 dtype %u", c.dtype);
+    if (c.row_len == 0 || c.row_len % 2 != 0)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: rope: head_dim must be even and divide the element count");
+    const uint64_t n = c.rows * c.row_len, ib = n * holo_dtype_size(c.dtype);
+    uint8_t *x, *co, *si, *ro, *codes, *scales;
+    HOLO_TRY(holo_resolve(ws, c.rope_output, ib, &ro, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.x, ib, &x, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.cos, ib, &co, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.sin, ib, &si, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.codes, n, &codes, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.scales, c.rows * 4, &scales, nullptr));
+    HOLO_TRY(check_disjoint({ro, ib}, c.rope_output.slot, {{x, ib}, {co, ib}, {si, ib}, {codes, n}, {scales, c.rows * 4}}));
+    HOLO_TRY(check_disjoint({codes, n}, c.codes.slot, {{x, ib}, {co, ib}, {si, ib}, {scales, c.rows * 4}}));
+    HOLO_TRY(check_disjoint({scales, c.rows * 4}, c.scales.slot, {{x, ib}, {co, ib}, {si, ib}}));
+    if (((uintptr_t)scales & 3u) != 0) return holo_fail_slot(c.scales.slot, "scales must be 4-byte aligned");
+    return holo_launch_rope_quantize(ctx, x, co, si, ro, (int8_t*)codes, (float*)scales, c.rows, c.row_len, c.dtype);
+}
+
 // Geometry rules shared by both attention forms (cpu/float_kernels.rs:4192-4266).
 int32_t attn_geometry(uint32_t b, uint32_t h, uint32_t kv, uint32_t m, uint32_t nnew, uint32_t d, uint32_t scale_bits,
                       uint32_t* hkv, float* scale_div, bool* empty) {
@@ -678,6 +699,7 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         case HOLO_K_QUANTIZE_ROWS_I8: return do_quantize_rows(ctx, call->u.quantize_rows_i8, ws);
         case HOLO_K_DECODE_ATTENTION_VALID_Q8: return do_attention_q8(ctx, call->u.decode_attention_valid_q8, ws);
         case HOLO_K_ALL_REDUCE: return do_all_reduce(ctx, call->u.all_reduce, ws);
+        case HOLO_K_ROPE_QUANTIZE_ROWS_I8: return do_rope_quantize(ctx, call->u.rope_quantize, ws);
         default:
             return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: KernelCall variant %u is not served by the B200 backend (no CPU fallback)", call->kind);
     }
@@ -786,6 +808,14 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             l->in(&a.q); l->in(&a.k_past); l->in(&a.k_past_scales); l->in(&a.v_past); l->in(&a.v_past_scales);
             l->in(&a.k_new); l->in(&a.k_new_scales); l->in(&a.v_new); l->in(&a.v_new_scales); l->in(&a.valid_len);
             l->out(&a.output, (uint64_t)a.batch * a.heads * a.q_rows * a.head_dim * holo_dtype_size(a.dtype));
+            return true;
+        }
+        case HOLO_K_ROPE_QUANTIZE_ROWS_I8: {
+            auto& q = c->u.rope_quantize;
+            l->in(&q.x); l->in(&q.cos); l->in(&q.sin);
+            l->out(&q.rope_output, q.rows * q.row_len * holo_dtype_size(q.dtype));
+            l->out(&q.codes, q.rows * q.row_len);
+            l->out(&q.scales, q.rows * 4);
             return true;
         }
         case HOLO_K_ALL_REDUCE:

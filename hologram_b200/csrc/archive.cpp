@@ -144,6 +144,12 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             c.head_dim = r.u32(); c.scale_bits = r.u32(); c.dtype = r.u8();
             break;
         }
+        case HOLO_K_ROPE_QUANTIZE_ROWS_I8: {
+            HoloRopeQuantizeCall& c = out->u.rope_quantize;
+            c.x = r.buf(); c.cos = r.buf(); c.sin = r.buf(); c.rope_output = r.buf(); c.codes = r.buf(); c.scales = r.buf();
+            c.rows = r.u64(); c.row_len = r.u32(); c.dtype = r.u8();
+            break;
+        }
         case HOLO_K_ALL_REDUCE: {
             HoloAllReduceCall& c = out->u.all_reduce;
             c.buffer = r.buf(); c.element_count = r.u64(); c.dtype = r.u8();

@@ -7,8 +7,9 @@
 // The tiled kernel is HBM-bound: every K/V code byte is read once per GQA group. Design:
 //   * persistent grid (2 CTAs per SM): the (plane, 128-key tile) pairs, plane = (batch, kv head),
 //     form one list in plane-major order and every CTA walks an equal contiguous share of it
-//     (flash-decoding split-KV with no idle tail and a ring that never drains); partial (max, sum,
-//     context) triples per (plane, CTA) go to a scratch buffer and a small second kernel merges them.
+//     (flash-decoding split-KV with no idle tail and a ring that never drains); a plane held by one
+//     CTA is finished by it, a plane shared by several goes through partial (max, sum, context)
+//     triples in a scratch buffer that the last sharer to count in merges (nobody waits).
 //   * a producer warp feeds a 3-stage ring with TMA (cp.async.bulk.tensor, 128B swizzle):
 //     K codes, V codes, K scales, V scales per stage; mbarrier full/empty pairs, bounded waits.
 //   * dequantisation is never materialised. q is split into three signed base-256 digits per

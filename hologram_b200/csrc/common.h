@@ -15,11 +15,11 @@ struct HoloSlot {
 };
 
 // One small op of a batched launch (see micro_batch_kernel).
-enum { HOLO_MICRO_KV_WRITE = 0, HOLO_MICRO_ROPE, HOLO_MICRO_QUANT_VEC, HOLO_MICRO_QUANT, HOLO_MICRO_BINARY_VEC, HOLO_MICRO_BINARY };
+enum { HOLO_MICRO_KV_WRITE = 0, HOLO_MICRO_ROPE, HOLO_MICRO_QUANT_VEC, HOLO_MICRO_QUANT, HOLO_MICRO_BINARY_VEC, HOLO_MICRO_BINARY, HOLO_MICRO_ROPE_QUANT };
 struct HoloMicroOp {
     uint32_t kind, cta_begin, cta_count, dtype;
     const void *p0, *p1, *p2;
-    void *o0, *o1;
+    void *o0, *o1, *o2;
     uint64_t n;
     uint32_t a, b, c, d;
 };
@@ -166,6 +166,8 @@ int32_t holo_launch_lut(holo_b200_ctx* ctx, const uint16_t* table, const uint16_
 int32_t holo_launch_binary(holo_b200_ctx* ctx, int op, const void* a, const void* b, void* out, uint64_t n, uint8_t dtype);
 int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* residual, const void* gamma, void* out,
                              uint32_t batch, uint32_t feature, float eps, uint8_t dtype);
+int32_t holo_launch_rope_quantize(holo_b200_ctx* ctx, const void* x, const void* c, const void* s, void* rope_out, int8_t* codes,
+                                  float* scales, uint64_t rows, uint32_t d, uint8_t dtype);
 int32_t holo_launch_transpose(holo_b200_ctx* ctx, const uint8_t* in, uint8_t* out, uint32_t rank, const uint32_t* dims,
                               const uint8_t* perm, uint32_t es);
 int32_t holo_launch_rope(holo_b200_ctx* ctx, const void* x, const void* c, const void* s, void* out, uint32_t head_dim,

@@ -359,6 +359,34 @@ __device__ __forceinline__ void quantize_rows_body(const void* __restrict__ x, i
     }
     if (lane == 0) scales[row] = __fdiv_rn(amax, 127.0f);
 }
+// RoPE of one head per warp followed by quantize_row_i8 of the rotated row: exactly rope_body then
+// quantize_rows_body on the narrowed values the RoPE stored (the warp re-reads its own stores).
+__device__ __forceinline__ void rope_quantize_body(const void* __restrict__ x, const void* __restrict__ c, const void* __restrict__ s,
+                                                   void* __restrict__ rope_out, int8_t* __restrict__ codes, float* __restrict__ scales,
+                                                   uint64_t rows, uint32_t d, int dtype, uint32_t block) {
+    const uint64_t row = (uint64_t)block * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const uint32_t lane = threadIdx.x & 31, half = d >> 1;
+    const uint64_t off = row * d;
+    for (uint32_t j = lane; j < d; j += 32) {
+        const uint64_t e = off + j;
+        const float xe = holo::load_float(x, e, dtype), ce = holo::load_float(c, e, dtype), se = holo::load_float(s, e, dtype);
+        float v;
+        if (j < half) v = __fsub_rn(__fmul_rn(xe, ce), __fmul_rn(holo::load_float(x, e + half, dtype), se));
+        else v = __fadd_rn(__fmul_rn(xe, ce), __fmul_rn(holo::load_float(x, e - half, dtype), se));
+        holo::store_float(rope_out, e, v, dtype);
+    }
+    __syncwarp();
+    quantize_rows_body(rope_out, dtype, rows, d, codes, scales, block);
+}
+__global__ void rope_quantize_kernel(const void* __restrict__ x, const void* __restrict__ c, const void* __restrict__ s,
+                                     void* __restrict__ rope_out, int8_t* __restrict__ codes, float* __restrict__ scales, uint64_t rows,
+                                     uint32_t d, int dtype) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    rope_quantize_body(x, c, s, rope_out, codes, scales, rows, d, dtype, blockIdx.x);
+}
+
 __global__ void quantize_rows_kernel(const void* __restrict__ x, int dtype, uint64_t rows, uint32_t d,
                                      int8_t* __restrict__ codes, float* __restrict__ scales) {
     holo_pdl_trigger();
@@ -440,6 +468,9 @@ __global__ void __launch_bounds__(256) micro_batch_kernel(const HoloMicroOp* __r
             break;
         case HOLO_MICRO_QUANT:
             quantize_rows_body(op.p0, (int)op.dtype, op.n, op.a, (int8_t*)op.o0, (float*)op.o1, block);
+            break;
+        case HOLO_MICRO_ROPE_QUANT:
+            rope_quantize_body(op.p0, op.p1, op.p2, op.o0, (int8_t*)op.o1, (float*)op.o2, op.n, op.a, (int)op.dtype, block);
             break;
         case HOLO_MICRO_BINARY_VEC:
             binary16_vec_body((int)op.a, (const uint4*)op.p0, (const uint4*)op.p1, (uint4*)op.o0, op.n, (int)op.dtype, block, op.cta_count);
@@ -602,6 +633,25 @@ int32_t holo_launch_kv_write(holo_b200_ctx* ctx, const uint8_t* cache, const uin
     if (planes > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "kv_cache_write: planes %u exceeds 65535", planes);
     dim3 grid(new_rows, planes);
     HOLO_CUDA(holo_launch_kernel(ctx, kv_write_rows_kernel, dim3(grid), dim3(32), 0, 1, newr, pos, out, bucket, new_rows, row_bytes));
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_rope_quantize(holo_b200_ctx* ctx, const void* x, const void* c, const void* s, void* rope_out, int8_t* codes,
+                                  float* scales, uint64_t rows, uint32_t d, uint8_t dtype) {
+    if (rows == 0 || d == 0) return HOLO_OK;
+    const int warps = 8;
+    const uint64_t blocks = (rows + warps - 1) / warps;
+    if (blocks > 0x7fffffffull) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "rope_quantize_rows_i8: too many rows");
+    if (ctx->record) {
+        HoloMicroOp m = {};
+        m.kind = HOLO_MICRO_ROPE_QUANT;
+        m.p0 = x; m.p1 = c; m.p2 = s; m.o0 = rope_out; m.o1 = codes; m.o2 = scales; m.a = d; m.n = rows; m.dtype = dtype;
+        record_op(ctx, m, blocks);
+        return HOLO_OK;
+    }
+    HOLO_CUDA(holo_launch_kernel(ctx, rope_quantize_kernel, dim3((unsigned)blocks), dim3(warps * 32), 0, 1, x, c, s, rope_out, codes, scales, rows,
+                                 d, (int)dtype));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }

@@ -65,7 +65,7 @@ struct holo_b200_session {
     std::vector<SessionNode> nodes;     // what a walk actually launches
     std::vector<MergedMatmul> merged;
     std::vector<MicroBatch> batches;
-    uint32_t fused = 0, moved_in_place = 0, merged_calls = 0, batched_calls = 0, reduce_adds = 0;
+    uint32_t fused = 0, moved_in_place = 0, merged_calls = 0, batched_calls = 0, reduce_adds = 0, rope_quant = 0;
     uint64_t device_bytes = 0;
     cudaGraphExec_t graph = nullptr;
 
@@ -165,6 +165,70 @@ uint32_t fuse_matmul_epilogue(std::vector<HoloKernelCall>& calls, const std::set
             c = f;
             dead[i] = true;
             ++fused;
+        }
+    }
+    std::vector<HoloKernelCall> kept;
+    for (size_t i = 0; i < calls.size(); ++i)
+        if (!dead[i]) kept.push_back(calls[i]);
+    calls.swap(kept);
+    return fused;
+}
+
+// A RotaryEmbedding whose output is read by a QuantizeRowsI8 over rows of the RoPE's head_dim (the K
+// path of a decoder layer) becomes one call that does both; the quantizer then no longer depends on
+// a separate launch and can share a batched launch with its siblings. The RoPE output is still
+// written (other readers keep working).
+uint32_t fuse_rope_quantize(std::vector<HoloKernelCall>& calls) {
+    if (getenv("HOLO_SESSION_NO_ROPE_QUANT")) return 0;
+    uint32_t fused = 0;
+    std::vector<bool> dead(calls.size(), false);
+    for (size_t i = 0; i < calls.size(); ++i) {
+        if (calls[i].kind != HOLO_K_ROTARY) continue;
+        const HoloRoPECall ro = calls[i].u.rope;
+        for (size_t j = i + 1; j < calls.size() && j < i + 8; ++j) {
+            if (dead[j]) continue;
+            // stop at anything that rewrites the RoPE's operands or output
+            HoloKernelCall tmp = calls[j];
+            HoloRefList refs;
+            bool clobber = false;
+            if (holo_collect_refs(&tmp, &refs))
+                for (int r = 0; r < refs.n; ++r)
+                    if (refs.written[r] && (refs.refs[r]->slot == ro.output.slot || refs.refs[r]->slot == ro.x.slot ||
+                                            refs.refs[r]->slot == ro.cos.slot || refs.refs[r]->slot == ro.sin.slot))
+                        clobber = true;
+            if (calls[j].kind == HOLO_K_QUANTIZE_ROWS_I8) {
+                const HoloQuantizeRowsI8Call q = calls[j].u.quantize_rows_i8;
+                // the quantizer moves up to the RoPE's position: nothing in between may touch its outputs
+                bool free_to_move = true;
+                for (size_t t = i + 1; t < j && free_to_move; ++t) {
+                    if (dead[t]) continue;
+                    HoloKernelCall mid = calls[t];
+                    HoloRefList mr;
+                    if (!holo_collect_refs(&mid, &mr)) { free_to_move = false; break; }
+                    for (int r = 0; r < mr.n; ++r)
+                        if (mr.refs[r]->slot == q.codes.slot || mr.refs[r]->slot == q.scales.slot) free_to_move = false;
+                }
+                if (free_to_move && same_range(q.input, ro.output) && q.row_len == ro.head_dim && q.rows * q.row_len == ro.element_count &&
+                    q.dtype == ro.dtype) {
+                    HoloKernelCall f;
+                    memset(&f, 0, sizeof f);
+                    f.kind = HOLO_K_ROPE_QUANTIZE_ROWS_I8;
+                    f.u.rope_quantize.x = ro.x;
+                    f.u.rope_quantize.cos = ro.cos;
+                    f.u.rope_quantize.sin = ro.sin;
+                    f.u.rope_quantize.rope_output = ro.output;
+                    f.u.rope_quantize.codes = q.codes;
+                    f.u.rope_quantize.scales = q.scales;
+                    f.u.rope_quantize.rows = q.rows;
+                    f.u.rope_quantize.row_len = q.row_len;
+                    f.u.rope_quantize.dtype = q.dtype;
+                    calls[i] = f;      // at the RoPE's position: its operands are ready there
+                    dead[j] = true;
+                    ++fused;
+                    break;
+                }
+            }
+            if (clobber) break;
         }
     }
     std::vector<HoloKernelCall> kept;
@@ -396,7 +460,8 @@ int32_t run_reduce_add(holo_b200_session* s, const SessionNode& n) {
 }
 
 bool batchable_kind(uint16_t k) {
-    return k == HOLO_K_KV_CACHE_WRITE || k == HOLO_K_ROTARY || k == HOLO_K_QUANTIZE_ROWS_I8 || k == HOLO_K_ADD || k == HOLO_K_MUL;
+    return k == HOLO_K_KV_CACHE_WRITE || k == HOLO_K_ROTARY || k == HOLO_K_QUANTIZE_ROWS_I8 || k == HOLO_K_ADD || k == HOLO_K_MUL ||
+           k == HOLO_K_ROPE_QUANTIZE_ROWS_I8;
 }
 
 // Group consecutive, mutually independent small glue calls (no member reads or writes a slot
@@ -766,6 +831,7 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
     for (const HoloPort& p : s->ar.inputs) in_slots.insert(p.slot);
     for (const HoloPort& p : s->ar.outputs) out_slots.insert(p.slot);
     s->fused = fuse_matmul_epilogue(s->calls, out_slots);
+    if (!s->addressed) s->rope_quant = fuse_rope_quantize(s->calls);
     {
         std::set<uint32_t> const_slots, written_slots;
         for (const HoloConstant& k : s->ar.constants) const_slots.insert(k.slot);

@@ -65,14 +65,15 @@ Nccl* nccl() {
 //   2. reduce:  for my slice, poll the W-1 incoming partials, sum in rank order in f32, truncate,
 //               add the residual, truncate; store locally and push the result to every peer
 //   3. gather:  poll the W-1 incoming result slices and store them
-// Phase 1 never waits, phase 2 waits only for phase 1 of peers, phase 3 only for their phase 2:
+// With two ranks the whole partial is pushed instead and each rank reduces the full message (one
+// NVLink hop instead of two). Phase 1 never waits, phase 2 waits only for phase 1 of peers, phase 3 only for their phase 2:
 // no cycle. Every poll is bounded. A mailbox region is rewritten one epoch later, which a rank
 // reaches only after it has received (hence the peer has finished reading) everything of this one.
 constexpr uint32_t P2P_MAX_ELEMS = 512 * 1024;              // 1 MiB of 16-bit elements
 constexpr uint32_t P2P_THREADS = 256;
 constexpr uint32_t P2P_MAX_CTAS = 64;
 constexpr uint64_t P2P_REGION_BYTES = (uint64_t)P2P_MAX_ELEMS * 4;   // n/4 units x 16 bytes
-constexpr uint64_t P2P_MAILBOX_BYTES = 2 * P2P_REGION_BYTES;         // incoming partials, incoming results
+constexpr uint64_t P2P_MAILBOX_BYTES = 4 * P2P_REGION_BYTES;         // incoming partials, incoming results, two one-shot buffers
 constexpr uint32_t P2P_WAIT_LIMIT = 1u << 22;               // polls before a thread gives up
 
 struct P2PParams {
@@ -83,6 +84,7 @@ struct P2PParams {
     uint32_t* state;           // local: [0] = epochs completed, [1] = CTAs finished in this launch
     uint32_t* status;
     uint32_t units_per_slice;  // n / 4 / world
+    uint32_t one_shot;         // two ranks: push the whole partial, reduce everything locally (one NVLink hop instead of two)
     int rank, world, dtype;
 };
 
@@ -114,6 +116,42 @@ __device__ __forceinline__ void all_reduce_p2p_body(const P2PParams& p, uint32_t
     uint2* out2 = reinterpret_cast<uint2*>(p.out);
     bool ok = true;
 
+    if (p.one_shot) {
+        // every unit is handled by the same thread in both steps, so `out` may alias `partial`
+        // The buffer alternates with the epoch: a peer may still be reading my previous message when
+        // I start the next one (nothing here makes me wait for its reads), but not the one before
+        // that, because I cannot finish an epoch before the peer has started it.
+        const uint32_t N = W * U;
+        const uint64_t region = (2 + (epoch & 1u)) * P2P_REGION_BYTES;
+        for (uint32_t unit = t; unit < N; unit += T) {
+            const uint2 d = part2[unit];
+            for (uint32_t k = 1; k < W; ++k) ll_store(p.mailbox[(me + k) % W] + region, (uint64_t)me * N + unit, d, epoch);
+        }
+        uint8_t* mine = p.mailbox[me] + region;
+        for (uint32_t unit = t; unit < N && ok; unit += T) {
+            const uint2 own = part2[unit];
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (uint32_t r = 0; r < W && ok; ++r) {
+                uint2 v = own;
+                if (r != me) ok = ll_load(mine, (uint64_t)r * N + unit, epoch, &v);
+                acc[0] = __fadd_rn(acc[0], holo::widen16((uint16_t)(v.x & 0xffffu), p.dtype));
+                acc[1] = __fadd_rn(acc[1], holo::widen16((uint16_t)(v.x >> 16), p.dtype));
+                acc[2] = __fadd_rn(acc[2], holo::widen16((uint16_t)(v.y & 0xffffu), p.dtype));
+                acc[3] = __fadd_rn(acc[3], holo::widen16((uint16_t)(v.y >> 16), p.dtype));
+            }
+            if (!ok) break;
+            uint16_t h[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) h[x] = holo::narrow16(acc[x], p.dtype);
+            if (res2) {
+                const uint2 rv = res2[unit];
+                const uint16_t rr[4] = {(uint16_t)(rv.x & 0xffffu), (uint16_t)(rv.x >> 16), (uint16_t)(rv.y & 0xffffu), (uint16_t)(rv.y >> 16)};
+#pragma unroll
+                for (int x = 0; x < 4; ++x) h[x] = holo::narrow16(__fadd_rn(holo::widen16(h[x], p.dtype), holo::widen16(rr[x], p.dtype)), p.dtype);
+            }
+            out2[unit] = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+        }
+    } else {
     // my slice's partials first: phase 2 may write `out` over them when out aliases partial only
     // at the same unit, which is read before it is written
     // 1. scatter
@@ -154,6 +192,7 @@ __device__ __forceinline__ void all_reduce_p2p_body(const P2PParams& p, uint32_t
         uint2 v;
         ok = ll_load(box + P2P_REGION_BYTES, (uint64_t)r * U + u, epoch, &v);
         if (ok) out2[(uint64_t)r * U + u] = v;
+    }
     }
     if (!ok) atomicOr(p.status, 8u);
     // the launch's last CTA advances the epoch (every CTA has read it by then)
@@ -227,7 +266,9 @@ extern "C" int32_t holo_b200_ctx_init_tp(holo_b200_ctx* ctx, const uint8_t id128
     uint8_t* dev_handles = nullptr;
     cudaIpcMemHandle_t handles[8];
     bool ok = want;
-    if (ok) ok = cudaMalloc(&mine, P2P_MAILBOX_BYTES) == cudaSuccess && cudaMemset(mine, 0, P2P_MAILBOX_BYTES) == cudaSuccess;
+    // cleared on the context's stream and waited for before any peer can learn the address
+    if (ok) ok = cudaMalloc(&mine, P2P_MAILBOX_BYTES) == cudaSuccess && cudaMemsetAsync(mine, 0, P2P_MAILBOX_BYTES, ctx->stream) == cudaSuccess &&
+                 cudaStreamSynchronize(ctx->stream) == cudaSuccess;
     if (ok) ok = cudaMalloc(&dev_handles, 8 * sizeof(cudaIpcMemHandle_t)) == cudaSuccess;
     cudaIpcMemHandle_t h;
     memset(&h, 0, sizeof h);
@@ -252,7 +293,8 @@ extern "C" int32_t holo_b200_ctx_init_tp(holo_b200_ctx* ctx, const uint8_t id128
             }
         }
     }
-    if (ok) ok = cudaMalloc(&ctx->tp_epochs, 256) == cudaSuccess && cudaMemset(ctx->tp_epochs, 0, 256) == cudaSuccess;
+    if (ok) ok = cudaMalloc(&ctx->tp_epochs, 256) == cudaSuccess && cudaMemsetAsync(ctx->tp_epochs, 0, 256, ctx->stream) == cudaSuccess &&
+                 cudaStreamSynchronize(ctx->stream) == cudaSuccess;
     cudaGetLastError();  // a failed attempt above must not poison later launches
     // agreement: min over ranks of "my set-up worked" (want == false on one rank switches all off;
     // a rank without a gather buffer cannot take part in a collective, so it has to fail init)
@@ -317,11 +359,12 @@ int32_t holo_all_reduce_add(holo_b200_ctx* ctx, const void* partial, const void*
         p.state = ctx->tp_epochs;
         p.status = ctx->dev_status;
         p.units_per_slice = (uint32_t)(count / 4 / ctx->tp_world);
+        p.one_shot = (ctx->tp_world == 2 && 4ull * ctx->tp_world * count <= P2P_REGION_BYTES && !getenv("HOLO_TP_TWO_SHOT")) ? 1u : 0u;
         p.rank = ctx->tp_rank;
         p.world = ctx->tp_world;
         p.dtype = dtype;
         // enough threads for one unit of the widest phase each, at most P2P_MAX_CTAS CTAs (all co-resident)
-        const uint64_t widest = (uint64_t)p.units_per_slice * (ctx->tp_world - 1);
+        const uint64_t widest = p.one_shot ? (uint64_t)p.units_per_slice * ctx->tp_world : (uint64_t)p.units_per_slice * (ctx->tp_world - 1);
         uint32_t ctas = (uint32_t)((widest + P2P_THREADS - 1) / P2P_THREADS);
         if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
         if (ctas < 1) ctas = 1;
@@ -360,10 +403,11 @@ extern "C" int32_t holo_b200_tp_emulate_all_reduce(holo_b200_ctx* ctx, int32_t w
     HOLO_CUDA(cudaSetDevice(ctx->device));
     uint8_t* boxes = nullptr;
     uint32_t* states = nullptr;
+    // cleared on the launch stream: a memset on the default stream is not ordered with it
     HOLO_CUDA(cudaMalloc(&boxes, (size_t)world * P2P_MAILBOX_BYTES));
-    HOLO_CUDA(cudaMemset(boxes, 0, (size_t)world * P2P_MAILBOX_BYTES));
+    HOLO_CUDA(cudaMemsetAsync(boxes, 0, (size_t)world * P2P_MAILBOX_BYTES, ctx->stream));
     HOLO_CUDA(cudaMalloc(&states, (size_t)world * 256));
-    HOLO_CUDA(cudaMemset(states, 0, (size_t)world * 256));
+    HOLO_CUDA(cudaMemsetAsync(states, 0, (size_t)world * 256, ctx->stream));
     P2PEmulation e;
     for (int r = 0; r < world; ++r) {
         P2PParams& p = e.rank[r];
@@ -374,11 +418,12 @@ extern "C" int32_t holo_b200_tp_emulate_all_reduce(holo_b200_ctx* ctx, int32_t w
         p.state = states + r * 64;
         p.status = ctx->dev_status;
         p.units_per_slice = (uint32_t)(count / 4 / world);
+        p.one_shot = (world == 2 && 4ull * world * count <= P2P_REGION_BYTES && !getenv("HOLO_TP_TWO_SHOT")) ? 1u : 0u;
         p.rank = r;
         p.world = world;
         p.dtype = dtype;
     }
-    const uint64_t widest = (uint64_t)e.rank[0].units_per_slice * (world - 1);
+    const uint64_t widest = e.rank[0].one_shot ? (uint64_t)e.rank[0].units_per_slice * world : (uint64_t)e.rank[0].units_per_slice * (world - 1);
     uint32_t ctas = (uint32_t)((widest + P2P_THREADS - 1) / P2P_THREADS);
     if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
     if (ctas < 1) ctas = 1;

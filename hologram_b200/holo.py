@@ -87,6 +87,10 @@ def encode_call(call):
                                           c.k_new_scales, c.v_new, c.v_new_scales, c.valid_len, c.output))
         return out + bufs + struct.pack("<IIIIIIIIB", c.batch, c.heads, c.kv_heads, c.q_rows, c.past_len, c.new_len,
                                         c.head_dim, c.scale_bits, c.dtype)
+    if k == kc.K_ROPE_QUANTIZE_ROWS_I8:
+        c = u.rope_quantize
+        return out + b"".join(_buf(b) for b in (c.x, c.cos, c.sin, c.rope_output, c.codes, c.scales)) + struct.pack(
+            "<QIB", c.rows, c.row_len, c.dtype)
     if k == kc.K_ALL_REDUCE:
         c = u.all_reduce
         return out + _buf(c.buffer) + struct.pack("<QB", c.element_count, c.dtype)

@@ -25,6 +25,7 @@ K_DECODE_ATTENTION = 119
 K_DEQUANTIZE, K_MATMUL_ACTIVATION, K_MATMUL_ADD = 105, 106, 107
 K_GATHER, K_CAST, K_KV_CACHE_WRITE, K_DECODE_ATTENTION_VALID = 114, 115, 120, 121
 K_QUANTIZE_ROWS_I8, K_DECODE_ATTENTION_VALID_Q8, K_ALL_REDUCE = 0x8001, 0x8002, 0x8003
+K_ROPE_QUANTIZE_ROWS_I8 = 0x8004
 LUT_KIND = {LUT_SIGMOID: K_SIGMOID, LUT_TANH: K_TANH, LUT_GELU: K_GELU, LUT_SILU: K_SILU, LUT_EXP: K_EXP, LUT_ERF: K_ERF}
 
 NO_SLOT = 0xFFFFFFFF
@@ -149,6 +150,12 @@ class DecodeAttentionValidQ8Call(C.Structure):
                 ("new_len", C.c_uint32), ("head_dim", C.c_uint32), ("scale_bits", C.c_uint32), ("dtype", C.c_uint8)]
 
 
+class RopeQuantizeCall(C.Structure):
+    """Extension: RotaryEmbedding then QuantizeRowsI8 of its result, one row = one head."""
+    _fields_ = [("x", BufferRef), ("cos", BufferRef), ("sin", BufferRef), ("rope_output", BufferRef), ("codes", BufferRef),
+                ("scales", BufferRef), ("rows", C.c_uint64), ("row_len", C.c_uint32), ("dtype", C.c_uint8)]
+
+
 class AllReduceCall(C.Structure):
     _fields_ = [("buffer", BufferRef), ("element_count", C.c_uint64), ("dtype", C.c_uint8)]
 
@@ -160,7 +167,8 @@ class _Payload(C.Union):
                 ("transpose", TransposeCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
                 ("decode_attention", DecodeAttentionCall),
                 ("decode_attention_valid", DecodeAttentionValidCall), ("quantize_rows_i8", QuantizeRowsI8Call),
-                ("decode_attention_valid_q8", DecodeAttentionValidQ8Call), ("all_reduce", AllReduceCall)]
+                ("decode_attention_valid_q8", DecodeAttentionValidQ8Call), ("all_reduce", AllReduceCall),
+                ("rope_quantize", RopeQuantizeCall)]
 
 
 class KernelCall(C.Structure):
@@ -231,6 +239,8 @@ class KernelCall(C.Structure):
     def DecodeAttentionValidQ8(cls, c): return cls.of(K_DECODE_ATTENTION_VALID_Q8, c)
     @classmethod
     def AllReduce(cls, c): return cls.of(K_ALL_REDUCE, c)
+    @classmethod
+    def RopeQuantizeRowsI8(cls, c): return cls.of(K_ROPE_QUANTIZE_ROWS_I8, c)
 
 
 KernelCall._FIELD = {
@@ -238,7 +248,7 @@ KernelCall._FIELD = {
     MatMulAddCall: "matmul_add", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
     LayoutCall: "layout", TransposeCall: "transpose", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
     DecodeAttentionCall: "decode_attention", DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
-    DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce",
+    DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce", RopeQuantizeCall: "rope_quantize",
 }
 
 

@@ -96,6 +96,9 @@ extern "C" {
 #define HOLO_K_QUANTIZE_ROWS_I8 0x8001
 #define HOLO_K_DECODE_ATTENTION_VALID_Q8 0x8002
 #define HOLO_K_ALL_REDUCE 0x8003
+/* RotaryEmbedding followed by QuantizeRowsI8 of its result, one row = one head (fused at load by the
+ * session when a RoPE output feeds a row quantizer of the same row length; bit-identical to the pair). */
+#define HOLO_K_ROPE_QUANTIZE_ROWS_I8 0x8004
 
 /* BufferRef (crates/hologram-compute/src/workspace.rs:16-24). length == 0 means "the slot's
  * full extent from offset". slot == UINT32_MAX marks an absent optional operand
@@ -245,6 +248,15 @@ typedef struct HoloDecodeAttentionValidQ8Call {
     uint8_t dtype;
 } HoloDecodeAttentionValidQ8Call;
 
+/* Extension: rope_output = RoPE(x, cos, sin) (RoPECall semantics, head_dim = the row length), then
+ * codes / scales = QuantizeRowsI8(rope_output). */
+typedef struct HoloRopeQuantizeCall {
+    HoloBufferRef x, cos, sin, rope_output, codes, scales;
+    uint64_t rows;
+    uint32_t row_len;
+    uint8_t dtype;
+} HoloRopeQuantizeCall;
+
 /* Extension. In-place sum over the context's tensor-parallel group (NCCL); a no-op when the
  * context has no group. */
 typedef struct HoloAllReduceCall {
@@ -275,6 +287,7 @@ typedef struct HoloKernelCall {
         HoloQuantizeRowsI8Call quantize_rows_i8;
         HoloDecodeAttentionValidQ8Call decode_attention_valid_q8;
         HoloAllReduceCall all_reduce;
+        HoloRopeQuantizeCall rope_quantize;
     } u;
 } HoloKernelCall;
 

@@ -259,3 +259,24 @@ def test_slice_and_concat_are_byte_placement(backend):
     with pytest.raises(hb.BackendError) as e:
         backend.dispatch(kc.KernelCall.Concat(kc.BinaryCall(kc.rb(0, 0, 2000), kc.rb(1, 0, 600), kc.rb(3), 1300, 16, BF)), ws)
     assert e.value.variant == "SlotOutOfRange" and e.value.slot == 3
+
+
+def test_rope_quantize_rows_is_the_pair_bit_for_bit(backend):
+    # extension 0x8004: RotaryEmbedding then QuantizeRowsI8 of its rows (the K path of a decoder layer)
+    rows, d = 64 * 8, 128
+    n = rows * d
+    x, c, s = synth_bf16(n, 1.0, 50), synth_bf16(n, 0.7, 51), synth_bf16(n, 0.7, 52)
+    x[: d] = 0                                     # an all-zero head: zero codes, scale 0
+    ws = hb.DeviceWorkspace(backend, 6)
+    for i, a in enumerate((x, c, s)):
+        ws.put(i, a)
+    ws.alloc(3, n * 2)
+    ws.alloc(4, n)
+    ws.alloc(5, rows * 4)
+    call = kc.RopeQuantizeCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), kc.rb(5), rows, d, BF)
+    backend.dispatch(kc.KernelCall.RopeQuantizeRowsI8(call), ws)
+    rot = orc.rope(x, c, s, d, BF)
+    codes, scales = orc.quantize_rows_i8(rot, BF, rows, d)
+    assert np.array_equal(ws.read(3, n * 2, np.uint16), rot)
+    assert np.array_equal(ws.read(4, n, np.int8), codes)
+    assert np.array_equal(ws.read(5, rows * 4, np.float32).view(np.uint32), scales.view(np.uint32))
