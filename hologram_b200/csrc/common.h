@@ -210,6 +210,10 @@ struct HoloMatmulSeg {
     // "up" projection; out[:, j] = narrow(widen(act(narrow(gate_j))) * widen(narrow(up_j))) (the
     // MatMulActivation -> Mul pair of a gated FFN in one epilogue). Single segment only.
     uint8_t gated = 0;
+    // 1: the product is a partial of a tensor-parallel sum: out = narrow(sum over ranks of
+    // narrow(A . B)) (+ residual), the exchange done by the matmul's own epilogue over peer memory
+    // when the group has the peer-memory transport, by a following all-reduce launch otherwise
+    uint8_t all_reduce = 0;
 };
 int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* b, uint32_t m, uint32_t k, uint32_t n,
                                  uint8_t dtype, const HoloMatmulSeg* segs, uint32_t nseg);

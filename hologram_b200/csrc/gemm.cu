@@ -22,6 +22,7 @@
 
 #include "common.h"
 #include "numerics.cuh"
+#include "p2p.cuh"
 
 namespace {
 
@@ -48,6 +49,11 @@ struct GemmParams {
     uint32_t m, n, k, kblocks, splits, box_m;
     int dtype;                // HOLO_DTYPE_BF16 or HOLO_DTYPE_F16 (operands and output)
     uint32_t gated;           // see HoloMatmulSeg::gated (BN = 128: columns 0..63 of a tile are gate, 64..127 up)
+    // tensor-parallel sum inside the epilogue (ar_world > 1): every rank's mailbox, the local epoch /
+    // ticket words, this rank
+    uint8_t* ar_mailbox[8];
+    uint32_t* ar_state;
+    uint32_t ar_world, ar_rank;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -135,6 +141,37 @@ __device__ __forceinline__ uint16_t gated_elem(float gate, float up, const uint1
     return holo::narrow16(__fmul_rn(holo::widen16(g, dtype), holo::widen16(u, dtype)), dtype);
 }
 
+// Tensor-parallel exchange of one unit (four narrowed results of this rank): `push` sends it to every
+// peer's mailbox; `sum` polls the peers' units and returns the f32 sums in rank order (this rank's
+// own value taking its place in the order). Same mailbox regions and epochs as the one-shot
+// all-reduce kernel.
+template <bool F16>
+__device__ __forceinline__ uint2 ar_pack(const float (&a)[4]) {
+    constexpr int dtype = F16 ? HOLO_DTYPE_F16 : HOLO_DTYPE_BF16;
+    return make_uint2((uint32_t)holo::narrow16(a[0], dtype) | ((uint32_t)holo::narrow16(a[1], dtype) << 16),
+                      (uint32_t)holo::narrow16(a[2], dtype) | ((uint32_t)holo::narrow16(a[3], dtype) << 16));
+}
+__device__ __forceinline__ void ar_push(const GemmParams& p, uint32_t epoch, uint64_t units, uint64_t unit, uint2 mine) {
+    const uint64_t off = p2p_oneshot_offset(epoch);
+    for (uint32_t k = 1; k < p.ar_world; ++k)
+        ll_store(p.ar_mailbox[(p.ar_rank + k) % p.ar_world] + off, (uint64_t)p.ar_rank * units + unit, mine, epoch);
+}
+template <bool F16>
+__device__ __forceinline__ bool ar_sum(const GemmParams& p, uint32_t epoch, uint64_t units, uint64_t unit, uint2 mine, float (&a)[4]) {
+    constexpr int dtype = F16 ? HOLO_DTYPE_F16 : HOLO_DTYPE_BF16;
+    const uint8_t* box = p.ar_mailbox[p.ar_rank] + p2p_oneshot_offset(epoch);
+    a[0] = a[1] = a[2] = a[3] = 0.0f;
+    for (uint32_t r = 0; r < p.ar_world; ++r) {
+        uint2 v = mine;
+        if (r != p.ar_rank && !ll_load(box, (uint64_t)r * units + unit, epoch, &v)) return false;
+        a[0] = __fadd_rn(a[0], holo::widen16((uint16_t)(v.x & 0xffffu), dtype));
+        a[1] = __fadd_rn(a[1], holo::widen16((uint16_t)(v.x >> 16), dtype));
+        a[2] = __fadd_rn(a[2], holo::widen16((uint16_t)(v.y & 0xffffu), dtype));
+        a[3] = __fadd_rn(a[3], holo::widen16((uint16_t)(v.y >> 16), dtype));
+    }
+    return true;
+}
+
 // A_ROWS = rows of the A tile that are backed by the ring (the TMA box never has more rows than
 // min(m, 128)). With fewer than 128 the MMA still reads 128 rows: the rest is whatever follows in
 // shared memory, and those accumulator rows are never stored. A smaller A slot buys more stages,
@@ -188,6 +225,8 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *s_tmem;
     holo_pdl_wait();  // barriers and TMEM were set up while the previous kernel drained
+    const uint32_t ar_epoch = p.ar_world > 1 ? *reinterpret_cast<volatile uint32_t*>(p.ar_state) + 1 : 0;
+    const uint64_t ar_units = ((uint64_t)p.m * p.n) >> 2;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -260,6 +299,41 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 #pragma unroll
                         for (int x = 0; x < 4; ++x)
                             reinterpret_cast<uint4*>(dst)[x] = make_uint4(packed[4 * x], packed[4 * x + 1], packed[4 * x + 2], packed[4 * x + 3]);
+                    }
+                }
+            }
+        } else if (ok && p.splits == 1 && p.ar_world > 1) {
+            // tensor-parallel sum in the epilogue: first push every unit of this thread's row, then
+            // collect the peers' units (the NVLink latency of all pushes overlaps)
+            const GemmSeg sg = p.seg[0];
+#pragma unroll 1
+            for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((quarter * 32u) << 16) + (uint32_t)(c * 32), v);
+                    const uint32_t col0 = n0 + c * 32;
+                    if (row >= p.m || col0 >= p.n) continue;
+#pragma unroll 1
+                    for (int x = 0; x < 8; ++x) {
+                        if (col0 + 4 * x >= p.n) break;
+                        const float mine4[4] = {__uint_as_float(v[4 * x]), __uint_as_float(v[4 * x + 1]), __uint_as_float(v[4 * x + 2]),
+                                                __uint_as_float(v[4 * x + 3])};
+                        const uint2 mine = ar_pack<F16>(mine4);
+                        const uint64_t idx = (uint64_t)row * p.n + col0 + 4 * x, unit = idx >> 2;
+                        if (pass == 0) {
+                            ar_push(p, ar_epoch, ar_units, unit, mine);
+                            continue;
+                        }
+                        float a4[4];
+                        if (!ar_sum<F16>(p, ar_epoch, ar_units, unit, mine, a4)) {
+                            atomicOr(p.status, 8u);
+                            continue;
+                        }
+                        uint16_t h[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) h[e] = epilogue_elem<F16>(a4[e], nullptr, sg.residual, idx + e);
+                        *reinterpret_cast<uint2*>(sg.out + idx) = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
                     }
                 }
             }
@@ -361,6 +435,7 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     }
                 }
             } else
+            for (int pass = p.ar_world > 1 ? 0 : 1; pass < 2; ++pass)
             for (uint32_t rl = rank + S_ * ew; rl < rows_valid; rl += S_ * 4) {
                 for (uint32_t u = lane; u < BN / 4; u += 32) {
                     const uint32_t off = rl * (BN * 4) + ((u ^ (rl & 7u)) * 16);
@@ -384,7 +459,20 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         const GemmSeg sg = p.seg[si];
                         const uint64_t idx = (uint64_t)grow * (sg.col_end - sg.col_begin) + (col - sg.col_begin);
                         uint16_t* dst = sg.out + idx;
-                        const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+                        float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+                        if (p.ar_world > 1) {
+                            // this rank's narrowed partial goes to the peers in the first pass; in the
+                            // second the sums over the ranks replace it (single segment: idx = row * n + col)
+                            const uint2 mine = ar_pack<F16>(a4);
+                            if (pass == 0) {
+                                ar_push(p, ar_epoch, ar_units, idx >> 2, mine);
+                                continue;
+                            }
+                            if (!ar_sum<F16>(p, ar_epoch, ar_units, idx >> 2, mine, a4)) {
+                                atomicOr(p.status, 8u);
+                                continue;
+                            }
+                        }
                         if (col + 4 <= sg.col_end && ((uintptr_t)dst & 7u) == 0) {
                             uint16_t h[4];
 #pragma unroll
@@ -410,6 +498,14 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+    if (p.ar_world > 1 && threadIdx.x == 0) {
+        // the launch's last CTA advances the group's epoch (every CTA has read it by then)
+        const uint32_t done = atomicAdd(p.ar_state + 1, 1u);
+        if (done == gridDim.x * gridDim.y * gridDim.z - 1) {
+            p.ar_state[1] = 0;
+            p.ar_state[0] = ar_epoch;
+        }
     }
 }
 
@@ -593,7 +689,38 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     if (splits > 8) splits = 8;  // one cluster (portable size) per output tile
     if (mtiles > 65535 || splits > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul grid too large");
 
+    // Tensor-parallel sum in the epilogue: needs the peer-memory transport, a single plain 16-bit
+    // segment, a message that fits the one-shot mailbox regions, and every CTA of the launch resident
+    // at once (a CTA waits for the same tile's CTAs on the other GPUs; with more CTAs than fit, a
+    // waiting first wave here could face a second wave there). Otherwise the matmul stores its
+    // narrowed partial and the all-reduce kernel follows.
+    const bool want_ar = segs[0].all_reduce != 0 && ctx->tp_world > 1;
+    bool fused_ar = want_ar && ctx->tp_p2p && nseg == 1 && !gated && !segs[0].fused_act && (n % 4) == 0 &&
+                    4ull * (uint64_t)ctx->tp_world * m * n <= P2P_ONESHOT_BYTES && !getenv("HOLO_TP_NO_FUSED_GEMM");
+    if (fused_ar) {
+        // one CTA per SM is always resident, clusters included: trim the K split to stay within that
+        const uint32_t tiles = ((n + bn - 1) / bn) * mtiles;
+        if (tiles > (uint32_t)ctx->sm_count) fused_ar = false;
+        else if (tiles * splits > (uint32_t)ctx->sm_count) splits = (uint32_t)ctx->sm_count / tiles;
+    }
+    if (want_ar && !fused_ar) {
+        HoloMatmulSeg plain = segs[0];
+        plain.all_reduce = 0;
+        plain.residual = nullptr;
+        HOLO_TRY(holo_launch_matmul_multi(ctx, a, b, m, k, n, dtype, &plain, 1));
+        return holo_all_reduce_add(ctx, segs[0].out, segs[0].residual, segs[0].out, (uint64_t)m * n, dtype);
+    }
     GemmParams p;
+    p.ar_world = 0;
+    p.ar_rank = 0;
+    p.ar_state = nullptr;
+    for (int r = 0; r < 8; ++r) p.ar_mailbox[r] = nullptr;
+    if (fused_ar) {
+        p.ar_world = (uint32_t)ctx->tp_world;
+        p.ar_rank = (uint32_t)ctx->tp_rank;
+        p.ar_state = ctx->tp_epochs;
+        for (int r = 0; r < 8; ++r) p.ar_mailbox[r] = ctx->tp_mailbox[r];
+    }
     for (uint32_t i = 0; i < MAX_SEGS; ++i) p.seg[i] = gs[i];
     p.nseg = nseg;
     p.status = ctx->dev_status;

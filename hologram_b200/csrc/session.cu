@@ -55,6 +55,9 @@ struct SessionNode {
     // `residual` / `sum_out` come from the Add
     bool reduce_add = false;
     HoloBufferRef residual = {HOLO_NO_SLOT, 0, 0}, sum_out = {HOLO_NO_SLOT, 0, 0};
+    // MatMul whose product is all-reduced and added to a residual: `call` is the MatMul; the sum over
+    // the ranks happens in the matmul's epilogue (or right after it), `residual` / `sum_out` as above
+    bool matmul_reduce_add = false;
 };
 
 struct holo_b200_session {
@@ -459,6 +462,46 @@ int32_t run_reduce_add(holo_b200_session* s, const SessionNode& n) {
     return holo_all_reduce_add(s->ctx, buf, res, dst, ar.element_count, ar.dtype);
 }
 
+// Tensor parallel: a plain MatMul whose product is only read by the AllReduce + Add node that
+// follows becomes one node: the row-parallel projection, the sum over the ranks and the residual
+// add in one launch (the exchange runs in the matmul's epilogue over peer memory).
+void fuse_matmul_reduce_add(holo_b200_session* s) {
+    if (getenv("HOLO_SESSION_NO_MATMUL_AR")) return;
+    std::vector<SessionNode> out;
+    for (size_t i = 0; i < s->nodes.size(); ++i) {
+        SessionNode n = s->nodes[i];
+        if (n.merged < 0 && n.batch < 0 && !n.reduce_add && n.call.kind == HOLO_K_MATMUL && i + 1 < s->nodes.size()) {
+            const SessionNode& nx = s->nodes[i + 1];
+            const HoloMatMulCall& mm = n.call.u.matmul;
+            if (nx.reduce_add && mm.dtype == HOLO_DTYPE_BF16 && same_range(nx.call.u.all_reduce.buffer, mm.output) &&
+                nx.call.u.all_reduce.element_count == (uint64_t)mm.m * mm.n && nx.call.u.all_reduce.dtype == mm.dtype) {
+                n.matmul_reduce_add = true;
+                n.residual = nx.residual;
+                n.sum_out = nx.sum_out;
+                out.push_back(n);
+                ++s->reduce_adds;   // one more call absorbed
+                ++i;
+                continue;
+            }
+        }
+        out.push_back(n);
+    }
+    s->nodes.swap(out);
+}
+
+int32_t run_matmul_reduce_add(holo_b200_session* s, const SessionNode& n) {
+    const HoloMatMulCall& mm = n.call.u.matmul;
+    const uint64_t ob = (uint64_t)mm.m * mm.n * 2;
+    uint8_t *a, *b, *res, *dst;
+    HOLO_TRY(holo_resolve(s->ws, mm.a, (uint64_t)mm.m * mm.k * 2, &a, nullptr));
+    HOLO_TRY(holo_resolve(s->ws, mm.b, (uint64_t)mm.k * mm.n * 2, &b, nullptr));
+    HOLO_TRY(holo_resolve(s->ws, n.residual, ob, &res, nullptr));
+    HOLO_TRY(holo_resolve(s->ws, n.sum_out, ob, &dst, nullptr));
+    HoloMatmulSeg sg = {dst, res, mm.n, 0};
+    sg.all_reduce = 1;
+    return holo_launch_matmul_multi(s->ctx, a, b, mm.m, mm.k, mm.n, mm.dtype, &sg, 1);
+}
+
 bool batchable_kind(uint16_t k) {
     return k == HOLO_K_KV_CACHE_WRITE || k == HOLO_K_ROTARY || k == HOLO_K_QUANTIZE_ROWS_I8 || k == HOLO_K_ADD || k == HOLO_K_MUL ||
            k == HOLO_K_ROPE_QUANTIZE_ROWS_I8;
@@ -798,7 +841,8 @@ namespace {
 
 int32_t run_calls(holo_b200_session* s) {
     for (const SessionNode& n : s->nodes) {
-        if (n.reduce_add) HOLO_TRY(run_reduce_add(s, n));
+        if (n.matmul_reduce_add) HOLO_TRY(run_matmul_reduce_add(s, n));
+        else if (n.reduce_add) HOLO_TRY(run_reduce_add(s, n));
         else if (n.merged >= 0) HOLO_TRY(run_merged(s, s->merged[n.merged]));
         else if (n.batch >= 0) HOLO_TRY(holo_launch_micro_batch(s->ctx, s->batches[n.batch].dev_ops, s->batches[n.batch].nops, s->batches[n.batch].total_ctas));
         else HOLO_TRY(holo_dispatch_internal(s->ctx, &n.call, s->ws));
@@ -854,6 +898,7 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
             plan_sibling_merges(s, const_slots, written_slots);
             fuse_gated_pairs(s, out_slots);
             fuse_all_reduce_add(s, out_slots);
+            fuse_matmul_reduce_add(s);
         }
     }
 

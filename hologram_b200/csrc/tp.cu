@@ -15,6 +15,7 @@
 
 #include "common.h"
 #include "numerics.cuh"
+#include "p2p.cuh"
 
 namespace {
 
@@ -69,12 +70,8 @@ Nccl* nccl() {
 // NVLink hop instead of two). Phase 1 never waits, phase 2 waits only for phase 1 of peers, phase 3 only for their phase 2:
 // no cycle. Every poll is bounded. A mailbox region is rewritten one epoch later, which a rank
 // reaches only after it has received (hence the peer has finished reading) everything of this one.
-constexpr uint32_t P2P_MAX_ELEMS = 512 * 1024;              // 1 MiB of 16-bit elements
 constexpr uint32_t P2P_THREADS = 256;
 constexpr uint32_t P2P_MAX_CTAS = 64;
-constexpr uint64_t P2P_REGION_BYTES = (uint64_t)P2P_MAX_ELEMS * 4;   // n/4 units x 16 bytes
-constexpr uint64_t P2P_MAILBOX_BYTES = 4 * P2P_REGION_BYTES;         // incoming partials, incoming results, two one-shot buffers
-constexpr uint32_t P2P_WAIT_LIMIT = 1u << 22;               // polls before a thread gives up
 
 struct P2PParams {
     const uint16_t* partial;   // local, [n] 16-bit floats
@@ -87,24 +84,6 @@ struct P2PParams {
     uint32_t one_shot;         // two ranks: push the whole partial, reduce everything locally (one NVLink hop instead of two)
     int rank, world, dtype;
 };
-
-__device__ __forceinline__ void ll_store(uint8_t* base, uint64_t unit, uint2 d, uint32_t epoch) {
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(base + unit * 16), "r"(d.x), "r"(epoch), "r"(d.y), "r"(epoch)
-                 : "memory");
-}
-// Poll one unit until both halves carry `epoch`; false after P2P_WAIT_LIMIT polls.
-__device__ __forceinline__ bool ll_load(const uint8_t* base, uint64_t unit, uint32_t epoch, uint2* d) {
-    for (uint32_t it = 0; it < P2P_WAIT_LIMIT; ++it) {
-        uint32_t a, fa, b, fb;
-        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(fa), "=r"(b), "=r"(fb) : "l"(base + unit * 16) : "memory");
-        if (fa == epoch && fb == epoch) {
-            *d = make_uint2(a, b);
-            return true;
-        }
-        if (it > 1024) __nanosleep(100);
-    }
-    return false;
-}
 
 // One rank's part of the all-reduce, run by `nctas` CTAs of which this is number `cta`.
 __device__ __forceinline__ void all_reduce_p2p_body(const P2PParams& p, uint32_t cta, uint32_t nctas) {
@@ -122,7 +101,7 @@ __device__ __forceinline__ void all_reduce_p2p_body(const P2PParams& p, uint32_t
         // I start the next one (nothing here makes me wait for its reads), but not the one before
         // that, because I cannot finish an epoch before the peer has started it.
         const uint32_t N = W * U;
-        const uint64_t region = (2 + (epoch & 1u)) * P2P_REGION_BYTES;
+        const uint64_t region = p2p_oneshot_offset(epoch);
         for (uint32_t unit = t; unit < N; unit += T) {
             const uint2 d = part2[unit];
             for (uint32_t k = 1; k < W; ++k) ll_store(p.mailbox[(me + k) % W] + region, (uint64_t)me * N + unit, d, epoch);
@@ -359,7 +338,7 @@ int32_t holo_all_reduce_add(holo_b200_ctx* ctx, const void* partial, const void*
         p.state = ctx->tp_epochs;
         p.status = ctx->dev_status;
         p.units_per_slice = (uint32_t)(count / 4 / ctx->tp_world);
-        p.one_shot = (ctx->tp_world == 2 && 4ull * ctx->tp_world * count <= P2P_REGION_BYTES && !getenv("HOLO_TP_TWO_SHOT")) ? 1u : 0u;
+        p.one_shot = (ctx->tp_world == 2 && 4ull * ctx->tp_world * count <= P2P_ONESHOT_BYTES && !getenv("HOLO_TP_TWO_SHOT")) ? 1u : 0u;
         p.rank = ctx->tp_rank;
         p.world = ctx->tp_world;
         p.dtype = dtype;
@@ -418,7 +397,7 @@ extern "C" int32_t holo_b200_tp_emulate_all_reduce(holo_b200_ctx* ctx, int32_t w
         p.state = states + r * 64;
         p.status = ctx->dev_status;
         p.units_per_slice = (uint32_t)(count / 4 / world);
-        p.one_shot = (world == 2 && 4ull * world * count <= P2P_REGION_BYTES && !getenv("HOLO_TP_TWO_SHOT")) ? 1u : 0u;
+        p.one_shot = (world == 2 && 4ull * world * count <= P2P_ONESHOT_BYTES && !getenv("HOLO_TP_TWO_SHOT")) ? 1u : 0u;
         p.rank = r;
         p.world = world;
         p.dtype = dtype;
