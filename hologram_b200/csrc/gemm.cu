@@ -641,7 +641,16 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     const bool tiny = (uint64_t)m * n * k < (1ull << 18);
     if ((nseg > 1 || gated) && (!tma_ok || tiny))
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: merged matmul needs the tensor-core path");
-    if (!tma_ok || tiny || getenv("HOLO_GEMM_FORCE_CELL")) {
+    const bool cell_path = !tma_ok || tiny || getenv("HOLO_GEMM_FORCE_CELL");
+    if (cell_path && segs[0].all_reduce && ctx->tp_world > 1) {
+        // the per-cell kernel has no exchange of its own: product first, then the all-reduce launch
+        HoloMatmulSeg plain = segs[0];
+        plain.all_reduce = 0;
+        plain.residual = nullptr;
+        HOLO_TRY(holo_launch_matmul_multi(ctx, a, b, m, k, n, dtype, &plain, 1));
+        return holo_all_reduce_add(ctx, segs[0].out, segs[0].residual, segs[0].out, (uint64_t)m * n, dtype);
+    }
+    if (cell_path) {
         dim3 grid((n + 127) / 128, m);
         if (m > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul m %u on the per-cell path", m);
         HOLO_CUDA(holo_launch_kernel(ctx, matmul_cell_kernel, dim3(grid), dim3(128), 0, 1, a, b, out, table,
