@@ -333,6 +333,40 @@ int32_t do_matmul(holo_b200_ctx* ctx, const HoloMatMulCall& c, uint8_t act, cons
     return holo_launch_matmul(ctx, a, b, out, c.m, c.k, c.n, c.dtype, act, res);
 }
 
+// matmul_dequant_float, the output-major W8A8 arm (cpu/float_kernels.rs:534-596) + epilogue (:727-766)
+int32_t do_matmul_dequant(holo_b200_ctx* ctx, const HoloMatMulDequantCall& c, holo_b200_workspace* ws) {
+    if (c.m == 0 || c.k == 0 || c.n == 0) return HOLO_OK;
+    if (c.dtype != HOLO_DTYPE_F32) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: only f32 output is supported");
+    if (!c.bq_omajor || c.act_quant != 1) {
+        if (c.bq_omajor || c.act_quant == 1)
+            return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: bq_omajor and W8A8 must be paired");
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: only the output-major W8A8 form is served by this backend");
+    }
+    const bool per_channel = c.channels > 0 && c.scales.slot != HOLO_NO_SLOT;
+    if (c.quant_dtype != HOLO_DTYPE_I8 || !per_channel || c.channels != c.n || c.inner != 1 || c.k > 133144u)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: W8A8 requires symmetric per-channel i8/i4/e8cb within the k bound (i8 is served)");
+    int act = -1;
+    if (c.act != 0) {
+        if (c.act != HOLO_FUSED_GELU && c.act != HOLO_FUSED_SILU && c.act != HOLO_FUSED_SIGMOID && c.act != HOLO_FUSED_TANH && c.act != HOLO_FUSED_EXP)
+            return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: fused activation %u is not served", c.act);
+        act = c.act == HOLO_FUSED_GELU ? HOLO_LUT_GELU : c.act == HOLO_FUSED_SILU ? HOLO_LUT_SILU : c.act == HOLO_FUSED_SIGMOID ? HOLO_LUT_SIGMOID
+              : c.act == HOLO_FUSED_TANH ? HOLO_LUT_TANH : HOLO_LUT_EXP;
+    }
+    const uint64_t ab = (uint64_t)c.m * c.k * 4, wb = (uint64_t)c.n * c.k, sb = (uint64_t)c.n * 4, ob = (uint64_t)c.m * c.n * 4;
+    uint8_t *a, *bq, *sc, *zp = nullptr, *res = nullptr, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, ob, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.a, ab, &a, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.bq, wb, &bq, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.scales, sb, &sc, nullptr));
+    if (c.zero_points.slot != HOLO_NO_SLOT) HOLO_TRY(holo_resolve(ws, c.zero_points, sb, &zp, nullptr));
+    if (c.residual.slot != HOLO_NO_SLOT) HOLO_TRY(holo_resolve(ws, c.residual, ob, &res, nullptr));
+    HOLO_TRY(check_disjoint({out, ob}, c.output.slot, {{a, ab}, {bq, wb}, {sc, sb}, {zp, zp ? sb : 0}, {res, res ? ob : 0}}));
+    if ((((uintptr_t)a | (uintptr_t)sc | (uintptr_t)zp | (uintptr_t)res | (uintptr_t)out) & 3u) != 0)
+        return holo_fail_slot(c.a.slot, "matmul_dequant f32 operands must be 4-byte aligned on the device");
+    return holo_launch_matmul_w8a8_omajor(ctx, (const float*)a, (const int8_t*)bq, (const float*)sc, (const int32_t*)zp, (const float*)res,
+                                          (float*)out, c.m, c.k, c.n, act);
+}
+
 // rms_norm_float (cpu/float_kernels.rs:1683-1756), epsilon rule :1324-1336
 // `with_residual`: add_rms_norm_float (:1567-1681); an absent residual operand makes it a plain RmsNorm
 int32_t do_rms_norm(holo_b200_ctx* ctx, const HoloNormCall& c, bool with_residual, holo_b200_workspace* ws) {
@@ -684,6 +718,7 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         case HOLO_K_MATMUL: return do_matmul(ctx, call->u.matmul, 0, nullptr, ws);
         case HOLO_K_MATMUL_ACTIVATION: return do_matmul(ctx, call->u.matmul_activation.mm, call->u.matmul_activation.act, nullptr, ws);
         case HOLO_K_MATMUL_ADD: return do_matmul(ctx, call->u.matmul_add.mm, 0, &call->u.matmul_add.residual, ws);
+        case HOLO_K_MATMUL_DEQUANT: return do_matmul_dequant(ctx, call->u.matmul_dequant, ws);
         case HOLO_K_RMS_NORM: return do_rms_norm(ctx, call->u.norm, false, ws);
         case HOLO_K_ADD_RMS_NORM: return do_rms_norm(ctx, call->u.norm, true, ws);
         case HOLO_K_ROTARY: return do_rope(ctx, call->u.rope, ws);
@@ -816,6 +851,12 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             l->out(&q.rope_output, q.rows * q.row_len * holo_dtype_size(q.dtype));
             l->out(&q.codes, q.rows * q.row_len);
             l->out(&q.scales, q.rows * 4);
+            return true;
+        }
+        case HOLO_K_MATMUL_DEQUANT: {
+            auto& q = c->u.matmul_dequant;
+            l->in(&q.a); l->in(&q.bq); l->in(&q.scales); l->in(&q.zero_points); l->in(&q.residual);
+            l->out(&q.output, (uint64_t)q.m * q.n * holo_dtype_size(q.dtype));
             return true;
         }
         case HOLO_K_ALL_REDUCE:

@@ -127,6 +127,14 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
             p_attn(b, c.batch, c.heads, c.kv_heads, c.q_rows, c.past_len, c.new_len, c.head_dim, c.scale_bits, c.dtype);
             return true;
         }
+        case HOLO_K_MATMUL_DEQUANT: {
+            // kernel_call.rs:1472-1500: the extended tag 116 (activation quantization / epilogue present)
+            const HoloMatMulDequantCall& c = u.matmul_dequant;
+            sig->opcode = 116;
+            b.u32(c.m).u32(c.k).u32(c.n).u32(c.channels).u32(c.inner).u8(c.quant_dtype).u8(c.dtype).u32(c.scale_bits).i32(c.zero_point)
+                .u8(c.act_quant).u8(c.act).u8(present(c.residual) ? 1 : 0);
+            return true;
+        }
         // extensions: the tag doubles as the opcode
         case HOLO_K_QUANTIZE_ROWS_I8: {
             const HoloQuantizeRowsI8Call& c = u.quantize_rows_i8;
@@ -166,6 +174,13 @@ bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* input
             in(u.matmul_activation.mm.a); in(u.matmul_activation.mm.b); *output = u.matmul_activation.mm.output.slot; return true;
         case HOLO_K_MATMUL_ADD:
             in(u.matmul_add.mm.a); in(u.matmul_add.mm.b); in(u.matmul_add.residual); *output = u.matmul_add.mm.output.slot; return true;
+        case HOLO_K_MATMUL_DEQUANT: {
+            const auto& c = u.matmul_dequant;
+            in(c.a); in(c.bq);
+            if (c.channels > 0 && present(c.scales)) { in(c.scales); in(c.zero_points); }
+            in(c.residual);
+            *output = c.output.slot; return true;
+        }
         case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM:
             // the reference lists x, gamma, beta (kernel_call.rs:1612-1616); the residual operand of
             // AddRmsNorm is added here so that two sums over different residuals never share a label

@@ -22,6 +22,7 @@ K_SIGMOID, K_TANH, K_GELU, K_SILU, K_EXP, K_ERF = 12, 13, 14, 15, 18, 32
 K_MATMUL, K_RMS_NORM, K_RESHAPE, K_ROTARY = 46, 51, 60, 75
 K_ADD_RMS_NORM, K_TRANSPOSE, K_CONCAT, K_SLICE = 54, 61, 62, 63
 K_DECODE_ATTENTION = 119
+K_MATMUL_DEQUANT = 116
 K_DEQUANTIZE, K_MATMUL_ACTIVATION, K_MATMUL_ADD = 105, 106, 107
 K_GATHER, K_CAST, K_KV_CACHE_WRITE, K_DECODE_ATTENTION_VALID = 114, 115, 120, 121
 K_QUANTIZE_ROWS_I8, K_DECODE_ATTENTION_VALID_Q8, K_ALL_REDUCE = 0x8001, 0x8002, 0x8003
@@ -67,6 +68,14 @@ class MatMulActivationCall(C.Structure):
 
 class MatMulAddCall(C.Structure):
     _fields_ = [("mm", MatMulCall), ("residual", BufferRef)]
+
+
+class MatMulDequantCall(C.Structure):
+    """kernel_call.rs:152-213 (wire form 116). Served: output-major W8A8 int8 (bq_omajor=1, act_quant=1)."""
+    _fields_ = [("a", BufferRef), ("bq", BufferRef), ("scales", BufferRef), ("zero_points", BufferRef), ("output", BufferRef),
+                ("m", C.c_uint32), ("k", C.c_uint32), ("n", C.c_uint32), ("channels", C.c_uint32), ("inner", C.c_uint32),
+                ("quant_dtype", C.c_uint8), ("dtype", C.c_uint8), ("scale_bits", C.c_uint32), ("zero_point", C.c_int32),
+                ("bq_omajor", C.c_uint8), ("act_quant", C.c_uint8), ("act", C.c_uint8), ("residual", BufferRef)]
 
 
 class NormCall(C.Structure):
@@ -162,7 +171,7 @@ class AllReduceCall(C.Structure):
 
 class _Payload(C.Union):
     _fields_ = [("unary", UnaryCall), ("binary", BinaryCall), ("matmul", MatMulCall),
-                ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("norm", NormCall),
+                ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("matmul_dequant", MatMulDequantCall), ("norm", NormCall),
                 ("rope", RoPECall), ("gather", GatherCall), ("cast", CastCall), ("layout", LayoutCall),
                 ("transpose", TransposeCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
                 ("decode_attention", DecodeAttentionCall),
@@ -208,6 +217,8 @@ class KernelCall(C.Structure):
     @classmethod
     def MatMulAdd(cls, c): return cls.of(K_MATMUL_ADD, c)
     @classmethod
+    def MatMulDequant(cls, c): return cls.of(K_MATMUL_DEQUANT, c)
+    @classmethod
     def RmsNorm(cls, c): return cls.of(K_RMS_NORM, c)
     @classmethod
     def AddRmsNorm(cls, c): return cls.of(K_ADD_RMS_NORM, c)
@@ -245,7 +256,7 @@ class KernelCall(C.Structure):
 
 KernelCall._FIELD = {
     UnaryCall: "unary", BinaryCall: "binary", MatMulCall: "matmul", MatMulActivationCall: "matmul_activation",
-    MatMulAddCall: "matmul_add", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
+    MatMulAddCall: "matmul_add", MatMulDequantCall: "matmul_dequant", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
     LayoutCall: "layout", TransposeCall: "transpose", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
     DecodeAttentionCall: "decode_attention", DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
     DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce", RopeQuantizeCall: "rope_quantize",

@@ -84,6 +84,7 @@ extern "C" {
 #define HOLO_K_MATMUL_ACTIVATION 106
 #define HOLO_K_MATMUL_ADD 107
 #define HOLO_K_GATHER 114
+#define HOLO_K_MATMUL_DEQUANT 116 /* the extended wire form (kernel_codec.rs D_MMDQ2); served: output-major W8A8 int8 */
 #define HOLO_K_CAST 115
 #define HOLO_K_DECODE_ATTENTION 119
 #define HOLO_K_KV_CACHE_WRITE 120
@@ -153,6 +154,20 @@ typedef struct HoloNormCall {
     uint64_t epsilon_bits;
     uint8_t dtype;
 } HoloNormCall;
+
+/* MatMulDequantCall (kernel_call.rs:152-213), wire form 116: out = act(A . dequant(Bq) [+ residual]).
+ * Served: the output-major W8A8 decode product (bq_omajor = 1, act_quant = 1 = W8A8_TOKEN_SYM): A f32
+ * [m,k], Bq i8 [n,k], symmetric per-channel scales f32 [n] (channels = n, inner = 1, zero points all 0),
+ * f32 output; every A row quantized with quantize_row_i8, exact i32 dot, one f32 writeback. */
+typedef struct HoloMatMulDequantCall {
+    HoloBufferRef a, bq, scales, zero_points, output;
+    uint32_t m, k, n, channels, inner;
+    uint8_t quant_dtype, dtype;
+    uint32_t scale_bits;
+    int32_t zero_point;
+    uint8_t bq_omajor, act_quant, act;
+    HoloBufferRef residual;
+} HoloMatMulDequantCall;
 
 /* TransposeCall (kernel_call.rs:491-499): output axis i is input axis perm[i]; rank <= 8 */
 typedef struct HoloTransposeCall {
@@ -274,6 +289,7 @@ typedef struct HoloKernelCall {
         HoloMatMulCall matmul;          /* MATMUL */
         HoloMatMulActivationCall matmul_activation;
         HoloMatMulAddCall matmul_add;
+        HoloMatMulDequantCall matmul_dequant;
         HoloNormCall norm;              /* RMS_NORM, ADD_RMS_NORM (norm of x + residual) */
         HoloRoPECall rope;              /* ROTARY */
         HoloGatherCall gather;

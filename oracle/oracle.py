@@ -163,6 +163,21 @@ def decode_attention_mask(q, kp, vp, kn, vn, mask, b, h, kv, m, past, new, d, sc
     return out
 
 
+def matmul_w8a8_omajor(a, bq, scales, m, k, n, residual=None, act=None):
+    """matmul_dequant_float, output-major W8A8 arm + epilogue (cpu/float_kernels.rs:534-596, 727-766):
+    a f32 [m,k], bq i8 [n,k], scales f32 [n]; act is a LUT activation id applied by the scalar function."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    bq = np.ascontiguousarray(bq, dtype=np.int8)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    out = np.zeros(m * n, dtype=np.float32)
+    lib.holo_or_matmul_i8_pc_omajor(_p(a), _p(bq), _p(scales), _p(out), m, k, n)
+    if residual is not None:
+        out = out + np.ascontiguousarray(residual, dtype=np.float32)
+    if act is not None:
+        out = np.array([lib.holo_or_act(act, float(v)) for v in out], dtype=np.float32)
+    return out
+
+
 def add_rms_norm(x, residual, gamma, batch, feature, eps_bits, dtype):
     x = np.ascontiguousarray(x)
     out = np.empty_like(x)

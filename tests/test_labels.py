@@ -74,3 +74,16 @@ def test_op_signature_frozen_bytes():
     import hologram_b200 as hb
     with pytest.raises(hb.BackendError):
         hs.op_signature(kc.KernelCall.AllReduce(kc.AllReduceCall(rb(0), 8, kc.DTYPE_BF16)))
+
+
+def test_matmul_dequant_signature_and_wire_are_the_frozen_bytes():
+    # crates/hologram-archive/tests/wire_stability.rs:57-68, 95-101: output-major W8A8 i8, tag / wire 116
+    from hologram_b200 import holo
+    buf = lambda i: kc.rb(i, 0, 64)
+    c = kc.MatMulDequantCall(buf(0), buf(1), buf(2), buf(3), buf(4), 1, 8, 4, 4, 1, 2, 8, 0, 0, 1, 1, 0, kc.NONE)
+    call = kc.KernelCall.MatMulDequant(c)
+    assert hs.op_signature(call) == (116, bytes.fromhex("010000000800000004000000040000000100000002080000000000000000010000"))
+    want = ("01000000740000000000000000000000000040000000000000000100000000000000000000004000000000000000020000000000000000"
+            "00000040000000000000000300000000000000000000004000000000000000040000000000000000000000400000000000000001000000"
+            "0800000004000000040000000100000002080000000000000000010100ffffffff00000000000000000000000000000000")
+    assert holo.encode_calls([call]).hex() == want

@@ -1,0 +1,85 @@
+"""Output-major W8A8 decode product (KernelCall::MatMulDequant, wire 116) on the GPU: exact-integer
+arithmetic, so every output bit must equal the CPU kernel's, including the reference's own FNV-1a-64
+golden (crates/hologram-compute/src/cpu/simd.rs:8236-8262)."""
+import numpy as np
+import pytest
+
+import hologram_b200 as hb
+from hologram_b200 import kernel_call as kc
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+F32, I8 = kc.DTYPE_F32, kc.DTYPE_I8
+
+
+def run(backend, a, bq, scales, m, k, n, residual=None, act=0, zero_points=None):
+    ws = hb.DeviceWorkspace(backend, 6)
+    ws.put(0, a)
+    ws.put(1, bq)
+    ws.put(2, scales)
+    ws.put(3, np.zeros(n, dtype=np.int32) if zero_points is None else zero_points)
+    ws.alloc(4, m * n * 4)
+    res = kc.NONE
+    if residual is not None:
+        ws.put(5, residual)
+        res = kc.rb(5)
+    call = kc.MatMulDequantCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), m, k, n, n, 1, I8, F32, 0, 0, 1, 1, act, res)
+    backend.dispatch(kc.KernelCall.MatMulDequant(call), ws)
+    out = ws.read(4, m * n * 4, np.float32).copy()
+    ws.close()
+    return out
+
+
+def test_reference_golden_fixture(backend):
+    m, k, n = 3, 64, 24
+    a = (np.array([float(i * 37 % 91) for i in range(m * k)], dtype=np.float32) - np.float32(45.0)) * np.float32(0.031)
+    scales = np.float32(0.011) + np.arange(n, dtype=np.float32) * np.float32(0.0007)
+    bq = np.array([(i * 31 % 255) - 127 for i in range(k * n)], dtype=np.int8)
+    out = run(backend, a, bq, scales, m, k, n)
+    assert orc.fnv1a64_f32(out) == 0x787CCDC172029F9B
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 4096, 14336), (4, 896, 4864), (1, 100, 7), (9, 250, 33), (2, 4096, 4096)])
+def test_bit_exact_against_the_cpu_kernel(backend, m, k, n):
+    rng = np.random.default_rng(m * 7 + n)
+    a = rng.standard_normal(m * k).astype(np.float32)
+    if m > 1:
+        a[:k] = 0.0                                   # a zero activation row gives a zero output row
+    bq = rng.integers(-127, 128, size=n * k, dtype=np.int8)
+    scales = (rng.random(n).astype(np.float32) + np.float32(0.01)) * np.float32(0.02)
+    got = run(backend, a, bq, scales, m, k, n)
+    want = orc.matmul_w8a8_omajor(a, bq, scales, m, k, n)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    if m > 1:
+        assert not got[:n].any()
+
+
+def test_epilogue_and_refusals(backend):
+    m, k, n = 2, 512, 96
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal(m * k).astype(np.float32)
+    bq = rng.integers(-127, 128, size=n * k, dtype=np.int8)
+    scales = (rng.random(n).astype(np.float32) + np.float32(0.01)) * np.float32(0.01)
+    r = rng.standard_normal(m * n).astype(np.float32)
+    got = run(backend, a, bq, scales, m, k, n, residual=r, act=kc.FUSED_SILU)
+    want = orc.matmul_w8a8_omajor(a, bq, scales, m, k, n, residual=r, act=kc.LUT_SILU)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # contract violations fail loud (cpu/float_kernels.rs:546-566)
+    ws = hb.DeviceWorkspace(backend, 5)
+    for i in range(5):
+        ws.alloc(i, 1 << 16)
+    base = [kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), 1, 64, 16, 16, 1, I8, F32, 0, 0]
+    for tail in ([1, 0, 0, kc.NONE], [0, 1, 0, kc.NONE], [0, 0, 0, kc.NONE]):          # unpaired omajor / W8A8; the [k,n] W8A32 form
+        with pytest.raises(hb.BackendError) as e:
+            backend.dispatch(kc.KernelCall.MatMulDequant(kc.MatMulDequantCall(*base, *tail)), ws)
+        assert e.value.variant == "UnsupportedOp"
+    bad = list(base)
+    bad[8] = 8                                                                          # channels != n
+    with pytest.raises(hb.BackendError) as e:
+        backend.dispatch(kc.KernelCall.MatMulDequant(kc.MatMulDequantCall(*bad, 1, 1, 0, kc.NONE)), ws)
+    assert e.value.variant == "UnsupportedOp"
+    # a non-zero zero point is not the symmetric form: reported at the next synchronising call
+    zp = np.zeros(n, dtype=np.int32)
+    zp[5] = 3
+    with pytest.raises(hb.BackendError):
+        run(backend, a, bq, scales, m, k, n, zero_points=zp)
