@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the B200 backend hot path.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload lut|lut_sweep|attention|matmul|gemv|decoder]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload lut|lut_sweep|attention|matmul|gemv|w8a8|decoder]
   python bench.py --impl reference ...      # the reference CPU path (oracle restatement) on host cores
 
 One JSON line on stdout (rank 0). Timed with CUDA events on the stream the kernels are
@@ -431,6 +431,62 @@ def workload_matmul(be, torch, rank, args, skinny=False):
     }
 
 
+def workload_w8a8(be, torch, rank, args):
+    """Output-major W8A8 decode product (MatMulDequant, wire 116): f32 activations [m, k], int8 weight
+    [n, k], per-channel scales; HBM-bound on the weight. Default 1 x 4096 x 14336."""
+    import hologram_b200 as hb
+    from hologram_b200 import kernel_call as kc
+    m, k, n = 1, 4096, 14336
+    if os.environ.get("HOLO_BENCH_MKN"):
+        m, k, n = (int(v) for v in os.environ["HOLO_BENCH_MKN"].split(","))
+    sets = max(2, int(300e6 // (n * k)) + 1)
+    g = torch.Generator(device="cuda").manual_seed(0xC6 + rank)
+    A = [torch.randn(m * k, generator=g, device="cuda") for _ in range(sets)]
+    W = [torch.randint(-127, 128, (n * k,), generator=g, device="cuda", dtype=torch.int8) for _ in range(sets)]
+    S = [torch.rand(n, generator=g, device="cuda") * 0.02 + 0.001 for _ in range(sets)]
+    Z = torch.zeros(n, dtype=torch.int32, device="cuda")
+    O = [torch.empty(m * n, device="cuda") for _ in range(sets)]
+    ws = hb.DeviceWorkspace(be, 4 * sets + 1)
+    ws.bind(4 * sets, Z.data_ptr(), n * 4)
+    calls = []
+    for i in range(sets):
+        for j, t in enumerate((A[i], W[i], S[i], O[i])):
+            ws.bind(4 * i + j, t.data_ptr(), t.numel() * t.element_size())
+        calls.append(kc.KernelCall.MatMulDequant(kc.MatMulDequantCall(
+            kc.rb(4 * i), kc.rb(4 * i + 1), kc.rb(4 * i + 2), kc.rb(4 * sets), kc.rb(4 * i + 3), m, k, n, n, 1, kc.DTYPE_I8, kc.DTYPE_F32,
+            0, 0, 1, 1, 0, kc.NONE)))
+    host = [t.cpu().pin_memory() for t in (A[0], W[0], S[0], Z, O[0])]
+    hws = hb.HostWorkspace([t.numpy().view(np.uint8) for t in host])
+    hcall = kc.KernelCall.MatMulDequant(kc.MatMulDequantCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), m, k, n, n, 1, kc.DTYPE_I8,
+                                                             kc.DTYPE_F32, 0, 0, 1, 1, 0, kc.NONE))
+    nbytes = float(n * k + 4 * (m * k + n + m * n))
+
+    def cpu_baseline():
+        from oracle import oracle as orc
+        a, w, sc = host[0].numpy(), host[1].numpy(), host[2].numpy()
+        best, t_end = 1e9, time.time() + 8
+        while time.time() < t_end:
+            t0 = time.perf_counter()
+            orc.matmul_w8a8_omajor(a, w, sc, m, k, n)
+            best = min(best, time.perf_counter() - t0)
+        return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                "sample": "the full product, best of ~8 s of serial passes of the scalar restatement"}
+
+    return {
+        "name": f"matmul_w8a8_omajor_{m}x{k}x{n}",
+        "metric": "matmul_w8a8_GBps", "unit": "GB/s", "dtype": "i8 x i8 -> i32, f32 writeback", "scaling": "weak",
+        "run_device": lambda step: be.dispatch(calls[step % sets], ws),
+        "run_host": lambda step: be.dispatch(hcall, hws),
+        "units_per_step": nbytes / 1e9, "launches_per_step": 1,
+        "roofline": {"bound": "hbm", "bytes_per_launch": nbytes, "kernel": "matmul_w8a8_omajor_kernel", "traffic": None},
+        "h2d": n * k + 4 * (m * k + 2 * n), "d2h": 4 * m * n,
+        "cpu_baseline": cpu_baseline,
+        "config": {"workload": f"output-major W8A8 decode product M={m} K={k} N={n} (quantized-weight GEMV, exact integer)",
+                   "l2": f"{sets} rotated operand sets (> 126 MB L2)"},
+        "keep": (A, W, S, Z, O, host),
+    }
+
+
 def workload_lut_sweep(be, torch, rank, args):
     """config[1]: SiLU, Sigmoid, Tanh, Exp, Erf x {f16, bf16} over [8192, 14336]; one step = the ten cells."""
     import hologram_b200 as hb
@@ -512,7 +568,7 @@ def workload_lut_sweep(be, torch, rank, args):
     }
 
 
-WORKLOADS = {"lut": workload_lut, "lut_sweep": workload_lut_sweep, "attention": workload_attention, "decoder": workload_decoder,
+WORKLOADS = {"lut": workload_lut, "lut_sweep": workload_lut_sweep, "w8a8": workload_w8a8, "attention": workload_attention, "decoder": workload_decoder,
              "matmul": workload_matmul, "gemv": lambda *a: workload_matmul(*a, skinny=True)}
 
 

@@ -393,6 +393,19 @@ int32_t do_rms_norm(holo_b200_ctx* ctx, const HoloNormCall& c, bool with_residua
     return holo_launch_rms_norm(ctx, x, res, g, out, c.batch, c.feature, eps, c.dtype);
 }
 
+// softmax_float (cpu/float_kernels.rs:1758-1875)
+int32_t do_softmax(holo_b200_ctx* ctx, const HoloSoftmaxCall& c, holo_b200_workspace* ws) {
+    if (c.batch == 0 || c.feature == 0) return HOLO_OK;
+    if (!holo_is_compute_float(c.dtype)) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: softmax dtype %u", c.dtype);
+    const uint64_t total = (uint64_t)c.batch * c.feature * holo_dtype_size(c.dtype);
+    uint8_t *x, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, 0, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.input, total, &x, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, total, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, total}, c.output.slot, {{x, total}}));
+    return holo_launch_softmax(ctx, x, out, c.batch, c.feature, c.dtype);
+}
+
 // rope_float (cpu/float_kernels.rs:3123-3190)
 int32_t do_rope(holo_b200_ctx* ctx, const HoloRoPECall& c, holo_b200_workspace* ws) {
     uint64_t n = c.element_count;
@@ -721,6 +734,7 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         case HOLO_K_MATMUL_DEQUANT: return do_matmul_dequant(ctx, call->u.matmul_dequant, ws);
         case HOLO_K_RMS_NORM: return do_rms_norm(ctx, call->u.norm, false, ws);
         case HOLO_K_ADD_RMS_NORM: return do_rms_norm(ctx, call->u.norm, true, ws);
+        case HOLO_K_SOFTMAX: return do_softmax(ctx, call->u.softmax, ws);
         case HOLO_K_ROTARY: return do_rope(ctx, call->u.rope, ws);
         case HOLO_K_GATHER: return do_gather(ctx, call->u.gather, ws);
         case HOLO_K_CAST: return do_cast(ctx, call->u.cast, ws);
@@ -776,6 +790,10 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
         case HOLO_K_RMS_NORM:
             l->in(&c->u.norm.x); l->in(&c->u.norm.gamma);
             l->out(&c->u.norm.output, (uint64_t)c->u.norm.batch * c->u.norm.feature * holo_dtype_size(c->u.norm.dtype));
+            return true;
+        case HOLO_K_SOFTMAX:
+            l->in(&c->u.softmax.input);
+            l->out(&c->u.softmax.output, (uint64_t)c->u.softmax.batch * c->u.softmax.feature * holo_dtype_size(c->u.softmax.dtype));
             return true;
         case HOLO_K_ROTARY:
             l->in(&c->u.rope.x); l->in(&c->u.rope.cos); l->in(&c->u.rope.sin);

@@ -84,6 +84,11 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             c.batch = r.u32(); c.feature = r.u32(); c.channels = r.u32(); c.num_groups = r.u32(); c.epsilon_bits = r.u64(); c.dtype = r.u8();
             break;
         }
+        case HOLO_K_SOFTMAX: {
+            HoloSoftmaxCall& c = out->u.softmax;
+            c.input = r.buf(); c.output = r.buf(); c.batch = r.u32(); c.feature = r.u32(); c.dtype = r.u8();
+            break;
+        }
         case HOLO_K_ROTARY: {
             HoloRoPECall& c = out->u.rope;
             c.x = r.buf(); c.cos = r.buf(); c.sin = r.buf(); c.output = r.buf(); c.head_dim = r.u32(); c.element_count = r.u64(); c.dtype = r.u8();

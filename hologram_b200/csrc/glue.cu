@@ -184,6 +184,58 @@ __global__ void transpose_kernel(const uint8_t* __restrict__ in, uint8_t* __rest
     }
 }
 
+// softmax_float, cpu/float_kernels.rs:1758-1875: m = max, e_j = exp_det(x_j - m), out_j = e_j / max(sum, 1e-30);
+// a row whose maximum is -inf is all zeros. One CTA per row; the sum is reduced in parallel (the CPU
+// sums left to right), so results agree to rounding of the sum, not bit for bit.
+__global__ void softmax_kernel(const void* __restrict__ x, void* __restrict__ out, uint32_t feature, int dtype) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    __shared__ float s_part[32];
+    __shared__ float s_val;
+    const uint64_t off = (uint64_t)blockIdx.x * feature;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    float mx = -INFINITY;
+    for (uint32_t j = threadIdx.x; j < feature; j += blockDim.x) {
+        const float v = holo::load_float(x, off + j, dtype);
+        mx = v > mx ? v : mx;       // f32::max ignores a NaN operand
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, mx, o);
+        mx = other > mx ? other : mx;
+    }
+    if (lane == 0) s_part[warp] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m = s_part[0];
+        for (uint32_t w = 1; w < nw; ++w) m = s_part[w] > m ? s_part[w] : m;
+        s_val = m;
+    }
+    __syncthreads();
+    mx = s_val;
+    if (mx == -INFINITY) {
+        for (uint32_t j = threadIdx.x; j < feature; j += blockDim.x) holo::store_float(out, off + j, 0.0f, dtype);
+        return;
+    }
+    float sum = 0.0f;
+    for (uint32_t j = threadIdx.x; j < feature; j += blockDim.x)
+        sum = __fadd_rn(sum, holo::exp_det(__fsub_rn(holo::load_float(x, off + j, dtype), mx)));
+    for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+    __syncthreads();
+    if (lane == 0) s_part[warp] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (uint32_t w = 0; w < nw; ++w) t = __fadd_rn(t, s_part[w]);
+        s_val = fmaxf(t, 1e-30f);
+    }
+    __syncthreads();
+    const float denom = s_val;
+    for (uint32_t j = threadIdx.x; j < feature; j += blockDim.x) {
+        const float e = holo::exp_det(__fsub_rn(holo::load_float(x, off + j, dtype), mx));
+        holo::store_float(out, off + j, __fdiv_rn(e, denom), dtype);
+    }
+}
+
 // rope_float, cpu/float_kernels.rs:3123-3190 (rotate-half; cos/sin share x's layout).
 __device__ __forceinline__ void rope_body(const void* __restrict__ x, const void* __restrict__ c, const void* __restrict__ s,
                                           void* __restrict__ out, uint32_t d, uint64_t n, int dtype, uint32_t block, uint32_t nblocks) {
@@ -543,6 +595,14 @@ int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* resi
     } else {
         HOLO_CUDA(holo_launch_kernel(ctx, rms_norm_kernel, dim3(batch), dim3(256), 0, 1, x, residual, gamma, out, feature, eps, (int)dtype));
     }
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_softmax(holo_b200_ctx* ctx, const void* x, void* out, uint32_t batch, uint32_t feature, uint8_t dtype) {
+    if (batch == 0 || feature == 0) return HOLO_OK;
+    const uint32_t threads = feature >= 1024 ? 256 : feature >= 128 ? 128 : 32;
+    HOLO_CUDA(holo_launch_kernel(ctx, softmax_kernel, dim3(batch), dim3(threads), 0, 1, x, out, feature, (int)dtype));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }

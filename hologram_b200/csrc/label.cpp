@@ -94,6 +94,7 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
             for (uint32_t i = 0; i < c.rank && i < 8; ++i) b.u32(c.dims[i]).u8(c.perm[i]);
             return true;
         }
+        case HOLO_K_SOFTMAX: sig->opcode = 63; b.u32(u.softmax.batch).u32(u.softmax.feature).u8(u.softmax.dtype); return true;
         case HOLO_K_ROTARY: sig->opcode = 74; b.u64(u.rope.element_count).u32(u.rope.head_dim).u8(u.rope.dtype); return true;
         case HOLO_K_GATHER: {
             const HoloGatherCall& c = u.gather;
@@ -189,6 +190,7 @@ bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* input
             *output = u.norm.output.slot; return true;
         case HOLO_K_RESHAPE: case HOLO_K_SLICE: in(u.layout.input); *output = u.layout.output.slot; return true;
         case HOLO_K_TRANSPOSE: in(u.transpose.input); *output = u.transpose.output.slot; return true;
+        case HOLO_K_SOFTMAX: in(u.softmax.input); *output = u.softmax.output.slot; return true;
         case HOLO_K_ROTARY: in(u.rope.x); in(u.rope.cos); in(u.rope.sin); *output = u.rope.output.slot; return true;
         case HOLO_K_GATHER: in(u.gather.data); in(u.gather.indices); *output = u.gather.output.slot; return true;
         case HOLO_K_CAST: in(u.cast.input); *output = u.cast.output.slot; return true;

@@ -62,6 +62,9 @@ def encode_call(call):
     if k == kc.K_CAST:
         c = u.cast
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<QBB", c.element_count, c.src_dtype, c.dst_dtype)
+    if k == kc.K_SOFTMAX:
+        c = u.softmax
+        return out + _buf(c.input) + _buf(c.output) + struct.pack("<IIB", c.batch, c.feature, c.dtype)
     if k == kc.K_TRANSPOSE:
         c = u.transpose
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<B8I8BB", c.rank, *c.dims, *c.perm, c.dtype)

@@ -20,7 +20,7 @@ FUSED_RELU, FUSED_GELU, FUSED_SILU, FUSED_SIGMOID, FUSED_TANH, FUSED_EXP = 1, 2,
 K_ADD, K_MUL = 5, 7
 K_SIGMOID, K_TANH, K_GELU, K_SILU, K_EXP, K_ERF = 12, 13, 14, 15, 18, 32
 K_MATMUL, K_RMS_NORM, K_RESHAPE, K_ROTARY = 46, 51, 60, 75
-K_ADD_RMS_NORM, K_TRANSPOSE, K_CONCAT, K_SLICE = 54, 61, 62, 63
+K_ADD_RMS_NORM, K_TRANSPOSE, K_CONCAT, K_SLICE, K_SOFTMAX = 54, 61, 62, 63, 64
 K_DECODE_ATTENTION = 119
 K_MATMUL_DEQUANT = 116
 K_DEQUANTIZE, K_MATMUL_ACTIVATION, K_MATMUL_ADD = 105, 106, 107
@@ -104,6 +104,10 @@ class LayoutCall(C.Structure):
     _fields_ = [("input", BufferRef), ("output", BufferRef), ("element_count", C.c_uint64), ("dtype", C.c_uint8)]
 
 
+class SoftmaxCall(C.Structure):
+    _fields_ = [("input", BufferRef), ("output", BufferRef), ("batch", C.c_uint32), ("feature", C.c_uint32), ("dtype", C.c_uint8)]
+
+
 class TransposeCall(C.Structure):
     """kernel_call.rs:491-499: output axis i is input axis perm[i]."""
     _fields_ = [("input", BufferRef), ("output", BufferRef), ("rank", C.c_uint8), ("dims", C.c_uint32 * 8),
@@ -173,7 +177,7 @@ class _Payload(C.Union):
     _fields_ = [("unary", UnaryCall), ("binary", BinaryCall), ("matmul", MatMulCall),
                 ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("matmul_dequant", MatMulDequantCall), ("norm", NormCall),
                 ("rope", RoPECall), ("gather", GatherCall), ("cast", CastCall), ("layout", LayoutCall),
-                ("transpose", TransposeCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
+                ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
                 ("decode_attention", DecodeAttentionCall),
                 ("decode_attention_valid", DecodeAttentionValidCall), ("quantize_rows_i8", QuantizeRowsI8Call),
                 ("decode_attention_valid_q8", DecodeAttentionValidQ8Call), ("all_reduce", AllReduceCall),
@@ -223,6 +227,8 @@ class KernelCall(C.Structure):
     @classmethod
     def AddRmsNorm(cls, c): return cls.of(K_ADD_RMS_NORM, c)
     @classmethod
+    def Softmax(cls, c): return cls.of(K_SOFTMAX, c)
+    @classmethod
     def Transpose(cls, c): return cls.of(K_TRANSPOSE, c)
     @classmethod
     def Concat(cls, c): return cls.of(K_CONCAT, c)
@@ -257,7 +263,7 @@ class KernelCall(C.Structure):
 KernelCall._FIELD = {
     UnaryCall: "unary", BinaryCall: "binary", MatMulCall: "matmul", MatMulActivationCall: "matmul_activation",
     MatMulAddCall: "matmul_add", MatMulDequantCall: "matmul_dequant", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
-    LayoutCall: "layout", TransposeCall: "transpose", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
+    LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
     DecodeAttentionCall: "decode_attention", DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
     DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce", RopeQuantizeCall: "rope_quantize",
 }

@@ -79,6 +79,7 @@ extern "C" {
 #define HOLO_K_TRANSPOSE 61
 #define HOLO_K_CONCAT 62
 #define HOLO_K_SLICE 63
+#define HOLO_K_SOFTMAX 64
 #define HOLO_K_ROTARY 75
 #define HOLO_K_DEQUANTIZE 105
 #define HOLO_K_MATMUL_ACTIVATION 106
@@ -168,6 +169,14 @@ typedef struct HoloMatMulDequantCall {
     uint8_t bq_omajor, act_quant, act;
     HoloBufferRef residual;
 } HoloMatMulDequantCall;
+
+/* SoftmaxCall (kernel_call.rs:549-556): rows of `feature` elements; max, deterministic exp of the
+ * shifted row, sum, divide; a row of -inf is all zeros. */
+typedef struct HoloSoftmaxCall {
+    HoloBufferRef input, output;
+    uint32_t batch, feature;
+    uint8_t dtype;
+} HoloSoftmaxCall;
 
 /* TransposeCall (kernel_call.rs:491-499): output axis i is input axis perm[i]; rank <= 8 */
 typedef struct HoloTransposeCall {
@@ -296,6 +305,7 @@ typedef struct HoloKernelCall {
         HoloCastCall cast;
         HoloLayoutCall layout;          /* RESHAPE SLICE (contiguous copies; a slice's start is the input ref's offset) */
         HoloTransposeCall transpose;
+        HoloSoftmaxCall softmax;
         HoloDequantizeCall dequantize;
         HoloKvCacheWriteCall kv_cache_write;
         HoloDecodeAttentionCall decode_attention;

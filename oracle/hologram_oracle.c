@@ -466,6 +466,28 @@ int holo_or_add_rms_norm(const void* x, const void* residual, const void* gamma,
     return 0;
 }
 
+/* ---- Softmax over rows: cpu/float_kernels.rs:1758-1875 (generic loop :1830-1873): f32::max fold,
+ * exp_det of the shifted row, left-to-right sum, e / max(sum, 1e-30); an all -inf row is zeros. */
+int holo_or_softmax(const void* x, void* out, uint32_t batch, uint32_t feature, int dtype) {
+    for (uint32_t bi = 0; bi < batch; ++bi) {
+        size_t off = (size_t)bi * feature;
+        float mx = -INFINITY;
+        for (uint32_t j = 0; j < feature; ++j) {
+            float v = read_float(x, off + j, dtype);
+            mx = v > mx ? v : (mx != mx ? v : mx);
+        }
+        if (mx == -INFINITY) {
+            for (uint32_t j = 0; j < feature; ++j) write_float(out, off + j, 0.0f, dtype);
+            continue;
+        }
+        float sum = 0.0f;
+        for (uint32_t j = 0; j < feature; ++j) sum += holo_or_exp_det(read_float(x, off + j, dtype) - mx);
+        float denom = sum > 1e-30f ? sum : 1e-30f;
+        for (uint32_t j = 0; j < feature; ++j) write_float(out, off + j, holo_or_exp_det(read_float(x, off + j, dtype) - mx) / denom, dtype);
+    }
+    return 0;
+}
+
 /* ---- Transpose: output axis i is input axis perm[i]; gather per output element.
  * cpu/float_kernels.rs:2980-3027. */
 int holo_or_transpose(const uint8_t* in, uint8_t* out, uint32_t rank, const uint32_t* dims, const uint8_t* perm, uint32_t es) {

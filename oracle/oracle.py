@@ -39,6 +39,7 @@ def _load(path):
         "holo_or_binary": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_rms_norm": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
         "holo_or_add_rms_norm": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
+        "holo_or_softmax": (C.c_int, [_c, _c, C.c_uint32, C.c_uint32, C.c_int]),
         "holo_or_transpose": (C.c_int, [_c, _c, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint8), C.c_uint32]),
         "holo_or_rope": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint64, C.c_int]),
         "holo_or_gather": (C.c_int, [_c, _c, C.c_int, _c, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int]),
@@ -185,6 +186,13 @@ def add_rms_norm(x, residual, gamma, batch, feature, eps_bits, dtype):
     g = None if gamma is None else np.ascontiguousarray(gamma)
     rc = lib.holo_or_add_rms_norm(_p(x), _p(r), _p(g), _p(out), batch, feature, eps_bits, dtype)
     assert rc == 0, rc
+    return out
+
+
+def softmax(x, batch, feature, dtype):
+    x = np.ascontiguousarray(x)
+    out = np.empty_like(x)
+    assert lib.holo_or_softmax(_p(x), _p(out), batch, feature, dtype) == 0
     return out
 
 

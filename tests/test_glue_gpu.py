@@ -280,3 +280,27 @@ def test_rope_quantize_rows_is_the_pair_bit_for_bit(backend):
     assert np.array_equal(ws.read(3, n * 2, np.uint16), rot)
     assert np.array_equal(ws.read(4, n, np.int8), codes)
     assert np.array_equal(ws.read(5, rows * 4, np.float32).view(np.uint32), scales.view(np.uint32))
+
+
+def test_softmax_rows(backend):
+    # softmax_float (cpu/float_kernels.rs:1758-1875); the parallel sum differs from the CPU's
+    # left-to-right sum by rounding only
+    for batch, feature, dt in ((64, 4096, kc.DTYPE_F32), (7, 33, kc.DTYPE_F32), (32, 1000, BF)):
+        rng = np.random.default_rng(feature)
+        x = (rng.standard_normal(batch * feature) * 3).astype(np.float32)
+        x[:feature] = -np.inf                       # an impossible distribution: exactly zero everywhere
+        x[feature + 3] = -np.inf
+        xin = x if dt == kc.DTYPE_F32 else orc.f32_to_bf16_rne(x)
+        ws = hb.DeviceWorkspace(backend, 2)
+        ws.put(0, xin)
+        ws.alloc(1, xin.nbytes)
+        backend.dispatch(kc.KernelCall.Softmax(kc.SoftmaxCall(kc.rb(0), kc.rb(1), batch, feature, dt)), ws)
+        want = orc.softmax(xin, batch, feature, dt)
+        if dt == kc.DTYPE_F32:
+            got = ws.read(1, xin.nbytes, np.float32)
+            assert not got[:feature].any() and got[feature + 3] == 0.0
+            assert np.allclose(got, want, rtol=2e-6, atol=1e-12)
+            assert np.allclose(got.reshape(batch, feature)[1:].sum(axis=1), 1.0, atol=1e-5)
+        else:
+            got, want = orc.bf16_to_f32(ws.read(1, xin.nbytes, np.uint16)), orc.bf16_to_f32(want)
+            assert norm_max_err(got, want) <= 1e-2 and np.mean(got.view(np.uint32) == want.view(np.uint32)) > 0.98

@@ -70,6 +70,8 @@ def test_op_signature_frozen_bytes():
     assert hs.op_signature(kc.KernelCall.Gather(ga)) == (114, struct.pack("<QQQQBB", 1, 32000, 4096, 64, kc.DTYPE_I32, kc.DTYPE_BF16))
     ca = kc.CastCall(rb(0), rb(1), 50, kc.DTYPE_BF16, kc.DTYPE_F32)
     assert hs.op_signature(kc.KernelCall.Cast(ca)) == (115, struct.pack("<QBB", 50, kc.DTYPE_BF16, kc.DTYPE_F32))
+    sm = kc.SoftmaxCall(rb(0), rb(1), 64, 4096, kc.DTYPE_F32)
+    assert hs.op_signature(kc.KernelCall.Softmax(sm)) == (63, struct.pack("<IIB", 64, 4096, kc.DTYPE_F32))
     # an all-reduce is not a function of local labels: no signature
     import hologram_b200 as hb
     with pytest.raises(hb.BackendError):

@@ -266,6 +266,23 @@ def test_add_rms_norm_and_transpose_restatements():
         assert np.array_equal(got, np.transpose(t.reshape(2, 3, 4, 5), perm).reshape(-1))
 
 
+def test_softmax_restatement_meets_the_reference_pins():
+    # crates/hologram-compute/tests/pinned_semantics.rs:193-217: a fully masked row is +0.0 everywhere, the
+    # finite sibling row is untouched; tests/conformance.rs:305-335: within 1e-4 of the f64 softmax at
+    # these shapes and every row sums to 1 within 1e-3
+    f = 5
+    rows = np.concatenate([np.full(f, -np.inf, np.float32), np.random.default_rng(9).standard_normal(f).astype(np.float32)])
+    sm = orc.softmax(rows, 2, f, kc.DTYPE_F32)
+    assert np.array_equal(sm[:f].view(np.uint32), np.zeros(f, np.uint32)) and np.all(np.isfinite(sm[f:]))
+    for idx, (b, feat) in enumerate(((1, 4), (8, 31), (16, 128), (4, 1024))):
+        x = (np.random.default_rng(0x300 + idx).random(b * feat, dtype=np.float32) * 2 - 1) * 4
+        got = orc.softmax(x, b, feat, kc.DTYPE_F32).reshape(b, feat)
+        x64 = x.astype(np.float64).reshape(b, feat)
+        e = np.exp(x64 - x64.max(axis=1, keepdims=True))
+        assert np.max(np.abs(got - e / e.sum(axis=1, keepdims=True))) < 1e-4
+        assert np.all(np.abs(got.sum(axis=1) - 1.0) < 1e-3)
+
+
 def test_mask_form_restatement_equals_scalar_form_bitwise():
     # the reference pins that a realized-length mask reproduces DecodeAttentionValid bit for bit
     # (crates/hologram-compute/tests/decode_attention_valid.rs:226-282); all-erased row = zeros
