@@ -478,7 +478,7 @@ def workload_w8a8(be, torch, rank, args):
         "run_device": lambda step: be.dispatch(calls[step % sets], ws),
         "run_host": lambda step: be.dispatch(hcall, hws),
         "units_per_step": nbytes / 1e9, "launches_per_step": 1,
-        "roofline": {"bound": "hbm", "bytes_per_launch": nbytes, "kernel": "matmul_w8a8_omajor_kernel", "traffic": None},
+        "roofline": {"bound": "hbm", "bytes_per_launch": nbytes, "kernel": "matmul_w8a8_stream_kernel", "traffic": None},
         "h2d": n * k + 4 * (m * k + 2 * n), "d2h": 4 * m * n,
         "cpu_baseline": cpu_baseline,
         "config": {"workload": f"output-major W8A8 decode product M={m} K={k} N={n} (quantized-weight GEMV, exact integer)",

@@ -369,10 +369,10 @@ int32_t do_matmul_dequant(holo_b200_ctx* ctx, const HoloMatMulDequantCall& c, ho
 
 // rms_norm_float (cpu/float_kernels.rs:1683-1756), epsilon rule :1324-1336
 // `with_residual`: add_rms_norm_float (:1567-1681); an absent residual operand makes it a plain RmsNorm
-int32_t do_rms_norm(holo_b200_ctx* ctx, const HoloNormCall& c, bool with_residual, holo_b200_workspace* ws) {
+int32_t do_norm(holo_b200_ctx* ctx, const HoloNormCall& c, bool with_residual, bool layer, holo_b200_workspace* ws) {
     if (c.batch == 0 || c.feature == 0) return HOLO_OK;
     if (!holo_is_compute_float(c.dtype))
-        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: rms_norm dtype %u", c.dtype);
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: %s dtype %u", layer ? "layer_norm" : "rms_norm", c.dtype);
     if (c.num_groups != 0) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: grouped norms are not served by this backend");
     float eps = 1e-9f;
     if (c.epsilon_bits != 0) {
@@ -382,14 +382,16 @@ int32_t do_rms_norm(holo_b200_ctx* ctx, const HoloNormCall& c, bool with_residua
             return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: norm epsilon must be a positive finite f32 (0 selects the default)");
     }
     size_t es = holo_dtype_size(c.dtype);
-    uint64_t total = (uint64_t)c.batch * c.feature * es;
-    uint8_t *x, *g = nullptr, *res = nullptr, *out;
+    uint64_t total = (uint64_t)c.batch * c.feature * es, row = (uint64_t)c.feature * es;
+    uint8_t *x, *g = nullptr, *beta = nullptr, *res = nullptr, *out;
     HOLO_TRY(holo_resolve(ws, c.output, 0, &out, nullptr));
     HOLO_TRY(holo_resolve(ws, c.x, total, &x, nullptr));
     if (with_residual && c.residual.slot != HOLO_NO_SLOT) HOLO_TRY(holo_resolve(ws, c.residual, total, &res, nullptr));
-    if (c.gamma.slot != HOLO_NO_SLOT) HOLO_TRY(holo_resolve(ws, c.gamma, (uint64_t)c.feature * es, &g, nullptr));
+    if (c.gamma.slot != HOLO_NO_SLOT) HOLO_TRY(holo_resolve(ws, c.gamma, row, &g, nullptr));
+    if (layer && c.beta.slot != HOLO_NO_SLOT) HOLO_TRY(holo_resolve(ws, c.beta, row, &beta, nullptr));
     HOLO_TRY(holo_resolve(ws, c.output, total, &out, nullptr));
-    HOLO_TRY(check_disjoint({out, total}, c.output.slot, {{x, total}, {res, res ? total : 0}, {g, g ? (uint64_t)c.feature * es : 0}}));
+    HOLO_TRY(check_disjoint({out, total}, c.output.slot, {{x, total}, {res, res ? total : 0}, {g, g ? row : 0}, {beta, beta ? row : 0}}));
+    if (layer) return holo_launch_layer_norm(ctx, x, g, beta, out, c.batch, c.feature, eps, c.dtype);   // layer_norm_float (cpu/float_kernels.rs:1338-1445)
     return holo_launch_rms_norm(ctx, x, res, g, out, c.batch, c.feature, eps, c.dtype);
 }
 
@@ -501,6 +503,31 @@ int32_t do_transpose(holo_b200_ctx* ctx, const HoloTransposeCall& c, holo_b200_w
     HOLO_TRY(check_disjoint({out, total * es}, c.output.slot, {{in, total * es}}));
     if (((uintptr_t)in | (uintptr_t)out) % es != 0) return holo_fail_slot(c.input.slot, "transpose operands must be aligned to the element size on the device");
     return holo_launch_transpose(ctx, in, out, c.rank, c.dims, c.perm, (uint32_t)es);
+}
+
+// expand_float / broadcast_binary_float (cpu/float_kernels.rs:3405-3444, :3250-3397). `other` null = Expand.
+int32_t do_broadcast(holo_b200_ctx* ctx, const char* name, HoloBufferRef small_ref, const HoloBufferRef* other_ref, HoloBufferRef out_ref,
+                     uint8_t rank, const uint32_t* in_dims, const uint32_t* out_dims, int op, int small_is_lhs, uint8_t dtype,
+                     holo_b200_workspace* ws) {
+    if (rank == 0 || rank > 8) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: %s: rank must be 1..=8", name);
+    const size_t es = holo_dtype_size(dtype);
+    if (es == 0) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: %s of a sub-byte dtype", name);
+    if (other_ref && !holo_is_compute_float(dtype)) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: %s dtype %u", name, dtype);
+    if (other_ref && op > HOLO_BROADCAST_MUL) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: %s: bad op", name);
+    uint64_t out_total = 1, small_total = 1;
+    for (uint32_t i = 0; i < rank; ++i) {
+        if (in_dims[i] != 1 && in_dims[i] != out_dims[i])
+            return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: %s: axis %u has %u elements against %u (must be 1 or equal)", name, i, in_dims[i], out_dims[i]);
+        out_total *= out_dims[i];
+        small_total *= in_dims[i];
+    }
+    uint8_t *small, *other = nullptr, *out;
+    HOLO_TRY(holo_resolve(ws, out_ref, out_total * es, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, small_ref, small_total * es, &small, nullptr));
+    if (other_ref) HOLO_TRY(holo_resolve(ws, *other_ref, out_total * es, &other, nullptr));
+    HOLO_TRY(check_disjoint({out, out_total * es}, out_ref.slot, {{small, small_total * es}, {other, other ? out_total * es : 0}}));
+    if (((uintptr_t)small | (uintptr_t)out | (uintptr_t)other) % es != 0) return holo_fail_slot(small_ref.slot, "broadcast operands must be aligned to the element size on the device");
+    return holo_launch_broadcast(ctx, small, other, out, rank, in_dims, out_dims, (uint32_t)es, other_ref ? op : -1, small_is_lhs, dtype);
 }
 
 // dequantize (cpu/kernels.rs:185-296)
@@ -732,8 +759,9 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         case HOLO_K_MATMUL_ACTIVATION: return do_matmul(ctx, call->u.matmul_activation.mm, call->u.matmul_activation.act, nullptr, ws);
         case HOLO_K_MATMUL_ADD: return do_matmul(ctx, call->u.matmul_add.mm, 0, &call->u.matmul_add.residual, ws);
         case HOLO_K_MATMUL_DEQUANT: return do_matmul_dequant(ctx, call->u.matmul_dequant, ws);
-        case HOLO_K_RMS_NORM: return do_rms_norm(ctx, call->u.norm, false, ws);
-        case HOLO_K_ADD_RMS_NORM: return do_rms_norm(ctx, call->u.norm, true, ws);
+        case HOLO_K_LAYER_NORM: return do_norm(ctx, call->u.norm, false, true, ws);
+        case HOLO_K_RMS_NORM: return do_norm(ctx, call->u.norm, false, false, ws);
+        case HOLO_K_ADD_RMS_NORM: return do_norm(ctx, call->u.norm, true, false, ws);
         case HOLO_K_SOFTMAX: return do_softmax(ctx, call->u.softmax, ws);
         case HOLO_K_ROTARY: return do_rope(ctx, call->u.rope, ws);
         case HOLO_K_GATHER: return do_gather(ctx, call->u.gather, ws);
@@ -741,6 +769,14 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         case HOLO_K_RESHAPE: case HOLO_K_SLICE: return do_reshape(ctx, call->u.layout, ws);
         case HOLO_K_CONCAT: return do_concat(ctx, call->u.binary, ws);
         case HOLO_K_TRANSPOSE: return do_transpose(ctx, call->u.transpose, ws);
+        case HOLO_K_EXPAND: {
+            const HoloExpandCall& c = call->u.expand;
+            return do_broadcast(ctx, "expand", c.input, nullptr, c.output, c.rank, c.in_dims, c.out_dims, -1, 1, c.dtype, ws);
+        }
+        case HOLO_K_BROADCAST_BINARY: {
+            const HoloBroadcastBinaryCall& c = call->u.broadcast_binary;
+            return do_broadcast(ctx, "broadcast_binary", c.small, &c.other, c.output, c.rank, c.in_dims, c.out_dims, c.op, c.small_is_lhs, c.dtype, ws);
+        }
         case HOLO_K_DEQUANTIZE: return do_dequantize(ctx, call->u.dequantize, ws);
         case HOLO_K_KV_CACHE_WRITE: return do_kv_write(ctx, call->u.kv_cache_write, ws);
         case HOLO_K_DECODE_ATTENTION: return do_attention_mask(ctx, call->u.decode_attention, ws);
@@ -787,10 +823,28 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
         case HOLO_K_ADD_RMS_NORM:
             l->in(&c->u.norm.residual);
             /* fall through */
+        case HOLO_K_LAYER_NORM:
+            l->in(&c->u.norm.beta);
+            /* fall through */
         case HOLO_K_RMS_NORM:
             l->in(&c->u.norm.x); l->in(&c->u.norm.gamma);
             l->out(&c->u.norm.output, (uint64_t)c->u.norm.batch * c->u.norm.feature * holo_dtype_size(c->u.norm.dtype));
             return true;
+        case HOLO_K_EXPAND: case HOLO_K_BROADCAST_BINARY: {
+            const bool bin = c->kind == HOLO_K_BROADCAST_BINARY;
+            const uint32_t* od = bin ? c->u.broadcast_binary.out_dims : c->u.expand.out_dims;
+            const uint8_t rank = bin ? c->u.broadcast_binary.rank : c->u.expand.rank;
+            uint64_t total = 1;
+            for (uint32_t i = 0; i < rank && i < 8; ++i) total *= od[i];
+            if (bin) {
+                l->in(&c->u.broadcast_binary.small); l->in(&c->u.broadcast_binary.other);
+                l->out(&c->u.broadcast_binary.output, total * holo_dtype_size(c->u.broadcast_binary.dtype));
+            } else {
+                l->in(&c->u.expand.input);
+                l->out(&c->u.expand.output, total * holo_dtype_size(c->u.expand.dtype));
+            }
+            return true;
+        }
         case HOLO_K_SOFTMAX:
             l->in(&c->u.softmax.input);
             l->out(&c->u.softmax.output, (uint64_t)c->u.softmax.batch * c->u.softmax.feature * holo_dtype_size(c->u.softmax.dtype));

@@ -78,10 +78,26 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
         case HOLO_K_MATMUL: get_matmul(r, out->u.matmul); break;
         case HOLO_K_MATMUL_ACTIVATION: get_matmul(r, out->u.matmul_activation.mm); out->u.matmul_activation.act = r.u8(); break;
         case HOLO_K_MATMUL_ADD: get_matmul(r, out->u.matmul_add.mm); out->u.matmul_add.residual = r.buf(); break;
-        case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM: {
+        case HOLO_K_LAYER_NORM: case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM: {
             HoloNormCall& c = out->u.norm;
             c.x = r.buf(); c.gamma = r.buf(); c.beta = r.buf(); c.residual = r.buf(); c.output = r.buf();
             c.batch = r.u32(); c.feature = r.u32(); c.channels = r.u32(); c.num_groups = r.u32(); c.epsilon_bits = r.u64(); c.dtype = r.u8();
+            break;
+        }
+        case HOLO_K_EXPAND: {
+            HoloExpandCall& c = out->u.expand;
+            c.input = r.buf(); c.output = r.buf(); c.rank = r.u8();
+            for (int i = 0; i < 8; ++i) c.in_dims[i] = r.u32();
+            for (int i = 0; i < 8; ++i) c.out_dims[i] = r.u32();
+            c.dtype = r.u8();
+            break;
+        }
+        case HOLO_K_BROADCAST_BINARY: {
+            HoloBroadcastBinaryCall& c = out->u.broadcast_binary;
+            c.small = r.buf(); c.other = r.buf(); c.output = r.buf();
+            c.rank = r.u8(); c.op = r.u8(); c.small_is_lhs = r.u8(); c.dtype = r.u8();
+            for (uint32_t i = 0; i < c.rank && i < 8; ++i) { c.in_dims[i] = r.u32(); c.out_dims[i] = r.u32(); }
+            if (c.rank > 8) return false;
             break;
         }
         case HOLO_K_SOFTMAX: {

@@ -168,6 +168,10 @@ int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* resi
                              uint32_t batch, uint32_t feature, float eps, uint8_t dtype);
 int32_t holo_launch_rope_quantize(holo_b200_ctx* ctx, const void* x, const void* c, const void* s, void* rope_out, int8_t* codes,
                                   float* scales, uint64_t rows, uint32_t d, uint8_t dtype);
+int32_t holo_launch_layer_norm(holo_b200_ctx* ctx, const void* x, const void* gamma, const void* beta, void* out, uint32_t batch,
+                               uint32_t feature, float eps, uint8_t dtype);
+int32_t holo_launch_broadcast(holo_b200_ctx* ctx, const uint8_t* small, const uint8_t* other, uint8_t* out, uint32_t rank,
+                              const uint32_t* in_dims, const uint32_t* out_dims, uint32_t es, int op, int small_is_lhs, uint8_t dtype);
 int32_t holo_launch_softmax(holo_b200_ctx* ctx, const void* x, void* out, uint32_t batch, uint32_t feature, uint8_t dtype);
 int32_t holo_launch_transpose(holo_b200_ctx* ctx, const uint8_t* in, uint8_t* out, uint32_t rank, const uint32_t* dims,
                               const uint8_t* perm, uint32_t es);

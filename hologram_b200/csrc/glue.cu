@@ -184,6 +184,84 @@ __global__ void transpose_kernel(const uint8_t* __restrict__ in, uint8_t* __rest
     }
 }
 
+// expand_float and broadcast_binary_float (cpu/float_kernels.rs:3405-3444, :3250-3397): every output element
+// reads the small operand at the row-major index built from its coordinates with stride 0 on the
+// broadcast axes. op < 0: a plain copy of `es` bytes (Expand); otherwise one f32 operation on the
+// widened operands, narrowed once (bit-identical to the CPU loop).
+struct BroadcastParams {
+    uint32_t out_dims[8];
+    uint64_t in_strides[8];
+    uint32_t rank, es;
+    uint64_t total;
+    int op, small_is_lhs, dtype;
+};
+__global__ void broadcast_kernel(const uint8_t* __restrict__ small, const uint8_t* __restrict__ other, uint8_t* __restrict__ out,
+                                 const BroadcastParams p) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; o < p.total; o += stride) {
+        uint64_t rem = o, idx = 0;
+        for (int i = (int)p.rank - 1; i >= 0; --i) {
+            idx += (rem % p.out_dims[i]) * p.in_strides[i];
+            rem /= p.out_dims[i];
+        }
+        if (p.op < 0) {
+            if (p.es == 4) reinterpret_cast<uint32_t*>(out)[o] = reinterpret_cast<const uint32_t*>(small)[idx];
+            else if (p.es == 2) reinterpret_cast<uint16_t*>(out)[o] = reinterpret_cast<const uint16_t*>(small)[idx];
+            else for (uint32_t b = 0; b < p.es; ++b) out[o * p.es + b] = small[idx * p.es + b];
+        } else {
+            const float sv = holo::load_float(small, idx, p.dtype), ov = holo::load_float(other, o, p.dtype);
+            const float a = p.small_is_lhs ? sv : ov, b = p.small_is_lhs ? ov : sv;
+            const float r = p.op == 0 ? __fadd_rn(a, b) : p.op == 1 ? __fsub_rn(a, b) : __fmul_rn(a, b);
+            holo::store_float(out, o, r, p.dtype);
+        }
+    }
+}
+
+// layer_norm_float, cpu/float_kernels.rs:1338-1445: mean, variance of the centred row, inv = 1/sqrt(var + eps),
+// out = (x - mean) * inv * gamma + beta (absent gamma = 1, absent beta = 0). One CTA per row; the two
+// sums are reduced in parallel (the CPU sums left to right), so results agree to rounding of the sums.
+__device__ __forceinline__ float block_sum(float v, float* s_part, float* s_val) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();
+    if (lane == 0) s_part[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (uint32_t w = 0; w < nw; ++w) t = __fadd_rn(t, s_part[w]);
+        *s_val = t;
+    }
+    __syncthreads();
+    return *s_val;
+}
+
+__global__ void layer_norm_kernel(const void* __restrict__ x, const void* __restrict__ gamma, const void* __restrict__ beta,
+                                  void* __restrict__ out, uint32_t feature, float eps, int dtype) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    __shared__ float s_part[32];
+    __shared__ float s_val;
+    const uint64_t off = (uint64_t)blockIdx.x * feature;
+    float sum = 0.0f;
+    for (uint32_t j = threadIdx.x; j < feature; j += blockDim.x) sum = __fadd_rn(sum, holo::load_float(x, off + j, dtype));
+    const float mean = __fdiv_rn(block_sum(sum, s_part, &s_val), (float)feature);
+    float sq = 0.0f;
+    for (uint32_t j = threadIdx.x; j < feature; j += blockDim.x) {
+        const float d = __fsub_rn(holo::load_float(x, off + j, dtype), mean);
+        sq = __fadd_rn(sq, __fmul_rn(d, d));
+    }
+    const float var = __fdiv_rn(block_sum(sq, s_part, &s_val), (float)feature);
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+    for (uint32_t j = threadIdx.x; j < feature; j += blockDim.x) {
+        const float g = gamma ? holo::load_float(gamma, j, dtype) : 1.0f;
+        const float b = beta ? holo::load_float(beta, j, dtype) : 0.0f;
+        const float d = __fsub_rn(holo::load_float(x, off + j, dtype), mean);
+        holo::store_float(out, off + j, __fadd_rn(__fmul_rn(__fmul_rn(d, inv), g), b), dtype);
+    }
+}
+
 // softmax_float, cpu/float_kernels.rs:1758-1875: m = max, e_j = exp_det(x_j - m), out_j = e_j / max(sum, 1e-30);
 // a row whose maximum is -inf is all zeros. One CTA per row; the sum is reduced in parallel (the CPU
 // sums left to right), so results agree to rounding of the sum, not bit for bit.
@@ -595,6 +673,34 @@ int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* resi
     } else {
         HOLO_CUDA(holo_launch_kernel(ctx, rms_norm_kernel, dim3(batch), dim3(256), 0, 1, x, residual, gamma, out, feature, eps, (int)dtype));
     }
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_broadcast(holo_b200_ctx* ctx, const uint8_t* small, const uint8_t* other, uint8_t* out, uint32_t rank,
+                              const uint32_t* in_dims, const uint32_t* out_dims, uint32_t es, int op, int small_is_lhs, uint8_t dtype) {
+    BroadcastParams p{};
+    p.rank = rank, p.es = es, p.op = op, p.small_is_lhs = small_is_lhs, p.dtype = dtype;
+    uint64_t stride = 1, total = 1;
+    for (int i = (int)rank - 1; i >= 0; --i) {
+        p.out_dims[i] = out_dims[i];
+        p.in_strides[i] = in_dims[i] == 1 ? 0 : stride;
+        stride *= in_dims[i];
+        total *= out_dims[i];
+    }
+    p.total = total;
+    if (total == 0) return HOLO_OK;
+    const uint64_t want = (total + 255) / 256, cap = (uint64_t)ctx->sm_count * 16;
+    HOLO_CUDA(holo_launch_kernel(ctx, broadcast_kernel, dim3((uint32_t)(want < cap ? want : cap)), dim3(256), 0, 1, small, other, out, p));
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_layer_norm(holo_b200_ctx* ctx, const void* x, const void* gamma, const void* beta, void* out, uint32_t batch,
+                               uint32_t feature, float eps, uint8_t dtype) {
+    if (batch == 0 || feature == 0) return HOLO_OK;
+    const uint32_t threads = feature >= 1024 ? 256 : feature >= 128 ? 128 : 32;
+    HOLO_CUDA(holo_launch_kernel(ctx, layer_norm_kernel, dim3(batch), dim3(threads), 0, 1, x, gamma, beta, out, feature, eps, (int)dtype));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }

@@ -77,9 +77,9 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
         case HOLO_K_MATMUL: sig->opcode = 45; p_matmul(b, u.matmul); return true;
         case HOLO_K_MATMUL_ACTIVATION: sig->opcode = 105; p_matmul(b, u.matmul_activation.mm); b.u8(u.matmul_activation.act); return true;
         case HOLO_K_MATMUL_ADD: sig->opcode = 106; p_matmul(b, u.matmul_add.mm); return true;
-        case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM: {
+        case HOLO_K_LAYER_NORM: case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM: {
             const HoloNormCall& c = u.norm;
-            sig->opcode = call.kind == HOLO_K_RMS_NORM ? 50 : 53;
+            sig->opcode = call.kind == HOLO_K_LAYER_NORM ? 49 : call.kind == HOLO_K_RMS_NORM ? 50 : 53;
             b.u32(c.batch).u32(c.feature).u32(c.channels).u32(c.num_groups).u64(c.epsilon_bits).u8(c.dtype).u8(present(c.residual) ? 1 : 0);
             return true;
         }
@@ -92,6 +92,20 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
             sig->opcode = 60;
             b.u8(c.rank).u8(c.dtype);
             for (uint32_t i = 0; i < c.rank && i < 8; ++i) b.u32(c.dims[i]).u8(c.perm[i]);
+            return true;
+        }
+        case HOLO_K_EXPAND: {
+            const HoloExpandCall& c = u.expand;
+            sig->opcode = 71;
+            b.u8(c.rank).u8(c.dtype);
+            for (uint32_t i = 0; i < c.rank && i < 8; ++i) b.u32(c.in_dims[i]).u32(c.out_dims[i]);
+            return true;
+        }
+        case HOLO_K_BROADCAST_BINARY: {
+            const HoloBroadcastBinaryCall& c = u.broadcast_binary;
+            sig->opcode = 112;
+            b.u8(c.rank).u8(c.op).u8(c.small_is_lhs ? 1 : 0).u8(c.dtype);
+            for (uint32_t i = 0; i < c.rank && i < 8; ++i) b.u32(c.in_dims[i]).u32(c.out_dims[i]);
             return true;
         }
         case HOLO_K_SOFTMAX: sig->opcode = 63; b.u32(u.softmax.batch).u32(u.softmax.feature).u8(u.softmax.dtype); return true;
@@ -182,7 +196,7 @@ bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* input
             in(c.residual);
             *output = c.output.slot; return true;
         }
-        case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM:
+        case HOLO_K_LAYER_NORM: case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM:
             // the reference lists x, gamma, beta (kernel_call.rs:1612-1616); the residual operand of
             // AddRmsNorm is added here so that two sums over different residuals never share a label
             in(u.norm.x); in(u.norm.gamma); in(u.norm.beta);
@@ -191,6 +205,8 @@ bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* input
         case HOLO_K_RESHAPE: case HOLO_K_SLICE: in(u.layout.input); *output = u.layout.output.slot; return true;
         case HOLO_K_TRANSPOSE: in(u.transpose.input); *output = u.transpose.output.slot; return true;
         case HOLO_K_SOFTMAX: in(u.softmax.input); *output = u.softmax.output.slot; return true;
+        case HOLO_K_EXPAND: in(u.expand.input); *output = u.expand.output.slot; return true;
+        case HOLO_K_BROADCAST_BINARY: in(u.broadcast_binary.small); in(u.broadcast_binary.other); *output = u.broadcast_binary.output.slot; return true;
         case HOLO_K_ROTARY: in(u.rope.x); in(u.rope.cos); in(u.rope.sin); *output = u.rope.output.slot; return true;
         case HOLO_K_GATHER: in(u.gather.data); in(u.gather.indices); *output = u.gather.output.slot; return true;
         case HOLO_K_CAST: in(u.cast.input); *output = u.cast.output.slot; return true;

@@ -177,11 +177,354 @@ matmul_w8a8_omajor_kernel(const float* __restrict__ a, const int8_t* __restrict_
     }
 }
 
+// ---- stream form: the weight is one contiguous [n, k] byte stream, so it is brought in like any
+// other stream: a copy warp keeps a ring of bulk async copies in flight (tiles of whole columns)
+// and the bytes in flight do not depend on registers. The eight product warps form four groups of
+// two that take tiles in turn (so one group's reduction and write-back overlap the others'
+// products); inside a group the warps split the tile's k range. Taken when k is a multiple of 16,
+// at most QS_STAGE_BYTES, and the weight is 16-byte aligned.
+constexpr int QS_GROUPS = 4;
+constexpr int QS_GROUP_WARPS = 2;
+constexpr int QS_WARPS = QS_GROUPS * QS_GROUP_WARPS;   // product warps; warp QS_WARPS is the copy warp
+constexpr int QS_MAX_STAGES = 12;             // as many as fit beside the quantized rows: the ring must cover DRAM latency plus the tiles being consumed
+constexpr int QS_MIN_STAGES = 5;
+constexpr uint32_t QS_STAGE_BYTES = 16384;
+constexpr int QS_MAX_COLS = 4;                 // columns per tile
+constexpr uint32_t QS_WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t qs_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool qs_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok = 0;
+    for (uint32_t it = 0; it < QS_WAIT_LIMIT && !ok; ++it) {
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    }
+    return ok != 0;
+}
+__device__ __forceinline__ void qs_product_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(QS_WARPS * 32) : "memory"); }
+__device__ __forceinline__ void qs_group_barrier(uint32_t group) {
+    asm volatile("bar.sync %0, %1;" ::"r"(2 + group), "n"(QS_GROUP_WARPS * 32) : "memory");
+}
+
+// Sums V values over the 32 lanes with about V shuffles instead of 5 V: at each step a lane keeps
+// one value of a pair and hands the other to its partner, so the number of live values halves.
+// Afterwards the total of value index `idx` sits in the lanes whose bits 4, 3, ... spell idx
+// (bit t of idx = lane bit 4 - t); exact for integers whatever the order.
+template <int V>
+__device__ __forceinline__ int qs_reduce(int (&vals)[V], uint32_t lane) {
+    int live = V;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        if (live > 1) {
+#pragma unroll
+            for (int j = 0; j < V / 2; ++j) {
+                if (j < live / 2) {
+                    const int x = vals[2 * j], y = vals[2 * j + 1];
+                    const bool hi = (lane & o) != 0;
+                    vals[j] = (hi ? y : x) + __shfl_xor_sync(0xffffffffu, hi ? x : y, o);
+                }
+            }
+            live >>= 1;
+        } else {
+            vals[0] += __shfl_xor_sync(0xffffffffu, vals[0], o);
+        }
+    }
+    return vals[0];
+}
+template <int V>
+__device__ __forceinline__ uint32_t qs_reduce_index(uint32_t lane) {
+    uint32_t idx = 0;
+#pragma unroll
+    for (int t = 0; (1 << t) < V; ++t) idx |= ((lane >> (4 - t)) & 1u) << t;
+    return idx;
+}
+
+// shared memory: [ROWS * k quantized rows][stages * QS_STAGE_BYTES ring][2 parities * QS_WARPS * 32 partial sums]
+//                [QS_MAX_ROWS scales][QS_WARPS maxima][abort flag][2 * QS_MAX_STAGES mbarriers]
+__host__ __device__ constexpr size_t qs_smem_bytes(uint32_t rows, uint32_t k, uint32_t stages) {
+    return (size_t)rows * k + (size_t)stages * QS_STAGE_BYTES + 2 * QS_WARPS * 32 * 4 + QG_MAX_ROWS * 4 + QS_WARPS * 4 + 16 + 16 * QS_MAX_STAGES;
+}
+constexpr size_t QS_SMEM_LIMIT = 226 * 1024;
+
+template <int ROWS>
+__global__ void __launch_bounds__((QS_WARPS + 1) * 32, 1)
+matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict__ bq, const float* __restrict__ scales,
+                          const int32_t* __restrict__ zero_points, const float* __restrict__ residual, float* __restrict__ out,
+                          uint32_t m0, uint32_t rows, uint32_t k, uint32_t n, uint32_t cols_per_tile, uint32_t stages, int act, uint32_t* status) {
+    constexpr int V = QS_MAX_COLS * ROWS;      // sums per tile
+    static_assert(V <= 32, "one partial slot per lane");
+    extern __shared__ __align__(128) unsigned char qs_mem[];
+    int8_t* s_q = reinterpret_cast<int8_t*>(qs_mem);
+    unsigned char* ring = qs_mem + (size_t)ROWS * k;
+    int* s_part = reinterpret_cast<int*>(ring + (size_t)stages * QS_STAGE_BYTES);
+    float* s_scale = reinterpret_cast<float*>(s_part + 2 * QS_WARPS * 32);
+    float* s_red = s_scale + QG_MAX_ROWS;
+    volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(s_red + QS_WARPS);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_red + QS_WARPS + 4);
+    const uint32_t bar_full = qs_smem(bars), bar_empty = qs_smem(bars + QS_MAX_STAGES);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t ntiles = (n + cols_per_tile - 1) / cols_per_tile;
+
+    holo_pdl_trigger();
+    if (tid == 0) {
+        for (uint32_t s = 0; s < stages; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_full + 8 * s));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_empty + 8 * s), "r"(QS_GROUP_WARPS));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        *s_abort = 0;
+    }
+    __syncthreads();
+    holo_pdl_wait();  // nothing above touches global memory
+
+    if (warp == QS_WARPS) {   // copy warp: tiles blockIdx.x, + gridDim.x, ... through the ring
+        if (lane != 0) return;
+        uint32_t i = 0;
+        for (uint32_t t = blockIdx.x; t < ntiles; t += gridDim.x, ++i) {
+            const uint32_t s = i % stages, use = i / stages;
+            if (use > 0 && (*s_abort || !qs_wait(bar_empty + 8 * s, (use - 1) & 1))) {
+                *s_abort = 1;
+                atomicOr(status, 2u);
+                break;
+            }
+            const uint32_t c0 = t * cols_per_tile, cols = n - c0 < cols_per_tile ? n - c0 : cols_per_tile;
+            const uint32_t bytes = cols * k;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_full + 8 * s), "r"(bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(qs_smem(ring + (size_t)s * QS_STAGE_BYTES)), "l"(bq + (uint64_t)c0 * k), "r"(bytes), "r"(bar_full + 8 * s) : "memory");
+        }
+        return;
+    }
+
+    // The writer threads of a group (one per column and row of a tile) fetch the column's scale, zero
+    // point and residual one tile ahead, so that no global-memory latency sits between two tiles.
+    const uint32_t group = warp / QS_GROUP_WARPS, gwarp = warp % QS_GROUP_WARPS, gtid = tid % (QS_GROUP_WARPS * 32);
+    const uint32_t wc = gtid / ROWS, wr = gtid % ROWS;      // this writer's column within the tile, and row
+    const bool writer = gtid < (uint32_t)V && wr < rows;
+    float sc_next = 0.0f, res_next = 0.0f;
+    int zp_next = 0;
+    auto fetch_epilogue = [&](uint32_t tile) {
+        sc_next = 0.0f, res_next = 0.0f, zp_next = 0;
+        const uint64_t col = (uint64_t)tile * cols_per_tile + wc;
+        if (writer && tile < ntiles && wc < cols_per_tile && col < n) {
+            sc_next = scales[col];
+            if (zero_points) zp_next = zero_points[col];
+            if (residual) res_next = residual[(uint64_t)(m0 + wr) * n + col];
+        }
+    };
+    fetch_epilogue(blockIdx.x + group * gridDim.x);
+
+    // ---- quantize_row_i8 of the activation rows, while the first tiles are on their way. The rows
+    // are done side by side (8 / ROWS warps each), with 128-bit loads issued sixteen at a time: the row
+    // comes from L2 and every dependent round trip would cost as much as streaming a few tiles. Each
+    // CTA starts its sweep of the row at a different 128-byte line, so that the CTAs do not all ask
+    // the same L2 lines at the same moment. ----
+    {
+        constexpr uint32_t WPR = QS_WARPS / ROWS, QT = WPR * 32, QB = 16;
+        const uint32_t qrow = warp / WPR, qtid = (warp % WPR) * 32 + lane;
+        const bool qlive = qrow < rows;
+        const float* row = a + (uint64_t)(m0 + (qlive ? qrow : 0)) * k;
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const bool a_vec = ((uintptr_t)a & 15u) == 0;   // k is a multiple of 16, so every row then starts on a 16-byte boundary
+        const uint32_t nq = k >> 2;
+        const uint32_t rot = (uint32_t)(((uint64_t)blockIdx.x * nq) / gridDim.x) & ~7u;
+        auto at = [&](uint32_t e) { return e + rot < nq ? e + rot : e + rot - nq; };   // e < nq
+        float amax = 0.0f;
+        auto upd = [&](float v) {
+            const float av = v < 0.0f ? -v : v;
+            if (av > amax) amax = av;
+        };
+        auto upd4 = [&](const float4& v) { upd(v.x), upd(v.y), upd(v.z), upd(v.w); };
+        float4 first[QB];   // the first batch stays in registers for the second pass
+        if (qlive && a_vec) {
+#pragma unroll
+            for (uint32_t u = 0; u < QB; ++u) {
+                const uint32_t j = qtid + u * QT;
+                first[u] = j < nq ? row4[at(j)] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < QB; ++u) upd4(first[u]);
+            for (uint32_t j0 = qtid + QB * QT; j0 < nq; j0 += QB * QT) {
+                float4 v[QB];
+#pragma unroll
+                for (uint32_t u = 0; u < QB; ++u) v[u] = j0 + u * QT < nq ? row4[at(j0 + u * QT)] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (uint32_t u = 0; u < QB; ++u) upd4(v[u]);
+            }
+        } else if (qlive) {
+            for (uint32_t j = qtid; j < k; j += QT) upd(row[j]);
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, amax, o);
+            if (other > amax) amax = other;
+        }
+        if (lane == 0) s_red[warp] = amax;
+        qs_product_barrier();
+        amax = s_red[qrow * WPR];
+#pragma unroll
+        for (uint32_t w = 1; w < WPR; ++w)
+            if (s_red[qrow * WPR + w] > amax) amax = s_red[qrow * WPR + w];
+        const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(127.0f, amax);
+        auto quant1 = [&](float x) {
+            const float t = __fmul_rn(x, inv);
+            const int q = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
+            return (uint32_t)(max(-127, min(127, q)) & 0xff);
+        };
+        auto pack4 = [&](const float4& v) {
+            return amax == 0.0f ? 0u : quant1(v.x) | (quant1(v.y) << 8) | (quant1(v.z) << 16) | (quant1(v.w) << 24);
+        };
+        if (qlive && a_vec) {
+            uint32_t* dst = reinterpret_cast<uint32_t*>(s_q + (size_t)qrow * k);
+#pragma unroll
+            for (uint32_t u = 0; u < QB; ++u)
+                if (qtid + u * QT < nq) dst[at(qtid + u * QT)] = pack4(first[u]);
+            for (uint32_t j0 = qtid + QB * QT; j0 < nq; j0 += QB * QT) {
+                float4 v[QB];
+#pragma unroll
+                for (uint32_t u = 0; u < QB; ++u) v[u] = j0 + u * QT < nq ? row4[at(j0 + u * QT)] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (uint32_t u = 0; u < QB; ++u)
+                    if (j0 + u * QT < nq) dst[at(j0 + u * QT)] = pack4(v[u]);
+            }
+        } else if (qlive) {
+            for (uint32_t j = qtid; j < k; j += QT) s_q[(size_t)qrow * k + j] = (int8_t)(amax == 0.0f ? 0 : (int)(int8_t)quant1(row[j]));
+        }
+        if (qlive && qtid == 0) s_scale[qrow] = amax == 0.0f ? 0.0f : __fdiv_rn(amax, 127.0f);
+        qs_product_barrier();
+    }
+
+    const uint32_t nvec = k >> 4;
+    const uint32_t ridx = qs_reduce_index<V>(lane);
+    const bool rlane = (lane & ((32u / (V < 32 ? V : 32)) - 1u)) == 0;   // one lane per value index stores the warp's sum
+    for (uint32_t i = group; ; i += QS_GROUPS) {
+        const uint32_t t = blockIdx.x + i * gridDim.x;
+        if (t >= ntiles) break;
+        const uint32_t s = i % stages, use = i / stages;
+        const uint32_t c0 = t * cols_per_tile, cols = n - c0 < cols_per_tile ? n - c0 : cols_per_tile;
+        const float sc = sc_next, res = res_next;
+        const int zp = zp_next;
+        fetch_epilogue(t + QS_GROUPS * gridDim.x);
+        const bool ok = !*s_abort && qs_wait(bar_full + 8 * s, use & 1);
+        if (!ok) {   // keep walking so that every warp of the group still meets the barrier below
+            *s_abort = 1;
+            atomicOr(status, 2u);
+        }
+        // U positions of the k range at a time, each into its own accumulators: with one or two rows a
+        // single chain of dependent dp4a per column would leave the loads of the next position waiting
+        constexpr int U = 1;
+        int accu[U][V];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int j = 0; j < V; ++j) accu[u][j] = 0;
+        if (ok) {
+            const int4* tile = reinterpret_cast<const int4*>(ring + (size_t)s * QS_STAGE_BYTES);
+            constexpr uint32_t GL = QS_GROUP_WARPS * 32;
+            for (uint32_t v0 = gwarp * 32 + lane; v0 < nvec; v0 += U * GL) {
+                int4 qv[U][ROWS];
+                int4 w[U][QS_MAX_COLS];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const uint32_t v = v0 + u * GL;
+                    if (v < nvec) {
+#pragma unroll
+                        for (int r = 0; r < ROWS; ++r) qv[u][r] = *reinterpret_cast<const int4*>(s_q + (size_t)r * k + (size_t)v * 16);
+#pragma unroll
+                        for (int c = 0; c < QS_MAX_COLS; ++c)
+                            if ((uint32_t)c < cols) w[u][c] = tile[(size_t)c * nvec + v];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (v0 + u * GL < nvec) {
+#pragma unroll
+                        for (int c = 0; c < QS_MAX_COLS; ++c) {
+                            if ((uint32_t)c < cols) {
+#pragma unroll
+                                for (int r = 0; r < ROWS; ++r) {
+                                    int x = accu[u][c * ROWS + r];
+                                    x = __dp4a(w[u][c].x, qv[u][r].x, x);
+                                    x = __dp4a(w[u][c].y, qv[u][r].y, x);
+                                    x = __dp4a(w[u][c].z, qv[u][r].z, x);
+                                    x = __dp4a(w[u][c].w, qv[u][r].w, x);
+                                    accu[u][c * ROWS + r] = x;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        int acc[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            acc[j] = accu[0][j];
+#pragma unroll
+            for (int u = 1; u < U; ++u) acc[j] += accu[u][j];
+        }
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_empty + 8 * s) : "memory");   // the tile has been consumed
+        int* part = s_part + ((i / QS_GROUPS) & 1) * (QS_WARPS * 32) + group * (QS_GROUP_WARPS * 32);
+        const int total = qs_reduce<V>(acc, lane);
+        if (rlane) part[gwarp * 32 + ridx] = total;
+        qs_group_barrier(group);
+        if (writer && wc < cols && ok) {
+            int sum = 0;
+#pragma unroll
+            for (int w = 0; w < QS_GROUP_WARPS; ++w) sum += part[w * 32 + gtid];
+            const uint32_t col = c0 + wc;
+            if (zp != 0) atomicOr(status, 16u);   // symmetric form only
+            const float sa = s_scale[wr];
+            float y = sa == 0.0f ? 0.0f : __fmul_rn(__int2float_rn(sum), __fmul_rn(sa, sc));
+            if (residual) y = __fadd_rn(y, res);
+            if (act >= 0) y = holo::lut_act_ref(act, y);
+            out[(uint64_t)(m0 + wr) * n + col] = y;
+        }
+    }
+}
+
+template <int ROWS>
+cudaError_t launch_stream(holo_b200_ctx* ctx, uint32_t grid, size_t smem, const float* a, const int8_t* bq, const float* scales,
+                          const int32_t* zero_points, const float* residual, float* out, uint32_t m0, uint32_t rows, uint32_t k,
+                          uint32_t n, uint32_t cols_per_tile, uint32_t stages, int act) {
+    static thread_local int configured_device = -1;
+    if (configured_device != ctx->device) {
+        cudaError_t e = cudaFuncSetAttribute(matmul_w8a8_stream_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QS_SMEM_LIMIT);
+        if (e != cudaSuccess) return e;
+        configured_device = ctx->device;
+    }
+    return holo_launch_kernel(ctx, matmul_w8a8_stream_kernel<ROWS>, dim3(grid), dim3((QS_WARPS + 1) * 32), smem, 1, a, bq, scales, zero_points,
+                              residual, out, m0, rows, k, n, cols_per_tile, stages, act, ctx->dev_status);
+}
+
 }  // namespace
 
 int32_t holo_launch_matmul_w8a8_omajor(holo_b200_ctx* ctx, const float* a, const int8_t* bq, const float* scales, const int32_t* zero_points,
                                        const float* residual, float* out, uint32_t m, uint32_t k, uint32_t n, int act) {
     if (m == 0 || k == 0 || n == 0) return HOLO_OK;
+    if ((k & 15u) == 0 && k <= QS_STAGE_BYTES && ((uintptr_t)bq & 15u) == 0 && !getenv("HOLO_W8A8_NO_STREAM")) {
+        uint32_t cols_per_tile = QS_STAGE_BYTES / k;
+        if (cols_per_tile > QS_MAX_COLS) cols_per_tile = QS_MAX_COLS;
+        const uint32_t ntiles = (n + cols_per_tile - 1) / cols_per_tile;
+        const uint32_t grid = ntiles < (uint32_t)ctx->sm_count ? ntiles : (uint32_t)ctx->sm_count;
+        uint32_t per = QG_MAX_ROWS;   // rows per launch: what fits beside the ring in shared memory
+        while (per > 1 && qs_smem_bytes(per, k, QS_MIN_STAGES) > QS_SMEM_LIMIT) per >>= 1;
+        for (uint32_t m0 = 0; m0 < m; m0 += per) {
+            const uint32_t take = m - m0 < per ? m - m0 : per;
+            const uint32_t rt = take > 4 ? 8 : take > 2 ? 4 : take;
+            uint32_t stages = QS_MAX_STAGES;
+            while (stages > QS_MIN_STAGES && qs_smem_bytes(rt, k, stages) > QS_SMEM_LIMIT) --stages;
+            const size_t smem = qs_smem_bytes(rt, k, stages);
+            cudaError_t e = rt == 8 ? launch_stream<8>(ctx, grid, smem, a, bq, scales, zero_points, residual, out, m0, take, k, n, cols_per_tile, stages, act)
+                          : rt == 4 ? launch_stream<4>(ctx, grid, smem, a, bq, scales, zero_points, residual, out, m0, take, k, n, cols_per_tile, stages, act)
+                          : rt == 2 ? launch_stream<2>(ctx, grid, smem, a, bq, scales, zero_points, residual, out, m0, take, k, n, cols_per_tile, stages, act)
+                                    : launch_stream<1>(ctx, grid, smem, a, bq, scales, zero_points, residual, out, m0, take, k, n, cols_per_tile, stages, act);
+            HOLO_CUDA(e);
+            ctx->launches++;
+        }
+        return HOLO_OK;
+    }
     const uint32_t kpad = (k + 15u) & ~15u;
     static thread_local int configured_device = -1;
     if (configured_device != ctx->device) {

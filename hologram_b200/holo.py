@@ -48,7 +48,7 @@ def encode_call(call):
         return out + b"".join(_buf(b) for b in (c.a, c.bq, c.scales, c.zero_points, c.output)) + struct.pack(
             "<IIIIIBBIIBBB", c.m, c.k, c.n, c.channels, c.inner, c.quant_dtype, c.dtype, c.scale_bits, c.zero_point & 0xFFFFFFFF,
             c.bq_omajor, c.act_quant, c.act) + _buf(c.residual)
-    if k in (kc.K_RMS_NORM, kc.K_ADD_RMS_NORM):
+    if k in (kc.K_LAYER_NORM, kc.K_RMS_NORM, kc.K_ADD_RMS_NORM):
         c = u.norm
         return out + _buf(c.x) + _buf(c.gamma) + _buf(c.beta) + _buf(c.residual) + _buf(c.output) + struct.pack(
             "<IIIIQB", c.batch, c.feature, c.channels, c.num_groups, c.epsilon_bits, c.dtype)
@@ -62,6 +62,13 @@ def encode_call(call):
     if k == kc.K_CAST:
         c = u.cast
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<QBB", c.element_count, c.src_dtype, c.dst_dtype)
+    if k == kc.K_EXPAND:
+        c = u.expand
+        return out + _buf(c.input) + _buf(c.output) + struct.pack("<B8I8IB", c.rank, *c.in_dims, *c.out_dims, c.dtype)
+    if k == kc.K_BROADCAST_BINARY:
+        c = u.broadcast_binary
+        dims = b"".join(struct.pack("<II", c.in_dims[i], c.out_dims[i]) for i in range(c.rank))
+        return out + _buf(c.small) + _buf(c.other) + _buf(c.output) + struct.pack("<BBBB", c.rank, c.op, c.small_is_lhs, c.dtype) + dims
     if k == kc.K_SOFTMAX:
         c = u.softmax
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<IIB", c.batch, c.feature, c.dtype)

@@ -20,6 +20,8 @@ FUSED_RELU, FUSED_GELU, FUSED_SILU, FUSED_SIGMOID, FUSED_TANH, FUSED_EXP = 1, 2,
 K_ADD, K_MUL = 5, 7
 K_SIGMOID, K_TANH, K_GELU, K_SILU, K_EXP, K_ERF = 12, 13, 14, 15, 18, 32
 K_MATMUL, K_RMS_NORM, K_RESHAPE, K_ROTARY = 46, 51, 60, 75
+K_LAYER_NORM, K_EXPAND, K_BROADCAST_BINARY = 50, 72, 112
+BROADCAST_ADD, BROADCAST_SUB, BROADCAST_MUL = 0, 1, 2
 K_ADD_RMS_NORM, K_TRANSPOSE, K_CONCAT, K_SLICE, K_SOFTMAX = 54, 61, 62, 63, 64
 K_DECODE_ATTENTION = 119
 K_MATMUL_DEQUANT = 116
@@ -108,6 +110,36 @@ class SoftmaxCall(C.Structure):
     _fields_ = [("input", BufferRef), ("output", BufferRef), ("batch", C.c_uint32), ("feature", C.c_uint32), ("dtype", C.c_uint8)]
 
 
+class ExpandCall(C.Structure):
+    """kernel_call.rs:539-547: an axis with in_dims[i] == 1 reads index 0, the others map 1:1."""
+    _fields_ = [("input", BufferRef), ("output", BufferRef), ("rank", C.c_uint8), ("in_dims", C.c_uint32 * 8),
+                ("out_dims", C.c_uint32 * 8), ("dtype", C.c_uint8)]
+
+    @classmethod
+    def make(cls, inp, out, in_dims, out_dims, dtype):
+        c = cls()
+        c.input, c.output, c.rank, c.dtype = inp, out, len(out_dims), dtype
+        for i, (a, b) in enumerate(zip(in_dims, out_dims)):
+            c.in_dims[i], c.out_dims[i] = a, b
+        return c
+
+
+class BroadcastBinaryCall(C.Structure):
+    """kernel_call.rs:292-317: out[o] = op(small[bcast(o)], other[o]) (swapped when small_is_lhs is 0)."""
+    _fields_ = [("small", BufferRef), ("other", BufferRef), ("output", BufferRef), ("rank", C.c_uint8),
+                ("in_dims", C.c_uint32 * 8), ("out_dims", C.c_uint32 * 8), ("op", C.c_uint8), ("small_is_lhs", C.c_uint8),
+                ("dtype", C.c_uint8)]
+
+    @classmethod
+    def make(cls, small, other, out, in_dims, out_dims, op, small_is_lhs, dtype):
+        c = cls()
+        c.small, c.other, c.output, c.rank = small, other, out, len(out_dims)
+        c.op, c.small_is_lhs, c.dtype = op, int(small_is_lhs), dtype
+        for i, (a, b) in enumerate(zip(in_dims, out_dims)):
+            c.in_dims[i], c.out_dims[i] = a, b
+        return c
+
+
 class TransposeCall(C.Structure):
     """kernel_call.rs:491-499: output axis i is input axis perm[i]."""
     _fields_ = [("input", BufferRef), ("output", BufferRef), ("rank", C.c_uint8), ("dims", C.c_uint32 * 8),
@@ -177,7 +209,7 @@ class _Payload(C.Union):
     _fields_ = [("unary", UnaryCall), ("binary", BinaryCall), ("matmul", MatMulCall),
                 ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("matmul_dequant", MatMulDequantCall), ("norm", NormCall),
                 ("rope", RoPECall), ("gather", GatherCall), ("cast", CastCall), ("layout", LayoutCall),
-                ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
+                ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("expand", ExpandCall), ("broadcast_binary", BroadcastBinaryCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
                 ("decode_attention", DecodeAttentionCall),
                 ("decode_attention_valid", DecodeAttentionValidCall), ("quantize_rows_i8", QuantizeRowsI8Call),
                 ("decode_attention_valid_q8", DecodeAttentionValidQ8Call), ("all_reduce", AllReduceCall),
@@ -225,9 +257,15 @@ class KernelCall(C.Structure):
     @classmethod
     def RmsNorm(cls, c): return cls.of(K_RMS_NORM, c)
     @classmethod
+    def LayerNorm(cls, c): return cls.of(K_LAYER_NORM, c)
+    @classmethod
     def AddRmsNorm(cls, c): return cls.of(K_ADD_RMS_NORM, c)
     @classmethod
     def Softmax(cls, c): return cls.of(K_SOFTMAX, c)
+    @classmethod
+    def Expand(cls, c): return cls.of(K_EXPAND, c)
+    @classmethod
+    def BroadcastBinary(cls, c): return cls.of(K_BROADCAST_BINARY, c)
     @classmethod
     def Transpose(cls, c): return cls.of(K_TRANSPOSE, c)
     @classmethod
@@ -263,7 +301,7 @@ class KernelCall(C.Structure):
 KernelCall._FIELD = {
     UnaryCall: "unary", BinaryCall: "binary", MatMulCall: "matmul", MatMulActivationCall: "matmul_activation",
     MatMulAddCall: "matmul_add", MatMulDequantCall: "matmul_dequant", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
-    LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
+    LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", ExpandCall: "expand", BroadcastBinaryCall: "broadcast_binary", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
     DecodeAttentionCall: "decode_attention", DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
     DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce", RopeQuantizeCall: "rope_quantize",
 }

@@ -73,6 +73,7 @@ extern "C" {
 #define HOLO_K_EXP 18
 #define HOLO_K_ERF 32
 #define HOLO_K_MATMUL 46
+#define HOLO_K_LAYER_NORM 50
 #define HOLO_K_RMS_NORM 51
 #define HOLO_K_ADD_RMS_NORM 54
 #define HOLO_K_RESHAPE 60
@@ -80,10 +81,12 @@ extern "C" {
 #define HOLO_K_CONCAT 62
 #define HOLO_K_SLICE 63
 #define HOLO_K_SOFTMAX 64
+#define HOLO_K_EXPAND 72
 #define HOLO_K_ROTARY 75
 #define HOLO_K_DEQUANTIZE 105
 #define HOLO_K_MATMUL_ACTIVATION 106
 #define HOLO_K_MATMUL_ADD 107
+#define HOLO_K_BROADCAST_BINARY 112
 #define HOLO_K_GATHER 114
 #define HOLO_K_MATMUL_DEQUANT 116 /* the extended wire form (kernel_codec.rs D_MMDQ2); served: output-major W8A8 int8 */
 #define HOLO_K_CAST 115
@@ -177,6 +180,28 @@ typedef struct HoloSoftmaxCall {
     uint32_t batch, feature;
     uint8_t dtype;
 } HoloSoftmaxCall;
+
+/* ExpandCall (kernel_call.rs:539-547): replicate `input` to out_dims; an axis with in_dims[i] == 1 reads
+ * index 0, every other axis maps 1:1 (in_dims[i] == out_dims[i]); rank <= 8; any dtype. */
+typedef struct HoloExpandCall {
+    HoloBufferRef input, output;
+    uint8_t rank;
+    uint32_t in_dims[8], out_dims[8];
+    uint8_t dtype;
+} HoloExpandCall;
+
+/* BroadcastBinaryCall (kernel_call.rs:292-317): out[o] = op(small[bcast(o)], other[o]), operands swapped when
+ * small_is_lhs == 0; op 0 add, 1 sub, 2 mul; `small` has in_dims (1 on the broadcast axes), `other` and the
+ * output have out_dims. */
+#define HOLO_BROADCAST_ADD 0
+#define HOLO_BROADCAST_SUB 1
+#define HOLO_BROADCAST_MUL 2
+typedef struct HoloBroadcastBinaryCall {
+    HoloBufferRef small, other, output;
+    uint8_t rank;
+    uint32_t in_dims[8], out_dims[8];
+    uint8_t op, small_is_lhs, dtype;
+} HoloBroadcastBinaryCall;
 
 /* TransposeCall (kernel_call.rs:491-499): output axis i is input axis perm[i]; rank <= 8 */
 typedef struct HoloTransposeCall {
@@ -306,6 +331,8 @@ typedef struct HoloKernelCall {
         HoloLayoutCall layout;          /* RESHAPE SLICE (contiguous copies; a slice's start is the input ref's offset) */
         HoloTransposeCall transpose;
         HoloSoftmaxCall softmax;
+        HoloExpandCall expand;
+        HoloBroadcastBinaryCall broadcast_binary;
         HoloDequantizeCall dequantize;
         HoloKvCacheWriteCall kv_cache_write;
         HoloDecodeAttentionCall decode_attention;

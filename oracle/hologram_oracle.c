@@ -438,6 +438,66 @@ int holo_or_rms_norm(const void* x, const void* gamma, void* out, uint32_t batch
     return 0;
 }
 
+/* ---- Expand and BroadcastBinary: cpu/float_kernels.rs:3405-3444 and :3250-3397. The small operand is read
+ * at the row-major index of the output coordinates with stride 0 on its size-1 axes. other == NULL:
+ * a copy of es bytes (Expand); else op 0 add, 1 sub, 2 mul in f32, operands swapped when !small_is_lhs. */
+int holo_or_broadcast(const void* small, const void* other, void* out, uint32_t rank, const uint32_t* in_dims,
+                      const uint32_t* out_dims, uint32_t es, int op, int small_is_lhs, int dtype) {
+    if (rank == 0 || rank > 8) return -3;
+    size_t strides[8], total = 1, stride = 1;
+    for (int i = (int)rank - 1; i >= 0; --i) {
+        strides[i] = in_dims[i] == 1 ? 0 : stride;
+        stride *= in_dims[i];
+        total *= out_dims[i];
+    }
+    for (size_t o = 0; o < total; ++o) {
+        size_t rem = o, idx = 0;
+        for (int i = (int)rank - 1; i >= 0; --i) {
+            idx += (rem % out_dims[i]) * strides[i];
+            rem /= out_dims[i];
+        }
+        if (!other) memcpy((uint8_t*)out + o * es, (const uint8_t*)small + idx * es, es);
+        else {
+            float sv = read_float(small, idx, dtype), ov = read_float(other, o, dtype);
+            float a = small_is_lhs ? sv : ov, b = small_is_lhs ? ov : sv;
+            if (op > 2) return -3;
+            write_float(out, o, op == 0 ? a + b : op == 1 ? a - b : a * b, dtype);
+        }
+    }
+    return 0;
+}
+
+/* ---- LayerNorm: cpu/float_kernels.rs:1338-1445 (generic loop :1414-1443): left-to-right mean, variance
+ * of the centred row, inv_std = 1/sqrt(var + eps), (x - mean) * inv_std * gamma + beta. */
+int holo_or_layer_norm(const void* x, const void* gamma, const void* beta, void* out, uint32_t batch, uint32_t feature,
+                       uint64_t epsilon_bits, int dtype) {
+    float eps;
+    if (epsilon_bits == 0) eps = 1e-9f;
+    else {
+        eps = f32_from_bits((uint32_t)epsilon_bits);
+        if (!(isfinite(eps) && eps > 0.0f)) return -3;
+    }
+    for (uint32_t bi = 0; bi < batch; ++bi) {
+        size_t off = (size_t)bi * feature;
+        float mean = 0.0f;
+        for (uint32_t j = 0; j < feature; ++j) mean += read_float(x, off + j, dtype);
+        mean /= (float)feature;
+        float var = 0.0f;
+        for (uint32_t j = 0; j < feature; ++j) {
+            float d = read_float(x, off + j, dtype) - mean;
+            var += d * d;
+        }
+        var /= (float)feature;
+        float inv_std = 1.0f / sqrtf(var + eps);
+        for (uint32_t j = 0; j < feature; ++j) {
+            float g = gamma ? read_float(gamma, j, dtype) : 1.0f;
+            float b = beta ? read_float(beta, j, dtype) : 0.0f;
+            write_float(out, off + j, (read_float(x, off + j, dtype) - mean) * inv_std * g + b, dtype);
+        }
+    }
+    return 0;
+}
+
 /* ---- AddRmsNorm: rms_norm over x + residual, the sum kept in f32 (not narrowed) before the
  * norm; a null residual makes it RmsNorm. cpu/float_kernels.rs:1567-1681 (generic-dtype loop
  * :1656-1679). */

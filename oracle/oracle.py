@@ -39,6 +39,8 @@ def _load(path):
         "holo_or_binary": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_rms_norm": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
         "holo_or_add_rms_norm": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
+        "holo_or_broadcast": (C.c_int, [_c, _c, _c, C.c_uint32, _c, _c, C.c_uint32, C.c_int, C.c_int, C.c_int]),
+        "holo_or_layer_norm": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
         "holo_or_softmax": (C.c_int, [_c, _c, C.c_uint32, C.c_uint32, C.c_int]),
         "holo_or_transpose": (C.c_int, [_c, _c, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint8), C.c_uint32]),
         "holo_or_rope": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint64, C.c_int]),
@@ -185,6 +187,27 @@ def add_rms_norm(x, residual, gamma, batch, feature, eps_bits, dtype):
     r = None if residual is None else np.ascontiguousarray(residual)
     g = None if gamma is None else np.ascontiguousarray(gamma)
     rc = lib.holo_or_add_rms_norm(_p(x), _p(r), _p(g), _p(out), batch, feature, eps_bits, dtype)
+    assert rc == 0, rc
+    return out
+
+
+def broadcast(small, other, in_dims, out_dims, itemsize, op=-1, small_is_lhs=True, dtype=DTYPE_F32):
+    """Expand (other None) or BroadcastBinary; returns the raw output bytes as uint8."""
+    small = np.ascontiguousarray(small)
+    other = None if other is None else np.ascontiguousarray(other)
+    ind, outd = np.asarray(in_dims, dtype=np.uint32), np.asarray(out_dims, dtype=np.uint32)
+    out = np.zeros(int(np.prod(outd, dtype=np.uint64)) * itemsize, dtype=np.uint8)
+    rc = lib.holo_or_broadcast(_p(small), _p(other), _p(out), len(outd), _p(ind), _p(outd), itemsize, op, int(small_is_lhs), dtype)
+    assert rc == 0, rc
+    return out
+
+
+def layer_norm(x, gamma, beta, batch, feature, eps_bits, dtype):
+    x = np.ascontiguousarray(x)
+    out = np.empty_like(x)
+    g = None if gamma is None else np.ascontiguousarray(gamma)
+    b = None if beta is None else np.ascontiguousarray(beta)
+    rc = lib.holo_or_layer_norm(_p(x), _p(g), _p(b), _p(out), batch, feature, eps_bits, dtype)
     assert rc == 0, rc
     return out
 

@@ -70,6 +70,12 @@ def test_op_signature_frozen_bytes():
     assert hs.op_signature(kc.KernelCall.Gather(ga)) == (114, struct.pack("<QQQQBB", 1, 32000, 4096, 64, kc.DTYPE_I32, kc.DTYPE_BF16))
     ca = kc.CastCall(rb(0), rb(1), 50, kc.DTYPE_BF16, kc.DTYPE_F32)
     assert hs.op_signature(kc.KernelCall.Cast(ca)) == (115, struct.pack("<QBB", 50, kc.DTYPE_BF16, kc.DTYPE_F32))
+    ln = kc.NormCall(rb(0), rb(1), rb(2), kc.NONE, rb(3), 4, 64, 0, 0, 0, kc.DTYPE_F32)
+    assert hs.op_signature(kc.KernelCall.LayerNorm(ln)) == (49, struct.pack("<IIIIQBB", 4, 64, 0, 0, 0, kc.DTYPE_F32, 0))
+    ex = kc.ExpandCall.make(rb(0), rb(1), (1, 4), (3, 4), kc.DTYPE_F32)
+    assert hs.op_signature(kc.KernelCall.Expand(ex)) == (71, struct.pack("<BBIIII", 2, kc.DTYPE_F32, 1, 3, 4, 4))
+    bb = kc.BroadcastBinaryCall.make(rb(0), rb(1), rb(2), (1, 4), (3, 4), kc.BROADCAST_SUB, False, kc.DTYPE_F32)
+    assert hs.op_signature(kc.KernelCall.BroadcastBinary(bb)) == (112, struct.pack("<BBBBIIII", 2, 1, 0, kc.DTYPE_F32, 1, 3, 4, 4))
     sm = kc.SoftmaxCall(rb(0), rb(1), 64, 4096, kc.DTYPE_F32)
     assert hs.op_signature(kc.KernelCall.Softmax(sm)) == (63, struct.pack("<IIB", 64, 4096, kc.DTYPE_F32))
     # an all-reduce is not a function of local labels: no signature

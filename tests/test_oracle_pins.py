@@ -283,6 +283,44 @@ def test_softmax_restatement_meets_the_reference_pins():
         assert np.all(np.abs(got.sum(axis=1) - 1.0) < 1e-3)
 
 
+def test_layer_norm_restatement_meets_the_reference_pins():
+    # crates/hologram-compute/tests/conformance.rs:336-395: within 1e-3 of the f64 layer norm at these shapes;
+    # tests/pinned_semantics.rs:245-275: the declared epsilon is authoritative, 0 selects 1e-9
+    eps = np.float32(1e-5)
+    bits = int(eps.view(np.uint32))
+    for idx, (b, f) in enumerate(((2, 8), (8, 33), (16, 256))):
+        rng = np.random.default_rng(0x400 + idx)
+        x, g, bt = (rng.standard_normal(n).astype(np.float32) for n in (b * f, f, f))
+        got = orc.layer_norm(x, g, bt, b, f, bits, kc.DTYPE_F32).reshape(b, f)
+        x64 = x.astype(np.float64).reshape(b, f)
+        mean = x64.mean(axis=1, keepdims=True)
+        var = ((x64 - mean) ** 2).mean(axis=1, keepdims=True)
+        want = (x64 - mean) / np.sqrt(var + float(eps)) * g.astype(np.float64) + bt.astype(np.float64)
+        assert np.max(np.abs(got - want)) < 1e-3
+    x = (np.float32(1.0) + np.arange(8, dtype=np.float32) * np.float32(1e-7)).astype(np.float32)
+    e12 = orc.layer_norm(x, None, None, 1, 8, int(np.float32(1e-12).view(np.uint32)), kc.DTYPE_F32)
+    e9 = orc.layer_norm(x, None, None, 1, 8, int(np.float32(1e-9).view(np.uint32)), kc.DTYPE_F32)
+    dflt = orc.layer_norm(x, None, None, 1, 8, 0, kc.DTYPE_F32)
+    assert not np.array_equal(e12.view(np.uint32), e9.view(np.uint32))
+    assert np.array_equal(dflt.view(np.uint32), e9.view(np.uint32))
+
+
+def test_broadcast_restatement_equals_numpy_broadcasting():
+    # expand_float / broadcast_binary_float (cpu/float_kernels.rs:3405-3444, :3250-3397): stride 0 on the
+    # size-1 axes of the small operand; one f32 operation per element
+    rng = np.random.default_rng(112)
+    in_dims, out_dims = (1, 5, 1, 7), (3, 5, 4, 7)
+    small = rng.standard_normal(int(np.prod(in_dims))).astype(np.float32)
+    other = rng.standard_normal(int(np.prod(out_dims))).astype(np.float32)
+    s4, o4 = small.reshape(in_dims), other.reshape(out_dims)
+    assert np.array_equal(orc.broadcast(small, None, in_dims, out_dims, 4).view(np.float32).reshape(out_dims), np.broadcast_to(s4, out_dims))
+    for op, fn in ((0, np.add), (1, np.subtract), (2, np.multiply)):
+        for lhs in (True, False):
+            want = fn(s4, o4) if lhs else fn(o4, s4)
+            got = orc.broadcast(small, other, in_dims, out_dims, 4, op, lhs, kc.DTYPE_F32).view(np.float32).reshape(out_dims)
+            assert np.array_equal(got.view(np.uint32), want.astype(np.float32).view(np.uint32))
+
+
 def test_mask_form_restatement_equals_scalar_form_bitwise():
     # the reference pins that a realized-length mask reproduces DecodeAttentionValid bit for bit
     # (crates/hologram-compute/tests/decode_attention_valid.rs:226-282); all-erased row = zeros

@@ -39,7 +39,8 @@ def test_reference_golden_fixture(backend):
     assert orc.fnv1a64_f32(out) == 0x787CCDC172029F9B
 
 
-@pytest.mark.parametrize("m,k,n", [(1, 4096, 14336), (4, 896, 4864), (1, 100, 7), (9, 250, 33), (2, 4096, 4096)])
+@pytest.mark.parametrize("m,k,n", [(1, 4096, 14336), (4, 896, 4864), (1, 100, 7), (9, 250, 33), (2, 4096, 4096),
+                                   (3, 14336, 130), (8, 1024, 1001), (9, 512, 37), (5, 16384, 21), (2, 16400, 9), (1, 64, 3)])
 def test_bit_exact_against_the_cpu_kernel(backend, m, k, n):
     rng = np.random.default_rng(m * 7 + n)
     a = rng.standard_normal(m * k).astype(np.float32)
