@@ -530,6 +530,32 @@ int32_t do_broadcast(holo_b200_ctx* ctx, const char* name, HoloBufferRef small_r
     return holo_launch_broadcast(ctx, small, other, out, rank, in_dims, out_dims, (uint32_t)es, other_ref ? op : -1, small_is_lhs, dtype);
 }
 
+// reduce_float (cpu/float_kernels.rs:1901-2022)
+uint64_t reduce_out_count(const HoloReduceCall& c) {
+    uint64_t out = 1;
+    if (c.rank == 0 || c.axes_mask == 0) return 1;
+    for (uint32_t i = 0; i < c.rank && i < 8; ++i)
+        if (!((c.axes_mask >> i) & 1u)) out *= c.dims[i];
+    return out;
+}
+int32_t do_reduce(holo_b200_ctx* ctx, const HoloReduceCall& c, int kind, int mean, holo_b200_workspace* ws) {
+    const uint64_t n = c.element_count;
+    if (n == 0) return HOLO_OK;
+    if (!holo_is_compute_float(c.dtype)) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: reduce dtype %u", c.dtype);
+    if (c.rank > 8) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: reduce: rank must be <= 8");
+    if (n > 0xffffffffull && c.rank == 0) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: reduce: a rank-0 input above 2^32 elements");
+    uint64_t prod = 1;
+    for (uint32_t i = 0; i < c.rank; ++i) prod *= c.dims[i];
+    if (c.rank > 0 && prod != n) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: reduce: dims product != element_count");
+    const size_t es = holo_dtype_size(c.dtype);
+    const uint64_t out_count = reduce_out_count(c);
+    uint8_t *in, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, out_count * es, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.input, n * es, &in, nullptr));
+    HOLO_TRY(check_disjoint({out, out_count * es}, c.output.slot, {{in, n * es}}));
+    return holo_launch_reduce(ctx, in, out, c.rank, c.dims, c.axes_mask, n, kind, mean, c.dtype);
+}
+
 // dequantize (cpu/kernels.rs:185-296)
 int32_t do_dequantize(holo_b200_ctx* ctx, const HoloDequantizeCall& c, holo_b200_workspace* ws) {
     if (c.quant_dtype != HOLO_DTYPE_I8 && c.quant_dtype != HOLO_DTYPE_U8) return holo_fail_slot(c.input.slot, "dequantize source must be i8 or u8");
@@ -769,6 +795,11 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         case HOLO_K_RESHAPE: case HOLO_K_SLICE: return do_reshape(ctx, call->u.layout, ws);
         case HOLO_K_CONCAT: return do_concat(ctx, call->u.binary, ws);
         case HOLO_K_TRANSPOSE: return do_transpose(ctx, call->u.transpose, ws);
+        case HOLO_K_REDUCE_SUM: return do_reduce(ctx, call->u.reduce, 0, 0, ws);
+        case HOLO_K_REDUCE_MEAN: return do_reduce(ctx, call->u.reduce, 0, 1, ws);
+        case HOLO_K_REDUCE_PROD: return do_reduce(ctx, call->u.reduce, 1, 0, ws);
+        case HOLO_K_REDUCE_MIN: return do_reduce(ctx, call->u.reduce, 2, 0, ws);
+        case HOLO_K_REDUCE_MAX: return do_reduce(ctx, call->u.reduce, 3, 0, ws);
         case HOLO_K_EXPAND: {
             const HoloExpandCall& c = call->u.expand;
             return do_broadcast(ctx, "expand", c.input, nullptr, c.output, c.rank, c.in_dims, c.out_dims, -1, 1, c.dtype, ws);
@@ -845,6 +876,10 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             }
             return true;
         }
+        case HOLO_K_REDUCE_SUM: case HOLO_K_REDUCE_MEAN: case HOLO_K_REDUCE_PROD: case HOLO_K_REDUCE_MIN: case HOLO_K_REDUCE_MAX:
+            l->in(&c->u.reduce.input);
+            l->out(&c->u.reduce.output, reduce_out_count(c->u.reduce) * holo_dtype_size(c->u.reduce.dtype));
+            return true;
         case HOLO_K_SOFTMAX:
             l->in(&c->u.softmax.input);
             l->out(&c->u.softmax.output, (uint64_t)c->u.softmax.batch * c->u.softmax.feature * holo_dtype_size(c->u.softmax.dtype));

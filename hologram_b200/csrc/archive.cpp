@@ -84,6 +84,14 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             c.batch = r.u32(); c.feature = r.u32(); c.channels = r.u32(); c.num_groups = r.u32(); c.epsilon_bits = r.u64(); c.dtype = r.u8();
             break;
         }
+        case HOLO_K_REDUCE_SUM: case HOLO_K_REDUCE_MEAN: case HOLO_K_REDUCE_PROD: case HOLO_K_REDUCE_MIN: case HOLO_K_REDUCE_MAX: {
+            HoloReduceCall& c = out->u.reduce;
+            c.input = r.buf(); c.output = r.buf(); c.element_count = r.u64(); c.rank = r.u8(); c.axes_mask = r.u32();
+            c.keepdims = r.u8(); c.dtype = r.u8();
+            if (c.rank > 8) return false;
+            for (uint32_t i = 0; i < c.rank; ++i) c.dims[i] = r.u32();
+            break;
+        }
         case HOLO_K_EXPAND: {
             HoloExpandCall& c = out->u.expand;
             c.input = r.buf(); c.output = r.buf(); c.rank = r.u8();

@@ -184,6 +184,70 @@ __global__ void transpose_kernel(const uint8_t* __restrict__ in, uint8_t* __rest
     }
 }
 
+// reduce_float, cpu/float_kernels.rs:1901-2022 (ReducePlan :2024-2099). kind 0 sum, 1 prod, 2 min, 3 max.
+struct ReduceParams {
+    uint32_t kept_dims[8], red_dims[8];
+    uint64_t kept_strides[8], red_strides[8];   // input strides (elements) of the kept and of the reduced axes
+    uint32_t n_kept, n_red;
+    uint64_t out_count, reduced_count;
+    int kind, mean, dtype;
+};
+__device__ __forceinline__ float reduce_fold(int kind, float a, float b) {
+    return kind == 0 ? __fadd_rn(a, b) : kind == 1 ? __fmul_rn(a, b) : kind == 2 ? fminf(a, b) : fmaxf(a, b);
+}
+__device__ __forceinline__ float reduce_init(int kind) { return kind == 0 ? 0.0f : kind == 1 ? 1.0f : kind == 2 ? INFINITY : -INFINITY; }
+
+// One thread per output cell, folding the cell's inputs in linear input order; with a 16-bit dtype the
+// running value is narrowed after every step, as the CPU loop keeps it in the output buffer.
+__global__ void reduce_cells_kernel(const void* __restrict__ in, void* __restrict__ out, const ReduceParams p) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    const uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= p.out_count) return;
+    uint64_t rem = o, base = 0;
+    for (int i = (int)p.n_kept - 1; i >= 0; --i) {
+        base += (rem % p.kept_dims[i]) * p.kept_strides[i];
+        rem /= p.kept_dims[i];
+    }
+    const bool narrow = p.dtype != HOLO_DTYPE_F32;
+    float acc = reduce_init(p.kind);
+    if (narrow) acc = holo::widen16(holo::narrow16(acc, p.dtype), p.dtype);
+    uint32_t coord[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint64_t off = base;
+    for (uint64_t r = 0; r < p.reduced_count; ++r) {
+        acc = reduce_fold(p.kind, acc, holo::load_float(in, off, p.dtype));
+        if (narrow) acc = holo::widen16(holo::narrow16(acc, p.dtype), p.dtype);
+        for (int a = (int)p.n_red - 1; a >= 0; --a) {   // odometer over the reduced axes, rightmost fastest
+            off += p.red_strides[a];
+            if (++coord[a] < p.red_dims[a]) break;
+            off -= p.red_strides[a] * p.red_dims[a];
+            coord[a] = 0;
+        }
+    }
+    if (p.mean) {
+        acc = __fmul_rn(acc, __fdiv_rn(1.0f, (float)p.reduced_count));
+    }
+    holo::store_float(out, o, acc, p.dtype);
+}
+
+// Full f32 reduction to one cell (sum, min, max): one CTA, tree order (the CPU folds in SIMD chunks here,
+// so the sum agrees to rounding; min and max are order-independent).
+__global__ void reduce_all_f32_kernel(const float* __restrict__ in, float* __restrict__ out, uint64_t n, int kind, int mean) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    __shared__ float s_part[32];
+    float acc = reduce_init(kind);
+    for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) acc = reduce_fold(kind, acc, in[i]);
+    for (int o = 16; o > 0; o >>= 1) acc = reduce_fold(kind, acc, __shfl_xor_sync(0xffffffffu, acc, o));
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = s_part[0];
+        for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) t = reduce_fold(kind, t, s_part[w]);
+        out[0] = mean ? __fdiv_rn(t, (float)n) : t;
+    }
+}
+
 // expand_float and broadcast_binary_float (cpu/float_kernels.rs:3405-3444, :3250-3397): every output element
 // reads the small operand at the row-major index built from its coordinates with stride 0 on the
 // broadcast axes. op < 0: a plain copy of `es` bytes (Expand); otherwise one f32 operation on the
@@ -672,6 +736,37 @@ int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* resi
                                      (const uint4*)gamma, (uint4*)out, feature, eps, (int)dtype));
     } else {
         HOLO_CUDA(holo_launch_kernel(ctx, rms_norm_kernel, dim3(batch), dim3(256), 0, 1, x, residual, gamma, out, feature, eps, (int)dtype));
+    }
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_reduce(holo_b200_ctx* ctx, const void* in, void* out, uint32_t rank, const uint32_t* dims, uint32_t axes_mask,
+                           uint64_t n, int kind, int mean, uint8_t dtype) {
+    ReduceParams p{};
+    p.kind = kind, p.mean = mean, p.dtype = dtype;
+    const bool full = rank == 0 || axes_mask == 0;
+    uint64_t stride = 1;
+    uint64_t strides[8];
+    for (int i = (int)rank - 1; i >= 0; --i) {
+        strides[i] = stride;
+        stride *= dims[i];
+    }
+    p.out_count = 1, p.reduced_count = rank == 0 ? n : 1;
+    for (uint32_t i = 0; i < rank; ++i) {
+        if (full || ((axes_mask >> i) & 1u)) {
+            p.red_dims[p.n_red] = dims[i], p.red_strides[p.n_red] = strides[i], ++p.n_red;
+            p.reduced_count *= dims[i];
+        } else {
+            p.kept_dims[p.n_kept] = dims[i], p.kept_strides[p.n_kept] = strides[i], ++p.n_kept;
+            p.out_count *= dims[i];
+        }
+    }
+    if (rank == 0) p.red_dims[0] = (uint32_t)n, p.red_strides[0] = 1, p.n_red = 1;
+    if (p.out_count == 1 && dtype == HOLO_DTYPE_F32 && kind != 1) {
+        HOLO_CUDA(holo_launch_kernel(ctx, reduce_all_f32_kernel, dim3(1), dim3(1024), 0, 1, (const float*)in, (float*)out, n, kind, mean));
+    } else {
+        HOLO_CUDA(holo_launch_kernel(ctx, reduce_cells_kernel, dim3((uint32_t)((p.out_count + 127) / 128)), dim3(128), 0, 1, in, out, p));
     }
     LAUNCH_CHECK(ctx);
     return HOLO_OK;

@@ -94,6 +94,13 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
             for (uint32_t i = 0; i < c.rank && i < 8; ++i) b.u32(c.dims[i]).u8(c.perm[i]);
             return true;
         }
+        case HOLO_K_REDUCE_SUM: case HOLO_K_REDUCE_MEAN: case HOLO_K_REDUCE_PROD: case HOLO_K_REDUCE_MIN: case HOLO_K_REDUCE_MAX: {
+            const HoloReduceCall& c = u.reduce;
+            sig->opcode = (uint16_t)(call.kind - 1);   // ReduceSum..ReduceMax are opcodes 54..58 (kernel_call.rs:1380-1384)
+            b.u64(c.element_count).u8(c.rank).u32(c.axes_mask).u8(c.keepdims ? 1 : 0).u8(c.dtype);
+            for (uint32_t i = 0; i < c.rank && i < 8; ++i) b.u32(c.dims[i]);
+            return true;
+        }
         case HOLO_K_EXPAND: {
             const HoloExpandCall& c = u.expand;
             sig->opcode = 71;
@@ -205,6 +212,8 @@ bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* input
         case HOLO_K_RESHAPE: case HOLO_K_SLICE: in(u.layout.input); *output = u.layout.output.slot; return true;
         case HOLO_K_TRANSPOSE: in(u.transpose.input); *output = u.transpose.output.slot; return true;
         case HOLO_K_SOFTMAX: in(u.softmax.input); *output = u.softmax.output.slot; return true;
+        case HOLO_K_REDUCE_SUM: case HOLO_K_REDUCE_MEAN: case HOLO_K_REDUCE_PROD: case HOLO_K_REDUCE_MIN: case HOLO_K_REDUCE_MAX:
+            in(u.reduce.input); *output = u.reduce.output.slot; return true;
         case HOLO_K_EXPAND: in(u.expand.input); *output = u.expand.output.slot; return true;
         case HOLO_K_BROADCAST_BINARY: in(u.broadcast_binary.small); in(u.broadcast_binary.other); *output = u.broadcast_binary.output.slot; return true;
         case HOLO_K_ROTARY: in(u.rope.x); in(u.rope.cos); in(u.rope.sin); *output = u.rope.output.slot; return true;

@@ -62,6 +62,10 @@ def encode_call(call):
     if k == kc.K_CAST:
         c = u.cast
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<QBB", c.element_count, c.src_dtype, c.dst_dtype)
+    if k in (kc.K_REDUCE_SUM, kc.K_REDUCE_MEAN, kc.K_REDUCE_PROD, kc.K_REDUCE_MIN, kc.K_REDUCE_MAX):
+        c = u.reduce
+        return out + _buf(c.input) + _buf(c.output) + struct.pack("<QBIBB", c.element_count, c.rank, c.axes_mask, c.keepdims, c.dtype) + struct.pack(
+            "<%dI" % c.rank, *list(c.dims)[:c.rank])
     if k == kc.K_EXPAND:
         c = u.expand
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<B8I8IB", c.rank, *c.in_dims, *c.out_dims, c.dtype)

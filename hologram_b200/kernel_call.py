@@ -22,6 +22,7 @@ K_SIGMOID, K_TANH, K_GELU, K_SILU, K_EXP, K_ERF = 12, 13, 14, 15, 18, 32
 K_MATMUL, K_RMS_NORM, K_RESHAPE, K_ROTARY = 46, 51, 60, 75
 K_LAYER_NORM, K_EXPAND, K_BROADCAST_BINARY = 50, 72, 112
 BROADCAST_ADD, BROADCAST_SUB, BROADCAST_MUL = 0, 1, 2
+K_REDUCE_SUM, K_REDUCE_MEAN, K_REDUCE_PROD, K_REDUCE_MIN, K_REDUCE_MAX = 55, 56, 57, 58, 59
 K_ADD_RMS_NORM, K_TRANSPOSE, K_CONCAT, K_SLICE, K_SOFTMAX = 54, 61, 62, 63, 64
 K_DECODE_ATTENTION = 119
 K_MATMUL_DEQUANT = 116
@@ -108,6 +109,23 @@ class LayoutCall(C.Structure):
 
 class SoftmaxCall(C.Structure):
     _fields_ = [("input", BufferRef), ("output", BufferRef), ("batch", C.c_uint32), ("feature", C.c_uint32), ("dtype", C.c_uint8)]
+
+
+class ReduceCall(C.Structure):
+    """kernel_call.rs:461-477: fold the axes set in axes_mask (0 = all); keepdims layout."""
+    _fields_ = [("input", BufferRef), ("output", BufferRef), ("element_count", C.c_uint64), ("rank", C.c_uint8),
+                ("dims", C.c_uint32 * 8), ("axes_mask", C.c_uint32), ("keepdims", C.c_uint8), ("dtype", C.c_uint8)]
+
+    @classmethod
+    def make(cls, inp, out, dims, axes_mask, dtype, keepdims=True):
+        c = cls()
+        c.input, c.output, c.rank, c.axes_mask, c.keepdims, c.dtype = inp, out, len(dims), axes_mask, int(keepdims), dtype
+        n = 1
+        for i, d in enumerate(dims):
+            c.dims[i] = d
+            n *= d
+        c.element_count = n
+        return c
 
 
 class ExpandCall(C.Structure):
@@ -209,7 +227,7 @@ class _Payload(C.Union):
     _fields_ = [("unary", UnaryCall), ("binary", BinaryCall), ("matmul", MatMulCall),
                 ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("matmul_dequant", MatMulDequantCall), ("norm", NormCall),
                 ("rope", RoPECall), ("gather", GatherCall), ("cast", CastCall), ("layout", LayoutCall),
-                ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("expand", ExpandCall), ("broadcast_binary", BroadcastBinaryCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
+                ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("expand", ExpandCall), ("reduce", ReduceCall), ("broadcast_binary", BroadcastBinaryCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
                 ("decode_attention", DecodeAttentionCall),
                 ("decode_attention_valid", DecodeAttentionValidCall), ("quantize_rows_i8", QuantizeRowsI8Call),
                 ("decode_attention_valid_q8", DecodeAttentionValidQ8Call), ("all_reduce", AllReduceCall),
@@ -265,6 +283,16 @@ class KernelCall(C.Structure):
     @classmethod
     def Expand(cls, c): return cls.of(K_EXPAND, c)
     @classmethod
+    def ReduceSum(cls, c): return cls.of(K_REDUCE_SUM, c)
+    @classmethod
+    def ReduceMean(cls, c): return cls.of(K_REDUCE_MEAN, c)
+    @classmethod
+    def ReduceProd(cls, c): return cls.of(K_REDUCE_PROD, c)
+    @classmethod
+    def ReduceMin(cls, c): return cls.of(K_REDUCE_MIN, c)
+    @classmethod
+    def ReduceMax(cls, c): return cls.of(K_REDUCE_MAX, c)
+    @classmethod
     def BroadcastBinary(cls, c): return cls.of(K_BROADCAST_BINARY, c)
     @classmethod
     def Transpose(cls, c): return cls.of(K_TRANSPOSE, c)
@@ -301,7 +329,7 @@ class KernelCall(C.Structure):
 KernelCall._FIELD = {
     UnaryCall: "unary", BinaryCall: "binary", MatMulCall: "matmul", MatMulActivationCall: "matmul_activation",
     MatMulAddCall: "matmul_add", MatMulDequantCall: "matmul_dequant", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
-    LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", ExpandCall: "expand", BroadcastBinaryCall: "broadcast_binary", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
+    LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", ExpandCall: "expand", ReduceCall: "reduce", BroadcastBinaryCall: "broadcast_binary", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
     DecodeAttentionCall: "decode_attention", DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
     DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce", RopeQuantizeCall: "rope_quantize",
 }

@@ -76,6 +76,11 @@ extern "C" {
 #define HOLO_K_LAYER_NORM 50
 #define HOLO_K_RMS_NORM 51
 #define HOLO_K_ADD_RMS_NORM 54
+#define HOLO_K_REDUCE_SUM 55
+#define HOLO_K_REDUCE_MEAN 56
+#define HOLO_K_REDUCE_PROD 57
+#define HOLO_K_REDUCE_MIN 58
+#define HOLO_K_REDUCE_MAX 59
 #define HOLO_K_RESHAPE 60
 #define HOLO_K_TRANSPOSE 61
 #define HOLO_K_CONCAT 62
@@ -180,6 +185,19 @@ typedef struct HoloSoftmaxCall {
     uint32_t batch, feature;
     uint8_t dtype;
 } HoloSoftmaxCall;
+
+/* ReduceCall (kernel_call.rs:461-477): fold the axes whose bit is set in axes_mask (0 or rank 0 = all) of a
+ * row-major tensor `dims[..rank]`; the output is the keepdims layout (reduced axes collapsed to 1). Every
+ * output cell folds its inputs in linear input order, as the CPU loop does; only the full f32 reduction to
+ * one cell is order-relaxed there (chunked SIMD), and here. */
+typedef struct HoloReduceCall {
+    HoloBufferRef input, output;
+    uint64_t element_count;
+    uint8_t rank;
+    uint32_t dims[8];
+    uint32_t axes_mask;
+    uint8_t keepdims, dtype;
+} HoloReduceCall;
 
 /* ExpandCall (kernel_call.rs:539-547): replicate `input` to out_dims; an axis with in_dims[i] == 1 reads
  * index 0, every other axis maps 1:1 (in_dims[i] == out_dims[i]); rank <= 8; any dtype. */
@@ -332,6 +350,7 @@ typedef struct HoloKernelCall {
         HoloTransposeCall transpose;
         HoloSoftmaxCall softmax;
         HoloExpandCall expand;
+        HoloReduceCall reduce;
         HoloBroadcastBinaryCall broadcast_binary;
         HoloDequantizeCall dequantize;
         HoloKvCacheWriteCall kv_cache_write;

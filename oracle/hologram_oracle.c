@@ -438,6 +438,47 @@ int holo_or_rms_norm(const void* x, const void* gamma, void* out, uint32_t batch
     return 0;
 }
 
+/* ---- Reduce: cpu/float_kernels.rs:1901-2022 with ReducePlan :2024-2099, the generic loop (:1995-2020): every
+ * output cell starts at the fold identity and takes its inputs in linear input order, the running value
+ * kept in the output buffer (so narrowed each step for a 16-bit dtype). kind 0 sum, 1 prod, 2 min, 3 max.
+ * (The f32 full reduction of the reference folds in SIMD chunks instead: same value up to rounding of a sum.) */
+int holo_or_reduce(const void* in, void* out, uint64_t n, uint32_t rank, const uint32_t* dims, uint32_t axes_mask,
+                   int kind, int mean, int dtype) {
+    if (rank > 8) return -3;
+    size_t in_dims[8], out_dims[8], out_stride[8];
+    int reduced[8];
+    size_t out_count = 1, reduced_count = 1;
+    int full = rank == 0 || axes_mask == 0;
+    for (uint32_t i = 0; i < rank; ++i) {
+        in_dims[i] = dims[i];
+        reduced[i] = full || ((axes_mask >> i) & 1u);
+        out_dims[i] = 1;
+        if (reduced[i]) reduced_count *= in_dims[i];
+        else { out_dims[i] = in_dims[i]; out_count *= in_dims[i]; }
+    }
+    if (rank == 0) reduced_count = n;
+    size_t s = 1;
+    for (int i = (int)rank - 1; i >= 0; --i) { out_stride[i] = s; s *= out_dims[i]; }
+    float init = kind == 0 ? 0.0f : kind == 1 ? 1.0f : kind == 2 ? INFINITY : -INFINITY;
+    for (size_t o = 0; o < out_count; ++o) write_float(out, o, init, dtype);
+    for (size_t i = 0; i < n; ++i) {
+        size_t rem = i, oo = 0;
+        for (int a = (int)rank - 1; a >= 0; --a) {
+            size_t c = rem % in_dims[a];
+            rem /= in_dims[a];
+            if (!reduced[a]) oo += c * out_stride[a];
+        }
+        float acc = read_float(out, oo, dtype), v = read_float(in, i, dtype);
+        acc = kind == 0 ? acc + v : kind == 1 ? acc * v : kind == 2 ? fminf(acc, v) : fmaxf(acc, v);
+        write_float(out, oo, acc, dtype);
+    }
+    if (mean) {
+        float inv = 1.0f / (float)reduced_count;
+        for (size_t o = 0; o < out_count; ++o) write_float(out, o, read_float(out, o, dtype) * inv, dtype);
+    }
+    return 0;
+}
+
 /* ---- Expand and BroadcastBinary: cpu/float_kernels.rs:3405-3444 and :3250-3397. The small operand is read
  * at the row-major index of the output coordinates with stride 0 on its size-1 axes. other == NULL:
  * a copy of es bytes (Expand); else op 0 add, 1 sub, 2 mul in f32, operands swapped when !small_is_lhs. */

@@ -39,6 +39,7 @@ def _load(path):
         "holo_or_binary": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_rms_norm": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
         "holo_or_add_rms_norm": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
+        "holo_or_reduce": (C.c_int, [_c, _c, C.c_uint64, C.c_uint32, _c, C.c_uint32, C.c_int, C.c_int, C.c_int]),
         "holo_or_broadcast": (C.c_int, [_c, _c, _c, C.c_uint32, _c, _c, C.c_uint32, C.c_int, C.c_int, C.c_int]),
         "holo_or_layer_norm": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
         "holo_or_softmax": (C.c_int, [_c, _c, C.c_uint32, C.c_uint32, C.c_int]),
@@ -187,6 +188,21 @@ def add_rms_norm(x, residual, gamma, batch, feature, eps_bits, dtype):
     r = None if residual is None else np.ascontiguousarray(residual)
     g = None if gamma is None else np.ascontiguousarray(gamma)
     rc = lib.holo_or_add_rms_norm(_p(x), _p(r), _p(g), _p(out), batch, feature, eps_bits, dtype)
+    assert rc == 0, rc
+    return out
+
+
+def reduce(x, dims, axes_mask, kind, mean, dtype):
+    """kind 0 sum, 1 prod, 2 min, 3 max; returns the keepdims-layout output cells."""
+    x = np.ascontiguousarray(x)
+    d = np.asarray(dims, dtype=np.uint32)
+    cells = 1
+    if len(dims) and axes_mask:
+        for i, v in enumerate(dims):
+            if not (axes_mask >> i) & 1:
+                cells *= v
+    out = np.zeros(cells, dtype=x.dtype)
+    rc = lib.holo_or_reduce(_p(x), _p(out), x.size, len(dims), _p(d), axes_mask, kind, int(mean), dtype)
     assert rc == 0, rc
     return out
 

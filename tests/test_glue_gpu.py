@@ -367,3 +367,36 @@ def test_expand_and_broadcast_binary(backend):
     assert e.value.variant == "UnsupportedOp"
     with pytest.raises(hb.BackendError):
         backend.dispatch(kc.KernelCall.BroadcastBinary(kc.BroadcastBinaryCall.make(kc.rb(0), kc.rb(1), kc.rb(2), (1, 3), (2, 3), 7, True, BF)), ws)
+
+
+def test_reduce_variants(backend):
+    # reduce_float (cpu/float_kernels.rs:1901-2022): each cell folds in linear input order -> bit-exact, also with
+    # the per-step narrowing of a 16-bit dtype; only the f32 full sum is order-relaxed (on the CPU too)
+    rng = np.random.default_rng(59)
+    ctors = ((kc.KernelCall.ReduceSum, 0, False), (kc.KernelCall.ReduceMean, 0, True), (kc.KernelCall.ReduceProd, 1, False),
+             (kc.KernelCall.ReduceMin, 2, False), (kc.KernelCall.ReduceMax, 3, False))
+    for dims, mask in (((64, 4096), 0b10), ((3, 4, 5, 2), 0b1010), ((7, 33, 5), 0b001), ((6, 50), 0b01), ((1000,), 0), ((4, 9), 0b11)):
+        n = int(np.prod(dims))
+        for dt in (kc.DTYPE_F32, BF):
+            x = (rng.standard_normal(n) * 0.7 + 1.0).astype(np.float32)
+            xin = x if dt == kc.DTYPE_F32 else orc.f32_to_bf16_rne(x)
+            ws = hb.DeviceWorkspace(backend, 2)
+            ws.put(0, xin)
+            ws.alloc(1, xin.nbytes)
+            for ctor, kind, mean in ctors:
+                backend.dispatch(ctor(kc.ReduceCall.make(kc.rb(0), kc.rb(1), dims, mask, dt)), ws)
+                want = orc.reduce(xin, dims, mask, kind, mean, dt)
+                got = ws.read(1, want.nbytes, want.dtype)
+                if dt == kc.DTYPE_F32 and want.size == 1 and kind == 0:
+                    assert np.allclose(got, want, rtol=1e-5)
+                else:
+                    assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (dims, mask, kind, dt)
+            ws.close()
+    ws = hb.DeviceWorkspace(backend, 2)
+    ws.alloc(0, 1024)
+    ws.alloc(1, 1024)
+    bad = kc.ReduceCall.make(kc.rb(0), kc.rb(1), (4, 4), 0b01, BF)
+    bad.element_count = 17
+    with pytest.raises(hb.BackendError) as e:
+        backend.dispatch(kc.KernelCall.ReduceSum(bad), ws)
+    assert e.value.variant == "UnsupportedOp"

@@ -321,6 +321,24 @@ def test_broadcast_restatement_equals_numpy_broadcasting():
             assert np.array_equal(got.view(np.uint32), want.astype(np.float32).view(np.uint32))
 
 
+def test_reduce_restatement_equals_numpy_on_exact_cases():
+    # reduce_float (cpu/float_kernels.rs:1901-2022): min / max are order-free, small-integer sums and
+    # products are exact in f32, so numpy gives the expected bits; keepdims layout = reduced axes dropped
+    rng = np.random.default_rng(55)
+    dims = (3, 4, 5, 2)
+    x = rng.integers(-4, 5, size=int(np.prod(dims))).astype(np.float32)
+    x4 = x.reshape(dims)
+    for mask, axes in ((0b0010, (1,)), (0b1010, (1, 3)), (0b0101, (0, 2)), (0, (0, 1, 2, 3)), (0b1111, (0, 1, 2, 3))):
+        for kind, fn in ((0, np.sum), (2, np.min), (3, np.max)):
+            got = orc.reduce(x, dims, mask, kind, False, kc.DTYPE_F32)
+            assert np.array_equal(got, fn(x4, axis=axes).astype(np.float32).reshape(-1))
+        got = orc.reduce(x, dims, mask, 0, True, kc.DTYPE_F32)
+        cnt = int(np.prod([dims[a] for a in axes]))
+        assert np.array_equal(got, (np.sum(x4, axis=axes).astype(np.float32) * (np.float32(1.0) / np.float32(cnt))).reshape(-1))
+    p = rng.integers(1, 3, size=24).astype(np.float32)
+    assert np.array_equal(orc.reduce(p, (2, 3, 4), 0b010, 1, False, kc.DTYPE_F32), np.prod(p.reshape(2, 3, 4), axis=1).reshape(-1))
+
+
 def test_mask_form_restatement_equals_scalar_form_bitwise():
     # the reference pins that a realized-length mask reproduces DecodeAttentionValid bit for bit
     # (crates/hologram-compute/tests/decode_attention_valid.rs:226-282); all-erased row = zeros
