@@ -183,6 +183,9 @@ matmul_w8a8_omajor_kernel(const float* __restrict__ a, const int8_t* __restrict_
 // two that take tiles in turn (so one group's reduction and write-back overlap the others'
 // products); inside a group the warps split the tile's k range. Taken when k is a multiple of 16,
 // at most QS_STAGE_BYTES, and the weight is 16-byte aligned.
+// Measured on B200: dp4a issues at about 16 lanes per clock per SM, so from four activation rows on
+// the product is bound by dp4a, not by HBM; the same loop on mma.sync.m16n8k32.s8 (weights as the B
+// operand) was slower at every row count.
 constexpr int QS_GROUPS = 4;
 constexpr int QS_GROUP_WARPS = 2;
 constexpr int QS_WARPS = QS_GROUPS * QS_GROUP_WARPS;   // product warps; warp QS_WARPS is the copy warp
@@ -410,58 +413,32 @@ matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict_
             *s_abort = 1;
             atomicOr(status, 2u);
         }
-        // U positions of the k range at a time, each into its own accumulators: with one or two rows a
-        // single chain of dependent dp4a per column would leave the loads of the next position waiting
-        constexpr int U = 1;
-        int accu[U][V];
+        int acc[V];
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-            for (int j = 0; j < V; ++j) accu[u][j] = 0;
+        for (int j = 0; j < V; ++j) acc[j] = 0;
         if (ok) {
             const int4* tile = reinterpret_cast<const int4*>(ring + (size_t)s * QS_STAGE_BYTES);
-            constexpr uint32_t GL = QS_GROUP_WARPS * 32;
-            for (uint32_t v0 = gwarp * 32 + lane; v0 < nvec; v0 += U * GL) {
-                int4 qv[U][ROWS];
-                int4 w[U][QS_MAX_COLS];
+#pragma unroll 2
+            for (uint32_t v = gwarp * 32 + lane; v < nvec; v += QS_GROUP_WARPS * 32) {
+                int4 qv[ROWS];
 #pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const uint32_t v = v0 + u * GL;
-                    if (v < nvec) {
+                for (int r = 0; r < ROWS; ++r) qv[r] = *reinterpret_cast<const int4*>(s_q + (size_t)r * k + (size_t)v * 16);
 #pragma unroll
-                        for (int r = 0; r < ROWS; ++r) qv[u][r] = *reinterpret_cast<const int4*>(s_q + (size_t)r * k + (size_t)v * 16);
+                for (int c = 0; c < QS_MAX_COLS; ++c) {
+                    if ((uint32_t)c < cols) {
+                        const int4 w = tile[(size_t)c * nvec + v];
 #pragma unroll
-                        for (int c = 0; c < QS_MAX_COLS; ++c)
-                            if ((uint32_t)c < cols) w[u][c] = tile[(size_t)c * nvec + v];
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    if (v0 + u * GL < nvec) {
-#pragma unroll
-                        for (int c = 0; c < QS_MAX_COLS; ++c) {
-                            if ((uint32_t)c < cols) {
-#pragma unroll
-                                for (int r = 0; r < ROWS; ++r) {
-                                    int x = accu[u][c * ROWS + r];
-                                    x = __dp4a(w[u][c].x, qv[u][r].x, x);
-                                    x = __dp4a(w[u][c].y, qv[u][r].y, x);
-                                    x = __dp4a(w[u][c].z, qv[u][r].z, x);
-                                    x = __dp4a(w[u][c].w, qv[u][r].w, x);
-                                    accu[u][c * ROWS + r] = x;
-                                }
-                            }
+                        for (int r = 0; r < ROWS; ++r) {
+                            int x = acc[c * ROWS + r];
+                            x = __dp4a(w.x, qv[r].x, x);
+                            x = __dp4a(w.y, qv[r].y, x);
+                            x = __dp4a(w.z, qv[r].z, x);
+                            x = __dp4a(w.w, qv[r].w, x);
+                            acc[c * ROWS + r] = x;
                         }
                     }
                 }
             }
-        }
-        int acc[V];
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-            acc[j] = accu[0][j];
-#pragma unroll
-            for (int u = 1; u < U; ++u) acc[j] += accu[u][j];
         }
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_empty + 8 * s) : "memory");   // the tile has been consumed
