@@ -307,6 +307,32 @@ int32_t do_binary(holo_b200_ctx* ctx, const HoloBinaryCall& c, int op, holo_b200
     return holo_launch_binary(ctx, op, a, b, out, c.element_count, c.dtype);
 }
 
+// unary_float / binary_float with an exact IEEE operation (cpu/float_kernels.rs:190-233, :236-296)
+int32_t do_elementwise(holo_b200_ctx* ctx, const HoloKernelCall* call, holo_b200_workspace* ws) {
+    const bool unary = holo_is_exact_unary(call->kind);
+    const uint8_t dtype = unary ? call->u.unary.dtype : call->u.binary.dtype;
+    const uint64_t n = unary ? call->u.unary.element_count : call->u.binary.element_count;
+    if (dtype == HOLO_DTYPE_F64)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: f64 is not a supported compute dtype (hologram computes in f16/bf16/f32)");
+    if (!holo_is_compute_float(dtype))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: the integer-ring form of variant %u is not served by this backend (dtype %u)", call->kind, dtype);
+    if (n == 0) return HOLO_OK;
+    const uint64_t bytes = n * holo_dtype_size(dtype);
+    uint8_t *a, *b = nullptr, *out;
+    if (unary) {
+        HOLO_TRY(holo_resolve(ws, call->u.unary.output, 0, &out, nullptr));
+        HOLO_TRY(holo_resolve(ws, call->u.unary.input, bytes, &a, nullptr));
+        HOLO_TRY(holo_resolve(ws, call->u.unary.output, bytes, &out, nullptr));
+        HOLO_TRY(check_disjoint({out, bytes}, call->u.unary.output.slot, {{a, bytes}}));
+    } else {
+        HOLO_TRY(holo_resolve(ws, call->u.binary.a, bytes, &a, nullptr));
+        HOLO_TRY(holo_resolve(ws, call->u.binary.b, bytes, &b, nullptr));
+        HOLO_TRY(holo_resolve(ws, call->u.binary.output, bytes, &out, nullptr));
+        HOLO_TRY(check_disjoint({out, bytes}, call->u.binary.a.slot, {{a, bytes}, {b, bytes}}));
+    }
+    return holo_launch_elementwise(ctx, (int)call->kind, a, b, out, n, dtype);
+}
+
 // matmul_float and its fused epilogues (cpu/float_kernels.rs:298-399, 822-891)
 int32_t do_matmul(holo_b200_ctx* ctx, const HoloMatMulCall& c, uint8_t act, const HoloBufferRef* residual,
                   holo_b200_workspace* ws) {
@@ -817,6 +843,7 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         case HOLO_K_ALL_REDUCE: return do_all_reduce(ctx, call->u.all_reduce, ws);
         case HOLO_K_ROPE_QUANTIZE_ROWS_I8: return do_rope_quantize(ctx, call->u.rope_quantize, ws);
         default:
+            if (holo_is_exact_unary(call->kind) || holo_is_exact_binary(call->kind)) return do_elementwise(ctx, call, ws);
             return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: KernelCall variant %u is not served by the B200 backend (no CPU fallback)", call->kind);
     }
 }
@@ -834,6 +861,16 @@ namespace {
 }  // namespace
 
 bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
+    if (holo_is_exact_unary(c->kind)) {
+        l->in(&c->u.unary.input);
+        l->out(&c->u.unary.output, c->u.unary.element_count * holo_dtype_size(c->u.unary.dtype));
+        return true;
+    }
+    if (holo_is_exact_binary(c->kind)) {
+        l->in(&c->u.binary.a); l->in(&c->u.binary.b);
+        l->out(&c->u.binary.output, c->u.binary.element_count * holo_dtype_size(c->u.binary.dtype));
+        return true;
+    }
     switch (c->kind) {
         case HOLO_K_SIGMOID: case HOLO_K_TANH: case HOLO_K_GELU: case HOLO_K_SILU: case HOLO_K_EXP: case HOLO_K_ERF:
             l->in(&c->u.unary.input);

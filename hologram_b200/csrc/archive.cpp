@@ -63,6 +63,12 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
     memset(out, 0, sizeof *out);
     const uint16_t d = r.u16();
     out->kind = d;
+    if (holo_is_exact_unary(d) || holo_is_exact_binary(d)) {
+        if (holo_is_exact_unary(d)) get_unary(r, out->u.unary);
+        else get_binary(r, out->u.binary);
+        if (!r.ok) return holo_fail(HOLO_ERR_INIT, "backend init failed: truncated KernelCalls section");
+        return HOLO_OK;
+    }
     switch (d) {
         case HOLO_K_SIGMOID: case HOLO_K_TANH: case HOLO_K_GELU: case HOLO_K_SILU: case HOLO_K_EXP: case HOLO_K_ERF:
             get_unary(r, out->u.unary); break;
@@ -88,7 +94,7 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             HoloReduceCall& c = out->u.reduce;
             c.input = r.buf(); c.output = r.buf(); c.element_count = r.u64(); c.rank = r.u8(); c.axes_mask = r.u32();
             c.keepdims = r.u8(); c.dtype = r.u8();
-            if (c.rank > 8) return false;
+            if (c.rank > 8) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: rank must be <= 8");
             for (uint32_t i = 0; i < c.rank; ++i) c.dims[i] = r.u32();
             break;
         }
@@ -105,7 +111,7 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             c.small = r.buf(); c.other = r.buf(); c.output = r.buf();
             c.rank = r.u8(); c.op = r.u8(); c.small_is_lhs = r.u8(); c.dtype = r.u8();
             for (uint32_t i = 0; i < c.rank && i < 8; ++i) { c.in_dims[i] = r.u32(); c.out_dims[i] = r.u32(); }
-            if (c.rank > 8) return false;
+            if (c.rank > 8) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: rank must be <= 8");
             break;
         }
         case HOLO_K_SOFTMAX: {

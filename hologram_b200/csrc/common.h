@@ -163,6 +163,15 @@ static inline cudaError_t holo_launch_kernel(holo_b200_ctx* ctx, void (*kernel)(
 int32_t holo_lut_table(holo_b200_ctx* ctx, uint8_t act, uint8_t dtype, const uint16_t** table);
 int32_t holo_launch_lut(holo_b200_ctx* ctx, const uint16_t* table, const uint16_t* in, uint16_t* out, uint64_t n);
 // glue.cu
+// the elementwise variants served as one exact IEEE operation per element (beyond Add / Mul and the LUT activations)
+inline bool holo_is_exact_unary(uint32_t k) {
+    return k == HOLO_K_NEG || k == HOLO_K_RELU || k == HOLO_K_SQRT || k == HOLO_K_RECIPROCAL || k == HOLO_K_CEIL || k == HOLO_K_FLOOR ||
+           k == HOLO_K_ROUND || k == HOLO_K_IS_NAN || k == HOLO_K_SIGN || k == HOLO_K_ABS;
+}
+inline bool holo_is_exact_binary(uint32_t k) {
+    return k == HOLO_K_SUB || k == HOLO_K_DIV || k == HOLO_K_MOD || (k >= HOLO_K_MIN && k <= HOLO_K_GREATER_OR_EQUAL);
+}
+int32_t holo_launch_elementwise(holo_b200_ctx* ctx, int tag, const void* a, const void* b, void* out, uint64_t n, uint8_t dtype);
 int32_t holo_launch_binary(holo_b200_ctx* ctx, int op, const void* a, const void* b, void* out, uint64_t n, uint8_t dtype);
 int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* residual, const void* gamma, void* out,
                              uint32_t batch, uint32_t feature, float eps, uint8_t dtype);

@@ -34,6 +34,20 @@ __global__ void binary_kernel(int op, const void* __restrict__ a, const void* __
     binary_body(op, a, b, out, n, dtype, blockIdx.x, gridDim.x);
 }
 
+// The exact elementwise forms beyond Add / Mul and the LUT activations (unary_float and binary_float,
+// cpu/float_kernels.rs:190-233, :236-296): widen, one IEEE operation, narrow; `tag` is the wire discriminant.
+__global__ void elementwise_kernel(int tag, const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ out,
+                                   uint64_t n, int dtype) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    const bool unary = holo::ew_is_unary(tag);
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float va = holo::load_float(a, i, dtype);
+        holo::store_float(out, i, unary ? holo::ew_unary(tag, va) : holo::ew_binary(tag, va, holo::load_float(b, i, dtype)), dtype);
+    }
+}
+
 // 16-bit fast path: eight elements per thread through 128-bit loads and stores.
 __device__ __forceinline__ void binary16_vec_body(int op, const uint4* __restrict__ a, const uint4* __restrict__ b,
                                                   uint4* __restrict__ out, uint64_t nvec, int dtype, uint32_t block, uint32_t nblocks) {
@@ -193,7 +207,7 @@ struct ReduceParams {
     int kind, mean, dtype;
 };
 __device__ __forceinline__ float reduce_fold(int kind, float a, float b) {
-    return kind == 0 ? __fadd_rn(a, b) : kind == 1 ? __fmul_rn(a, b) : kind == 2 ? fminf(a, b) : fmaxf(a, b);
+    return kind == 0 ? __fadd_rn(a, b) : kind == 1 ? __fmul_rn(a, b) : kind == 2 ? holo::min_ref(a, b) : holo::max_ref(a, b);
 }
 __device__ __forceinline__ float reduce_init(int kind) { return kind == 0 ? 0.0f : kind == 1 ? 1.0f : kind == 2 ? INFINITY : -INFINITY; }
 
@@ -721,6 +735,13 @@ int32_t holo_launch_binary(holo_b200_ctx* ctx, int op, const void* a, const void
     } else {
         HOLO_CUDA(holo_launch_kernel(ctx, binary_kernel, dim3(ew_blocks(n)), dim3(EW_THREADS), 0, 1, op, a, b, out, n, dtype));
     }
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_elementwise(holo_b200_ctx* ctx, int tag, const void* a, const void* b, void* out, uint64_t n, uint8_t dtype) {
+    if (n == 0) return HOLO_OK;
+    HOLO_CUDA(holo_launch_kernel(ctx, elementwise_kernel, dim3(ew_blocks(n)), dim3(EW_THREADS), 0, 1, tag, a, b, out, n, (int)dtype));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }

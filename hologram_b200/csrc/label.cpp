@@ -3,6 +3,7 @@
 #include <string.h>
 
 #include "blake3.h"
+#include "common.h"
 
 void holo_label_from_digest(const uint8_t digest[32], uint8_t out[HOLO_LABEL_BYTES]) {
     static const char HEX[] = "0123456789abcdef";
@@ -63,6 +64,19 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
     *sig = HoloOpSignature();
     Pb b{sig};
     const auto& u = call.u;
+    // the exact elementwise variants: opcode = wire discriminant - 1 (kernel_call.rs:1325-1368); Min, Max and
+    // Equal are commutative (:1302-1315)
+    if (holo_is_exact_unary(call.kind)) {
+        sig->opcode = (uint16_t)(call.kind - 1);
+        b.u64(u.unary.element_count).u16(u.unary.witt_bits).u8(u.unary.dtype);
+        return true;
+    }
+    if (holo_is_exact_binary(call.kind)) {
+        sig->opcode = (uint16_t)(call.kind - 1);
+        sig->commutative = call.kind == HOLO_K_MIN || call.kind == HOLO_K_MAX || call.kind == HOLO_K_EQUAL;
+        b.u64(u.binary.element_count).u16(u.binary.witt_bits).u8(u.binary.dtype);
+        return true;
+    }
     switch (call.kind) {
         // unary / binary: element_count u64, witt_bits u16, dtype u8 (p_unary / p_binary)
         case HOLO_K_SIGMOID: sig->opcode = 11; break;
@@ -186,6 +200,8 @@ bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* input
         if (present(r)) inputs->push_back(r.slot);
     };
     const auto& u = call.u;
+    if (holo_is_exact_unary(call.kind)) { in(u.unary.input); *output = u.unary.output.slot; return true; }
+    if (holo_is_exact_binary(call.kind)) { in(u.binary.a); in(u.binary.b); *output = u.binary.output.slot; return true; }
     switch (call.kind) {
         case HOLO_K_SIGMOID: case HOLO_K_TANH: case HOLO_K_GELU: case HOLO_K_SILU: case HOLO_K_EXP: case HOLO_K_ERF:
             in(u.unary.input); *output = u.unary.output.slot; return true;

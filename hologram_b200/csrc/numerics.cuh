@@ -136,4 +136,53 @@ __device__ __forceinline__ float lut_act_ref(int act, float x) {
     return y;
 }
 
+// Elementwise float forms that are exact IEEE operations (cpu/float_kernels.rs:3446-3500 unary, :3660-3733
+// binary), keyed by the call's wire discriminant. NaN results follow the x86-64 SSE convention the CPU
+// backend runs under (see lut_act_ref): an arithmetic result that is NaN is the first NaN operand
+// quieted, or the default NaN 0xFFC00000 for an invalid operation.
+__device__ __forceinline__ float quiet_nan(float x) { return __uint_as_float(__float_as_uint(x) | 0x00400000u); }
+__device__ __forceinline__ float nan_fix2(float y, float a, float b) {
+    if (y == y) return y;
+    return a != a ? quiet_nan(a) : b != b ? quiet_nan(b) : __uint_as_float(0xFFC00000u);
+}
+// f32::min / f32::max: the other operand when one is NaN; of two equal operands (+0 and -0) the first
+__device__ __forceinline__ float min_ref(float a, float b) { return a != a ? b : (b < a ? b : a); }
+__device__ __forceinline__ float max_ref(float a, float b) { return a != a ? b : (b > a ? b : a); }
+__device__ __forceinline__ bool ew_is_unary(int tag) {
+    return tag == 1 || tag == 11 || tag == 21 || tag == 22 || (tag >= 29 && tag <= 31) || (tag >= 33 && tag <= 35);
+}
+__device__ __forceinline__ float ew_unary(int tag, float x) {
+    switch (tag) {
+        case 1: return __uint_as_float(__float_as_uint(x) ^ 0x80000000u);                       // Neg
+        case 11: return max_ref(x, 0.0f);                                                       // Relu: x.max(0.0)
+        case 21: return nan_fix2(__fsqrt_rn(x), x, x);                                          // Sqrt
+        case 22: return nan_fix2(__fdiv_rn(1.0f, x), x, x);                                     // Reciprocal
+        case 29: return nan_fix2(ceilf(x), x, x);
+        case 30: return nan_fix2(floorf(x), x, x);
+        case 31: return nan_fix2(roundf(x), x, x);                                              // half away from zero
+        case 33: return x != x ? 1.0f : 0.0f;                                                   // IsNaN
+        case 34: return x > 0.0f ? 1.0f : x < 0.0f ? -1.0f : 0.0f;                              // Sign
+        default: return __uint_as_float(__float_as_uint(x) & 0x7fffffffu);                      // Abs
+    }
+}
+__device__ __forceinline__ float ew_binary(int tag, float a, float b) {
+    switch (tag) {
+        case 6: return nan_fix2(__fsub_rn(a, b), a, b);
+        case 36: return nan_fix2(__fdiv_rn(a, b), a, b);
+        case 38: {   // floored modulo: a - floor(a / b) * b, every step rounded
+            const float d = nan_fix2(__fdiv_rn(a, b), a, b);
+            const float f = nan_fix2(floorf(d), d, d);
+            const float m = nan_fix2(__fmul_rn(f, b), f, b);
+            return nan_fix2(__fsub_rn(a, m), a, m);
+        }
+        case 39: return min_ref(a, b);
+        case 40: return max_ref(a, b);
+        case 41: return a == b ? 1.0f : 0.0f;
+        case 42: return a < b ? 1.0f : 0.0f;
+        case 43: return a <= b ? 1.0f : 0.0f;
+        case 44: return a > b ? 1.0f : 0.0f;
+        default: return a >= b ? 1.0f : 0.0f;
+    }
+}
+
 }  // namespace holo

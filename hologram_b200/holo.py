@@ -33,9 +33,9 @@ def encode_call(call):
     """`u16 discriminant + payload` for one KernelCall (kernel_codec.rs encode_one)."""
     k, u = call.kind, call.u
     out = struct.pack("<H", k)
-    if k in (kc.K_SIGMOID, kc.K_TANH, kc.K_GELU, kc.K_SILU, kc.K_EXP, kc.K_ERF):
+    if k in (kc.K_SIGMOID, kc.K_TANH, kc.K_GELU, kc.K_SILU, kc.K_EXP, kc.K_ERF) + kc.EXACT_UNARY:
         return out + _unary(u.unary)
-    if k in (kc.K_ADD, kc.K_MUL, kc.K_CONCAT):
+    if k in (kc.K_ADD, kc.K_MUL, kc.K_CONCAT) + kc.EXACT_BINARY:
         return out + _binary(u.binary)
     if k == kc.K_MATMUL:
         return out + _matmul(u.matmul)

@@ -18,6 +18,11 @@ FUSED_RELU, FUSED_GELU, FUSED_SILU, FUSED_SIGMOID, FUSED_TANH, FUSED_EXP = 1, 2,
 
 # variant tags = archive wire discriminants (crates/hologram-archive/src/kernel_codec.rs:19-128)
 K_ADD, K_MUL = 5, 7
+# exact elementwise variants (one IEEE operation per element)
+K_NEG, K_RELU, K_SQRT, K_RECIPROCAL, K_CEIL, K_FLOOR, K_ROUND, K_IS_NAN, K_SIGN, K_ABS = 1, 11, 21, 22, 29, 30, 31, 33, 34, 35
+K_SUB, K_DIV, K_MOD, K_MIN, K_MAX, K_EQUAL, K_LESS, K_LESS_OR_EQUAL, K_GREATER, K_GREATER_OR_EQUAL = 6, 36, 38, 39, 40, 41, 42, 43, 44, 45
+EXACT_UNARY = (K_NEG, K_RELU, K_SQRT, K_RECIPROCAL, K_CEIL, K_FLOOR, K_ROUND, K_IS_NAN, K_SIGN, K_ABS)
+EXACT_BINARY = (K_SUB, K_DIV, K_MOD, K_MIN, K_MAX, K_EQUAL, K_LESS, K_LESS_OR_EQUAL, K_GREATER, K_GREATER_OR_EQUAL)
 K_SIGMOID, K_TANH, K_GELU, K_SILU, K_EXP, K_ERF = 12, 13, 14, 15, 18, 32
 K_MATMUL, K_RMS_NORM, K_RESHAPE, K_ROTARY = 46, 51, 60, 75
 K_LAYER_NORM, K_EXPAND, K_BROADCAST_BINARY = 50, 72, 112
@@ -246,6 +251,12 @@ class KernelCall(C.Structure):
         kc.kind = kind
         setattr(kc.u, cls._FIELD[type(payload)], payload)
         return kc
+
+    @classmethod
+    def Elementwise(cls, kind, c):
+        """Any of EXACT_UNARY (UnaryCall) or EXACT_BINARY (BinaryCall), by wire discriminant."""
+        assert kind in EXACT_UNARY + EXACT_BINARY
+        return cls.of(kind, c)
 
     # constructors named after the reference variants
     @classmethod

@@ -64,14 +64,34 @@ extern "C" {
 /* ---- KernelCall variant tags. Values are the archive wire discriminants
  * (crates/hologram-archive/src/kernel_codec.rs:19-128) so a decoded .holo call list maps
  * 1:1. Tags >= 0x8000 are extensions with no reference counterpart (documented below). */
+#define HOLO_K_NEG 1
 #define HOLO_K_ADD 5
+#define HOLO_K_SUB 6
 #define HOLO_K_MUL 7
+#define HOLO_K_RELU 11
 #define HOLO_K_SIGMOID 12
 #define HOLO_K_TANH 13
 #define HOLO_K_GELU 14
 #define HOLO_K_SILU 15
 #define HOLO_K_EXP 18
+#define HOLO_K_SQRT 21
+#define HOLO_K_RECIPROCAL 22
+#define HOLO_K_CEIL 29
+#define HOLO_K_FLOOR 30
+#define HOLO_K_ROUND 31
 #define HOLO_K_ERF 32
+#define HOLO_K_IS_NAN 33
+#define HOLO_K_SIGN 34
+#define HOLO_K_ABS 35
+#define HOLO_K_DIV 36
+#define HOLO_K_MOD 38
+#define HOLO_K_MIN 39
+#define HOLO_K_MAX 40
+#define HOLO_K_EQUAL 41
+#define HOLO_K_LESS 42
+#define HOLO_K_LESS_OR_EQUAL 43
+#define HOLO_K_GREATER 44
+#define HOLO_K_GREATER_OR_EQUAL 45
 #define HOLO_K_MATMUL 46
 #define HOLO_K_LAYER_NORM 50
 #define HOLO_K_RMS_NORM 51

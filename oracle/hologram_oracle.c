@@ -412,6 +412,42 @@ int holo_or_binary(int op, const void* a, const void* b, void* out, uint64_t n, 
     return 0;
 }
 
+/* ---- the exact elementwise forms, keyed by wire discriminant: unary cpu/float_kernels.rs:3446-3500 through
+ * unary_float (:190-233), binary :3660-3733 through binary_float (:236-296). f32::min / f32::max return the
+ * other operand when one is NaN and the first of two equal operands. */
+static float min_ref(float a, float b) { return a != a ? b : (b < a ? b : a); }
+static float max_ref(float a, float b) { return a != a ? b : (b > a ? b : a); }
+int holo_or_elementwise(int tag, const void* a, const void* b, void* out, uint64_t n, int dtype) {
+    for (uint64_t i = 0; i < n; ++i) {
+        float x = read_float(a, i, dtype), y = b ? read_float(b, i, dtype) : 0.0f, r;
+        switch (tag) {
+            case 1: r = -x; break;
+            case 11: r = max_ref(x, 0.0f); break;
+            case 21: r = sqrtf(x); break;
+            case 22: r = 1.0f / x; break;
+            case 29: r = ceilf(x); break;
+            case 30: r = floorf(x); break;
+            case 31: r = roundf(x); break;
+            case 33: r = x != x ? 1.0f : 0.0f; break;
+            case 34: r = x > 0.0f ? 1.0f : x < 0.0f ? -1.0f : 0.0f; break;
+            case 35: r = fabsf(x); break;
+            case 6: r = x - y; break;
+            case 36: r = x / y; break;
+            case 38: r = x - floorf(x / y) * y; break;
+            case 39: r = min_ref(x, y); break;
+            case 40: r = max_ref(x, y); break;
+            case 41: r = x == y ? 1.0f : 0.0f; break;
+            case 42: r = x < y ? 1.0f : 0.0f; break;
+            case 43: r = x <= y ? 1.0f : 0.0f; break;
+            case 44: r = x > y ? 1.0f : 0.0f; break;
+            case 45: r = x >= y ? 1.0f : 0.0f; break;
+            default: return -3;
+        }
+        write_float(out, i, r, dtype);
+    }
+    return 0;
+}
+
 /* ---- RMS norm: cpu/float_kernels.rs:1683-1756 (generic loop), epsilon :1324-1336 ------ */
 int holo_or_rms_norm(const void* x, const void* gamma, void* out, uint32_t batch, uint32_t feature,
                      uint64_t epsilon_bits, int dtype) {
@@ -469,7 +505,7 @@ int holo_or_reduce(const void* in, void* out, uint64_t n, uint32_t rank, const u
             if (!reduced[a]) oo += c * out_stride[a];
         }
         float acc = read_float(out, oo, dtype), v = read_float(in, i, dtype);
-        acc = kind == 0 ? acc + v : kind == 1 ? acc * v : kind == 2 ? fminf(acc, v) : fmaxf(acc, v);
+        acc = kind == 0 ? acc + v : kind == 1 ? acc * v : kind == 2 ? min_ref(acc, v) : max_ref(acc, v);
         write_float(out, oo, acc, dtype);
     }
     if (mean) {

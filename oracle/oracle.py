@@ -39,6 +39,7 @@ def _load(path):
         "holo_or_binary": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_rms_norm": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
         "holo_or_add_rms_norm": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
+        "holo_or_elementwise": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_reduce": (C.c_int, [_c, _c, C.c_uint64, C.c_uint32, _c, C.c_uint32, C.c_int, C.c_int, C.c_int]),
         "holo_or_broadcast": (C.c_int, [_c, _c, _c, C.c_uint32, _c, _c, C.c_uint32, C.c_int, C.c_int, C.c_int]),
         "holo_or_layer_norm": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
@@ -144,6 +145,16 @@ def binary(op, a, b, dtype):
     b = np.ascontiguousarray(b)
     out = np.empty_like(a)
     assert lib.holo_or_binary(op, _p(a), _p(b), _p(out), a.size, dtype) == 0
+    return out
+
+
+def elementwise(tag, a, b, dtype):
+    """The exact unary (b None) and binary variants, by wire discriminant."""
+    a = np.ascontiguousarray(a)
+    b = None if b is None else np.ascontiguousarray(b)
+    out = np.empty_like(a)
+    rc = lib.holo_or_elementwise(tag, _p(a), _p(b), _p(out), a.size, dtype)
+    assert rc == 0, rc
     return out
 
 

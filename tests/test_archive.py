@@ -59,6 +59,24 @@ def test_unserved_discriminant_is_refused():
     assert e.value.variant == "UnsupportedOp"
 
 
+def test_every_served_glue_variant_survives_the_wire():
+    # writer (hologram_b200/holo.py) and reader (csrc/archive.cpp) agree on the field order and widths of
+    # kernel_codec.rs put_norm / put_softmax / put_reduce / put_expand / put_broadcast_binary / put_transpose
+    rb = kc.rb
+    calls = [
+        kc.KernelCall.LayerNorm(kc.NormCall(rb(0), rb(1), rb(2), kc.NONE, rb(3), 4, 64, 0, 0, 0, kc.DTYPE_F32)),
+        kc.KernelCall.Softmax(kc.SoftmaxCall(rb(0), rb(1), 4, 64, kc.DTYPE_F32)),
+        kc.KernelCall.ReduceSum(kc.ReduceCall.make(rb(0), rb(1), (4, 8, 2), 0b010, kc.DTYPE_F32)),
+        kc.KernelCall.ReduceMax(kc.ReduceCall.make(rb(0), rb(1), (64,), 0, kc.DTYPE_BF16)),
+        kc.KernelCall.Expand(kc.ExpandCall.make(rb(0), rb(1), (1, 8), (4, 8), kc.DTYPE_BF16)),
+        kc.KernelCall.BroadcastBinary(kc.BroadcastBinaryCall.make(rb(0), rb(1), rb(2), (1, 8), (4, 8), kc.BROADCAST_MUL, True, kc.DTYPE_F32)),
+        kc.KernelCall.Transpose(kc.TransposeCall.make(rb(0), rb(1), (2, 3, 4), (2, 0, 1), kc.DTYPE_F32)),
+    ]
+    for n in range(1, len(calls) + 1):      # a misread length in call i would derail call i + 1
+        img = holo.assemble([(holo.SEC_KERNEL_CALLS, [holo.encode_calls(calls[:n])]), (holo.SEC_WEIGHTS, [struct.pack("<I", 0)])])
+        assert hb.archive_check(img)[0] == n
+
+
 def test_tensor_parallel_shards_partition_the_weights():
     cfg = small_cfg()
     cfg.n_heads, cfg.n_kv_heads = 4, 2

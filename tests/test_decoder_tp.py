@@ -1,4 +1,4 @@
-"""Tensor-parallel decoder: host-side logic on CPU (gloo, world size 2), GPU run at N = 2."""
+"""Tensor-parallel decoder: host-side logic on CPU (gloo, world size 2), GPU runs at N = 2 and N = 4."""
 import os
 import subprocess
 import sys
@@ -17,7 +17,7 @@ from oracle import oracle as orc
 from decoder_common import oracle_step, step_inputs, small_cfg
 mode = %(mode)r
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-cfg = small_cfg(layers=1, batch=2, bucket=128)
+cfg = %(cfg)s
 img, info = dh.build_decoder_step(cfg, rank, world)
 vals = step_inputs(cfg, info, 9, 128, seed=11, tp_rank=rank)
 if mode == "cpu":
@@ -59,9 +59,15 @@ dist.destroy_process_group()
 '''
 
 
-def _launch(mode, tmp_path, world=2):
+SMALL = "small_cfg(layers=1, batch=2, bucket=128)"
+# four KV heads, so that four ranks each own one; the row-parallel products take the fused all-reduce epilogue
+WIDE = ("dh.DecoderConfig(d_model=1024, n_heads=8, n_kv_heads=4, head_dim=128, ffn=2048, vocab=2048, n_layers=2, "
+        "batch=8, bucket=128)")
+
+
+def _launch(mode, tmp_path, world=2, cfg=SMALL):
     script = tmp_path / f"worker_{mode}.py"
-    script.write_text(WORKER % {"root": ROOT, "mode": mode, "out": str(tmp_path)})
+    script.write_text(WORKER % {"root": ROOT, "mode": mode, "out": str(tmp_path), "cfg": cfg})
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     port = 29500 + os.getpid() % 500
     subprocess.check_call([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
@@ -122,5 +128,21 @@ def test_tp2_on_two_gpus_matches_single_rank(tmp_path):
             assert np.max(np.abs(orc.bf16_to_f32(got[0]) - total)) <= 2.0 ** -6 * np.max(np.abs(total))
     want = _single_rank_reference()
     got = np.concatenate([r0.reshape(want.shape[0], -1), r1.reshape(want.shape[0], -1)], axis=1)
+    err = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
+    assert err <= 2e-2, err
+
+
+@pytest.mark.gpu
+def test_tp4_on_four_gpus_matches_the_gloo_interpreter(tmp_path):
+    # the same per-rank archives through the CPU interpreter (all-reduce over gloo) and through the
+    # sessions on four GPUs (all-reduce inside the product's epilogue, over peer memory)
+    import torch
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    want = np.concatenate([r.reshape(8, -1) for r in _launch("cpu", tmp_path, 4, WIDE)], axis=1)
+    got = np.concatenate([r.reshape(8, -1) for r in _launch("gpu", tmp_path, 4, WIDE)], axis=1)
+    for rep in range(3):
+        res = [np.load(tmp_path / f"allreduce_{rep}_{r}.npy") for r in range(4)]
+        assert all(np.array_equal(res[0], x) for x in res[1:])
     err = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
     assert err <= 2e-2, err

@@ -400,3 +400,37 @@ def test_reduce_variants(backend):
     with pytest.raises(hb.BackendError) as e:
         backend.dispatch(kc.KernelCall.ReduceSum(bad), ws)
     assert e.value.variant == "UnsupportedOp"
+
+
+def test_exact_elementwise_variants(backend):
+    # unary_float / binary_float with one IEEE operation per element (cpu/float_kernels.rs:190-296, :3446-3500,
+    # :3660-3733): bit-exact, every 16-bit code for the unary forms (NaN inputs included)
+    codes = np.arange(65536, dtype=np.uint16)
+    rng = np.random.default_rng(45)
+    special = np.array([0.0, -0.0, 1.0, -1.0, 0.5, -0.5, 1.5, -1.5, 2.5, -2.5, np.inf, -np.inf, 3e38, -3e38, 1e-40, -1e-40], dtype=np.float32)
+    f32 = np.concatenate([special, (rng.standard_normal(4096 - special.size) * 7).astype(np.float32)])
+    for tag in kc.EXACT_UNARY:
+        for dt, x in ((BF, codes), (kc.DTYPE_F16, codes), (kc.DTYPE_F32, f32)):
+            ws = hb.DeviceWorkspace(backend, 2)
+            ws.put(0, x)
+            ws.alloc(1, x.nbytes)
+            backend.dispatch(kc.KernelCall.Elementwise(tag, kc.UnaryCall(kc.rb(0), kc.rb(1), x.size, 0, dt)), ws)
+            want = orc.elementwise(tag, x, None, dt)
+            got = ws.read(1, x.nbytes, x.dtype)
+            assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (tag, dt, np.flatnonzero(got.view(np.uint8) != want.view(np.uint8))[:4])
+            ws.close()
+    a32 = np.concatenate([np.repeat(special, special.size), (rng.standard_normal(4096) * 5).astype(np.float32)])
+    b32 = np.concatenate([np.tile(special, special.size), (rng.standard_normal(4096) * 3).astype(np.float32)])
+    for tag in kc.EXACT_BINARY:
+        for dt in (kc.DTYPE_F32, BF, kc.DTYPE_F16):
+            a, b = (a32, b32) if dt == kc.DTYPE_F32 else ((orc.f32_to_bf16_rne(a32), orc.f32_to_bf16_rne(b32)) if dt == BF else
+                                                           (a32.astype(np.float16).view(np.uint16), b32.astype(np.float16).view(np.uint16)))
+            ws = hb.DeviceWorkspace(backend, 3)
+            ws.put(0, a)
+            ws.put(1, b)
+            ws.alloc(2, a.nbytes)
+            backend.dispatch(kc.KernelCall.Elementwise(tag, kc.BinaryCall(kc.rb(0), kc.rb(1), kc.rb(2), a.size, 0, dt)), ws)
+            want = orc.elementwise(tag, a, b, dt)
+            got = ws.read(2, a.nbytes, a.dtype)
+            assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (tag, dt, np.flatnonzero(got.view(np.uint8) != want.view(np.uint8))[:4])
+            ws.close()

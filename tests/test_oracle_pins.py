@@ -339,6 +339,24 @@ def test_reduce_restatement_equals_numpy_on_exact_cases():
     assert np.array_equal(orc.reduce(p, (2, 3, 4), 0b010, 1, False, kc.DTYPE_F32), np.prod(p.reshape(2, 3, 4), axis=1).reshape(-1))
 
 
+def test_exact_elementwise_restatement_on_known_answers():
+    # cpu/float_kernels.rs:3446-3500, :3660-3733: IEEE division by zero, floored modulo whose sign follows
+    # the divisor, half-away-from-zero rounding, NaN-ignoring min / max, comparisons as 1.0 / 0.0
+    f = lambda *v: np.array(v, dtype=np.float32)
+    e = lambda tag, a, b=None: orc.elementwise(tag, a, b, kc.DTYPE_F32)
+    assert np.array_equal(e(kc.K_DIV, f(1, -1, 6), f(0, 0, 4)), f(np.inf, -np.inf, 1.5))
+    assert np.isnan(e(kc.K_DIV, f(0), f(0))[0]) and np.isnan(e(kc.K_MOD, f(1), f(0))[0])
+    assert np.array_equal(e(kc.K_MOD, f(5, -5, 5, -5), f(3, 3, -3, -3)), f(2, 1, -1, -2))
+    assert np.array_equal(e(kc.K_ROUND, f(0.5, -0.5, 1.5, 2.5, -2.5)), f(1, -1, 2, 3, -3))
+    assert np.array_equal(e(kc.K_MIN, f(np.nan, 1, 2), f(3, np.nan, 1)), f(3, 1, 1))
+    assert np.array_equal(e(kc.K_MAX, f(np.nan, 1, 2), f(3, np.nan, 1)), f(3, 1, 2))
+    assert np.array_equal(e(kc.K_RELU, f(-1, 2, np.nan)), f(0, 2, 0))
+    assert np.array_equal(e(kc.K_SIGN, f(-3, 0, 7, np.nan)), f(-1, 0, 1, 0))
+    assert np.array_equal(e(kc.K_IS_NAN, f(np.nan, 1)), f(1, 0))
+    assert np.array_equal(e(kc.K_LESS_OR_EQUAL, f(1, 2, np.nan), f(1, 1, 1)), f(1, 0, 0))
+    assert np.array_equal(e(kc.K_SQRT, f(4, 2)), np.sqrt(f(4, 2))) and np.array_equal(e(kc.K_RECIPROCAL, f(4, 0)), f(0.25, np.inf))
+
+
 def test_mask_form_restatement_equals_scalar_form_bitwise():
     # the reference pins that a realized-length mask reproduces DecodeAttentionValid bit for bit
     # (crates/hologram-compute/tests/decode_attention_valid.rs:226-282); all-erased row = zeros
