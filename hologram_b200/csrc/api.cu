@@ -680,6 +680,43 @@ int32_t attn_geometry(uint32_t b, uint32_t h, uint32_t kv, uint32_t m, uint32_t 
     return HOLO_OK;
 }
 
+// attention_float (cpu/float_kernels.rs:2244-2395): the prefill form. It is the decode row (:2420-2477) with an
+// empty cache, the whole sequence as the chunk, and the causal law either on or off.
+int32_t do_attention_legacy(holo_b200_ctx* ctx, const HoloAttentionCall& c, holo_b200_workspace* ws) {
+    if (c.batch == 0 || c.heads == 0 || c.seq == 0 || c.head_dim == 0) return HOLO_OK;
+    HoloAttnArgs a = {};
+    a.hkv = c.kv_heads == 0 ? c.heads : c.kv_heads;
+    if (c.heads % a.hkv != 0)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: attention: heads must be a multiple of kv_heads (grouped-query)");
+    if (c.dtype == HOLO_DTYPE_F64)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: f64 is not a supported compute dtype (hologram computes in f16/bf16/f32)");
+    if (!holo_is_compute_float(c.dtype))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: attention: only f32/f16/bf16 are supported compute dtypes");
+    float dflt = sqrtf((float)c.head_dim);
+    if (dflt < 1.0f) dflt = 1.0f;
+    a.scale_div = dflt;
+    if (c.scale_bits != 0) {
+        float sm;
+        memcpy(&sm, &c.scale_bits, 4);
+        if (sm > 0.0f) a.scale_div = 1.0f / sm;
+    }
+    const size_t es = holo_dtype_size(c.dtype);
+    const uint64_t qt = (uint64_t)c.batch * c.heads * c.seq * c.head_dim * es;
+    const uint64_t kt = (uint64_t)c.batch * a.hkv * c.seq * c.head_dim * es;
+    uint8_t *q, *k, *v, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, 0, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.q, qt, &q, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.k, kt, &k, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.v, kt, &v, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, qt, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, qt}, c.output.slot, {{q, qt}, {k, kt}, {v, kt}}));
+    a.q = q; a.k_new = k; a.v_new = v; a.out = out;
+    a.b = c.batch; a.h = c.heads; a.m = c.seq; a.past = 0; a.nnew = c.seq; a.d = c.head_dim;
+    a.dtype = c.dtype;
+    a.all_new = c.causal == 0;
+    return holo_launch_decode_attention(ctx, a);
+}
+
 // decode_attention_valid_float (cpu/float_kernels.rs:4192-4307)
 int32_t do_attention(holo_b200_ctx* ctx, const HoloDecodeAttentionValidCall& c, holo_b200_workspace* ws) {
     HoloAttnArgs a = {};
@@ -836,6 +873,7 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         }
         case HOLO_K_DEQUANTIZE: return do_dequantize(ctx, call->u.dequantize, ws);
         case HOLO_K_KV_CACHE_WRITE: return do_kv_write(ctx, call->u.kv_cache_write, ws);
+        case HOLO_K_ATTENTION: return do_attention_legacy(ctx, call->u.attention, ws);
         case HOLO_K_DECODE_ATTENTION: return do_attention_mask(ctx, call->u.decode_attention, ws);
         case HOLO_K_DECODE_ATTENTION_VALID: return do_attention(ctx, call->u.decode_attention_valid, ws);
         case HOLO_K_QUANTIZE_ROWS_I8: return do_quantize_rows(ctx, call->u.quantize_rows_i8, ws);
@@ -917,6 +955,12 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             l->in(&c->u.reduce.input);
             l->out(&c->u.reduce.output, reduce_out_count(c->u.reduce) * holo_dtype_size(c->u.reduce.dtype));
             return true;
+        case HOLO_K_ATTENTION: {
+            HoloAttentionCall& t = c->u.attention;
+            l->in(&t.q); l->in(&t.k); l->in(&t.v);
+            l->out(&t.output, (uint64_t)t.batch * t.heads * t.seq * t.head_dim * holo_dtype_size(t.dtype));
+            return true;
+        }
         case HOLO_K_SOFTMAX:
             l->in(&c->u.softmax.input);
             l->out(&c->u.softmax.output, (uint64_t)c->u.softmax.batch * c->u.softmax.feature * holo_dtype_size(c->u.softmax.dtype));

@@ -98,6 +98,13 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             for (uint32_t i = 0; i < c.rank; ++i) c.dims[i] = r.u32();
             break;
         }
+        case HOLO_K_ATTENTION: {
+            HoloAttentionCall& c = out->u.attention;
+            c.q = r.buf(); c.k = r.buf(); c.v = r.buf(); c.output = r.buf();
+            c.batch = r.u32(); c.heads = r.u32(); c.seq = r.u32(); c.head_dim = r.u32(); c.kv_heads = r.u32();
+            c.causal = r.u8(); c.scale_bits = r.u32(); c.dtype = r.u8();
+            break;
+        }
         case HOLO_K_EXPAND: {
             HoloExpandCall& c = out->u.expand;
             c.input = r.buf(); c.output = r.buf(); c.rank = r.u8();

@@ -37,8 +37,8 @@ decode_attention_generic_kernel(HoloAttnArgs a) {
     // scalar-mask form: the first min(valid_len, past) cache rows, then chunk rows 0..qi;
     // additive-mask form (decode_attention_row, cpu/float_kernels.rs:2420-2477): every key, the
     // mask row added to the scaled score
-    const uint32_t vis_past = a.mask ? a.past : min(*a.valid_len, a.past);
-    const uint32_t new_vis = a.mask ? a.nnew : min(qi + 1, a.nnew);
+    const uint32_t vis_past = a.mask || !a.valid_len ? a.past : min(*a.valid_len, a.past);
+    const uint32_t new_vis = a.mask || a.all_new ? a.nnew : min(qi + 1, a.nnew);
     const float* mask_row = a.mask ? a.mask + (uint64_t)qi * (a.past + a.nnew) : nullptr;
     const uint32_t vis = vis_past + new_vis;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -203,13 +203,14 @@ struct HoloAttnArgs {
     const void* q;
     const void *k_past, *v_past, *k_new, *v_new;              // bf16/f16/f32 rows, or i8 codes when quantized
     const float *k_past_s, *v_past_s, *k_new_s, *v_new_s;     // per-row scales (quantized form only)
-    const uint32_t* valid_len;   // scalar-mask form
+    const uint32_t* valid_len;   // scalar-mask form; null = every cache row is visible
     const float* mask;           // additive-mask form ([m, past + nnew] f32) when non-null: every key takes part
     void* out;
     uint32_t b, h, hkv, m, past, nnew, d;
     float scale_div;  // scores are divided by this
     uint8_t dtype;    // q / out dtype (and KV dtype in the unquantized form)
     bool quantized;
+    bool all_new;     // scalar-mask form without the causal law: query row i sees every chunk row (legacy non-causal Attention)
 };
 int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a);
 // gemm.cu

@@ -115,6 +115,12 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
             for (uint32_t i = 0; i < c.rank && i < 8; ++i) b.u32(c.dims[i]);
             return true;
         }
+        case HOLO_K_ATTENTION: {
+            const HoloAttentionCall& c = u.attention;
+            sig->opcode = 68;
+            b.u32(c.batch).u32(c.heads).u32(c.seq).u32(c.head_dim).u32(c.kv_heads).u8(c.causal ? 1 : 0).u32(c.scale_bits).u8(c.dtype);
+            return true;
+        }
         case HOLO_K_EXPAND: {
             const HoloExpandCall& c = u.expand;
             sig->opcode = 71;
@@ -230,6 +236,7 @@ bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* input
         case HOLO_K_SOFTMAX: in(u.softmax.input); *output = u.softmax.output.slot; return true;
         case HOLO_K_REDUCE_SUM: case HOLO_K_REDUCE_MEAN: case HOLO_K_REDUCE_PROD: case HOLO_K_REDUCE_MIN: case HOLO_K_REDUCE_MAX:
             in(u.reduce.input); *output = u.reduce.output.slot; return true;
+        case HOLO_K_ATTENTION: in(u.attention.q); in(u.attention.k); in(u.attention.v); *output = u.attention.output.slot; return true;
         case HOLO_K_EXPAND: in(u.expand.input); *output = u.expand.output.slot; return true;
         case HOLO_K_BROADCAST_BINARY: in(u.broadcast_binary.small); in(u.broadcast_binary.other); *output = u.broadcast_binary.output.slot; return true;
         case HOLO_K_ROTARY: in(u.rope.x); in(u.rope.cos); in(u.rope.sin); *output = u.rope.output.slot; return true;

@@ -66,6 +66,10 @@ def encode_call(call):
         c = u.reduce
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<QBIBB", c.element_count, c.rank, c.axes_mask, c.keepdims, c.dtype) + struct.pack(
             "<%dI" % c.rank, *list(c.dims)[:c.rank])
+    if k == kc.K_ATTENTION:
+        c = u.attention
+        return out + _buf(c.q) + _buf(c.k) + _buf(c.v) + _buf(c.output) + struct.pack(
+            "<IIIIIBIB", c.batch, c.heads, c.seq, c.head_dim, c.kv_heads, c.causal, c.scale_bits, c.dtype)
     if k == kc.K_EXPAND:
         c = u.expand
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<B8I8IB", c.rank, *c.in_dims, *c.out_dims, c.dtype)

@@ -25,7 +25,7 @@ EXACT_UNARY = (K_NEG, K_RELU, K_SQRT, K_RECIPROCAL, K_CEIL, K_FLOOR, K_ROUND, K_
 EXACT_BINARY = (K_SUB, K_DIV, K_MOD, K_MIN, K_MAX, K_EQUAL, K_LESS, K_LESS_OR_EQUAL, K_GREATER, K_GREATER_OR_EQUAL)
 K_SIGMOID, K_TANH, K_GELU, K_SILU, K_EXP, K_ERF = 12, 13, 14, 15, 18, 32
 K_MATMUL, K_RMS_NORM, K_RESHAPE, K_ROTARY = 46, 51, 60, 75
-K_LAYER_NORM, K_EXPAND, K_BROADCAST_BINARY = 50, 72, 112
+K_LAYER_NORM, K_EXPAND, K_BROADCAST_BINARY, K_ATTENTION = 50, 72, 112, 69
 BROADCAST_ADD, BROADCAST_SUB, BROADCAST_MUL = 0, 1, 2
 K_REDUCE_SUM, K_REDUCE_MEAN, K_REDUCE_PROD, K_REDUCE_MIN, K_REDUCE_MAX = 55, 56, 57, 58, 59
 K_ADD_RMS_NORM, K_TRANSPOSE, K_CONCAT, K_SLICE, K_SOFTMAX = 54, 61, 62, 63, 64
@@ -114,6 +114,13 @@ class LayoutCall(C.Structure):
 
 class SoftmaxCall(C.Structure):
     _fields_ = [("input", BufferRef), ("output", BufferRef), ("batch", C.c_uint32), ("feature", C.c_uint32), ("dtype", C.c_uint8)]
+
+
+class AttentionCall(C.Structure):
+    """kernel_call.rs:575-594: q [b, heads, seq, d], k / v [b, kv_heads, seq, d]; causal: row i sees keys j <= i."""
+    _fields_ = [("q", BufferRef), ("k", BufferRef), ("v", BufferRef), ("output", BufferRef), ("batch", C.c_uint32),
+                ("heads", C.c_uint32), ("seq", C.c_uint32), ("head_dim", C.c_uint32), ("kv_heads", C.c_uint32),
+                ("causal", C.c_uint8), ("scale_bits", C.c_uint32), ("dtype", C.c_uint8)]
 
 
 class ReduceCall(C.Structure):
@@ -232,7 +239,7 @@ class _Payload(C.Union):
     _fields_ = [("unary", UnaryCall), ("binary", BinaryCall), ("matmul", MatMulCall),
                 ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("matmul_dequant", MatMulDequantCall), ("norm", NormCall),
                 ("rope", RoPECall), ("gather", GatherCall), ("cast", CastCall), ("layout", LayoutCall),
-                ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("expand", ExpandCall), ("reduce", ReduceCall), ("broadcast_binary", BroadcastBinaryCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
+                ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("expand", ExpandCall), ("reduce", ReduceCall), ("attention", AttentionCall), ("broadcast_binary", BroadcastBinaryCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
                 ("decode_attention", DecodeAttentionCall),
                 ("decode_attention_valid", DecodeAttentionValidCall), ("quantize_rows_i8", QuantizeRowsI8Call),
                 ("decode_attention_valid_q8", DecodeAttentionValidQ8Call), ("all_reduce", AllReduceCall),
@@ -294,6 +301,8 @@ class KernelCall(C.Structure):
     @classmethod
     def Expand(cls, c): return cls.of(K_EXPAND, c)
     @classmethod
+    def Attention(cls, c): return cls.of(K_ATTENTION, c)
+    @classmethod
     def ReduceSum(cls, c): return cls.of(K_REDUCE_SUM, c)
     @classmethod
     def ReduceMean(cls, c): return cls.of(K_REDUCE_MEAN, c)
@@ -340,7 +349,7 @@ class KernelCall(C.Structure):
 KernelCall._FIELD = {
     UnaryCall: "unary", BinaryCall: "binary", MatMulCall: "matmul", MatMulActivationCall: "matmul_activation",
     MatMulAddCall: "matmul_add", MatMulDequantCall: "matmul_dequant", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
-    LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", ExpandCall: "expand", ReduceCall: "reduce", BroadcastBinaryCall: "broadcast_binary", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
+    LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", ExpandCall: "expand", ReduceCall: "reduce", AttentionCall: "attention", BroadcastBinaryCall: "broadcast_binary", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
     DecodeAttentionCall: "decode_attention", DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
     DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce", RopeQuantizeCall: "rope_quantize",
 }

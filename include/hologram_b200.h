@@ -106,6 +106,7 @@ extern "C" {
 #define HOLO_K_CONCAT 62
 #define HOLO_K_SLICE 63
 #define HOLO_K_SOFTMAX 64
+#define HOLO_K_ATTENTION 69
 #define HOLO_K_EXPAND 72
 #define HOLO_K_ROTARY 75
 #define HOLO_K_DEQUANTIZE 105
@@ -205,6 +206,17 @@ typedef struct HoloSoftmaxCall {
     uint32_t batch, feature;
     uint8_t dtype;
 } HoloSoftmaxCall;
+
+/* AttentionCall (kernel_call.rs:575-594): scaled dot-product attention over q [batch, heads, seq, head_dim] and
+ * k, v [batch, kv_heads, seq, head_dim] (kv_heads 0 = heads; query head h reads kv head h / (heads / kv_heads));
+ * causal: query row i sees keys j <= i; scale_bits: f32 bits of the score multiplier, 0 = 1/sqrt(head_dim). */
+typedef struct HoloAttentionCall {
+    HoloBufferRef q, k, v, output;
+    uint32_t batch, heads, seq, head_dim, kv_heads;
+    uint8_t causal;
+    uint32_t scale_bits;
+    uint8_t dtype;
+} HoloAttentionCall;
 
 /* ReduceCall (kernel_call.rs:461-477): fold the axes whose bit is set in axes_mask (0 or rank 0 = all) of a
  * row-major tensor `dims[..rank]`; the output is the keepdims layout (reduced axes collapsed to 1). Every
@@ -371,6 +383,7 @@ typedef struct HoloKernelCall {
         HoloSoftmaxCall softmax;
         HoloExpandCall expand;
         HoloReduceCall reduce;
+        HoloAttentionCall attention;
         HoloBroadcastBinaryCall broadcast_binary;
         HoloDequantizeCall dequantize;
         HoloKvCacheWriteCall kv_cache_write;

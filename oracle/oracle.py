@@ -148,6 +148,17 @@ def binary(op, a, b, dtype):
     return out
 
 
+def attention(q, k, v, b, h, kv, seq, d, causal, scale_bits, dtype):
+    """attention_float (cpu/float_kernels.rs:2244-2395). Its per-row arithmetic (:2352-2388: dot / scale, -inf for the
+    keys the causal law hides, max shift, deterministic exp, left-to-right sum, e / max(sum, 1e-30), context in key
+    order) is the decode row (:2420-2477) with an empty cache, the sequence as the chunk and a 0 / -inf mask."""
+    mask = np.zeros((seq, seq), dtype=np.float32)
+    if causal:
+        mask[np.triu_indices(seq, 1)] = -np.inf
+    empty = np.zeros(0, dtype=np.asarray(q).dtype)
+    return decode_attention_mask(q, empty, empty, k, v, mask, b, h, kv, seq, 0, seq, d, scale_bits, dtype)
+
+
 def elementwise(tag, a, b, dtype):
     """The exact unary (b None) and binary variants, by wire discriminant."""
     a = np.ascontiguousarray(a)

@@ -45,3 +45,22 @@ def norm_max_err(got_f32, want_f32):
 def unary(act, inp, out, n, dtype):
     return kc.lut_call(act, kc.UnaryCall(kc.rb(inp) if isinstance(inp, int) else inp,
                                          kc.rb(out) if isinstance(out, int) else out, n, 16, dtype))
+
+
+# the four legacy-Attention cases of the reference's conformance suite (causal, grouped-query, explicit scale):
+# (batch, heads, kv_heads, seq, head_dim, causal, score multiplier or None)
+ATTENTION_CASES = ((1, 4, 4, 16, 8, True, None), (2, 8, 2, 12, 16, False, None), (1, 6, 3, 24, 16, True, 0.125), (1, 8, 1, 31, 8, True, None))
+
+
+def attention_f64(q, k, v, b, h, hkv, s, d, causal, mult):
+    """Scaled dot-product attention in float64 (grouped-query, optional causal law)."""
+    import numpy as np
+    q4 = q.astype(np.float64).reshape(b, h, s, d)
+    k4 = np.repeat(k.astype(np.float64).reshape(b, hkv, s, d), h // hkv, axis=1)
+    v4 = np.repeat(v.astype(np.float64).reshape(b, hkv, s, d), h // hkv, axis=1)
+    div = (1.0 / mult) if mult else max(np.sqrt(d), 1.0)
+    sc = np.einsum("bhqd,bhkd->bhqk", q4, k4) / div
+    if causal:
+        sc = np.where(np.triu(np.ones((s, s), dtype=bool), 1), -np.inf, sc)
+    e = np.exp(sc - sc.max(axis=-1, keepdims=True))
+    return np.einsum("bhqk,bhkd->bhqd", e / e.sum(axis=-1, keepdims=True), v4).reshape(-1)

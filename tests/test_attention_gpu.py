@@ -264,3 +264,29 @@ def test_config4_full_size_codes_and_attention(backend):
     err = norm_max_err(got, want)
     print(f"config-4 attention: max|err|/max|ref| = {err:.3e}")
     assert err <= 1e-2
+
+
+def test_legacy_attention_prefill_form(backend):
+    # KernelCall::Attention (wire 69; attention_float, cpu/float_kernels.rs:2244-2395): the reference's own
+    # conformance cases plus a longer bf16 prefill; online softmax on the GPU against the CPU's two-pass row
+    from helpers import ATTENTION_CASES
+    cases = [(c, kc.DTYPE_F32) for c in ATTENTION_CASES] + [((2, 8, 2, 160, 128, True, None), BF), ((1, 4, 4, 96, 64, False, None), BF)]
+    for idx, ((b, h, hkv, s, d, causal, mult), dt) in enumerate(cases):
+        rng = np.random.default_rng(0x8c0 + idx)
+        q, k, v = (rng.standard_normal(n).astype(np.float32) for n in (b * h * s * d, b * hkv * s * d, b * hkv * s * d))
+        if dt == BF:
+            q, k, v = (orc.f32_to_bf16_rne(x) for x in (q, k, v))
+        bits = int(np.float32(mult).view(np.uint32)) if mult else 0
+        kvh = hkv if hkv != h else 0
+        ws = hb.DeviceWorkspace(backend, 4)
+        for i, x in enumerate((q, k, v)):
+            ws.put(i, x)
+        ws.alloc(3, q.nbytes)
+        call = kc.AttentionCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), b, h, s, d, kvh, int(causal), bits, dt)
+        backend.dispatch(kc.KernelCall.Attention(call), ws)
+        want = orc.attention(q, k, v, b, h, kvh, s, d, causal, bits, dt)
+        got = ws.read(3, q.nbytes, q.dtype)
+        if dt == BF:
+            got, want = orc.bf16_to_f32(got), orc.bf16_to_f32(want)
+        assert norm_max_err(got, want) <= (1e-2 if dt == BF else 2e-4), (idx, norm_max_err(got, want))
+        ws.close()

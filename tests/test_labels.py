@@ -76,6 +76,8 @@ def test_op_signature_frozen_bytes():
         assert hs.op_signature(kc.KernelCall.Elementwise(kind, kc.UnaryCall(rb(0), rb(1), 9, 0, kc.DTYPE_BF16))) == (kind - 1, struct.pack("<QHB", 9, 0, kc.DTYPE_BF16))
     for kind in kc.EXACT_BINARY:
         assert hs.op_signature(kc.KernelCall.Elementwise(kind, kc.BinaryCall(rb(0), rb(1), rb(2), 9, 0, kc.DTYPE_F32))) == (kind - 1, struct.pack("<QHB", 9, 0, kc.DTYPE_F32))
+    at = kc.AttentionCall(rb(0), rb(1), rb(2), rb(3), 1, 8, 31, 8, 1, 1, 0, kc.DTYPE_F32)
+    assert hs.op_signature(kc.KernelCall.Attention(at)) == (68, struct.pack("<IIIIIBIB", 1, 8, 31, 8, 1, 1, 0, kc.DTYPE_F32))
     rd = kc.ReduceCall.make(rb(0), rb(1), (3, 4), 0b10, kc.DTYPE_F32)
     assert hs.op_signature(kc.KernelCall.ReduceMax(rd)) == (58, struct.pack("<QBIBBII", 12, 2, 2, 1, kc.DTYPE_F32, 3, 4))
     ex = kc.ExpandCall.make(rb(0), rb(1), (1, 4), (3, 4), kc.DTYPE_F32)

@@ -357,6 +357,18 @@ def test_exact_elementwise_restatement_on_known_answers():
     assert np.array_equal(e(kc.K_SQRT, f(4, 2)), np.sqrt(f(4, 2))) and np.array_equal(e(kc.K_RECIPROCAL, f(4, 0)), f(0.25, np.inf))
 
 
+def test_legacy_attention_restatement_meets_the_reference_conformance_cases():
+    # crates/hologram-compute/tests/conformance.rs:778-935 (kc8c): causal, grouped-query and explicit-scale cases
+    # against a float64 attention, 1e-4
+    from helpers import ATTENTION_CASES, attention_f64
+    for idx, (b, h, hkv, s, d, causal, mult) in enumerate(ATTENTION_CASES):
+        rng = np.random.default_rng(0x8c0 + idx)
+        q, k, v = (rng.standard_normal(n).astype(np.float32) for n in (b * h * s * d, b * hkv * s * d, b * hkv * s * d))
+        bits = int(np.float32(mult).view(np.uint32)) if mult else 0
+        got = orc.attention(q, k, v, b, h, hkv if hkv != h else 0, s, d, causal, bits, kc.DTYPE_F32)
+        assert np.max(np.abs(got - attention_f64(q, k, v, b, h, hkv, s, d, causal, mult))) < 1e-4
+
+
 def test_mask_form_restatement_equals_scalar_form_bitwise():
     # the reference pins that a realized-length mask reproduces DecodeAttentionValid bit for bit
     # (crates/hologram-compute/tests/decode_attention_valid.rs:226-282); all-erased row = zeros
