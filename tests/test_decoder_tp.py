@@ -65,10 +65,10 @@ WIDE = ("dh.DecoderConfig(d_model=1024, n_heads=8, n_kv_heads=4, head_dim=128, f
         "batch=8, bucket=128)")
 
 
-def _launch(mode, tmp_path, world=2, cfg=SMALL):
+def _launch(mode, tmp_path, world=2, cfg=SMALL, **extra_env):
     script = tmp_path / f"worker_{mode}.py"
     script.write_text(WORKER % {"root": ROOT, "mode": mode, "out": str(tmp_path), "cfg": cfg})
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **extra_env)
     port = 29500 + os.getpid() % 500
     subprocess.check_call([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                            "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)], env=env, timeout=600)
@@ -132,17 +132,27 @@ def test_tp2_on_two_gpus_matches_single_rank(tmp_path):
     assert err <= 2e-2, err
 
 
-@pytest.mark.gpu
-def test_tp4_on_four_gpus_matches_the_gloo_interpreter(tmp_path):
-    # the same per-rank archives through the CPU interpreter (all-reduce over gloo) and through the
-    # sessions on four GPUs (all-reduce inside the product's epilogue, over peer memory)
+def _tp4(tmp_path, **extra_env):
     import torch
     if torch.cuda.device_count() < 4:
         pytest.skip("needs 4 GPUs")
     want = np.concatenate([r.reshape(8, -1) for r in _launch("cpu", tmp_path, 4, WIDE)], axis=1)
-    got = np.concatenate([r.reshape(8, -1) for r in _launch("gpu", tmp_path, 4, WIDE)], axis=1)
+    got = np.concatenate([r.reshape(8, -1) for r in _launch("gpu", tmp_path, 4, WIDE, **extra_env)], axis=1)
     for rep in range(3):
         res = [np.load(tmp_path / f"allreduce_{rep}_{r}.npy") for r in range(4)]
         assert all(np.array_equal(res[0], x) for x in res[1:])
     err = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
     assert err <= 2e-2, err
+
+
+@pytest.mark.gpu
+def test_tp4_on_four_gpus_matches_the_gloo_interpreter(tmp_path):
+    # the same per-rank archives through the CPU interpreter (all-reduce over gloo) and through the
+    # sessions on four GPUs (products, then the all-reduce kernel over peer memory)
+    _tp4(tmp_path)
+
+
+@pytest.mark.gpu
+def test_tp4_with_the_all_reduce_in_the_product_epilogue(tmp_path):
+    # groups above two ranks take the fused product + all-reduce only when asked
+    _tp4(tmp_path, HOLO_TP_FUSED_GEMM_ANY_WORLD="1")
