@@ -148,21 +148,30 @@ __device__ __forceinline__ float nan_fix2(float y, float a, float b) {
 // f32::min / f32::max: the other operand when one is NaN; of two equal operands (+0 and -0) the first
 __device__ __forceinline__ float min_ref(float a, float b) { return a != a ? b : (b < a ? b : a); }
 __device__ __forceinline__ float max_ref(float a, float b) { return a != a ? b : (b > a ? b : a); }
+// Neg and Abs are bit operations on the CPU (a NaN keeps its payload). Written as integer PTX so that the
+// compiler cannot fold them into neg.f32 / abs.f32, which return the canonical NaN.
+__device__ __forceinline__ float sign_bits(float x, uint32_t mask, bool clear) {
+    uint32_t r;
+    if (clear) asm volatile("and.b32 %0, %1, %2;" : "=r"(r) : "r"(__float_as_uint(x)), "r"(mask));
+    else asm volatile("xor.b32 %0, %1, %2;" : "=r"(r) : "r"(__float_as_uint(x)), "r"(mask));
+    return __uint_as_float(r);
+}
 __device__ __forceinline__ bool ew_is_unary(int tag) {
     return tag == 1 || tag == 11 || tag == 21 || tag == 22 || (tag >= 29 && tag <= 31) || (tag >= 33 && tag <= 35);
 }
+// Ceil / Floor / Round: the software libm the CPU backend links returns every |x| >= 2^23, a NaN included, unchanged.
 __device__ __forceinline__ float ew_unary(int tag, float x) {
     switch (tag) {
-        case 1: return __uint_as_float(__float_as_uint(x) ^ 0x80000000u);                       // Neg
+        case 1: return sign_bits(x, 0x80000000u, false);                                        // Neg
         case 11: return max_ref(x, 0.0f);                                                       // Relu: x.max(0.0)
         case 21: return nan_fix2(__fsqrt_rn(x), x, x);                                          // Sqrt
         case 22: return nan_fix2(__fdiv_rn(1.0f, x), x, x);                                     // Reciprocal
-        case 29: return nan_fix2(ceilf(x), x, x);
-        case 30: return nan_fix2(floorf(x), x, x);
-        case 31: return nan_fix2(roundf(x), x, x);                                              // half away from zero
+        case 29: return x != x ? x : ceilf(x);
+        case 30: return x != x ? x : floorf(x);
+        case 31: return x != x ? x : roundf(x);   // half away from zero
         case 33: return x != x ? 1.0f : 0.0f;                                                   // IsNaN
         case 34: return x > 0.0f ? 1.0f : x < 0.0f ? -1.0f : 0.0f;                              // Sign
-        default: return __uint_as_float(__float_as_uint(x) & 0x7fffffffu);                      // Abs
+        default: return sign_bits(x, 0x7fffffffu, true);                                        // Abs
     }
 }
 __device__ __forceinline__ float ew_binary(int tag, float a, float b) {

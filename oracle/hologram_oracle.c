@@ -425,9 +425,9 @@ int holo_or_elementwise(int tag, const void* a, const void* b, void* out, uint64
             case 11: r = max_ref(x, 0.0f); break;
             case 21: r = sqrtf(x); break;
             case 22: r = 1.0f / x; break;
-            case 29: r = ceilf(x); break;
-            case 30: r = floorf(x); break;
-            case 31: r = roundf(x); break;
+            case 29: r = x != x ? x : ceilf(x); break;   /* libm ceilf/floorf/roundf return a NaN operand unchanged */
+            case 30: r = x != x ? x : floorf(x); break;
+            case 31: r = x != x ? x : roundf(x); break;
             case 33: r = x != x ? 1.0f : 0.0f; break;
             case 34: r = x > 0.0f ? 1.0f : x < 0.0f ? -1.0f : 0.0f; break;
             case 35: r = fabsf(x); break;
