@@ -15,6 +15,9 @@ _NP = {kc.DTYPE_F32: np.float32, kc.DTYPE_BF16: np.uint16, kc.DTYPE_F16: np.uint
 _LUT = {kc.K_SIGMOID: kc.LUT_SIGMOID, kc.K_TANH: kc.LUT_TANH, kc.K_GELU: kc.LUT_GELU, kc.K_SILU: kc.LUT_SILU,
         kc.K_EXP: kc.LUT_EXP, kc.K_ERF: kc.LUT_ERF}
 
+_REDUCE = {kc.K_REDUCE_SUM: (0, False), kc.K_REDUCE_MEAN: (0, True), kc.K_REDUCE_PROD: (1, False), kc.K_REDUCE_MIN: (2, False),
+           kc.K_REDUCE_MAX: (3, False)}
+
 
 def _get(slots, ref, nbytes, dtype):
     buf = slots[ref.slot]
@@ -55,6 +58,45 @@ def run(calls, slots, all_reduce=None):
             x = _get(slots, c.x, c.batch * c.feature * es(c.dtype), c.dtype)
             g = _get(slots, c.gamma, c.feature * es(c.dtype), c.dtype) if c.gamma.slot != kc.NO_SLOT else None
             _put(slots, c.output, orc.rms_norm(x, g, c.batch, c.feature, c.epsilon_bits, c.dtype))
+        elif k == kc.K_LAYER_NORM:
+            c = u.norm
+            row = c.feature * es(c.dtype)
+            x = _get(slots, c.x, c.batch * row, c.dtype)
+            g = _get(slots, c.gamma, row, c.dtype) if c.gamma.slot != kc.NO_SLOT else None
+            b = _get(slots, c.beta, row, c.dtype) if c.beta.slot != kc.NO_SLOT else None
+            _put(slots, c.output, orc.layer_norm(x, g, b, c.batch, c.feature, c.epsilon_bits, c.dtype))
+        elif k == kc.K_SOFTMAX:
+            c = u.softmax
+            x = _get(slots, c.input, c.batch * c.feature * es(c.dtype), c.dtype)
+            _put(slots, c.output, orc.softmax(x, c.batch, c.feature, c.dtype))
+        elif k in _REDUCE:
+            c = u.reduce
+            dims = [c.dims[i] for i in range(c.rank)]
+            kind, mean = _REDUCE[k]
+            _put(slots, c.output, orc.reduce(_get(slots, c.input, c.element_count * es(c.dtype), c.dtype), dims, c.axes_mask, kind, mean, c.dtype))
+        elif k in (kc.K_EXPAND, kc.K_BROADCAST_BINARY):
+            c = u.expand if k == kc.K_EXPAND else u.broadcast_binary
+            ind, outd = [c.in_dims[i] for i in range(c.rank)], [c.out_dims[i] for i in range(c.rank)]
+            small = _get(slots, c.input if k == kc.K_EXPAND else c.small, int(np.prod(ind)) * es(c.dtype), c.dtype)
+            if k == kc.K_EXPAND:
+                _put(slots, c.output, orc.broadcast(small, None, ind, outd, es(c.dtype)))
+            else:
+                other = _get(slots, c.other, int(np.prod(outd)) * es(c.dtype), c.dtype)
+                _put(slots, c.output, orc.broadcast(small, other, ind, outd, es(c.dtype), c.op, bool(c.small_is_lhs), c.dtype))
+        elif k in kc.EXACT_UNARY:
+            c = u.unary
+            _put(slots, c.output, orc.elementwise(k, _get(slots, c.input, c.element_count * es(c.dtype), c.dtype), None, c.dtype))
+        elif k in kc.EXACT_BINARY:
+            c = u.binary
+            n = c.element_count * es(c.dtype)
+            _put(slots, c.output, orc.elementwise(k, _get(slots, c.a, n, c.dtype), _get(slots, c.b, n, c.dtype), c.dtype))
+        elif k == kc.K_ATTENTION:
+            c = u.attention
+            hkv = c.kv_heads or c.heads
+            q = _get(slots, c.q, c.batch * c.heads * c.seq * c.head_dim * es(c.dtype), c.dtype)
+            kk = _get(slots, c.k, c.batch * hkv * c.seq * c.head_dim * es(c.dtype), c.dtype)
+            v = _get(slots, c.v, c.batch * hkv * c.seq * c.head_dim * es(c.dtype), c.dtype)
+            _put(slots, c.output, orc.attention(q, kk, v, c.batch, c.heads, c.kv_heads, c.seq, c.head_dim, bool(c.causal), c.scale_bits, c.dtype))
         elif k == kc.K_CONCAT:
             c = u.binary
             a = slots[c.a.slot][c.a.offset:c.a.offset + c.a.length] if c.a.length else slots[c.a.slot][c.a.offset:]
