@@ -186,7 +186,9 @@ struct GemmSmem {
     static constexpr uint32_t TOTAL = BARS + 256 + 1024;
 };
 
-template <int BN, int STAGES, int A_ROWS, bool F16>
+// AR: the instantiation whose epilogue carries the tensor-parallel sum; the plain one compiles none of it
+// (a run-time test in the epilogue cost the 4096^3 product a tenth of its time).
+template <int BN, int STAGES, int A_ROWS, bool F16, bool AR>
 __global__ void __launch_bounds__(GEMM_THREADS)
 matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
     using S = GemmSmem<BN, STAGES, A_ROWS>;
@@ -225,7 +227,7 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *s_tmem;
     holo_pdl_wait();  // barriers and TMEM were set up while the previous kernel drained
-    const uint32_t ar_epoch = p.ar_world > 1 ? *reinterpret_cast<volatile uint32_t*>(p.ar_state) + 1 : 0;
+    const uint32_t ar_epoch = (AR && p.ar_world > 1) ? *reinterpret_cast<volatile uint32_t*>(p.ar_state) + 1 : 0;
     const uint64_t ar_units = ((uint64_t)p.m * p.n) >> 2;
 
     if (warp == 0) {
@@ -302,7 +304,7 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     }
                 }
             }
-        } else if (ok && p.splits == 1 && p.ar_world > 1) {
+        } else if (ok && p.splits == 1 && (AR && p.ar_world > 1)) {
             // tensor-parallel sum in the epilogue: first push every unit of this thread's row, then
             // collect the peers' units (the NVLink latency of all pushes overlaps)
             const GemmSeg sg = p.seg[0];
@@ -435,7 +437,7 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     }
                 }
             } else
-            for (int pass = p.ar_world > 1 ? 0 : 1; pass < 2; ++pass)
+            for (int pass = (AR && p.ar_world > 1) ? 0 : 1; pass < 2; ++pass)
             for (uint32_t rl = rank + S_ * ew; rl < rows_valid; rl += S_ * 4) {
                 for (uint32_t u = lane; u < BN / 4; u += 32) {
                     const uint32_t off = rl * (BN * 4) + ((u ^ (rl & 7u)) * 16);
@@ -460,7 +462,7 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         const uint64_t idx = (uint64_t)grow * (sg.col_end - sg.col_begin) + (col - sg.col_begin);
                         uint16_t* dst = sg.out + idx;
                         float a4[4] = {acc.x, acc.y, acc.z, acc.w};
-                        if (p.ar_world > 1) {
+                        if ((AR && p.ar_world > 1)) {
                             // this rank's narrowed partial goes to the peers in the first pass; in the
                             // second the sums over the ranks replace it (single segment: idx = row * n + col)
                             const uint2 mine = ar_pack<F16>(a4);
@@ -499,7 +501,7 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
     }
-    if (p.ar_world > 1 && threadIdx.x == 0) {
+    if ((AR && p.ar_world > 1) && threadIdx.x == 0) {
         // the launch's last CTA advances the group's epoch (every CTA has read it by then)
         const uint32_t done = atomicAdd(p.ar_state + 1, 1u);
         if (done == gridDim.x * gridDim.y * gridDim.z - 1) {
@@ -568,18 +570,24 @@ int32_t make_map_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t 
     return HOLO_OK;
 }
 
-template <int BN, int STAGES, int A_ROWS, bool F16>
-int32_t launch_umma_dt(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid) {
+template <int BN, int STAGES, int A_ROWS, bool F16, bool AR>
+int32_t launch_umma_ar(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid) {
     using S = GemmSmem<BN, STAGES, A_ROWS>;
     static thread_local int configured_device = -1;
     if (configured_device != ctx->device) {
-        HOLO_CUDA(cudaFuncSetAttribute(matmul_bf16_umma_kernel<BN, STAGES, A_ROWS, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+        HOLO_CUDA(cudaFuncSetAttribute(matmul_bf16_umma_kernel<BN, STAGES, A_ROWS, F16, AR>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
         configured_device = ctx->device;
     }
     // the K slices of one output tile form a cluster along grid z
-    HOLO_CUDA(holo_launch_kernel(ctx, matmul_bf16_umma_kernel<BN, STAGES, A_ROWS, F16>, grid, dim3(GEMM_THREADS), S::TOTAL, p.splits, ma, mb, p));
+    HOLO_CUDA(holo_launch_kernel(ctx, matmul_bf16_umma_kernel<BN, STAGES, A_ROWS, F16, AR>, grid, dim3(GEMM_THREADS), S::TOTAL, p.splits, ma, mb, p));
     ctx->launches++;
     return HOLO_OK;
+}
+
+template <int BN, int STAGES, int A_ROWS, bool F16>
+int32_t launch_umma_dt(holo_b200_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid) {
+    if (p.ar_world > 1) return launch_umma_ar<BN, STAGES, A_ROWS, F16, true>(ctx, ma, mb, p, grid);
+    return launch_umma_ar<BN, STAGES, A_ROWS, F16, false>(ctx, ma, mb, p, grid);
 }
 
 template <int BN, int STAGES, int A_ROWS>
