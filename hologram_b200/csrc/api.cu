@@ -556,6 +556,25 @@ int32_t do_broadcast(holo_b200_ctx* ctx, const char* name, HoloBufferRef small_r
     return holo_launch_broadcast(ctx, small, other, out, rank, in_dims, out_dims, (uint32_t)es, other_ref ? op : -1, small_is_lhs, dtype);
 }
 
+// dequant_activation (cpu/kernels.rs:311-381)
+int32_t do_dequant_activation(holo_b200_ctx* ctx, const HoloDequantActivationCall& c, holo_b200_workspace* ws) {
+    const uint64_t n = c.element_count;
+    if (c.quant_dtype != HOLO_DTYPE_I8 && c.quant_dtype != HOLO_DTYPE_U8 && c.quant_dtype != HOLO_DTYPE_I4)
+        return holo_fail_slot(c.input.slot, "dequant_activation source must be i8, u8 or i4");
+    if (c.dtype != HOLO_DTYPE_F32) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: dequant_activation writes f32 (dtype %u)", c.dtype);
+    if (c.act >= HOLO_LUT_COUNT) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: dequant_activation: unknown activation id %u", c.act);
+    const uint64_t in_bytes = c.quant_dtype == HOLO_DTYPE_I4 ? (n + 1) / 2 : n;
+    uint8_t *in, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, 0, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.input, in_bytes, &in, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, n * 4, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, n * 4}, c.output.slot, {{in, in_bytes}}));
+    if (((uintptr_t)out & 3u) != 0) return holo_fail_slot(c.output.slot, "dequant_activation output must be 4-byte aligned on the device");
+    float scale;
+    memcpy(&scale, &c.scale_bits, 4);
+    return holo_launch_dequant_activation(ctx, in, (float*)out, n, c.quant_dtype, c.act, scale, c.zero_point);
+}
+
 // reduce_float (cpu/float_kernels.rs:1901-2022)
 uint64_t reduce_out_count(const HoloReduceCall& c) {
     uint64_t out = 1;
@@ -873,6 +892,7 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         }
         case HOLO_K_DEQUANTIZE: return do_dequantize(ctx, call->u.dequantize, ws);
         case HOLO_K_KV_CACHE_WRITE: return do_kv_write(ctx, call->u.kv_cache_write, ws);
+        case HOLO_K_DEQUANT_ACTIVATION: return do_dequant_activation(ctx, call->u.dequant_activation, ws);
         case HOLO_K_ATTENTION: return do_attention_legacy(ctx, call->u.attention, ws);
         case HOLO_K_DECODE_ATTENTION: return do_attention_mask(ctx, call->u.decode_attention, ws);
         case HOLO_K_DECODE_ATTENTION_VALID: return do_attention(ctx, call->u.decode_attention_valid, ws);
@@ -961,6 +981,10 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             l->out(&t.output, (uint64_t)t.batch * t.heads * t.seq * t.head_dim * holo_dtype_size(t.dtype));
             return true;
         }
+        case HOLO_K_DEQUANT_ACTIVATION:
+            l->in(&c->u.dequant_activation.input);
+            l->out(&c->u.dequant_activation.output, c->u.dequant_activation.element_count * 4);
+            return true;
         case HOLO_K_SOFTMAX:
             l->in(&c->u.softmax.input);
             l->out(&c->u.softmax.output, (uint64_t)c->u.softmax.batch * c->u.softmax.feature * holo_dtype_size(c->u.softmax.dtype));

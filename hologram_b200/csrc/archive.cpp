@@ -98,6 +98,12 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             for (uint32_t i = 0; i < c.rank; ++i) c.dims[i] = r.u32();
             break;
         }
+        case HOLO_K_DEQUANT_ACTIVATION: {
+            HoloDequantActivationCall& c = out->u.dequant_activation;
+            c.input = r.buf(); c.output = r.buf(); c.element_count = r.u64(); c.quant_dtype = r.u8(); c.act = r.u8(); c.dtype = r.u8();
+            c.scale_bits = r.u32(); c.zero_point = (int32_t)r.u32();
+            break;
+        }
         case HOLO_K_ATTENTION: {
             HoloAttentionCall& c = out->u.attention;
             c.q = r.buf(); c.k = r.buf(); c.v = r.buf(); c.output = r.buf();

@@ -181,6 +181,8 @@ int32_t holo_launch_layer_norm(holo_b200_ctx* ctx, const void* x, const void* ga
                                uint32_t feature, float eps, uint8_t dtype);
 int32_t holo_launch_broadcast(holo_b200_ctx* ctx, const uint8_t* small, const uint8_t* other, uint8_t* out, uint32_t rank,
                               const uint32_t* in_dims, const uint32_t* out_dims, uint32_t es, int op, int small_is_lhs, uint8_t dtype);
+int32_t holo_launch_dequant_activation(holo_b200_ctx* ctx, const uint8_t* in, float* out, uint64_t n, uint8_t quant_dtype, uint8_t act,
+                                       float scale, int32_t zero_point);
 int32_t holo_launch_reduce(holo_b200_ctx* ctx, const void* in, void* out, uint32_t rank, const uint32_t* dims, uint32_t axes_mask,
                            uint64_t n, int kind, int mean, uint8_t dtype);
 int32_t holo_launch_softmax(holo_b200_ctx* ctx, const void* x, void* out, uint32_t batch, uint32_t feature, uint8_t dtype);

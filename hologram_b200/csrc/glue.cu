@@ -198,6 +198,45 @@ __global__ void transpose_kernel(const uint8_t* __restrict__ in, uint8_t* __rest
     }
 }
 
+// dequant_activation, cpu/kernels.rs:311-381: the composition activation((q - zp) * scale) has at most 256
+// distinct inputs, so every CTA builds the table of all of them in shared memory (one entry per thread,
+// the same f32 arithmetic and scalar activation as dequantize followed by the unary call) and then
+// streams: 1 byte in, 4 bytes out per element (i4: two elements per byte, low nibble first).
+__global__ void __launch_bounds__(256)
+dequant_activation_kernel(const uint8_t* __restrict__ in, float* __restrict__ out, uint64_t n, int quant_dtype, int act, float scale, int zp) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    __shared__ float s_table[256];
+    {
+        const int raw = threadIdx.x;
+        int q = raw;
+        if (quant_dtype == HOLO_DTYPE_I8) q = (int)(int8_t)raw;
+        else if (quant_dtype == HOLO_DTYPE_I4) q = (raw & 15) >= 8 ? (raw & 15) - 16 : (raw & 15);
+        s_table[raw] = holo::lut_act_ref(act, __fmul_rn(__int2float_rn(q - zp), scale));
+    }
+    __syncthreads();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, t0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (quant_dtype == HOLO_DTYPE_I4) {
+        for (uint64_t b = t0; b < (n + 1) / 2; b += stride) {
+            const uint8_t byte = in[b];
+            out[2 * b] = s_table[byte & 15];
+            if (2 * b + 1 < n) out[2 * b + 1] = s_table[byte >> 4];
+        }
+        return;
+    }
+    const bool vec = (((uintptr_t)in | (uintptr_t)out) & 15u) == 0;
+    const uint64_t nvec = vec ? n >> 4 : 0;
+    for (uint64_t v = t0; v < nvec; v += stride) {
+        const uint4 w = reinterpret_cast<const uint4*>(in)[v];
+        const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            reinterpret_cast<float4*>(out)[v * 4 + j] = make_float4(s_table[words[j] & 255u], s_table[(words[j] >> 8) & 255u],
+                                                                    s_table[(words[j] >> 16) & 255u], s_table[words[j] >> 24]);
+    }
+    for (uint64_t i = (nvec << 4) + t0; i < n; i += stride) out[i] = s_table[in[i]];
+}
+
 // reduce_float, cpu/float_kernels.rs:1901-2022 (ReducePlan :2024-2099). kind 0 sum, 1 prod, 2 min, 3 max.
 struct ReduceParams {
     uint32_t kept_dims[8], red_dims[8];
@@ -758,6 +797,17 @@ int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* resi
     } else {
         HOLO_CUDA(holo_launch_kernel(ctx, rms_norm_kernel, dim3(batch), dim3(256), 0, 1, x, residual, gamma, out, feature, eps, (int)dtype));
     }
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_dequant_activation(holo_b200_ctx* ctx, const uint8_t* in, float* out, uint64_t n, uint8_t quant_dtype, uint8_t act,
+                                       float scale, int32_t zero_point) {
+    if (n == 0) return HOLO_OK;
+    const uint64_t units = quant_dtype == HOLO_DTYPE_I4 ? (n + 1) / 2 : (n + 15) / 16;
+    const uint64_t want = (units + 255) / 256, cap = (uint64_t)ctx->sm_count * 8;
+    HOLO_CUDA(holo_launch_kernel(ctx, dequant_activation_kernel, dim3((uint32_t)(want < cap ? want : cap)), dim3(256), 0, 1, in, out, n,
+                                 (int)quant_dtype, (int)act, scale, (int)zero_point));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }

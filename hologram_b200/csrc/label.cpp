@@ -115,6 +115,12 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
             for (uint32_t i = 0; i < c.rank && i < 8; ++i) b.u32(c.dims[i]);
             return true;
         }
+        case HOLO_K_DEQUANT_ACTIVATION: {
+            const HoloDequantActivationCall& c = u.dequant_activation;
+            sig->opcode = 113;
+            b.u64(c.element_count).u8(c.quant_dtype).u8(c.act).u8(c.dtype).u32(c.scale_bits).u32((uint32_t)c.zero_point);
+            return true;
+        }
         case HOLO_K_ATTENTION: {
             const HoloAttentionCall& c = u.attention;
             sig->opcode = 68;
@@ -236,6 +242,7 @@ bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* input
         case HOLO_K_SOFTMAX: in(u.softmax.input); *output = u.softmax.output.slot; return true;
         case HOLO_K_REDUCE_SUM: case HOLO_K_REDUCE_MEAN: case HOLO_K_REDUCE_PROD: case HOLO_K_REDUCE_MIN: case HOLO_K_REDUCE_MAX:
             in(u.reduce.input); *output = u.reduce.output.slot; return true;
+        case HOLO_K_DEQUANT_ACTIVATION: in(u.dequant_activation.input); *output = u.dequant_activation.output.slot; return true;
         case HOLO_K_ATTENTION: in(u.attention.q); in(u.attention.k); in(u.attention.v); *output = u.attention.output.slot; return true;
         case HOLO_K_EXPAND: in(u.expand.input); *output = u.expand.output.slot; return true;
         case HOLO_K_BROADCAST_BINARY: in(u.broadcast_binary.small); in(u.broadcast_binary.other); *output = u.broadcast_binary.output.slot; return true;

@@ -8,6 +8,7 @@ import ctypes as C
 # dtype tags (crates/hologram-types/src/dtype_id.rs:51-74)
 DTYPE_BOOL, DTYPE_U8, DTYPE_I8, DTYPE_U64, DTYPE_I32, DTYPE_I64 = 0, 1, 2, 3, 4, 5
 DTYPE_F16, DTYPE_BF16, DTYPE_F32, DTYPE_F64 = 6, 7, 8, 9
+DTYPE_I4 = 10     # two signed nibbles per byte, low nibble first
 
 # lut_act ids (kernel_call.rs:877-885)
 LUT_SIGMOID, LUT_TANH, LUT_GELU, LUT_SILU, LUT_EXP, LUT_ERF = 0, 1, 2, 3, 4, 5
@@ -25,7 +26,7 @@ EXACT_UNARY = (K_NEG, K_RELU, K_SQRT, K_RECIPROCAL, K_CEIL, K_FLOOR, K_ROUND, K_
 EXACT_BINARY = (K_SUB, K_DIV, K_MOD, K_MIN, K_MAX, K_EQUAL, K_LESS, K_LESS_OR_EQUAL, K_GREATER, K_GREATER_OR_EQUAL)
 K_SIGMOID, K_TANH, K_GELU, K_SILU, K_EXP, K_ERF = 12, 13, 14, 15, 18, 32
 K_MATMUL, K_RMS_NORM, K_RESHAPE, K_ROTARY = 46, 51, 60, 75
-K_LAYER_NORM, K_EXPAND, K_BROADCAST_BINARY, K_ATTENTION = 50, 72, 112, 69
+K_LAYER_NORM, K_EXPAND, K_BROADCAST_BINARY, K_ATTENTION, K_DEQUANT_ACTIVATION = 50, 72, 112, 69, 113
 BROADCAST_ADD, BROADCAST_SUB, BROADCAST_MUL = 0, 1, 2
 K_REDUCE_SUM, K_REDUCE_MEAN, K_REDUCE_PROD, K_REDUCE_MIN, K_REDUCE_MAX = 55, 56, 57, 58, 59
 K_ADD_RMS_NORM, K_TRANSPOSE, K_CONCAT, K_SLICE, K_SOFTMAX = 54, 61, 62, 63, 64
@@ -114,6 +115,12 @@ class LayoutCall(C.Structure):
 
 class SoftmaxCall(C.Structure):
     _fields_ = [("input", BufferRef), ("output", BufferRef), ("batch", C.c_uint32), ("feature", C.c_uint32), ("dtype", C.c_uint8)]
+
+
+class DequantActivationCall(C.Structure):
+    """kernel_call.rs:265-290: out = act((q - zero_point) * scale), i8 / u8 / i4 in, f32 out; act is a LUT_* id."""
+    _fields_ = [("input", BufferRef), ("output", BufferRef), ("element_count", C.c_uint64), ("quant_dtype", C.c_uint8),
+                ("act", C.c_uint8), ("dtype", C.c_uint8), ("scale_bits", C.c_uint32), ("zero_point", C.c_int32)]
 
 
 class AttentionCall(C.Structure):
@@ -239,7 +246,7 @@ class _Payload(C.Union):
     _fields_ = [("unary", UnaryCall), ("binary", BinaryCall), ("matmul", MatMulCall),
                 ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("matmul_dequant", MatMulDequantCall), ("norm", NormCall),
                 ("rope", RoPECall), ("gather", GatherCall), ("cast", CastCall), ("layout", LayoutCall),
-                ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("expand", ExpandCall), ("reduce", ReduceCall), ("attention", AttentionCall), ("broadcast_binary", BroadcastBinaryCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
+                ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("expand", ExpandCall), ("reduce", ReduceCall), ("attention", AttentionCall), ("dequant_activation", DequantActivationCall), ("broadcast_binary", BroadcastBinaryCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
                 ("decode_attention", DecodeAttentionCall),
                 ("decode_attention_valid", DecodeAttentionValidCall), ("quantize_rows_i8", QuantizeRowsI8Call),
                 ("decode_attention_valid_q8", DecodeAttentionValidQ8Call), ("all_reduce", AllReduceCall),
@@ -303,6 +310,8 @@ class KernelCall(C.Structure):
     @classmethod
     def Attention(cls, c): return cls.of(K_ATTENTION, c)
     @classmethod
+    def DequantActivation(cls, c): return cls.of(K_DEQUANT_ACTIVATION, c)
+    @classmethod
     def ReduceSum(cls, c): return cls.of(K_REDUCE_SUM, c)
     @classmethod
     def ReduceMean(cls, c): return cls.of(K_REDUCE_MEAN, c)
@@ -349,7 +358,7 @@ class KernelCall(C.Structure):
 KernelCall._FIELD = {
     UnaryCall: "unary", BinaryCall: "binary", MatMulCall: "matmul", MatMulActivationCall: "matmul_activation",
     MatMulAddCall: "matmul_add", MatMulDequantCall: "matmul_dequant", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
-    LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", ExpandCall: "expand", ReduceCall: "reduce", AttentionCall: "attention", BroadcastBinaryCall: "broadcast_binary", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
+    LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", ExpandCall: "expand", ReduceCall: "reduce", AttentionCall: "attention", DequantActivationCall: "dequant_activation", BroadcastBinaryCall: "broadcast_binary", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
     DecodeAttentionCall: "decode_attention", DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
     DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce", RopeQuantizeCall: "rope_quantize",
 }

@@ -43,6 +43,7 @@ extern "C" {
 #define HOLO_DTYPE_BF16 7
 #define HOLO_DTYPE_F32 8
 #define HOLO_DTYPE_F64 9
+#define HOLO_DTYPE_I4 10 /* two signed nibbles per byte, low nibble first; DequantActivation input only */
 
 /* ---- lut_act ids (crates/hologram-compute/src/kernel_call.rs:877-885) */
 #define HOLO_LUT_SIGMOID 0
@@ -113,6 +114,7 @@ extern "C" {
 #define HOLO_K_MATMUL_ACTIVATION 106
 #define HOLO_K_MATMUL_ADD 107
 #define HOLO_K_BROADCAST_BINARY 112
+#define HOLO_K_DEQUANT_ACTIVATION 113
 #define HOLO_K_GATHER 114
 #define HOLO_K_MATMUL_DEQUANT 116 /* the extended wire form (kernel_codec.rs D_MMDQ2); served: output-major W8A8 int8 */
 #define HOLO_K_CAST 115
@@ -206,6 +208,17 @@ typedef struct HoloSoftmaxCall {
     uint32_t batch, feature;
     uint8_t dtype;
 } HoloSoftmaxCall;
+
+/* DequantActivationCall (kernel_call.rs:265-290): out[i] = act((q[i] - zero_point) as f32 * scale) as f32 for a
+ * per-tensor-quantized i8 / u8 / i4 input; act is a HOLO_LUT_* id. The composition is one table over the 256
+ * (16) possible codes, built per launch (cpu/kernels.rs:311-381). */
+typedef struct HoloDequantActivationCall {
+    HoloBufferRef input, output;
+    uint64_t element_count;
+    uint8_t quant_dtype, act, dtype;
+    uint32_t scale_bits;
+    int32_t zero_point;
+} HoloDequantActivationCall;
 
 /* AttentionCall (kernel_call.rs:575-594): scaled dot-product attention over q [batch, heads, seq, head_dim] and
  * k, v [batch, kv_heads, seq, head_dim] (kv_heads 0 = heads; query head h reads kv head h / (heads / kv_heads));
@@ -384,6 +397,7 @@ typedef struct HoloKernelCall {
         HoloExpandCall expand;
         HoloReduceCall reduce;
         HoloAttentionCall attention;
+        HoloDequantActivationCall dequant_activation;
         HoloBroadcastBinaryCall broadcast_binary;
         HoloDequantizeCall dequantize;
         HoloKvCacheWriteCall kv_cache_write;

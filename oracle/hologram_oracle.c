@@ -198,6 +198,24 @@ static int fused_to_lut_act(int fused, int* act) {
     }
 }
 
+/* ---- DequantActivation: cpu/kernels.rs:311-381: table[code] = act((q - zp) as f32 * scale) over the 256 (16)
+ * codes, then one lookup per element; i8 codes are signed bytes, u8 unsigned, i4 signed nibbles, low first. */
+int holo_or_dequant_activation(const uint8_t* in, float* out, uint64_t n, int quant_dtype, int act, float scale, int32_t zp) {
+    float table[256];
+    if (quant_dtype != HOLO_DTYPE_I8 && quant_dtype != HOLO_DTYPE_U8 && quant_dtype != 10) return -3;
+    for (int raw = 0; raw < 256; ++raw) {
+        int q = quant_dtype == HOLO_DTYPE_I8 ? (int)(int8_t)raw : quant_dtype == HOLO_DTYPE_U8 ? raw : ((raw & 15) >= 8 ? (raw & 15) - 16 : (raw & 15));
+        table[raw] = holo_or_act(act, (float)(q - zp) * scale);
+    }
+    for (uint64_t i = 0; i < n; ++i) {
+        if (quant_dtype == 10) {
+            uint8_t byte = in[i / 2];
+            out[i] = table[(i & 1) ? (byte >> 4) : (byte & 15)];
+        } else out[i] = table[in[i]];
+    }
+    return 0;
+}
+
 /* ---- LUT: cpu/lut.rs:43-98 ---------------------------------------------------------- */
 
 /* cpu/lut.rs:43-67: entry = narrow(f(widen(bits))) for all 65536 patterns. */

@@ -39,6 +39,7 @@ def _load(path):
         "holo_or_binary": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_rms_norm": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
         "holo_or_add_rms_norm": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
+        "holo_or_dequant_activation": (C.c_int, [_c, _c, C.c_uint64, C.c_int, C.c_int, C.c_float, C.c_int32]),
         "holo_or_elementwise": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_reduce": (C.c_int, [_c, _c, C.c_uint64, C.c_uint32, _c, C.c_uint32, C.c_int, C.c_int, C.c_int]),
         "holo_or_broadcast": (C.c_int, [_c, _c, _c, C.c_uint32, _c, _c, C.c_uint32, C.c_int, C.c_int, C.c_int]),
@@ -145,6 +146,14 @@ def binary(op, a, b, dtype):
     b = np.ascontiguousarray(b)
     out = np.empty_like(a)
     assert lib.holo_or_binary(op, _p(a), _p(b), _p(out), a.size, dtype) == 0
+    return out
+
+
+def dequant_activation(codes, n, quant_dtype, act, scale, zero_point):
+    codes = np.ascontiguousarray(codes).view(np.uint8)
+    out = np.empty(n, dtype=np.float32)
+    rc = lib.holo_or_dequant_activation(_p(codes), _p(out), n, quant_dtype, act, float(np.float32(scale)), zero_point)
+    assert rc == 0, rc
     return out
 
 

@@ -71,6 +71,10 @@ def test_every_served_glue_variant_survives_the_wire():
         kc.KernelCall.Expand(kc.ExpandCall.make(rb(0), rb(1), (1, 8), (4, 8), kc.DTYPE_BF16)),
         kc.KernelCall.BroadcastBinary(kc.BroadcastBinaryCall.make(rb(0), rb(1), rb(2), (1, 8), (4, 8), kc.BROADCAST_MUL, True, kc.DTYPE_F32)),
         kc.KernelCall.Transpose(kc.TransposeCall.make(rb(0), rb(1), (2, 3, 4), (2, 0, 1), kc.DTYPE_F32)),
+        kc.KernelCall.Attention(kc.AttentionCall(rb(0), rb(1), rb(2), rb(3), 1, 8, 31, 8, 1, 1, 0, kc.DTYPE_F32)),
+        kc.KernelCall.DequantActivation(kc.DequantActivationCall(rb(0), rb(1), 256, kc.DTYPE_I8, kc.LUT_GELU, kc.DTYPE_F32, 0x3D4CCCCD, -7)),
+        kc.KernelCall.Elementwise(kc.K_DIV, kc.BinaryCall(rb(0), rb(1), rb(2), 9, 0, kc.DTYPE_F32)),
+        kc.KernelCall.Elementwise(kc.K_SQRT, kc.UnaryCall(rb(0), rb(1), 9, 0, kc.DTYPE_BF16)),
     ]
     for n in range(1, len(calls) + 1):      # a misread length in call i would derail call i + 1
         img = holo.assemble([(holo.SEC_KERNEL_CALLS, [holo.encode_calls(calls[:n])]), (holo.SEC_WEIGHTS, [struct.pack("<I", 0)])])

@@ -434,3 +434,21 @@ def test_exact_elementwise_variants(backend):
             got = ws.read(2, a.nbytes, a.dtype)
             assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (tag, dt, np.flatnonzero(got.view(np.uint8) != want.view(np.uint8))[:4])
             ws.close()
+
+
+def test_dequant_activation_table(backend):
+    # dequant_activation (cpu/kernels.rs:311-381): bit-exact; every code, odd lengths, unaligned input, i4 nibbles
+    rng = np.random.default_rng(113)
+    for qd, act, n, off in ((kc.DTYPE_I8, kc.LUT_GELU, 256, 0), (kc.DTYPE_I8, kc.LUT_SILU, 1 << 20, 0), (kc.DTYPE_U8, kc.LUT_TANH, 100003, 0),
+                            (kc.DTYPE_I8, kc.LUT_SIGMOID, 5000, 3), (kc.DTYPE_I4, kc.LUT_GELU, 4097, 0)):
+        nbytes = (n + 1) // 2 if qd == kc.DTYPE_I4 else n
+        codes = np.arange(256, dtype=np.uint8) if n == 256 else rng.integers(0, 256, size=nbytes, dtype=np.uint8)
+        scale, zp = np.float32(0.05), -7
+        ws = hb.DeviceWorkspace(backend, 2)
+        ws.put(0, np.concatenate([np.zeros(off, np.uint8), codes]))
+        ws.alloc(1, n * 4)
+        call = kc.DequantActivationCall(kc.rb(0, off, nbytes), kc.rb(1), n, qd, act, kc.DTYPE_F32, int(scale.view(np.uint32)), zp)
+        backend.dispatch(kc.KernelCall.DequantActivation(call), ws)
+        want = orc.dequant_activation(codes, n, qd, act, scale, zp)
+        assert np.array_equal(ws.read(1, n * 4, np.float32).view(np.uint32), want.view(np.uint32)), (qd, act, n)
+        ws.close()

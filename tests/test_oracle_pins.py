@@ -369,6 +369,23 @@ def test_legacy_attention_restatement_meets_the_reference_conformance_cases():
         assert np.max(np.abs(got - attention_f64(q, k, v, b, h, hkv, s, d, causal, mult))) < 1e-4
 
 
+def test_dequant_activation_restatement_is_the_unfused_composition():
+    # crates/hologram-compute/tests/dequant_activation.rs:66-140: over every i8 code (scale 0.05, zero point -7)
+    # the fused table is bit-identical to Dequantize (-> f32) followed by the scalar activation
+    codes = np.arange(256, dtype=np.uint8)
+    scale, zp = np.float32(0.05), -7
+    for act in (kc.LUT_GELU, kc.LUT_SILU, kc.LUT_SIGMOID, kc.LUT_TANH):
+        fused = orc.dequant_activation(codes, 256, kc.DTYPE_I8, act, scale, zp)
+        deq = orc.dequantize(codes.view(np.int8), None, None, 0, 0, float(scale), zp, kc.DTYPE_F32)
+        unfused = np.array([orc.lib.holo_or_act(act, float(v)) for v in deq], dtype=np.float32)
+        assert np.array_equal(fused.view(np.uint32), unfused.view(np.uint32))
+    # i4: two signed nibbles per byte, low nibble first
+    packed = np.array([0x80 | 0x07, 0xF1], dtype=np.uint8)          # 7, -8, 1, -1
+    got = orc.dequant_activation(packed, 4, kc.DTYPE_I4, kc.LUT_SIGMOID, np.float32(0.5), 0)
+    want = np.array([orc.lib.holo_or_act(kc.LUT_SIGMOID, float(np.float32(q) * np.float32(0.5))) for q in (7, -8, 1, -1)], dtype=np.float32)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
 def test_mask_form_restatement_equals_scalar_form_bitwise():
     # the reference pins that a realized-length mask reproduces DecodeAttentionValid bit for bit
     # (crates/hologram-compute/tests/decode_attention_valid.rs:226-282); all-erased row = zeros
