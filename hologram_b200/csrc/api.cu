@@ -369,8 +369,9 @@ int32_t do_matmul_dequant(holo_b200_ctx* ctx, const HoloMatMulDequantCall& c, ho
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: only the output-major W8A8 form is served by this backend");
     }
     const bool per_channel = c.channels > 0 && c.scales.slot != HOLO_NO_SLOT;
-    if (c.quant_dtype != HOLO_DTYPE_I8 || !per_channel || c.channels != c.n || c.inner != 1 || c.k > 133144u)
-        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: W8A8 requires symmetric per-channel i8/i4/e8cb within the k bound (i8 is served)");
+    const bool i4 = c.quant_dtype == HOLO_DTYPE_I4;
+    if ((c.quant_dtype != HOLO_DTYPE_I8 && !i4) || !per_channel || c.channels != c.n || c.inner != 1 || c.k > 133144u || (i4 && (c.k & 1u)))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: W8A8 requires symmetric per-channel i8/i4/e8cb within the k bound (i8 and packed i4 are served)");
     int act = -1;
     if (c.act != 0) {
         if (c.act != HOLO_FUSED_GELU && c.act != HOLO_FUSED_SILU && c.act != HOLO_FUSED_SIGMOID && c.act != HOLO_FUSED_TANH && c.act != HOLO_FUSED_EXP)
@@ -378,7 +379,7 @@ int32_t do_matmul_dequant(holo_b200_ctx* ctx, const HoloMatMulDequantCall& c, ho
         act = c.act == HOLO_FUSED_GELU ? HOLO_LUT_GELU : c.act == HOLO_FUSED_SILU ? HOLO_LUT_SILU : c.act == HOLO_FUSED_SIGMOID ? HOLO_LUT_SIGMOID
               : c.act == HOLO_FUSED_TANH ? HOLO_LUT_TANH : HOLO_LUT_EXP;
     }
-    const uint64_t ab = (uint64_t)c.m * c.k * 4, wb = (uint64_t)c.n * c.k, sb = (uint64_t)c.n * 4, ob = (uint64_t)c.m * c.n * 4;
+    const uint64_t ab = (uint64_t)c.m * c.k * 4, wb = i4 ? (uint64_t)c.n * (c.k / 2) : (uint64_t)c.n * c.k, sb = (uint64_t)c.n * 4, ob = (uint64_t)c.m * c.n * 4;
     uint8_t *a, *bq, *sc, *zp = nullptr, *res = nullptr, *out;
     HOLO_TRY(holo_resolve(ws, c.output, ob, &out, nullptr));
     HOLO_TRY(holo_resolve(ws, c.a, ab, &a, nullptr));
@@ -390,7 +391,7 @@ int32_t do_matmul_dequant(holo_b200_ctx* ctx, const HoloMatMulDequantCall& c, ho
     if ((((uintptr_t)a | (uintptr_t)sc | (uintptr_t)zp | (uintptr_t)res | (uintptr_t)out) & 3u) != 0)
         return holo_fail_slot(c.a.slot, "matmul_dequant f32 operands must be 4-byte aligned on the device");
     return holo_launch_matmul_w8a8_omajor(ctx, (const float*)a, (const int8_t*)bq, (const float*)sc, (const int32_t*)zp, (const float*)res,
-                                          (float*)out, c.m, c.k, c.n, act);
+                                          (float*)out, c.m, c.k, c.n, act, i4);
 }
 
 // rms_norm_float (cpu/float_kernels.rs:1683-1756), epsilon rule :1324-1336

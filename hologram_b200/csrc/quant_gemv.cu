@@ -244,13 +244,17 @@ __device__ __forceinline__ uint32_t qs_reduce_index(uint32_t lane) {
 }
 
 // shared memory: [ROWS * k quantized rows][stages * QS_STAGE_BYTES ring][2 parities * QS_WARPS * 32 partial sums]
-//                [QS_MAX_ROWS scales][QS_WARPS maxima][abort flag][2 * QS_MAX_STAGES mbarriers]
+//                [QS_MAX_ROWS scales][QS_WARPS maxima][abort flag][QS_MAX_ROWS row sums][2 * QS_MAX_STAGES mbarriers]
 __host__ __device__ constexpr size_t qs_smem_bytes(uint32_t rows, uint32_t k, uint32_t stages) {
-    return (size_t)rows * k + (size_t)stages * QS_STAGE_BYTES + 2 * QS_WARPS * 32 * 4 + QG_MAX_ROWS * 4 + QS_WARPS * 4 + 16 + 16 * QS_MAX_STAGES;
+    return (size_t)rows * k + (size_t)stages * QS_STAGE_BYTES + 2 * QS_WARPS * 32 * 4 + QG_MAX_ROWS * 4 + QS_WARPS * 4 + 16 + QG_MAX_ROWS * 4 + 16 * QS_MAX_STAGES;
 }
 constexpr size_t QS_SMEM_LIMIT = 226 * 1024;
 
-template <int ROWS>
+// I4 (matmul_i4_pc_omajor, cpu/simd.rs:6164-6260): the weight is [n, k/2] bytes of packed signed nibbles, low
+// nibble first. A 32-bit weight word holds eight elements; (w ^ 0x88888888) & 0x0F0F0F0F are the even elements
+// plus 8 and the same of w >> 4 the odd ones, so the quantized row is kept with the even and the odd elements
+// of every eight in two separate words (two dp4a per weight word) and 8 * sum(row) is taken off at the end.
+template <int ROWS, bool I4>
 __global__ void __launch_bounds__((QS_WARPS + 1) * 32, 1)
 matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict__ bq, const float* __restrict__ scales,
                           const int32_t* __restrict__ zero_points, const float* __restrict__ residual, float* __restrict__ out,
@@ -264,10 +268,12 @@ matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict_
     float* s_scale = reinterpret_cast<float*>(s_part + 2 * QS_WARPS * 32);
     float* s_red = s_scale + QG_MAX_ROWS;
     volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(s_red + QS_WARPS);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_red + QS_WARPS + 4);
+    int* s_sum = reinterpret_cast<int*>(s_red + QS_WARPS + 4);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_sum + QG_MAX_ROWS);
     const uint32_t bar_full = qs_smem(bars), bar_empty = qs_smem(bars + QS_MAX_STAGES);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t ntiles = (n + cols_per_tile - 1) / cols_per_tile;
+    const uint32_t kw = I4 ? k >> 1 : k;   // bytes of one weight column
 
     holo_pdl_trigger();
     if (tid == 0) {
@@ -277,6 +283,7 @@ matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict_
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         *s_abort = 0;
+        for (int r = 0; r < QG_MAX_ROWS; ++r) s_sum[r] = 0;
     }
     __syncthreads();
     holo_pdl_wait();  // nothing above touches global memory
@@ -292,10 +299,10 @@ matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict_
                 break;
             }
             const uint32_t c0 = t * cols_per_tile, cols = n - c0 < cols_per_tile ? n - c0 : cols_per_tile;
-            const uint32_t bytes = cols * k;
+            const uint32_t bytes = cols * kw;
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_full + 8 * s), "r"(bytes) : "memory");
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(qs_smem(ring + (size_t)s * QS_STAGE_BYTES)), "l"(bq + (uint64_t)c0 * k), "r"(bytes), "r"(bar_full + 8 * s) : "memory");
+                         ::"r"(qs_smem(ring + (size_t)s * QS_STAGE_BYTES)), "l"(bq + (uint64_t)c0 * kw), "r"(bytes), "r"(bar_full + 8 * s) : "memory");
         }
         return;
     }
@@ -374,30 +381,50 @@ matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict_
             const int q = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
             return (uint32_t)(max(-127, min(127, q)) & 0xff);
         };
-        auto pack4 = [&](const float4& v) {
-            return amax == 0.0f ? 0u : quant1(v.x) | (quant1(v.y) << 8) | (quant1(v.z) << 16) | (quant1(v.w) << 24);
+        int qsum = 0;   // I4: the row's sum of codes
+        // the four codes of elements 4j .. 4j+3 go to their place in the row: in order (i8), or the even ones
+        // to the first and the odd ones to the second word of the eight elements they belong to (i4)
+        auto put4 = [&](uint32_t j, const float4& v) {
+            const uint32_t q0 = amax == 0.0f ? 0u : quant1(v.x), q1 = amax == 0.0f ? 0u : quant1(v.y);
+            const uint32_t q2 = amax == 0.0f ? 0u : quant1(v.z), q3 = amax == 0.0f ? 0u : quant1(v.w);
+            int8_t* base = s_q + (size_t)qrow * k;
+            if (I4) {
+                qsum += (int)(int8_t)q0 + (int)(int8_t)q1 + (int)(int8_t)q2 + (int)(int8_t)q3;
+                uint16_t* half = reinterpret_cast<uint16_t*>(base + (size_t)(j >> 1) * 8 + (j & 1) * 2);
+                half[0] = (uint16_t)(q0 | (q2 << 8));
+                half[2] = (uint16_t)(q1 | (q3 << 8));
+            } else {
+                reinterpret_cast<uint32_t*>(base)[j] = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+            }
         };
         if (qlive && a_vec) {
-            uint32_t* dst = reinterpret_cast<uint32_t*>(s_q + (size_t)qrow * k);
 #pragma unroll
             for (uint32_t u = 0; u < QB; ++u)
-                if (qtid + u * QT < nq) dst[at(qtid + u * QT)] = pack4(first[u]);
+                if (qtid + u * QT < nq) put4(at(qtid + u * QT), first[u]);
             for (uint32_t j0 = qtid + QB * QT; j0 < nq; j0 += QB * QT) {
                 float4 v[QB];
 #pragma unroll
                 for (uint32_t u = 0; u < QB; ++u) v[u] = j0 + u * QT < nq ? row4[at(j0 + u * QT)] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
                 for (uint32_t u = 0; u < QB; ++u)
-                    if (j0 + u * QT < nq) dst[at(j0 + u * QT)] = pack4(v[u]);
+                    if (j0 + u * QT < nq) put4(at(j0 + u * QT), v[u]);
             }
         } else if (qlive) {
-            for (uint32_t j = qtid; j < k; j += QT) s_q[(size_t)qrow * k + j] = (int8_t)(amax == 0.0f ? 0 : (int)(int8_t)quant1(row[j]));
+            for (uint32_t j = qtid; j < k; j += QT) {
+                const int q = amax == 0.0f ? 0 : (int)(int8_t)quant1(row[j]);
+                qsum += q;
+                s_q[(size_t)qrow * k + (I4 ? (j >> 3) * 8 + (j & 1) * 4 + ((j & 7) >> 1) : j)] = (int8_t)q;
+            }
+        }
+        if (I4) {
+            for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
+            if (qlive && lane == 0) atomicAdd(s_sum + qrow, qsum);
         }
         if (qlive && qtid == 0) s_scale[qrow] = amax == 0.0f ? 0.0f : __fdiv_rn(amax, 127.0f);
         qs_product_barrier();
     }
 
-    const uint32_t nvec = k >> 4;
+    const uint32_t nvec = kw >> 4;   // 16-byte weight units of a column
     const uint32_t ridx = qs_reduce_index<V>(lane);
     const bool rlane = (lane & ((32u / (V < 32 ? V : 32)) - 1u)) == 0;   // one lane per value index stores the warp's sum
     for (uint32_t i = group; ; i += QS_GROUPS) {
@@ -420,6 +447,37 @@ matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict_
             const int4* tile = reinterpret_cast<const int4*>(ring + (size_t)s * QS_STAGE_BYTES);
 #pragma unroll 2
             for (uint32_t v = gwarp * 32 + lane; v < nvec; v += QS_GROUP_WARPS * 32) {
+                if (I4) {
+                    // one 16-byte weight unit = 32 elements = 32 bytes of the row: words (even, odd) x 4
+                    int4 qa[ROWS], qb[ROWS];
+#pragma unroll
+                    for (int r = 0; r < ROWS; ++r) {
+                        qa[r] = *reinterpret_cast<const int4*>(s_q + (size_t)r * k + (size_t)v * 32);
+                        qb[r] = *reinterpret_cast<const int4*>(s_q + (size_t)r * k + (size_t)v * 32 + 16);
+                    }
+#pragma unroll
+                    for (int c = 0; c < QS_MAX_COLS; ++c) {
+                        if ((uint32_t)c < cols) {
+                            const int4 w = tile[(size_t)c * nvec + v];
+                            const uint32_t x0 = (uint32_t)w.x ^ 0x88888888u, x1 = (uint32_t)w.y ^ 0x88888888u;
+                            const uint32_t x2 = (uint32_t)w.z ^ 0x88888888u, x3 = (uint32_t)w.w ^ 0x88888888u;
+#pragma unroll
+                            for (int r = 0; r < ROWS; ++r) {
+                                int x = acc[c * ROWS + r];
+                                x = __dp4a((int)(x0 & 0x0F0F0F0Fu), qa[r].x, x);
+                                x = __dp4a((int)((x0 >> 4) & 0x0F0F0F0Fu), qa[r].y, x);
+                                x = __dp4a((int)(x1 & 0x0F0F0F0Fu), qa[r].z, x);
+                                x = __dp4a((int)((x1 >> 4) & 0x0F0F0F0Fu), qa[r].w, x);
+                                x = __dp4a((int)(x2 & 0x0F0F0F0Fu), qb[r].x, x);
+                                x = __dp4a((int)((x2 >> 4) & 0x0F0F0F0Fu), qb[r].y, x);
+                                x = __dp4a((int)(x3 & 0x0F0F0F0Fu), qb[r].z, x);
+                                x = __dp4a((int)((x3 >> 4) & 0x0F0F0F0Fu), qb[r].w, x);
+                                acc[c * ROWS + r] = x;
+                            }
+                        }
+                    }
+                    continue;
+                }
                 int4 qv[ROWS];
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r) qv[r] = *reinterpret_cast<const int4*>(s_q + (size_t)r * k + (size_t)v * 16);
@@ -450,6 +508,7 @@ matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict_
             int sum = 0;
 #pragma unroll
             for (int w = 0; w < QS_GROUP_WARPS; ++w) sum += part[w * 32 + gtid];
+            if (I4) sum -= 8 * s_sum[wr];
             const uint32_t col = c0 + wc;
             if (zp != 0) atomicOr(status, 16u);   // symmetric form only
             const float sa = s_scale[wr];
@@ -461,27 +520,31 @@ matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict_
     }
 }
 
-template <int ROWS>
+template <int ROWS, bool I4>
 cudaError_t launch_stream(holo_b200_ctx* ctx, uint32_t grid, size_t smem, const float* a, const int8_t* bq, const float* scales,
                           const int32_t* zero_points, const float* residual, float* out, uint32_t m0, uint32_t rows, uint32_t k,
                           uint32_t n, uint32_t cols_per_tile, uint32_t stages, int act) {
     static thread_local int configured_device = -1;
     if (configured_device != ctx->device) {
-        cudaError_t e = cudaFuncSetAttribute(matmul_w8a8_stream_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QS_SMEM_LIMIT);
+        cudaError_t e = cudaFuncSetAttribute(matmul_w8a8_stream_kernel<ROWS, I4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QS_SMEM_LIMIT);
         if (e != cudaSuccess) return e;
         configured_device = ctx->device;
     }
-    return holo_launch_kernel(ctx, matmul_w8a8_stream_kernel<ROWS>, dim3(grid), dim3((QS_WARPS + 1) * 32), smem, 1, a, bq, scales, zero_points,
+    return holo_launch_kernel(ctx, matmul_w8a8_stream_kernel<ROWS, I4>, dim3(grid), dim3((QS_WARPS + 1) * 32), smem, 1, a, bq, scales, zero_points,
                               residual, out, m0, rows, k, n, cols_per_tile, stages, act, ctx->dev_status);
 }
 
 }  // namespace
 
 int32_t holo_launch_matmul_w8a8_omajor(holo_b200_ctx* ctx, const float* a, const int8_t* bq, const float* scales, const int32_t* zero_points,
-                                       const float* residual, float* out, uint32_t m, uint32_t k, uint32_t n, int act) {
+                                       const float* residual, float* out, uint32_t m, uint32_t k, uint32_t n, int act, bool i4) {
     if (m == 0 || k == 0 || n == 0) return HOLO_OK;
-    if ((k & 15u) == 0 && k <= QS_STAGE_BYTES && ((uintptr_t)bq & 15u) == 0 && !getenv("HOLO_W8A8_NO_STREAM")) {
-        uint32_t cols_per_tile = QS_STAGE_BYTES / k;
+    const uint32_t kw = i4 ? k >> 1 : k;   // bytes of one weight column
+    const bool streamable = (kw & 15u) == 0 && kw <= QS_STAGE_BYTES && ((uintptr_t)bq & 15u) == 0;
+    if (i4 && (!streamable || (size_t)k > 64 * 1024))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: the packed-i4 form is served for k a multiple of 32 up to 32768 and a 16-byte aligned weight");
+    if (streamable && (i4 || !getenv("HOLO_W8A8_NO_STREAM"))) {
+        uint32_t cols_per_tile = QS_STAGE_BYTES / kw;
         if (cols_per_tile > QS_MAX_COLS) cols_per_tile = QS_MAX_COLS;
         const uint32_t ntiles = (n + cols_per_tile - 1) / cols_per_tile;
         const uint32_t grid = ntiles < (uint32_t)ctx->sm_count ? ntiles : (uint32_t)ctx->sm_count;
@@ -493,10 +556,10 @@ int32_t holo_launch_matmul_w8a8_omajor(holo_b200_ctx* ctx, const float* a, const
             uint32_t stages = QS_MAX_STAGES;
             while (stages > QS_MIN_STAGES && qs_smem_bytes(rt, k, stages) > QS_SMEM_LIMIT) --stages;
             const size_t smem = qs_smem_bytes(rt, k, stages);
-            cudaError_t e = rt == 8 ? launch_stream<8>(ctx, grid, smem, a, bq, scales, zero_points, residual, out, m0, take, k, n, cols_per_tile, stages, act)
-                          : rt == 4 ? launch_stream<4>(ctx, grid, smem, a, bq, scales, zero_points, residual, out, m0, take, k, n, cols_per_tile, stages, act)
-                          : rt == 2 ? launch_stream<2>(ctx, grid, smem, a, bq, scales, zero_points, residual, out, m0, take, k, n, cols_per_tile, stages, act)
-                                    : launch_stream<1>(ctx, grid, smem, a, bq, scales, zero_points, residual, out, m0, take, k, n, cols_per_tile, stages, act);
+#define QS_LAUNCH(R, Q) launch_stream<R, Q>(ctx, grid, smem, a, bq, scales, zero_points, residual, out, m0, take, k, n, cols_per_tile, stages, act)
+            cudaError_t e = i4 ? (rt == 8 ? QS_LAUNCH(8, true) : rt == 4 ? QS_LAUNCH(4, true) : rt == 2 ? QS_LAUNCH(2, true) : QS_LAUNCH(1, true))
+                               : (rt == 8 ? QS_LAUNCH(8, false) : rt == 4 ? QS_LAUNCH(4, false) : rt == 2 ? QS_LAUNCH(2, false) : QS_LAUNCH(1, false));
+#undef QS_LAUNCH
             HOLO_CUDA(e);
             ctx->launches++;
         }

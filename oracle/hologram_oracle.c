@@ -325,6 +325,33 @@ void holo_or_matmul_i8_pc_omajor(const float* a, const int8_t* bq, const float* 
     free(q);
 }
 
+/* W4A8 output-major GEMV (matmul_i4_pc_omajor, cpu/simd.rs:6164-6260, scalar inner :6149-6160): the weight is
+ * [n, k/2] bytes of packed nibbles, element l of a column = nibble l of its span, low nibble first, nibble
+ * 0..7 -> 0..7 and 8..15 -> -8..-1 (:5664-5679); otherwise the i8 kernel: quantized row, exact i32 dot,
+ * one f32 writeback; a zero row gives a zero output row. */
+void holo_or_matmul_i4_pc_omajor(const float* a, const uint8_t* bq, const float* scales, float* out,
+                                 size_t m, size_t k, size_t n) {
+    int8_t* q = (int8_t*)malloc(k ? k : 1);
+    size_t kb = k / 2;
+    for (size_t i = 0; i < m; ++i) {
+        float sa = holo_or_quantize_row_i8(a + i * k, q, k);
+        if (sa == 0.0f) {
+            for (size_t j = 0; j < n; ++j) out[i * n + j] = 0.0f;
+            continue;
+        }
+        for (size_t j = 0; j < n; ++j) {
+            int32_t acc = 0;
+            for (size_t kk = 0; kk < k; ++kk) {
+                uint8_t byte = bq[j * kb + (kk >> 1)];
+                int nib = (kk & 1) ? (byte >> 4) : (byte & 15);
+                acc += (int32_t)q[kk] * (nib >= 8 ? nib - 16 : nib);
+            }
+            out[i * n + j] = (float)acc * (sa * scales[j]);
+        }
+    }
+    free(q);
+}
+
 /* ---- dequantize: cpu/kernels.rs:185-296 (i8 / u8 source, per-channel or per-tensor) -- */
 int holo_or_dequantize(const void* in, int quant_dtype, const float* scales, const int32_t* zps,
                        uint32_t channels, uint32_t inner, float scale, int32_t zp,

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 F32, I8 = kc.DTYPE_F32, kc.DTYPE_I8
 
 
-def run(backend, a, bq, scales, m, k, n, residual=None, act=0, zero_points=None):
+def run(backend, a, bq, scales, m, k, n, residual=None, act=0, zero_points=None, quant=I8):
     ws = hb.DeviceWorkspace(backend, 6)
     ws.put(0, a)
     ws.put(1, bq)
@@ -23,7 +23,7 @@ def run(backend, a, bq, scales, m, k, n, residual=None, act=0, zero_points=None)
     if residual is not None:
         ws.put(5, residual)
         res = kc.rb(5)
-    call = kc.MatMulDequantCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), m, k, n, n, 1, I8, F32, 0, 0, 1, 1, act, res)
+    call = kc.MatMulDequantCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), m, k, n, n, 1, quant, F32, 0, 0, 1, 1, act, res)
     backend.dispatch(kc.KernelCall.MatMulDequant(call), ws)
     out = ws.read(4, m * n * 4, np.float32).copy()
     ws.close()
@@ -84,3 +84,26 @@ def test_epilogue_and_refusals(backend):
     zp[5] = 3
     with pytest.raises(hb.BackendError):
         run(backend, a, bq, scales, m, k, n, zero_points=zp)
+
+
+def test_packed_i4_reference_golden_and_bit_exactness(backend):
+    # W4A8: [n, k/2] packed signed nibbles, low nibble first (matmul_i4_pc_omajor, cpu/simd.rs:6164-6260); the
+    # reference's FNV golden for this tier (:8257-8265), then seeded shapes against the CPU kernel
+    m, k, n = 3, 64, 24
+    a = (np.array([float(i * 37 % 91) for i in range(m * k)], dtype=np.float32) - np.float32(45.0)) * np.float32(0.031)
+    scales = np.float32(0.011) + np.arange(n, dtype=np.float32) * np.float32(0.0007)
+    bq4 = np.array([(i * 53 + 9) % 251 for i in range(k * n // 2)], dtype=np.uint8)
+    assert orc.fnv1a64_f32(run(backend, a, bq4, scales, m, k, n, quant=kc.DTYPE_I4)) == 0x4C5123C024AF97AE
+    for m, k, n in ((1, 4096, 14336), (4, 4096, 1001), (2, 14336, 130), (8, 1024, 77), (9, 512, 37), (1, 32768, 5), (3, 32, 3)):
+        rng = np.random.default_rng(m * 11 + n)
+        a = rng.standard_normal(m * k).astype(np.float32)
+        if m > 1:
+            a[:k] = 0.0
+        bq = rng.integers(0, 256, size=n * k // 2, dtype=np.uint8)
+        scales = (rng.random(n).astype(np.float32) + np.float32(0.01)) * np.float32(0.02)
+        got = run(backend, a, bq, scales, m, k, n, quant=kc.DTYPE_I4)
+        want = orc.matmul_w8a8_omajor(a, bq, scales, m, k, n, i4=True)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (m, k, n)
+    with pytest.raises(hb.BackendError) as e:      # k = 48: columns of 24 bytes do not stream in 16-byte units
+        run(backend, np.ones(48, np.float32), np.zeros(48, np.uint8), np.ones(2, np.float32), 1, 48, 2, quant=kc.DTYPE_I4)
+    assert e.value.variant == "UnsupportedOp"
