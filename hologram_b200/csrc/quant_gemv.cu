@@ -192,7 +192,8 @@ constexpr int QS_WARPS = QS_GROUPS * QS_GROUP_WARPS;   // product warps; warp QS
 constexpr int QS_MAX_STAGES = 12;             // as many as fit beside the quantized rows: the ring must cover DRAM latency plus the tiles being consumed
 constexpr int QS_MIN_STAGES = 5;
 constexpr uint32_t QS_STAGE_BYTES = 16384;
-constexpr int QS_MAX_COLS = 4;                 // columns per tile
+constexpr int QS_MAX_COLS = 4;                 // columns per tile (8 for the packed-i4 weight up to four rows: its columns are half as long)
+__host__ __device__ constexpr int qs_max_cols(int rows, bool i4) { return i4 && rows <= 4 ? 2 * QS_MAX_COLS : QS_MAX_COLS; }
 constexpr uint32_t QS_WAIT_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t qs_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -259,7 +260,8 @@ __global__ void __launch_bounds__((QS_WARPS + 1) * 32, 1)
 matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict__ bq, const float* __restrict__ scales,
                           const int32_t* __restrict__ zero_points, const float* __restrict__ residual, float* __restrict__ out,
                           uint32_t m0, uint32_t rows, uint32_t k, uint32_t n, uint32_t cols_per_tile, uint32_t stages, int act, uint32_t* status) {
-    constexpr int V = QS_MAX_COLS * ROWS;      // sums per tile
+    constexpr int MAXC = qs_max_cols(ROWS, I4);
+    constexpr int V = MAXC * ROWS;             // sums per tile
     static_assert(V <= 32, "one partial slot per lane");
     extern __shared__ __align__(128) unsigned char qs_mem[];
     int8_t* s_q = reinterpret_cast<int8_t*>(qs_mem);
@@ -456,7 +458,7 @@ matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict_
                         qb[r] = *reinterpret_cast<const int4*>(s_q + (size_t)r * k + (size_t)v * 32 + 16);
                     }
 #pragma unroll
-                    for (int c = 0; c < QS_MAX_COLS; ++c) {
+                    for (int c = 0; c < MAXC; ++c) {
                         if ((uint32_t)c < cols) {
                             const int4 w = tile[(size_t)c * nvec + v];
                             const uint32_t x0 = (uint32_t)w.x ^ 0x88888888u, x1 = (uint32_t)w.y ^ 0x88888888u;
@@ -482,7 +484,7 @@ matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict_
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r) qv[r] = *reinterpret_cast<const int4*>(s_q + (size_t)r * k + (size_t)v * 16);
 #pragma unroll
-                for (int c = 0; c < QS_MAX_COLS; ++c) {
+                for (int c = 0; c < MAXC; ++c) {
                     if ((uint32_t)c < cols) {
                         const int4 w = tile[(size_t)c * nvec + v];
 #pragma unroll
@@ -544,15 +546,15 @@ int32_t holo_launch_matmul_w8a8_omajor(holo_b200_ctx* ctx, const float* a, const
     if (i4 && (!streamable || (size_t)k > 64 * 1024))
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: the packed-i4 form is served for k a multiple of 32 up to 32768 and a 16-byte aligned weight");
     if (streamable && (i4 || !getenv("HOLO_W8A8_NO_STREAM"))) {
-        uint32_t cols_per_tile = QS_STAGE_BYTES / kw;
-        if (cols_per_tile > QS_MAX_COLS) cols_per_tile = QS_MAX_COLS;
-        const uint32_t ntiles = (n + cols_per_tile - 1) / cols_per_tile;
-        const uint32_t grid = ntiles < (uint32_t)ctx->sm_count ? ntiles : (uint32_t)ctx->sm_count;
         uint32_t per = QG_MAX_ROWS;   // rows per launch: what fits beside the ring in shared memory
         while (per > 1 && qs_smem_bytes(per, k, QS_MIN_STAGES) > QS_SMEM_LIMIT) per >>= 1;
         for (uint32_t m0 = 0; m0 < m; m0 += per) {
             const uint32_t take = m - m0 < per ? m - m0 : per;
             const uint32_t rt = take > 4 ? 8 : take > 2 ? 4 : take;
+            uint32_t cols_per_tile = QS_STAGE_BYTES / kw;
+            if (cols_per_tile > (uint32_t)qs_max_cols((int)rt, i4)) cols_per_tile = (uint32_t)qs_max_cols((int)rt, i4);
+            const uint32_t ntiles = (n + cols_per_tile - 1) / cols_per_tile;
+            const uint32_t grid = ntiles < (uint32_t)ctx->sm_count ? ntiles : (uint32_t)ctx->sm_count;
             uint32_t stages = QS_MAX_STAGES;
             while (stages > QS_MIN_STAGES && qs_smem_bytes(rt, k, stages) > QS_SMEM_LIMIT) --stages;
             const size_t smem = qs_smem_bytes(rt, k, stages);
