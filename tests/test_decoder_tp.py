@@ -132,14 +132,18 @@ def test_tp2_on_two_gpus_matches_single_rank(tmp_path):
     assert err <= 2e-2, err
 
 
-def _tp4(tmp_path, **extra_env):
+WIDE8 = ("dh.DecoderConfig(d_model=2048, n_heads=16, n_kv_heads=8, head_dim=128, ffn=4096, vocab=4096, n_layers=2, "
+         "batch=8, bucket=128)")
+
+
+def _tp4(tmp_path, world=4, cfg=WIDE, **extra_env):
     import torch
-    if torch.cuda.device_count() < 4:
-        pytest.skip("needs 4 GPUs")
-    want = np.concatenate([r.reshape(8, -1) for r in _launch("cpu", tmp_path, 4, WIDE)], axis=1)
-    got = np.concatenate([r.reshape(8, -1) for r in _launch("gpu", tmp_path, 4, WIDE, **extra_env)], axis=1)
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    want = np.concatenate([r.reshape(8, -1) for r in _launch("cpu", tmp_path, world, cfg)], axis=1)
+    got = np.concatenate([r.reshape(8, -1) for r in _launch("gpu", tmp_path, world, cfg, **extra_env)], axis=1)
     for rep in range(3):
-        res = [np.load(tmp_path / f"allreduce_{rep}_{r}.npy") for r in range(4)]
+        res = [np.load(tmp_path / f"allreduce_{rep}_{r}.npy") for r in range(world)]
         assert all(np.array_equal(res[0], x) for x in res[1:])
     err = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
     assert err <= 2e-2, err
@@ -156,3 +160,9 @@ def test_tp4_on_four_gpus_matches_the_gloo_interpreter(tmp_path):
 def test_tp4_with_the_all_reduce_in_the_product_epilogue(tmp_path):
     # groups above two ranks take the fused product + all-reduce only when asked
     _tp4(tmp_path, HOLO_TP_FUSED_GEMM_ANY_WORLD="1")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fused", [False, True])
+def test_tp8_on_eight_gpus_matches_the_gloo_interpreter(tmp_path, fused):
+    _tp4(tmp_path, 8, WIDE8, **({"HOLO_TP_FUSED_GEMM_ANY_WORLD": "1"} if fused else {}))
