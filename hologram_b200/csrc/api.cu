@@ -369,9 +369,13 @@ int32_t do_matmul_dequant(holo_b200_ctx* ctx, const HoloMatMulDequantCall& c, ho
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: only the output-major W8A8 form is served by this backend");
     }
     const bool per_channel = c.channels > 0 && c.scales.slot != HOLO_NO_SLOT;
-    const bool i4 = c.quant_dtype == HOLO_DTYPE_I4;
-    if ((c.quant_dtype != HOLO_DTYPE_I8 && !i4) || !per_channel || c.channels != c.n || c.inner != 1 || c.k > 133144u || (i4 && (c.k & 1u)))
-        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: W8A8 requires symmetric per-channel i8/i4/e8cb within the k bound (i8 and packed i4 are served)");
+    const bool i4 = c.quant_dtype == HOLO_DTYPE_I4, e8 = c.quant_dtype == HOLO_DTYPE_E8CB;
+    if (e8 != (c.codebook.slot != HOLO_NO_SLOT))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: a codebook operand goes with the E8 codebook weight tier and only with it");
+    if (e8 && (c.k & 7u))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: k must be a multiple of 8 (whole E8 groups)");
+    if ((c.quant_dtype != HOLO_DTYPE_I8 && !i4 && !e8) || !per_channel || c.channels != c.n || c.inner != 1 || c.k > 133144u || (i4 && (c.k & 1u)))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: W8A8 requires symmetric per-channel i8/i4/e8cb within the k bound (all three are served)");
     int act = -1;
     if (c.act != 0) {
         if (c.act != HOLO_FUSED_GELU && c.act != HOLO_FUSED_SILU && c.act != HOLO_FUSED_SIGMOID && c.act != HOLO_FUSED_TANH && c.act != HOLO_FUSED_EXP)
@@ -379,9 +383,10 @@ int32_t do_matmul_dequant(holo_b200_ctx* ctx, const HoloMatMulDequantCall& c, ho
         act = c.act == HOLO_FUSED_GELU ? HOLO_LUT_GELU : c.act == HOLO_FUSED_SILU ? HOLO_LUT_SILU : c.act == HOLO_FUSED_SIGMOID ? HOLO_LUT_SIGMOID
               : c.act == HOLO_FUSED_TANH ? HOLO_LUT_TANH : HOLO_LUT_EXP;
     }
-    const uint64_t ab = (uint64_t)c.m * c.k * 4, wb = i4 ? (uint64_t)c.n * (c.k / 2) : (uint64_t)c.n * c.k, sb = (uint64_t)c.n * 4, ob = (uint64_t)c.m * c.n * 4;
-    uint8_t *a, *bq, *sc, *zp = nullptr, *res = nullptr, *out;
+    const uint64_t ab = (uint64_t)c.m * c.k * 4, wb = e8 ? (uint64_t)c.n * (c.k / 8) : i4 ? (uint64_t)c.n * (c.k / 2) : (uint64_t)c.n * c.k, sb = (uint64_t)c.n * 4, ob = (uint64_t)c.m * c.n * 4;
+    uint8_t *a, *bq, *sc, *zp = nullptr, *res = nullptr, *out, *cb = nullptr;
     HOLO_TRY(holo_resolve(ws, c.output, ob, &out, nullptr));
+    if (e8) HOLO_TRY(holo_resolve(ws, c.codebook, 2048, &cb, nullptr));   // the full index space: 256 entries x 8 coordinates
     HOLO_TRY(holo_resolve(ws, c.a, ab, &a, nullptr));
     HOLO_TRY(holo_resolve(ws, c.bq, wb, &bq, nullptr));
     HOLO_TRY(holo_resolve(ws, c.scales, sb, &sc, nullptr));
@@ -390,6 +395,9 @@ int32_t do_matmul_dequant(holo_b200_ctx* ctx, const HoloMatMulDequantCall& c, ho
     HOLO_TRY(check_disjoint({out, ob}, c.output.slot, {{a, ab}, {bq, wb}, {sc, sb}, {zp, zp ? sb : 0}, {res, res ? ob : 0}}));
     if ((((uintptr_t)a | (uintptr_t)sc | (uintptr_t)zp | (uintptr_t)res | (uintptr_t)out) & 3u) != 0)
         return holo_fail_slot(c.a.slot, "matmul_dequant f32 operands must be 4-byte aligned on the device");
+    if (e8)
+        return holo_launch_matmul_e8cb_omajor(ctx, (const float*)a, bq, (const int8_t*)cb, (const float*)sc, (const int32_t*)zp, (const float*)res,
+                                              (float*)out, c.m, c.k, c.n, act);
     return holo_launch_matmul_w8a8_omajor(ctx, (const float*)a, (const int8_t*)bq, (const float*)sc, (const int32_t*)zp, (const float*)res,
                                           (float*)out, c.m, c.k, c.n, act, i4);
 }
@@ -867,7 +875,7 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         case HOLO_K_MATMUL: return do_matmul(ctx, call->u.matmul, 0, nullptr, ws);
         case HOLO_K_MATMUL_ACTIVATION: return do_matmul(ctx, call->u.matmul_activation.mm, call->u.matmul_activation.act, nullptr, ws);
         case HOLO_K_MATMUL_ADD: return do_matmul(ctx, call->u.matmul_add.mm, 0, &call->u.matmul_add.residual, ws);
-        case HOLO_K_MATMUL_DEQUANT: return do_matmul_dequant(ctx, call->u.matmul_dequant, ws);
+        case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: return do_matmul_dequant(ctx, call->u.matmul_dequant, ws);
         case HOLO_K_LAYER_NORM: return do_norm(ctx, call->u.norm, false, true, ws);
         case HOLO_K_RMS_NORM: return do_norm(ctx, call->u.norm, false, false, ws);
         case HOLO_K_ADD_RMS_NORM: return do_norm(ctx, call->u.norm, true, false, ws);
@@ -1066,9 +1074,10 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             l->out(&q.scales, q.rows * 4);
             return true;
         }
-        case HOLO_K_MATMUL_DEQUANT: {
+        case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
             auto& q = c->u.matmul_dequant;
             l->in(&q.a); l->in(&q.bq); l->in(&q.scales); l->in(&q.zero_points); l->in(&q.residual);
+            if (c->kind == HOLO_K_MATMUL_DEQUANT_CODEBOOK) l->in(&q.codebook);
             l->out(&q.output, (uint64_t)q.m * q.n * holo_dtype_size(q.dtype));
             return true;
         }

@@ -192,11 +192,13 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             c.head_dim = r.u32(); c.scale_bits = r.u32(); c.dtype = r.u8();
             break;
         }
-        case HOLO_K_MATMUL_DEQUANT: {
+        case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
             HoloMatMulDequantCall& c = out->u.matmul_dequant;
             c.a = r.buf(); c.bq = r.buf(); c.scales = r.buf(); c.zero_points = r.buf(); c.output = r.buf();
             c.m = r.u32(); c.k = r.u32(); c.n = r.u32(); c.channels = r.u32(); c.inner = r.u32(); c.quant_dtype = r.u8(); c.dtype = r.u8();
             c.scale_bits = r.u32(); c.zero_point = (int32_t)r.u32(); c.bq_omajor = r.u8(); c.act_quant = r.u8(); c.act = r.u8(); c.residual = r.buf();
+            c.codebook = HoloBufferRef{HOLO_NO_SLOT, 0, 0};
+            if (d == HOLO_K_MATMUL_DEQUANT_CODEBOOK) c.codebook = r.buf();
             break;
         }
         case HOLO_K_ROPE_QUANTIZE_ROWS_I8: {

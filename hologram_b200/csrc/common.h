@@ -237,6 +237,8 @@ struct HoloMatmulSeg {
 int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* b, uint32_t m, uint32_t k, uint32_t n,
                                  uint8_t dtype, const HoloMatmulSeg* segs, uint32_t nseg);
 // quant_gemv.cu
+int32_t holo_launch_matmul_e8cb_omajor(holo_b200_ctx* ctx, const float* a, const uint8_t* bq, const int8_t* codebook, const float* scales,
+                                       const int32_t* zero_points, const float* residual, float* out, uint32_t m, uint32_t k, uint32_t n, int act);
 int32_t holo_launch_matmul_w8a8_omajor(holo_b200_ctx* ctx, const float* a, const int8_t* bq, const float* scales, const int32_t* zero_points,
                                        const float* residual, float* out, uint32_t m, uint32_t k, uint32_t n, int act, bool i4);
 // tp.cu

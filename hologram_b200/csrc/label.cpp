@@ -175,12 +175,14 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
             p_attn(b, c.batch, c.heads, c.kv_heads, c.q_rows, c.past_len, c.new_len, c.head_dim, c.scale_bits, c.dtype);
             return true;
         }
-        case HOLO_K_MATMUL_DEQUANT: {
-            // kernel_call.rs:1472-1500: the extended tag 116 (activation quantization / epilogue present)
+        case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
+            // kernel_call.rs:1472-1500: the extended tag 116 (activation quantization / epilogue present); a bound
+            // codebook takes tag 117 and one more byte
             const HoloMatMulDequantCall& c = u.matmul_dequant;
-            sig->opcode = 116;
+            sig->opcode = (uint16_t)call.kind;
             b.u32(c.m).u32(c.k).u32(c.n).u32(c.channels).u32(c.inner).u8(c.quant_dtype).u8(c.dtype).u32(c.scale_bits).i32(c.zero_point)
                 .u8(c.act_quant).u8(c.act).u8(present(c.residual) ? 1 : 0);
+            if (call.kind == HOLO_K_MATMUL_DEQUANT_CODEBOOK) b.u8(1);
             return true;
         }
         // extensions: the tag doubles as the opcode
@@ -224,10 +226,11 @@ bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* input
             in(u.matmul_activation.mm.a); in(u.matmul_activation.mm.b); *output = u.matmul_activation.mm.output.slot; return true;
         case HOLO_K_MATMUL_ADD:
             in(u.matmul_add.mm.a); in(u.matmul_add.mm.b); in(u.matmul_add.residual); *output = u.matmul_add.mm.output.slot; return true;
-        case HOLO_K_MATMUL_DEQUANT: {
+        case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
             const auto& c = u.matmul_dequant;
             in(c.a); in(c.bq);
             if (c.channels > 0 && present(c.scales)) { in(c.scales); in(c.zero_points); }
+            if (call.kind == HOLO_K_MATMUL_DEQUANT_CODEBOOK) in(c.codebook);   // after the quant operands, before the residual (kernel_call.rs:1589-1598)
             in(c.residual);
             *output = c.output.slot; return true;
         }

@@ -29,6 +29,43 @@ __device__ __forceinline__ int4 ld_weight(const int4* p) {
     return v;
 }
 
+// quantize_row_i8 (cpu/simd.rs:4761-4785) of `rows` activation rows into shared memory [rows][kpad]; every
+// thread of the CTA takes part (QG_WARPS warps), and every CTA does all rows: they are tiny.
+__device__ __forceinline__ void quantize_rows_to_shared(const float* __restrict__ a, uint32_t m0, uint32_t rows, uint32_t k, uint32_t kpad,
+                                                        int8_t* s_q, float* s_scale, float* s_red) {
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (uint32_t r = 0; r < rows; ++r) {
+        const float* row = a + (uint64_t)(m0 + r) * k;
+        float amax = 0.0f;
+        for (uint32_t j = tid; j < k; j += blockDim.x) {
+            const float v = row[j], av = v < 0.0f ? -v : v;
+            if (av > amax) amax = av;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, amax, o);
+            if (other > amax) amax = other;
+        }
+        if (lane == 0) s_red[warp] = amax;
+        __syncthreads();
+        amax = s_red[0];
+        for (int w = 1; w < QG_WARPS; ++w)
+            if (s_red[w] > amax) amax = s_red[w];
+        const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(127.0f, amax);
+        for (uint32_t j = tid; j < kpad; j += blockDim.x) {
+            int q = 0;
+            if (j < k && amax != 0.0f) {
+                const float t = __fmul_rn(row[j], inv);
+                q = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
+                q = max(-127, min(127, q));
+            }
+            s_q[(size_t)r * kpad + j] = (int8_t)q;
+        }
+        if (tid == 0) s_scale[r] = amax == 0.0f ? 0.0f : __fdiv_rn(amax, 127.0f);
+        __syncthreads();
+    }
+
+}
+
 __global__ void __launch_bounds__(QG_WARPS * 32)
 matmul_w8a8_omajor_kernel(const float* __restrict__ a, const int8_t* __restrict__ bq, const float* __restrict__ scales,
                           const int32_t* __restrict__ zero_points, const float* __restrict__ residual, float* __restrict__ out,
@@ -66,36 +103,7 @@ matmul_w8a8_omajor_kernel(const float* __restrict__ a, const int8_t* __restrict_
         prefetched = true;
     }
 
-    // ---- quantize_row_i8 of each activation row (every CTA does all rows: they are tiny) ----
-    for (uint32_t r = 0; r < rows; ++r) {
-        const float* row = a + (uint64_t)(m0 + r) * k;
-        float amax = 0.0f;
-        for (uint32_t j = tid; j < k; j += blockDim.x) {
-            const float v = row[j], av = v < 0.0f ? -v : v;
-            if (av > amax) amax = av;
-        }
-        for (int o = 16; o > 0; o >>= 1) {
-            const float other = __shfl_xor_sync(0xffffffffu, amax, o);
-            if (other > amax) amax = other;
-        }
-        if (lane == 0) s_red[warp] = amax;
-        __syncthreads();
-        amax = s_red[0];
-        for (int w = 1; w < QG_WARPS; ++w)
-            if (s_red[w] > amax) amax = s_red[w];
-        const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(127.0f, amax);
-        for (uint32_t j = tid; j < kpad; j += blockDim.x) {
-            int q = 0;
-            if (j < k && amax != 0.0f) {
-                const float t = __fmul_rn(row[j], inv);
-                q = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
-                q = max(-127, min(127, q));
-            }
-            s_q[(size_t)r * kpad + j] = (int8_t)q;
-        }
-        if (tid == 0) s_scale[r] = amax == 0.0f ? 0.0f : __fdiv_rn(amax, 127.0f);
-        __syncthreads();
-    }
+    quantize_rows_to_shared(a, m0, rows, k, kpad, s_q, s_scale, s_red);
 
     // ---- columns: each warp takes two columns at a time (grid-stride), four 128-bit weight loads
     // per lane and column in flight before the first dp4a ----
@@ -172,6 +180,74 @@ matmul_w8a8_omajor_kernel(const float* __restrict__ a, const int8_t* __restrict_
                 if (residual) y = __fadd_rn(y, residual[idx]);
                 if (act >= 0) y = holo::lut_act_ref(act, y);
                 out[idx] = y;
+            }
+        }
+    }
+}
+
+// E8 codebook tier (W1A8; matmul_e8cb_omajor, cpu/simd.rs:6845-6960): the weight is [n, k/8] bytes, each the index of
+// an 8-element i8 block of the model's 256 x 8 codebook (a constant operand); otherwise the i8 product: quantized
+// row, exact i32 dot, one f32 writeback. The index stream is an eighth of the i8 weight, so the kernel is bound by
+// the dp4a count and the shared-memory lookups, not by HBM: the codebook (2 KiB) and the rows sit in shared memory,
+// one warp per column, a lane takes sixteen indices per 128-bit load.
+__global__ void __launch_bounds__(QG_WARPS * 32)
+matmul_e8cb_omajor_kernel(const float* __restrict__ a, const uint8_t* __restrict__ bq, const int8_t* __restrict__ codebook,
+                          const float* __restrict__ scales, const int32_t* __restrict__ zero_points, const float* __restrict__ residual,
+                          float* __restrict__ out, uint32_t m0, uint32_t rows, uint32_t k, uint32_t n, int act, uint32_t* status) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    extern __shared__ __align__(16) int8_t s_q[];          // [rows][kpad] quantized activations
+    __shared__ __align__(16) int2 s_cb[256];
+    __shared__ float s_scale[QG_MAX_ROWS];
+    __shared__ float s_red[QG_WARPS];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t kpad = (k + 15u) & ~15u, groups = k >> 3;
+    for (uint32_t i = tid; i < 256; i += blockDim.x) {
+        const int8_t* e = codebook + (size_t)i * 8;
+        s_cb[i] = make_int2((int)((uint32_t)(uint8_t)e[0] | ((uint32_t)(uint8_t)e[1] << 8) | ((uint32_t)(uint8_t)e[2] << 16) | ((uint32_t)(uint8_t)e[3] << 24)),
+                            (int)((uint32_t)(uint8_t)e[4] | ((uint32_t)(uint8_t)e[5] << 8) | ((uint32_t)(uint8_t)e[6] << 16) | ((uint32_t)(uint8_t)e[7] << 24)));
+    }
+    quantize_rows_to_shared(a, m0, rows, k, kpad, s_q, s_scale, s_red);   // ends with a barrier: the codebook is in place too
+
+    const bool vec_ok = ((uintptr_t)bq & 15u) == 0 && (groups & 15u) == 0;   // every column's indices start on a 16-byte boundary
+    for (uint32_t col = blockIdx.x * QG_WARPS + warp; col < n; col += gridDim.x * QG_WARPS) {
+        if (lane == 0 && zero_points && zero_points[col] != 0) atomicOr(status, 16u);   // symmetric form only
+        const uint8_t* idx = bq + (uint64_t)col * groups;
+        int acc[QG_MAX_ROWS];
+#pragma unroll
+        for (int r = 0; r < QG_MAX_ROWS; ++r) acc[r] = 0;
+        auto group = [&](uint32_t g, uint32_t code) {
+            const int2 w = s_cb[code];
+#pragma unroll
+            for (int r = 0; r < QG_MAX_ROWS; ++r)
+                if ((uint32_t)r < rows) {
+                    const int2 q = *reinterpret_cast<const int2*>(s_q + (size_t)r * kpad + (size_t)g * 8);
+                    acc[r] = __dp4a(w.x, q.x, acc[r]);
+                    acc[r] = __dp4a(w.y, q.y, acc[r]);
+                }
+        };
+        if (vec_ok) {
+            for (uint32_t v = lane; v < (groups >> 4); v += 32) {
+                const int4 w = ld_weight(reinterpret_cast<const int4*>(idx) + v);
+                const uint32_t words[4] = {(uint32_t)w.x, (uint32_t)w.y, (uint32_t)w.z, (uint32_t)w.w};
+#pragma unroll
+                for (int j = 0; j < 16; ++j) group(v * 16 + j, (words[j >> 2] >> (8 * (j & 3))) & 255u);
+            }
+        } else {
+            for (uint32_t g = lane; g < groups; g += 32) group(g, idx[g]);
+        }
+#pragma unroll
+        for (int r = 0; r < QG_MAX_ROWS; ++r) {
+            if ((uint32_t)r >= rows) break;
+            int sum = acc[r];
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);   // integer: any order is exact
+            if (lane == 0) {
+                const float sa = s_scale[r];
+                const uint64_t o = (uint64_t)(m0 + r) * n + col;
+                float y = sa == 0.0f ? 0.0f : __fmul_rn(__int2float_rn(sum), __fmul_rn(sa, scales[col]));
+                if (residual) y = __fadd_rn(y, residual[o]);
+                if (act >= 0) y = holo::lut_act_ref(act, y);
+                out[o] = y;
             }
         }
     }
@@ -537,6 +613,30 @@ cudaError_t launch_stream(holo_b200_ctx* ctx, uint32_t grid, size_t smem, const 
 }
 
 }  // namespace
+
+int32_t holo_launch_matmul_e8cb_omajor(holo_b200_ctx* ctx, const float* a, const uint8_t* bq, const int8_t* codebook, const float* scales,
+                                       const int32_t* zero_points, const float* residual, float* out, uint32_t m, uint32_t k, uint32_t n, int act) {
+    if (m == 0 || k == 0 || n == 0) return HOLO_OK;
+    const uint32_t kpad = (k + 15u) & ~15u;
+    static thread_local int configured_device = -1;
+    if (configured_device != ctx->device) {
+        HOLO_CUDA(cudaFuncSetAttribute(matmul_e8cb_omajor_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured_device = ctx->device;
+    }
+    uint32_t per = QG_MAX_ROWS;   // rows per launch: what fits the shared-memory activation buffer
+    while (per > 1 && (size_t)per * kpad > 200 * 1024) per >>= 1;
+    if ((size_t)per * kpad > 200 * 1024)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: k %u does not fit the shared-memory activation row", k);
+    const uint32_t want = (n + QG_WARPS - 1) / QG_WARPS, cap = 4u * (uint32_t)ctx->sm_count;
+    const uint32_t grid = want < cap ? want : cap;
+    for (uint32_t m0 = 0; m0 < m; m0 += per) {
+        const uint32_t take = m - m0 < per ? m - m0 : per;
+        HOLO_CUDA(holo_launch_kernel(ctx, matmul_e8cb_omajor_kernel, dim3(grid), dim3(QG_WARPS * 32), (size_t)take * kpad, 1, a, bq, codebook, scales,
+                                     zero_points, residual, out, m0, take, k, n, act, ctx->dev_status));
+        ctx->launches++;
+    }
+    return HOLO_OK;
+}
 
 int32_t holo_launch_matmul_w8a8_omajor(holo_b200_ctx* ctx, const float* a, const int8_t* bq, const float* scales, const int32_t* zero_points,
                                        const float* residual, float* out, uint32_t m, uint32_t k, uint32_t n, int act, bool i4) {

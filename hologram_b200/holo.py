@@ -43,11 +43,11 @@ def encode_call(call):
         return out + _matmul(u.matmul_activation.mm) + struct.pack("<B", u.matmul_activation.act)
     if k == kc.K_MATMUL_ADD:
         return out + _matmul(u.matmul_add.mm) + _buf(u.matmul_add.residual)
-    if k == kc.K_MATMUL_DEQUANT:
+    if k in (kc.K_MATMUL_DEQUANT, kc.K_MATMUL_DEQUANT_CODEBOOK):
         c = u.matmul_dequant
         return out + b"".join(_buf(b) for b in (c.a, c.bq, c.scales, c.zero_points, c.output)) + struct.pack(
             "<IIIIIBBIIBBB", c.m, c.k, c.n, c.channels, c.inner, c.quant_dtype, c.dtype, c.scale_bits, c.zero_point & 0xFFFFFFFF,
-            c.bq_omajor, c.act_quant, c.act) + _buf(c.residual)
+            c.bq_omajor, c.act_quant, c.act) + _buf(c.residual) + (_buf(c.codebook) if k == kc.K_MATMUL_DEQUANT_CODEBOOK else b"")
     if k in (kc.K_LAYER_NORM, kc.K_RMS_NORM, kc.K_ADD_RMS_NORM):
         c = u.norm
         return out + _buf(c.x) + _buf(c.gamma) + _buf(c.beta) + _buf(c.residual) + _buf(c.output) + struct.pack(

@@ -32,6 +32,8 @@ K_REDUCE_SUM, K_REDUCE_MEAN, K_REDUCE_PROD, K_REDUCE_MIN, K_REDUCE_MAX = 55, 56,
 K_ADD_RMS_NORM, K_TRANSPOSE, K_CONCAT, K_SLICE, K_SOFTMAX = 54, 61, 62, 63, 64
 K_DECODE_ATTENTION = 119
 K_MATMUL_DEQUANT = 116
+K_MATMUL_DEQUANT_CODEBOOK = 117   # the same call with a codebook operand bound (E8 codebook weights)
+DTYPE_E8CB = 11
 K_DEQUANTIZE, K_MATMUL_ACTIVATION, K_MATMUL_ADD = 105, 106, 107
 K_GATHER, K_CAST, K_KV_CACHE_WRITE, K_DECODE_ATTENTION_VALID = 114, 115, 120, 121
 K_QUANTIZE_ROWS_I8, K_DECODE_ATTENTION_VALID_Q8, K_ALL_REDUCE = 0x8001, 0x8002, 0x8003
@@ -84,7 +86,12 @@ class MatMulDequantCall(C.Structure):
     _fields_ = [("a", BufferRef), ("bq", BufferRef), ("scales", BufferRef), ("zero_points", BufferRef), ("output", BufferRef),
                 ("m", C.c_uint32), ("k", C.c_uint32), ("n", C.c_uint32), ("channels", C.c_uint32), ("inner", C.c_uint32),
                 ("quant_dtype", C.c_uint8), ("dtype", C.c_uint8), ("scale_bits", C.c_uint32), ("zero_point", C.c_int32),
-                ("bq_omajor", C.c_uint8), ("act_quant", C.c_uint8), ("act", C.c_uint8), ("residual", BufferRef)]
+                ("bq_omajor", C.c_uint8), ("act_quant", C.c_uint8), ("act", C.c_uint8), ("residual", BufferRef), ("codebook", BufferRef)]
+
+    def __init__(self, *args, **kw):
+        super().__init__(*args, **kw)
+        if len(args) < 19 and "codebook" not in kw:
+            self.codebook = NONE
 
 
 class NormCall(C.Structure):
@@ -296,7 +303,7 @@ class KernelCall(C.Structure):
     @classmethod
     def MatMulAdd(cls, c): return cls.of(K_MATMUL_ADD, c)
     @classmethod
-    def MatMulDequant(cls, c): return cls.of(K_MATMUL_DEQUANT, c)
+    def MatMulDequant(cls, c): return cls.of(K_MATMUL_DEQUANT_CODEBOOK if c.codebook.slot != NO_SLOT else K_MATMUL_DEQUANT, c)
     @classmethod
     def RmsNorm(cls, c): return cls.of(K_RMS_NORM, c)
     @classmethod

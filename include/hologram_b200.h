@@ -43,6 +43,7 @@ extern "C" {
 #define HOLO_DTYPE_BF16 7
 #define HOLO_DTYPE_F32 8
 #define HOLO_DTYPE_F64 9
+#define HOLO_DTYPE_E8CB 11 /* one u8 index of an 8-element codebook block per eight weights; MatMulDequant weight only */
 #define HOLO_DTYPE_I4 10 /* two signed nibbles per byte, low nibble first; DequantActivation input only */
 
 /* ---- lut_act ids (crates/hologram-compute/src/kernel_call.rs:877-885) */
@@ -116,6 +117,7 @@ extern "C" {
 #define HOLO_K_BROADCAST_BINARY 112
 #define HOLO_K_DEQUANT_ACTIVATION 113
 #define HOLO_K_GATHER 114
+#define HOLO_K_MATMUL_DEQUANT_CODEBOOK 117 /* kernel_codec.rs D_MMDQ3: the same call with a codebook operand bound (E8 codebook weight tier) */
 #define HOLO_K_MATMUL_DEQUANT 116 /* the extended wire form (kernel_codec.rs D_MMDQ2); served: output-major W8A8 int8 */
 #define HOLO_K_CAST 115
 #define HOLO_K_DECODE_ATTENTION 119
@@ -199,6 +201,7 @@ typedef struct HoloMatMulDequantCall {
     int32_t zero_point;
     uint8_t bq_omajor, act_quant, act;
     HoloBufferRef residual;
+    HoloBufferRef codebook; /* tag 117 only: the model's 256 x 8 i8 codebook (2048 bytes); slot HOLO_NO_SLOT otherwise */
 } HoloMatMulDequantCall;
 
 /* SoftmaxCall (kernel_call.rs:549-556): rows of `feature` elements; max, deterministic exp of the

@@ -352,6 +352,31 @@ void holo_or_matmul_i4_pc_omajor(const float* a, const uint8_t* bq, const float*
     free(q);
 }
 
+/* W1A8 output-major GEMV over the E8 codebook tier (matmul_e8cb_omajor, cpu/simd.rs:6845-6960): the weight is
+ * [n, k/8] u8 indices, index g of a column selects the 8 i8 values codebook[idx * 8 .. + 8] for elements
+ * 8g .. 8g + 7; otherwise the i8 kernel: quantized row, exact i32 dot, one f32 writeback. */
+void holo_or_matmul_e8cb_omajor(const float* a, const uint8_t* bq, const int8_t* codebook, const float* scales, float* out,
+                                size_t m, size_t k, size_t n) {
+    int8_t* q = (int8_t*)malloc(k ? k : 1);
+    size_t groups = k / 8;
+    for (size_t i = 0; i < m; ++i) {
+        float sa = holo_or_quantize_row_i8(a + i * k, q, k);
+        if (sa == 0.0f) {
+            for (size_t j = 0; j < n; ++j) out[i * n + j] = 0.0f;
+            continue;
+        }
+        for (size_t j = 0; j < n; ++j) {
+            int32_t acc = 0;
+            for (size_t g = 0; g < groups; ++g) {
+                const int8_t* e = codebook + (size_t)bq[j * groups + g] * 8;
+                for (int t = 0; t < 8; ++t) acc += (int32_t)q[g * 8 + t] * (int32_t)e[t];
+            }
+            out[i * n + j] = (float)acc * (sa * scales[j]);
+        }
+    }
+    free(q);
+}
+
 /* ---- dequantize: cpu/kernels.rs:185-296 (i8 / u8 source, per-channel or per-tensor) -- */
 int holo_or_dequantize(const void* in, int quant_dtype, const float* scales, const int32_t* zps,
                        uint32_t channels, uint32_t inner, float scale, int32_t zp,

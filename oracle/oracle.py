@@ -39,6 +39,7 @@ def _load(path):
         "holo_or_binary": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_rms_norm": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
         "holo_or_add_rms_norm": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
+        "holo_or_matmul_e8cb_omajor": (None, [_c, _c, _c, _c, _c, C.c_size_t, C.c_size_t, C.c_size_t]),
         "holo_or_matmul_i4_pc_omajor": (None, [_c, _c, _c, _c, C.c_size_t, C.c_size_t, C.c_size_t]),
         "holo_or_dequant_activation": (C.c_int, [_c, _c, C.c_uint64, C.c_int, C.c_int, C.c_float, C.c_int32]),
         "holo_or_elementwise": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
@@ -199,14 +200,19 @@ def decode_attention_mask(q, kp, vp, kn, vn, mask, b, h, kv, m, past, new, d, sc
     return out
 
 
-def matmul_w8a8_omajor(a, bq, scales, m, k, n, residual=None, act=None, i4=False):
+def matmul_w8a8_omajor(a, bq, scales, m, k, n, residual=None, act=None, i4=False, codebook=None):
     """matmul_dequant_float, output-major W8A8 arm + epilogue (cpu/float_kernels.rs:534-596, 727-766):
     a f32 [m,k], bq i8 [n,k], scales f32 [n]; act is a LUT activation id applied by the scalar function."""
     a = np.ascontiguousarray(a, dtype=np.float32)
-    bq = np.ascontiguousarray(bq, dtype=np.uint8 if i4 else np.int8)   # i4: [n, k/2] packed nibbles (cpu/simd.rs:6164-6171)
+    bq = np.ascontiguousarray(bq, dtype=np.uint8 if (i4 or codebook is not None) else np.int8)   # i4: [n, k/2] packed nibbles (cpu/simd.rs:6164-6171)
     scales = np.ascontiguousarray(scales, dtype=np.float32)
     out = np.zeros(m * n, dtype=np.float32)
-    (lib.holo_or_matmul_i4_pc_omajor if i4 else lib.holo_or_matmul_i8_pc_omajor)(_p(a), _p(bq), _p(scales), _p(out), m, k, n)
+    if codebook is not None:     # E8 codebook tier: [n, k/8] indices into the model's 256 x 8 i8 codebook (cpu/simd.rs:6856-6861)
+        cb = np.ascontiguousarray(codebook, dtype=np.int8)
+        assert cb.size == 2048
+        lib.holo_or_matmul_e8cb_omajor(_p(a), _p(bq), _p(cb), _p(scales), _p(out), m, k, n)
+    else:
+        (lib.holo_or_matmul_i4_pc_omajor if i4 else lib.holo_or_matmul_i8_pc_omajor)(_p(a), _p(bq), _p(scales), _p(out), m, k, n)
     if residual is not None:
         out = out + np.ascontiguousarray(residual, dtype=np.float32)
     if act is not None:

@@ -105,3 +105,19 @@ def test_matmul_dequant_signature_and_wire_are_the_frozen_bytes():
             "00000040000000000000000300000000000000000000004000000000000000040000000000000000000000400000000000000001000000"
             "0800000004000000040000000100000002080000000000000000010100ffffffff00000000000000000000000000000000")
     assert holo.encode_calls([call]).hex() == want
+
+
+def test_matmul_dequant_with_a_codebook_takes_tag_117_and_one_more_byte():
+    # kernel_call.rs:1486-1494 (signature), :1589-1598 (codebook operand after the quant operands, before the residual),
+    # kernel_codec.rs:525-533 (wire form D_MMDQ3 = the 116 body followed by the codebook reference)
+    from hologram_b200 import holo
+    buf = lambda i: kc.rb(i, 0, 64)
+    c = kc.MatMulDequantCall(buf(0), buf(1), buf(2), buf(3), buf(4), 1, 8, 4, 4, 1, kc.DTYPE_E8CB, 8, 0, 0, 1, 1, 0, kc.NONE)
+    plain = holo.encode_calls([kc.KernelCall.MatMulDequant(c)])
+    c.codebook = buf(5)
+    call = kc.KernelCall.MatMulDequant(c)
+    assert call.kind == 117
+    op, params = hs.op_signature(call)
+    assert op == 117 and params == struct.pack("<IIIIIBBIiBBBB", 1, 8, 4, 4, 1, kc.DTYPE_E8CB, 8, 0, 0, 1, 0, 0, 1)
+    wire = holo.encode_calls([call])
+    assert wire[4:6] == struct.pack("<H", 117) and wire[6:-20] == plain[6:] and wire[-20:] == struct.pack("<IQQ", 5, 0, 64)

@@ -386,6 +386,21 @@ def test_dequant_activation_restatement_is_the_unfused_composition():
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+def test_quantized_weight_tier_restatements_reproduce_the_reference_goldens():
+    # crates/hologram-compute/src/cpu/simd.rs:8236-8281: the FNV-1a-64 of the output bits of the three
+    # output-major decode products (i8, packed i4, E8 codebook) on the reference's fixed operands
+    m, k, n = 3, 64, 24
+    a = (np.array([float(i * 37 % 91) for i in range(m * k)], dtype=np.float32) - np.float32(45.0)) * np.float32(0.031)
+    scales = np.float32(0.011) + np.arange(n, dtype=np.float32) * np.float32(0.0007)
+    bq = np.array([(i * 31 % 255) - 127 for i in range(k * n)], dtype=np.int8)
+    assert orc.fnv1a64_f32(orc.matmul_w8a8_omajor(a, bq, scales, m, k, n)) == 0x787CCDC172029F9B
+    bq4 = np.array([(i * 53 + 9) % 251 for i in range(k * n // 2)], dtype=np.uint8)
+    assert orc.fnv1a64_f32(orc.matmul_w8a8_omajor(a, bq4, scales, m, k, n, i4=True)) == 0x4C5123C024AF97AE
+    cb = np.array([(i * 37 + 11) % 255 - 127 for i in range(256 * 8)], dtype=np.int8)
+    bq8 = np.array([(i * 17 + 3) % 256 for i in range(n * (k // 8))], dtype=np.uint8)
+    assert orc.fnv1a64_f32(orc.matmul_w8a8_omajor(a, bq8, scales, m, k, n, codebook=cb)) == 0x88AC55A91DD5AA0D
+
+
 def test_mask_form_restatement_equals_scalar_form_bitwise():
     # the reference pins that a realized-length mask reproduces DecodeAttentionValid bit for bit
     # (crates/hologram-compute/tests/decode_attention_valid.rs:226-282); all-erased row = zeros

@@ -12,8 +12,8 @@ pytestmark = pytest.mark.gpu
 F32, I8 = kc.DTYPE_F32, kc.DTYPE_I8
 
 
-def run(backend, a, bq, scales, m, k, n, residual=None, act=0, zero_points=None, quant=I8):
-    ws = hb.DeviceWorkspace(backend, 6)
+def run(backend, a, bq, scales, m, k, n, residual=None, act=0, zero_points=None, quant=I8, codebook=None):
+    ws = hb.DeviceWorkspace(backend, 7)
     ws.put(0, a)
     ws.put(1, bq)
     ws.put(2, scales)
@@ -24,6 +24,9 @@ def run(backend, a, bq, scales, m, k, n, residual=None, act=0, zero_points=None,
         ws.put(5, residual)
         res = kc.rb(5)
     call = kc.MatMulDequantCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), m, k, n, n, 1, quant, F32, 0, 0, 1, 1, act, res)
+    if codebook is not None:
+        ws.put(6, codebook)
+        call.codebook = kc.rb(6)
     backend.dispatch(kc.KernelCall.MatMulDequant(call), ws)
     out = ws.read(4, m * n * 4, np.float32).copy()
     ws.close()
@@ -107,3 +110,29 @@ def test_packed_i4_reference_golden_and_bit_exactness(backend):
     with pytest.raises(hb.BackendError) as e:      # k = 48: columns of 24 bytes do not stream in 16-byte units
         run(backend, np.ones(48, np.float32), np.zeros(48, np.uint8), np.ones(2, np.float32), 1, 48, 2, quant=kc.DTYPE_I4)
     assert e.value.variant == "UnsupportedOp"
+
+
+def test_e8_codebook_reference_golden_and_bit_exactness(backend):
+    # W1A8: [n, k/8] indices into the model's 256 x 8 i8 codebook (matmul_e8cb_omajor, cpu/simd.rs:6845-6960; wire
+    # form 117 with the codebook operand); the reference's FNV golden for this tier (:8266-8280), then seeded shapes
+    m, k, n = 3, 64, 24
+    a = (np.array([float(i * 37 % 91) for i in range(m * k)], dtype=np.float32) - np.float32(45.0)) * np.float32(0.031)
+    scales = np.float32(0.011) + np.arange(n, dtype=np.float32) * np.float32(0.0007)
+    cb = np.array([(i * 37 + 11) % 255 - 127 for i in range(256 * 8)], dtype=np.int8)
+    bq8 = np.array([(i * 17 + 3) % 256 for i in range(n * (k // 8))], dtype=np.uint8)
+    assert orc.fnv1a64_f32(run(backend, a, bq8, scales, m, k, n, quant=kc.DTYPE_E8CB, codebook=cb)) == 0x88AC55A91DD5AA0D
+    rng = np.random.default_rng(117)
+    cb = rng.integers(-127, 128, size=2048, dtype=np.int8)
+    for m, k, n in ((1, 4096, 14336), (4, 4096, 1001), (2, 14336, 130), (9, 520, 37), (1, 8, 3)):
+        a = rng.standard_normal(m * k).astype(np.float32)
+        if m > 1:
+            a[:k] = 0.0
+        bq = rng.integers(0, 256, size=n * k // 8, dtype=np.uint8)
+        scales = (rng.random(n).astype(np.float32) + np.float32(0.01)) * np.float32(0.02)
+        got = run(backend, a, bq, scales, m, k, n, quant=kc.DTYPE_E8CB, codebook=cb)
+        want = orc.matmul_w8a8_omajor(a, bq, scales, m, k, n, codebook=cb)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (m, k, n)
+    for kwargs in (dict(quant=kc.DTYPE_E8CB), dict(quant=I8, codebook=cb)):      # the tier and the codebook operand go together
+        with pytest.raises(hb.BackendError) as e:
+            run(backend, np.ones(64, np.float32), np.zeros(64, np.uint8), np.ones(2, np.float32), 1, 64, 2, **kwargs)
+        assert e.value.variant == "UnsupportedOp"
