@@ -440,29 +440,36 @@ def workload_w8a8(be, torch, rank, args):
     if os.environ.get("HOLO_BENCH_MKN"):
         m, k, n = (int(v) for v in os.environ["HOLO_BENCH_MKN"].split(","))
     i4 = bool(os.environ.get("HOLO_BENCH_I4"))          # the packed-nibble weight tier (W4A8): half the weight bytes
-    wbytes = n * k // 2 if i4 else n * k
-    qd = kc.DTYPE_I4 if i4 else kc.DTYPE_I8
+    e8 = bool(os.environ.get("HOLO_BENCH_E8"))          # the E8 codebook tier (W1A8): one index byte per eight weights
+    wbytes = n * k // 8 if e8 else n * k // 2 if i4 else n * k
+    qd = kc.DTYPE_E8CB if e8 else kc.DTYPE_I4 if i4 else kc.DTYPE_I8
     sets = max(2, int(300e6 // wbytes) + 1)
     g = torch.Generator(device="cuda").manual_seed(0xC6 + rank)
     A = [torch.randn(m * k, generator=g, device="cuda") for _ in range(sets)]
-    W = [torch.randint(0, 256, (wbytes,), generator=g, device="cuda", dtype=torch.uint8) if i4 else
+    W = [torch.randint(0, 256, (wbytes,), generator=g, device="cuda", dtype=torch.uint8) if (i4 or e8) else
          torch.randint(-127, 128, (n * k,), generator=g, device="cuda", dtype=torch.int8) for _ in range(sets)]
     S = [torch.rand(n, generator=g, device="cuda") * 0.02 + 0.001 for _ in range(sets)]
     Z = torch.zeros(n, dtype=torch.int32, device="cuda")
     O = [torch.empty(m * n, device="cuda") for _ in range(sets)]
-    ws = hb.DeviceWorkspace(be, 4 * sets + 1)
+    CB = torch.randint(-127, 128, (2048,), generator=g, device="cuda", dtype=torch.int8)
+    ws = hb.DeviceWorkspace(be, 4 * sets + 2)
     ws.bind(4 * sets, Z.data_ptr(), n * 4)
+    ws.bind(4 * sets + 1, CB.data_ptr(), 2048)
     calls = []
     for i in range(sets):
         for j, t in enumerate((A[i], W[i], S[i], O[i])):
             ws.bind(4 * i + j, t.data_ptr(), t.numel() * t.element_size())
-        calls.append(kc.KernelCall.MatMulDequant(kc.MatMulDequantCall(
-            kc.rb(4 * i), kc.rb(4 * i + 1), kc.rb(4 * i + 2), kc.rb(4 * sets), kc.rb(4 * i + 3), m, k, n, n, 1, qd, kc.DTYPE_F32,
-            0, 0, 1, 1, 0, kc.NONE)))
-    host = [t.cpu().pin_memory() for t in (A[0], W[0], S[0], Z, O[0])]
+        mc = kc.MatMulDequantCall(kc.rb(4 * i), kc.rb(4 * i + 1), kc.rb(4 * i + 2), kc.rb(4 * sets), kc.rb(4 * i + 3), m, k, n, n, 1, qd,
+                                  kc.DTYPE_F32, 0, 0, 1, 1, 0, kc.NONE)
+        if e8:
+            mc.codebook = kc.rb(4 * sets + 1)
+        calls.append(kc.KernelCall.MatMulDequant(mc))
+    host = [t.cpu().pin_memory() for t in (A[0], W[0], S[0], Z, O[0], CB)]
     hws = hb.HostWorkspace([t.numpy().view(np.uint8) for t in host])
-    hcall = kc.KernelCall.MatMulDequant(kc.MatMulDequantCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), m, k, n, n, 1, qd,
-                                                             kc.DTYPE_F32, 0, 0, 1, 1, 0, kc.NONE))
+    hc = kc.MatMulDequantCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), m, k, n, n, 1, qd, kc.DTYPE_F32, 0, 0, 1, 1, 0, kc.NONE)
+    if e8:
+        hc.codebook = kc.rb(5)
+    hcall = kc.KernelCall.MatMulDequant(hc)
     nbytes = float(wbytes + 4 * (m * k + n + m * n))
 
     def cpu_baseline():
@@ -471,18 +478,18 @@ def workload_w8a8(be, torch, rank, args):
         best, t_end = 1e9, time.time() + 8
         while time.time() < t_end:
             t0 = time.perf_counter()
-            orc.matmul_w8a8_omajor(a, w, sc, m, k, n, i4=i4)
+            orc.matmul_w8a8_omajor(a, w, sc, m, k, n, i4=i4, codebook=host[5].numpy() if e8 else None)
             best = min(best, time.perf_counter() - t0)
         return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
                 "sample": "the full product, best of ~8 s of serial passes of the scalar restatement"}
 
     return {
-        "name": f"matmul_{'w4a8' if i4 else 'w8a8'}_omajor_{m}x{k}x{n}",
+        "name": f"matmul_{'w1a8_e8cb' if e8 else 'w4a8' if i4 else 'w8a8'}_omajor_{m}x{k}x{n}",
         "metric": "matmul_w8a8_GBps", "unit": "GB/s", "dtype": "i4 x i8 -> i32, f32 writeback" if i4 else "i8 x i8 -> i32, f32 writeback", "scaling": "weak",
         "run_device": lambda step: be.dispatch(calls[step % sets], ws),
         "run_host": lambda step: be.dispatch(hcall, hws),
         "units_per_step": nbytes / 1e9, "launches_per_step": 1,
-        "roofline": {"bound": "hbm", "bytes_per_launch": nbytes, "kernel": "matmul_w8a8_stream_kernel", "traffic": None},
+        "roofline": {"bound": "hbm", "bytes_per_launch": nbytes, "kernel": "matmul_e8cb_omajor_kernel" if e8 else "matmul_w8a8_stream_kernel", "traffic": None},
         "h2d": wbytes + 4 * (m * k + 2 * n), "d2h": 4 * m * n,
         "cpu_baseline": cpu_baseline,
         "config": {"workload": f"output-major W8A8 decode product M={m} K={k} N={n} (quantized-weight GEMV, exact integer)",
