@@ -31,8 +31,11 @@ __device__ __forceinline__ int4 ld_weight(const int4* p) {
 
 // quantize_row_i8 (cpu/simd.rs:4761-4785) of `rows` activation rows into shared memory [rows][kpad]; every
 // thread of the CTA takes part (QG_WARPS warps), and every CTA does all rows: they are tiny.
+// `chunk` != 0 (E8 tier): the 8-element groups of a row are stored transposed in blocks of 16, group g at
+// position (g % 16) * chunk + g / 16 (chunk = groups / 16), so that lanes holding sixteen consecutive indices each
+// read neighbouring 8-byte groups at every step instead of the same bank.
 __device__ __forceinline__ void quantize_rows_to_shared(const float* __restrict__ a, uint32_t m0, uint32_t rows, uint32_t k, uint32_t kpad,
-                                                        int8_t* s_q, float* s_scale, float* s_red) {
+                                                        int8_t* s_q, float* s_scale, float* s_red, uint32_t chunk = 0) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (uint32_t r = 0; r < rows; ++r) {
         const float* row = a + (uint64_t)(m0 + r) * k;
@@ -58,7 +61,9 @@ __device__ __forceinline__ void quantize_rows_to_shared(const float* __restrict_
                 q = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
                 q = max(-127, min(127, q));
             }
-            s_q[(size_t)r * kpad + j] = (int8_t)q;
+            const uint32_t g = j >> 3;
+            const uint32_t pos = chunk ? ((g & 15u) * chunk + (g >> 4)) * 8 + (j & 7u) : j;
+            s_q[(size_t)r * kpad + pos] = (int8_t)q;
         }
         if (tid == 0) s_scale[r] = amax == 0.0f ? 0.0f : __fdiv_rn(amax, 127.0f);
         __syncthreads();
@@ -207,9 +212,10 @@ matmul_e8cb_omajor_kernel(const float* __restrict__ a, const uint8_t* __restrict
         s_cb[i] = make_int2((int)((uint32_t)(uint8_t)e[0] | ((uint32_t)(uint8_t)e[1] << 8) | ((uint32_t)(uint8_t)e[2] << 16) | ((uint32_t)(uint8_t)e[3] << 24)),
                             (int)((uint32_t)(uint8_t)e[4] | ((uint32_t)(uint8_t)e[5] << 8) | ((uint32_t)(uint8_t)e[6] << 16) | ((uint32_t)(uint8_t)e[7] << 24)));
     }
-    quantize_rows_to_shared(a, m0, rows, k, kpad, s_q, s_scale, s_red);   // ends with a barrier: the codebook is in place too
-
     const bool vec_ok = ((uintptr_t)bq & 15u) == 0 && (groups & 15u) == 0;   // every column's indices start on a 16-byte boundary
+    const uint32_t chunk = vec_ok ? groups >> 4 : 0;
+    quantize_rows_to_shared(a, m0, rows, k, kpad, s_q, s_scale, s_red, chunk);   // ends with a barrier: the codebook is in place too
+
     for (uint32_t col = blockIdx.x * QG_WARPS + warp; col < n; col += gridDim.x * QG_WARPS) {
         if (lane == 0 && zero_points && zero_points[col] != 0) atomicOr(status, 16u);   // symmetric form only
         const uint8_t* idx = bq + (uint64_t)col * groups;
@@ -221,7 +227,7 @@ matmul_e8cb_omajor_kernel(const float* __restrict__ a, const uint8_t* __restrict
 #pragma unroll
             for (int r = 0; r < QG_MAX_ROWS; ++r)
                 if ((uint32_t)r < rows) {
-                    const int2 q = *reinterpret_cast<const int2*>(s_q + (size_t)r * kpad + (size_t)g * 8);
+                    const int2 q = *reinterpret_cast<const int2*>(s_q + (size_t)r * kpad + (size_t)g * 8);   // g = the group's position in the row
                     acc[r] = __dp4a(w.x, q.x, acc[r]);
                     acc[r] = __dp4a(w.y, q.y, acc[r]);
                 }
@@ -231,7 +237,7 @@ matmul_e8cb_omajor_kernel(const float* __restrict__ a, const uint8_t* __restrict
                 const int4 w = ld_weight(reinterpret_cast<const int4*>(idx) + v);
                 const uint32_t words[4] = {(uint32_t)w.x, (uint32_t)w.y, (uint32_t)w.z, (uint32_t)w.w};
 #pragma unroll
-                for (int j = 0; j < 16; ++j) group(v * 16 + j, (words[j >> 2] >> (8 * (j & 3))) & 255u);
+                for (int j = 0; j < 16; ++j) group(j * chunk + v, (words[j >> 2] >> (8 * (j & 3))) & 255u);   // index 16 v + j, stored at j * chunk + v
             }
         } else {
             for (uint32_t g = lane; g < groups; g += 32) group(g, idx[g]);
