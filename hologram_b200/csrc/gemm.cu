@@ -712,11 +712,12 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     // waiting first wave here could face a second wave there). Otherwise the matmul stores its
     // narrowed partial and the all-reduce kernel follows.
     const bool want_ar = segs[0].all_reduce != 0 && ctx->tp_world > 1;
-    // The fused form has run on two GPUs; larger groups take it only when asked (HOLO_TP_FUSED_GEMM_ANY_WORLD)
-    // until they have been measured on hardware, and otherwise use the all-reduce kernel, which has.
+    // Opt-in (HOLO_TP_FUSED_GEMM; two ranks, or any group size with HOLO_TP_FUSED_GEMM_ANY_WORLD): measured on two
+    // GPUs the product followed by the all-reduce kernel is faster (1.376 against 1.456 ms per decoder step), because
+    // the fused launch must trim its K split to keep every CTA resident and its tiles wait on the peer's tiles.
     bool fused_ar = want_ar && ctx->tp_p2p && nseg == 1 && !gated && !segs[0].fused_act && (n % 4) == 0 &&
-                    4ull * (uint64_t)ctx->tp_world * m * n <= P2P_ONESHOT_BYTES && !getenv("HOLO_TP_NO_FUSED_GEMM") &&
-                    (ctx->tp_world == 2 || getenv("HOLO_TP_FUSED_GEMM_ANY_WORLD"));
+                    4ull * (uint64_t)ctx->tp_world * m * n <= P2P_ONESHOT_BYTES &&
+                    ((ctx->tp_world == 2 && getenv("HOLO_TP_FUSED_GEMM")) || getenv("HOLO_TP_FUSED_GEMM_ANY_WORLD"));
     if (fused_ar) {
         // one CTA per SM is always resident, clusters included: trim the K split to stay within that
         const uint32_t tiles = ((n + bn - 1) / bn) * mtiles;

@@ -105,11 +105,13 @@ def test_tp2_interpreter_over_gloo_matches_single_rank(tmp_path):
 
 
 @pytest.mark.gpu
-def test_tp2_on_two_gpus_matches_single_rank(tmp_path):
+@pytest.mark.parametrize("fused", [False, True])
+def test_tp2_on_two_gpus_matches_single_rank(tmp_path, fused):
+    # fused: the all-reduce inside the row-parallel product's epilogue (opt-in); otherwise product, then all-reduce kernel
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    r0, r1 = _launch("gpu", tmp_path)
+    r0, r1 = _launch("gpu", tmp_path, **({"HOLO_TP_FUSED_GEMM": "1"} if fused else {}))
     # the bare all-reduces: both ranks hold the same bits; over peer memory they are exactly the
     # f32 sum in rank order, truncated to bf16 (NCCL rounds and orders differently: tolerance)
     sys.path.insert(0, ROOT)
