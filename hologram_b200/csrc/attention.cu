@@ -63,7 +63,6 @@ struct FaParams {
     uint32_t past, G, planes, max_slots, box_rows;
     float scale_div;
     int dtype;
-    int debug_skip;  // measurement aid: 1 = consumers only release the tiles (pure streaming)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -402,7 +401,7 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             // keys of this warp: tile rows 32*warp .. +31; number of visible rows in the tile
             const uint32_t limit = t < tiles_past ? min((uint32_t)TK, vis_past - t * TK) : 1u;
             const uint32_t row0 = warp * 32;
-            if (!aborted && row0 < limit && !p.debug_skip) {
+            if (!aborted && row0 < limit) {
                 // ---- scores: S[(head,digit)][key] = sum_c Qdigit * Kcode (exact i32) ----
                 int sacc[4][4];
     #pragma unroll
@@ -733,7 +732,6 @@ int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a) 
     p.box_rows = box_rows;
     p.scale_div = a.scale_div;
     p.dtype = a.dtype;
-    p.debug_skip = getenv("HOLO_ATTN_DEBUG_SKIP") ? 1 : 0;
     HOLO_CUDA(holo_launch_kernel(ctx, decode_attention_q8_kernel, dim3(nctas), dim3(FA_THREADS), SMEM_TOTAL, 1, mk, mv, mks, mvs, p));
     HOLO_CUDA(cudaGetLastError());
     ctx->launches++;
@@ -843,7 +841,6 @@ extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const
     p.box_rows = box_rows;
     p.scale_div = scale_div;
     p.dtype = dtype;
-    p.debug_skip = 0;
     decode_attention_q8_kernel<<<nctas, FA_THREADS, SMEM_TOTAL, stream>>>(mk, mv, mks, mvs, p);
     HOLO_CUDA(cudaGetLastError());
     return HOLO_OK;
