@@ -607,7 +607,9 @@ __device__ __forceinline__ void quantize_rows_body(const void* __restrict__ x, i
     if (lane == 0) scales[row] = __fdiv_rn(amax, 127.0f);
 }
 // RoPE of one head per warp followed by quantize_row_i8 of the rotated row: exactly rope_body then
-// quantize_rows_body on the narrowed values the RoPE stored (the warp re-reads its own stores).
+// quantize_rows_body on the narrowed values the RoPE stored. Up to 256 elements per head the narrowed
+// values stay in registers (no round trip through memory between the two steps); longer rows re-read
+// the warp's own stores.
 __device__ __forceinline__ void rope_quantize_body(const void* __restrict__ x, const void* __restrict__ c, const void* __restrict__ s,
                                                    void* __restrict__ rope_out, int8_t* __restrict__ codes, float* __restrict__ scales,
                                                    uint64_t rows, uint32_t d, int dtype, uint32_t block) {
@@ -615,16 +617,55 @@ __device__ __forceinline__ void rope_quantize_body(const void* __restrict__ x, c
     if (row >= rows) return;
     const uint32_t lane = threadIdx.x & 31, half = d >> 1;
     const uint64_t off = row * d;
-    for (uint32_t j = lane; j < d; j += 32) {
+    constexpr int KEEP = 8;                 // 8 x 32 lanes = 256 elements
+    const bool keep = d <= 32 * KEEP;
+    float kept[KEEP];
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) kept[i] = 0.0f;
+    auto rotate = [&](uint32_t j) {
         const uint64_t e = off + j;
         const float xe = holo::load_float(x, e, dtype), ce = holo::load_float(c, e, dtype), se = holo::load_float(s, e, dtype);
         float v;
         if (j < half) v = __fsub_rn(__fmul_rn(xe, ce), __fmul_rn(holo::load_float(x, e + half, dtype), se));
         else v = __fadd_rn(__fmul_rn(xe, ce), __fmul_rn(holo::load_float(x, e - half, dtype), se));
         holo::store_float(rope_out, e, v, dtype);
+        return dtype == HOLO_DTYPE_F32 ? v : holo::widen16(holo::narrow16(v, dtype), dtype);   // what the store kept
+    };
+    if (!keep) {
+        for (uint32_t j = lane; j < d; j += 32) rotate(j);
+        __syncwarp();
+        quantize_rows_body(rope_out, dtype, rows, d, codes, scales, block);
+        return;
     }
-    __syncwarp();
-    quantize_rows_body(rope_out, dtype, rows, d, codes, scales, block);
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+        const uint32_t j = lane + 32 * i;
+        if (j < d) {
+            kept[i] = rotate(j);
+            const float av = kept[i] < 0.0f ? -kept[i] : kept[i];
+            if (av > amax) amax = av;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, amax, o);
+        if (other > amax) amax = other;
+    }
+    const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(127.0f, amax);
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+        const uint32_t j = lane + 32 * i;
+        if (j < d) {
+            int r = 0;
+            if (amax != 0.0f) {
+                const float t = __fmul_rn(kept[i], inv);
+                r = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
+                r = max(-127, min(127, r));
+            }
+            codes[off + j] = (int8_t)r;
+        }
+    }
+    if (lane == 0) scales[row] = amax == 0.0f ? 0.0f : __fdiv_rn(amax, 127.0f);
 }
 __global__ void rope_quantize_kernel(const void* __restrict__ x, const void* __restrict__ c, const void* __restrict__ s,
                                      void* __restrict__ rope_out, int8_t* __restrict__ codes, float* __restrict__ scales, uint64_t rows,
@@ -699,8 +740,17 @@ __global__ void quantize_rows16_vec_kernel(const uint16_t* __restrict__ x, int d
 __global__ void __launch_bounds__(256) micro_batch_kernel(const HoloMicroOp* __restrict__ ops, uint32_t nops) {
     holo_pdl_trigger();
     holo_pdl_wait();
+    // which op owns this CTA: up to 32 ops are looked at by one lane each (one round trip to the descriptors
+    // instead of a chain of dependent loads); the ops' CTA ranges are ascending
     uint32_t oi = 0;
-    while (oi + 1 < nops && blockIdx.x >= ops[oi].cta_begin + ops[oi].cta_count) ++oi;
+    if (nops <= 32) {
+        const uint32_t lane = threadIdx.x & 31;
+        const uint32_t end = lane < nops ? ops[lane].cta_begin + ops[lane].cta_count : 0xffffffffu;
+        oi = __popc(__ballot_sync(0xffffffffu, blockIdx.x >= end));
+        if (oi >= nops) oi = nops - 1;
+    } else {
+        while (oi + 1 < nops && blockIdx.x >= ops[oi].cta_begin + ops[oi].cta_count) ++oi;
+    }
     const HoloMicroOp op = ops[oi];
     const uint32_t block = blockIdx.x - op.cta_begin;
     switch (op.kind) {
