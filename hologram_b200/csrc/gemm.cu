@@ -213,8 +213,7 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_accum, 1);
-        holo_pdl_wait();  // the status word is the first thing read from global memory
-        *s_abort = (*reinterpret_cast<volatile uint32_t*>(p.status) & 4u) ? 1u : 0u;
+        *s_abort = 0;   // the sticky abort bit of the status word is read by an epilogue warp, off the producer's path
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -276,6 +275,8 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         // ---------------- epilogue warps (TMEM lane quarter = warp % 4) ----------------
         const uint32_t quarter = warp & 3u;
         const uint32_t row = m0 + quarter * 32 + lane;
+        // an earlier launch gave up on a wait: store nothing (the round trip to the status word overlaps the mainloop)
+        if (warp == 2 && lane == 0 && (*reinterpret_cast<volatile uint32_t*>(p.status) & 4u)) *s_abort = 1;
         if (nkb != 0) mbar_wait(bar_accum, 0, s_abort, p.status);
         asm volatile("bar.sync 1, 128;" ::: "memory");   // all four epilogue warps see the same abort state
         const bool ok = !*s_abort;

@@ -125,7 +125,9 @@ rms_norm16_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res
     const bool active = threadIdx.x < nvec;
     float v[8];
     float acc = 0.0f;
+    uint4 g = make_uint4(0, 0, 0, 0);
     if (active) {
+        if (gamma) g = gamma[threadIdx.x];   // requested with the row, not after the reduction: one round trip less
         uint4 w = x[off + threadIdx.x];
         const uint32_t* pw = &w.x;
 #pragma unroll
@@ -156,7 +158,6 @@ rms_norm16_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res
     __syncthreads();
     if (!active) return;
     const float inv = s_inv;
-    uint4 g = gamma ? gamma[threadIdx.x] : make_uint4(0, 0, 0, 0);
     const uint32_t* pg = &g.x;
     uint4 r;
     uint32_t* pr = &r.x;
