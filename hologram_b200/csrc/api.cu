@@ -565,6 +565,20 @@ int32_t do_broadcast(holo_b200_ctx* ctx, const char* name, HoloBufferRef small_r
     return holo_launch_broadcast(ctx, small, other, out, rank, in_dims, out_dims, (uint32_t)es, other_ref ? op : -1, small_is_lhs, dtype);
 }
 
+// where_float (cpu/float_kernels.rs:2908-2937)
+int32_t do_where(holo_b200_ctx* ctx, const HoloWhereCall& c, holo_b200_workspace* ws) {
+    if (!holo_is_compute_float(c.dtype)) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: where dtype %u", c.dtype);
+    const uint64_t n = c.element_count, bytes = n * holo_dtype_size(c.dtype);
+    uint8_t *cond, *a, *b, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, 0, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.cond, n, &cond, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.a, bytes, &a, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.b, bytes, &b, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.output, bytes, &out, nullptr));
+    HOLO_TRY(check_disjoint({out, bytes}, c.output.slot, {{cond, n}, {a, bytes}, {b, bytes}}));
+    return holo_launch_where(ctx, cond, a, b, out, n, c.dtype);
+}
+
 // dequant_activation (cpu/kernels.rs:311-381)
 int32_t do_dequant_activation(holo_b200_ctx* ctx, const HoloDequantActivationCall& c, holo_b200_workspace* ws) {
     const uint64_t n = c.element_count;
@@ -901,6 +915,7 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         }
         case HOLO_K_DEQUANTIZE: return do_dequantize(ctx, call->u.dequantize, ws);
         case HOLO_K_KV_CACHE_WRITE: return do_kv_write(ctx, call->u.kv_cache_write, ws);
+        case HOLO_K_WHERE: return do_where(ctx, call->u.where, ws);
         case HOLO_K_DEQUANT_ACTIVATION: return do_dequant_activation(ctx, call->u.dequant_activation, ws);
         case HOLO_K_ATTENTION: return do_attention_legacy(ctx, call->u.attention, ws);
         case HOLO_K_DECODE_ATTENTION: return do_attention_mask(ctx, call->u.decode_attention, ws);
@@ -990,6 +1005,10 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             l->out(&t.output, (uint64_t)t.batch * t.heads * t.seq * t.head_dim * holo_dtype_size(t.dtype));
             return true;
         }
+        case HOLO_K_WHERE:
+            l->in(&c->u.where.cond); l->in(&c->u.where.a); l->in(&c->u.where.b);
+            l->out(&c->u.where.output, c->u.where.element_count * holo_dtype_size(c->u.where.dtype));
+            return true;
         case HOLO_K_DEQUANT_ACTIVATION:
             l->in(&c->u.dequant_activation.input);
             l->out(&c->u.dequant_activation.output, c->u.dequant_activation.element_count * 4);

@@ -98,6 +98,11 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             for (uint32_t i = 0; i < c.rank; ++i) c.dims[i] = r.u32();
             break;
         }
+        case HOLO_K_WHERE: {
+            HoloWhereCall& c = out->u.where;
+            c.cond = r.buf(); c.a = r.buf(); c.b = r.buf(); c.output = r.buf(); c.element_count = r.u64(); c.dtype = r.u8();
+            break;
+        }
         case HOLO_K_DEQUANT_ACTIVATION: {
             HoloDequantActivationCall& c = out->u.dequant_activation;
             c.input = r.buf(); c.output = r.buf(); c.element_count = r.u64(); c.quant_dtype = r.u8(); c.act = r.u8(); c.dtype = r.u8();

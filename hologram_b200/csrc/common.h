@@ -181,6 +181,7 @@ int32_t holo_launch_layer_norm(holo_b200_ctx* ctx, const void* x, const void* ga
                                uint32_t feature, float eps, uint8_t dtype);
 int32_t holo_launch_broadcast(holo_b200_ctx* ctx, const uint8_t* small, const uint8_t* other, uint8_t* out, uint32_t rank,
                               const uint32_t* in_dims, const uint32_t* out_dims, uint32_t es, int op, int small_is_lhs, uint8_t dtype);
+int32_t holo_launch_where(holo_b200_ctx* ctx, const uint8_t* cond, const void* a, const void* b, void* out, uint64_t n, uint8_t dtype);
 int32_t holo_launch_dequant_activation(holo_b200_ctx* ctx, const uint8_t* in, float* out, uint64_t n, uint8_t quant_dtype, uint8_t act,
                                        float scale, int32_t zero_point);
 int32_t holo_launch_reduce(holo_b200_ctx* ctx, const void* in, void* out, uint32_t rank, const uint32_t* dims, uint32_t axes_mask,

@@ -199,6 +199,17 @@ __global__ void transpose_kernel(const uint8_t* __restrict__ in, uint8_t* __rest
     }
 }
 
+// where_float, cpu/float_kernels.rs:2908-2937: a byte of condition per element picks a or b; the value goes
+// through the dtype's read and write as on the CPU (an f16 NaN comes out as the one quiet pattern).
+__global__ void where_kernel(const uint8_t* __restrict__ cond, const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ out,
+                             uint64_t n, int dtype) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        holo::store_float(out, i, cond[i] != 0 ? holo::load_float(a, i, dtype) : holo::load_float(b, i, dtype), dtype);
+}
+
 // dequant_activation, cpu/kernels.rs:311-381: the composition activation((q - zp) * scale) has at most 256
 // distinct inputs, so every CTA builds the table of all of them in shared memory (one entry per thread,
 // the same f32 arithmetic and scalar activation as dequantize followed by the unary call) and then
@@ -848,6 +859,13 @@ int32_t holo_launch_rms_norm(holo_b200_ctx* ctx, const void* x, const void* resi
     } else {
         HOLO_CUDA(holo_launch_kernel(ctx, rms_norm_kernel, dim3(batch), dim3(256), 0, 1, x, residual, gamma, out, feature, eps, (int)dtype));
     }
+    LAUNCH_CHECK(ctx);
+    return HOLO_OK;
+}
+
+int32_t holo_launch_where(holo_b200_ctx* ctx, const uint8_t* cond, const void* a, const void* b, void* out, uint64_t n, uint8_t dtype) {
+    if (n == 0) return HOLO_OK;
+    HOLO_CUDA(holo_launch_kernel(ctx, where_kernel, dim3(ew_blocks(n)), dim3(EW_THREADS), 0, 1, cond, a, b, out, n, (int)dtype));
     LAUNCH_CHECK(ctx);
     return HOLO_OK;
 }

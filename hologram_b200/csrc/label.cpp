@@ -115,6 +115,7 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
             for (uint32_t i = 0; i < c.rank && i < 8; ++i) b.u32(c.dims[i]);
             return true;
         }
+        case HOLO_K_WHERE: sig->opcode = 77; b.u64(u.where.element_count).u8(u.where.dtype); return true;
         case HOLO_K_DEQUANT_ACTIVATION: {
             const HoloDequantActivationCall& c = u.dequant_activation;
             sig->opcode = 113;
@@ -245,6 +246,7 @@ bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* input
         case HOLO_K_SOFTMAX: in(u.softmax.input); *output = u.softmax.output.slot; return true;
         case HOLO_K_REDUCE_SUM: case HOLO_K_REDUCE_MEAN: case HOLO_K_REDUCE_PROD: case HOLO_K_REDUCE_MIN: case HOLO_K_REDUCE_MAX:
             in(u.reduce.input); *output = u.reduce.output.slot; return true;
+        case HOLO_K_WHERE: in(u.where.cond); in(u.where.a); in(u.where.b); *output = u.where.output.slot; return true;
         case HOLO_K_DEQUANT_ACTIVATION: in(u.dequant_activation.input); *output = u.dequant_activation.output.slot; return true;
         case HOLO_K_ATTENTION: in(u.attention.q); in(u.attention.k); in(u.attention.v); *output = u.attention.output.slot; return true;
         case HOLO_K_EXPAND: in(u.expand.input); *output = u.expand.output.slot; return true;

@@ -66,6 +66,9 @@ def encode_call(call):
         c = u.reduce
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<QBIBB", c.element_count, c.rank, c.axes_mask, c.keepdims, c.dtype) + struct.pack(
             "<%dI" % c.rank, *list(c.dims)[:c.rank])
+    if k == kc.K_WHERE:
+        c = u.where
+        return out + _buf(c.cond) + _buf(c.a) + _buf(c.b) + _buf(c.output) + struct.pack("<QB", c.element_count, c.dtype)
     if k == kc.K_DEQUANT_ACTIVATION:
         c = u.dequant_activation
         return out + _buf(c.input) + _buf(c.output) + struct.pack("<QBBBIi", c.element_count, c.quant_dtype, c.act, c.dtype, c.scale_bits, c.zero_point)

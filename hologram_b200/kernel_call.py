@@ -26,7 +26,7 @@ EXACT_UNARY = (K_NEG, K_RELU, K_SQRT, K_RECIPROCAL, K_CEIL, K_FLOOR, K_ROUND, K_
 EXACT_BINARY = (K_SUB, K_DIV, K_MOD, K_MIN, K_MAX, K_EQUAL, K_LESS, K_LESS_OR_EQUAL, K_GREATER, K_GREATER_OR_EQUAL)
 K_SIGMOID, K_TANH, K_GELU, K_SILU, K_EXP, K_ERF = 12, 13, 14, 15, 18, 32
 K_MATMUL, K_RMS_NORM, K_RESHAPE, K_ROTARY = 46, 51, 60, 75
-K_LAYER_NORM, K_EXPAND, K_BROADCAST_BINARY, K_ATTENTION, K_DEQUANT_ACTIVATION = 50, 72, 112, 69, 113
+K_LAYER_NORM, K_EXPAND, K_BROADCAST_BINARY, K_ATTENTION, K_DEQUANT_ACTIVATION, K_WHERE = 50, 72, 112, 69, 113, 78
 BROADCAST_ADD, BROADCAST_SUB, BROADCAST_MUL = 0, 1, 2
 K_REDUCE_SUM, K_REDUCE_MEAN, K_REDUCE_PROD, K_REDUCE_MIN, K_REDUCE_MAX = 55, 56, 57, 58, 59
 K_ADD_RMS_NORM, K_TRANSPOSE, K_CONCAT, K_SLICE, K_SOFTMAX = 54, 61, 62, 63, 64
@@ -122,6 +122,12 @@ class LayoutCall(C.Structure):
 
 class SoftmaxCall(C.Structure):
     _fields_ = [("input", BufferRef), ("output", BufferRef), ("batch", C.c_uint32), ("feature", C.c_uint32), ("dtype", C.c_uint8)]
+
+
+class WhereCall(C.Structure):
+    """kernel_call.rs:761-769: out[i] = cond[i] != 0 ? a[i] : b[i]; one condition byte per element."""
+    _fields_ = [("cond", BufferRef), ("a", BufferRef), ("b", BufferRef), ("output", BufferRef), ("element_count", C.c_uint64),
+                ("dtype", C.c_uint8)]
 
 
 class DequantActivationCall(C.Structure):
@@ -253,7 +259,7 @@ class _Payload(C.Union):
     _fields_ = [("unary", UnaryCall), ("binary", BinaryCall), ("matmul", MatMulCall),
                 ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("matmul_dequant", MatMulDequantCall), ("norm", NormCall),
                 ("rope", RoPECall), ("gather", GatherCall), ("cast", CastCall), ("layout", LayoutCall),
-                ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("expand", ExpandCall), ("reduce", ReduceCall), ("attention", AttentionCall), ("dequant_activation", DequantActivationCall), ("broadcast_binary", BroadcastBinaryCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
+                ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("expand", ExpandCall), ("reduce", ReduceCall), ("attention", AttentionCall), ("dequant_activation", DequantActivationCall), ("where", WhereCall), ("broadcast_binary", BroadcastBinaryCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
                 ("decode_attention", DecodeAttentionCall),
                 ("decode_attention_valid", DecodeAttentionValidCall), ("quantize_rows_i8", QuantizeRowsI8Call),
                 ("decode_attention_valid_q8", DecodeAttentionValidQ8Call), ("all_reduce", AllReduceCall),
@@ -319,6 +325,8 @@ class KernelCall(C.Structure):
     @classmethod
     def DequantActivation(cls, c): return cls.of(K_DEQUANT_ACTIVATION, c)
     @classmethod
+    def Where(cls, c): return cls.of(K_WHERE, c)
+    @classmethod
     def ReduceSum(cls, c): return cls.of(K_REDUCE_SUM, c)
     @classmethod
     def ReduceMean(cls, c): return cls.of(K_REDUCE_MEAN, c)
@@ -365,7 +373,7 @@ class KernelCall(C.Structure):
 KernelCall._FIELD = {
     UnaryCall: "unary", BinaryCall: "binary", MatMulCall: "matmul", MatMulActivationCall: "matmul_activation",
     MatMulAddCall: "matmul_add", MatMulDequantCall: "matmul_dequant", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
-    LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", ExpandCall: "expand", ReduceCall: "reduce", AttentionCall: "attention", DequantActivationCall: "dequant_activation", BroadcastBinaryCall: "broadcast_binary", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
+    LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", ExpandCall: "expand", ReduceCall: "reduce", AttentionCall: "attention", DequantActivationCall: "dequant_activation", WhereCall: "where", BroadcastBinaryCall: "broadcast_binary", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
     DecodeAttentionCall: "decode_attention", DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
     DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce", RopeQuantizeCall: "rope_quantize",
 }

@@ -111,6 +111,7 @@ extern "C" {
 #define HOLO_K_ATTENTION 69
 #define HOLO_K_EXPAND 72
 #define HOLO_K_ROTARY 75
+#define HOLO_K_WHERE 78
 #define HOLO_K_DEQUANTIZE 105
 #define HOLO_K_MATMUL_ACTIVATION 106
 #define HOLO_K_MATMUL_ADD 107
@@ -211,6 +212,13 @@ typedef struct HoloSoftmaxCall {
     uint32_t batch, feature;
     uint8_t dtype;
 } HoloSoftmaxCall;
+
+/* WhereCall (kernel_call.rs:761-769): out[i] = cond[i] != 0 ? a[i] : b[i]; cond is one byte per element. */
+typedef struct HoloWhereCall {
+    HoloBufferRef cond, a, b, output;
+    uint64_t element_count;
+    uint8_t dtype;
+} HoloWhereCall;
 
 /* DequantActivationCall (kernel_call.rs:265-290): out[i] = act((q[i] - zero_point) as f32 * scale) as f32 for a
  * per-tensor-quantized i8 / u8 / i4 input; act is a HOLO_LUT_* id. The composition is one table over the 256
@@ -401,6 +409,7 @@ typedef struct HoloKernelCall {
         HoloReduceCall reduce;
         HoloAttentionCall attention;
         HoloDequantActivationCall dequant_activation;
+        HoloWhereCall where;
         HoloBroadcastBinaryCall broadcast_binary;
         HoloDequantizeCall dequantize;
         HoloKvCacheWriteCall kv_cache_write;

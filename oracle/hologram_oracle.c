@@ -518,6 +518,12 @@ int holo_or_elementwise(int tag, const void* a, const void* b, void* out, uint64
     return 0;
 }
 
+/* ---- Where: cpu/float_kernels.rs:2908-2937 (a condition byte per element; the value passes through read / write) */
+int holo_or_where(const uint8_t* cond, const void* a, const void* b, void* out, uint64_t n, int dtype) {
+    for (uint64_t i = 0; i < n; ++i) write_float(out, i, cond[i] != 0 ? read_float(a, i, dtype) : read_float(b, i, dtype), dtype);
+    return 0;
+}
+
 /* ---- RMS norm: cpu/float_kernels.rs:1683-1756 (generic loop), epsilon :1324-1336 ------ */
 int holo_or_rms_norm(const void* x, const void* gamma, void* out, uint32_t batch, uint32_t feature,
                      uint64_t epsilon_bits, int dtype) {

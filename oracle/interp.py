@@ -90,6 +90,10 @@ def run(calls, slots, all_reduce=None):
             c = u.binary
             n = c.element_count * es(c.dtype)
             _put(slots, c.output, orc.elementwise(k, _get(slots, c.a, n, c.dtype), _get(slots, c.b, n, c.dtype), c.dtype))
+        elif k == kc.K_WHERE:
+            c = u.where
+            n = c.element_count * es(c.dtype)
+            _put(slots, c.output, orc.where(_get(slots, c.cond, c.element_count, kc.DTYPE_U8), _get(slots, c.a, n, c.dtype), _get(slots, c.b, n, c.dtype), c.dtype))
         elif k == kc.K_ATTENTION:
             c = u.attention
             hkv = c.kv_heads or c.heads

@@ -42,6 +42,7 @@ def _load(path):
         "holo_or_matmul_e8cb_omajor": (None, [_c, _c, _c, _c, _c, C.c_size_t, C.c_size_t, C.c_size_t]),
         "holo_or_matmul_i4_pc_omajor": (None, [_c, _c, _c, _c, C.c_size_t, C.c_size_t, C.c_size_t]),
         "holo_or_dequant_activation": (C.c_int, [_c, _c, C.c_uint64, C.c_int, C.c_int, C.c_float, C.c_int32]),
+        "holo_or_where": (C.c_int, [_c, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_elementwise": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_reduce": (C.c_int, [_c, _c, C.c_uint64, C.c_uint32, _c, C.c_uint32, C.c_int, C.c_int, C.c_int]),
         "holo_or_broadcast": (C.c_int, [_c, _c, _c, C.c_uint32, _c, _c, C.c_uint32, C.c_int, C.c_int, C.c_int]),
@@ -168,6 +169,13 @@ def attention(q, k, v, b, h, kv, seq, d, causal, scale_bits, dtype):
         mask[np.triu_indices(seq, 1)] = -np.inf
     empty = np.zeros(0, dtype=np.asarray(q).dtype)
     return decode_attention_mask(q, empty, empty, k, v, mask, b, h, kv, seq, 0, seq, d, scale_bits, dtype)
+
+
+def where(cond, a, b, dtype):
+    cond, a, b = (np.ascontiguousarray(v) for v in (cond, a, b))
+    out = np.empty_like(a)
+    assert lib.holo_or_where(_p(cond.view(np.uint8)), _p(a), _p(b), _p(out), a.size, dtype) == 0
+    return out
 
 
 def elementwise(tag, a, b, dtype):

@@ -75,6 +75,7 @@ def test_every_served_glue_variant_survives_the_wire():
         kc.KernelCall.DequantActivation(kc.DequantActivationCall(rb(0), rb(1), 256, kc.DTYPE_I8, kc.LUT_GELU, kc.DTYPE_F32, 0x3D4CCCCD, -7)),
         kc.KernelCall.Elementwise(kc.K_DIV, kc.BinaryCall(rb(0), rb(1), rb(2), 9, 0, kc.DTYPE_F32)),
         kc.KernelCall.Elementwise(kc.K_SQRT, kc.UnaryCall(rb(0), rb(1), 9, 0, kc.DTYPE_BF16)),
+        kc.KernelCall.Where(kc.WhereCall(rb(0), rb(1), rb(2), rb(3), 9, kc.DTYPE_BF16)),
     ]
     for n in range(1, len(calls) + 1):      # a misread length in call i would derail call i + 1
         img = holo.assemble([(holo.SEC_KERNEL_CALLS, [holo.encode_calls(calls[:n])]), (holo.SEC_WEIGHTS, [struct.pack("<I", 0)])])

@@ -452,3 +452,20 @@ def test_dequant_activation_table(backend):
         want = orc.dequant_activation(codes, n, qd, act, scale, zp)
         assert np.array_equal(ws.read(1, n * 4, np.float32).view(np.uint32), want.view(np.uint32)), (qd, act, n)
         ws.close()
+
+
+def test_where_selects_by_condition_bytes(backend):
+    # where_float (cpu/float_kernels.rs:2908-2937): bit-exact, every 16-bit code on both sides
+    rng = np.random.default_rng(78)
+    codes = np.arange(65536, dtype=np.uint16)
+    for dt, a, b in ((BF, codes, codes[::-1].copy()), (kc.DTYPE_F16, codes, codes[::-1].copy()),
+                     (kc.DTYPE_F32, rng.standard_normal(5001).astype(np.float32), rng.standard_normal(5001).astype(np.float32))):
+        cond = rng.integers(0, 3, size=a.size, dtype=np.uint8)      # 0 picks b, anything else a
+        ws = hb.DeviceWorkspace(backend, 4)
+        for i, v in enumerate((cond, a, b)):
+            ws.put(i, v)
+        ws.alloc(3, a.nbytes)
+        backend.dispatch(kc.KernelCall.Where(kc.WhereCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), a.size, dt)), ws)
+        want = orc.where(cond, a, b, dt)
+        assert np.array_equal(ws.read(3, a.nbytes, a.dtype).view(np.uint8), want.view(np.uint8))
+        ws.close()

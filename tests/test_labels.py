@@ -78,6 +78,8 @@ def test_op_signature_frozen_bytes():
         assert hs.op_signature(kc.KernelCall.Elementwise(kind, kc.BinaryCall(rb(0), rb(1), rb(2), 9, 0, kc.DTYPE_F32))) == (kind - 1, struct.pack("<QHB", 9, 0, kc.DTYPE_F32))
     dq = kc.DequantActivationCall(rb(0), rb(1), 256, kc.DTYPE_I8, kc.LUT_GELU, kc.DTYPE_F32, 0x3D4CCCCD, -7)
     assert hs.op_signature(kc.KernelCall.DequantActivation(dq)) == (113, struct.pack("<QBBBIi", 256, kc.DTYPE_I8, kc.LUT_GELU, kc.DTYPE_F32, 0x3D4CCCCD, -7))
+    wh = kc.WhereCall(rb(0), rb(1), rb(2), rb(3), 77, kc.DTYPE_BF16)
+    assert hs.op_signature(kc.KernelCall.Where(wh)) == (77, struct.pack("<QB", 77, kc.DTYPE_BF16))
     at = kc.AttentionCall(rb(0), rb(1), rb(2), rb(3), 1, 8, 31, 8, 1, 1, 0, kc.DTYPE_F32)
     assert hs.op_signature(kc.KernelCall.Attention(at)) == (68, struct.pack("<IIIIIBIB", 1, 8, 31, 8, 1, 1, 0, kc.DTYPE_F32))
     rd = kc.ReduceCall.make(rb(0), rb(1), (3, 4), 0b10, kc.DTYPE_F32)
