@@ -1,4 +1,6 @@
 """`.holo` wire format: writer vs the reference's frozen bytes, and the host-only loader checks (no GPU)."""
+import json
+import os
 import struct
 
 import blake3
@@ -14,8 +16,7 @@ from hologram_b200 import kernel_call as kc
 def test_plain_matmul_wire_bytes_are_the_reference_golden():
     # crates/hologram-archive/tests/wire_stability.rs:103-108
     c = kc.KernelCall.MatMul(kc.MatMulCall(kc.rb(0, 0, 64), kc.rb(1, 0, 64), kc.rb(2, 0, 64), 2, 8, 4, 8, 0))
-    want = ("010000002e0000000000000000000000000040000000000000000100000000000000000000004000000000000000"
-            "020000000000000000000000400000000000000002000000080000000400000008" "00")
+    want = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))["wire_bytes"]["plain_matmul"]["hex"]
     assert holo.encode_calls([c]).hex() == want
 
 

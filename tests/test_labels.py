@@ -5,6 +5,8 @@ Pins: the frozen op-signature bytes of `plain_matmul`
 (crates/hologram-archive/tests/wire_stability.rs:103-108, 116-125); label shape and sensitivity as
 in crates/hologram-archive/src/address.rs:293-330; the digest itself against the independent
 Python `blake3` package."""
+import json
+import os
 import struct
 
 import blake3
@@ -102,10 +104,9 @@ def test_matmul_dequant_signature_and_wire_are_the_frozen_bytes():
     buf = lambda i: kc.rb(i, 0, 64)
     c = kc.MatMulDequantCall(buf(0), buf(1), buf(2), buf(3), buf(4), 1, 8, 4, 4, 1, 2, 8, 0, 0, 1, 1, 0, kc.NONE)
     call = kc.KernelCall.MatMulDequant(c)
-    assert hs.op_signature(call) == (116, bytes.fromhex("010000000800000004000000040000000100000002080000000000000000010000"))
-    want = ("01000000740000000000000000000000000040000000000000000100000000000000000000004000000000000000020000000000000000"
-            "00000040000000000000000300000000000000000000004000000000000000040000000000000000000000400000000000000001000000"
-            "0800000004000000040000000100000002080000000000000000010100ffffffff00000000000000000000000000000000")
+    golden = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))["wire_bytes"]["matmul_dequant_w8a8_omajor"]
+    assert hs.op_signature(call) == (golden["signature_opcode"], bytes.fromhex(golden["signature_params_hex"]))
+    want = golden["hex"]
     assert holo.encode_calls([call]).hex() == want
 
 

@@ -1,6 +1,8 @@
 """The oracle against every known-answer value the reference's own tests hold for this path
 (no GPU). File:line citations are into the reference tree."""
 import math
+import json
+import os
 import struct
 
 import numpy as np
@@ -393,12 +395,13 @@ def test_quantized_weight_tier_restatements_reproduce_the_reference_goldens():
     a = (np.array([float(i * 37 % 91) for i in range(m * k)], dtype=np.float32) - np.float32(45.0)) * np.float32(0.031)
     scales = np.float32(0.011) + np.arange(n, dtype=np.float32) * np.float32(0.0007)
     bq = np.array([(i * 31 % 255) - 127 for i in range(k * n)], dtype=np.int8)
-    assert orc.fnv1a64_f32(orc.matmul_w8a8_omajor(a, bq, scales, m, k, n)) == 0x787CCDC172029F9B
+    golden = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))["fnv1a64_of_output_bits"]
+    assert orc.fnv1a64_f32(orc.matmul_w8a8_omajor(a, bq, scales, m, k, n)) == int(golden["i8_w8a8"], 16)
     bq4 = np.array([(i * 53 + 9) % 251 for i in range(k * n // 2)], dtype=np.uint8)
-    assert orc.fnv1a64_f32(orc.matmul_w8a8_omajor(a, bq4, scales, m, k, n, i4=True)) == 0x4C5123C024AF97AE
+    assert orc.fnv1a64_f32(orc.matmul_w8a8_omajor(a, bq4, scales, m, k, n, i4=True)) == int(golden["i4_w4a8"], 16)
     cb = np.array([(i * 37 + 11) % 255 - 127 for i in range(256 * 8)], dtype=np.int8)
     bq8 = np.array([(i * 17 + 3) % 256 for i in range(n * (k // 8))], dtype=np.uint8)
-    assert orc.fnv1a64_f32(orc.matmul_w8a8_omajor(a, bq8, scales, m, k, n, codebook=cb)) == 0x88AC55A91DD5AA0D
+    assert orc.fnv1a64_f32(orc.matmul_w8a8_omajor(a, bq8, scales, m, k, n, codebook=cb)) == int(golden["e8cb_w1a8"], 16)
 
 
 def test_mask_form_restatement_equals_scalar_form_bitwise():
