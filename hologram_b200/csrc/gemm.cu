@@ -688,7 +688,9 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
         } else {
             bn = tiles128 >= 16 ? 128 : 64;
             const uint32_t tiles = bn == 128 ? tiles128 : tiles64;
-            splits = (192 + tiles - 1) / tiles;   // measured: about one CTA per SM beats two at these sizes
+            uint32_t target = 240;   // CTAs aimed at; measured on the decoder step: 240 beats 192, 224 and 256 (1.735 / 1.745 / 1.741 / 1.779 ms)
+            if (const char* e = getenv("HOLO_GEMM_CTA_TARGET")) target = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : target;
+            splits = (target + tiles - 1) / tiles;
             if (splits > 8) splits = 8;
             if (splits > kblocks / 8) splits = kblocks / 8 ? kblocks / 8 : 1;
         }
