@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libhologram_b200.so")
-SOURCES = ["api.cu", "lut.cu", "glue.cu", "attention.cu", "gemm.cu", "quant_gemv.cu", "tp.cu", "session.cu", "archive.cpp", "blake3.cpp", "label.cpp"]
+SOURCES = ["api.cu", "lut.cu", "glue.cu", "attention.cu", "gemm.cu", "quant_gemv.cu", "tp.cu", "session.cu", "addressed.cpp", "pool.cpp", "archive.cpp", "blake3.cpp", "label.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fno-fast-math", "--expt-relaxed-constexpr",

@@ -359,14 +359,71 @@ int32_t do_matmul(holo_b200_ctx* ctx, const HoloMatMulCall& c, uint8_t act, cons
     return holo_launch_matmul(ctx, a, b, out, c.m, c.k, c.n, c.dtype, act, res);
 }
 
+// matmul_add_activation_float (cpu/float_kernels.rs:899-938): act(A . B + residual), served on the exact per-cell kernel
+int32_t do_matmul_add_activation(holo_b200_ctx* ctx, const HoloMatMulAddActivationCall& c, holo_b200_workspace* ws) {
+    const HoloMatMulCall& mm = c.mm;
+    if (mm.m == 0 || mm.k == 0 || mm.n == 0) return HOLO_OK;
+    if (mm.dtype == HOLO_DTYPE_F64)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: f64 is not a supported compute dtype (hologram computes in f16/bf16/f32)");
+    if (!holo_is_compute_float(mm.dtype))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul: only f32/f16/bf16 are supported compute dtypes (dtype %u)", mm.dtype);
+    if (mm.b_packed) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: panel-packed B is not served by this backend");
+    if (c.act != HOLO_FUSED_GELU && c.act != HOLO_FUSED_SILU && c.act != HOLO_FUSED_SIGMOID && c.act != HOLO_FUSED_TANH && c.act != HOLO_FUSED_EXP)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_add_activation: fused activation %u is not served", c.act);
+    const uint64_t es = holo_dtype_size(mm.dtype);
+    const uint64_t ab = (uint64_t)mm.m * mm.k * es, bb = (uint64_t)mm.k * mm.n * es, ob = (uint64_t)mm.m * mm.n * es;
+    uint8_t *a, *b, *out, *res;
+    HOLO_TRY(holo_resolve(ws, mm.a, ab, &a, nullptr));
+    HOLO_TRY(holo_resolve(ws, mm.b, bb, &b, nullptr));
+    HOLO_TRY(holo_resolve(ws, mm.output, ob, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.residual, ob, &res, nullptr));
+    HOLO_TRY(check_disjoint({out, ob}, mm.output.slot, {{a, ab}, {b, bb}, {res, ob}}));
+    return holo_launch_matmul_add_activation(ctx, a, b, out, mm.m, mm.k, mm.n, mm.dtype, c.act, res);
+}
+
+// matmul_dequant_float over a [k, n] weight with f32 activations (cpu/float_kernels.rs:596-731) + epilogue (:733-770)
+int32_t do_matmul_dequant_kn(holo_b200_ctx* ctx, const HoloMatMulDequantCall& c, holo_b200_workspace* ws) {
+    const bool per_channel = c.channels > 0 && c.scales.slot != HOLO_NO_SLOT;
+    if (c.codebook.slot != HOLO_NO_SLOT || c.quant_dtype == HOLO_DTYPE_E8CB)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: quant_dtype is not scalar-decodable (e8cb needs its codebook operand and the fused omajor path)");
+    if (c.quant_dtype != HOLO_DTYPE_I8 && c.quant_dtype != HOLO_DTYPE_U8 && c.quant_dtype != HOLO_DTYPE_I4)
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: unknown quantized weight tier");
+    int act = -1;
+    if (c.act != 0) {
+        if (c.act != HOLO_FUSED_GELU && c.act != HOLO_FUSED_SILU && c.act != HOLO_FUSED_SIGMOID && c.act != HOLO_FUSED_TANH && c.act != HOLO_FUSED_EXP)
+            return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: fused activation %u is not served", c.act);
+        act = c.act == HOLO_FUSED_GELU ? HOLO_LUT_GELU : c.act == HOLO_FUSED_SILU ? HOLO_LUT_SILU : c.act == HOLO_FUSED_SIGMOID ? HOLO_LUT_SIGMOID
+              : c.act == HOLO_FUSED_TANH ? HOLO_LUT_TANH : HOLO_LUT_EXP;
+    }
+    const uint64_t kn = (uint64_t)c.k * c.n;
+    const uint64_t ab = (uint64_t)c.m * c.k * 4, wb = c.quant_dtype == HOLO_DTYPE_I4 ? (kn + 1) / 2 : kn, sb = (uint64_t)c.channels * 4, ob = (uint64_t)c.m * c.n * 4;
+    uint8_t *a, *bq, *sc = nullptr, *zp = nullptr, *res = nullptr, *out;
+    HOLO_TRY(holo_resolve(ws, c.output, ob, &out, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.a, ab, &a, nullptr));
+    HOLO_TRY(holo_resolve(ws, c.bq, wb, &bq, nullptr));
+    if (per_channel) {
+        HOLO_TRY(holo_resolve(ws, c.scales, sb, &sc, nullptr));
+        HOLO_TRY(holo_resolve(ws, c.zero_points, sb, &zp, nullptr));
+    }
+    if (c.residual.slot != HOLO_NO_SLOT) HOLO_TRY(holo_resolve(ws, c.residual, ob, &res, nullptr));
+    HOLO_TRY(check_disjoint({out, ob}, c.output.slot, {{a, ab}, {bq, wb}, {sc, sc ? sb : 0}, {zp, zp ? sb : 0}, {res, res ? ob : 0}}));
+    if ((((uintptr_t)a | (uintptr_t)sc | (uintptr_t)zp | (uintptr_t)res | (uintptr_t)out) & 3u) != 0)
+        return holo_fail_slot(c.a.slot, "matmul_dequant f32 operands must be 4-byte aligned on the device");
+    float scale;
+    memcpy(&scale, &c.scale_bits, 4);
+    return holo_launch_matmul_dequant_kn(ctx, (const float*)a, bq, (const float*)sc, (const int32_t*)zp, (const float*)res, (float*)out, c.m, c.k, c.n,
+                                         c.channels, c.inner, c.quant_dtype, scale, c.zero_point, act);
+}
+
 // matmul_dequant_float, the output-major W8A8 arm (cpu/float_kernels.rs:534-596) + epilogue (:727-766)
 int32_t do_matmul_dequant(holo_b200_ctx* ctx, const HoloMatMulDequantCall& c, holo_b200_workspace* ws) {
     if (c.m == 0 || c.k == 0 || c.n == 0) return HOLO_OK;
     if (c.dtype != HOLO_DTYPE_F32) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: only f32 output is supported");
     if (!c.bq_omajor || c.act_quant != 1) {
-        if (c.bq_omajor || c.act_quant == 1)
+        // an output-major weight must never be read with the [k,n] interpretation, and W8A8 has one emitter (float_kernels.rs:534-553)
+        if (c.bq_omajor || c.act_quant != 0)
             return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: bq_omajor and W8A8 must be paired");
-        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: only the output-major W8A8 form is served by this backend");
+        return do_matmul_dequant_kn(ctx, c, ws);
     }
     const bool per_channel = c.channels > 0 && c.scales.slot != HOLO_NO_SLOT;
     const bool i4 = c.quant_dtype == HOLO_DTYPE_I4, e8 = c.quant_dtype == HOLO_DTYPE_E8CB;
@@ -889,7 +946,9 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
         case HOLO_K_MATMUL: return do_matmul(ctx, call->u.matmul, 0, nullptr, ws);
         case HOLO_K_MATMUL_ACTIVATION: return do_matmul(ctx, call->u.matmul_activation.mm, call->u.matmul_activation.act, nullptr, ws);
         case HOLO_K_MATMUL_ADD: return do_matmul(ctx, call->u.matmul_add.mm, 0, &call->u.matmul_add.residual, ws);
-        case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: return do_matmul_dequant(ctx, call->u.matmul_dequant, ws);
+        case HOLO_K_MATMUL_ADD_ACTIVATION: return do_matmul_add_activation(ctx, call->u.matmul_add_activation, ws);
+        case HOLO_K_MATMUL_DEQUANT_PLAIN: case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK:
+            return do_matmul_dequant(ctx, call->u.matmul_dequant, ws);
         case HOLO_K_LAYER_NORM: return do_norm(ctx, call->u.norm, false, true, ws);
         case HOLO_K_RMS_NORM: return do_norm(ctx, call->u.norm, false, false, ws);
         case HOLO_K_ADD_RMS_NORM: return do_norm(ctx, call->u.norm, true, false, ws);
@@ -962,11 +1021,12 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             l->in(&c->u.binary.a); l->in(&c->u.binary.b);
             l->out(&c->u.binary.output, c->u.binary.element_count * holo_dtype_size(c->u.binary.dtype));
             return true;
-        case HOLO_K_MATMUL: case HOLO_K_MATMUL_ACTIVATION: case HOLO_K_MATMUL_ADD: {
-            // the three variants start with the same MatMulCall
+        case HOLO_K_MATMUL: case HOLO_K_MATMUL_ACTIVATION: case HOLO_K_MATMUL_ADD: case HOLO_K_MATMUL_ADD_ACTIVATION: {
+            // the four variants start with the same MatMulCall
             HoloMatMulCall& mm = c->u.matmul;
             l->in(&mm.a); l->in(&mm.b);
             if (c->kind == HOLO_K_MATMUL_ADD) l->in(&c->u.matmul_add.residual);
+            if (c->kind == HOLO_K_MATMUL_ADD_ACTIVATION) l->in(&c->u.matmul_add_activation.residual);
             l->out(&mm.output, (uint64_t)mm.m * mm.n * holo_dtype_size(mm.dtype));
             return true;
         }
@@ -1093,7 +1153,7 @@ bool holo_collect_refs(HoloKernelCall* c, HoloRefList* l) {
             l->out(&q.scales, q.rows * 4);
             return true;
         }
-        case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
+        case HOLO_K_MATMUL_DEQUANT_PLAIN: case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
             auto& q = c->u.matmul_dequant;
             l->in(&q.a); l->in(&q.bq); l->in(&q.scales); l->in(&q.zero_points); l->in(&q.residual);
             if (c->kind == HOLO_K_MATMUL_DEQUANT_CODEBOOK) l->in(&q.codebook);

@@ -14,7 +14,7 @@ struct Reader {
     uint64_t n, cur = 0;
     bool ok = true;
     bool need(uint64_t k) {
-        if (!ok || cur + k > n) ok = false;
+        if (!ok || k > n - cur) ok = false;   // cur <= n always; written so that a huge k cannot wrap
         return ok;
     }
     uint8_t u8() { return need(1) ? p[cur++] : 0; }
@@ -84,6 +84,9 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
         case HOLO_K_MATMUL: get_matmul(r, out->u.matmul); break;
         case HOLO_K_MATMUL_ACTIVATION: get_matmul(r, out->u.matmul_activation.mm); out->u.matmul_activation.act = r.u8(); break;
         case HOLO_K_MATMUL_ADD: get_matmul(r, out->u.matmul_add.mm); out->u.matmul_add.residual = r.buf(); break;
+        case HOLO_K_MATMUL_ADD_ACTIVATION:
+            get_matmul(r, out->u.matmul_add_activation.mm); out->u.matmul_add_activation.residual = r.buf(); out->u.matmul_add_activation.act = r.u8();
+            break;
         case HOLO_K_LAYER_NORM: case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM: {
             HoloNormCall& c = out->u.norm;
             c.x = r.buf(); c.gamma = r.buf(); c.beta = r.buf(); c.residual = r.buf(); c.output = r.buf();
@@ -197,12 +200,14 @@ int32_t decode_call(Reader& r, HoloKernelCall* out) {
             c.head_dim = r.u32(); c.scale_bits = r.u32(); c.dtype = r.u8();
             break;
         }
-        case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
+        case HOLO_K_MATMUL_DEQUANT_PLAIN: case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
             HoloMatMulDequantCall& c = out->u.matmul_dequant;
             c.a = r.buf(); c.bq = r.buf(); c.scales = r.buf(); c.zero_points = r.buf(); c.output = r.buf();
             c.m = r.u32(); c.k = r.u32(); c.n = r.u32(); c.channels = r.u32(); c.inner = r.u32(); c.quant_dtype = r.u8(); c.dtype = r.u8();
-            c.scale_bits = r.u32(); c.zero_point = (int32_t)r.u32(); c.bq_omajor = r.u8(); c.act_quant = r.u8(); c.act = r.u8(); c.residual = r.buf();
-            c.codebook = HoloBufferRef{HOLO_NO_SLOT, 0, 0};
+            c.scale_bits = r.u32(); c.zero_point = (int32_t)r.u32();
+            c.residual = c.codebook = HoloBufferRef{HOLO_NO_SLOT, 0, 0};
+            if (d == HOLO_K_MATMUL_DEQUANT_PLAIN) break;   // D_MMDQ: every extended field at its default
+            c.bq_omajor = r.u8(); c.act_quant = r.u8(); c.act = r.u8(); c.residual = r.buf();
             if (d == HOLO_K_MATMUL_DEQUANT_CODEBOOK) c.codebook = r.buf();
             break;
         }
@@ -246,7 +251,7 @@ int32_t decode_ports(const uint8_t* p, uint64_t n, std::vector<HoloPort>* out) {
 
 }  // namespace
 
-int32_t holo_archive_parse(const uint8_t* data, uint64_t len, bool verify, HoloArchive* out) {
+int32_t holo_archive_parse(const uint8_t* data, uint64_t len, bool verify, HoloArchive* out, bool allow_missing_weights) {
     // header: magic, version in [2, 3], flags, section count (loader.rs:141-179)
     if (len < 10 + 32) return holo_fail(HOLO_ERR_INIT, "backend init failed: archive shorter than header + footer");
     if (memcmp(data, "HOLO", 4) != 0) return holo_fail(HOLO_ERR_INIT, "backend init failed: bad .holo magic");
@@ -356,10 +361,17 @@ int32_t holo_archive_parse(const uint8_t* data, uint64_t len, bool verify, HoloA
                 if (!r.need(32)) return holo_fail(HOLO_ERR_INIT, "backend init failed: truncated constant reference");
                 std::string fp((const char*)p + r.cur, 32);
                 r.cur += 32;
+                c.by_reference = true;
+                memcpy(c.fingerprint, fp.data(), 32);
                 auto it = weights.find(fp);
-                if (it == weights.end()) return holo_fail(HOLO_ERR_INIT, "backend init failed: constant references a weight that is not in the archive");
-                c.bytes = it->second.first;
-                c.len = it->second.second;
+                if (it != weights.end()) {
+                    c.bytes = it->second.first;
+                    c.len = it->second.second;
+                } else if (!allow_missing_weights) {
+                    // a weightless archive loaded without a provider must fail loud: an empty body would be
+                    // the label of empty content and every kernel downstream would read zeros (session.rs:669-686)
+                    return holo_fail(HOLO_ERR_INIT, "backend init failed: constant references a weight that is not in the archive");
+                }
             } else {
                 return holo_fail(HOLO_ERR_INIT, "backend init failed: unknown constant tag %u", tag);
             }
@@ -370,5 +382,23 @@ int32_t holo_archive_parse(const uint8_t* data, uint64_t len, bool verify, HoloA
     for (const auto& lv : out->exec_plan)
         for (uint32_t idx : lv)
             if (idx >= out->calls.size()) return holo_fail(HOLO_ERR_INIT, "backend init failed: ExecPlan index %u out of range", idx);
+    // Slot numbers size the session's tables: a well-formed archive numbers its slots densely, so
+    // none can exceed the number of buffer references it contains (12 per call at most, plus
+    // ports and constants). A larger number is a malformed image, not a reason to allocate for it.
+    const uint64_t slot_cap = 12ull * out->calls.size() + out->inputs.size() + out->outputs.size() + out->constants.size() + 64;
+    auto slot_ok = [&](uint32_t slot) { return slot == HOLO_NO_SLOT || slot < slot_cap; };
+    for (HoloKernelCall& c : out->calls) {
+        HoloRefList refs;
+        if (!holo_collect_refs(&c, &refs)) continue;
+        for (int r = 0; r < refs.n; ++r)
+            if (!slot_ok(refs.refs[r]->slot))
+                return holo_fail(HOLO_ERR_INIT, "backend init failed: slot number %u is beyond what this archive can address", refs.refs[r]->slot);
+    }
+    for (const HoloPort& p : out->inputs)
+        if (p.slot >= slot_cap) return holo_fail(HOLO_ERR_INIT, "backend init failed: slot number %u is beyond what this archive can address", p.slot);
+    for (const HoloPort& p : out->outputs)
+        if (p.slot >= slot_cap) return holo_fail(HOLO_ERR_INIT, "backend init failed: slot number %u is beyond what this archive can address", p.slot);
+    for (const HoloConstant& k : out->constants)
+        if (k.slot >= slot_cap) return holo_fail(HOLO_ERR_INIT, "backend init failed: slot number %u is beyond what this archive can address", k.slot);
     return HOLO_OK;
 }

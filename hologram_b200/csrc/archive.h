@@ -21,8 +21,10 @@ struct HoloPort {
 struct HoloConstant {
     uint32_t slot = 0;
     uint8_t dtype = 0;
-    const uint8_t* bytes = nullptr;  // points into the archive image
+    const uint8_t* bytes = nullptr;  // points into the archive image; null when the body is not in the archive (paged load only)
     uint64_t len = 0;
+    bool by_reference = false;       // constant_codec.rs tag 1: the body is a weight named by its fingerprint
+    uint8_t fingerprint[32] = {};    // BLAKE3 of the body (by_reference only)
 };
 struct HoloExtension {
     std::string key;
@@ -41,4 +43,6 @@ struct HoloArchive {
 // Parse (and, when `verify`, check the BLAKE3 footer and every weight fingerprint of) an
 // archive image. `data` must outlive `out`. Returns HOLO_OK or a negative status with the
 // thread-local message set.
-int32_t holo_archive_parse(const uint8_t* data, uint64_t len, bool verify, HoloArchive* out);
+// `allow_missing_weights`: a constant may reference a weight that the archive does not carry (a
+// weightless archive, loaded with a weight provider); otherwise that is an error.
+int32_t holo_archive_parse(const uint8_t* data, uint64_t len, bool verify, HoloArchive* out, bool allow_missing_weights = false);

@@ -22,6 +22,9 @@
 #include <cuda.h>
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
+
+#include <mutex>
 
 #include "attention_generic.cuh"
 #include "common.h"
@@ -758,6 +761,27 @@ struct StaticDevice {
     bool ready = false;
 };
 StaticDevice g_static_dev[64];
+std::mutex g_static_mutex;   // the first call on a device may come from several host threads at once
+
+// One-time set-up for the calling thread's current device. In host code the arrays' names are only
+// handles for the runtime: the addresses a kernel can use come from cudaGetSymbolAddress, with
+// this device current.
+int32_t static_device(StaticDevice** out) {
+    int dev = 0;
+    HOLO_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: device ordinal %d", dev);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticDevice& sd = g_static_dev[dev];
+    if (!sd.ready) {
+        HOLO_CUDA(cudaGetSymbolAddress(&sd.scratch, g_attn_static_scratch));
+        HOLO_CUDA(cudaGetSymbolAddress((void**)&sd.status, g_attn_static_status));
+        HOLO_CUDA(cudaDeviceGetAttribute(&sd.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        HOLO_CUDA(cudaFuncSetAttribute(decode_attention_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        sd.ready = true;
+    }
+    *out = &sd;
+    return HOLO_OK;
+}
 }  // namespace
 
 extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const void* q, const int8_t* k_past,
@@ -781,20 +805,9 @@ extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP,
                          "unsupported op: decode_attention_q8_static serves head_dim 128, at most 4 query heads per kv head, a cache "
                          "bucket that is a multiple of 4 rows, 16-byte aligned code/scale pointers and batch*kv_heads <= 65535");
-    int dev = 0;
-    HOLO_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: device ordinal %d", dev);
-    StaticDevice& sd = g_static_dev[dev];
-    if (!sd.ready) {
-        // One-time set-up for this device (its first call; make it before any stream capture).
-        // In host code the array's name is only a handle for the runtime: the address a
-        // kernel can use comes from cudaGetSymbolAddress, with this device current.
-        HOLO_CUDA(cudaGetSymbolAddress(&sd.scratch, g_attn_static_scratch));
-        HOLO_CUDA(cudaGetSymbolAddress((void**)&sd.status, g_attn_static_status));
-        HOLO_CUDA(cudaDeviceGetAttribute(&sd.sm_count, cudaDevAttrMultiProcessorCount, dev));
-        HOLO_CUDA(cudaFuncSetAttribute(decode_attention_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
-        sd.ready = true;
-    }
+    StaticDevice* sdp = nullptr;
+    HOLO_TRY(static_device(&sdp));   // the first call on a device sets it up: make it before any stream capture
+    StaticDevice& sd = *sdp;
     const uint32_t tiles = (past_len + TK - 1) / TK + 1;
     const uint32_t nctas = persistent_ctas(tiles, planes, sd.sm_count);
     const uint32_t max_slots = nctas / planes + 2;
@@ -818,10 +831,12 @@ extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const
     HOLO_TRY(make_codes_map(&mv, v_past, past_len, planes, box_rows));
     HOLO_TRY(make_scales_map(&mks, k_past_scales, past_len, planes, box_rows));
     HOLO_TRY(make_scales_map(&mvs, v_past_scales, past_len, planes, box_rows));
-    // The status word and the planes' arrival counters must start at zero (a CTA that sees
-    // status bit 1 set does not start; a launch that gave up may have left counters behind). The
-    // partials need no clearing: every (plane, slot) the merge reads is rewritten first.
-    HOLO_CUDA(cudaMemsetAsync(sd.status, 0, (64 + (size_t)planes) * sizeof(uint32_t), stream));
+    // The planes' arrival counters must start at zero (a launch that gave up may have left counts
+    // behind). The partials need no clearing: every (plane, slot) the merge reads is rewritten first.
+    // The status word is NOT cleared here: a bounded wait that gave up stays recorded (and the CTAs of
+    // later launches return at once, writing nothing) until holo_b200_decode_attention_q8_static_status
+    // has reported it.
+    HOLO_CUDA(cudaMemsetAsync(sd.status + 64, 0, (size_t)planes * sizeof(uint32_t), stream));
     FaParams p;
     p.q = q;
     p.k_new = k_new;
@@ -844,4 +859,22 @@ extern "C" int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const
     decode_attention_q8_kernel<<<nctas, FA_THREADS, SMEM_TOTAL, stream>>>(mk, mv, mks, mvs, p);
     HOLO_CUDA(cudaGetLastError());
     return HOLO_OK;
+}
+
+// Device-side failures of the allocation-free entry point. The launches above return before the
+// kernel has run, so a bounded wait that gives up inside it (its CTAs then return without writing
+// `out`) can only be reported afterwards: this call copies the 4-byte status word back on
+// `cuda_stream` (a device-to-host copy of the built-in word: no allocation), waits for the stream,
+// and returns HOLO_ERR_DISPATCH if a wait gave up since the last query, clearing the record so
+// that later calls run again. HOLO_OK otherwise.
+extern "C" int32_t holo_b200_decode_attention_q8_static_status(void* cuda_stream) {
+    StaticDevice* sd = nullptr;
+    HOLO_TRY(static_device(&sd));
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    uint32_t st = 0;
+    HOLO_CUDA(cudaMemcpyAsync(&st, sd->status, 4, cudaMemcpyDeviceToHost, stream));
+    HOLO_CUDA(cudaStreamSynchronize(stream));
+    if (st == 0) return HOLO_OK;
+    HOLO_CUDA(cudaMemsetAsync(sd->status, 0, 4, stream));
+    return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: a device-side bounded wait gave up in decode_attention_q8_static (status 0x%x)", st);
 }

@@ -48,6 +48,7 @@ struct holo_b200_ctx {
     bool record_failed = false;
     // tensor-parallel group
     void* nccl_comm = nullptr;
+    bool nccl_nonblocking = false;   // the communicator was made in NCCL's non-blocking mode: calls on it are polled to completion
     int tp_rank = 0, tp_world = 1;
     // peer-memory transport: every rank's mailbox as mapped here, per-chunk epoch counters
     bool tp_p2p = false;
@@ -235,6 +236,9 @@ struct HoloMatmulSeg {
     // when the group has the peer-memory transport, by a following all-reduce launch otherwise
     uint8_t all_reduce = 0;
 };
+// act(A . B + residual) on the exact per-cell kernel (MatMulAddActivation)
+int32_t holo_launch_matmul_add_activation(holo_b200_ctx* ctx, const void* a, const void* b, void* out, uint32_t m, uint32_t k, uint32_t n,
+                                          uint8_t dtype, uint8_t fused_act, const void* residual);
 int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* b, uint32_t m, uint32_t k, uint32_t n,
                                  uint8_t dtype, const HoloMatmulSeg* segs, uint32_t nseg);
 // quant_gemv.cu
@@ -242,6 +246,9 @@ int32_t holo_launch_matmul_e8cb_omajor(holo_b200_ctx* ctx, const float* a, const
                                        const int32_t* zero_points, const float* residual, float* out, uint32_t m, uint32_t k, uint32_t n, int act);
 int32_t holo_launch_matmul_w8a8_omajor(holo_b200_ctx* ctx, const float* a, const int8_t* bq, const float* scales, const int32_t* zero_points,
                                        const float* residual, float* out, uint32_t m, uint32_t k, uint32_t n, int act, bool i4);
+int32_t holo_launch_matmul_dequant_kn(holo_b200_ctx* ctx, const float* a, const uint8_t* bq, const float* scales, const int32_t* zero_points,
+                                      const float* residual, float* out, uint32_t m, uint32_t k, uint32_t n, uint32_t channels, uint32_t inner,
+                                      uint8_t quant_dtype, float scale, int32_t zero_point, int act);
 // tp.cu
 int32_t holo_all_reduce(holo_b200_ctx* ctx, void* buf, uint64_t n, uint8_t dtype);
 int32_t holo_all_reduce_add(holo_b200_ctx* ctx, const void* partial, const void* residual, void* out, uint64_t n, uint8_t dtype);

@@ -518,9 +518,11 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 // reference's own per-cell recurrence, an ascending-k fused multiply-add chain (mul-then-add in
 // the n % 8 column tail, cpu/simd.rs:746-799) -- bit-identical to the CPU kernel. For f32 the
 // fused activation is the scalar function itself (no table exists for 32-bit patterns).
+// `add_first` (MatMulAddActivation, cpu/float_kernels.rs:899-938): the residual is added before the activation and
+// nothing is narrowed between the two; for 16-bit dtypes the product itself is narrowed once, as the matmul stores it.
 __global__ void matmul_cell_kernel(const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ out,
                                    const uint16_t* __restrict__ table, int act, const void* __restrict__ residual, uint32_t m,
-                                   uint32_t k, uint32_t n, int dtype) {
+                                   uint32_t k, uint32_t n, int dtype, int add_first) {
     holo_pdl_trigger();
     holo_pdl_wait();
     const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x, i = blockIdx.y;
@@ -532,6 +534,16 @@ __global__ void matmul_cell_kernel(const void* __restrict__ a, const void* __res
         acc = fused ? __fmaf_rn(av, bv, acc) : __fadd_rn(acc, __fmul_rn(av, bv));
     }
     const uint64_t idx = (uint64_t)i * n + j;
+    if (add_first) {
+        if (dtype == HOLO_DTYPE_F32) {
+            acc = __fadd_rn(acc, reinterpret_cast<const float*>(residual)[idx]);
+            reinterpret_cast<float*>(out)[idx] = holo::lut_act_ref(act, acc);
+        } else {
+            const float v = __fadd_rn(holo::widen16(holo::narrow16(acc, dtype), dtype), holo::widen16(reinterpret_cast<const uint16_t*>(residual)[idx], dtype));
+            reinterpret_cast<uint16_t*>(out)[idx] = holo::narrow16(holo::lut_act_ref(act, v), dtype);
+        }
+        return;
+    }
     if (dtype == HOLO_DTYPE_F32) {
         if (act >= 0) acc = holo::lut_act_ref(act, acc);
         if (residual) acc = __fadd_rn(acc, reinterpret_cast<const float*>(residual)[idx]);
@@ -620,6 +632,15 @@ int32_t holo_launch_matmul(holo_b200_ctx* ctx, const void* a, const void* b, voi
     return holo_launch_matmul_multi(ctx, a, b, m, k, n, dtype, &sg, 1);
 }
 
+int32_t holo_launch_matmul_add_activation(holo_b200_ctx* ctx, const void* a, const void* b, void* out, uint32_t m, uint32_t k, uint32_t n,
+                                          uint8_t dtype, uint8_t fused_act, const void* residual) {
+    if (m > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul m %u on the per-cell path", m);
+    HOLO_CUDA(holo_launch_kernel(ctx, matmul_cell_kernel, dim3((n + 127) / 128, m), dim3(128), 0, 1, a, b, out, (const uint16_t*)nullptr,
+                                 lut_id_of_fused(fused_act), residual, m, k, n, (int)dtype, 1));
+    ctx->launches++;
+    return HOLO_OK;
+}
+
 // C[:, segment i] = epilogue_i(A . B[:, segment i]) for 1..3 column segments of one [k, n] B.
 int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* b, uint32_t m, uint32_t k, uint32_t n,
                                  uint8_t dtype, const HoloMatmulSeg* segs, uint32_t nseg) {
@@ -663,7 +684,7 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
         dim3 grid((n + 127) / 128, m);
         if (m > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul m %u on the per-cell path", m);
         HOLO_CUDA(holo_launch_kernel(ctx, matmul_cell_kernel, dim3(grid), dim3(128), 0, 1, a, b, out, table,
-                                     segs[0].fused_act ? lut_id_of_fused(segs[0].fused_act) : -1, residual, m, k, n, (int)dtype));
+                                     segs[0].fused_act ? lut_id_of_fused(segs[0].fused_act) : -1, residual, m, k, n, (int)dtype, 0));
         HOLO_CUDA(cudaGetLastError());
         ctx->launches++;
         return HOLO_OK;

@@ -35,6 +35,53 @@ void holo_label_derive(uint16_t opcode, const uint8_t* params, size_t params_len
     holo_label_from_digest(d, out);
 }
 
+// derive_label_boundary (address.rs:197-221): op label = address_bytes(opcode LE16 || params); every
+// operand label is folded in order through the ordered product address_bytes(left digest || right
+// digest) (compose.rs:154-164); with no operand the op label is composed with itself.
+namespace {
+bool label_digest(const uint8_t* label, uint8_t out[32]) {   // decode_blake3: "blake3:" + 64 lowercase hex digits
+    if (memcmp(label, "blake3:", 7) != 0) return false;
+    for (int i = 0; i < 32; ++i) {
+        int v = 0;
+        for (int h = 0; h < 2; ++h) {
+            const uint8_t c = label[7 + 2 * i + h];
+            int d;
+            if (c >= '0' && c <= '9') d = c - '0';
+            else if (c >= 'a' && c <= 'f') d = c - 'a' + 10;
+            else return false;
+            v = v * 16 + d;
+        }
+        out[i] = (uint8_t)v;
+    }
+    return true;
+}
+bool compose_ordered(const uint8_t* left, const uint8_t* right, uint8_t out[HOLO_LABEL_BYTES]) {
+    uint8_t canon[64];
+    if (!label_digest(left, canon) || !label_digest(right, canon + 32)) return false;
+    holo_label_of_bytes(canon, 64, out);
+    return true;
+}
+}  // namespace
+
+bool holo_label_derive_boundary(uint16_t opcode, const uint8_t* params, size_t params_len, const uint8_t* labels, size_t n_labels,
+                                uint8_t out[HOLO_LABEL_BYTES]) {
+    std::vector<uint8_t> pre;
+    pre.push_back((uint8_t)(opcode & 0xff));
+    pre.push_back((uint8_t)(opcode >> 8));
+    pre.insert(pre.end(), params, params + params_len);
+    uint8_t acc[HOLO_LABEL_BYTES], op_label[HOLO_LABEL_BYTES];
+    holo_label_of_bytes(pre.data(), pre.size(), op_label);
+    memcpy(acc, op_label, HOLO_LABEL_BYTES);
+    for (size_t i = 0; i < n_labels; ++i) {
+        uint8_t next[HOLO_LABEL_BYTES];
+        if (!compose_ordered(acc, labels + i * HOLO_LABEL_BYTES, next)) return false;
+        memcpy(acc, next, HOLO_LABEL_BYTES);
+    }
+    if (n_labels == 0 && !compose_ordered(op_label, op_label, acc)) return false;
+    memcpy(out, acc, HOLO_LABEL_BYTES);
+    return true;
+}
+
 namespace {
 // Little-endian parameter builder (kernel_call.rs:950-993).
 struct Pb {
@@ -91,6 +138,7 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
         case HOLO_K_MATMUL: sig->opcode = 45; p_matmul(b, u.matmul); return true;
         case HOLO_K_MATMUL_ACTIVATION: sig->opcode = 105; p_matmul(b, u.matmul_activation.mm); b.u8(u.matmul_activation.act); return true;
         case HOLO_K_MATMUL_ADD: sig->opcode = 106; p_matmul(b, u.matmul_add.mm); return true;
+        case HOLO_K_MATMUL_ADD_ACTIVATION: sig->opcode = 107; p_matmul(b, u.matmul_add_activation.mm); b.u8(u.matmul_add_activation.act); return true;
         case HOLO_K_LAYER_NORM: case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM: {
             const HoloNormCall& c = u.norm;
             sig->opcode = call.kind == HOLO_K_LAYER_NORM ? 49 : call.kind == HOLO_K_RMS_NORM ? 50 : 53;
@@ -176,14 +224,21 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
             p_attn(b, c.batch, c.heads, c.kv_heads, c.q_rows, c.past_len, c.new_len, c.head_dim, c.scale_bits, c.dtype);
             return true;
         }
-        case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
-            // kernel_call.rs:1472-1500: the extended tag 116 (activation quantization / epilogue present); a bound
-            // codebook takes tag 117 and one more byte
+        case HOLO_K_MATMUL_DEQUANT_PLAIN: case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
+            // kernel_call.rs:1472-1500: the all-default form keeps tag 108 and the base bytes; activation quantization
+            // or an epilogue take the extended tag 116 (the layout-only bq_omajor does not); a bound codebook takes
+            // tag 117 and one more byte
             const HoloMatMulDequantCall& c = u.matmul_dequant;
-            sig->opcode = (uint16_t)call.kind;
-            b.u32(c.m).u32(c.k).u32(c.n).u32(c.channels).u32(c.inner).u8(c.quant_dtype).u8(c.dtype).u32(c.scale_bits).i32(c.zero_point)
-                .u8(c.act_quant).u8(c.act).u8(present(c.residual) ? 1 : 0);
-            if (call.kind == HOLO_K_MATMUL_DEQUANT_CODEBOOK) b.u8(1);
+            b.u32(c.m).u32(c.k).u32(c.n).u32(c.channels).u32(c.inner).u8(c.quant_dtype).u8(c.dtype).u32(c.scale_bits).i32(c.zero_point);
+            if (present(c.codebook)) {
+                sig->opcode = 117;
+                b.u8(c.act_quant).u8(c.act).u8(present(c.residual) ? 1 : 0).u8(1);
+            } else if (c.act_quant != 0 || c.act != 0 || present(c.residual)) {
+                sig->opcode = 116;
+                b.u8(c.act_quant).u8(c.act).u8(present(c.residual) ? 1 : 0);
+            } else {
+                sig->opcode = 108;
+            }
             return true;
         }
         // extensions: the tag doubles as the opcode
@@ -209,7 +264,7 @@ bool holo_op_signature(const HoloKernelCall& call, HoloOpSignature* sig) {
     return true;
 }
 
-bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* inputs, uint32_t* output) {
+bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* inputs, uint32_t* output, bool residual_in_label) {
     inputs->clear();
     auto in = [&](const HoloBufferRef& r) {
         if (present(r)) inputs->push_back(r.slot);
@@ -227,19 +282,23 @@ bool holo_call_operands(const HoloKernelCall& call, std::vector<uint32_t>* input
             in(u.matmul_activation.mm.a); in(u.matmul_activation.mm.b); *output = u.matmul_activation.mm.output.slot; return true;
         case HOLO_K_MATMUL_ADD:
             in(u.matmul_add.mm.a); in(u.matmul_add.mm.b); in(u.matmul_add.residual); *output = u.matmul_add.mm.output.slot; return true;
-        case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
+        case HOLO_K_MATMUL_ADD_ACTIVATION: {
+            const auto& c = u.matmul_add_activation;
+            in(c.mm.a); in(c.mm.b); in(c.residual); *output = c.mm.output.slot; return true;
+        }
+        case HOLO_K_MATMUL_DEQUANT_PLAIN: case HOLO_K_MATMUL_DEQUANT: case HOLO_K_MATMUL_DEQUANT_CODEBOOK: {
             const auto& c = u.matmul_dequant;
             in(c.a); in(c.bq);
             if (c.channels > 0 && present(c.scales)) { in(c.scales); in(c.zero_points); }
-            if (call.kind == HOLO_K_MATMUL_DEQUANT_CODEBOOK) in(c.codebook);   // after the quant operands, before the residual (kernel_call.rs:1589-1598)
+            if (present(c.codebook)) in(c.codebook);   // after the quant operands, before the residual (kernel_call.rs:1589-1598)
             in(c.residual);
             *output = c.output.slot; return true;
         }
         case HOLO_K_LAYER_NORM: case HOLO_K_RMS_NORM: case HOLO_K_ADD_RMS_NORM:
-            // the reference lists x, gamma, beta (kernel_call.rs:1612-1616); the residual operand of
-            // AddRmsNorm is added here so that two sums over different residuals never share a label
+            // the reference lists x, gamma, beta (kernel_call.rs:1612-1616), for AddRmsNorm too; on request the
+            // residual operand is appended so that two sums over different residuals never share a label
             in(u.norm.x); in(u.norm.gamma); in(u.norm.beta);
-            if (call.kind == HOLO_K_ADD_RMS_NORM) in(u.norm.residual);
+            if (call.kind == HOLO_K_ADD_RMS_NORM && residual_in_label) in(u.norm.residual);
             *output = u.norm.output.slot; return true;
         case HOLO_K_RESHAPE: case HOLO_K_SLICE: in(u.layout.input); *output = u.layout.output.slot; return true;
         case HOLO_K_TRANSPOSE: in(u.transpose.input); *output = u.transpose.output.slot; return true;

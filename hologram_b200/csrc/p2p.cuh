@@ -26,9 +26,10 @@ __device__ __forceinline__ void ll_store(uint8_t* base, uint64_t unit, uint2 d, 
     asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(base + unit * 16), "r"(d.x), "r"(epoch), "r"(d.y), "r"(epoch)
                  : "memory");
 }
-// Poll one unit until both halves carry `epoch`; false after P2P_WAIT_LIMIT polls.
-__device__ __forceinline__ bool ll_load(const uint8_t* base, uint64_t unit, uint32_t epoch, uint2* d) {
-    for (uint32_t it = 0; it < P2P_WAIT_LIMIT; ++it) {
+// Poll one unit until both halves carry `epoch`; false after `limit` polls (a peer that never sends: the
+// caller records the failure and returns, the host reports it).
+__device__ __forceinline__ bool ll_load(const uint8_t* base, uint64_t unit, uint32_t epoch, uint2* d, uint32_t limit = P2P_WAIT_LIMIT) {
+    for (uint32_t it = 0; it < limit; ++it) {
         uint32_t a, fa, b, fb;
         asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(fa), "=r"(b), "=r"(fb) : "l"(base + unit * 16) : "memory");
         if (fa == epoch && fb == epoch) {

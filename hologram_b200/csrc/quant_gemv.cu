@@ -604,6 +604,83 @@ matmul_w8a8_stream_kernel(const float* __restrict__ a, const int8_t* __restrict_
     }
 }
 
+// ---- the [k, n] weight form with f32 activations ("W8A32", matmul_dequant_float, cpu/float_kernels.rs:596-731) ----
+// Two arithmetic definitions, chosen exactly as the CPU backend chooses:
+//  * fused (m <= 3, i8, one scale per output column, every zero point 0; cpu/simd.rs:3480-3570): per cell an
+//    ascending-k chain acc = fma(a, (f32)q, acc) over the integer levels, then acc * scale[j] once. The last
+//    n % 8 columns use multiply-then-add, as the scalar remainder loop does.
+//  * dequantize-then-multiply (everything else): w = (f32)(q - zp[ch]) * scale[ch] with ch = (index / inner) %
+//    channels (or the per-tensor pair), then the f32 matmul's per-cell chain (fma, multiply-then-add in the
+//    n % 8 column tail; cpu/simd.rs:709-802).
+// The two factor the scale differently, so their bits differ: the choice must be the reference's. It depends on
+// the zero-point values, which live on the device: a one-CTA kernel reduces them to a flag first.
+// One thread per four output cells of a row; bit-exact by construction (one chain per cell).
+__global__ void zero_points_all_zero_kernel(const int32_t* __restrict__ zps, uint32_t n, uint32_t* flag) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    int nonzero = 0;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) nonzero |= zps[i] != 0;
+    nonzero = __syncthreads_or(nonzero);
+    if (threadIdx.x == 0) *flag = nonzero ? 0u : 1u;
+}
+
+__device__ __forceinline__ int read_level(const uint8_t* bq, uint64_t i, int quant_dtype) {
+    if (quant_dtype == HOLO_DTYPE_I8) return (int)(int8_t)bq[i];
+    if (quant_dtype == HOLO_DTYPE_U8) return (int)bq[i];
+    const uint8_t byte = bq[i >> 1];
+    const int v = (i & 1) ? (byte >> 4) : (byte & 0x0F);
+    return v >= 8 ? v - 16 : v;
+}
+
+constexpr int KN_COLS = 4;
+__global__ void __launch_bounds__(128)
+matmul_dequant_kn_kernel(const float* __restrict__ a, const uint8_t* __restrict__ bq, const float* __restrict__ scales,
+                         const int32_t* __restrict__ zps, const float* __restrict__ residual, float* __restrict__ out, uint32_t m, uint32_t k,
+                         uint32_t n, uint32_t channels, uint32_t inner, int quant_dtype, float scale, int32_t zp, int act, int fused_eligible,
+                         const uint32_t* __restrict__ zero_flag) {
+    holo_pdl_trigger();
+    holo_pdl_wait();
+    const uint32_t j0 = (blockIdx.x * blockDim.x + threadIdx.x) * KN_COLS, i = blockIdx.y;
+    if (j0 >= n || i >= m) return;
+    const bool per_ch = scales != nullptr;
+    const bool fused = fused_eligible && *zero_flag != 0;
+    const uint32_t tail_begin = n - (n % 8);
+    float acc[KN_COLS];
+#pragma unroll
+    for (int c = 0; c < KN_COLS; ++c) acc[c] = 0.0f;
+    const float* arow = a + (uint64_t)i * k;
+    for (uint32_t kk = 0; kk < k; ++kk) {
+        const float av = arow[kk];
+#pragma unroll
+        for (int c = 0; c < KN_COLS; ++c) {
+            const uint32_t j = j0 + c;
+            if (j >= n) break;
+            const uint64_t idx = (uint64_t)kk * n + j;
+            const int q = read_level(bq, idx, quant_dtype);
+            float w;
+            if (fused) {
+                w = (float)q;
+            } else if (per_ch) {
+                const uint32_t ch = (uint32_t)((idx / inner) % channels);
+                w = __fmul_rn((float)(q - zps[ch]), scales[ch]);
+            } else {
+                w = __fmul_rn((float)(q - zp), scale);
+            }
+            acc[c] = j < tail_begin ? __fmaf_rn(av, w, acc[c]) : __fadd_rn(acc[c], __fmul_rn(av, w));
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < KN_COLS; ++c) {
+        const uint32_t j = j0 + c;
+        if (j >= n) break;
+        float y = fused ? __fmul_rn(acc[c], scales[j]) : acc[c];
+        const uint64_t o = (uint64_t)i * n + j;
+        if (residual) y = __fadd_rn(y, residual[o]);
+        if (act >= 0) y = holo::lut_act_ref(act, y);
+        out[o] = y;
+    }
+}
+
 template <int ROWS, bool I4>
 cudaError_t launch_stream(holo_b200_ctx* ctx, uint32_t grid, size_t smem, const float* a, const int8_t* bq, const float* scales,
                           const int32_t* zero_points, const float* residual, float* out, uint32_t m0, uint32_t rows, uint32_t k,
@@ -691,5 +768,29 @@ int32_t holo_launch_matmul_w8a8_omajor(holo_b200_ctx* ctx, const float* a, const
                                      zero_points, residual, out, m0, take, k, n, act, ctx->dev_status));
         ctx->launches++;
     }
+    return HOLO_OK;
+}
+
+
+// MatMulDequant over a [k, n] weight with f32 activations (see matmul_dequant_kn_kernel). `scales` / `zero_points`
+// null = per-tensor (scale, zero_point).
+int32_t holo_launch_matmul_dequant_kn(holo_b200_ctx* ctx, const float* a, const uint8_t* bq, const float* scales, const int32_t* zero_points,
+                                      const float* residual, float* out, uint32_t m, uint32_t k, uint32_t n, uint32_t channels, uint32_t inner,
+                                      uint8_t quant_dtype, float scale, int32_t zero_point, int act) {
+    if (m == 0 || k == 0 || n == 0) return HOLO_OK;
+    if (m > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul_dequant: m %u on the [k,n] path", m);
+    const bool per_ch = scales != nullptr;
+    if (inner == 0) inner = 1;
+    // FUSED_W8A32_MAX_M = 3 (kernel_call.rs decode_gate)
+    const int fused_eligible = per_ch && quant_dtype == HOLO_DTYPE_I8 && m <= 3 && channels == n && inner == 1;
+    uint32_t* flag = ctx->dev_status + 16;   // a spare word of the status block
+    if (fused_eligible) {
+        HOLO_CUDA(holo_launch_kernel(ctx, zero_points_all_zero_kernel, dim3(1), dim3(256), 0, 1, zero_points, n, flag));
+        ctx->launches++;
+    }
+    const uint32_t per_cta = 128 * KN_COLS;
+    HOLO_CUDA(holo_launch_kernel(ctx, matmul_dequant_kn_kernel, dim3((n + per_cta - 1) / per_cta, m), dim3(128), 0, 1, a, bq, scales, zero_points, residual,
+                                 out, m, k, n, channels, inner, (int)quant_dtype, scale, zero_point, act, fused_eligible, (const uint32_t*)flag));
+    ctx->launches++;
     return HOLO_OK;
 }

@@ -21,85 +21,7 @@
 #include <string>
 #include <unordered_map>
 
-#include "archive.h"
-#include "common.h"
-#include "label.h"
-
-// A merged group of sibling matmuls: products of one A against several constant weights,
-// executed as one matmul against the column-concatenated weights with one output segment each.
-struct MergedMatmul {
-    HoloBufferRef a;
-    uint32_t m = 0, k = 0, n = 0, nseg = 0;
-    void* b_concat = nullptr;          // [k, n] bf16, owned by the session
-    HoloBufferRef out[3];
-    uint32_t width[3] = {0, 0, 0};
-    uint8_t act[3] = {0, 0, 0};
-    HoloBufferRef b_src[3];
-    // gated pair: out[0] = act(A W0), out[1] = A W1 and the Mul of the two run as one product whose
-    // weights alternate 64-column blocks of W0 and W1; `gated_out` receives act(A W0) * (A W1)
-    bool gated = false;
-    HoloBufferRef gated_out = {HOLO_NO_SLOT, 0, 0};
-};
-
-// A run of mutually independent small glue calls executed as one launch.
-struct MicroBatch {
-    HoloMicroOp* dev_ops = nullptr;    // owned by the session
-    uint32_t nops = 0, total_ctas = 0, ncalls = 0;
-};
-
-struct SessionNode {
-    int merged = -1;                   // index into holo_b200_session::merged, or -1
-    int batch = -1;                    // index into holo_b200_session::batches, or -1
-    HoloKernelCall call;               // the plain call when both are -1
-    // AllReduce followed by the residual Add, run as one launch: `call` is the AllReduce,
-    // `residual` / `sum_out` come from the Add
-    bool reduce_add = false;
-    HoloBufferRef residual = {HOLO_NO_SLOT, 0, 0}, sum_out = {HOLO_NO_SLOT, 0, 0};
-    // MatMul whose product is all-reduced and added to a residual: `call` is the MatMul; the sum over
-    // the ranks happens in the matmul's epilogue (or right after it), `residual` / `sum_out` as above
-    bool matmul_reduce_add = false;
-};
-
-struct holo_b200_session {
-    holo_b200_ctx* ctx = nullptr;
-    holo_b200_workspace* ws = nullptr;
-    HoloArchive ar;
-    std::vector<HoloKernelCall> calls;  // execution order, after fusion (merged groups keep their members here)
-    std::vector<SessionNode> nodes;     // what a walk actually launches
-    std::vector<MergedMatmul> merged;
-    std::vector<MicroBatch> batches;
-    uint32_t fused = 0, moved_in_place = 0, merged_calls = 0, batched_calls = 0, reduce_adds = 0, rope_quant = 0;
-    uint64_t device_bytes = 0;
-    cudaGraphExec_t graph = nullptr;
-
-    // ---- content-addressed execution (loaded with HOLO_SESSION_ADDRESSED) ----
-    // The walk of crates/hologram-exec/src/session.rs:1052-1289 over device memory: every value
-    // has a label derived from its operation and its operands' labels; the pool keeps device
-    // buffers by label, so a value that is already resident is bound to its consumer's slot by
-    // pointer (no dispatch, no copy, no host round trip), and a whole-graph repeat is answered
-    // from the memo of input labels -> output labels.
-    bool addressed = false;
-    struct NodeMeta {
-        HoloOpSignature sig;
-        std::vector<uint32_t> inputs, outputs;
-        bool addressable = false;
-    };
-    struct PoolEntry {
-        void* ptr = nullptr;
-        uint64_t bytes = 0;
-        uint64_t last_walk = 0;
-    };
-    std::vector<NodeMeta> meta;                           // one per call
-    std::vector<uint64_t> slot_need;                      // bytes a slot must hold
-    std::vector<HoloSlot> static_binding;                 // the load-time buffer of every slot
-    std::vector<std::string> slot_label_init;             // constants' labels ("" = none)
-    std::vector<uint8_t> is_output_slot;
-    std::unordered_map<std::string, PoolEntry> pool;      // label -> resident device buffer (owned)
-    std::vector<PoolEntry> free_list;                     // released buffers, reused best-fit <= 2x
-    std::vector<PoolEntry> transients;                    // unlabelled results of the current walk
-    std::unordered_map<std::string, std::pair<std::string, uint64_t>> memo;   // input labels -> (output labels, tick)
-    uint64_t walk_no = 0, memo_tick = 0, pool_bytes = 0;
-};
+#include "session.h"
 
 namespace {
 
@@ -116,72 +38,118 @@ uint8_t fused_act_of(uint16_t kind) {  // KernelCall::fused_activation, kernel_c
     }
 }
 
-// fuse_matmul_epilogue: a bf16 MatMul whose output is read by exactly one later call, which is
-// a table-backed activation over the whole product or an Add with the product as one operand,
-// and is not itself a graph output, is folded into that consumer's position.
-uint32_t fuse_matmul_epilogue(std::vector<HoloKernelCall>& calls, const std::set<uint32_t>& output_slots) {
-    uint32_t fused = 0;
-    std::vector<bool> dead(calls.size(), false);
-    for (size_t i = 0; i < calls.size(); ++i) {
-        if (dead[i] || calls[i].kind != HOLO_K_MATMUL) continue;
-        const HoloMatMulCall mm = calls[i].u.matmul;
-        if (mm.dtype != HOLO_DTYPE_BF16 && mm.dtype != HOLO_DTYPE_F16 && mm.dtype != HOLO_DTYPE_F32) continue;
-        if (output_slots.count(mm.output.slot)) continue;
-        int consumer = -1, readers = 0;
-        bool clobbered = false;
-        for (size_t j = i + 1; j < calls.size(); ++j) {
-            if (dead[j]) continue;
-            HoloKernelCall tmp = calls[j];
-            HoloRefList refs;
-            if (!holo_collect_refs(&tmp, &refs)) continue;
-            for (int r = 0; r < refs.n; ++r) {
-                if (refs.refs[r]->slot != mm.output.slot) continue;
-                if (refs.written[r]) clobbered = true;
-                else {
-                    ++readers;
-                    consumer = (int)j;
+// fuse_matmul_epilogue (session.rs:2150-2377), with the reference's rules: the producer is a MatMul whose
+// output slot has exactly one producer and exactly one reader in the whole call list and is not a graph
+// output; the reader is a table-backed activation over it, or an Add with it as one operand whose other
+// operand (the residual) is produced at a strictly earlier schedule level than the matmul (or by no call:
+// an input or a constant). The fused call takes the PRODUCER's place; the reader is dropped. For f32 an
+// activation that is the single reader of the Add's result is absorbed too (MatMulAddActivation: with no
+// narrowing to skip, the triple is bit-identical to the three calls).
+uint32_t fuse_matmul_epilogue(std::vector<HoloKernelCall>& calls, std::vector<uint32_t>& level, const std::set<uint32_t>& output_slots) {
+    const size_t n = calls.size();
+    std::unordered_map<uint32_t, uint32_t> prod_count, read_count, slot_level;
+    std::unordered_map<uint32_t, size_t> read_idx;
+    for (size_t i = 0; i < n; ++i) {
+        HoloKernelCall tmp = calls[i];
+        HoloRefList refs;
+        if (!holo_collect_refs(&tmp, &refs)) continue;
+        for (int r = 0; r < refs.n; ++r) {
+            const uint32_t slot = refs.refs[r]->slot;
+            if (slot == HOLO_NO_SLOT) continue;
+            if (refs.written[r]) {
+                ++prod_count[slot];
+                slot_level[slot] = level[i];
+                if (calls[i].kind == HOLO_K_ALL_REDUCE) {   // rewritten in place: also a reader
+                    ++read_count[slot];
+                    read_idx[slot] = i;
                 }
+            } else {
+                ++read_count[slot];
+                read_idx[slot] = i;
             }
         }
-        if (readers != 1 || clobbered || consumer < 0) continue;
-        HoloKernelCall& c = calls[consumer];
-        const uint64_t count = (uint64_t)mm.m * mm.n;
+    }
+    std::vector<bool> absorbed(n, false), has_fused(n, false);
+    std::vector<HoloKernelCall> fused(n);
+    uint32_t count = 0;
+    for (size_t i = 0; i < n; ++i) {
+        if (calls[i].kind != HOLO_K_MATMUL) continue;
+        const HoloMatMulCall mm = calls[i].u.matmul;
+        if (mm.dtype != HOLO_DTYPE_BF16 && mm.dtype != HOLO_DTYPE_F16 && mm.dtype != HOLO_DTYPE_F32) continue;
+        const uint32_t s = mm.output.slot;
+        if (s == HOLO_NO_SLOT || output_slots.count(s)) continue;
+        if (prod_count[s] != 1 || read_count[s] != 1) continue;
+        const size_t j = read_idx[s];
+        if (j == i || absorbed[j]) continue;
+        const HoloKernelCall& c = calls[j];
+        const uint64_t cells = (uint64_t)mm.m * mm.n;
         const uint8_t act = fused_act_of(c.kind);
-        if (act && same_range(c.u.unary.input, mm.output) && c.u.unary.element_count == count && c.u.unary.dtype == mm.dtype) {
-            HoloKernelCall f;
-            memset(&f, 0, sizeof f);
+        HoloKernelCall f;
+        memset(&f, 0, sizeof f);
+        if (act) {
+            if (!same_range(c.u.unary.input, mm.output) || c.u.unary.element_count != cells || c.u.unary.dtype != mm.dtype) continue;
             f.kind = HOLO_K_MATMUL_ACTIVATION;
             f.u.matmul_activation.mm = mm;
             f.u.matmul_activation.mm.output = c.u.unary.output;
             f.u.matmul_activation.act = act;
-            c = f;
-            dead[i] = true;
-            ++fused;
-        } else if (c.kind == HOLO_K_ADD && c.u.binary.element_count == count && c.u.binary.dtype == mm.dtype &&
-                   (same_range(c.u.binary.a, mm.output) != same_range(c.u.binary.b, mm.output))) {
-            HoloKernelCall f;
-            memset(&f, 0, sizeof f);
-            f.kind = HOLO_K_MATMUL_ADD;
-            f.u.matmul_add.mm = mm;
-            f.u.matmul_add.mm.output = c.u.binary.output;
-            f.u.matmul_add.residual = same_range(c.u.binary.a, mm.output) ? c.u.binary.b : c.u.binary.a;
-            c = f;
-            dead[i] = true;
-            ++fused;
+            fused[i] = f;
+            has_fused[i] = true;
+            absorbed[j] = true;
+            ++count;
+        } else if (c.kind == HOLO_K_ADD) {
+            if (c.u.binary.element_count != cells || c.u.binary.dtype != mm.dtype) continue;
+            if (same_range(c.u.binary.a, mm.output) == same_range(c.u.binary.b, mm.output)) continue;
+            const HoloBufferRef residual = same_range(c.u.binary.a, mm.output) ? c.u.binary.b : c.u.binary.a;
+            // the residual must be ready no later than the matmul that absorbs it
+            auto rl = slot_level.find(residual.slot);
+            if (rl != slot_level.end() && !(rl->second < level[i])) continue;
+            const uint32_t add_out = c.u.binary.output.slot;
+            bool triple = false;
+            if (mm.dtype == HOLO_DTYPE_F32 && add_out != HOLO_NO_SLOT && !output_slots.count(add_out) && prod_count[add_out] == 1 &&
+                read_count[add_out] == 1) {
+                const size_t k = read_idx[add_out];
+                const uint8_t act2 = k != j && !absorbed[k] ? fused_act_of(calls[k].kind) : 0;
+                if (act2 && same_range(calls[k].u.unary.input, c.u.binary.output) && calls[k].u.unary.element_count == cells &&
+                    calls[k].u.unary.dtype == mm.dtype) {
+                    f.kind = HOLO_K_MATMUL_ADD_ACTIVATION;
+                    f.u.matmul_add_activation.mm = mm;
+                    f.u.matmul_add_activation.mm.output = calls[k].u.unary.output;
+                    f.u.matmul_add_activation.residual = residual;
+                    f.u.matmul_add_activation.act = act2;
+                    absorbed[k] = true;
+                    ++count;
+                    triple = true;
+                }
+            }
+            if (!triple) {
+                f.kind = HOLO_K_MATMUL_ADD;
+                f.u.matmul_add.mm = mm;
+                f.u.matmul_add.mm.output = c.u.binary.output;
+                f.u.matmul_add.residual = residual;
+            }
+            fused[i] = f;
+            has_fused[i] = true;
+            absorbed[j] = true;
+            ++count;
         }
     }
     std::vector<HoloKernelCall> kept;
-    for (size_t i = 0; i < calls.size(); ++i)
-        if (!dead[i]) kept.push_back(calls[i]);
+    std::vector<uint32_t> kept_level;
+    for (size_t i = 0; i < n; ++i) {
+        if (absorbed[i]) continue;
+        kept.push_back(has_fused[i] ? fused[i] : calls[i]);
+        kept_level.push_back(level[i]);
+    }
     calls.swap(kept);
-    return fused;
+    level.swap(kept_level);
+    return count;
 }
 
 // A RotaryEmbedding whose output is read by a QuantizeRowsI8 over rows of the RoPE's head_dim (the K
 // path of a decoder layer) becomes one call that does both; the quantizer then no longer depends on
 // a separate launch and can share a batched launch with its siblings. The RoPE output is still
 // written (other readers keep working).
-uint32_t fuse_rope_quantize(std::vector<HoloKernelCall>& calls) {
+uint32_t fuse_rope_quantize(std::vector<HoloKernelCall>& calls, std::vector<uint32_t>& level) {
     if (getenv("HOLO_SESSION_NO_ROPE_QUANT")) return 0;
     uint32_t fused = 0;
     std::vector<bool> dead(calls.size(), false);
@@ -235,9 +203,14 @@ uint32_t fuse_rope_quantize(std::vector<HoloKernelCall>& calls) {
         }
     }
     std::vector<HoloKernelCall> kept;
+    std::vector<uint32_t> kept_level;
     for (size_t i = 0; i < calls.size(); ++i)
-        if (!dead[i]) kept.push_back(calls[i]);
+        if (!dead[i]) {
+            kept.push_back(calls[i]);
+            kept_level.push_back(level[i]);
+        }
     calls.swap(kept);
+    level.swap(kept_level);
     return fused;
 }
 
@@ -596,223 +569,7 @@ int32_t plan_micro_batches(holo_b200_session* s) {
     return HOLO_OK;
 }
 
-// ---- content-addressed execution ---------------------------------------------------------------
-std::string label_str(const uint8_t* l) { return std::string(reinterpret_cast<const char*>(l), HOLO_LABEL_BYTES); }
-
-int32_t prepare_addressed(holo_b200_session* s) {
-    const size_t n_slots = s->ws->slots.size();
-    s->static_binding = s->ws->slots;
-    s->slot_label_init.assign(n_slots, std::string());
-    s->is_output_slot.assign(n_slots, 0);
-    for (const HoloPort& p : s->ar.outputs) s->is_output_slot[p.slot] = 1;
-    // constants are leaves: their label is the label of their bytes (for a weight that is the
-    // archive's fingerprint, crates/hologram-archive/src/address.rs:63-74)
-    for (const HoloConstant& k : s->ar.constants) {
-        uint8_t l[HOLO_LABEL_BYTES];
-        holo_label_of_bytes(k.bytes, k.len, l);
-        s->slot_label_init[k.slot] = label_str(l);
-    }
-    s->meta.resize(s->calls.size());
-    for (size_t i = 0; i < s->calls.size(); ++i) {
-        holo_b200_session::NodeMeta& m = s->meta[i];
-        const HoloKernelCall& c = s->calls[i];
-        uint32_t out = HOLO_NO_SLOT;
-        m.addressable = holo_op_signature(c, &m.sig) && holo_call_operands(c, &m.inputs, &out);
-        if (m.addressable) {
-            m.outputs.push_back(out);
-        } else if (c.kind == HOLO_K_QUANTIZE_ROWS_I8) {
-            // two outputs: codes take the plain derivation, scales the derivation with an index byte
-            m.addressable = holo_op_signature(c, &m.sig);
-            m.inputs = {c.u.quantize_rows_i8.input.slot};
-            m.outputs = {c.u.quantize_rows_i8.codes.slot, c.u.quantize_rows_i8.scales.slot};
-        } else {
-            HoloKernelCall tmp = c;
-            HoloRefList refs;
-            if (holo_collect_refs(&tmp, &refs))
-                for (int r = 0; r < refs.n; ++r)
-                    if (refs.written[r]) m.outputs.push_back(refs.refs[r]->slot);
-        }
-    }
-    return HOLO_OK;
-}
-
-// A zero-filled device buffer of at least `bytes`: the best fit from the released buffers that
-// is no more than twice the size (crates/hologram-exec/src/buffer.rs:528-551), else a new one.
-int32_t pool_acquire(holo_b200_session* s, uint64_t bytes, holo_b200_session::PoolEntry* out) {
-    bytes = (std::max<uint64_t>(bytes, 64) + 63) & ~63ull;
-    int best = -1;
-    for (size_t i = 0; i < s->free_list.size(); ++i) {
-        const uint64_t have = s->free_list[i].bytes;
-        if (have >= bytes && have <= 2 * bytes && (best < 0 || have < s->free_list[best].bytes)) best = (int)i;
-    }
-    if (best >= 0) {
-        *out = s->free_list[best];
-        s->free_list.erase(s->free_list.begin() + best);
-    } else {
-        out->ptr = nullptr;
-        HOLO_CUDA(cudaMalloc(&out->ptr, bytes));
-        out->bytes = bytes;
-        s->pool_bytes += bytes;
-    }
-    HOLO_CUDA(cudaMemsetAsync(out->ptr, 0, out->bytes, s->ctx->stream));   // reuse never leaks old bytes (buffer.rs:86-108)
-    return HOLO_OK;
-}
-
-void bind_slot_static(holo_b200_session* s, uint32_t slot) {
-    s->ws->slots[slot].ptr = s->static_binding[slot].ptr;
-    s->ws->slots[slot].bytes = s->static_binding[slot].bytes;
-    s->ws->slots[slot].owned = false;
-}
-
-void bind_slot(holo_b200_session* s, uint32_t slot, void* ptr, uint64_t bytes) {
-    HoloSlot& sl = s->ws->slots[slot];
-    sl.ptr = ptr;
-    sl.bytes = bytes;
-    sl.owned = false;   // the pool (or static_binding) owns it
-}
-
 }  // namespace
-
-extern "C" int32_t holo_b200_session_execute_addressed(holo_b200_session* s, const uint8_t* input_labels, uint32_t n_inputs,
-                                                       uint8_t* output_labels, uint32_t n_outputs, HoloAddressedStats* stats) {
-    if (!s) return holo_fail(HOLO_ERR_INIT, "null session");
-    if (!s->addressed) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: the session was not loaded with HOLO_SESSION_ADDRESSED");
-    if (n_inputs != s->ar.inputs.size() || n_outputs != s->ar.outputs.size() || !input_labels || !output_labels)
-        return holo_fail(HOLO_ERR_SHAPE_MISMATCH, "shape mismatch: execute_addressed takes %zu input labels and %zu output labels",
-                         s->ar.inputs.size(), s->ar.outputs.size());
-    HOLO_CUDA(cudaSetDevice(s->ctx->device));
-    HoloAddressedStats st = {};
-    ++s->walk_no;
-
-    // whole-graph memo (session.rs:63-111): the same input labels give the same output labels;
-    // the outputs are bound from the pool if they are all still resident
-    const std::string key(reinterpret_cast<const char*>(input_labels), (size_t)n_inputs * HOLO_LABEL_BYTES);
-    auto hit = s->memo.find(key);
-    if (hit != s->memo.end()) {
-        bool resident = true;
-        for (uint32_t o = 0; o < n_outputs && resident; ++o)
-            resident = s->pool.count(hit->second.first.substr((size_t)o * HOLO_LABEL_BYTES, HOLO_LABEL_BYTES)) != 0;
-        if (resident) {
-            hit->second.second = ++s->memo_tick;
-            for (uint32_t o = 0; o < n_outputs; ++o) {
-                holo_b200_session::PoolEntry& e = s->pool[hit->second.first.substr((size_t)o * HOLO_LABEL_BYTES, HOLO_LABEL_BYTES)];
-                e.last_walk = s->walk_no;
-                bind_slot(s, s->ar.outputs[o].slot, e.ptr, e.bytes);
-            }
-            memcpy(output_labels, hit->second.first.data(), (size_t)n_outputs * HOLO_LABEL_BYTES);
-            st.memo_hit = 1;
-            st.pool_bytes = s->pool_bytes;
-            if (stats) *stats = st;
-            return HOLO_OK;
-        }
-    }
-
-    // results of the previous walk that had no label are free again
-    for (auto& e : s->transients) s->free_list.push_back(e);
-    s->transients.clear();
-
-    std::vector<std::string> label = s->slot_label_init;
-    for (uint32_t i = 0; i < n_inputs; ++i) {
-        const uint32_t slot = s->ar.inputs[i].slot;
-        label[slot] = label_str(input_labels + (size_t)i * HOLO_LABEL_BYTES);
-        bind_slot(s, slot, s->static_binding[slot].ptr, s->static_binding[slot].bytes);   // the caller wrote the input there
-    }
-    for (size_t ci = 0; ci < s->calls.size(); ++ci) {
-        const holo_b200_session::NodeMeta& m = s->meta[ci];
-        // operand labels, in kernel order; a commutative op sorts them (session.rs:1095-1102)
-        std::vector<std::string> in;
-        bool addressable = m.addressable;
-        for (uint32_t sl : m.inputs) {
-            if (label[sl].empty()) { addressable = false; break; }
-            in.push_back(label[sl]);
-        }
-        std::vector<std::string> out_label(m.outputs.size());
-        if (addressable) {
-            if (m.sig.commutative) std::sort(in.begin(), in.end());
-            std::string cat;
-            for (const std::string& l : in) cat += l;
-            for (size_t o = 0; o < m.outputs.size(); ++o) {
-                uint8_t l[HOLO_LABEL_BYTES];
-                if (s->calls[ci].kind == HOLO_K_RESHAPE && !in.empty()) {
-                    out_label[o] = in[0];   // a reshape relabels nothing: its value is its input's (session.rs:1107-1114)
-                    continue;
-                }
-                uint8_t params[80];
-                memcpy(params, m.sig.params, m.sig.len);
-                size_t plen = m.sig.len;
-                if (o > 0) params[plen++] = (uint8_t)o;
-                holo_label_derive(m.sig.opcode, params, plen, reinterpret_cast<const uint8_t*>(cat.data()), in.size(), l);
-                out_label[o] = label_str(l);
-            }
-        }
-        // interior reuse: every result resident and none a graph output -> bind, do not dispatch
-        bool reuse = addressable;
-        for (size_t o = 0; o < m.outputs.size() && reuse; ++o)
-            reuse = !s->is_output_slot[m.outputs[o]] && s->pool.count(out_label[o]) != 0;
-        if (reuse) {
-            for (size_t o = 0; o < m.outputs.size(); ++o) {
-                holo_b200_session::PoolEntry& e = s->pool[out_label[o]];
-                e.last_walk = s->walk_no;
-                bind_slot(s, m.outputs[o], e.ptr, e.bytes);
-                label[m.outputs[o]] = out_label[o];
-            }
-            ++st.skipped;
-            continue;
-        }
-        for (size_t o = 0; o < m.outputs.size(); ++o) {
-            const uint32_t slot = m.outputs[o];
-            holo_b200_session::PoolEntry e;
-            HOLO_TRY(pool_acquire(s, slot < s->slot_need.size() ? s->slot_need[slot] : 64, &e));
-            e.last_walk = s->walk_no;
-            bind_slot(s, slot, e.ptr, e.bytes);
-            if (addressable) {
-                auto old = s->pool.find(out_label[o]);
-                if (old != s->pool.end()) s->free_list.push_back(old->second);   // recomputed (a graph output): the old copy goes
-                s->pool[out_label[o]] = e;
-                label[slot] = out_label[o];
-            } else {
-                s->transients.push_back(e);
-                label[slot].clear();
-            }
-        }
-        HOLO_TRY(holo_dispatch_internal(s->ctx, &s->calls[ci], s->ws));
-        ++st.dispatched;
-    }
-    // output labels; an output without a label (not derivable) reports 71 zero bytes
-    std::string outs;
-    bool all = true;
-    for (uint32_t o = 0; o < n_outputs; ++o) {
-        const std::string& l = label[s->ar.outputs[o].slot];
-        if (l.empty()) {
-            memset(output_labels + (size_t)o * HOLO_LABEL_BYTES, 0, HOLO_LABEL_BYTES);
-            all = false;
-        } else {
-            memcpy(output_labels + (size_t)o * HOLO_LABEL_BYTES, l.data(), HOLO_LABEL_BYTES);
-        }
-        outs += l.empty() ? std::string(HOLO_LABEL_BYTES, '\0') : l;
-    }
-    if (all) {
-        if (s->memo.size() >= 1024 && !s->memo.count(key)) {   // least recently used entry goes (session.rs:93-105)
-            auto lru = s->memo.begin();
-            for (auto it = s->memo.begin(); it != s->memo.end(); ++it)
-                if (it->second.second < lru->second.second) lru = it;
-            s->memo.erase(lru);
-        }
-        s->memo[key] = {outs, ++s->memo_tick};
-    }
-    // two-generation rotation: what neither this walk nor the one before touched is released
-    for (auto it = s->pool.begin(); it != s->pool.end();) {
-        if (it->second.last_walk + 1 < s->walk_no) {
-            s->free_list.push_back(it->second);
-            it = s->pool.erase(it);
-        } else {
-            ++it;
-        }
-    }
-    st.pool_bytes = s->pool_bytes;
-    if (stats) *stats = st;
-    return HOLO_OK;
-}
 
 extern "C" int32_t holo_b200_label_bytes(const uint8_t* data, uint64_t len, uint8_t out71[71]) {
     if ((!data && len) || !out71) return holo_fail(HOLO_ERR_INIT, "null argument");
@@ -854,12 +611,22 @@ int32_t run_calls(holo_b200_session* s) {
 
 extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* archive, uint64_t len, int32_t verify,
                                           holo_b200_session** out) {
+    return holo_session_load_impl(ctx, archive, len, verify, nullptr, 0, out);
+}
+
+int32_t holo_session_load_impl(holo_b200_ctx* ctx, const uint8_t* archive, uint64_t len, int32_t verify, const HoloWeightProvider* provider,
+                               uint64_t budget, holo_b200_session** out) {
     if (!ctx || !archive || !out) return holo_fail(HOLO_ERR_INIT, "backend init failed: null argument");
     HOLO_CUDA(cudaSetDevice(ctx->device));
     holo_b200_session* s = new holo_b200_session();
     s->ctx = ctx;
-    s->addressed = (verify & HOLO_SESSION_ADDRESSED) != 0;
-    int32_t rc = holo_archive_parse(archive, len, (verify & HOLO_SESSION_VERIFY) != 0, &s->ar);
+    s->addressed = (verify & HOLO_SESSION_ADDRESSED) != 0 || provider != nullptr;
+    s->ad.residual_in_label = (verify & HOLO_SESSION_LABEL_RESIDUAL) != 0;
+    if (provider) {
+        s->ad.provider = *provider;
+        s->ad.paged = true;
+    }
+    int32_t rc = holo_archive_parse(archive, len, (verify & HOLO_SESSION_VERIFY) != 0, &s->ar, provider != nullptr);
     if (rc != HOLO_OK) {
         delete s;
         return rc;
@@ -867,15 +634,29 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
     // execution order: ExecPlan levels, else one level in call order (session.rs:473)
     if (s->ar.exec_plan.empty()) {
         s->calls = s->ar.calls;
+        s->call_level.assign(s->calls.size(), 0);
     } else {
-        for (const auto& lv : s->ar.exec_plan)
-            for (uint32_t idx : lv) s->calls.push_back(s->ar.calls[idx]);
+        for (size_t li = 0; li < s->ar.exec_plan.size(); ++li)
+            for (uint32_t idx : s->ar.exec_plan[li]) {
+                s->calls.push_back(s->ar.calls[idx]);
+                s->call_level.push_back((uint32_t)li);
+            }
     }
     std::set<uint32_t> in_slots, out_slots;
     for (const HoloPort& p : s->ar.inputs) in_slots.insert(p.slot);
     for (const HoloPort& p : s->ar.outputs) out_slots.insert(p.slot);
-    s->fused = fuse_matmul_epilogue(s->calls, out_slots);
-    if (!s->addressed) s->rope_quant = fuse_rope_quantize(s->calls);
+    // a paged weight's length comes from the provider (session.rs:587-600)
+    for (HoloConstant& k : s->ar.constants) {
+        if (k.bytes || !k.by_reference) continue;
+        const int64_t sz = provider && provider->size ? provider->size(provider->user, k.fingerprint) : -1;
+        if (sz < 0) {
+            delete s;
+            return holo_fail(HOLO_ERR_INIT, "backend init failed: the weight provider does not have a weight the archive references");
+        }
+        k.len = (uint64_t)sz;
+    }
+    s->fused = fuse_matmul_epilogue(s->calls, s->call_level, out_slots);
+    if (!s->addressed) s->rope_quant = fuse_rope_quantize(s->calls, s->call_level);
     {
         std::set<uint32_t> const_slots, written_slots;
         for (const HoloConstant& k : s->ar.constants) const_slots.insert(k.slot);
@@ -942,9 +723,20 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
             ++s->moved_in_place;
         }
     }
+    // A paged session keeps load-time buffers only for what the pool cannot supply: resident constants
+    // and the input ports (values written there by the caller); everything else lives in the pool.
+    std::vector<uint8_t> lazy_slot(n_slots, 0), no_static(n_slots, 0);
+    if (s->ad.paged) {
+        std::fill(no_static.begin(), no_static.end(), 1);
+        for (const HoloPort& p : s->ar.inputs) no_static[p.slot] = 0;
+        for (const HoloConstant& k : s->ar.constants) {
+            if (k.by_reference && !out_slots.count(k.slot)) lazy_slot[k.slot] = 1;
+            else no_static[k.slot] = 0;
+        }
+    }
     rc = holo_b200_workspace_create(ctx, n_slots, &s->ws);
     for (uint32_t i = 0; rc == HOLO_OK && i < n_slots; ++i) {
-        if (alias[i] >= 0) continue;
+        if (alias[i] >= 0 || no_static[i]) continue;
         uint64_t bytes = std::max<uint64_t>(need[i], 64);
         bytes = (bytes + 63) & ~63ull;
         rc = holo_b200_workspace_alloc(s->ws, i, bytes);
@@ -959,15 +751,23 @@ extern "C" int32_t holo_b200_session_load(holo_b200_ctx* ctx, const uint8_t* arc
     }
     for (size_t i = 0; rc == HOLO_OK && i < s->ar.constants.size(); ++i) {
         const HoloConstant& k = s->ar.constants[i];
+        if (lazy_slot[k.slot]) continue;   // paged in on first use
+        const uint8_t* body = k.bytes;
+        if (!body && provider && provider->get_range) body = (const uint8_t*)provider->get_range(provider->user, k.fingerprint, 0, k.len);
+        if (!body && k.len) {
+            rc = holo_fail(HOLO_ERR_INIT, "backend init failed: the weight provider could not serve a resident constant");
+            break;
+        }
         HoloBufferRef ref = {k.slot, 0, 0};
-        rc = holo_b200_workspace_upload(s->ws, ref, k.bytes, k.len);
+        rc = holo_b200_workspace_upload(s->ws, ref, body, k.len);
     }
     if (rc == HOLO_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = holo_fail(HOLO_ERR_INIT, "backend init failed: constant upload");
     if (rc == HOLO_OK) rc = build_merged_weights(s);
     if (rc == HOLO_OK && !s->addressed) rc = plan_micro_batches(s);
     if (rc == HOLO_OK && s->addressed) {
-        s->slot_need.assign(need.begin(), need.end());
-        rc = prepare_addressed(s);
+        s->ad.pool.reset();
+        rc = holo_addressed_prepare(s, need);
+        if (rc == HOLO_OK && s->ad.paged) s->ad.pool->set_lazy_budget(budget);
     }
     if (rc != HOLO_OK) {
         if (s->ws) holo_b200_workspace_destroy(s->ws);
@@ -987,13 +787,7 @@ extern "C" void holo_b200_session_destroy(holo_b200_session* s) {
         if (g.b_concat) cudaFree(g.b_concat);
     for (MicroBatch& b : s->batches)
         if (b.dev_ops) cudaFree(b.dev_ops);
-    if (s->addressed) {
-        // hand the load-time buffers back to the workspace before it frees them, then the pool's own
-        for (size_t i = 0; i < s->static_binding.size() && i < s->ws->slots.size(); ++i) s->ws->slots[i] = s->static_binding[i];
-        for (auto& kv : s->pool) cudaFree(kv.second.ptr);
-        for (auto& e : s->free_list) cudaFree(e.ptr);
-        for (auto& e : s->transients) cudaFree(e.ptr);
-    }
+    if (s->addressed) holo_addressed_destroy(s);   // hands the load-time buffers back to the workspace, frees the pool's own
     if (s->ws) holo_b200_workspace_destroy(s->ws);
     delete s;
 }
@@ -1047,7 +841,8 @@ extern "C" int32_t holo_b200_session_call(holo_b200_session* s, uint32_t index, 
 extern "C" int32_t holo_b200_session_execute(holo_b200_session* s) {
     if (!s) return holo_fail(HOLO_ERR_INIT, "null session");
     if (s->addressed) {   // the plain walk of an addressed session runs on the load-time buffers
-        for (size_t i = 0; i < s->static_binding.size(); ++i) bind_slot_static(s, (uint32_t)i);
+        if (s->ad.paged) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: a paged session executes through execute_addressed");
+        holo_addressed_bind_static(s);
     }
     HOLO_CUDA(cudaSetDevice(s->ctx->device));
     if (s->graph) {

@@ -22,6 +22,19 @@ namespace {
 typedef struct { char internal[128]; } NcclUniqueId;
 typedef int (*GetUniqueIdFn)(NcclUniqueId*);
 typedef int (*CommInitRankFn)(void**, int, NcclUniqueId, int);
+// ncclConfig_t as NCCL 2.17 laid it out; later versions only append fields and read `size` / `version` to know
+// how much the caller filled in
+struct NcclConfig {
+    size_t size;
+    unsigned int magic, version;
+    int blocking, cga_cluster_size, min_ctas, max_ctas;
+    const char* net_name;
+    int split_share;
+};
+typedef int (*CommInitRankConfigFn)(void**, int, NcclUniqueId, int, NcclConfig*);
+typedef int (*CommGetAsyncErrorFn)(void*, int*);
+typedef int (*CommAbortFn)(void*);
+constexpr int NCCL_IN_PROGRESS = 7;
 typedef int (*AllReduceFn)(const void*, void*, size_t, int, int, void*, cudaStream_t);
 typedef int (*AllGatherFn)(const void*, void*, size_t, int, void*, cudaStream_t);
 typedef int (*CommDestroyFn)(void*);
@@ -35,6 +48,9 @@ struct Nccl {
     AllGatherFn all_gather = nullptr;
     CommDestroyFn comm_destroy = nullptr;
     GetErrorStringFn get_error_string = nullptr;
+    CommInitRankConfigFn comm_init_rank_config = nullptr;
+    CommGetAsyncErrorFn comm_get_async_error = nullptr;
+    CommAbortFn comm_abort = nullptr;
 };
 
 Nccl* nccl() {
@@ -51,6 +67,9 @@ Nccl* nccl() {
             n.all_gather = (AllGatherFn)dlsym(n.lib, "ncclAllGather");
             n.comm_destroy = (CommDestroyFn)dlsym(n.lib, "ncclCommDestroy");
             n.get_error_string = (GetErrorStringFn)dlsym(n.lib, "ncclGetErrorString");
+            n.comm_init_rank_config = (CommInitRankConfigFn)dlsym(n.lib, "ncclCommInitRankConfig");
+            n.comm_get_async_error = (CommGetAsyncErrorFn)dlsym(n.lib, "ncclCommGetAsyncError");
+            n.comm_abort = (CommAbortFn)dlsym(n.lib, "ncclCommAbort");
         }
     }
     if (!n.lib || !n.get_unique_id || !n.comm_init_rank || !n.all_reduce || !n.comm_destroy) return nullptr;
@@ -82,6 +101,7 @@ struct P2PParams {
     uint32_t* status;
     uint32_t units_per_slice;  // n / 4 / world
     uint32_t one_shot;         // two ranks: push the whole partial, reduce everything locally (one NVLink hop instead of two)
+    uint32_t wait_limit;       // polls of one unit before a thread gives up
     int rank, world, dtype;
 };
 
@@ -112,7 +132,7 @@ __device__ __forceinline__ void all_reduce_p2p_body(const P2PParams& p, uint32_t
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             for (uint32_t r = 0; r < W && ok; ++r) {
                 uint2 v = own;
-                if (r != me) ok = ll_load(mine, (uint64_t)r * N + unit, epoch, &v);
+                if (r != me) ok = ll_load(mine, (uint64_t)r * N + unit, epoch, &v, p.wait_limit);
                 acc[0] = __fadd_rn(acc[0], holo::widen16((uint16_t)(v.x & 0xffffu), p.dtype));
                 acc[1] = __fadd_rn(acc[1], holo::widen16((uint16_t)(v.x >> 16), p.dtype));
                 acc[2] = __fadd_rn(acc[2], holo::widen16((uint16_t)(v.y & 0xffffu), p.dtype));
@@ -145,7 +165,7 @@ __device__ __forceinline__ void all_reduce_p2p_body(const P2PParams& p, uint32_t
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         for (uint32_t r = 0; r < W && ok; ++r) {
             uint2 v = own;
-            if (r != me) ok = ll_load(box, (uint64_t)r * U + u, epoch, &v);
+            if (r != me) ok = ll_load(box, (uint64_t)r * U + u, epoch, &v, p.wait_limit);
             acc[0] = __fadd_rn(acc[0], holo::widen16((uint16_t)(v.x & 0xffffu), p.dtype));
             acc[1] = __fadd_rn(acc[1], holo::widen16((uint16_t)(v.x >> 16), p.dtype));
             acc[2] = __fadd_rn(acc[2], holo::widen16((uint16_t)(v.y & 0xffffu), p.dtype));
@@ -169,7 +189,7 @@ __device__ __forceinline__ void all_reduce_p2p_body(const P2PParams& p, uint32_t
     for (uint32_t idx = t; idx < (W - 1) * U && ok; idx += T) {
         const uint32_t r = (me + 1 + idx / U) % W, u = idx % U;
         uint2 v;
-        ok = ll_load(box + P2P_REGION_BYTES, (uint64_t)r * U + u, epoch, &v);
+        ok = ll_load(box + P2P_REGION_BYTES, (uint64_t)r * U + u, epoch, &v, p.wait_limit);
         if (ok) out2[(uint64_t)r * U + u] = v;
     }
     }
@@ -196,8 +216,10 @@ __global__ void __launch_bounds__(P2P_THREADS) all_reduce_p2p_kernel(const P2PPa
 // the ranks' CTAs wait on one another, hence the cooperative launch (all CTAs co-resident).
 struct P2PEmulation {
     P2PParams rank[8];
+    int withheld;   // this emulated rank never sends (its CTAs return at once): what a dead peer looks like to the others
 };
 __global__ void __launch_bounds__(P2P_THREADS) all_reduce_p2p_emulation_kernel(const P2PEmulation e) {
+    if ((int)blockIdx.y == e.withheld) return;
     all_reduce_p2p_body(e.rank[blockIdx.y], blockIdx.x, gridDim.x);
 }
 
@@ -218,7 +240,35 @@ extern "C" int32_t holo_b200_nccl_unique_id(uint8_t out128[128]) {
     return HOLO_OK;
 }
 
+namespace {
+// Wait until a non-blocking communicator has finished what it was asked to do. Returns the NCCL result
+// (0 = done), or -1 when `timeout_ms` ran out first (the caller aborts the communicator).
+int nccl_wait(Nccl* n, void* comm, uint32_t timeout_ms) {
+    if (!n->comm_get_async_error) return 0;
+    struct timespec t0;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (;;) {
+        int state = 0;
+        const int rc = n->comm_get_async_error(comm, &state);
+        if (rc != 0) return rc;
+        if (state != NCCL_IN_PROGRESS) return state;
+        struct timespec t1;
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        const uint64_t ms = (uint64_t)(t1.tv_sec - t0.tv_sec) * 1000u + (uint64_t)((t1.tv_nsec - t0.tv_nsec) / 1000000);
+        if (timeout_ms && ms >= timeout_ms) return -1;
+        struct timespec nap = {0, 2 * 1000 * 1000};
+        nanosleep(&nap, nullptr);
+    }
+}
+}  // namespace
+
 extern "C" int32_t holo_b200_ctx_init_tp(holo_b200_ctx* ctx, const uint8_t id128[128], int32_t rank, int32_t world) {
+    uint32_t timeout_ms = 120000;
+    if (const char* e = getenv("HOLO_TP_INIT_TIMEOUT_MS")) timeout_ms = (uint32_t)atoll(e);
+    return holo_b200_ctx_init_tp_timeout(ctx, id128, rank, world, timeout_ms);
+}
+
+extern "C" int32_t holo_b200_ctx_init_tp_timeout(holo_b200_ctx* ctx, const uint8_t id128[128], int32_t rank, int32_t world, uint32_t timeout_ms) {
     if (!ctx) return holo_fail(HOLO_ERR_INIT, "null context");
     if (world < 1 || rank < 0 || rank >= world) return holo_fail(HOLO_ERR_INIT, "backend init failed: rank %d of %d", rank, world);
     if (world == 1) {
@@ -232,34 +282,75 @@ extern "C" int32_t holo_b200_ctx_init_tp(holo_b200_ctx* ctx, const uint8_t id128
     NcclUniqueId id;
     memcpy(id.internal, id128, 128);
     void* comm = nullptr;
-    int rc = n->comm_init_rank(&comm, world, id, rank);
-    if (rc != 0) return nccl_fail(n, rc, "ncclCommInitRank");
+    int rc;
+    const bool nonblocking = n->comm_init_rank_config && n->comm_get_async_error && n->comm_abort && !getenv("HOLO_TP_BLOCKING_INIT");
+    if (nonblocking) {
+        // Non-blocking set-up with a host-side time limit: the group forms over the bootstrap network before
+        // anything is enqueued on a GPU, so a rank that never joins (or joins with another world size) is a
+        // host timeout here, followed by an abort of the half-made communicator, never a hung collective.
+        NcclConfig cfg;
+        memset(&cfg, 0, sizeof cfg);
+        cfg.size = sizeof cfg;
+        cfg.magic = 0xcafebeef;
+        cfg.version = 2 * 10000 + 17 * 100;   // NCCL_VERSION(2, 17, 0): the layout filled in here
+        cfg.blocking = 0;
+        cfg.cga_cluster_size = cfg.min_ctas = cfg.max_ctas = cfg.split_share = (int)0x80000000;   // NCCL_CONFIG_UNDEF_INT
+        cfg.net_name = nullptr;
+        rc = n->comm_init_rank_config(&comm, world, id, rank, &cfg);
+        if (rc != 0 && rc != NCCL_IN_PROGRESS) return nccl_fail(n, rc, "ncclCommInitRankConfig");
+        rc = nccl_wait(n, comm, timeout_ms);
+        if (rc != 0) {
+            if (comm) n->comm_abort(comm);
+            if (rc == -1)
+                return holo_fail(HOLO_ERR_INIT, "backend init failed: the tensor-parallel group of %d ranks did not form within %u ms (rank %d waited; "
+                                 "a rank is missing or was given another world size)", world, timeout_ms, rank);
+            return nccl_fail(n, rc, "ncclCommInitRankConfig (asynchronous)");
+        }
+        ctx->nccl_nonblocking = true;
+    } else {
+        rc = n->comm_init_rank(&comm, world, id, rank);
+        if (rc != 0) return nccl_fail(n, rc, "ncclCommInitRank");
+    }
     ctx->nccl_comm = comm;
     ctx->tp_rank = rank;
     ctx->tp_world = world;
-    // Peer-memory mailboxes. Any failure here (IPC not permitted, no peer access, more than 8
-    // ranks) leaves the group on NCCL alone; the ranks agree on the outcome through a min-reduce.
+    // Peer-memory mailboxes. Every rank of the group takes part in the two collectives below whatever its own
+    // outcome was (transport switched off by HOLO_TP_P2P=0, IPC not permitted, an allocation that failed): a rank
+    // that skipped one would leave its peers waiting inside it. The ranks agree on the transport through a
+    // min-reduce of "my set-up worked", so one rank's "no" switches all of them to NCCL.
     const char* env = getenv("HOLO_TP_P2P");
-    bool want = world <= 8 && n->all_gather && !(env && atoi(env) == 0);
+    const bool want = world <= 8 && n->all_gather && !(env && atoi(env) == 0);
     uint8_t* mine = nullptr;
     uint8_t* dev_handles = nullptr;
     cudaIpcMemHandle_t handles[8];
+    cudaIpcMemHandle_t h;
+    memset(&h, 0, sizeof h);
+    // the exchange buffer is needed by every rank: without it this rank cannot take part, and init fails here,
+    // before any collective (the peers' set-up then runs into its own time limit instead of a hung kernel)
+    if (cudaMalloc(&dev_handles, 8 * sizeof(cudaIpcMemHandle_t)) != cudaSuccess) {
+        cudaGetLastError();
+        return holo_fail(HOLO_ERR_INIT, "backend init failed: tensor-parallel set-up could not allocate device memory");
+    }
     bool ok = want;
     // cleared on the context's stream and waited for before any peer can learn the address
     if (ok) ok = cudaMalloc(&mine, P2P_MAILBOX_BYTES) == cudaSuccess && cudaMemsetAsync(mine, 0, P2P_MAILBOX_BYTES, ctx->stream) == cudaSuccess &&
                  cudaStreamSynchronize(ctx->stream) == cudaSuccess;
-    if (ok) ok = cudaMalloc(&dev_handles, 8 * sizeof(cudaIpcMemHandle_t)) == cudaSuccess;
-    cudaIpcMemHandle_t h;
-    memset(&h, 0, sizeof h);
     if (ok) ok = cudaIpcGetMemHandle(&h, mine) == cudaSuccess;
-    if (dev_handles) {
-        // every rank takes part in the gather, whether or not its own set-up worked
+    bool collectives_ok = true;
+    if (n->all_gather) {
         cudaMemcpy(dev_handles + (size_t)rank * sizeof h, &h, sizeof h, cudaMemcpyHostToDevice);
         rc = n->all_gather(dev_handles + (size_t)rank * sizeof h, dev_handles, sizeof h, /*ncclInt8*/ 0, comm, ctx->stream);
-        if (rc != 0 || cudaStreamSynchronize(ctx->stream) != cudaSuccess) ok = false;
+        if (ctx->nccl_nonblocking && (rc == 0 || rc == NCCL_IN_PROGRESS)) rc = nccl_wait(n, comm, timeout_ms);
+        if (rc != 0 || cudaStreamSynchronize(ctx->stream) != cudaSuccess) collectives_ok = false;
         if (cudaMemcpy(handles, dev_handles, world * sizeof h, cudaMemcpyDeviceToHost) != cudaSuccess) ok = false;
     } else {
         ok = false;
+    }
+    if (!collectives_ok) {
+        cudaFree(dev_handles);
+        if (mine) cudaFree(mine);
+        cudaGetLastError();
+        return holo_fail(HOLO_ERR_INIT, "backend init failed: the handle exchange of the tensor-parallel group did not complete (NCCL result %d)", rc);
     }
     if (ok) {
         for (int r = 0; r < world && ok; ++r) {
@@ -275,14 +366,15 @@ extern "C" int32_t holo_b200_ctx_init_tp(holo_b200_ctx* ctx, const uint8_t id128
     if (ok) ok = cudaMalloc(&ctx->tp_epochs, 256) == cudaSuccess && cudaMemsetAsync(ctx->tp_epochs, 0, 256, ctx->stream) == cudaSuccess &&
                  cudaStreamSynchronize(ctx->stream) == cudaSuccess;
     cudaGetLastError();  // a failed attempt above must not poison later launches
-    // agreement: min over ranks of "my set-up worked" (want == false on one rank switches all off;
-    // a rank without a gather buffer cannot take part in a collective, so it has to fail init)
-    if (!dev_handles && want) return holo_fail(HOLO_ERR_INIT, "backend init failed: tensor-parallel set-up could not allocate device memory");
-    if (dev_handles) {
+    {
         float flag = ok ? 1.0f : 0.0f;
         cudaMemcpy(dev_handles, &flag, 4, cudaMemcpyHostToDevice);
         rc = n->all_reduce(dev_handles, dev_handles, 1, /*ncclFloat32*/ 7, /*ncclMin*/ 3, comm, ctx->stream);
-        if (rc != 0 || cudaStreamSynchronize(ctx->stream) != cudaSuccess) return nccl_fail(n, rc, "ncclAllReduce (transport agreement)");
+        if (ctx->nccl_nonblocking && (rc == 0 || rc == NCCL_IN_PROGRESS)) rc = nccl_wait(n, comm, timeout_ms);
+        if (rc != 0 || cudaStreamSynchronize(ctx->stream) != cudaSuccess) {
+            cudaFree(dev_handles);
+            return nccl_fail(n, rc, "ncclAllReduce (transport agreement)");
+        }
         cudaMemcpy(&flag, dev_handles, 4, cudaMemcpyDeviceToHost);
         ok = flag > 0.5f;
         cudaFree(dev_handles);
@@ -328,8 +420,12 @@ void holo_tp_destroy(holo_b200_ctx* ctx) {
 int32_t holo_all_reduce_add(holo_b200_ctx* ctx, const void* partial, const void* residual, void* out, uint64_t count, uint8_t dtype) {
     if (count == 0) return HOLO_OK;
     const bool sixteen = dtype == HOLO_DTYPE_BF16 || dtype == HOLO_DTYPE_F16;
-    const bool aligned = (((uintptr_t)partial | (uintptr_t)residual | (uintptr_t)out) & 7u) == 0;
-    if (ctx->tp_world > 1 && ctx->tp_p2p && sixteen && aligned && count <= P2P_MAX_ELEMS && (count % (4ull * ctx->tp_world)) == 0) {
+    // Which transport carries a message is decided by values every rank shares (dtype, count), never by a
+    // local pointer: two ranks taking different routes would wait for each other for ever. A buffer that the
+    // peer-memory kernel cannot take (not 8-byte aligned) is therefore refused, loudly, instead of rerouted.
+    if (ctx->tp_world > 1 && ctx->tp_p2p && sixteen && count <= P2P_MAX_ELEMS && (count % (4ull * ctx->tp_world)) == 0) {
+        if ((((uintptr_t)partial | (uintptr_t)residual | (uintptr_t)out) & 7u) != 0)
+            return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: all_reduce operands must be 8-byte aligned on the peer-memory transport");
         P2PParams p;
         p.partial = (const uint16_t*)partial;
         p.residual = (const uint16_t*)residual;
@@ -339,6 +435,7 @@ int32_t holo_all_reduce_add(holo_b200_ctx* ctx, const void* partial, const void*
         p.status = ctx->dev_status;
         p.units_per_slice = (uint32_t)(count / 4 / ctx->tp_world);
         p.one_shot = (ctx->tp_world == 2 && 4ull * ctx->tp_world * count <= P2P_ONESHOT_BYTES && !getenv("HOLO_TP_TWO_SHOT")) ? 1u : 0u;
+        p.wait_limit = P2P_WAIT_LIMIT;
         p.rank = ctx->tp_rank;
         p.world = ctx->tp_world;
         p.dtype = dtype;
@@ -359,6 +456,7 @@ int32_t holo_all_reduce_add(holo_b200_ctx* ctx, const void* partial, const void*
         // ncclDataType_t: ncclFloat16 = 6, ncclFloat32 = 7, ncclBfloat16 = 9; ncclSum = 0
         int dt = dtype == HOLO_DTYPE_F32 ? 7 : dtype == HOLO_DTYPE_F16 ? 6 : 9;
         int rc = n->all_reduce(out, out, (size_t)count, dt, 0, ctx->nccl_comm, ctx->stream);
+        if (ctx->nccl_nonblocking && (rc == 0 || rc == NCCL_IN_PROGRESS)) rc = nccl_wait(n, ctx->nccl_comm, 60000);   // enqueue only; the kernel runs on the stream
         if (rc != 0) return nccl_fail(n, rc, "ncclAllReduce");
     }
     if (residual) return holo_launch_binary(ctx, 0, out, residual, out, count, dtype);
@@ -375,7 +473,13 @@ int32_t holo_all_reduce(holo_b200_ctx* ctx, void* buf, uint64_t count, uint8_t d
 // may alias partials). Mailboxes are allocated for the call and freed again. For tests.
 extern "C" int32_t holo_b200_tp_emulate_all_reduce(holo_b200_ctx* ctx, int32_t world, const void* const* partials, const void* const* residuals,
                                                    void* const* outs, uint64_t count, uint8_t dtype, int32_t repeats) {
-    if (!ctx || world < 2 || world > 8 || !partials || !outs) return holo_fail(HOLO_ERR_INIT, "backend init failed: bad argument");
+    return holo_b200_tp_emulate_all_reduce_ex(ctx, world, partials, residuals, outs, count, dtype, repeats, -1, 0);
+}
+
+extern "C" int32_t holo_b200_tp_emulate_all_reduce_ex(holo_b200_ctx* ctx, int32_t world, const void* const* partials, const void* const* residuals,
+                                                      void* const* outs, uint64_t count, uint8_t dtype, int32_t repeats, int32_t withheld_rank,
+                                                      uint32_t poll_limit) {
+    if (!ctx || world < 2 || world > 8 || !partials || !outs || withheld_rank >= world) return holo_fail(HOLO_ERR_INIT, "backend init failed: bad argument");
     if ((dtype != HOLO_DTYPE_BF16 && dtype != HOLO_DTYPE_F16) || count == 0 || count > P2P_MAX_ELEMS || (count % (4ull * world)) != 0)
         return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: the peer-memory all-reduce takes 16-bit messages of at most %u elements, a multiple of 4 x world",
                          P2P_MAX_ELEMS);
@@ -398,6 +502,7 @@ extern "C" int32_t holo_b200_tp_emulate_all_reduce(holo_b200_ctx* ctx, int32_t w
         p.status = ctx->dev_status;
         p.units_per_slice = (uint32_t)(count / 4 / world);
         p.one_shot = (world == 2 && 4ull * world * count <= P2P_ONESHOT_BYTES && !getenv("HOLO_TP_TWO_SHOT")) ? 1u : 0u;
+        p.wait_limit = poll_limit ? poll_limit : P2P_WAIT_LIMIT;
         p.rank = r;
         p.world = world;
         p.dtype = dtype;
@@ -406,6 +511,7 @@ extern "C" int32_t holo_b200_tp_emulate_all_reduce(holo_b200_ctx* ctx, int32_t w
     uint32_t ctas = (uint32_t)((widest + P2P_THREADS - 1) / P2P_THREADS);
     if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
     if (ctas < 1) ctas = 1;
+    e.withheld = withheld_rank;
     void* args[] = {&e};
     cudaError_t err = cudaSuccess;
     for (int i = 0; i < repeats && err == cudaSuccess; ++i) {
@@ -416,5 +522,6 @@ extern "C" int32_t holo_b200_tp_emulate_all_reduce(holo_b200_ctx* ctx, int32_t w
     cudaFree(boxes);
     cudaFree(states);
     if (err != cudaSuccess) return holo_cuda_fail(err, "all_reduce_p2p_emulation_kernel");
-    return HOLO_OK;
+    // a poll that ran out left its mark in the status word: report it here, as every synchronising call does
+    return holo_b200_ctx_synchronize(ctx);
 }

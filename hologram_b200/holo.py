@@ -43,11 +43,17 @@ def encode_call(call):
         return out + _matmul(u.matmul_activation.mm) + struct.pack("<B", u.matmul_activation.act)
     if k == kc.K_MATMUL_ADD:
         return out + _matmul(u.matmul_add.mm) + _buf(u.matmul_add.residual)
-    if k in (kc.K_MATMUL_DEQUANT, kc.K_MATMUL_DEQUANT_CODEBOOK):
+    if k == kc.K_MATMUL_ADD_ACTIVATION:
+        c = u.matmul_add_activation
+        return out + _matmul(c.mm) + _buf(c.residual) + struct.pack("<B", c.act)
+    if k in (kc.K_MATMUL_DEQUANT_PLAIN, kc.K_MATMUL_DEQUANT, kc.K_MATMUL_DEQUANT_CODEBOOK):
         c = u.matmul_dequant
-        return out + b"".join(_buf(b) for b in (c.a, c.bq, c.scales, c.zero_points, c.output)) + struct.pack(
-            "<IIIIIBBIIBBB", c.m, c.k, c.n, c.channels, c.inner, c.quant_dtype, c.dtype, c.scale_bits, c.zero_point & 0xFFFFFFFF,
-            c.bq_omajor, c.act_quant, c.act) + _buf(c.residual) + (_buf(c.codebook) if k == kc.K_MATMUL_DEQUANT_CODEBOOK else b"")
+        base = out + b"".join(_buf(b) for b in (c.a, c.bq, c.scales, c.zero_points, c.output)) + struct.pack(
+            "<IIIIIBBII", c.m, c.k, c.n, c.channels, c.inner, c.quant_dtype, c.dtype, c.scale_bits, c.zero_point & 0xFFFFFFFF)
+        if k == kc.K_MATMUL_DEQUANT_PLAIN:
+            return base
+        return base + struct.pack("<BBB", c.bq_omajor, c.act_quant, c.act) + _buf(c.residual) + (
+            _buf(c.codebook) if k == kc.K_MATMUL_DEQUANT_CODEBOOK else b"")
     if k in (kc.K_LAYER_NORM, kc.K_RMS_NORM, kc.K_ADD_RMS_NORM):
         c = u.norm
         return out + _buf(c.x) + _buf(c.gamma) + _buf(c.beta) + _buf(c.residual) + _buf(c.output) + struct.pack(
@@ -161,7 +167,9 @@ class HoloWriter:
             by_reference = len(body) > 256
         (self.weight_constants if by_reference else self.inline_constants).append((slot, dtype, body))
 
-    def finish(self):
+    def finish(self, weightless=False):
+        """The archive image. `weightless`: constants stored by reference keep their fingerprints but the Weights
+        section carries no bodies (they come from a weight provider at load, crates/hologram-exec/src/session.rs:417)."""
         weights, order, const = {}, [], struct.pack("<I", len(self.inline_constants) + len(self.weight_constants))
         for slot, dtype, body in self.inline_constants:
             const += struct.pack("<BIBI", 0, slot, dtype, len(body)) + bytes(body)
@@ -171,6 +179,9 @@ class HoloWriter:
                 weights[fp] = body
                 order.append(fp)
             const += struct.pack("<BIB", 1, slot, dtype) + fp
+        self.weight_bodies = dict(weights)          # fingerprint -> body, what a weight provider serves
+        if weightless:
+            order = []
         wsec = [struct.pack("<I", len(order))]
         for fp in order:
             wsec += [fp, struct.pack("<Q", len(weights[fp])), weights[fp]]

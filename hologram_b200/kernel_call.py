@@ -32,6 +32,8 @@ K_REDUCE_SUM, K_REDUCE_MEAN, K_REDUCE_PROD, K_REDUCE_MIN, K_REDUCE_MAX = 55, 56,
 K_ADD_RMS_NORM, K_TRANSPOSE, K_CONCAT, K_SLICE, K_SOFTMAX = 54, 61, 62, 63, 64
 K_DECODE_ATTENTION = 119
 K_MATMUL_DEQUANT = 116
+K_MATMUL_DEQUANT_PLAIN = 111      # the all-default wire form ([k,n] weight, f32 activations)
+K_MATMUL_ADD_ACTIVATION = 108
 K_MATMUL_DEQUANT_CODEBOOK = 117   # the same call with a codebook operand bound (E8 codebook weights)
 DTYPE_E8CB = 11
 K_DEQUANTIZE, K_MATMUL_ACTIVATION, K_MATMUL_ADD = 105, 106, 107
@@ -81,8 +83,14 @@ class MatMulAddCall(C.Structure):
     _fields_ = [("mm", MatMulCall), ("residual", BufferRef)]
 
 
+class MatMulAddActivationCall(C.Structure):
+    """kernel_call.rs:913-929: out = act(A . B + residual)."""
+    _fields_ = [("mm", MatMulCall), ("residual", BufferRef), ("act", C.c_uint8)]
+
+
 class MatMulDequantCall(C.Structure):
-    """kernel_call.rs:152-213 (wire form 116). Served: output-major W8A8 int8 (bq_omajor=1, act_quant=1)."""
+    """kernel_call.rs:152-213 (wire forms 111 / 116 / 117). Served: output-major W8A8 (bq_omajor=1, act_quant=1) over
+    i8 / i4 / e8cb weights, and the [k,n] form with f32 activations (bq_omajor=0, act_quant=0) over i8 / u8 / i4."""
     _fields_ = [("a", BufferRef), ("bq", BufferRef), ("scales", BufferRef), ("zero_points", BufferRef), ("output", BufferRef),
                 ("m", C.c_uint32), ("k", C.c_uint32), ("n", C.c_uint32), ("channels", C.c_uint32), ("inner", C.c_uint32),
                 ("quant_dtype", C.c_uint8), ("dtype", C.c_uint8), ("scale_bits", C.c_uint32), ("zero_point", C.c_int32),
@@ -257,7 +265,7 @@ class AllReduceCall(C.Structure):
 
 class _Payload(C.Union):
     _fields_ = [("unary", UnaryCall), ("binary", BinaryCall), ("matmul", MatMulCall),
-                ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("matmul_dequant", MatMulDequantCall), ("norm", NormCall),
+                ("matmul_activation", MatMulActivationCall), ("matmul_add", MatMulAddCall), ("matmul_add_activation", MatMulAddActivationCall), ("matmul_dequant", MatMulDequantCall), ("norm", NormCall),
                 ("rope", RoPECall), ("gather", GatherCall), ("cast", CastCall), ("layout", LayoutCall),
                 ("transpose", TransposeCall), ("softmax", SoftmaxCall), ("expand", ExpandCall), ("reduce", ReduceCall), ("attention", AttentionCall), ("dequant_activation", DequantActivationCall), ("where", WhereCall), ("broadcast_binary", BroadcastBinaryCall), ("dequantize", DequantizeCall), ("kv_cache_write", KvCacheWriteCall),
                 ("decode_attention", DecodeAttentionCall),
@@ -309,7 +317,14 @@ class KernelCall(C.Structure):
     @classmethod
     def MatMulAdd(cls, c): return cls.of(K_MATMUL_ADD, c)
     @classmethod
-    def MatMulDequant(cls, c): return cls.of(K_MATMUL_DEQUANT_CODEBOOK if c.codebook.slot != NO_SLOT else K_MATMUL_DEQUANT, c)
+    def MatMulAddActivation(cls, c): return cls.of(K_MATMUL_ADD_ACTIVATION, c)
+    @classmethod
+    def MatMulDequant(cls, c):
+        # the wire form follows the call (kernel_codec.rs:525-544): a codebook takes 117, any extended field 116, else 111
+        if c.codebook.slot != NO_SLOT:
+            return cls.of(K_MATMUL_DEQUANT_CODEBOOK, c)
+        extended = c.bq_omajor or c.act_quant or c.act or c.residual.slot != NO_SLOT
+        return cls.of(K_MATMUL_DEQUANT if extended else K_MATMUL_DEQUANT_PLAIN, c)
     @classmethod
     def RmsNorm(cls, c): return cls.of(K_RMS_NORM, c)
     @classmethod
@@ -372,7 +387,7 @@ class KernelCall(C.Structure):
 
 KernelCall._FIELD = {
     UnaryCall: "unary", BinaryCall: "binary", MatMulCall: "matmul", MatMulActivationCall: "matmul_activation",
-    MatMulAddCall: "matmul_add", MatMulDequantCall: "matmul_dequant", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
+    MatMulAddCall: "matmul_add", MatMulAddActivationCall: "matmul_add_activation", MatMulDequantCall: "matmul_dequant", NormCall: "norm", RoPECall: "rope", GatherCall: "gather", CastCall: "cast",
     LayoutCall: "layout", TransposeCall: "transpose", SoftmaxCall: "softmax", ExpandCall: "expand", ReduceCall: "reduce", AttentionCall: "attention", DequantActivationCall: "dequant_activation", WhereCall: "where", BroadcastBinaryCall: "broadcast_binary", DequantizeCall: "dequantize", KvCacheWriteCall: "kv_cache_write",
     DecodeAttentionCall: "decode_attention", DecodeAttentionValidCall: "decode_attention_valid", QuantizeRowsI8Call: "quantize_rows_i8",
     DecodeAttentionValidQ8Call: "decode_attention_valid_q8", AllReduceCall: "all_reduce", RopeQuantizeCall: "rope_quantize",

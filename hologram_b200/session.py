@@ -5,7 +5,7 @@ import ctypes as C
 import numpy as np
 
 from . import kernel_call as kc
-from .backend import DeviceWorkspace, _check, _host_ptr, lib
+from .backend import DeviceWorkspace, WeightStore, _check, _host_ptr, lib
 
 vp, u32, u64, i32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32
 for _name, _res, _args in [
@@ -23,6 +23,14 @@ for _name, _res, _args in [
     ("holo_b200_label_bytes", i32, [vp, u64, vp]),
     ("holo_b200_label_derive", i32, [C.c_uint16, vp, u32, vp, u32, vp]),
     ("holo_b200_op_signature", i32, [C.POINTER(kc.KernelCall), C.POINTER(C.c_uint16), vp, C.POINTER(u32)]),
+    ("holo_b200_label_derive_boundary", i32, [C.c_uint16, vp, u32, vp, u32, vp]),
+    ("holo_b200_session_intern_input", i32, [vp, vp, u64, vp]),
+    ("holo_b200_session_resolve", i32, [vp, vp, vp, u64, C.POINTER(u64), C.POINTER(i32)]),
+    ("holo_b200_session_retain_label", i32, [vp, vp, C.POINTER(i32)]),
+    ("holo_b200_session_release_label", i32, [vp, vp, C.POINTER(i32)]),
+    ("holo_b200_session_leased_count", u32, [vp]),
+    ("holo_b200_session_load_paged", i32, [vp, vp, u64, i32, vp, u64, C.POINTER(vp)]),
+    ("holo_b200_session_tier_report", i32, [vp, i32, vp]),
 ]:
     _fn = getattr(lib, _name)
     _fn.restype, _fn.argtypes = _res, _args
@@ -31,13 +39,25 @@ SESSION_SYMBOLS = ["holo_b200_session_load", "holo_b200_session_destroy", "holo_
                    "holo_b200_session_info", "holo_b200_session_nodes", "holo_b200_session_port", "holo_b200_session_call",
                    "holo_b200_session_execute", "holo_b200_session_capture", "holo_b200_archive_check",
                    "holo_b200_session_execute_addressed", "holo_b200_label_bytes", "holo_b200_label_derive",
-                   "holo_b200_op_signature"]
+                   "holo_b200_op_signature", "holo_b200_label_derive_boundary", "holo_b200_session_intern_input",
+                   "holo_b200_session_resolve", "holo_b200_session_retain_label", "holo_b200_session_release_label",
+                   "holo_b200_session_leased_count", "holo_b200_session_load_paged", "holo_b200_session_tier_report"]
 
 LABEL_BYTES = 71
 
 
 class AddressedStats(C.Structure):
-    _fields_ = [("dispatched", u32), ("skipped", u32), ("memo_hit", u32), ("pool_bytes", u64)]
+    _fields_ = [("dispatched", u32), ("skipped", u32), ("memo_hit", u32), ("pool_bytes", u64), ("moved", u32), ("paged_in", u32)]
+
+
+class TierReport(C.Structure):
+    """`TierReport` (crates/hologram-exec/src/coherence.rs:78-93)."""
+    _fields_ = [("cpu_l1_calls", u32), ("cpu_l2_calls", u32), ("cpu_main_calls", u32), ("device_calls", u32),
+                ("total_migration_slots", u32), ("levels_with_migrations", u32)]
+
+
+TIER_COMPILED, TIER_FORCE_ALL_CPU, TIER_FORCE_ALL_DEVICE = 0, 1, 2
+SESSION_LABEL_RESIDUAL = 4
 
 
 def label_bytes(data):
@@ -55,6 +75,16 @@ def label_derive(opcode, params, labels):
     out = np.empty(LABEL_BYTES, dtype=np.uint8)
     _check(lib.holo_b200_label_derive(opcode, _host_ptr(pr) if pr.size else None, pr.size, _host_ptr(lb) if lb.size else None,
                                       len(labels), _host_ptr(out)))
+    return out.tobytes()
+
+
+def label_derive_boundary(opcode, params, labels):
+    """`derive_label_boundary` (address.rs:197-221): the label a graph output is retained and reported under."""
+    pr = np.frombuffer(bytes(params), dtype=np.uint8)
+    lb = np.frombuffer(b"".join(labels), dtype=np.uint8)
+    out = np.empty(LABEL_BYTES, dtype=np.uint8)
+    _check(lib.holo_b200_label_derive_boundary(opcode, _host_ptr(pr) if pr.size else None, pr.size, _host_ptr(lb) if lb.size else None,
+                                               len(labels), _host_ptr(out)))
     return out.tobytes()
 
 
@@ -84,11 +114,18 @@ class Port:
 
 
 class InferenceSession:
-    def __init__(self, backend, archive_bytes, verify=True, addressed=False):
+    def __init__(self, backend, archive_bytes, verify=True, addressed=False, label_residual=False, weight_store=None, budget=0):
+        """`weight_store` (a WeightStore) makes this `load_paged` (session.rs:417): by-reference constants page in from it
+        within `budget` resident bytes (0 = never evict)."""
         h = vp()
         buf = np.frombuffer(archive_bytes, dtype=np.uint8)
-        flags = (1 if verify else 0) | (2 if addressed else 0)
-        _check(lib.holo_b200_session_load(backend._h, _host_ptr(buf), buf.size, flags, C.byref(h)))
+        flags = (1 if verify else 0) | (2 if addressed else 0) | (SESSION_LABEL_RESIDUAL if label_residual else 0)
+        if weight_store is not None:
+            self._store = weight_store      # the provider must outlive the session
+            addressed = True
+            _check(lib.holo_b200_session_load_paged(backend._h, _host_ptr(buf), buf.size, flags, C.byref(weight_store.struct), budget, C.byref(h)))
+        else:
+            _check(lib.holo_b200_session_load(backend._h, _host_ptr(buf), buf.size, flags, C.byref(h)))
         self.addressed = addressed
         self._h = h
         self.backend = backend
@@ -126,6 +163,44 @@ class InferenceSession:
                                                        len(self.outputs), C.byref(st)))
         raw = outs.tobytes()
         return [raw[i * LABEL_BYTES:(i + 1) * LABEL_BYTES] for i in range(len(self.outputs))], st
+
+    def intern_input(self, data):
+        """`intern_input` (session.rs:1018-1022): store host bytes in the pool under the label of their content."""
+        a = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        out = np.empty(LABEL_BYTES, dtype=np.uint8)
+        _check(lib.holo_b200_session_intern_input(self._h, _host_ptr(a) if a.size else None, a.size, _host_ptr(out)))
+        return out.tobytes()
+
+    def resolve(self, label, dtype=np.uint8):
+        """`resolve` (session.rs:1027-1029): the bytes of a resident label, or None."""
+        n, here = u64(), i32()
+        lb = C.c_char_p(bytes(label))
+        _check(lib.holo_b200_session_resolve(self._h, lb, None, 0, C.byref(n), C.byref(here)))
+        if not here.value:
+            return None
+        out = np.empty(n.value, dtype=np.uint8)
+        _check(lib.holo_b200_session_resolve(self._h, lb, _host_ptr(out) if out.size else None, out.size, C.byref(n), C.byref(here)))
+        return out.view(dtype)
+
+    def retain_label(self, label):
+        ok = i32()
+        _check(lib.holo_b200_session_retain_label(self._h, C.c_char_p(bytes(label)), C.byref(ok)))
+        return bool(ok.value)
+
+    def release_label(self, label):
+        ok = i32()
+        _check(lib.holo_b200_session_release_label(self._h, C.c_char_p(bytes(label)), C.byref(ok)))
+        return bool(ok.value)
+
+    @property
+    def leased_count(self):
+        return int(lib.holo_b200_session_leased_count(self._h))
+
+    def tier_report(self, policy=TIER_FORCE_ALL_DEVICE):
+        """`tier_report` (session.rs:797) under a routing policy; this backend executes under TIER_FORCE_ALL_DEVICE."""
+        rep = TierReport()
+        _check(lib.holo_b200_session_tier_report(self._h, policy, C.byref(rep)))
+        return rep
 
     def close(self):
         if getattr(self, "_h", None):

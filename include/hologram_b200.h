@@ -2,9 +2,9 @@
  * hologram_b200.h — C ABI of the B200 (sm_100a) backend for hologram's tensor engine.
  *
  * The library is a drop-in for ONE boundary of the reference: `Backend::dispatch(&KernelCall,
- * &mut Workspace)` (crates/hologram-compute/src/backend.rs:8-15). A Rust `impl Backend` (see
- * INTEGRATION.md) forwards each call through `holo_b200_dispatch`; everything above that
- * boundary (compiler, archive, session walk) stays the reference's.
+ * &mut Workspace)` (crates/hologram-compute/src/backend.rs:8-15). A Rust `impl Backend`
+ * forwards each call through `holo_b200_dispatch`; everything above that boundary (compiler,
+ * archive, session walk) stays the reference's.
  *
  * Conventions follow crates/hologram-ffi (src/lib.rs:48-92): every function returns an
  * int32_t status (0 = ok, negative = one `BackendError` variant), the text of the last
@@ -115,6 +115,8 @@ extern "C" {
 #define HOLO_K_DEQUANTIZE 105
 #define HOLO_K_MATMUL_ACTIVATION 106
 #define HOLO_K_MATMUL_ADD 107
+#define HOLO_K_MATMUL_ADD_ACTIVATION 108 /* kernel_codec.rs D_MMAA: act(A . B + residual), no narrowing between the add and the activation */
+#define HOLO_K_MATMUL_DEQUANT_PLAIN 111  /* kernel_codec.rs D_MMDQ: the all-default MatMulDequant ([k,n] weight, f32 activations: "W8A32") */
 #define HOLO_K_BROADCAST_BINARY 112
 #define HOLO_K_DEQUANT_ACTIVATION 113
 #define HOLO_K_GATHER 114
@@ -182,6 +184,15 @@ typedef struct HoloMatMulAddCall {
     HoloBufferRef residual;
 } HoloMatMulAddCall;
 
+/* MatMulAddActivationCall (kernel_call.rs:913-929): out = act(A . B + residual). The reference forms it for f32
+ * only (session.rs:2220-2226, where no narrowing is skipped); for 16-bit dtypes the product is narrowed once, the sum
+ * and the activation are taken in f32 and narrowed once more (cpu/float_kernels.rs:933-936). */
+typedef struct HoloMatMulAddActivationCall {
+    HoloMatMulCall mm;
+    HoloBufferRef residual;
+    uint8_t act; /* HOLO_FUSED_* */
+} HoloMatMulAddActivationCall;
+
 /* NormCall (kernel_call.rs:423-446); RmsNorm uses x, gamma, output, batch, feature, epsilon_bits */
 typedef struct HoloNormCall {
     HoloBufferRef x, gamma, beta, residual, output;
@@ -190,10 +201,15 @@ typedef struct HoloNormCall {
     uint8_t dtype;
 } HoloNormCall;
 
-/* MatMulDequantCall (kernel_call.rs:152-213), wire form 116: out = act(A . dequant(Bq) [+ residual]).
- * Served: the output-major W8A8 decode product (bq_omajor = 1, act_quant = 1 = W8A8_TOKEN_SYM): A f32
- * [m,k], Bq i8 [n,k], symmetric per-channel scales f32 [n] (channels = n, inner = 1, zero points all 0),
- * f32 output; every A row quantized with quantize_row_i8, exact i32 dot, one f32 writeback. */
+/* MatMulDequantCall (kernel_call.rs:152-213), wire forms 111 / 116 / 117: out = act(A . dequant(Bq) [+ residual]).
+ * Served: (1) the output-major W8A8 decode product (bq_omajor = 1, act_quant = 1 = W8A8_TOKEN_SYM): A f32
+ * [m,k], Bq i8 / i4 / e8cb [n,k], symmetric per-channel scales f32 [n] (channels = n, inner = 1, zero points all 0),
+ * f32 output; every A row quantized with quantize_row_i8, exact i32 dot, one f32 writeback.
+ * (2) the [k,n] form with f32 activations (bq_omajor = 0, act_quant = 0, "W8A32", cpu/float_kernels.rs:596-731):
+ * Bq i8 / u8 / i4 [k,n], per-tensor (scale_bits, zero_point) or per-channel scales / zero points; every output cell
+ * is the reference's ascending-k multiply-add chain over the dequantized weights (for m <= 3 with symmetric
+ * per-column i8 scales: the chain over the integer levels, the column scale applied once at the end,
+ * cpu/simd.rs:3480-3570). */
 typedef struct HoloMatMulDequantCall {
     HoloBufferRef a, bq, scales, zero_points, output;
     uint32_t m, k, n, channels, inner;
@@ -397,6 +413,7 @@ typedef struct HoloKernelCall {
         HoloMatMulCall matmul;          /* MATMUL */
         HoloMatMulActivationCall matmul_activation;
         HoloMatMulAddCall matmul_add;
+        HoloMatMulAddActivationCall matmul_add_activation;
         HoloMatMulDequantCall matmul_dequant;
         HoloNormCall norm;              /* RMS_NORM, ADD_RMS_NORM (norm of x + residual) */
         HoloRoPECall rope;              /* ROTARY */
@@ -543,45 +560,163 @@ int32_t holo_b200_archive_check(const uint8_t* archive, uint64_t len, int32_t ve
  * The first call on each device looks the array up (the device of the calling thread must be the
  * stream's device); make that first call before any stream capture begins. All calls share the
  * array: two calls that overlap on the GPU (different streams) race on it. Enqueues on
- * `cuda_stream` and returns without synchronising. */
+ * `cuda_stream` and returns without synchronising; a failure inside the kernel (a bounded wait
+ * that gave up: nothing is written to `out`) is reported by the status call below, and until it
+ * has been reported the kernels of later calls return at once without writing. */
 int32_t holo_b200_decode_attention_q8_static(void* cuda_stream, const void* q, const int8_t* k_past,
                                              const float* k_past_scales, const int8_t* v_past, const float* v_past_scales,
                                              const int8_t* k_new, const float* k_new_scales, const int8_t* v_new,
                                              const float* v_new_scales, const uint32_t* valid_len, void* out,
                                              uint32_t batch, uint32_t heads, uint32_t kv_heads, uint32_t past_len,
                                              uint32_t head_dim, uint32_t scale_bits, uint8_t dtype);
+/* Companion of the entry point above (no counterpart in the reference either): waits for
+ * `cuda_stream`, reads the 4-byte status word of the built-in array back (no allocation) and
+ * returns HOLO_ERR_DISPATCH if a bounded device-side wait gave up since the last query, clearing
+ * the record; HOLO_OK otherwise. Call it where the caller synchronises anyway (per step). */
+int32_t holo_b200_decode_attention_q8_static_status(void* cuda_stream);
 
 /* ---- content-addressed execution (crates/hologram-exec/src/session.rs:942-984 execute_addressed,
- * :1052-1289 the walk; labels crates/hologram-archive/src/address.rs:83-116).
- * A label is 71 ASCII bytes, "blake3:" + 64 hex digits. Load the session with
- * HOLO_SESSION_ADDRESSED or-ed into `verify`; write the inputs, pass their labels (port order) and
- * receive the outputs' labels. A node whose derived label is already resident in the session's
- * device pool is bound by pointer and not dispatched; a repeat of the same input labels is answered
- * from the memo without touching the device. Labels returned for outputs are the internal
- * derivation (derive_label); the witnessed boundary form of the reference is not produced. */
+ * :1052-1289 the walk; labels crates/hologram-archive/src/address.rs:83-116, :197-221).
+ * A label is 71 ASCII bytes, "blake3:" + 64 hex digits. Load the session with HOLO_SESSION_ADDRESSED
+ * or-ed into `verify`. Values live in a label-keyed pool of device buffers (the device-resident
+ * BufferArena, crates/hologram-exec/src/buffer.rs:149-207): intern the inputs (or feed a previous
+ * call's output labels straight back in), pass their labels in port order and receive the outputs'
+ * labels. A node whose derived label is already resident is bound by pointer and not dispatched; a
+ * repeat of the same input labels is answered from the memo without touching the device; a
+ * KvCacheWrite whose cache value is uniquely owned is realised as the in-place move (session.rs:1313-1370).
+ * Interior values carry the cheap derivation (derive_label); a graph output is retained, and reported,
+ * under the boundary form (derive_label_boundary, address.rs:197-221). An output that has no derivable
+ * label (it depends on a value the labels do not see, e.g. a tensor-parallel sum) is labelled by its bytes
+ * (the only place a result is read back and hashed).
+ * An input label that is not resident in the pool is taken from the bytes the caller wrote to the
+ * port's slot (a device-to-device copy into the pool). */
 #define HOLO_SESSION_VERIFY 1
 #define HOLO_SESSION_ADDRESSED 2
+/* The operand list the reference derives a norm's label from is x, gamma, beta (kernel_call.rs:1612-1616),
+ * so AddRmsNorm(x, r1) and AddRmsNorm(x, r2) share a label there. That is the default here too (labels are
+ * byte-identical to the reference's). With this flag the residual operand is appended, so that two sums
+ * over different residuals never share a label. */
+#define HOLO_SESSION_LABEL_RESIDUAL 4
 typedef struct HoloAddressedStats {
     uint32_t dispatched; /* calls launched by this walk */
-    uint32_t skipped;    /* calls answered by a resident value */
+    uint32_t skipped;    /* calls answered by a resident value (moves included, as in the reference's last_skipped) */
     uint32_t memo_hit;   /* 1: the whole graph was answered from the memo */
-    uint64_t pool_bytes; /* device bytes owned by the label pool (resident + released) */
+    uint64_t pool_bytes; /* device bytes the label pool has allocated (released buffers included) */
+    uint32_t moved;      /* KvCacheWrite calls realised as the in-place move */
+    uint32_t paged_in;   /* weights paged in from the provider so far (load_paged sessions) */
 } HoloAddressedStats;
 int32_t holo_b200_session_execute_addressed(holo_b200_session* s, const uint8_t* input_labels, uint32_t n_inputs,
                                             uint8_t* output_labels, uint32_t n_outputs, HoloAddressedStats* stats);
+/* intern_input (session.rs:1018-1022): hash `len` host bytes once, store them in the pool under that
+ * label (no slot is bound) and return the label; use it as an input of execute_addressed. */
+int32_t holo_b200_session_intern_input(holo_b200_session* s, const void* host, uint64_t len, uint8_t out71[71]);
+/* resolve (session.rs:1027-1029): copy the bytes of a resident label to the host (at most `cap`
+ * bytes; *len receives the value's length). *resident = 0 when the label is not in the pool. Synchronises. */
+int32_t holo_b200_session_resolve(holo_b200_session* s, const uint8_t label71[71], void* host, uint64_t cap, uint64_t* len,
+                                  int32_t* resident);
+/* retain_label / release_label (session.rs:1000-1012; buffer.rs:795-836): a leased value survives every
+ * walk until released (residency by ownership, not recency) and refuses the in-place KvCacheWrite move, so
+ * a step on a leased cache takes the honest copy and the leased pre-image stays bit-intact: the rollback
+ * primitive of speculative decoding and branch search. Refcounted. *ok = 0 when the label is not resident
+ * (retain) or holds no lease (release). */
+int32_t holo_b200_session_retain_label(holo_b200_session* s, const uint8_t label71[71], int32_t* ok);
+int32_t holo_b200_session_release_label(holo_b200_session* s, const uint8_t label71[71], int32_t* ok);
+/* leased_count (session.rs:1479). */
+uint32_t holo_b200_session_leased_count(holo_b200_session* s);
 /* address_bytes: the label of a leaf value (address.rs:83-86). */
 int32_t holo_b200_label_bytes(const uint8_t* data, uint64_t len, uint8_t out71[71]);
 /* derive_label: BLAKE3(opcode LE16 || params || labels...) as a label (address.rs:108-116). */
 int32_t holo_b200_label_derive(uint16_t opcode, const uint8_t* params, uint32_t params_len, const uint8_t* labels,
                                uint32_t n_labels, uint8_t out71[71]);
+/* derive_label_boundary (address.rs:197-221): the label of (opcode LE16 || params), then every operand label
+ * folded in order through the ordered product address_bytes(left digest || right digest)
+ * (crates/hologram-archive/src/compose.rs:154-164); with no operand the op label is composed with itself. */
+int32_t holo_b200_label_derive_boundary(uint16_t opcode, const uint8_t* params, uint32_t params_len, const uint8_t* labels,
+                                        uint32_t n_labels, uint8_t out71[71]);
 /* KernelCall::op_signature (kernel_call.rs:1321-1516): opcode and scalar parameter bytes. */
 int32_t holo_b200_op_signature(const HoloKernelCall* call, uint16_t* opcode, uint8_t params64[64], uint32_t* params_len);
+
+/* ---- paged weights (session.rs:417 load_paged; buffer.rs:491 pin_lazy, :650 page_and_bind_group).
+ * The session keeps a bounded window of HBM over a host-side weight set instead of a full copy:
+ * constants stored by reference (the large bodies) are declared by fingerprint at load, paged in from
+ * the provider (ideally pinned host memory) right before the first call that reads them, and evicted
+ * least-recently-used to keep the resident bytes within `budget_bytes` (0 = never evict). A model that
+ * fits the budget pages each weight once and then runs like a fully resident load; results are
+ * bit-identical either way. The archive may omit the Weights section (a weightless archive).
+ * Implies HOLO_SESSION_ADDRESSED. The provider must outlive the session. */
+typedef struct HoloWeightProvider {
+    void* user;
+    /* full body length for a fingerprint, or -1 if the provider does not have it (weight.rs:56) */
+    int64_t (*size)(void* user, const uint8_t fingerprint[32]);
+    /* pointer to bytes [offset, offset + len) of the body, valid until the session is destroyed, or NULL (weight.rs:61) */
+    const void* (*get_range)(void* user, const uint8_t fingerprint[32], uint64_t offset, uint64_t len);
+} HoloWeightProvider;
+int32_t holo_b200_session_load_paged(holo_b200_ctx* ctx, const uint8_t* archive, uint64_t len, int32_t verify,
+                                     const HoloWeightProvider* provider, uint64_t budget_bytes, holo_b200_session** out);
+
+/* ---- memory-tier report (crates/hologram-exec/src/coherence.rs:78-154, session.rs:797 tier_report;
+ * crates/hologram-types/src/memory_tier.rs:41-51). Every call has a tier that is a pure function of its
+ * dtype's bit width (<= 8: CpuL1, <= 16: CpuL2, <= 24: CpuMain, else Device; layout-only calls CpuMain);
+ * a policy maps it to the effective tier and the level-boundary migration schedule follows from it.
+ * This backend runs every call on the device whatever its tier: HOLO_TIER_FORCE_ALL_DEVICE is the policy
+ * it executes under (no slot ever migrates after its first upload); the other policies are reported
+ * for comparison with the reference's planner, nothing is executed differently. */
+#define HOLO_TIER_COMPILED 0
+#define HOLO_TIER_FORCE_ALL_CPU 1
+#define HOLO_TIER_FORCE_ALL_DEVICE 2
+typedef struct HoloTierReport {
+    uint32_t cpu_l1_calls, cpu_l2_calls, cpu_main_calls, device_calls;
+    uint32_t total_migration_slots, levels_with_migrations;
+} HoloTierReport;
+int32_t holo_b200_session_tier_report(holo_b200_session* s, int32_t policy, HoloTierReport* out);
+
+/* ---- label-keyed buffer pool on its own (the BufferArena operations the executor calls,
+ * buffer.rs:273-952). `ctx` NULL gives a pool over plain host memory: the same table logic with no
+ * device, for unit tests of the residency rules. Labels are 71 bytes. Functions returning int32_t
+ * report 1 / 0 for the reference's bool results and a negative status on failure. */
+typedef struct holo_b200_pool holo_b200_pool;
+int32_t holo_b200_pool_create(holo_b200_ctx* ctx, holo_b200_pool** out);
+void holo_b200_pool_destroy(holo_b200_pool* p);
+int32_t holo_b200_pool_rebind_reset(holo_b200_pool* p, uint32_t n_slots);
+int32_t holo_b200_pool_store_unbound(holo_b200_pool* p, const uint8_t label71[71], const void* host, uint64_t len);
+int32_t holo_b200_pool_pin_bytes(holo_b200_pool* p, const uint8_t label71[71], const void* host, uint64_t len);
+int32_t holo_b200_pool_bind_fresh(holo_b200_pool* p, uint32_t slot, uint64_t len);
+int32_t holo_b200_pool_bind_resident(holo_b200_pool* p, uint32_t slot, const uint8_t label71[71]);
+int32_t holo_b200_pool_retain(holo_b200_pool* p, uint32_t slot, const uint8_t label71[71]);
+/* steal_transient + bind_stolen: on success (1) the label is retired and its buffer is bound to `out_slot` */
+int32_t holo_b200_pool_steal_transient(holo_b200_pool* p, const uint8_t label71[71], const uint32_t* allowed_slots,
+                                       uint32_t n_allowed, uint32_t out_slot);
+int32_t holo_b200_pool_lease(holo_b200_pool* p, const uint8_t label71[71]);
+int32_t holo_b200_pool_release(holo_b200_pool* p, const uint8_t label71[71]);
+int32_t holo_b200_pool_resident(holo_b200_pool* p, const uint8_t label71[71]);
+int32_t holo_b200_pool_bindable_input(holo_b200_pool* p, const uint8_t label71[71]);
+int32_t holo_b200_pool_resolve(holo_b200_pool* p, const uint8_t label71[71], void* host, uint64_t cap, uint64_t* len);
+/* pointer and length of the buffer bound to a slot (1), or 0 when the slot is unbound */
+int32_t holo_b200_pool_slot(holo_b200_pool* p, uint32_t slot, void** ptr, uint64_t* len);
+/* write host bytes into the buffer bound to a slot (the role a kernel's output plays) */
+int32_t holo_b200_pool_write_slot(holo_b200_pool* p, uint32_t slot, const void* host, uint64_t len);
+int32_t holo_b200_pool_set_lazy_budget(holo_b200_pool* p, uint64_t bytes);
+int32_t holo_b200_pool_pin_lazy(holo_b200_pool* p, const uint8_t label71[71], const uint8_t fingerprint[32], uint64_t size);
+int32_t holo_b200_pool_page_and_bind(holo_b200_pool* p, const uint32_t* slots, const uint8_t* labels, uint32_t n,
+                                     const HoloWeightProvider* provider);
+typedef struct HoloPoolStats {
+    uint64_t owned_bytes, lazy_resident_bytes, pages_in;
+    uint32_t leased, transient, released;
+} HoloPoolStats;
+int32_t holo_b200_pool_stats(holo_b200_pool* p, HoloPoolStats* out);
 
 /* ---- tensor-parallel group (no reference counterpart: the reference is single-device).
  * `nccl_unique_id` is the 128-byte ncclUniqueId produced by holo_b200_nccl_unique_id on rank 0
  * and broadcast by the host launcher. */
 int32_t holo_b200_nccl_unique_id(uint8_t out128[128]);
 int32_t holo_b200_ctx_init_tp(holo_b200_ctx* ctx, const uint8_t nccl_unique_id[128], int32_t rank, int32_t world);
+/* The same with a host-side time limit on the group's set-up: the communicator is created in NCCL's
+ * non-blocking mode and polled (ncclCommGetAsyncError); if the group has not formed after `timeout_ms`
+ * (a rank that never joins, a wrong world size on one rank) the attempt is aborted on the host and
+ * HOLO_ERR_INIT is returned. Nothing is enqueued on the GPU before the group has formed. 0 = no limit.
+ * holo_b200_ctx_init_tp uses HOLO_TP_INIT_TIMEOUT_MS (default 120000). */
+int32_t holo_b200_ctx_init_tp_timeout(holo_b200_ctx* ctx, const uint8_t nccl_unique_id[128], int32_t rank, int32_t world,
+                                      uint32_t timeout_ms);
 /* How the group's all-reduces of decode-sized 16-bit messages travel: 0 = no group, 1 = NCCL,
  * 2 = the library's own one-shot kernel over peer memory (CUDA IPC mailboxes; every rank sums
  * in rank order, so all ranks hold identical bits). Set HOLO_TP_P2P=0 to stay on NCCL. */
@@ -592,6 +727,13 @@ int32_t holo_b200_ctx_tp_transport(holo_b200_ctx* ctx);
  * may be null; outs may alias partials). Synchronises. */
 int32_t holo_b200_tp_emulate_all_reduce(holo_b200_ctx* ctx, int32_t world, const void* const* partials, const void* const* residuals,
                                         void* const* outs, uint64_t count, uint8_t dtype, int32_t repeats);
+/* The same self-check with a peer that never sends: the CTAs of `withheld_rank` (-1 = none) return at once,
+ * so the other ranks' polls of its units run out after `poll_limit` polls (0 = the library's limit), every
+ * waiting thread gives up, the kernel ends and the call returns HOLO_ERR_DISPATCH (the context stays
+ * usable: the next call works). This is how a dead peer surfaces on the host. */
+int32_t holo_b200_tp_emulate_all_reduce_ex(holo_b200_ctx* ctx, int32_t world, const void* const* partials, const void* const* residuals,
+                                           void* const* outs, uint64_t count, uint8_t dtype, int32_t repeats, int32_t withheld_rank,
+                                           uint32_t poll_limit);
 
 /* Library version / build info string (static storage). */
 const char* holo_b200_version(void);

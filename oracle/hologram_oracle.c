@@ -473,6 +473,75 @@ int holo_or_matmul_add(const void* a, const void* b, const void* residual, void*
     return 0;
 }
 
+/* matmul_add_activation_float, cpu/float_kernels.rs:899-938: the matmul result is written (narrowed) first; then
+ * v = read(out) + read(residual) and write(f(v)) with nothing narrowed between the add and the activation. */
+int holo_or_matmul_add_activation(const void* a, const void* b, const void* residual, void* out, uint32_t m, uint32_t k, uint32_t n,
+                                  int dtype, int fused_act) {
+    int act;
+    if (!fused_to_lut_act(fused_act, &act)) return -3;
+    int rc = holo_or_matmul(a, b, out, m, k, n, dtype);
+    if (rc) return rc;
+    size_t count = (size_t)m * n;
+    for (size_t i = 0; i < count; ++i) {
+        float v = read_float(out, i, dtype) + read_float(residual, i, dtype);
+        write_float(out, i, holo_or_act(act, v), dtype);
+    }
+    return 0;
+}
+
+/* matmul_dequant_float over a [k, n] weight with f32 activations, cpu/float_kernels.rs:596-731, and its epilogue
+ * (:733-770). scales == NULL: per-tensor (scale, zp). quant_dtype: i8 (2), u8 (1), i4 (10: two nibbles per byte,
+ * low first, index i = kk * n + j). Two definitions:
+ *  - m <= 3, i8, channels == n, inner == 1, every zero point 0: matmul_i8_per_channel (cpu/simd.rs:3480-3570): per
+ *    cell an ascending-k chain over the integer levels (fused multiply-add in the 16- and 8-column panels,
+ *    multiply-then-add in the scalar remainder of n % 8 columns), then acc * scales[j];
+ *  - otherwise the weight is dequantized, (q - zp[ch]) as f32 * scale[ch] with ch = (i / inner) % channels, and the
+ *    f32 matmul runs on it (holo_or_matmul's per-cell order).
+ * Then out += residual (if any) and the activation (act < 0: none; a lut_act id otherwise). */
+int holo_or_matmul_dequant_kn(const float* a, const uint8_t* bq, const float* scales, const int32_t* zps, const float* residual, float* out,
+                              uint32_t m, uint32_t k, uint32_t n, uint32_t channels, uint32_t inner, int quant_dtype, float scale, int32_t zp,
+                              int act) {
+    if (m == 0 || k == 0 || n == 0) return 0;
+    if (quant_dtype != HOLO_DTYPE_I8 && quant_dtype != HOLO_DTYPE_U8 && quant_dtype != 10) return -3;
+    if (inner == 0) inner = 1;
+    int per_ch = channels > 0 && scales != NULL;
+    int fused = per_ch && quant_dtype == HOLO_DTYPE_I8 && m <= 3 && channels == n && inner == 1;
+    if (fused)
+        for (uint32_t j = 0; j < n; ++j)
+            if (zps[j] != 0) { fused = 0; break; }
+    uint32_t n_fma = n - (n % 8);
+    for (uint32_t i = 0; i < m; ++i) {
+        for (uint32_t j = 0; j < n; ++j) {
+            float acc = 0.0f;
+            for (uint32_t kk = 0; kk < k; ++kk) {
+                size_t idx = (size_t)kk * n + j;
+                int q;
+                if (quant_dtype == HOLO_DTYPE_I8) q = (int)(int8_t)bq[idx];
+                else if (quant_dtype == HOLO_DTYPE_U8) q = (int)bq[idx];
+                else {
+                    uint8_t byte = bq[idx / 2];
+                    int v = (idx & 1) ? (byte >> 4) : (byte & 15);
+                    q = v >= 8 ? v - 16 : v;
+                }
+                float w;
+                if (fused) w = (float)q;
+                else if (per_ch) {
+                    size_t ch = (idx / inner) % channels;
+                    w = (float)(q - zps[ch]) * scales[ch];
+                } else w = (float)(q - zp) * scale;
+                float av = a[(size_t)i * k + kk];
+                if (j < n_fma) acc = fmaf(av, w, acc);
+                else acc = acc + av * w;
+            }
+            float y = fused ? acc * scales[j] : acc;
+            if (residual) y = y + residual[(size_t)i * n + j];
+            if (act >= 0) y = holo_or_act(act, y);
+            out[(size_t)i * n + j] = y;
+        }
+    }
+    return 0;
+}
+
 /* ---- elementwise binary: cpu/float_kernels.rs:252-296 (op 0 = add, 1 = mul) ---------- */
 int holo_or_binary(int op, const void* a, const void* b, void* out, uint64_t n, int dtype) {
     for (uint64_t i = 0; i < n; ++i) {

@@ -36,6 +36,9 @@ def _load(path):
         "holo_or_matmul": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int]),
         "holo_or_matmul_activation": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, C.c_int]),
         "holo_or_matmul_add": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int]),
+        "holo_or_matmul_add_activation": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, C.c_int]),
+        "holo_or_matmul_dequant_kn": (C.c_int, [_c, _c, _c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int,
+                                                C.c_float, C.c_int32, C.c_int]),
         "holo_or_binary": (C.c_int, [C.c_int, _c, _c, _c, C.c_uint64, C.c_int]),
         "holo_or_rms_norm": (C.c_int, [_c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
         "holo_or_add_rms_norm": (C.c_int, [_c, _c, _c, _c, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int]),
@@ -140,6 +143,30 @@ def matmul(a, b, m, k, n, dtype, act=0, residual=None, which=None):
         rc = L.holo_or_matmul_activation(_p(a), _p(b), _p(out), m, k, n, dtype, act)
     else:
         rc = L.holo_or_matmul(_p(a), _p(b), _p(out), m, k, n, dtype)
+    assert rc == 0, rc
+    return out
+
+
+def matmul_add_activation(a, b, residual, m, k, n, dtype, act):
+    """matmul_add_activation_float (cpu/float_kernels.rs:899-938); act is a fused_activation id."""
+    a, b, r = (np.ascontiguousarray(v) for v in (a, b, residual))
+    out = np.zeros(m * n, dtype=_np_store(dtype))
+    rc = lib.holo_or_matmul_add_activation(_p(a), _p(b), _p(r), _p(out), m, k, n, dtype, act)
+    assert rc == 0, rc
+    return out
+
+
+def matmul_dequant_kn(a, bq, m, k, n, quant_dtype, scales=None, zero_points=None, channels=0, inner=1, scale=1.0, zero_point=0,
+                      residual=None, act=None):
+    """matmul_dequant_float over a [k, n] weight with f32 activations (cpu/float_kernels.rs:596-770); act is a LUT id."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    bq = np.ascontiguousarray(bq).view(np.uint8)
+    sc = None if scales is None else np.ascontiguousarray(scales, dtype=np.float32)
+    zp = None if zero_points is None else np.ascontiguousarray(zero_points, dtype=np.int32)
+    res = None if residual is None else np.ascontiguousarray(residual, dtype=np.float32)
+    out = np.zeros(m * n, dtype=np.float32)
+    rc = lib.holo_or_matmul_dequant_kn(_p(a), _p(bq), _p(sc), _p(zp), _p(res), _p(out), m, k, n, channels, inner, quant_dtype,
+                                       float(np.float32(scale)), zero_point, -1 if act is None else act)
     assert rc == 0, rc
     return out
 

@@ -101,3 +101,56 @@ def test_tensor_parallel_shards_partition_the_weights():
     # AllReduce precedes each residual add on every rank
     kinds = [c.kind for c in i0["calls"]]
     assert kinds.count(kc.K_ALL_REDUCE) == 2 * cfg.n_layers
+
+
+def _calls_only(body, extra=()):
+    return holo.assemble([(holo.SEC_KERNEL_CALLS, [body]), (holo.SEC_WEIGHTS, [struct.pack("<I", 0)])] + list(extra))
+
+
+def test_wrapped_weight_length_is_refused():
+    # a 64-bit body length near 2^64 must not wrap past the bounds check of the Weights section
+    for blen in (0xFFFFFFFFFFFFFFF0, 0xFFFFFFFFFFFFFFFF, 1 << 40):
+        weights = struct.pack("<I", 1) + b"\x11" * 32 + struct.pack("<Q", blen) + b"tail"
+        img = holo.assemble([(holo.SEC_KERNEL_CALLS, [struct.pack("<I", 0)]), (holo.SEC_WEIGHTS, [weights])])
+        with pytest.raises(hb.BackendError) as e:
+            hb.archive_check(img, verify=False)
+        assert "truncated" in str(e.value)
+
+
+def test_absurd_slot_numbers_are_refused():
+    # slot numbers size the session's tables: one call naming slot 0xFFFFFFFE must not make the loader plan 32 GB
+    c = kc.KernelCall.Gelu(kc.UnaryCall(kc.rb(0, 0, 64), kc.rb(0xFFFFFFFE, 0, 64), 32, 16, kc.DTYPE_BF16))
+    with pytest.raises(hb.BackendError) as e:
+        hb.archive_check(_calls_only(holo.encode_calls([c])), verify=False)
+    assert "slot number" in str(e.value)
+    ok = kc.KernelCall.Gelu(kc.UnaryCall(kc.rb(0, 0, 64), kc.rb(1, 0, 64), 32, 16, kc.DTYPE_BF16))
+    ports = holo.encode_ports([holo.Port("x", 1 << 30, 32, kc.DTYPE_BF16, [32])])
+    with pytest.raises(hb.BackendError):
+        hb.archive_check(_calls_only(holo.encode_calls([ok]), [(holo.SEC_INPUTS, [ports])]), verify=False)
+    assert hb.archive_check(_calls_only(holo.encode_calls([ok])), verify=False)[0] == 1
+
+
+def test_weightless_archive_needs_a_provider():
+    # a constant stored by reference whose body is not in the archive: a plain load must fail loud, never bind
+    # the label of empty content (crates/hologram-exec/src/session.rs:669-686)
+    w = holo.HoloWriter()
+    w.add_constant(0, kc.DTYPE_BF16, bytes(1024), by_reference=True)
+    w.calls = [kc.KernelCall.Gelu(kc.UnaryCall(kc.rb(0, 0, 1024), kc.rb(1, 0, 1024), 512, 16, kc.DTYPE_BF16))]
+    assert hb.archive_check(w.finish())[3] == 1
+    with pytest.raises(hb.BackendError) as e:
+        hb.archive_check(w.finish(weightless=True))
+    assert "not in the archive" in str(e.value)
+
+
+def test_new_wire_forms_survive_the_reader():
+    rb = kc.rb
+    mm = kc.MatMulCall(rb(0, 0, 64), rb(1, 0, 64), rb(2, 0, 64), 2, 8, 4, 8, 0)
+    calls = [
+        kc.KernelCall.MatMulAddActivation(kc.MatMulAddActivationCall(mm, rb(3, 0, 32), kc.FUSED_GELU)),
+        kc.KernelCall.MatMulDequant(kc.MatMulDequantCall(rb(0), rb(1), rb(2), rb(3), rb(4), 2, 8, 4, 4, 1, kc.DTYPE_I8, 8, 0, 0, 0, 0, 0, kc.NONE)),
+        kc.KernelCall.MatMulDequant(kc.MatMulDequantCall(rb(0), rb(1), kc.NONE, kc.NONE, rb(4), 2, 8, 4, 0, 1, kc.DTYPE_I4, 8, 0x3C000000, 1, 0, 0, kc.FUSED_TANH, rb(5))),
+        kc.KernelCall.Softmax(kc.SoftmaxCall(rb(0), rb(1), 4, 64, kc.DTYPE_F32)),
+    ]
+    assert [c.kind for c in calls[:3]] == [108, 111, 116]
+    for n in range(1, len(calls) + 1):
+        assert hb.archive_check(_calls_only(holo.encode_calls(calls[:n])), verify=False)[0] == n

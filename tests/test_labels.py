@@ -124,3 +124,61 @@ def test_matmul_dequant_with_a_codebook_takes_tag_117_and_one_more_byte():
     assert op == 117 and params == struct.pack("<IIIIIBBIiBBBB", 1, 8, 4, 4, 1, kc.DTYPE_E8CB, 8, 0, 0, 1, 0, 0, 1)
     wire = holo.encode_calls([call])
     assert wire[4:6] == struct.pack("<H", 117) and wire[6:-20] == plain[6:] and wire[-20:] == struct.pack("<IQQ", 5, 0, 64)
+
+
+def _b3(data):
+    return blake3.blake3(data).digest()
+
+
+def test_boundary_label_is_the_ordered_product_of_digests():
+    # address.rs:197-221 + compose.rs:154-164, computed by hand with the independent blake3 package:
+    # op label = address_bytes(opcode LE16 || params); acc = address_bytes(digest(acc) || digest(operand)) per operand
+    a = hs.label_bytes(np.arange(10, dtype=np.uint8))
+    b = hs.label_bytes(np.arange(11, dtype=np.uint8))
+    da, db = _b3(bytes(range(10))), _b3(bytes(range(11)))
+    params = bytes([9, 8, 7])
+    op = _b3(struct.pack("<H", 45) + params)
+    two = _b3(_b3(op + da) + db)
+    assert hs.label_derive_boundary(45, params, [a, b]) == b"blake3:" + two.hex().encode()
+    # one operand; and no operand at all: the op label composed with itself
+    assert hs.label_derive_boundary(45, params, [a]) == b"blake3:" + _b3(op + da).hex().encode()
+    assert hs.label_derive_boundary(45, params, []) == b"blake3:" + _b3(op + op).hex().encode()
+    # order-sensitive, and a different function of the same pieces than the interior derivation
+    assert hs.label_derive_boundary(45, params, [b, a]) != hs.label_derive_boundary(45, params, [a, b])
+    assert hs.label_derive_boundary(45, params, [a, b]) != hs.label_derive(45, params, [a, b])
+    # a malformed operand label is refused (decode_blake3)
+    import hologram_b200 as hb
+    with pytest.raises(hb.BackendError):
+        hs.label_derive_boundary(45, params, [b"sha256:" + b"0" * 64])
+    with pytest.raises(hb.BackendError):
+        hs.label_derive_boundary(45, params, [b"blake3:" + b"G" * 64])
+
+
+def test_matmul_dequant_plain_form_keeps_tag_108_and_wire_111():
+    # kernel_call.rs:1475-1500: the all-default form (the [k,n] weight with f32 activations) keeps the base bytes under
+    # tag 108; the layout-only bq_omajor does not change the signature; an epilogue or W8A8 takes tag 116
+    from hologram_b200 import holo
+    buf = lambda i: kc.rb(i, 0, 64)
+    c = kc.MatMulDequantCall(buf(0), buf(1), buf(2), buf(3), buf(4), 2, 8, 4, 4, 1, kc.DTYPE_I8, 8, 0x3C000000, -3, 0, 0, 0, kc.NONE)
+    call = kc.KernelCall.MatMulDequant(c)
+    base = struct.pack("<IIIIIBBIi", 2, 8, 4, 4, 1, kc.DTYPE_I8, 8, 0x3C000000, -3)
+    assert call.kind == kc.K_MATMUL_DEQUANT_PLAIN and hs.op_signature(call) == (108, base)
+    wire = holo.encode_calls([call])
+    assert wire[4:6] == struct.pack("<H", 111) and len(wire) == 4 + 2 + 5 * 20 + len(base)
+    c.act = kc.FUSED_SILU
+    ext = kc.KernelCall.MatMulDequant(c)
+    assert ext.kind == kc.K_MATMUL_DEQUANT and hs.op_signature(ext) == (116, base + bytes([0, kc.FUSED_SILU, 0]))
+    c.act, c.residual = 0, buf(5)
+    assert hs.op_signature(kc.KernelCall.MatMulDequant(c)) == (116, base + bytes([0, 0, 1]))
+
+
+def test_matmul_add_activation_signature_and_wire():
+    # kernel_call.rs:1469 (opcode 107: matmul parameters then the activation), kernel_codec.rs:519-524 (wire 108)
+    from hologram_b200 import holo
+    mm = kc.MatMulCall(kc.rb(0, 0, 64), kc.rb(1, 0, 64), kc.rb(2, 0, 64), 2, 8, 4, 8, 0)
+    call = kc.KernelCall.MatMulAddActivation(kc.MatMulAddActivationCall(mm, kc.rb(3, 0, 32), kc.FUSED_GELU))
+    assert hs.op_signature(call) == (107, bytes.fromhex("02000000080000000400000008") + bytes([kc.FUSED_GELU]))
+    wire = holo.encode_calls([call])
+    plain = holo.encode_calls([kc.KernelCall.MatMul(mm)])
+    assert wire[4:6] == struct.pack("<H", 108) and wire[6:6 + len(plain) - 6] == plain[6:]
+    assert wire[-21:] == struct.pack("<IQQB", 3, 0, 32, kc.FUSED_GELU)

@@ -56,6 +56,19 @@ def test_sweep_cells_reduced_rows(backend, act, dtype):
     assert np.array_equal(run_lut(backend, act, dtype, bits), orc.unary_lut(act, dtype, bits))
 
 
+@pytest.mark.parametrize("act,dtype", [(kc.LUT_SILU, kc.DTYPE_BF16), (kc.LUT_TANH, kc.DTYPE_F16), (kc.LUT_EXP, kc.DTYPE_F16),
+                                       (kc.LUT_ERF, kc.DTYPE_BF16)])
+def test_sweep_cells_full_size(backend, act, dtype):
+    # whole [8192, 14336] cells (117,440,512 elements, 470 MB of traffic each), one per dtype plus the
+    # clamped f16 Exp cell and an Erf cell, bit-exact over every element
+    n = 8192 * 14336
+    clamp = (-20.0, 11.0) if (act == kc.LUT_EXP and dtype == kc.DTYPE_F16) else None
+    bits = synth_bits(n, dtype, 4.0, 0x2C2 + act, clamp=clamp)
+    got = run_lut(backend, act, dtype, bits)
+    want = orc.unary_lut(act, dtype, bits)
+    assert np.array_equal(got, want)
+
+
 @pytest.mark.parametrize("n", [1, 7, 8, 9, 255, 4099, (1 << 21) + 5, (1 << 22) + 3])
 def test_ragged_sizes(backend, n):
     bits = synth_bits(n, kc.DTYPE_BF16, 3.0, n)

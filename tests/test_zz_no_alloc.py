@@ -4,10 +4,12 @@
 call time (an engine that owns all of HBM through its own arena, or one that cannot afford
 the implicit device synchronisation of the CUDA allocator): its split-KV partials live in an
 array inside the library. Here it is called twice in a row, with different inputs, through the
-C ABI with raw device pointers, and each result must equal what `holo_b200_dispatch` produces
-for the same call (same kernels, same split count: bit-identical, which is inside the
-1e-2 tolerance the attention tests use). The second call also shows that whatever the first
-one left in the shared array does not leak into later results.
+C ABI with raw device pointers. Each result is checked against the CPU oracle's composition
+(Cast / Dequantize / DecodeAttentionValid / Cast) within the 1e-2 tolerance the attention tests
+use, and must also equal what `holo_b200_dispatch` produces for the same call (same kernel, same
+split count: bit-identical). The second call also shows that whatever the first one left in the
+shared array does not leak into later results. The companion status call must report a clean
+run.
 """
 import ctypes as C
 
@@ -24,6 +26,9 @@ pytestmark = pytest.mark.gpu
 fn = lib.holo_b200_decode_attention_q8_static
 fn.restype = C.c_int32
 fn.argtypes = [C.c_void_p] * 12 + [C.c_uint32] * 6 + [C.c_uint8]
+status_fn = lib.holo_b200_decode_attention_q8_static_status
+status_fn.restype = C.c_int32
+status_fn.argtypes = [C.c_void_p]
 
 
 def make_case(b, h, kv, past, d, seed):
@@ -56,10 +61,15 @@ def test_static_scratch_attention_matches_dispatch_twice():
             rc = fn(be.stream, *ptrs, b, h, kv, past, d, 0, kc.DTYPE_BF16)
             assert rc == 0, lib.holo_b200_last_error()
             got = ws.read(11, b * h * d * 2, np.uint16)
-            assert np.array_equal(got, want)
-            ref = orc.bf16_to_f32(want)
+            assert status_fn(be.stream) == 0, lib.holo_b200_last_error()
+            # the oracle: the reference composition over the same codes and scales
+            rc, ref_bits = orc.decode_attention_valid_q8(arrs[0], kc.DTYPE_BF16, *arrs[1:], valid, b, h, kv, 1, past, 1, d, 0)
+            assert rc == 0
+            ref = orc.bf16_to_f32(ref_bits)
             err = np.max(np.abs(orc.bf16_to_f32(got) - ref)) / np.max(np.abs(ref))
+            print(f"static entry point vs oracle: max|err|/max|ref| = {err:.3e}")
             assert err <= 1e-2
+            assert np.array_equal(got, want)      # and bit-identical to the dispatch path
             ws.close()
         # a shape whose partials do not fit the built-in array is refused, loudly, before any launch
         rc = fn(be.stream, *([C.c_void_p(256)] * 11), 4096, 32, 8, 65536, 128, 0, kc.DTYPE_BF16)
