@@ -87,6 +87,13 @@ void sync_slot(holo_b200_session* s, uint32_t slot) {
     sl.owned = false;   // the pool (or the load-time table) owns it
 }
 
+// Between walks an input port's slot is unbound: inputs enter an addressed session by label (intern_input), and a
+// write through the workspace must never scribble over the pooled value that was bound there during the last walk.
+void restore_input_ports(holo_b200_session* s) {
+    for (const HoloPort& p : s->ar.inputs)
+        if (p.slot < s->ws->slots.size()) s->ws->slots[p.slot] = HoloSlot();
+}
+
 // call_dtype (kernel_call.rs:1668-1760) for the served variants
 uint8_t call_dtype(const HoloKernelCall& c) {
     const auto& u = c.u;
@@ -260,6 +267,7 @@ extern "C" int32_t holo_b200_session_execute_addressed(holo_b200_session* s, con
                 sync_slot(s, slot);
             }
             memcpy(output_labels, hit->second.first.data(), (size_t)n_outputs * HOLO_LABEL_BYTES);
+            restore_input_ports(s);
             ad.last_dispatched = 0;
             ad.last_skipped = (uint32_t)s->calls.size();
             ad.last_moved = 0;
@@ -272,14 +280,16 @@ extern "C" int32_t holo_b200_session_execute_addressed(holo_b200_session* s, con
         }
     }
 
-    // Refuse before any state change (session.rs:959-971): an input that is neither bindable after the
-    // rotation nor written to its port's load-time buffer cannot be served.
+    // Refuse before any state change (session.rs:959-971): the rotation below ages the pool, so a call that
+    // cannot bind must not rotate. Bindability is checked against what survives the rotation: pinned, the
+    // current generation, leases, paged-in weights. A label living only in the previous generation is one
+    // rotation from reclamation: intern the value again (that promotes it) or feed a fresh output label.
     std::vector<std::string> in_label(n_inputs);
     for (uint32_t i = 0; i < n_inputs; ++i) {
         in_label[i] = label_str(input_labels + (size_t)i * HOLO_LABEL_BYTES);
-        const uint32_t slot = s->ar.inputs[i].slot;
-        if (!pool.bindable_input(in_label[i]) && !ad.static_binding[slot].ptr)
-            return holo_fail(HOLO_ERR_SHAPE_MISMATCH, "shape mismatch: input %u is not resident under its label and its port has no load-time buffer", i);
+        if (!pool.bindable_input(in_label[i]))
+            return holo_fail(HOLO_ERR_SHAPE_MISMATCH, "shape mismatch: input %u (%s) is not resident under its label: intern it, or pass a label a walk returned",
+                             i, s->ar.inputs[i].name.c_str());
     }
 
     pool.rebind_reset(n_slots);
@@ -292,15 +302,7 @@ extern "C" int32_t holo_b200_session_execute_addressed(holo_b200_session* s, con
     std::vector<std::string> label = ad.slot_label_init;
     for (uint32_t i = 0; i < n_inputs; ++i) {
         const uint32_t slot = s->ar.inputs[i].slot;
-        if (!pool.bindable_input(in_label[i])) {
-            // the caller wrote the value to the port's slot: take it into the pool under its label
-            const uint64_t nb = s->ar.inputs[i].element_count * holo_dtype_size(s->ar.inputs[i].dtype);
-            const size_t bi = pool.bind_fresh(slot, std::max<uint64_t>(nb, slot < ad.slot_need.size() ? ad.slot_need[slot] : 0));
-            if (bi == HoloPool::UNBOUND) return holo_fail(HOLO_ERR_DISPATCH, "dispatch failed: the label pool could not allocate %llu bytes", (unsigned long long)nb);
-            const uint64_t copy = std::min<uint64_t>(pool.buffer_len(bi), ad.static_binding[slot].bytes);
-            if (copy) HOLO_CUDA(cudaMemcpyAsync(pool.buffer_ptr(bi), ad.static_binding[slot].ptr, copy, cudaMemcpyDeviceToDevice, s->ctx->stream));
-            pool.retain(slot, in_label[i]);
-        } else if (!pool.bind_resident(slot, in_label[i])) {
+        if (!pool.bind_resident(slot, in_label[i])) {
             return holo_fail(HOLO_ERR_SHAPE_MISMATCH, "shape mismatch: input %u could not be bound by its label", i);
         }
         sync_slot(s, slot);
@@ -464,6 +466,7 @@ extern "C" int32_t holo_b200_session_execute_addressed(holo_b200_session* s, con
         ad.memo.erase(lru);
     }
     ad.memo[key] = {outs, ++ad.memo_tick};
+    restore_input_ports(s);
     ad.last_dispatched = st.dispatched;
     ad.last_skipped = st.skipped;
     ad.last_moved = st.moved;

@@ -130,10 +130,10 @@ int32_t holo_dispatch_internal(holo_b200_ctx* ctx, const HoloKernelCall* call, h
 __device__ __forceinline__ void holo_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void holo_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// cluster_z > 1 makes grid z a thread-block cluster dimension.
+// A thread-block cluster of `cluster` CTAs along grid x (cluster_x) or grid z (cluster_z); 1 = no cluster.
 template <typename... KArgs, typename... Args>
-static inline cudaError_t holo_launch_kernel(holo_b200_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                             unsigned cluster_z, Args&&... args) {
+static inline cudaError_t holo_launch_kernel_cluster(holo_b200_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                                     unsigned cluster_x, unsigned cluster_z, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -146,16 +146,22 @@ static inline cudaError_t holo_launch_kernel(holo_b200_ctx* ctx, void (*kernel)(
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;
     }
-    if (cluster_z > 1) {
+    if (cluster_z > 1 || cluster_x > 1) {
         attr[na].id = cudaLaunchAttributeClusterDimension;
-        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.x = cluster_x > 1 ? cluster_x : 1;
         attr[na].val.clusterDim.y = 1;
-        attr[na].val.clusterDim.z = cluster_z;
+        attr[na].val.clusterDim.z = cluster_z > 1 ? cluster_z : 1;
         ++na;
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+// cluster_z > 1 makes grid z a thread-block cluster dimension.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t holo_launch_kernel(holo_b200_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                             unsigned cluster_z, Args&&... args) {
+    return holo_launch_kernel_cluster(ctx, kernel, grid, block, smem, 1u, cluster_z, static_cast<Args&&>(args)...);
 }
 #endif
 

@@ -19,6 +19,7 @@
 // the CTA still frees its TMEM before it exits.
 #include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "common.h"
 #include "numerics.cuh"
@@ -54,6 +55,9 @@ struct GemmParams {
     uint8_t* ar_mailbox[8];
     uint32_t* ar_state;
     uint32_t ar_world, ar_rank;
+    // CTA-pair kernel: work items [0, tail_begin) are whole 256 x 256 tiles; from tail_begin on every tile is two
+    // items of 256 x 128 (the last, partial round of tiles is cut in two so that it keeps every pair busy)
+    uint32_t tail_begin, n_items;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -513,6 +517,400 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 }
 
 
+// ---- persistent kernel for compute-bound shapes ---------------------------------------------------
+// One CTA per SM walks the 128 x 256 output tiles (tile t, t + grid, ...). A 128 x 128 tile reads 32 KiB of
+// shared-memory operands per 64-deep k-block for 64 MMA clocks, which is the shared-memory bandwidth itself;
+// at 128 x 256 the same A block feeds twice the columns (48 KiB for 128 clocks), so the tensor pipe is no
+// longer starved by its operands. The accumulator is double-buffered in TMEM (2 x 256 columns = all 512):
+// while the four epilogue warps drain tile i from one half, the issuer already accumulates tile i + 1 into
+// the other, and the TMA producer runs ahead through a 4-stage ring that never drains between tiles.
+//   warp 0   TMA producer (ring slot counter runs across tiles)
+//   warp 1   tcgen05.mma issuer; commits ring slots back to the producer and finished accumulators to the epilogue
+//   warps 2-5 epilogue: tcgen05.ld, narrow, epilogue op, store; hands the TMEM half back to the issuer
+// Every wait is bounded; a wait that gives up raises the status bit, every role leaves its loop, and the
+// CTA still frees its TMEM.
+constexpr int PBN = 256, PSTAGES = 4;
+struct PersistSmem {
+    static constexpr uint32_t A_BYTES = BM * BK * 2;            // 16 KiB
+    static constexpr uint32_t B_BYTES = BK * PBN * 2;           // 32 KiB
+    static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
+    static constexpr uint32_t RING = PSTAGES * STAGE;           // 192 KiB
+    static constexpr uint32_t TOTAL = RING + 256 + 1024;        // barriers, TMEM slot, abort flag; alignment slack
+};
+
+template <bool F16>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+matmul_umma_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    using S = PersistSmem;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* sm = smem_raw + (base - raw);
+    const uint32_t bar_full = base + S::RING, bar_empty = bar_full + 8 * PSTAGES;
+    const uint32_t bar_acc_full = bar_empty + 8 * PSTAGES, bar_acc_empty = bar_acc_full + 16;
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sm + S::RING + 16 * PSTAGES + 32);
+    volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(sm + S::RING + 16 * PSTAGES + 36);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tiles_n = (p.n + PBN - 1) / PBN, tiles_m = (p.m + BM - 1) / BM, ntiles = tiles_n * tiles_m;
+
+    holo_pdl_trigger();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PSTAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full + 8 * b, 1);
+            mbar_init(bar_acc_empty + 8 * b, 4);   // one arrival per epilogue warp
+        }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *s_tmem;
+    holo_pdl_wait();
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            const uint32_t tx = S::A_BYTES + S::B_BYTES;
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int m0 = (int)((tile / tiles_n) * BM), n0 = (int)((tile % tiles_n) * PBN);
+                for (uint32_t kb = 0; kb < p.kblocks; ++kb, ++it) {
+                    const uint32_t s = it % PSTAGES, use = it / PSTAGES;
+                    if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1, s_abort, p.status)) { ok = false; break; }
+                    const uint32_t st = base + s * S::STAGE;
+                    const int k0 = (int)(kb * BK);
+                    mbar_arrive_expect_tx(bar_full + 8 * s, tx);
+                    tma_load_2d(st, &map_a, k0, m0, bar_full + 8 * s);
+#pragma unroll
+                    for (int h = 0; h < PBN / 64; ++h) tma_load_2d(st + S::A_BYTES + h * (BK * 128), &map_b, n0 + 64 * h, k0, bar_full + 8 * s);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t fmt = F16 ? 0u : 1u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(PBN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            uint32_t it = 0, t = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
+                const uint32_t buf = t & 1u, use = t >> 1;
+                // the epilogue must have drained this half of TMEM (its previous use) before it is overwritten
+                if (use > 0 && !mbar_wait(bar_acc_empty + 8 * buf, (use - 1) & 1, s_abort, p.status)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + buf * (uint32_t)PBN;
+                for (uint32_t kb = 0; kb < p.kblocks; ++kb, ++it) {
+                    const uint32_t s = it % PSTAGES;
+                    if (!mbar_wait(bar_full + 8 * s, (it / PSTAGES) & 1, s_abort, p.status)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = base + s * S::STAGE, b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+                    for (int j = 0; j < BK / 16; ++j) {
+                        const uint64_t da = smem_desc(a_addr + j * 32, 16, 1024);
+                        const uint64_t db = smem_desc(b_addr + j * 2048, BK * 128, 1024);
+                        umma_bf16(tmem_d, da, db, idesc, (kb | (uint32_t)j) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(bar_empty + 8 * s);
+                }
+                if (ok) umma_commit(bar_acc_full + 8 * buf);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps (TMEM lane quarter = warp % 4) ----------------
+        const uint32_t quarter = warp & 3u;
+        if (warp == 2 && lane == 0 && (*reinterpret_cast<volatile uint32_t*>(p.status) & 4u)) *s_abort = 1;   // an earlier launch gave up: store nothing
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        uint32_t t = 0;
+        for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++t) {
+            const uint32_t buf = t & 1u, use = t >> 1;
+            const uint32_t m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * PBN;
+            const uint32_t row = m0 + quarter * 32 + lane;
+            const bool got = mbar_wait(bar_acc_full + 8 * buf, use & 1, s_abort, p.status);
+            if (!got || *s_abort) break;    // the abort flag is shared: every warp of the CTA leaves its loop
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem_d = tmem_base + buf * (uint32_t)PBN + ((quarter * 32u) << 16);
+#pragma unroll 1
+            for (int c = 0; c < PBN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_d + (uint32_t)(c * 32), v);
+                const uint32_t col0 = n0 + c * 32;
+                if (row < p.m && col0 < p.n) {
+                    uint32_t si = 0;
+                    while (si + 1 < p.nseg && col0 >= p.seg[si].col_end) ++si;
+                    const GemmSeg sg = p.seg[si];
+                    const uint64_t idx0 = (uint64_t)row * (sg.col_end - sg.col_begin) + (col0 - sg.col_begin);
+                    uint16_t* dst = sg.out + idx0;
+                    if (col0 + 32 <= sg.col_end && ((uintptr_t)dst & 15u) == 0) {
+                        uint32_t w[16];
+#pragma unroll
+                        for (int x = 0; x < 16; ++x) {
+                            const uint16_t lo = epilogue_elem<F16>(__uint_as_float(v[2 * x]), sg.table, sg.residual, idx0 + 2 * x);
+                            const uint16_t hi = epilogue_elem<F16>(__uint_as_float(v[2 * x + 1]), sg.table, sg.residual, idx0 + 2 * x + 1);
+                            w[x] = (uint32_t)lo | ((uint32_t)hi << 16);
+                        }
+#pragma unroll
+                        for (int x = 0; x < 4; ++x)
+                            reinterpret_cast<uint4*>(dst)[x] = make_uint4(w[4 * x], w[4 * x + 1], w[4 * x + 2], w[4 * x + 3]);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 32; ++x)
+                            if (col0 + x < sg.col_end) dst[x] = epilogue_elem<F16>(__uint_as_float(v[x]), sg.table, sg.residual, idx0 + x);
+                    }
+                }
+            }
+            // this half of TMEM may be overwritten once all four warps have read it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
+        }
+    }
+    // everyone meets here, whatever happened above, so that TMEM is always released
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ---- persistent kernel on CTA pairs (tcgen05 cta_group::2) -----------------------------------------
+// At 128 x 256 per CTA the product is bound by what the SMs can pull out of L2 (48 KiB of operands per
+// 4.2 MFLOP). Two CTAs of a cluster share one 256 x 256 tile instead: CTA r of the pair loads rows
+// [128 r, 128 r + 128) of the A block and columns [128 r, 128 r + 128) of the B block (32 KiB per CTA for the
+// same 4.2 MFLOP per CTA, a third less L2 traffic), the leader CTA issues one tcgen05.mma.cta_group::2 per
+// 16-deep k step which reads both CTAs' shared memory, and each CTA ends up with its own 128 rows x 256
+// columns of the accumulator in its own TMEM. No multicast load is involved: every CTA fetches its own
+// halves with plain tiled TMA loads, which signal the leader's barrier.
+//   both CTAs  warp 0: TMA producer for its halves (waits on its own "empty" barriers, signals the leader's "full")
+//   leader     warp 1: MMA issuer; tcgen05.commit multicasts "slot free" and "accumulator ready" to both CTAs
+//   both CTAs  warps 2-5: epilogue from their own TMEM; hand the TMEM half back by arriving on the leader's barrier
+// The accumulator is double-buffered (2 x 256 columns), the ring has 7 stages and never drains between tiles.
+// Every mbarrier wait is bounded; the only unbounded waits are the two cluster barriers (after barrier set-up
+// and before TMEM is released), which every thread of both CTAs reaches after bounded waits only.
+constexpr int QSTAGES = 7;
+struct PairSmem {
+    static constexpr uint32_t A_BYTES = BM * BK * 2;            // this CTA's 128 rows: 16 KiB
+    static constexpr uint32_t B_BYTES = BK * 128 * 2;           // this CTA's 128 columns: 16 KiB
+    static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
+    static constexpr uint32_t RING = QSTAGES * STAGE;           // 224 KiB: what arrives from L2 takes 1-2 us, so every KiB in flight counts
+    static constexpr uint32_t TOTAL = RING + 256 + 1024;
+};
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t cta_rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on the barrier at this offset in both CTAs of the pair once the MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)3)
+                 : "memory");
+}
+
+// Work item w of the pair kernel: tile row, first column and width (256, or 128 for the halves of a tail tile).
+struct PairItem {
+    uint32_t m_tile, n0, bn;
+};
+__device__ __forceinline__ PairItem pair_item(const GemmParams& p, uint32_t w, uint32_t tiles_n) {
+    PairItem it;
+    if (w < p.tail_begin) {
+        it.m_tile = w / tiles_n;
+        it.n0 = (w % tiles_n) * 256;
+        it.bn = 256;
+    } else {
+        const uint32_t h = w - p.tail_begin, tile = p.tail_begin + (h >> 1);
+        it.m_tile = tile / tiles_n;
+        it.n0 = (tile % tiles_n) * 256 + (h & 1u) * 128;
+        it.bn = 128;
+    }
+    return it;
+}
+
+template <bool F16>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+matmul_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    using S = PairSmem;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* sm = smem_raw + (base - raw);
+    const uint32_t bar_full = base + S::RING, bar_empty = bar_full + 8 * QSTAGES;
+    const uint32_t bar_acc_full = bar_empty + 8 * QSTAGES, bar_acc_empty = bar_acc_full + 16;
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sm + S::RING + 16 * QSTAGES + 32);
+    volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(sm + S::RING + 16 * QSTAGES + 36);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the pair is a cluster of two along grid x (the hardware pairs CTAs whose cluster rank differs in the lowest bit)
+    const uint32_t rank = blockIdx.x & 1u, pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;   // rank 0 = leader
+    const uint32_t tiles_n = (p.n + 255) / 256, tiles_m = (p.m + 255) / 256, ntiles = tiles_n * tiles_m;
+
+    holo_pdl_trigger();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < QSTAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);    // the leader's one arrive.expect_tx; the bytes come from both CTAs
+            mbar_init(bar_empty + 8 * s, 1);   // one multicast commit
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full + 8 * b, 1);
+            mbar_init(bar_acc_empty + 8 * b, 8);   // four epilogue warps of each CTA (used in the leader only)
+        }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        // the same warp of both CTAs allocates the pair's TMEM columns
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    // the peer's loads signal the leader's barriers: nobody starts before both CTAs have set theirs up
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *s_tmem;
+    holo_pdl_wait();
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t w = pair; w < p.n_items && ok; w += npairs) {
+                const PairItem item = pair_item(p, w, tiles_n);
+                // this CTA's halves: rows [128 r, +128) of the A block, columns [bn/2 r, +bn/2) of the B block
+                const int m0 = (int)(item.m_tile * 256 + rank * 128), n0 = (int)(item.n0 + rank * (item.bn >> 1));
+                const uint32_t tx = 2u * (S::A_BYTES + (item.bn >> 1) * BK * 2);
+                for (uint32_t kb = 0; kb < p.kblocks; ++kb, ++it) {
+                    const uint32_t s = it % QSTAGES, use = it / QSTAGES;
+                    if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1, s_abort, p.status)) { ok = false; break; }
+                    const uint32_t st = base + s * S::STAGE;
+                    const int k0 = (int)(kb * BK);
+                    if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, tx);
+                    const uint32_t leader_bar = map_to_cta(bar_full + 8 * s, 0);
+                    tma_load_2d_pair(st, &map_a, k0, m0, leader_bar);
+                    tma_load_2d_pair(st + S::A_BYTES, &map_b, n0, k0, leader_bar);
+                    if (item.bn == 256) tma_load_2d_pair(st + S::A_BYTES + BK * 128, &map_b, n0 + 64, k0, leader_bar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t fmt = F16 ? 0u : 1u;
+            // D = f32, A = B = bf16 / f16, A K-major, B N-major, N = 256 (128 for a tail half), M = 256 (128 rows in each CTA)
+            const uint32_t idesc_base = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(256 >> 4) << 24);
+            uint32_t it = 0, t = 0;
+            bool ok = true;
+            for (uint32_t w = pair; w < p.n_items && ok; w += npairs, ++t) {
+                const uint32_t idesc = idesc_base | ((pair_item(p, w, tiles_n).bn >> 3) << 17);
+                const uint32_t buf = t & 1u, use = t >> 1;
+                if (use > 0 && !mbar_wait(bar_acc_empty + 8 * buf, (use - 1) & 1, s_abort, p.status)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + buf * 256u;
+                for (uint32_t kb = 0; kb < p.kblocks; ++kb, ++it) {
+                    const uint32_t s = it % QSTAGES;
+                    if (!mbar_wait(bar_full + 8 * s, (it / QSTAGES) & 1, s_abort, p.status)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = base + s * S::STAGE, b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+                    for (int j = 0; j < BK / 16; ++j) {
+                        const uint64_t da = smem_desc(a_addr + j * 32, 16, 1024);
+                        const uint64_t db = smem_desc(b_addr + j * 2048, BK * 128, 1024);
+                        umma_bf16_pair(tmem_d, da, db, idesc, (kb | (uint32_t)j) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_pair(bar_empty + 8 * s);
+                }
+                if (ok) umma_commit_pair(bar_acc_full + 8 * buf);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps (both CTAs; TMEM lane quarter = warp % 4) ----------------
+        const uint32_t quarter = warp & 3u;
+        if (warp == 2 && lane == 0 && (*reinterpret_cast<volatile uint32_t*>(p.status) & 4u)) *s_abort = 1;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const uint32_t leader_acc_empty = map_to_cta(bar_acc_empty, 0);
+        uint32_t t = 0;
+        for (uint32_t w = pair; w < p.n_items; w += npairs, ++t) {
+            const uint32_t buf = t & 1u, use = t >> 1;
+            const PairItem item = pair_item(p, w, tiles_n);
+            const uint32_t m0 = item.m_tile * 256 + rank * 128, n0 = item.n0;
+            const uint32_t row = m0 + quarter * 32 + lane;
+            const bool got = mbar_wait(bar_acc_full + 8 * buf, use & 1, s_abort, p.status);
+            if (!got || *s_abort) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem_d = tmem_base + buf * 256u + ((quarter * 32u) << 16);
+#pragma unroll 1
+            for (int c = 0; c < (int)(item.bn / 32); ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_d + (uint32_t)(c * 32), v);
+                const uint32_t col0 = n0 + c * 32;
+                if (row < p.m && col0 < p.n) {
+                    uint32_t si = 0;
+                    while (si + 1 < p.nseg && col0 >= p.seg[si].col_end) ++si;
+                    const GemmSeg sg = p.seg[si];
+                    const uint64_t idx0 = (uint64_t)row * (sg.col_end - sg.col_begin) + (col0 - sg.col_begin);
+                    uint16_t* dst = sg.out + idx0;
+                    if (col0 + 32 <= sg.col_end && ((uintptr_t)dst & 15u) == 0) {
+                        uint32_t w[16];
+#pragma unroll
+                        for (int x = 0; x < 16; ++x) {
+                            const uint16_t lo = epilogue_elem<F16>(__uint_as_float(v[2 * x]), sg.table, sg.residual, idx0 + 2 * x);
+                            const uint16_t hi = epilogue_elem<F16>(__uint_as_float(v[2 * x + 1]), sg.table, sg.residual, idx0 + 2 * x + 1);
+                            w[x] = (uint32_t)lo | ((uint32_t)hi << 16);
+                        }
+#pragma unroll
+                        for (int x = 0; x < 4; ++x)
+                            reinterpret_cast<uint4*>(dst)[x] = make_uint4(w[4 * x], w[4 * x + 1], w[4 * x + 2], w[4 * x + 3]);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 32; ++x)
+                            if (col0 + x < sg.col_end) dst[x] = epilogue_elem<F16>(__uint_as_float(v[x]), sg.table, sg.residual, idx0 + x);
+                    }
+                }
+            }
+            // this half of both CTAs' TMEM may be overwritten once all eight epilogue warps of the pair have read it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(leader_acc_empty + 8 * buf) : "memory");
+        }
+    }
+    // Nobody frees TMEM or leaves (and gives up the shared memory the pair's MMAs and barriers live in) before
+    // both CTAs are through.
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
 // Shapes the tensor-core path cannot take (row pitches that are not 16-byte multiples,
 // unaligned bases), tiny problems and every f32 product: one thread per output cell running the
 // reference's own per-cell recurrence, an ascending-k fused multiply-add chain (mul-then-add in
@@ -691,6 +1089,96 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     }
     const uint32_t kblocks = (k + BK - 1) / BK, mtiles = (m + BM - 1) / BM;
     const uint32_t slots = 2u * (uint32_t)ctx->sm_count;
+    // Compute-bound shapes (at least one 128 x 256 tile per SM): the persistent kernel.
+    {
+        const uint32_t ptiles = mtiles * ((n + PBN - 1) / PBN);
+        bool persistent = mtiles >= 2 && ptiles >= (uint32_t)ctx->sm_count && !gated && !(segs[0].all_reduce && ctx->tp_world > 1);
+        if (const char* e = getenv("HOLO_GEMM_PERSISTENT")) persistent = persistent && atoi(e) != 0;
+        // 256 x 256 tiles on CTA pairs when there is at least one per pair of SMs
+        const uint32_t qtiles = ((m + 255) / 256) * ((n + 255) / 256), pairs = (uint32_t)ctx->sm_count / 2;
+        bool paired = persistent && qtiles >= pairs;
+        if (const char* e = getenv("HOLO_GEMM_PAIR")) paired = paired && atoi(e) != 0;
+        if (paired) {
+            GemmParams p;
+            memset(&p, 0, sizeof p);
+            for (uint32_t i = 0; i < MAX_SEGS; ++i) p.seg[i] = gs[i];
+            p.nseg = nseg;
+            p.status = ctx->dev_status;
+            p.m = m; p.n = n; p.k = k; p.kblocks = kblocks; p.splits = 1;
+            p.box_m = BM;
+            p.dtype = dtype;
+            CUtensorMap ma, mb;
+            HOLO_TRY(make_map_2d(&ma, a, k, m, BK, BM));
+            HOLO_TRY(make_map_2d(&mb, b, n, k, 64, BK));
+            static thread_local int configured_pair[2] = {-1, -1};
+            static thread_local int resident_pairs[2] = {0, 0};
+            const int which = dtype == HOLO_DTYPE_F16 ? 1 : 0;
+            if (configured_pair[which] != ctx->device) {
+                if (which) HOLO_CUDA(cudaFuncSetAttribute(matmul_umma_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL));
+                else HOLO_CUDA(cudaFuncSetAttribute(matmul_umma_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL));
+                // how many pairs the chip can hold at once (a GPC with an odd number of SMs leaves one unpaired)
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(2 * pairs, 1, 1);
+                cfg.blockDim = dim3(GEMM_THREADS);
+                cfg.dynamicSmemBytes = PairSmem::TOTAL;
+                cudaLaunchAttribute at;
+                at.id = cudaLaunchAttributeClusterDimension;
+                at.val.clusterDim.x = 2;
+                at.val.clusterDim.y = 1;
+                at.val.clusterDim.z = 1;
+                cfg.attrs = &at;
+                cfg.numAttrs = 1;
+                int nclusters = 0;
+                cudaError_t oe = which ? cudaOccupancyMaxActiveClusters(&nclusters, matmul_umma_pair_kernel<true>, &cfg)
+                                       : cudaOccupancyMaxActiveClusters(&nclusters, matmul_umma_pair_kernel<false>, &cfg);
+                if (oe != cudaSuccess || nclusters <= 0) {
+                    cudaGetLastError();
+                    nclusters = (int)pairs;
+                }
+                resident_pairs[which] = nclusters;
+                configured_pair[which] = ctx->device;
+            }
+            uint32_t grid = qtiles < pairs ? qtiles : pairs;
+            if (grid > (uint32_t)resident_pairs[which]) grid = (uint32_t)resident_pairs[which];
+            if (const char* e = getenv("HOLO_GEMM_PAIR_GRID")) grid = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : grid;
+            // The last, partial round: when its tiles cut in two still fit one round, run them as 256 x 128 halves
+            // (every pair busy for half a tile's time instead of some pairs for a whole one). Same k order per cell.
+            const uint32_t rest = qtiles % grid;
+            const bool split_tail = rest != 0 && 2 * rest <= grid && !getenv("HOLO_GEMM_NO_TAIL_SPLIT");
+            p.tail_begin = split_tail ? qtiles - rest : qtiles;
+            p.n_items = split_tail ? qtiles + rest : qtiles;
+            // the two CTAs of a pair are a cluster along grid x
+            if (which) HOLO_CUDA(holo_launch_kernel_cluster(ctx, matmul_umma_pair_kernel<true>, dim3(2 * grid), dim3(GEMM_THREADS), PairSmem::TOTAL, 2u, 1u, ma, mb, p));
+            else HOLO_CUDA(holo_launch_kernel_cluster(ctx, matmul_umma_pair_kernel<false>, dim3(2 * grid), dim3(GEMM_THREADS), PairSmem::TOTAL, 2u, 1u, ma, mb, p));
+            ctx->launches++;
+            return HOLO_OK;
+        }
+        if (persistent) {
+            GemmParams p;
+            memset(&p, 0, sizeof p);
+            for (uint32_t i = 0; i < MAX_SEGS; ++i) p.seg[i] = gs[i];
+            p.nseg = nseg;
+            p.status = ctx->dev_status;
+            p.m = m; p.n = n; p.k = k; p.kblocks = kblocks; p.splits = 1;
+            p.box_m = BM;
+            p.dtype = dtype;
+            CUtensorMap ma, mb;
+            HOLO_TRY(make_map_2d(&ma, a, k, m, BK, BM));
+            HOLO_TRY(make_map_2d(&mb, b, n, k, 64, BK));
+            const uint32_t grid = ptiles < (uint32_t)ctx->sm_count ? ptiles : (uint32_t)ctx->sm_count;
+            static thread_local int configured_device[2] = {-1, -1};
+            const int which = dtype == HOLO_DTYPE_F16 ? 1 : 0;
+            if (configured_device[which] != ctx->device) {
+                if (which) HOLO_CUDA(cudaFuncSetAttribute(matmul_umma_persistent_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PersistSmem::TOTAL));
+                else HOLO_CUDA(cudaFuncSetAttribute(matmul_umma_persistent_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PersistSmem::TOTAL));
+                configured_device[which] = ctx->device;
+            }
+            if (which) HOLO_CUDA(holo_launch_kernel(ctx, matmul_umma_persistent_kernel<true>, dim3(grid), dim3(GEMM_THREADS), PersistSmem::TOTAL, 1, ma, mb, p));
+            else HOLO_CUDA(holo_launch_kernel(ctx, matmul_umma_persistent_kernel<false>, dim3(grid), dim3(GEMM_THREADS), PersistSmem::TOTAL, 1, ma, mb, p));
+            ctx->launches++;
+            return HOLO_OK;
+        }
+    }
     // Tile width and K split. Compute-bound shapes (many tiles) take 128-wide tiles and no
     // split. HBM-bound skinny shapes want 128..slots co-resident CTAs sharing the memory
     // system: narrow tiles first, then a K split whose f32 partials stay small.

@@ -588,8 +588,8 @@ int32_t holo_b200_decode_attention_q8_static_status(void* cuda_stream);
  * under the boundary form (derive_label_boundary, address.rs:197-221). An output that has no derivable
  * label (it depends on a value the labels do not see, e.g. a tensor-parallel sum) is labelled by its bytes
  * (the only place a result is read back and hashed).
- * An input label that is not resident in the pool is taken from the bytes the caller wrote to the
- * port's slot (a device-to-device copy into the pool). */
+ * Every input label must be resident (interned since the last walk, returned by the last walk, leased or
+ * pinned); otherwise the call is refused before any state changes (session.rs:959-971). */
 #define HOLO_SESSION_VERIFY 1
 #define HOLO_SESSION_ADDRESSED 2
 /* The operand list the reference derives a norm's label from is x, gamma, beta (kernel_call.rs:1612-1616),

@@ -52,9 +52,10 @@ def test_subgraph_reuse_memo_and_bounded_pool(backend):
     x, z1, z2 = (synth_bf16(m * k, 1.0, s) for s in (10, 11, 12))
 
     def run(x, z):
-        sess.write("x", x)
-        sess.write("z", z)
-        labels, st = sess.execute_addressed([hs.label_bytes(x), hs.label_bytes(z)])
+        # inputs enter by label: intern_input hashes the bytes once and stores them in the pool (session.rs:1018-1022)
+        lx, lz = sess.intern_input(x), sess.intern_input(z)
+        assert (lx, lz) == (hs.label_bytes(x), hs.label_bytes(z))
+        labels, st = sess.execute_addressed([lx, lz])
         return labels, st, sess.read("out", np.uint16).copy()
 
     l1, s1, o1 = run(x, z1)
@@ -97,9 +98,12 @@ def test_decoder_step_addressed_equals_plain(backend):
     vals = step_inputs(cfg, info, 100, 100, seed=5)
     for name, arr in vals.items():
         plain.write(name, arr)
-        addr.write(name, arr)
     plain.execute()
-    labels, st = addr.execute_addressed([hs.label_bytes(vals[p.name]) for p in addr.inputs])
+    # a label that was never interned is refused before anything changes (session.rs:959-971)
+    with pytest.raises(hb.BackendError) as e:
+        addr.execute_addressed([hs.label_bytes(vals[p.name]) for p in addr.inputs])
+    assert e.value.variant == "ShapeMismatch" and "not resident" in str(e.value)
+    labels, st = addr.execute_addressed([addr.intern_input(vals[p.name]) for p in addr.inputs])
     # every call ran; the four KvCacheWrite calls as in-place moves of their (uniquely owned) cache buffers
     assert st.memo_hit == 0 and st.dispatched + st.moved == addr.n_calls and st.moved == 4 * cfg.n_layers
     assert np.array_equal(addr.read("logits", np.uint16), plain.read("logits", np.uint16))
@@ -111,12 +115,11 @@ def test_decoder_step_addressed_equals_plain(backend):
     assert st2.memo_hit == 1 and labels2 == labels
     assert np.array_equal(addr.read("logits", np.uint16), plain.read("logits", np.uint16))
     # a new position only: the embedding / norm / projections of the same tokens are reused
+    # (the caches of the first step were moved into its outputs: their labels are gone, the values are interned again)
     vals2 = dict(vals)
     vals2["pos"] = np.array([101], dtype=np.int32)
-    for name, arr in vals2.items():
-        addr.write(name, arr)
-    _, st3 = addr.execute_addressed([hs.label_bytes(vals2[p.name]) for p in addr.inputs])
-    assert st3.memo_hit == 0 and st3.skipped > 0 and st3.dispatched < addr.n_calls
+    _, st3 = addr.execute_addressed([addr.intern_input(vals2[p.name]) for p in addr.inputs])
+    assert st3.memo_hit == 0 and st3.skipped > st3.moved and st3.dispatched + st3.moved < addr.n_calls
     plain.close()
     addr.close()
 
@@ -223,7 +226,8 @@ def test_decode_loop_by_labels_keeps_pool_bytes_constant(backend):
         v = step_inputs(cfg, info, 100 + step, 100 + step, seed=5)
         for name in ("pos", "valid_len", "cos_q", "sin_q", "cos_k", "sin_k"):
             plain.write(name, v[name])
-            labels[name] = addr.intern_input(v[name])
+        for name in ("token_ids", "pos", "valid_len", "cos_q", "sin_q", "cos_k", "sin_k"):
+            labels[name] = addr.intern_input(v[name])     # interning again keeps an unchanged value live (it promotes the label)
         plain.execute()
         outs, st = addr.execute_addressed([labels[p.name] for p in addr.inputs])
         assert st.moved == 4 * cfg.n_layers and st.memo_hit == 0

@@ -419,3 +419,38 @@ def test_mask_form_restatement_equals_scalar_form_bitwise():
     mask = np.full((1, past + 1), -np.inf, np.float32)
     z = orc.decode_attention_mask(*arrs, mask, b, h, kv, 1, past, 1, d, 0, kc.DTYPE_F32)
     assert not np.any(z)
+
+
+def test_kn_dequant_matmul_restatement_against_the_naive_loop():
+    # crates/hologram-compute/src/cpu/simd.rs:7175-7204 (matmul_i8_per_channel_matches_naive): the fused per-channel kernel
+    # within 1e-4 (relative, floor 1) of the naive multiply-add loop with the scale applied at the end, on the
+    # reference's four shapes and value laws
+    for m, k, n in ((1, 64, 48), (3, 17, 33), (5, 9, 16), (1, 2048, 64)):
+        a = (((np.arange(m * k) % 13).astype(np.float32)) - np.float32(6.0)) * np.float32(0.1)
+        bq = ((np.arange(k * n, dtype=np.int64) % 255) - 127).astype(np.int8)
+        scales = np.float32(0.01) + np.arange(n, dtype=np.float32) * np.float32(0.001)
+        got = orc.matmul_dequant_kn(a, bq, m, k, n, kc.DTYPE_I8, scales, np.zeros(n, dtype=np.int32), channels=n, inner=1)
+        want = (a.reshape(m, k).astype(np.float64) @ bq.reshape(k, n).astype(np.float64)) * scales.astype(np.float64)
+        err = np.abs(got.reshape(m, n) - want) / np.maximum(np.abs(want), 1.0)
+        assert err.max() < 1e-4
+    # the two definitions factor the scale differently: with nonzero zero points the weight is dequantized first
+    rng = np.random.default_rng(0)
+    m, k, n = 2, 64, 16
+    a = rng.standard_normal(m * k).astype(np.float32)
+    bq = rng.integers(-127, 128, size=k * n, dtype=np.int8)
+    sc = (rng.random(n, dtype=np.float32) * np.float32(0.02) + np.float32(0.001)).astype(np.float32)
+    zp = rng.integers(-3, 4, size=n, dtype=np.int32)
+    got = orc.matmul_dequant_kn(a, bq, m, k, n, kc.DTYPE_I8, sc, zp, channels=n, inner=1)
+    deq = ((bq.reshape(k, n).astype(np.int32) - zp[None, :]).astype(np.float32) * sc[None, :]).astype(np.float32)
+    assert np.array_equal(got.view(np.uint32), orc.matmul(a, deq.reshape(-1), m, k, n, kc.DTYPE_F32).view(np.uint32))
+
+
+def test_matmul_add_activation_restatement_is_the_unfused_f32_triple():
+    # session.rs:2220-2226: for f32 the triple is bit-identical to the three separate calls (no narrowing to skip)
+    rng = np.random.default_rng(5)
+    m, k, n = 4, 40, 24
+    a, b, r = (rng.standard_normal(c, dtype=np.float32) for c in (m * k, k * n, m * n))
+    got = orc.matmul_add_activation(a, b, r, m, k, n, kc.DTYPE_F32, kc.FUSED_GELU)
+    s = orc.matmul(a, b, m, k, n, kc.DTYPE_F32) + r
+    want = np.array([orc.lib.holo_or_act(kc.LUT_GELU, float(v)) for v in s], dtype=np.float32)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))

@@ -73,7 +73,7 @@ def test_epilogue_and_refusals(backend):
     for i in range(5):
         ws.alloc(i, 1 << 16)
     base = [kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), 1, 64, 16, 16, 1, I8, F32, 0, 0]
-    for tail in ([1, 0, 0, kc.NONE], [0, 1, 0, kc.NONE], [0, 0, 0, kc.NONE]):          # unpaired omajor / W8A8; the [k,n] W8A32 form
+    for tail in ([1, 0, 0, kc.NONE], [0, 1, 0, kc.NONE]):          # unpaired omajor / W8A8 (the [k,n] form with f32 activations is served)
         with pytest.raises(hb.BackendError) as e:
             backend.dispatch(kc.KernelCall.MatMulDequant(kc.MatMulDequantCall(*base, *tail)), ws)
         assert e.value.variant == "UnsupportedOp"
@@ -136,3 +136,71 @@ def test_e8_codebook_reference_golden_and_bit_exactness(backend):
         with pytest.raises(hb.BackendError) as e:
             run(backend, np.ones(64, np.float32), np.zeros(64, np.uint8), np.ones(2, np.float32), 1, 64, 2, **kwargs)
         assert e.value.variant == "UnsupportedOp"
+
+
+def run_kn(backend, a, bq, m, k, n, quant, scales=None, zero_points=None, channels=0, inner=1, scale=1.0, zero_point=0, residual=None, act=0):
+    """MatMulDequant over a [k, n] weight with f32 activations (wire 111, or 116 when an epilogue is bound)."""
+    ws = hb.DeviceWorkspace(backend, 6)
+    ws.put(0, a)
+    ws.put(1, bq)
+    sc, zp, res = kc.NONE, kc.NONE, kc.NONE
+    if scales is not None:
+        ws.put(2, scales)
+        ws.put(3, zero_points)
+        sc, zp = kc.rb(2), kc.rb(3)
+    if residual is not None:
+        ws.put(5, residual)
+        res = kc.rb(5)
+    ws.alloc(4, m * n * 4)
+    sb = int(np.float32(scale).view(np.uint32))
+    call = kc.MatMulDequantCall(kc.rb(0), kc.rb(1), sc, zp, kc.rb(4), m, k, n, channels, inner, quant, F32, sb, zero_point, 0, 0, act, res)
+    backend.dispatch(kc.KernelCall.MatMulDequant(call), ws)
+    out = ws.read(4, m * n * 4, np.float32).copy()
+    ws.close()
+    return out
+
+
+LUT_OF_FUSED = {kc.FUSED_GELU: kc.LUT_GELU, kc.FUSED_SILU: kc.LUT_SILU, kc.FUSED_TANH: kc.LUT_TANH}
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 64, 48), (3, 17, 33), (5, 9, 16), (1, 2048, 64), (2, 4096, 1000), (4, 128, 24), (1, 4096, 14336)])
+def test_kn_form_per_channel_i8_is_bit_exact(backend, m, k, n):
+    # m <= 3 with every zero point 0 takes the integer-level chain with the scale applied once (cpu/simd.rs:3480-3570);
+    # m > 3, or a nonzero zero point, dequantizes first (cpu/float_kernels.rs:640-731): different bits, the reference's choice
+    rng = np.random.default_rng(m * 131 + n)
+    a = rng.standard_normal(m * k).astype(np.float32)
+    bq = rng.integers(-127, 128, size=k * n, dtype=np.int8)
+    scales = (rng.random(n, dtype=np.float32) * np.float32(0.02) + np.float32(0.001)).astype(np.float32)
+    for zps in (np.zeros(n, dtype=np.int32), rng.integers(-3, 4, size=n, dtype=np.int32)):
+        got = run_kn(backend, a, bq, m, k, n, I8, scales, zps, channels=n, inner=1)
+        want = orc.matmul_dequant_kn(a, bq, m, k, n, I8, scales, zps, channels=n, inner=1)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_kn_form_tiers_layouts_and_epilogue(backend):
+    rng = np.random.default_rng(17)
+    m, k, n = 3, 96, 40
+    a = rng.standard_normal(m * k).astype(np.float32)
+    res = rng.standard_normal(m * n).astype(np.float32)
+    # per-tensor u8 with a zero point, and a fused residual + activation (wire 116 with bq_omajor = act_quant = 0)
+    bq = rng.integers(0, 256, size=k * n, dtype=np.uint8)
+    got = run_kn(backend, a, bq, m, k, n, kc.DTYPE_U8, scale=0.0123, zero_point=131, residual=res, act=kc.FUSED_SILU)
+    want = orc.matmul_dequant_kn(a, bq, m, k, n, kc.DTYPE_U8, scale=0.0123, zero_point=131, residual=res, act=LUT_OF_FUSED[kc.FUSED_SILU])
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # packed i4 (two nibbles per byte, low first, index kk * n + j), per-channel along k (channels = k, inner = n)
+    bq4 = rng.integers(0, 256, size=k * n // 2, dtype=np.uint8)
+    sc = (rng.random(k, dtype=np.float32) * np.float32(0.1) + np.float32(0.01)).astype(np.float32)
+    zp = rng.integers(-2, 3, size=k, dtype=np.int32)
+    got = run_kn(backend, a, bq4, m, k, n, kc.DTYPE_I4, sc, zp, channels=k, inner=n, act=kc.FUSED_TANH)
+    want = orc.matmul_dequant_kn(a, bq4, m, k, n, kc.DTYPE_I4, sc, zp, channels=k, inner=n, act=LUT_OF_FUSED[kc.FUSED_TANH])
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # an output-major weight must never be read with the [k, n] interpretation, and W8A8 has one emitter
+    ws = hb.DeviceWorkspace(backend, 5)
+    for i in range(5):
+        ws.alloc(i, 1 << 16)
+    for omajor, act_quant in ((1, 0), (0, 1)):
+        call = kc.MatMulDequantCall(kc.rb(0), kc.rb(1), kc.rb(2), kc.rb(3), kc.rb(4), 1, 64, 16, 16, 1, I8, F32, 0, 0, omajor, act_quant, 0, kc.NONE)
+        with pytest.raises(hb.BackendError) as e:
+            backend.dispatch(kc.KernelCall.MatMulDequant(call), ws)
+        assert e.value.variant == "UnsupportedOp" and "paired" in str(e.value)
+    ws.close()
