@@ -204,6 +204,7 @@ extern "C" int32_t holo_b200_workspace_bind(holo_b200_workspace* ws, uint32_t sl
     s.ptr = device_ptr;
     s.bytes = bytes;
     s.owned = false;
+    s.constant = false;
     return HOLO_OK;
 }
 
@@ -356,7 +357,8 @@ int32_t do_matmul(holo_b200_ctx* ctx, const HoloMatMulCall& c, uint8_t act, cons
         HOLO_TRY(holo_resolve(ws, *residual, ob, &res, nullptr));
         HOLO_TRY(check_disjoint({out, ob}, c.output.slot, {{res, ob}}));
     }
-    return holo_launch_matmul(ctx, a, b, out, c.m, c.k, c.n, c.dtype, act, res);
+    const bool b_constant = c.b.slot < ws->slots.size() && ws->slots[c.b.slot].constant;
+    return holo_launch_matmul(ctx, a, b, out, c.m, c.k, c.n, c.dtype, act, res, b_constant);
 }
 
 // matmul_add_activation_float (cpu/float_kernels.rs:899-938): act(A . B + residual), served on the exact per-cell kernel

@@ -12,6 +12,9 @@ struct HoloSlot {
     void* ptr = nullptr;
     uint64_t bytes = 0;
     bool owned = false;
+    // a session's weight that none of its calls writes (set at load, cleared by a rebind): kernels may read it
+    // without waiting for the launch before them
+    bool constant = false;
 };
 
 // One small op of a batched launch (see micro_batch_kernel).
@@ -225,7 +228,7 @@ struct HoloAttnArgs {
 int32_t holo_launch_decode_attention(holo_b200_ctx* ctx, const HoloAttnArgs& a);
 // gemm.cu
 int32_t holo_launch_matmul(holo_b200_ctx* ctx, const void* a, const void* b, void* out, uint32_t m, uint32_t k,
-                           uint32_t n, uint8_t dtype, uint8_t fused_act, const void* residual);
+                           uint32_t n, uint8_t dtype, uint8_t fused_act, const void* residual, bool b_constant = false);
 // One column segment of a merged matmul: `width` columns of the product go to `out`
 // ([m, width] row-major) through their own epilogue.
 struct HoloMatmulSeg {
@@ -241,7 +244,21 @@ struct HoloMatmulSeg {
     // narrow(A . B)) (+ residual), the exchange done by the matmul's own epilogue over peer memory
     // when the group has the peer-memory transport, by a following all-reduce launch otherwise
     uint8_t all_reduce = 0;
+    // Work on the stored [m, width] values by heads of 128 columns, done by the product's own epilogue in place
+    // of the calls that would read `out`: 1 = RotaryEmbedding (head_dim 128; cos / sin laid out like out) into
+    // rope_out; 2 = that, then QuantizeRowsI8 of the rotated rows (one row per head) into codes / scales;
+    // 3 = QuantizeRowsI8 of the stored rows. `out` is still written. See holo_matmul_head_ops_ok.
+    uint8_t head_op = 0;
+    // 1 (first segment speaks for the product): B is a constant weight that no launch of the stream writes, so
+    // the kernel may request its first tiles before it waits for the previous kernel
+    uint8_t b_constant = 0;
+    const void* cos = nullptr;
+    const void* sin = nullptr;
+    void* rope_out = nullptr;
+    int8_t* codes = nullptr;
+    float* scales = nullptr;
 };
+bool holo_matmul_head_ops_ok(uint32_t m, uint32_t k, uint32_t n, uint8_t dtype, const HoloMatmulSeg* segs, uint32_t nseg);
 // act(A . B + residual) on the exact per-cell kernel (MatMulAddActivation)
 int32_t holo_launch_matmul_add_activation(holo_b200_ctx* ctx, const void* a, const void* b, void* out, uint32_t m, uint32_t k, uint32_t n,
                                           uint8_t dtype, uint8_t fused_act, const void* residual);

@@ -40,6 +40,12 @@ struct GemmSeg {
     const uint16_t* table;    // 65536-entry LUT of the fused activation or null
     const uint16_t* residual; // bf16 [m, width] or null
     uint32_t col_begin, col_end;
+    // per-head work on the stored values (heads of 128 columns, one tile each; see HoloMatmulSeg::head_op)
+    uint32_t head_op;
+    const uint16_t *cos, *sin;
+    uint16_t* rope_out;
+    int8_t* codes;
+    float* scales;
 };
 constexpr int MAX_SEGS = 3;
 
@@ -50,6 +56,8 @@ struct GemmParams {
     uint32_t m, n, k, kblocks, splits, box_m;
     int dtype;                // HOLO_DTYPE_BF16 or HOLO_DTYPE_F16 (operands and output)
     uint32_t gated;           // see HoloMatmulSeg::gated (BN = 128: columns 0..63 of a tile are gate, 64..127 up)
+    uint32_t head_ops;        // some segment has a head_op (BN = 128, K split inside a cluster)
+    uint32_t b_constant;      // B is a weight no kernel of the stream writes: its first tiles may be requested before the dependency wait
     // tensor-parallel sum inside the epilogue (ar_world > 1): every rank's mailbox, the local epoch /
     // ticket words, this rank
     uint8_t* ar_mailbox[8];
@@ -229,25 +237,48 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *s_tmem;
+    // A constant B (a weight nothing in the stream rewrites) does not depend on the previous kernel: the first
+    // ring-full of its tiles is requested before the wait, so those bytes are on their way (or already here)
+    // when A becomes readable. Each stage's barrier expects the A bytes too and completes only with them.
+    const uint32_t pre = p.b_constant ? min(nkb, (uint32_t)STAGES) : 0u;
+    if (warp == 0 && lane == 0) {
+        const uint32_t tx = p.box_m * BK * 2 + S::B_BYTES;
+        for (uint32_t i = 0; i < pre; ++i) {
+            const uint32_t st = base + i * S::STAGE;
+            const int k0 = (int)((kb_begin + i) * BK);
+            mbar_arrive_expect_tx(bar_full + 8 * i, tx);
+#pragma unroll
+            for (int h = 0; h < BN / 64; ++h)
+                tma_load_2d(st + S::A_BYTES + h * (BK * 128), &map_b, (int)(n0 + 64 * h), k0, bar_full + 8 * i);
+        }
+    }
     holo_pdl_wait();  // barriers and TMEM were set up while the previous kernel drained
     const uint32_t ar_epoch = (AR && p.ar_world > 1) ? *reinterpret_cast<volatile uint32_t*>(p.ar_state) + 1 : 0;
     const uint64_t ar_units = ((uint64_t)p.m * p.n) >> 2;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (lane == 0 && !*s_abort) {
+        if (lane == 0) {
             const uint32_t tx = p.box_m * BK * 2 + S::B_BYTES;
-            for (uint32_t i = 0; i < nkb; ++i) {
+            // after an abort nothing new is requested, but the stages whose B tiles are already in flight still get
+            // their A tiles: their barriers then complete and the loop below sees the copies land before the CTA ends
+            const uint32_t todo = *s_abort ? pre : nkb;
+            for (uint32_t i = 0; i < todo; ++i) {
                 const uint32_t s = i % STAGES, use = i / STAGES;
                 if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1, s_abort, p.status)) break;
                 const uint32_t st = base + s * S::STAGE;
                 const int k0 = (int)((kb_begin + i) * BK);
-                mbar_arrive_expect_tx(bar_full + 8 * s, tx);
+                if (i >= pre) mbar_arrive_expect_tx(bar_full + 8 * s, tx);
                 tma_load_2d(st, &map_a, k0, (int)m0, bar_full + 8 * s);
+                if (i >= pre) {
 #pragma unroll
-                for (int h = 0; h < BN / 64; ++h)
-                    tma_load_2d(st + S::A_BYTES + h * (BK * 128), &map_b, (int)(n0 + 64 * h), k0, bar_full + 8 * s);
+                    for (int h = 0; h < BN / 64; ++h)
+                        tma_load_2d(st + S::A_BYTES + h * (BK * 128), &map_b, (int)(n0 + 64 * h), k0, bar_full + 8 * s);
+                }
             }
+            if (*s_abort)
+                for (uint32_t i = 0; i < pre; ++i)
+                    for (uint32_t it = 0; it < WAIT_LIMIT && !mbar_try_wait(bar_full + 8 * i, 0); ++it) __nanosleep(64);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
@@ -439,6 +470,83 @@ matmul_bf16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         const uint16_t h2 = gated_elem<F16>(acc[0].z, acc[1].z, p.seg[0].table), h3 = gated_elem<F16>(acc[0].w, acc[1].w, p.seg[0].table);
                         *reinterpret_cast<uint2*>(p.seg[0].out + (uint64_t)grow * half_n + col) =
                             make_uint2((uint32_t)h0 | ((uint32_t)h1 << 16), (uint32_t)h2 | ((uint32_t)h3 << 16));
+                    }
+                }
+            } else if (BN == 128 && p.head_ops) {
+                // One tile is one 128-wide head of one segment, and a warp holds a whole row of it (lane u: columns
+                // 4u .. 4u+3). After the product is stored, the same warp rotates the stored values (rotate-half
+                // RoPE: column j pairs with j +- 64, i.e. lane u with lane u ^ 16) and / or quantizes the row to i8
+                // codes with one f32 scale: the arithmetic of the RotaryEmbedding and QuantizeRowsI8 calls on the
+                // values the matmul stored, without their launches.
+                constexpr int dt = F16 ? HOLO_DTYPE_F16 : HOLO_DTYPE_BF16;
+                uint32_t si = 0;
+                while (si + 1 < p.nseg && n0 >= p.seg[si].col_end) ++si;
+                const GemmSeg sg = p.seg[si];
+                const uint32_t width = sg.col_end - sg.col_begin, colseg = n0 - sg.col_begin + lane * 4;
+                for (uint32_t rl = rank + S_ * ew; rl < rows_valid; rl += S_ * 4) {
+                    const uint32_t off = rl * (BN * 4) + ((lane ^ (rl & 7u)) * 16);
+                    float4 part[8];
+#pragma unroll
+                    for (uint32_t sidx = 0; sidx < 8; ++sidx) {
+                        part[sidx] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (sidx < S_)
+                            asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(part[sidx].x), "=f"(part[sidx].y), "=f"(part[sidx].z), "=f"(part[sidx].w)
+                                         : "r"(remote[sidx] + off));
+                    }
+                    float4 acc = part[0];
+#pragma unroll
+                    for (uint32_t sidx = 1; sidx < 8; ++sidx)
+                        if (sidx < S_) { acc.x += part[sidx].x; acc.y += part[sidx].y; acc.z += part[sidx].z; acc.w += part[sidx].w; }
+                    const uint64_t grow = m0 + rl, idx = grow * width + colseg;
+                    const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+                    uint16_t h[4];
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) h[x] = epilogue_elem<F16>(a4[x], sg.table, sg.residual, idx + x);
+                    *reinterpret_cast<uint2*>(sg.out + idx) = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+                    if (sg.head_op == 0) continue;
+                    float v[4];
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) v[x] = holo::widen16(h[x], dt);
+                    if (sg.head_op != 3) {
+                        const uint2 cw = *reinterpret_cast<const uint2*>(sg.cos + idx), sw = *reinterpret_cast<const uint2*>(sg.sin + idx);
+                        const uint16_t c16[4] = {(uint16_t)(cw.x & 0xffffu), (uint16_t)(cw.x >> 16), (uint16_t)(cw.y & 0xffffu), (uint16_t)(cw.y >> 16)};
+                        const uint16_t s16[4] = {(uint16_t)(sw.x & 0xffffu), (uint16_t)(sw.x >> 16), (uint16_t)(sw.y & 0xffffu), (uint16_t)(sw.y >> 16)};
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            const float other = __shfl_xor_sync(0xffffffffu, v[x], 16);
+                            const float xc = __fmul_rn(v[x], holo::widen16(c16[x], dt)), os = __fmul_rn(other, holo::widen16(s16[x], dt));
+                            h[x] = holo::narrow16(lane < 16 ? __fsub_rn(xc, os) : __fadd_rn(xc, os), dt);
+                        }
+                        *reinterpret_cast<uint2*>(sg.rope_out + idx) = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) v[x] = holo::widen16(h[x], dt);   // what the store kept
+                    }
+                    if (sg.head_op >= 2) {
+                        float amax = 0.0f;
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            const float av = v[x] < 0.0f ? -v[x] : v[x];
+                            if (av > amax) amax = av;
+                        }
+                        for (int o = 16; o > 0; o >>= 1) {
+                            const float other = __shfl_xor_sync(0xffffffffu, amax, o);
+                            if (other > amax) amax = other;
+                        }
+                        const bool zero = amax == 0.0f;
+                        const float inv = zero ? 0.0f : __fdiv_rn(127.0f, amax);
+                        uint32_t packed = 0;
+                        if (!zero) {
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) {
+                                const float t = __fmul_rn(v[x], inv);
+                                int r = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
+                                r = max(-127, min(127, r));
+                                packed |= ((uint32_t)r & 0xffu) << (8 * x);
+                            }
+                        }
+                        *reinterpret_cast<uint32_t*>(sg.codes + idx) = packed;
+                        if (lane == 0) sg.scales[idx >> 7] = zero ? 0.0f : __fdiv_rn(amax, 127.0f);
                     }
                 }
             } else
@@ -1025,8 +1133,9 @@ static int32_t act_table(holo_b200_ctx* ctx, uint8_t fused_act, uint8_t dtype, c
 }
 
 int32_t holo_launch_matmul(holo_b200_ctx* ctx, const void* a, const void* b, void* out, uint32_t m, uint32_t k, uint32_t n,
-                           uint8_t dtype, uint8_t fused_act, const void* residual) {
+                           uint8_t dtype, uint8_t fused_act, const void* residual, bool b_constant) {
     HoloMatmulSeg sg = {out, residual, n, fused_act};
+    sg.b_constant = b_constant ? 1 : 0;
     return holo_launch_matmul_multi(ctx, a, b, m, k, n, dtype, &sg, 1);
 }
 
@@ -1040,11 +1149,32 @@ int32_t holo_launch_matmul_add_activation(holo_b200_ctx* ctx, const void* a, con
 }
 
 // C[:, segment i] = epilogue_i(A . B[:, segment i]) for 1..3 column segments of one [k, n] B.
+// Whether the segments' head_op requests can ride this product: the tensor-core path with one row tile, K
+// split at least two ways inside a cluster, every segment a whole number of 128-column heads, no gate, no
+// tensor-parallel sum. The session asks before it folds a RotaryEmbedding / QuantizeRowsI8 into a product.
+bool holo_matmul_head_ops_ok(uint32_t m, uint32_t k, uint32_t n, uint8_t dtype, const HoloMatmulSeg* segs, uint32_t nseg) {
+    if (dtype != HOLO_DTYPE_BF16 && dtype != HOLO_DTYPE_F16) return false;
+    if (m == 0 || m > (uint32_t)BM || k < 2 * BK || (k % 8) != 0 || (n % 128) != 0 || nseg < 1 || nseg > MAX_SEGS) return false;
+    if ((uint64_t)m * n * k < (1ull << 18) || encode_tiled_fn() == nullptr) return false;
+    // the compute-bound kernels have no head epilogue (they need two row tiles, excluded above)
+    for (uint32_t i = 0; i < nseg; ++i) {
+        if ((segs[i].width % 128) != 0 || segs[i].gated || segs[i].all_reduce) return false;
+        if (segs[i].head_op > 3) return false;
+        if (segs[i].head_op == 1 || segs[i].head_op == 2)
+            if (!segs[i].cos || !segs[i].sin || !segs[i].rope_out || (((uintptr_t)segs[i].cos | (uintptr_t)segs[i].sin | (uintptr_t)segs[i].rope_out) & 7u)) return false;
+        if (segs[i].head_op >= 2)
+            if (!segs[i].codes || !segs[i].scales || ((uintptr_t)segs[i].codes & 3u) || ((uintptr_t)segs[i].scales & 3u)) return false;
+        if (segs[i].head_op && ((uintptr_t)segs[i].out & 7u)) return false;
+    }
+    return true;
+}
+
 int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* b, uint32_t m, uint32_t k, uint32_t n,
                                  uint8_t dtype, const HoloMatmulSeg* segs, uint32_t nseg) {
     if (nseg < 1 || nseg > MAX_SEGS) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul segment count %u", nseg);
     GemmSeg gs[MAX_SEGS] = {};
     uint32_t col = 0;
+    bool head_ops = false;
     for (uint32_t i = 0; i < nseg; ++i) {
         if (dtype != HOLO_DTYPE_F32) HOLO_TRY(act_table(ctx, segs[i].fused_act, dtype, &gs[i].table));
         gs[i].out = (uint16_t*)segs[i].out;
@@ -1053,7 +1183,16 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
         col += segs[i].width;
         gs[i].col_end = col;
         if (i + 1 < nseg && (col % 32) != 0) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul segment boundary %u is not a multiple of 32", col);
+        gs[i].head_op = segs[i].head_op;
+        gs[i].cos = (const uint16_t*)segs[i].cos;
+        gs[i].sin = (const uint16_t*)segs[i].sin;
+        gs[i].rope_out = (uint16_t*)segs[i].rope_out;
+        gs[i].codes = segs[i].codes;
+        gs[i].scales = segs[i].scales;
+        head_ops |= segs[i].head_op != 0;
     }
+    if (head_ops && !holo_matmul_head_ops_ok(m, k, n, dtype, segs, nseg))
+        return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul head epilogue needs m <= 128, k >= 128 and 128-column segments");
     const bool gated = segs[0].gated != 0;
     if (gated) {
         if (nseg != 1 || (segs[0].width % 64) != 0 || dtype == HOLO_DTYPE_F32)
@@ -1214,6 +1353,15 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
         if (splits > kblocks / 8) splits = kblocks / 8 ? kblocks / 8 : 1;
     }
     if (const char* e = getenv("HOLO_GEMM_SPLITS")) splits = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : 1;
+    if (head_ops) {
+        // the per-head epilogue lives in the cluster reduction of 128-wide tiles (one head per tile)
+        if (bn != 128) {
+            bn = 128;
+            splits = (240 + tiles128 - 1) / tiles128;
+            if (splits > kblocks / 8) splits = kblocks / 8 ? kblocks / 8 : 1;
+        }
+        if (splits < 2) splits = 2;
+    }
     if (splits > kblocks) splits = kblocks;
     if (splits > 8) splits = 8;  // one cluster (portable size) per output tile
     if (mtiles > 65535 || splits > 65535) return holo_fail(HOLO_ERR_UNSUPPORTED_OP, "unsupported op: matmul grid too large");
@@ -1261,6 +1409,8 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     p.box_m = m < (uint32_t)BM ? m : (uint32_t)BM;
     p.dtype = dtype;
     p.gated = gated ? 1u : 0u;
+    p.head_ops = head_ops ? 1u : 0u;
+    p.b_constant = segs[0].b_constant && !getenv("HOLO_GEMM_NO_EARLY_B") ? 1u : 0u;
     CUtensorMap ma, mb;
     HOLO_TRY(make_map_2d(&ma, a, k, m, BK, p.box_m));
     HOLO_TRY(make_map_2d(&mb, b, n, k, 64, BK));

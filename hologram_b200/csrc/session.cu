@@ -312,6 +312,28 @@ int32_t build_merged_weights(holo_b200_session* s) {
     return HOLO_OK;
 }
 
+int32_t resolve_head_op(holo_b200_session* s, const MergedMatmul& g, uint32_t t, HoloMatmulSeg* seg) {
+    seg->head_op = g.head_op[t];
+    if (!g.head_op[t]) return HOLO_OK;
+    const uint64_t count = (uint64_t)g.m * g.width[t];
+    uint8_t* ptr;
+    if (g.head_op[t] != 3) {
+        HOLO_TRY(holo_resolve(s->ws, g.cos[t], count * 2, &ptr, nullptr));
+        seg->cos = ptr;
+        HOLO_TRY(holo_resolve(s->ws, g.sin[t], count * 2, &ptr, nullptr));
+        seg->sin = ptr;
+        HOLO_TRY(holo_resolve(s->ws, g.rope_out[t], count * 2, &ptr, nullptr));
+        seg->rope_out = ptr;
+    }
+    if (g.head_op[t] >= 2) {
+        HOLO_TRY(holo_resolve(s->ws, g.codes[t], count, &ptr, nullptr));
+        seg->codes = (int8_t*)ptr;
+        HOLO_TRY(holo_resolve(s->ws, g.scales[t], count / 128 * 4, &ptr, nullptr));
+        seg->scales = (float*)ptr;
+    }
+    return HOLO_OK;
+}
+
 int32_t run_merged(holo_b200_session* s, const MergedMatmul& g) {
     uint8_t* a;
     HOLO_TRY(holo_resolve(s->ws, g.a, (uint64_t)g.m * g.k * 2, &a, nullptr));
@@ -324,6 +346,7 @@ int32_t run_merged(holo_b200_session* s, const MergedMatmul& g) {
         segs[0].width = g.width[0];
         segs[0].fused_act = g.act[0];
         segs[0].gated = 1;
+        segs[0].b_constant = 1;
         return holo_launch_matmul_multi(s->ctx, a, g.b_concat, g.m, g.k, g.n, HOLO_DTYPE_BF16, segs, 1);
     }
     for (uint32_t t = 0; t < g.nseg; ++t) {
@@ -333,8 +356,86 @@ int32_t run_merged(holo_b200_session* s, const MergedMatmul& g) {
         segs[t].residual = nullptr;
         segs[t].width = g.width[t];
         segs[t].fused_act = g.act[t];
+        HOLO_TRY(resolve_head_op(s, g, t, &segs[t]));
     }
+    segs[0].b_constant = 1;   // the concatenated weights are the session's own copy
     return holo_launch_matmul_multi(s->ctx, a, g.b_concat, g.m, g.k, g.n, HOLO_DTYPE_BF16, segs, g.nseg);
+}
+
+// The per-head calls that directly follow a merged product and read one of its segments (the RoPE of q, the
+// RoPE + quantize of k, the quantize of v in a decoder layer) move into the product's epilogue: the warp that
+// stores a head's 128 values applies the call's arithmetic to the stored values in registers. The calls'
+// results are bit-for-bit those of the separate launches, which disappear.
+void fuse_head_ops(holo_b200_session* s) {
+    if (getenv("HOLO_SESSION_NO_HEAD_FUSE")) return;
+    std::vector<SessionNode> out;
+    for (size_t i = 0; i < s->nodes.size(); ++i) {
+        out.push_back(s->nodes[i]);
+        if (s->nodes[i].merged < 0) continue;
+        MergedMatmul& g = s->merged[s->nodes[i].merged];
+        if (g.gated || g.m > 128) continue;
+        uint32_t absorbed = 0;
+        size_t j = i + 1;
+        for (; j < s->nodes.size(); ++j) {
+            const SessionNode& nx = s->nodes[j];
+            if (nx.merged >= 0 || nx.batch >= 0 || nx.reduce_add || nx.matmul_reduce_add) break;
+            const HoloKernelCall& c = nx.call;
+            HoloBufferRef x, cs = {HOLO_NO_SLOT, 0, 0}, sn = cs, ro = cs, codes = cs, scales = cs;
+            uint8_t op = 0, dtype = 0;
+            uint32_t row_len = 0;
+            uint64_t count = 0;
+            if (c.kind == HOLO_K_ROTARY) {
+                op = 1; x = c.u.rope.x; cs = c.u.rope.cos; sn = c.u.rope.sin; ro = c.u.rope.output;
+                row_len = c.u.rope.head_dim; count = c.u.rope.element_count; dtype = c.u.rope.dtype;
+            } else if (c.kind == HOLO_K_ROPE_QUANTIZE_ROWS_I8) {
+                const auto& q = c.u.rope_quantize;
+                op = 2; x = q.x; cs = q.cos; sn = q.sin; ro = q.rope_output; codes = q.codes; scales = q.scales;
+                row_len = q.row_len; count = q.rows * q.row_len; dtype = q.dtype;
+            } else if (c.kind == HOLO_K_QUANTIZE_ROWS_I8) {
+                const auto& q = c.u.quantize_rows_i8;
+                op = 3; x = q.input; codes = q.codes; scales = q.scales;
+                row_len = q.row_len; count = q.rows * q.row_len; dtype = q.dtype;
+            } else {
+                break;
+            }
+            int t = -1;
+            for (uint32_t u = 0; u < g.nseg; ++u)
+                if (same_range(x, g.out[u]) && g.head_op[u] == 0) t = (int)u;
+            if (t < 0 || row_len != 128 || dtype != HOLO_DTYPE_BF16 || count != (uint64_t)g.m * g.width[t]) break;
+            // what the call writes is nothing the product reads or writes
+            bool clash = false;
+            for (const HoloBufferRef* w : {&ro, &codes, &scales}) {
+                if (w->slot == HOLO_NO_SLOT) continue;
+                clash |= w->slot == g.a.slot;
+                for (uint32_t u = 0; u < g.nseg; ++u) clash |= w->slot == g.out[u].slot || w->slot == g.cos[u].slot || w->slot == g.sin[u].slot;
+            }
+            // ... and nothing the call itself reads (the separate launches refuse overlapping operands)
+            for (const HoloBufferRef* w : {&ro, &codes, &scales})
+                for (const HoloBufferRef* r : {&x, &cs, &sn, &ro, &codes, &scales})
+                    if (w != r && w->slot != HOLO_NO_SLOT && w->slot == r->slot) clash = true;
+            if (clash) break;
+            // would the product take it? (resolve the operands as a walk would)
+            MergedMatmul trial = g;
+            trial.head_op[t] = op;
+            trial.cos[t] = cs; trial.sin[t] = sn; trial.rope_out[t] = ro; trial.codes[t] = codes; trial.scales[t] = scales;
+            HoloMatmulSeg segs[3];
+            bool ok = true;
+            for (uint32_t u = 0; u < trial.nseg && ok; ++u) {
+                uint8_t* o;
+                ok = holo_resolve(s->ws, trial.out[u], (uint64_t)trial.m * trial.width[u] * 2, &o, nullptr) == HOLO_OK;
+                segs[u].out = o;
+                segs[u].width = trial.width[u];
+                segs[u].fused_act = trial.act[u];
+                ok = ok && resolve_head_op(s, trial, u, &segs[u]) == HOLO_OK;
+            }
+            if (!ok || !holo_matmul_head_ops_ok(trial.m, trial.k, trial.n, HOLO_DTYPE_BF16, segs, trial.nseg)) break;
+            g = trial;
+            ++absorbed;
+        }
+        s->head_fused += absorbed;
+        i = j - 1;   // the absorbed nodes are dropped
+    }
+    s->nodes.swap(out);
 }
 
 // Gated FFN: a merged pair {act(A W0), A W1} whose two results are read only by the Mul that follows
@@ -472,6 +573,7 @@ int32_t run_matmul_reduce_add(holo_b200_session* s, const SessionNode& n) {
     HOLO_TRY(holo_resolve(s->ws, n.sum_out, ob, &dst, nullptr));
     HoloMatmulSeg sg = {dst, res, mm.n, 0};
     sg.all_reduce = 1;
+    sg.b_constant = mm.b.slot < s->ws->slots.size() && s->ws->slots[mm.b.slot].constant;
     return holo_launch_matmul_multi(s->ctx, a, b, mm.m, mm.k, mm.n, mm.dtype, &sg, 1);
 }
 
@@ -667,6 +769,8 @@ int32_t holo_session_load_impl(holo_b200_ctx* ctx, const uint8_t* archive, uint6
                     if (refs.written[r]) written_slots.insert(refs.refs[r]->slot);
         }
         for (const HoloPort& p : s->ar.inputs) written_slots.insert(p.slot);   // inputs are rewritten by the caller
+        for (uint32_t slot : const_slots)
+            if (!written_slots.count(slot)) s->weight_slots.push_back(slot);
         if (s->addressed) {
             // one node per call: merged weights, batched launches and aliased slots all bake
             // device pointers in at load, which the label-keyed pool rebinds per walk
@@ -763,6 +867,10 @@ int32_t holo_session_load_impl(holo_b200_ctx* ctx, const uint8_t* archive, uint6
     }
     if (rc == HOLO_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = holo_fail(HOLO_ERR_INIT, "backend init failed: constant upload");
     if (rc == HOLO_OK) rc = build_merged_weights(s);
+    if (rc == HOLO_OK && !s->addressed)
+        for (uint32_t slot : s->weight_slots)
+            if (slot < s->ws->slots.size() && s->ws->slots[slot].ptr) s->ws->slots[slot].constant = true;
+    if (rc == HOLO_OK && !s->addressed) fuse_head_ops(s);
     if (rc == HOLO_OK && !s->addressed) rc = plan_micro_batches(s);
     if (rc == HOLO_OK && s->addressed) {
         s->ad.pool.reset();
@@ -809,7 +917,7 @@ extern "C" int32_t holo_b200_session_info(holo_b200_session* s, uint32_t* n_call
 extern "C" int32_t holo_b200_session_nodes(holo_b200_session* s, uint32_t* n_nodes, uint32_t* n_merged_calls) {
     if (!s) return holo_fail(HOLO_ERR_INIT, "null session");
     if (n_nodes) *n_nodes = (uint32_t)s->nodes.size();
-    if (n_merged_calls) *n_merged_calls = s->merged_calls + s->batched_calls + 2 * s->reduce_adds;
+    if (n_merged_calls) *n_merged_calls = s->merged_calls + s->batched_calls + s->head_fused + 2 * s->reduce_adds;
     return HOLO_OK;
 }
 

@@ -25,6 +25,14 @@ struct MergedMatmul {
     // weights alternate 64-column blocks of W0 and W1; `gated_out` receives act(A W0) * (A W1)
     bool gated = false;
     HoloBufferRef gated_out = {HOLO_NO_SLOT, 0, 0};
+    // per-head calls that read segment t and follow the product directly, absorbed into its epilogue
+    // (HoloMatmulSeg::head_op): the RotaryEmbedding's cos / sin / output, the quantizer's codes / scales
+    uint8_t head_op[3] = {0, 0, 0};
+    HoloBufferRef cos[3] = {{HOLO_NO_SLOT, 0, 0}, {HOLO_NO_SLOT, 0, 0}, {HOLO_NO_SLOT, 0, 0}};
+    HoloBufferRef sin[3] = {{HOLO_NO_SLOT, 0, 0}, {HOLO_NO_SLOT, 0, 0}, {HOLO_NO_SLOT, 0, 0}};
+    HoloBufferRef rope_out[3] = {{HOLO_NO_SLOT, 0, 0}, {HOLO_NO_SLOT, 0, 0}, {HOLO_NO_SLOT, 0, 0}};
+    HoloBufferRef codes[3] = {{HOLO_NO_SLOT, 0, 0}, {HOLO_NO_SLOT, 0, 0}, {HOLO_NO_SLOT, 0, 0}};
+    HoloBufferRef scales[3] = {{HOLO_NO_SLOT, 0, 0}, {HOLO_NO_SLOT, 0, 0}, {HOLO_NO_SLOT, 0, 0}};
 };
 
 // A run of mutually independent small glue calls executed as one launch.
@@ -85,7 +93,8 @@ struct holo_b200_session {
     std::vector<SessionNode> nodes;     // what a walk actually launches
     std::vector<MergedMatmul> merged;
     std::vector<MicroBatch> batches;
-    uint32_t fused = 0, moved_in_place = 0, merged_calls = 0, batched_calls = 0, reduce_adds = 0, rope_quant = 0;
+    std::vector<uint32_t> weight_slots; // constants that no call writes
+    uint32_t fused = 0, moved_in_place = 0, merged_calls = 0, batched_calls = 0, reduce_adds = 0, rope_quant = 0, head_fused = 0;
     uint64_t device_bytes = 0;
     cudaGraphExec_t graph = nullptr;
     bool addressed = false;

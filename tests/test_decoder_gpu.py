@@ -35,11 +35,11 @@ def test_load_fuses_and_moves_in_place(backend):
     assert kinds.count(kc.K_MATMUL_ACTIVATION) == cfg.n_layers and kinds.count(kc.K_MATMUL_ADD) == 2 * cfg.n_layers
     assert kc.K_SILU not in kinds and kc.K_ADD not in kinds
     # launches per walk: q/k/v and gate/up (shared A) run as 2 merged matmuls per layer, the gate/up
-    # product also absorbing the SwiGLU Mul; the RoPE pair, the quantizer pair and all trailing KV
-    # appends run as batched launches (RoPE q, RoPE+quantize k, quantize v share one)
+    # product also absorbing the SwiGLU Mul; RoPE q, RoPE+quantize k and quantize v ride the q/k/v
+    # product's epilogue; all trailing KV appends run as one batched launch
     L = cfg.n_layers
     assert sess.merged_calls == 6 * L + 3 * L + 4 * L
-    assert sess.n_nodes == 8 * L + 4
+    assert sess.n_nodes == 7 * L + 4
     assert [p.name for p in sess.outputs][0] == "logits"
     # the moved cache shares its buffer with the input port
     assert sess.device_ptr("l0.k_codes")[0] == sess.device_ptr("l0.k_codes_next")[0]
@@ -105,6 +105,37 @@ def test_two_steps_and_graph_replay(backend):
     assert not np.array_equal(outs[0][0], outs[0][1])
 
 
+@pytest.mark.parametrize("full_width", [False, True])
+def test_head_epilogue_is_the_separate_calls_bit_for_bit(backend, full_width, monkeypatch):
+    # RoPE(q), RoPE + quantize(k) and quantize(v) inside the q/k/v product's epilogue against the same
+    # archive loaded with that fusion off (three calls in one batched launch): every output port, the
+    # appended cache rows and scales included, must be identical.
+    cfg = dh.DecoderConfig(n_layers=1) if full_width else small_cfg()
+    position, valid_len = (4096 + 5, 4096) if full_width else (150, 150)
+    if not full_width:
+        # the small q/k/v product would otherwise take another tile width and K split with the head epilogue than
+        # without (the f32 partial sums then group differently): pin both loads to the same tiling
+        monkeypatch.setenv("HOLO_GEMM_BN", "128")
+        monkeypatch.setenv("HOLO_GEMM_SPLITS", "2")
+    outs = []
+    for off in (True, False):
+        if off:
+            monkeypatch.setenv("HOLO_SESSION_NO_HEAD_FUSE", "1")
+        else:
+            monkeypatch.delenv("HOLO_SESSION_NO_HEAD_FUSE")
+        sess, info = load(backend, cfg)
+        assert sess.n_nodes == (8 if off else 7) * cfg.n_layers + 4
+        vals = step_inputs(cfg, info, position, valid_len, seed=21)
+        for name, arr in vals.items():
+            sess.write(name, arr)
+        sess.execute()
+        outs.append({p.name: sess.read(p.name, np.uint8).copy() for p in sess.outputs})
+        sess.close()
+    assert outs[0].keys() == outs[1].keys()
+    for name in outs[0]:
+        assert np.array_equal(outs[0][name], outs[1][name]), name
+
+
 def test_full_width_layer_matches_cpu_interpreter(backend):
     # The benchmarked archive at its real widths (d_model 4096, 32 query / 8 KV heads, SwiGLU 14336,
     # vocabulary 32000, batch 64, 4096 cached positions, int8 KV), one layer deep: every merged q/k/v,
@@ -114,7 +145,7 @@ def test_full_width_layer_matches_cpu_interpreter(backend):
     cfg = dh.DecoderConfig(n_layers=1)
     position, valid_len = 4096 + 17, 4096
     sess, info = load(backend, cfg)
-    assert sess.n_nodes == 8 * cfg.n_layers + 4
+    assert sess.n_nodes == 7 * cfg.n_layers + 4
     vals = step_inputs(cfg, info, position, valid_len, seed=11)
     for name, arr in vals.items():
         sess.write(name, arr)
