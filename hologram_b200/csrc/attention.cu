@@ -12,6 +12,8 @@
 //     triples in a scratch buffer that the last sharer to count in merges (nobody waits).
 //   * a producer warp feeds a 3-stage ring with TMA (cp.async.bulk.tensor, 128B swizzle):
 //     K codes, V codes, K scales, V scales per stage; mbarrier full/empty pairs, bounded waits.
+//     While the ring is full the same warp prepares the query digits of the share's next plane
+//     in a second digit tile, so the consumers change planes without rebuilding them.
 //   * dequantisation is never materialised. q is split into three signed base-256 digits per
 //     head (rows of one m16 tile), so q.k is an exact integer dot on the int8 tensor-core path
 //     (mma.sync m16n8k32 s8) fed straight from the swizzled tile by ldmatrix; the per-row K
@@ -46,8 +48,8 @@ constexpr int FA_THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr int MAXG = 4;           // query heads per kv head served by the tiled kernel
 constexpr uint32_t STAGE_K = 0, STAGE_V = TK * HD, STAGE_SK = 2 * TK * HD, STAGE_SV = 2 * TK * HD + TK * 4;
 constexpr uint32_t STAGE_BYTES = 2 * TK * HD + 2 * TK * 4;  // 33792
-constexpr uint32_t SMEM_Q = STAGES * STAGE_BYTES;            // 16 x 128 B digit tile
-constexpr uint32_t SMEM_MISC = SMEM_Q + 16 * HD;             // cq[4], bad[4], abort, barriers
+constexpr uint32_t SMEM_Q = STAGES * STAGE_BYTES;            // two 16 x 128 B query digit tiles (this segment's, the next one's)
+constexpr uint32_t SMEM_MISC = SMEM_Q + 2 * 16 * HD;         // cq[2][4], bad[2][4], abort, barriers
 constexpr uint32_t SMEM_MERGE = SMEM_MISC + 256;             // 4 warps x 4 heads x (128 + 2) f32
 constexpr uint32_t SMEM_TOTAL = SMEM_MERGE + CONSUMER_WARPS * MAXG * (HD + 2) * 4 + 1024;  // + alignment slack
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
@@ -139,7 +141,23 @@ __device__ __forceinline__ float exp2_guard(float s, float m) {
     // exp(s - m) for a finite or -inf score s against reference m (m may be -inf before the
     // first fold, which must yield +inf so that the fold triggers).
     if (s == -INFINITY) return 0.0f;
-    return exp2f((s - m) * LOG2E);
+    return exp2f(s - m);
+}
+
+// Digits of one query element against its head's exponent: qi = rn(q * 2^(21-ex)), |qi| < 2^22, cut into
+// three signed base-256 digits (L0 most significant). The power of two is built from its bits where it is
+// a normal number (exact, like scalbnf) and by scalbnf otherwise (heads whose largest element is below 2^-105).
+__device__ __forceinline__ void q_digits(float qv, int ex, int& L0, int& L1, int& L2) {
+    const float scaled = ex >= -105 ? qv * __uint_as_float((uint32_t)(127 + 21 - ex) << 23) : scalbnf(qv, 21 - ex);
+    const int qi = __float2int_rn(scaled);
+    L2 = ((qi + 128) & 255) - 128;
+    const int q1 = (qi - L2) >> 8;
+    L1 = ((q1 + 128) & 255) - 128;
+    L0 = (q1 - L1) >> 8;
+}
+__device__ __forceinline__ float q_unit(int ex, float scale_div) {   // 2^(ex-21) / scale_div
+    const float u = ex >= -105 ? __uint_as_float((uint32_t)(127 + ex - 21) << 23) : scalbnf(1.0f, ex - 21);
+    return u / scale_div;
 }
 
 // Ownership of the global tile list: CTA c of n takes tiles [total*c/n, total*(c+1)/n).
@@ -183,7 +201,7 @@ __device__ __forceinline__ void merge_slots(const FaParams& p, uint32_t plane, u
                 const float wm = ml[j][gg].x;
                 if (wm != -INFINITY) {
                     const float nm = fmaxf(M[gg], wm);
-                    const float fo = exp2_guard(M[gg], nm), fn = exp2f((wm - nm) * LOG2E);
+                    const float fo = exp2_guard(M[gg], nm), fn = exp2f(wm - nm);
                     L[gg] = fmaf(ml[j][gg].y, fn, L[gg] * fo);
                     O[gg] = fmaf(ov[j][gg], fn, O[gg] * fo);
                     M[gg] = nm;
@@ -199,7 +217,8 @@ __device__ __forceinline__ void merge_slots(const FaParams& p, uint32_t plane, u
 // plane contributing ceil(visible/128) cache tiles plus one tile for this step's new row. Each
 // CTA owns an equal contiguous share of that list, so its TMA ring never drains between planes
 // and no wave of CTAs ends with idle SMs. A share covers parts of a few planes ("segments"); for
-// each segment the consumers rebuild the query digits, run the tiles, merge their four running
+// each segment the consumers take the query digits (built by themselves for the first segment, by
+// the producer warp for the later ones), run the tiles, merge their four running
 // (max, sum, context) triples, and either write the plane's result (the CTA had the whole plane)
 // or store a partial and count in on the plane's arrival counter; the CTA that counts in last
 // merges the plane's partials. Nobody waits for anybody: a CTA that is not last simply goes on.
@@ -208,49 +227,140 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                            const __grid_constant__ CUtensorMap map_ks, const __grid_constant__ CUtensorMap map_vs,
                            const FaParams p) {
     holo_pdl_trigger();
-    holo_pdl_wait();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* sm = smem_raw + (base - raw);
-    float* s_cq = reinterpret_cast<float*>(sm + SMEM_MISC);            // [4]
-    uint32_t* s_bad = reinterpret_cast<uint32_t*>(sm + SMEM_MISC + 16);  // [4]
+    float* s_cq = reinterpret_cast<float*>(sm + SMEM_MISC);            // [2][4]
+    uint32_t* s_bad = reinterpret_cast<uint32_t*>(sm + SMEM_MISC + 64);  // [2][4]
     volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(sm + SMEM_MISC + 32);
     uint32_t* s_fast = reinterpret_cast<uint32_t*>(sm + SMEM_MISC + 36);
     uint32_t* s_last = reinterpret_cast<uint32_t*>(sm + SMEM_MISC + 192);  // [9]
-    float* s_red = reinterpret_cast<float*>(sm + SMEM_MISC + 64);       // [4 warps][4 heads]
     const uint32_t bar_full = base + SMEM_MISC + 128, bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_q_full = base + SMEM_MISC + 96, bar_q_empty = bar_q_full + 16;   // two digit tiles: filled / read
     float* mo = reinterpret_cast<float*>(sm + SMEM_MERGE);  // [warp][head][HD]
     float* mml = mo + CONSUMER_WARPS * MAXG * HD;            // [warp][head][2]
-
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t G = p.G, nctas = gridDim.x, cta = blockIdx.x;
-    const uint32_t vis_past = min(*p.valid_len, p.past);
-    const uint32_t tiles_past = (vis_past + TK - 1) / TK;
-    const uint32_t T = tiles_past + 1;  // + the tile holding this step's new row
-    const uint32_t total = p.planes * T;
-    const uint32_t g0 = fa_start(cta, total, nctas), g1 = fa_start(cta + 1, total, nctas);
-
-    // an earlier launch gave up on a wait: do not start
-    if (*reinterpret_cast<volatile uint32_t*>(p.status) & 2u) return;
+    // what touches no global memory is done while the previous kernel drains
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, CONSUMER_WARPS);
         }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_q_full + 8 * b, 1);
+            mbar_init(bar_q_empty + 8 * b, CONSUMER_WARPS);
+        }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    holo_pdl_wait();
+
+    const uint32_t G = p.G, nctas = gridDim.x, cta = blockIdx.x;
+    // an earlier launch gave up on a wait: do not start (both loads are in flight together)
+    const uint32_t sticky = *reinterpret_cast<volatile uint32_t*>(p.status);
+    const uint32_t vis_past = min(*p.valid_len, p.past);
+    const uint32_t tiles_past = (vis_past + TK - 1) / TK;
+    const uint32_t T = tiles_past + 1;  // + the tile holding this step's new row
+    const uint32_t total = p.planes * T;
+    const uint32_t g0 = fa_start(cta, total, nctas), g1 = fa_start(cta + 1, total, nctas);
+    if (sticky & 2u) return;
     __syncthreads();
 
     if (warp == CONSUMER_WARPS) {
         // ---------------- producer warp ----------------
         const uint32_t tx_bytes = p.box_rows * HD * 2 + p.box_rows * 4 * 2;
+        // Besides feeding the ring, this warp prepares the query digits of every segment of the share (one
+        // segment = the share's tiles of one plane) in its idle time, one segment ahead of the consumers:
+        // q = (L0*65536 + L1*256 + L2) * 2^(ex-21) per head, one row of the m16 tile per (head, digit): rows g,
+        // 4+g, 8+g hold L0, L1, L2 of head g; rows 12.. are zero. Two digit tiles alternate; a tile is
+        // rewritten only after all four consumer warps have taken the previous content into registers.
+        const uint32_t plane0 = g0 / T;
+        const uint32_t nseg = g1 > g0 ? (g1 - 1) / T - plane0 + 1 : 0;
+        // the first segment's digits are made by the consumer warps themselves (they have nothing else to do yet)
+        uint32_t job = 1, job_head = 0;   // segment whose digits come next; heads of it already written
+        bool dead = false;
+        // the job's query elements (this lane's four per head): requested when the job before it is finished
+        // (the first job's before the first tiles), so a whole segment lies between the request and the use
+        float qj[MAXG][4];
+        auto job_load = [&]() {
+#pragma unroll
+            for (int h = 0; h < MAXG; ++h)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    qj[h][e] = (job < nseg && (uint32_t)h < G) ? holo::load_float(p.q, ((uint64_t)(plane0 + job) * G + h) * HD + 4 * lane + e, p.dtype) : 0.0f;
+        };
+        job_load();
+        auto job_step = [&]() {           // one head of segment `job`; whole warp
+            const uint32_t b = job & 1u, gg = job_head;
+            if (gg == 0 && job >= 2) {
+                bool ok = true;
+                if (lane == 0) ok = mbar_wait(bar_q_empty + 8 * b, ((job >> 1) - 1) & 1, s_abort, p.status);
+                if (!__shfl_sync(0xffffffffu, ok, 0)) { dead = true; return; }
+            }
+            float qv[4];
+            float a = 0.0f;
+            bool isnan_ = false;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                qv[e] = gg == 0 ? qj[0][e] : gg == 1 ? qj[1][e] : gg == 2 ? qj[2][e] : qj[3][e];
+                a = fmaxf(a, fabsf(qv[e]));
+                isnan_ |= qv[e] != qv[e];   // NaN elements are dropped by fmaxf; detect them separately
+            }
+            for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+            const float amax = __any_sync(0xffffffffu, isnan_) ? INFINITY : a;
+            const uint32_t be = (__float_as_uint(amax) >> 23) & 0xffu;
+            uint32_t w0 = 0, w1 = 0, w2 = 0, bad = 0;
+            float cqv = 0.0f;
+            if (be == 255u) {
+                bad = 1;  // inf / NaN in q: the reference yields NaN for the whole head
+            } else if (be != 0u) {
+                const int ex = (int)be - 127;  // amax < 2^(ex+1)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    int L0, L1, L2;
+                    q_digits(qv[e], ex, L0, L1, L2);
+                    w0 |= ((uint32_t)L0 & 0xffu) << (8 * e);
+                    w1 |= ((uint32_t)L1 & 0xffu) << (8 * e);
+                    w2 |= ((uint32_t)L2 & 0xffu) << (8 * e);
+                }
+                cqv = q_unit(ex, p.scale_div);
+            }
+            uint32_t* sq32 = reinterpret_cast<uint32_t*>(sm + SMEM_Q + b * 16 * HD);
+            sq32[(gg * HD) / 4 + lane] = w0;
+            sq32[((4 + gg) * HD) / 4 + lane] = w1;
+            sq32[((8 + gg) * HD) / 4 + lane] = w2;
+            sq32[((12 + gg) * HD) / 4 + lane] = 0;
+            if (lane == 0) {
+                s_cq[b * 4 + gg] = cqv;
+                s_bad[b * 4 + gg] = bad;
+            }
+            if (++job_head == (uint32_t)MAXG) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_q_full + 8 * b);
+                job_head = 0;
+                ++job;
+                job_load();
+            }
+        };
+        asm volatile("bar.sync 2, %0;" ::"n"(FA_THREADS) : "memory");   // the consumers' first query loads are out
         uint32_t it = 0;
-        for (uint32_t g = g0; g < g1; ++g, ++it) {
+        for (uint32_t g = g0; g < g1 && !dead; ++g, ++it) {
             const uint32_t s = it % STAGES, use = it / STAGES;
             const uint32_t plane = g / T, t = g % T;
+            const uint32_t seg = plane - plane0;
+            // the first round of tiles goes out before anything else; from then on a segment's digits are complete
+            // before its first tile is handed over, and the next segment's are worked on while the ring is full
+            if (use > 0 || g + 1 == g1) {
+                while (job <= seg && !dead) job_step();
+            }
             if (use > 0) {
+                while (job < nseg && job <= seg + 1 && !dead) {
+                    uint32_t free_now = 0;
+                    if (lane == 0) free_now = mbar_try_wait(bar_empty + 8 * s, (use - 1) & 1);
+                    if (__shfl_sync(0xffffffffu, free_now, 0)) break;
+                    job_step();
+                }
                 bool ok = true;
                 if (lane == 0) ok = mbar_wait(bar_empty + 8 * s, (use - 1) & 1, s_abort, p.status);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -276,6 +386,7 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);
             }
         }
+        while (job < nseg && !dead) job_step();
         return;
     }
 
@@ -285,6 +396,7 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     const uint32_t g = r & 3;           // head served by this lane
     const uint32_t selA = hi_group ? 0x0051u : 0x0062u;  // digit byte of (x, y): L1 = byte 1, L0 = byte 2
     const uint32_t selB = hi_group ? 0x0073u : 0x0040u;  // zero byte 3, or L2 = byte 0
+    const float digit_w = hi_group ? 256.0f : 65536.0f;  // weight of the group's first digit row against its second
     int acc[8][2][4];
     float of[32];
     float m_ref, l_sum, sref, inv_sref;
@@ -318,6 +430,30 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     bool aborted = false;
     uint32_t gt = g0;
     uint32_t npend = 0, pend_plane[2], pend_first[2], pend_last[2], pend_sharers[2], pend_before[2];  // thread 0 only
+    // thread 0: a partial that has been stored but not yet counted in on its plane (see below)
+    bool pub_wait = false;
+    uint32_t pub_plane = 0, pub_first = 0, pub_last = 0, pub_sharers = 0;
+    auto count_in = [&]() {
+        __threadfence();   // release: the CTA's stores were ordered before this thread by the barrier after them
+        if (npend < 2) {
+            // the count comes back while the next segment streams; it is read at the end
+            pend_before[npend] = atomicAdd(p.arrivals + pub_plane, 1u);
+            pend_plane[npend] = pub_plane;
+            pend_first[npend] = pub_first;
+            pend_last[npend] = pub_last;
+            pend_sharers[npend] = pub_sharers;
+            ++npend;
+        }
+        pub_wait = false;
+    };
+    uint32_t seg_no = 0, bad_heads = 0;
+    // The first plane's query is requested before the producer asks for its first tiles: behind those 100 KB per
+    // CTA the few hundred bytes would wait for microseconds.
+    float q_first[MAXG];
+#pragma unroll
+    for (int gg = 0; gg < MAXG; ++gg)
+        q_first[gg] = (g0 < g1 && (uint32_t)gg < G) ? holo::load_float(p.q, ((uint64_t)(g0 / T) * G + gg) * HD + tid, p.dtype) : 0.0f;
+    asm volatile("bar.arrive 2, %0;" ::"n"(FA_THREADS) : "memory");
     while (gt < g1) {
         const uint32_t plane = gt / T;
         const uint32_t seg_end = min(g1, (plane + 1) * T);
@@ -326,51 +462,46 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         uint32_t probe = 0;
         if (tid == 0 && fa_owner(plane * T, total, nctas) == cta && fa_owner(plane * T + T - 1, total, nctas) != cta)
             asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(probe) : "l"(p.arrivals + plane) : "memory");
-        // ---- query digits of this plane: q = (L0*65536 + L1*256 + L2) * 2^(ex-21), one row of
-        // the m16 tile per (head, digit): rows g, 4+g, 8+g hold L0, L1, L2 of head g; rows 12.. zero.
+        // ---- query digits of this plane, prepared by the producer warp: A fragments, scale, bad-head flags ----
         {
-            int8_t* sq = reinterpret_cast<int8_t*>(sm + SMEM_Q);
-            float qv[MAXG];
+            const uint32_t qb = seg_no & 1u;
+            if (seg_no == 0) {
+                // the share's first plane: all four warps build the digit tile (thread = element of the head)
+                int8_t* sq = reinterpret_cast<int8_t*>(sm + SMEM_Q);
+                float* s_red = mo;   // the merge area is idle until the segment ends
+                float qv[MAXG];
 #pragma unroll
-            for (int gg = 0; gg < MAXG; ++gg) {
-                qv[gg] = (uint32_t)gg < G ? holo::load_float(p.q, ((uint64_t)plane * G + gg) * HD + tid, p.dtype) : 0.0f;
-                float a = fabsf(qv[gg]);
-                for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-                // NaN elements are dropped by fmaxf; detect them separately
-                uint32_t nanbit = __any_sync(0xffffffffu, qv[gg] != qv[gg]);
-                if (lane == 0) s_red[warp * 4 + gg] = nanbit ? INFINITY : a;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+                for (int gg = 0; gg < MAXG; ++gg) {
+                    qv[gg] = q_first[gg];
+                    float a = fabsf(qv[gg]);
+                    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+                    const uint32_t nanbit = __any_sync(0xffffffffu, qv[gg] != qv[gg]);
+                    if (lane == 0) s_red[warp * 4 + gg] = nanbit ? INFINITY : a;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
 #pragma unroll
-            for (int gg = 0; gg < MAXG; ++gg) {
-                float amax = fmaxf(fmaxf(s_red[gg], s_red[4 + gg]), fmaxf(s_red[8 + gg], s_red[12 + gg]));
-                uint32_t be = (__float_as_uint(amax) >> 23) & 0xffu;
-                int L0 = 0, L1 = 0, L2 = 0;
-                float cqv = 0.0f;
-                uint32_t bad = 0;
-                if (be == 255u) {
-                    bad = 1;  // inf / NaN in q: the reference yields NaN for the whole head
-                } else if (be != 0u) {
-                    int ex = (int)be - 127;  // amax < 2^(ex+1)
-                    int qi = __float2int_rn(scalbnf(qv[gg], 21 - ex));  // |qi| < 2^22 keeps L0 within int8
-                    L2 = ((qi + 128) & 255) - 128;
-                    int q1 = (qi - L2) >> 8;
-                    L1 = ((q1 + 128) & 255) - 128;
-                    L0 = (q1 - L1) >> 8;
-                    cqv = scalbnf(1.0f, ex - 21) / p.scale_div;
+                for (int gg = 0; gg < MAXG; ++gg) {
+                    const float amax = fmaxf(fmaxf(s_red[gg], s_red[4 + gg]), fmaxf(s_red[8 + gg], s_red[12 + gg]));
+                    const uint32_t be = (__float_as_uint(amax) >> 23) & 0xffu;
+                    int L0 = 0, L1 = 0, L2 = 0;
+                    if (be != 255u && be != 0u) q_digits(qv[gg], (int)be - 127, L0, L1, L2);
+                    sq[gg * HD + tid] = (int8_t)L0;
+                    sq[(4 + gg) * HD + tid] = (int8_t)L1;
+                    sq[(8 + gg) * HD + tid] = (int8_t)L2;
+                    sq[(12 + gg) * HD + tid] = 0;
+                    if (tid == 0) {
+                        s_cq[gg] = (be != 255u && be != 0u) ? q_unit((int)be - 127, p.scale_div) : 0.0f;
+                        s_bad[gg] = be == 255u;   // inf / NaN in q: the reference yields NaN for the whole head
+                    }
                 }
-                sq[(gg)*HD + tid] = (int8_t)L0;
-                sq[(4 + gg) * HD + tid] = (int8_t)L1;
-                sq[(8 + gg) * HD + tid] = (int8_t)L2;
-                sq[(12 + gg) * HD + tid] = 0;
-                if (tid == 0) {
-                    s_cq[gg] = cqv;
-                    s_bad[gg] = bad;
-                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (tid == 0) mbar_arrive(bar_q_full);   // keeps the tile's phases in step with the producer's
+            } else if (!aborted && !mbar_wait(bar_q_full + 8 * qb, (seg_no >> 1) & 1, s_abort, p.status)) {
+                aborted = true;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            cq = s_cq[g];
-            const uint32_t* sq32 = reinterpret_cast<const uint32_t*>(sm + SMEM_Q);
+            cq = s_cq[qb * 4 + g] * LOG2E;   // scores, running maxima and the stored partial maxima are in log2 units
+            bad_heads = s_bad[qb * 4] | (s_bad[qb * 4 + 1] << 1) | (s_bad[qb * 4 + 2] << 2) | (s_bad[qb * 4 + 3] << 3);
+            const uint32_t* sq32 = reinterpret_cast<const uint32_t*>(sm + SMEM_Q + qb * 16 * HD);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
                 qa[ks][0] = sq32[(r * HD + 32 * ks + 4 * i) >> 2];
@@ -378,6 +509,9 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 qa[ks][2] = sq32[(r * HD + 32 * ks + 16 + 4 * i) >> 2];
                 qa[ks][3] = sq32[((r + 8) * HD + 32 * ks + 16 + 4 * i) >> 2];
             }
+            __syncwarp();
+            if (lane == 0 && !aborted) mbar_arrive(bar_q_empty + 8 * qb);   // the tile may be rewritten
+            ++seg_no;
         }
 #pragma unroll
         for (int c = 0; c < 8; ++c)
@@ -421,18 +555,27 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 }
                 const float* sk = reinterpret_cast<const float*>(sp + STAGE_SK);
                 const float* sv = reinterpret_cast<const float*>(sp + STAGE_SV);
-                float sc[8], svv[8];
+                // Both lane groups hold digit sums of the same 8 (head, key) scores (the low group L0 and L2, the
+                // high group L1). Each group finishes four of them: the low group those of key blocks 0 and 1, the
+                // high group those of blocks 2 and 3; it gets the partner's part of its own four by one shuffle
+                // each and hands the finished weights back the same way. Everything in between (scales, exp,
+                // digit scaling) then runs once per score instead of once per group.
+                float sc[4], svv[4];
                 float mt = -INFINITY;
     #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    const uint32_t key = row0 + 8 * nt + 2 * i;
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    const int nt_lo = h2, nt_hi = 2 + h2;
+                    const uint32_t key = row0 + 8 * (hi_group ? nt_hi : nt_lo) + 2 * i;
                     const float2 k2 = *reinterpret_cast<const float2*>(sk + key);
                     const float2 v2 = *reinterpret_cast<const float2*>(sv + key);
     #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        float part = hi_group ? __int2float_rn(sacc[nt][e]) * 256.0f
-                                              : fmaf(__int2float_rn(sacc[nt][e]), 65536.0f, __int2float_rn(sacc[nt][2 + e]));
-                        float full = part + __shfl_xor_sync(0xffffffffu, part, 16);
+                        // this lane's digits of the low group's score and of the high group's score (the high group's
+                        // second row is the zero row, so one formula with the group's digit weight serves both)
+                        const float for_lo = fmaf(__int2float_rn(sacc[nt_lo][e]), digit_w, __int2float_rn(sacc[nt_lo][2 + e]));
+                        const float for_hi = fmaf(__int2float_rn(sacc[nt_hi][e]), digit_w, __int2float_rn(sacc[nt_hi][2 + e]));
+                        const float theirs = __shfl_xor_sync(0xffffffffu, hi_group ? for_lo : for_hi, 16);
+                        const float full = (hi_group ? for_hi : for_lo) + theirs;
                         float kscale = e ? k2.y : k2.x;
                         float sval = full * (kscale * cq);
                         float vscale = e ? v2.y : v2.x;
@@ -440,42 +583,47 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                             sval = -INFINITY;
                             vscale = 0.0f;
                         }
-                        sc[nt * 2 + e] = sval;
-                        svv[nt * 2 + e] = vscale;
+                        sc[h2 * 2 + e] = sval;
+                        svv[h2 * 2 + e] = vscale;
                         mt = fmaxf(mt, sval);
                     }
                 }
-                mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
-                mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
                 // ---- weights relative to the running reference, scaled for digit extraction ----
-                float pe[8], ps[8];
-                float pmax = 0.0f;
+                float pe[4], ps[4];
+                // largest scaled weight, compared as bit patterns: for weights >= 0 that is the float order, and a NaN
+                // or a negative value (a corrupt scale) compares above every finite weight, which forces the fold
+                uint32_t pmax = 0u;
     #pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                    pe[x] = exp2_guard(sc[x], m_ref);
+                for (int x = 0; x < 4; ++x) {
+                    // before the first fold m_ref is -inf and sref 0: whatever comes out here is recomputed below
+                    pe[x] = exp2f(sc[x] - m_ref);
                     ps[x] = pe[x] * svv[x] * sref;
-                    pmax = fmaxf(pmax, ps[x] != ps[x] ? INFINITY : ps[x]);
+                    pmax = max(pmax, __float_as_uint(ps[x]));
                 }
-                pmax = fmaxf(pmax, __shfl_xor_sync(0xffffffffu, pmax, 1));
-                pmax = fmaxf(pmax, __shfl_xor_sync(0xffffffffu, pmax, 2));
-                const bool need = !(pmax < 16777215.0f) || mt > m_ref + 60.0f || sref == 0.0f || since_fold >= 1024;
+                // each lane judges its own four scores; the maxima over a head's lanes are only formed when some lane
+                // of the warp asks for a new reference (rare), which keeps six dependent shuffles off every tile
+                const bool need = !(pmax < 0x4B7FFFFFu) || mt > m_ref + 86.0f || sref == 0.0f || since_fold >= 1024;
                 if (__any_sync(0xffffffffu, need)) {
                     fold();
+                    mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
+                    mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
+                    mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
                     const float m_new = fmaxf(m_ref, mt);
-                    const float alpha = m_ref == -INFINITY ? 0.0f : exp2f((m_ref - m_new) * LOG2E);
+                    const float alpha = m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_new);
     #pragma unroll
                     for (int x = 0; x < 32; ++x) of[x] *= alpha;
                     l_sum *= alpha;
                     m_ref = m_new;
                     float pm = 0.0f;
     #pragma unroll
-                    for (int x = 0; x < 8; ++x) {
+                    for (int x = 0; x < 4; ++x) {
                         pe[x] = exp2_guard(sc[x], m_ref);
                         float w = pe[x] * svv[x];
                         pm = fmaxf(pm, w);
                     }
                     pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, 1));
                     pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, 2));
+                    pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, 16));
                     int sexp = 0;
                     const uint32_t pbe = (__float_as_uint(pm) >> 23) & 0xffu;
                     if (pbe != 0u && pbe != 255u) sexp = 15 - ((int)pbe - 127);
@@ -483,13 +631,16 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                     sref = __uint_as_float((uint32_t)(127 + sexp) << 23);
                     inv_sref = __uint_as_float((uint32_t)(127 - sexp) << 23);
     #pragma unroll
-                    for (int x = 0; x < 8; ++x) ps[x] = fminf(pe[x] * svv[x] * sref, 16777215.0f);
+                    for (int x = 0; x < 4; ++x) ps[x] = fminf(pe[x] * svv[x] * sref, 16777215.0f);
                 }
                 uint32_t pi[8];
     #pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                    l_sum += pe[x];
-                    pi[x] = __float2uint_rn(fmaxf(ps[x], 0.0f));
+                for (int x = 0; x < 4; ++x) {
+                    l_sum += pe[x];   // this group's four keys; the groups' sums meet when the segment ends
+                    const uint32_t mine = __float2uint_rn(ps[x]);   // saturating: a negative or NaN weight (a corrupt scale) counts as 0
+                    const uint32_t theirs = __shfl_xor_sync(0xffffffffu, mine, 16);
+                    pi[x] = hi_group ? theirs : mine;
+                    pi[4 + x] = hi_group ? mine : theirs;
                 }
                 uint32_t pa[4];
                 pa[0] = __byte_perm(__byte_perm(pi[0], pi[1], selA), __byte_perm(pi[2], pi[3], selA), 0x5410);
@@ -508,11 +659,13 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             }
             __syncwarp();
             if (lane == 0 && !aborted) mbar_arrive(bar_empty + 8 * s);
+            if (tid == 0 && pub_wait) count_in();
         }
         fold();
         // ---- merge the four warps' triples; finish the plane or publish this segment's partial ----
         l_sum += __shfl_xor_sync(0xffffffffu, l_sum, 1);
         l_sum += __shfl_xor_sync(0xffffffffu, l_sum, 2);
+        l_sum += __shfl_xor_sync(0xffffffffu, l_sum, 16);
 #pragma unroll
         for (int x = 0; x < 32; ++x) of[x] += __shfl_xor_sync(0xffffffffu, of[x], 16);
         if (!hi_group) {
@@ -556,12 +709,12 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                     for (int w = 0; w < CONSUMER_WARPS; ++w) {
                         float wm = mml[(w * MAXG + gg) * 2];
                         if (wm != -INFINITY) {
-                            float f = exp2f((wm - M[gg]) * LOG2E);
+                            float f = exp2f(wm - M[gg]);
                             L[gg] = fmaf(mml[(w * MAXG + gg) * 2 + 1], f, L[gg]);
                             O[gg] = fmaf(mo[(w * MAXG + gg) * HD + c], f, O[gg]);
                         }
                     }
-                    if (s_bad[gg]) { O[gg] = NAN; L[gg] = 1.0f; M[gg] = 0.0f; }
+                    if ((bad_heads >> gg) & 1u) { O[gg] = NAN; L[gg] = 1.0f; M[gg] = 0.0f; }
                 }
             }
             if (sharers == 1) {
@@ -583,24 +736,23 @@ decode_attention_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                         p.part_o[pidx * HD + c] = O[gg];
                         if (c == 0) *reinterpret_cast<float2*>(p.part_ml + pidx * 2) = make_float2(M[gg], L[gg]);
                     }
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (tid == 0 && npend < 2) {
-                    // the count comes back while the next segment streams; it is read at the end
-                    pend_before[npend] = atomicAdd(p.arrivals + plane, 1u);
-                    pend_plane[npend] = plane;
-                    pend_first[npend] = first;
-                    pend_last[npend] = last;
-                    pend_sharers[npend] = sharers;
-                    ++npend;
+                // Counting in needs the partial to be visible first. The barrier that ends the segment orders every
+                // thread's stores before thread 0; thread 0 then fences and counts in after the next segment's first
+                // tile (or before the final merges), when the stores have long drained and the fence costs nothing.
+                if (tid == 0) {
+                    pub_wait = true;
+                    pub_plane = plane;
+                    pub_first = first;
+                    pub_last = last;
+                    pub_sharers = sharers;
                 }
             }
         }
-        // the merge area, the digit tile and s_red are rewritten by the next segment
+        // the merge area is rewritten by the next segment
         asm volatile("bar.sync 1, 128;" ::: "memory");
     }
-
     // ---- a CTA that counted in last on a plane merges that plane's partials ----
+    if (tid == 0 && pub_wait) count_in();
     if (tid == 0) {
         s_last[0] = s_last[1] = 0;
         s_last[2] = npend;
