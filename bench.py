@@ -30,14 +30,54 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML read-only queries from a thread
+    every few milliseconds (nvidia-smi in a loop, far coarser, only if NVML cannot be loaded)."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, uuid=None):
+        self.index, self.uuid, self.rows, self.proc = index, uuid, [], None
+        self.nvml, self.handle, self.thread, self.stop_flag = None, None, None, False
+        self.sm, self.mask, self.sm_max = [], 0, None
+
+    def _nvml_open(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = None
+            if self.uuid:
+                for cand in (self.uuid, "GPU-" + self.uuid):
+                    try:
+                        h = pynvml.nvmlDeviceGetHandleByUUID(cand.encode() if isinstance(cand, str) else cand)
+                        break
+                    except Exception:
+                        h = None
+            if h is None:
+                h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            self.nvml, self.handle = pynvml, h
+            return True
+        except Exception:
+            self.nvml = None
+            return False
+
+    def _poll(self):
+        n, h = self.nvml, self.handle
+        reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop_flag:
+            try:
+                self.sm.append(float(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)))
+                self.mask |= int(reasons(h))
+            except Exception:
+                pass
+            time.sleep(0.004)
 
     def start(self):
+        if self._nvml_open():
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -51,6 +91,12 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        if self.thread:
+            self.stop_flag = True
+            self.thread.join(timeout=1.0)
+            reasons = sorted(name for bit, name in self.REASON_BITS.items() if self.mask & bit)
+            return {"sm_mhz": float(np.median(self.sm)) if self.sm else None, "sm_max_mhz": self.sm_max,
+                    "reasons": reasons, "samples": len(self.sm), "source": "nvml"}
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -60,7 +106,7 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower().startswith("active")})
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+                "reasons": reasons, "samples": len(sm), "source": "nvidia-smi"}
 
 
 # ------------------------------------------------------------------------------------------
@@ -640,15 +686,27 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sub", action="store_true", help="decoder workload: skip the LUT and attention sub-results")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="profiling aid, one GPU: run rank 0's shard of an N-way tensor-parallel attention / decoder without the "
+                         "exchange between ranks (the kernels then have the shapes of an N-GPU run); not a benchmark line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    # Libraries loaded below may write to stdout (NCCL prints its version there): stdout carries the one JSON
+    # line and nothing else, everything else goes to stderr.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        os.write(json_fd, (json.dumps(obj) + "\n").encode())
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
     if args.impl == "reference":
-        return main_reference(args, rank, world)
+        return main_reference(args, rank, world, emit)
 
     import torch
     import torch.distributed as dist
@@ -667,7 +725,8 @@ def main():
         dist.broadcast_object_list(uid, src=0)
         be.init_tp(uid[0], rank, world)
     fn = WORKLOADS[args.workload]
-    wl = fn(be, torch, rank, args, world) if args.workload in ("attention", "decoder") else fn(be, torch, rank, args)
+    shard_world = args.shard_of if (args.shard_of > 1 and world == 1) else world
+    wl = fn(be, torch, rank, args, shard_world) if args.workload in ("attention", "decoder") else fn(be, torch, rank, args)
 
     def barrier():
         torch.cuda.synchronize()
@@ -709,7 +768,11 @@ def main():
     def measure(w, steps, warmup):
         """One workload: device-resident timing over `steps` x repeats steps with its own clock sample."""
         reps = repeats_for(w["run_device"], steps, warmup)
-        smp = ClockSampler(local_rank)
+        try:
+            uuid = str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+        except Exception:
+            uuid = None
+        smp = ClockSampler(local_rank, uuid)
         if rank == 0:
             smp.start()
         total_ms, n_launch = timed(w["run_device"], steps * reps, 3)
@@ -787,12 +850,14 @@ def main():
     if rank == 0:
         if sub:
             line["sub"] = sub
-        print(json.dumps(line), flush=True)
+        if shard_world != world:
+            line["profiling_only"] = f"rank 0's shard of a {shard_world}-way run on one GPU, no exchange between ranks"
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
-def main_reference(args, rank, world):
+def main_reference(args, rank, world, emit):
     """The reference's CPU implementation of the path (the C restatement, all host threads),
     timed on a bounded sample per step. Rank 0 only."""
     if rank != 0:
@@ -817,7 +882,7 @@ def main_reference(args, rank, world):
         t_layers = [sample.layer_step() for _ in range(max(1, args.steps))]
         t_step = sample.t_step(float(np.mean(t_layers)))
         value = cfg.batch / t_step
-        print(json.dumps({
+        emit({
             "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": len(t_layers), "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16 (int8 KV cache, f32 accumulation)", "data": "synthetic (seeded)",
@@ -828,7 +893,7 @@ def main_reference(args, rank, world):
                              "sample": f"per step: 1 of {cfg.n_layers} layers at full shapes on all host threads (mean {np.mean(t_layers):.2f} s), "
                                        f"the LM head timed once ({sample.t_head:.2f} s); ms_per_step = {cfg.n_layers} x layer + head"},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        }), flush=True)
+        })
         return
     if wlname == "lut":
         n = 16_777_216
@@ -859,13 +924,13 @@ def main_reference(args, rank, world):
     dt = time.perf_counter() - t0
     value = units * frac * args.steps / dt
     cores = os.cpu_count()
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3 / frac, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": dtype, "data": "synthetic (seeded)", "config": cfg,
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }), flush=True)
+    })
 
 
 if __name__ == "__main__":

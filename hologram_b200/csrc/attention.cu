@@ -26,6 +26,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "attention_generic.cuh"
@@ -820,13 +821,26 @@ int32_t make_scales_map(CUtensorMap* map, const void* ptr, uint32_t past, uint32
     return HOLO_OK;
 }
 
-// Grid of the persistent kernel: HOLO_ATTN_MINB CTAs per SM (all co-resident), never more than
-// there are tiles. A plane is then shared by at most nctas / planes + 2 CTAs.
+// Grid of the persistent kernel: at most HOLO_ATTN_MINB CTAs per SM (all co-resident), never more than
+// there are tiles. Shares that line up with the planes are worth a few idle CTA slots: a CTA that holds
+// whole planes neither stores partials nor merges, and one that holds an exact fraction of a plane never
+// changes planes in mid-share. So when the plane count divides evenly into at least three quarters of the
+// slots (k CTAs per plane, or m planes per CTA), that count is taken; measured on B200 at 256 of 296 slots:
+// 101.7 -> 91.6 us for 256 planes x 65 tiles, 59.8 -> 51.7 us for 128 planes x 33 tiles. Otherwise every slot
+// is used and a plane is shared by at most nctas / planes + 2 CTAs.
 uint32_t persistent_ctas(uint32_t tiles_per_plane, uint32_t planes, int sm_count) {
-    uint64_t want = (uint64_t)HOLO_ATTN_MINB * (uint32_t)sm_count;
-    if (const char* env = getenv("HOLO_ATTN_CTAS"))
-        if (atoi(env) > 0) want = (uint64_t)atoi(env);
+    uint64_t slots = (uint64_t)HOLO_ATTN_MINB * (uint32_t)sm_count;
     const uint64_t total = (uint64_t)tiles_per_plane * planes;
+    if (const char* env = getenv("HOLO_ATTN_CTAS"))
+        if (atoi(env) > 0) return (uint32_t)std::min<uint64_t>((uint64_t)atoi(env), total);
+    uint64_t want = slots;
+    if (planes > 0 && planes <= slots) {
+        const uint64_t k = slots / planes;
+        if (planes * k * 4 >= slots * 3 && k <= tiles_per_plane) want = planes * k;
+    } else if (planes > slots) {
+        const uint64_t m = (planes + slots - 1) / slots;
+        if (planes % m == 0 && (planes / m) * 4 >= slots * 3) want = planes / m;
+    }
     return (uint32_t)(want < total ? want : total);
 }
 
