@@ -1340,7 +1340,12 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
             if (const char* e = getenv("HOLO_GEMM_CTA_TARGET")) target = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : target;
             splits = (target + tiles - 1) / tiles;
             if (splits > 8) splits = 8;
-            if (splits > kblocks / 8) splits = kblocks / 8 ? kblocks / 8 : 1;
+            // k-blocks a slice keeps at least. Two: the 1/4 and 1/8 shards of the decoder's row-parallel products (K = 1024,
+            // 512) then still spread over 64-128 CTAs; with eight they ran on 32 (measured on one GPU over a rank's shard of
+            // the decoder step: 0.724 -> 0.648 ms at 1/8, 0.901 -> 0.822 ms at 1/4; one k-block per slice was no better)
+            uint32_t min_kb = 2;
+            if (const char* e = getenv("HOLO_GEMM_MIN_KB")) min_kb = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : min_kb;
+            if (splits > kblocks / min_kb) splits = kblocks / min_kb ? kblocks / min_kb : 1;
         }
     } else if (tiles128 < slots / 2) {
         bn = tiles64 <= slots ? 64 : 128;
