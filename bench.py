@@ -175,7 +175,7 @@ def workload_lut(be, torch, rank, args):
         "units_per_step": n * 4 / 1e9,  # GB of algorithmic traffic per step
         "launches_per_step": 1,
         "roofline": {"bound": "hbm", "bytes_per_launch": n * 4, "kernel": "lut_stream_kernel",
-                     "traffic": 34_192_896, "traffic_note": "ncu, profiles/lut_stream_kernel_gelu_bf16_16Mi.md: 33.70 MB read + 0.49 MB written inside the kernel window (the output is still dirty in L2)"},
+                     "traffic": 34_007_808, "traffic_note": "ncu, profiles/lut_stream_kernel_gelu_bf16_16Mi.md: 33.70 MB read + 0.31 MB written inside the kernel window (the output is still dirty in L2)"},
         "h2d": n * 2, "d2h": n * 2,
         "cpu_baseline": cpu_baseline,
         "config": {"workload": LUT_WORKLOAD, "l2": "8 rotated buffer pairs (512 MiB) > 126 MB L2"},
@@ -249,7 +249,7 @@ def workload_attention(be, torch, rank, args, world=1):
         "units_per_step": algo / 1e9,
         "launches_per_step": 1,
         "roofline": {"bound": "hbm", "bytes_per_launch": algo, "kernel": "decode_attention_q8_kernel",
-                     "traffic": 560_289_536 // world, "traffic_note": "ncu at N=1, profiles/decode_attention_q8_kernel_b32_h32_kv8_L8192.md: 554.85 MB read + 5.44 MB written"},
+                     "traffic": 556_297_984 // world, "traffic_note": "ncu at N=1 of the same number of key rows (the decoder's call), profiles/decode_attention_q8_kernel_b32_h32_kv8_L8192.md: 554.48 MB read + 1.81 MB written; divided by N for a shard (traffic is proportional to the rows)"},
         "h2d": sum(t.numel() * t.element_size() for t in tensors[:-1]), "d2h": out.numel() * 2,
         "cpu_baseline": cpu_baseline,
         "config": {"workload": attention_workload_string(b, h * world, kv * world, d, past), "parallelism": f"kv-head shards x{world}",
@@ -340,7 +340,7 @@ def workload_decoder(be, torch, rank, args, world=1):
         sess.execute()
         _check(lib.holo_b200_workspace_download(sess.workspace._h, kc.rb(sess.port("logits").slot), ctypes.c_void_p(logits_host.data_ptr()), B * info["vocab"] * 2))
 
-    # the dominant kernel of the step (44 % of the ncu launch list): one layer's int8-KV attention
+    # the dominant kernel of the step (47 % of the ncu launch list): one layer's int8-KV attention
     attn_calls = [sess.call(i) for i in range(sess.n_calls) if sess.call(i).kind == kc.K_DECODE_ATTENTION_VALID_Q8]
     attn_bytes = 2 * rows * (hd + 4) + 2 * B * H * hd * 2 + 2 * B * KV * (hd + 4)
 
@@ -362,9 +362,9 @@ def workload_decoder(be, torch, rank, args, world=1):
         "units_per_step": B / world,   # the batch is replicated over the TP group: count it once
         "launches_per_step": sess.n_calls,
         "roofline": {"bound": "hbm", "bytes_per_launch": attn_bytes, "kernel": "decode_attention_q8_kernel, one layer",
-                     "run": run_dominant, "traffic": (560_289_536 // world) if (B, L) == (64, 4096) else None,
-                     "traffic_note": "ncu capture of the same kernel on the same number of key rows (config[3]: 32 x 8 x 8192 = 64 x 8 x 4096 rows), "
-                                     "profiles/decode_attention_q8_kernel_b32_h32_kv8_L8192.md",
+                     "run": run_dominant, "traffic": (556_297_984 // world) if (B, L) == (64, 4096) else None,
+                     "traffic_note": "ncu capture of this very call in a one-layer archive at N=1 (554.48 MB read + 1.81 MB written), "
+                                     "profiles/decode_attention_q8_kernel_b32_h32_kv8_L8192.md; divided by N for a shard (traffic is proportional to the rows)",
                      "step_bytes": algo},
         "h2d": sum(v.numel() for v in pinned.values()), "d2h": B * info["vocab"] * 2,
         "cpu_baseline": cpu_baseline,
@@ -511,9 +511,9 @@ def workload_matmul(be, torch, rank, args, skinny=False):
         "units_per_step": nbytes / 1e9 if skinny else flops / 1e12,
         "launches_per_step": 1,
         "roofline": ({"bound": "hbm", "bytes_per_launch": nbytes, "kernel": "matmul_bf16_umma_kernel", "traffic": None} if skinny else
-                     {"bound": "tensor", "flops_per_launch": flops, "kernel": "matmul_bf16_umma_kernel",
-                      "traffic": 82_481_152 if (m, k, n) == (4096, 4096, 4096) else None,
-                      "traffic_note": "ncu, profiles/matmul_bf16_umma_kernel.md: 67.35 MB read + 15.13 MB written inside the kernel window"}),
+                     {"bound": "tensor", "flops_per_launch": flops, "kernel": "matmul_umma_pair_kernel" if (m >= 256 and n >= 256 and -(-m // 256) * -(-n // 256) >= 74) else "matmul_bf16_umma_kernel",
+                      "traffic": 82_627_072 if (m, k, n) == (4096, 4096, 4096) else None,
+                      "traffic_note": "ncu, profiles/matmul_bf16_umma_kernel.md: 69.58 MB read + 13.05 MB written inside the kernel window"}),
         "h2d": 2 * (m * k + k * n), "d2h": 2 * m * n,
         "cpu_baseline": cpu_baseline, "extra": burst,
         "config": {"workload": f"config[2]: bf16 matmul M={m} K={k} N={n}, f32 accumulation, bf16 output, A,B ~ N(0, 1/K)",
