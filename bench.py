@@ -821,6 +821,8 @@ def main():
         }
         if wl["roofline"]["bound"] == "tensor":
             line["roofline"]["frac_of_burst_peak"] = achieved / peaks["bf16_tflops"]
+        else:
+            line["roofline"]["frac_of_nominal_8TBps"] = achieved / 8000.0
         if "step_bytes" in wl["roofline"]:
             sb = wl["roofline"]["step_bytes"] / (per_step_ms / 1e3) / 1e9
             line["step_roofline"] = {"bound": "hbm", "achieved": sb, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": sb / peaks["hbm_gbs"],
