@@ -1331,7 +1331,13 @@ int32_t holo_launch_matmul_multi(holo_b200_ctx* ctx, const void* a, const void* 
     uint32_t splits = 1;
     const uint32_t tiles128 = mtiles * ((n + 127) / 128), tiles64 = mtiles * ((n + 63) / 64);
     if (mtiles == 1 && tiles128 < 200) {
-        if (tiles64 >= (uint32_t)ctx->sm_count) {
+        // 128-wide tiles read 256-byte weight rows instead of 128-byte ones; when two K slices of them still fit one
+        // wave, that beats a 64-wide tile per SM (16 x 4096 x 14336: 26.0 -> 23.3 us)
+        const uint32_t fit128 = tiles128 ? slots / tiles128 : 0;
+        if (tiles64 >= (uint32_t)ctx->sm_count && fit128 >= 2 && kblocks >= 8 && !getenv("HOLO_GEMM_OLD_NARROW")) {
+            bn = 128;
+            splits = 2;   // three slices (288 CTAs in clusters of 3) did not all become resident: 64 x 4096 x 12288 took 32.6 us against 25.3
+        } else if (tiles64 >= (uint32_t)ctx->sm_count) {
             bn = 64;
         } else {
             bn = tiles128 >= 16 ? 128 : 64;
